@@ -1,0 +1,161 @@
+/*
+ * tq_abi.h - C ABI of libtq_b200.so: TurboQuant KV-cache compression and attention over the
+ * compressed cache, as hand-written sm_100a CUDA kernels.
+ *
+ * The reference (alex-rentel/mlx-turboquant v1.0.4) is pure Python on MLX and has no FFI; each
+ * entry point below names the reference function whose device-side work it replaces
+ * (file:line inside that project).
+ *
+ * Conventions
+ *   - Every pointer is a caller-owned DEVICE pointer unless it is marked "host".
+ *   - Every call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = legacy
+ *     default stream) and allocates nothing.
+ *   - Return value: TQ_OK or a negative TQ_ERR_*; tq_last_error() gives the thread-local text.
+ *     Nothing throws, aborts or traps.
+ *   - "rows" are vectors of length d.  Row r of lane o lives at
+ *     base + o*lane_stride + r*row_stride (strides in ELEMENTS of that array; packed arrays
+ *     count strides in rows of their own byte width).
+ *   - Packed byte layouts are the reference's (packing.py:9-208): 4-bit v0|v1<<4; 2-bit
+ *     v0|v1<<2|v2<<4|v3<<6; 1-bit bit i = v_i; 3-bit 8 codes -> 3 bytes little-endian.
+ *   - bits_lo == 0 means integer bit-width (one packed array, bits_hi for all d coordinates).
+ *     bits_lo > 0 is the reference's fractional mode (cache.py:253-274): coordinates
+ *     [0, d/2) at bits_hi into packed_hi, [d/2, d) at bits_lo into packed_lo.
+ */
+#ifndef TQ_ABI_H
+#define TQ_ABI_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TQ_ABI_VERSION 1
+
+enum { TQ_OK = 0, TQ_ERR_INVALID = -1, TQ_ERR_UNSUPPORTED = -2, TQ_ERR_LAUNCH = -3, TQ_ERR_TIMEOUT = -4 };
+enum { TQ_F16 = 0, TQ_BF16 = 1, TQ_F32 = 2 };
+
+/* Library / ABI version (TQ_ABI_VERSION). */
+int tq_version(void);
+/* Text of the last error on the calling thread ("" if none). Host pointer, owned by the library. */
+const char* tq_last_error(void);
+
+/* ---- codec ------------------------------------------------------------------------------ */
+
+/* pack_indices (packing.py:211-222): idx (n, d) u8 -> packed (n, d*bits/8) u8, bits in 1..4. */
+int tq_pack(const uint8_t* idx, uint8_t* packed, int64_t n, int d, int bits, void* stream);
+/* unpack_indices (packing.py:225-236). */
+int tq_unpack(const uint8_t* packed, uint8_t* idx, int64_t n, int d, int bits, void* stream);
+/* quantize_scalar (codebook.py:203-225): idx = #{b : y > boundary_b}; n_bnd <= 255. */
+int tq_quantize_scalar(const float* y, const float* boundaries, int n_bnd, uint8_t* idx, int64_t count,
+                       void* stream);
+/* dequantize_scalar (codebook.py:228-238): out = centroids[idx]. */
+int tq_dequantize_scalar(const uint8_t* idx, const float* centroids, int n_cent, float* out, int64_t count,
+                         void* stream);
+/* quantize_scalar + pack_indices on already-rotated float32 rows (cache.py:249-250, 269-273).
+ * Bit-exact with the reference given the same y. */
+int tq_quantize_from_rotated(const float* y, int64_t n, int d, const float* bnd_hi, int bits_hi,
+                             const float* bnd_lo, int bits_lo, uint8_t* packed_hi, uint8_t* packed_lo,
+                             void* stream);
+
+/* ---- rotation --------------------------------------------------------------------------- */
+
+/* rotate / pre_rotate_query (rotation.py:55-65, 81-110): out = x @ R^T; inverse != 0 gives
+ * inverse_rotate (rotation.py:68-78): out = x @ R.  x (n, d) of x_dtype, rot (d, d) f32, out f32. */
+int tq_rotate(const void* x, int x_dtype, const float* rot, float* out, int64_t n, int d, int inverse,
+              void* stream);
+
+/* ---- quantize: norm -> normalise -> rotate -> boundary count -> pack ---------------------- */
+
+typedef struct {
+    const void* x;            /* (n_lanes, n_rows, d) of x_dtype */
+    int x_dtype;              /* TQ_F16 / TQ_BF16 / TQ_F32 */
+    int d;                    /* 64, 96, 128 or 256 (any multiple of 16 up to 256) */
+    int64_t n_lanes, n_rows;  /* lanes = batch*kv_heads, rows = tokens of this chunk */
+    int64_t x_lane_stride, x_row_stride; /* elements */
+    const float* rot;         /* (d, d) float32, row-major */
+    const float* bnd_hi; int bits_hi;    /* 2^bits_hi - 1 boundaries */
+    const float* bnd_lo; int bits_lo;    /* 0 = integer mode */
+    uint8_t* packed_hi;       /* row (o, r) at packed_hi + (o*out_lane_stride + r)*width_hi */
+    uint8_t* packed_lo;       /* fractional mode only */
+    float* norms;             /* (o*out_lane_stride + r) */
+    int64_t out_lane_stride;  /* rows */
+    /* optional 1-bit QJL sketch of the residual (cache.py:396-427, qjl.py:47-67); NULL = off.
+     * qjl_proj_rot is S @ R^T (m, d) float32 with m == 32; centroids are needed for the residual. */
+    const float* qjl_proj_rot; const float* cent_hi; const float* cent_lo;
+    uint32_t* qjl_bits;       /* bit i = sign of projection i (1 = non-negative) */
+    float* qjl_gamma;         /* ||x - dequant(x)|| */
+    float* y_out;             /* optional (n_lanes*n_rows, d) float32 rotated rows, or NULL */
+} tq_quantize_args;
+
+/* TurboQuantMSE.quantize / cache._quantize_kv(_fractional) (quantizer.py:54-85, cache.py:232-274);
+ * metal_quantize_4bit (kernels.py:363-409). */
+int tq_quantize_pack(const tq_quantize_args* a, void* stream);
+
+/* ---- dequantize: unpack -> centroid -> inverse rotation -> scale ------------------------- */
+
+typedef struct {
+    const uint8_t* packed_hi; const uint8_t* packed_lo; const float* norms;
+    int64_t n_lanes, n_rows, in_lane_stride;  /* rows */
+    int d; int bits_hi, bits_lo;
+    const float* cent_hi; const float* cent_lo; const float* rot;
+    /* optional QJL correction added to the output (qjl.py:70-94): S (m, d), m == 32 */
+    const float* qjl_proj; const uint32_t* qjl_bits; const float* qjl_gamma;
+    void* out; int out_dtype; int64_t out_lane_stride, out_row_stride; /* elements */
+} tq_dequantize_args;
+
+/* TurboQuantMSE.dequantize / cache._dequantize_kv(_fractional) / metal_dequantize
+ * (quantizer.py:87-109, cache.py:276-343, kernels.py:313-360). */
+int tq_dequantize(const tq_dequantize_args* a, void* stream);
+
+/* ---- fused QK scores --------------------------------------------------------------------- */
+
+/* fused_qk_scores_{2,3,4}bit (kernels.py:558-629): out[q,k] = norms[k] * sum_j q_rot[q,j]*c[idx(k,j)];
+ * raw scores, single head. q_rot (t_q, d) f32, packed (t_kv, d*bits/8), out (t_q, t_kv) f32. */
+int tq_qk_scores(const float* q_rot, const uint8_t* packed, const float* norms, const float* centroids,
+                 int bits, int d, int64_t t_q, int64_t t_kv, float* out, void* stream);
+
+/* ---- decode attention over [fp16 sink | packed middle | fp16 residual] ------------------- */
+
+typedef struct {
+    int batch, n_q_heads, n_kv_heads, d;
+    const void* q; int q_dtype;              /* (batch, n_q_heads, d): one query token */
+    float scale;                             /* softmax scale, normally d^-0.5 */
+    const float* rot;                        /* (d, d) */
+    /* packed middle: lane = b*n_kv_heads + h, token t at row lane*c_lane_stride + t */
+    int64_t c_len, c_lane_stride;
+    int k_bits_hi, k_bits_lo, v_bits_hi, v_bits_lo;
+    const uint8_t *k_hi, *k_lo, *v_hi, *v_lo;
+    const float *k_norms, *v_norms;
+    const float *k_cent_hi, *k_cent_lo, *v_cent_hi, *v_cent_lo;
+    /* optional QJL sketches of the K and V residuals (m == 32); qjl_proj is S (m, d) */
+    const float* qjl_proj;
+    const uint32_t *k_qjl_bits, *v_qjl_bits; const float *k_qjl_gamma, *v_qjl_gamma;
+    /* uncompressed regions, (lanes, cap, d) of dense_dtype; *_len valid tokens */
+    int dense_dtype;
+    const void *sink_k, *sink_v; int64_t sink_len, sink_lane_stride;   /* stride in tokens */
+    const void *res_k, *res_v;   int64_t res_len,  res_lane_stride;
+    void* out; int out_dtype;                /* (batch, n_q_heads, d) */
+    void* workspace; size_t workspace_bytes; /* >= tq_decode_workspace_bytes(...) */
+} tq_decode_args;
+
+/* Scratch bytes tq_decode_attn needs for these sizes (host-side arithmetic only). */
+size_t tq_decode_workspace_bytes(int batch, int n_q_heads, int n_kv_heads, int d, int64_t c_len,
+                                 int64_t dense_len);
+
+/* One decode step of attention computed directly on the compressed cache.  Replaces what the
+ * reference does as dense reassembly (cache.py:674-706) followed by the consumer's
+ * scaled-dot-product attention; the math on packed keys is that of kernels.py:439-479
+ * (pre-rotated query, rotation.py:81-110) extended with softmax and values. */
+int tq_decode_attn(const tq_decode_args* a, void* stream);
+
+/* Host-side tuning knobs of the split heuristic (process-wide; no reference counterpart):
+ *   "decode_ctas_per_sm" 1..8, "decode_splits" 0 (auto)..448, "decode_force_general" 0/1.
+ * Changing them changes tq_decode_workspace_bytes for the same sizes. */
+int tq_set_tuning(const char* key, int value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TQ_ABI_H */

@@ -1,0 +1,134 @@
+"""Decode attention straight from the packed cache against the oracle.
+
+Oracle = reference cache (restated, pinned) -> dense K/V -> float32 softmax attention.  Tolerance: 1e-3
+of the output's largest magnitude (the task's bound for attention outputs at fp32 accumulation).
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import cu, host, host_tables, kv_like
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(oracle, rs, b, hq, hkv, t, d, kb, vb, rw, sink, chunk=0, dtype=np.float16):
+    from mlx_turboquant_b200 import TurboQuantKVCache
+    k, v = kv_like(rs, (b, hkv, t, d), dtype), kv_like(rs, (b, hkv, t, d), dtype)
+    q = (rs.randn(b, hq, 1, d) / np.sqrt(d)).astype(dtype)
+    c = TurboQuantKVCache(head_dim=d, num_kv_heads=hkv, key_bits=kb, value_bits=vb, residual_window=rw,
+                          fp16_sink_size=sink, chunk_size=chunk)
+    c.update(cu(k), cu(v))
+    ref_c = oracle.KVCacheOracle(d, host_tables(d), kb, vb, rw, fp16_sink_size=sink, chunk_size=chunk)
+    rk, rv = ref_c.update_and_fetch(k, v)
+    assert (c._compressed_len, c._sink_len, c._fp16_len) == (ref_c.comp_len, ref_c.sink_len, ref_c.fp_len)
+    return c, cu(q), oracle.attention(q, rk, rv)
+
+
+def _check(out, ref, tol=1e-3):
+    err = np.abs(host(out.float()) - ref).max() / np.abs(ref).max()
+    assert np.isfinite(host(out.float())).all() and err < tol, err
+
+
+@pytest.mark.parametrize("t", (1, 15, 16, 17, 129, 300, 1000, 2500))
+def test_k4v2_direct_path_lengths(oracle, t):
+    """d = 128, 4-bit keys / 2-bit values: the table-lookup kernel, ragged token counts, GQA 4."""
+    rs = np.random.RandomState(t)
+    c, q, ref = _case(oracle, rs, 1, 8, 2, t, 128, 4, 2, 32, 8)
+    _check(c.attend(q), ref)
+
+
+@pytest.mark.parametrize("d", (64, 96, 128, 256))
+@pytest.mark.parametrize("kb,vb", ((4, 2), (3, 2), (2, 2), (3.5, 3.5), (4, 4), (2, 3)))
+def test_general_path_bit_widths_and_head_dims(oracle, d, kb, vb):
+    rs = np.random.RandomState(int(d + 10 * kb + vb))
+    c, q, ref = _case(oracle, rs, 2, 4, 2, 333, d, kb, vb, 16, 4)
+    _check(c.attend(q), ref)
+
+
+@pytest.mark.parametrize("hq,hkv", ((4, 4), (8, 1), (16, 1), (12, 4), (32, 8)))
+def test_head_grouping(oracle, hq, hkv):
+    """MHA, GQA up to 8 query heads per KV head in one pass, 16 per KV head in two head groups."""
+    rs = np.random.RandomState(hq * 100 + hkv)
+    c, q, ref = _case(oracle, rs, 1, hq, hkv, 700, 128, 4, 2, 64, 16)
+    _check(c.attend(q), ref)
+
+
+def test_direct_and_general_paths_agree(oracle):
+    from mlx_turboquant_b200.kernels import set_tuning
+    rs = np.random.RandomState(9)
+    c, q, ref = _case(oracle, rs, 2, 8, 2, 4000, 128, 4, 2, 128, 128)
+    a = c.attend(q)
+    set_tuning("decode_force_general", 1)
+    try:
+        g = c.attend(q)
+    finally:
+        set_tuning("decode_force_general", 0)
+    _check(a, ref)
+    _check(g, ref)
+    assert np.abs(host(a.float()) - host(g.float())).max() <= 2e-3 * np.abs(ref).max()
+    for splits in (1, 3, 64):                       # the result does not depend on the split count
+        set_tuning("decode_splits", splits)
+        try:
+            _check(c.attend(q), ref)
+        finally:
+            set_tuning("decode_splits", 0)
+
+
+def test_regions_present_or_absent(oracle):
+    rs = np.random.RandomState(10)
+    for (t, rw, sink) in ((40, 64, 0), (40, 64, 8), (500, 0, 0), (500, 16, 0), (8, 64, 16)):
+        c, q, ref = _case(oracle, rs, 1, 4, 2, t, 128, 4, 2, rw, sink)
+        _check(c.attend(q), ref)
+    from mlx_turboquant_b200 import TurboQuantKVCache
+    with pytest.raises(ValueError):
+        TurboQuantKVCache(128, 2).attend(q)
+    with pytest.raises(NotImplementedError):
+        c.attend(torch.zeros(1, 4, 2, 128, device="cuda", dtype=torch.float16))
+
+
+@pytest.mark.parametrize("dtype", (np.float32,))
+def test_float32_cache_and_query(oracle, dtype):
+    rs = np.random.RandomState(12)
+    c, q, ref = _case(oracle, rs, 1, 8, 2, 600, 128, 4, 2, 32, 8, dtype=dtype)
+    out = c.attend(q)
+    assert out.dtype == torch.float32
+    _check(out, ref)
+
+
+def test_incremental_decode_steps_match_dense_attention(oracle):
+    """Prefill then 40 single-token steps; every step's packed attention equals attention over the
+    dense tensors the same cache returns (the reference's own consumer contract)."""
+    from mlx_turboquant_b200 import TurboQuantKVCache
+    rs = np.random.RandomState(13)
+    d, hkv, hq = 128, 2, 8
+    c = TurboQuantKVCache(head_dim=d, num_kv_heads=hkv, residual_window=16, fp16_sink_size=4)
+    k, v = cu(kv_like(rs, (1, hkv, 340, d))), cu(kv_like(rs, (1, hkv, 340, d)))
+    c.update(k[:, :, :300], v[:, :, :300])
+    for i in range(300, 340):
+        dk, dv = c.update_and_fetch(k[:, :, i:i + 1], v[:, :, i:i + 1])
+        q = cu((rs.randn(1, hq, 1, d) / np.sqrt(d)).astype(np.float16))
+        ref = oracle.attention(host(q), host(dk), host(dv))
+        _check(c.attend(q), ref)
+
+
+def test_benchmark_shape_against_gpu_dense_attention():
+    """Llama-3.1-8B layer shape at the full 32768-token context (128 sink + 32512 packed + 128 recent):
+    too large for the CPU oracle in a test, so the packed kernel is checked against float32 softmax
+    attention over the dense tensors the same cache returns (torch, on the GPU)."""
+    from mlx_turboquant_b200 import TurboQuantKVCache
+    g = torch.Generator(device="cuda").manual_seed(1001)
+    b, hq, hkv, t, d = 1, 32, 8, 32768, 128
+    scale = torch.exp(0.5 * torch.randn(b, hkv, t, 1, device="cuda", generator=g))
+    k = (torch.randn(b, hkv, t, d, device="cuda", generator=g) * scale).half()
+    v = (torch.randn(b, hkv, t, d, device="cuda", generator=g) * scale).half()
+    q = (torch.randn(b, hq, 1, d, device="cuda", generator=g) / d ** 0.5).half()
+    c = TurboQuantKVCache(head_dim=d, num_kv_heads=hkv, residual_window=128, fp16_sink_size=128)
+    dk, dv = c.update_and_fetch(k, v)
+    assert (c._sink_len, c._compressed_len, c._fp16_len) == (128, 32512, 128)
+    kk = dk.float().repeat_interleave(hq // hkv, dim=1)
+    vv = dv.float().repeat_interleave(hq // hkv, dim=1)
+    p = torch.softmax((q.float() @ kk.transpose(-1, -2)) * d ** -0.5, dim=-1)
+    ref = (p @ vv).cpu().numpy()
+    _check(c.attend(q), ref)
