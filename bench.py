@@ -1,0 +1,399 @@
+"""Benchmark of the compressed-attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Headline workload (N = 1): single-layer decode attention over a compressed cache at the
+Llama-3.1-8B layer shape - 32 query heads, 8 KV heads, head_dim 128, batch 1, context 32768 =
+128 fp16 sink + 32512 tokens packed at 4-bit keys / 2-bit values + 128 fp16 recent tokens.
+One STEP is that attention for the 32 layers of the model, each layer with its own cache, so the
+working set (0.9 GB) is far larger than L2.  Synthetic seeded K/V/Q with the benchmark's
+distributions stand in for model activations.
+
+Printed JSON (one line): `value` = algorithmic HBM GB/s over all GPUs with everything resident in
+HBM (CUDA-graph replay of the 32 launches, CUDA events); `e2e` = the same quantity through the
+public cache API with host buffers (pinned host -> device copies of the new token's q/k/v and the
+device -> host read of the result inside the timed region); `roofline` for the dominant kernel;
+`cpu_baseline` = the reference's own per-step work (dense reassembly + float32 attention) restated on
+the host cores; `secondary` = quantize+pack throughput in Mtokens/s.
+
+`--impl reference` times that CPU restatement alone (no GPU work on its path).
+With N > 1 (launched under torchrun) every rank owns an independent set of sequences: no data-path
+collective, weak scaling, time = max over ranks.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+# ---- workload constants (Llama-3.1-8B layer, 32K context, K4/V2) ----------------------------------------
+LAYERS, HQ, HKV, D, CTX, SINK, RW = 32, 32, 8, 128, 32768, 128, 128
+T_C = CTX - SINK - RW
+# algorithmic bytes of one layer-step: packed codes + norms, fp16 sink/recent tokens, query in, result out
+BYTES_PER_LAYER_STEP = HKV * T_C * (D * 4 // 8 + 4 + D * 2 // 8 + 4) + HKV * (SINK + RW) * 2 * D * 2 + HQ * D * 4
+WORKLOAD = "llama31_8b_layer_decode_attn_ctx32768_k4v2_sink128_rw128"
+# quantize+pack: 4096-token chunks x 8 KV heads, K and V, fp16 in; bytes per (token, head): read 2*D*2, write codes + norms
+QCHUNK = 4096
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU every 100 ms while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+
+    def __enter__(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+            return self
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def _run(self):
+        nv = self._nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                 "hw_power_brake": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=1)
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ---- the reference's per-step work, restated on the CPU ---------------------------------------------------
+def cpu_reference_step_factory(layers: int, seed0: int = 1000):
+    """Build `layers` reference-style caches on the host (oracle: quantize, dequantize -> dense middle) and
+    return (step_fn, info).  step_fn() does, per layer, what the reference does per decode step: append the
+    token, reassemble dense [sink | middle | recent] float32 K/V (cache.py:682-706) and run float32 GQA
+    attention on it."""
+    from mlx_turboquant_b200.codebook import get_codebook_host
+    from oracle import tq_oracle as orc
+    try:
+        from oracle import c_oracle
+        clib = c_oracle.load()
+    except Exception:
+        clib = None
+    tables = {b: get_codebook_host(D, b) for b in (1, 2, 3, 4)}
+    caches = []
+    for li in range(layers):
+        rs = np.random.RandomState(seed0 + li)
+        k = (rs.randn(1, HKV, CTX, D).astype(np.float32) * np.exp(0.5 * rs.randn(1, HKV, CTX, 1)).astype(np.float32)).astype(np.float16)
+        v = (rs.randn(1, HKV, CTX, D).astype(np.float32) * np.exp(0.5 * rs.randn(1, HKV, CTX, 1)).astype(np.float32)).astype(np.float16)
+        c = orc.KVCacheOracle(D, tables, 4, 2, RW, fp16_sink_size=SINK)
+        if clib is not None:
+            c_oracle.use_c_kernels(c, clib)
+        c.update_and_fetch(k, v)
+        caches.append(c)
+    rs = np.random.RandomState(seed0 + 999)
+    q = (rs.randn(1, HQ, 1, D) / np.sqrt(D)).astype(np.float16)
+    kn = (rs.randn(1, HKV, 1, D)).astype(np.float16)
+    threads = clib.tqo_threads() if clib is not None else (os.cpu_count() or 1)
+
+    def step():
+        out = None
+        for c in caches:
+            # the recent-token buffer is restored after the step so every step sees the same 32768+1 tokens
+            saved = c.fp_len, c.offset
+            dk, dv = c.update_and_fetch(kn, kn)
+            out = c_oracle.attention(clib, q, dk, dv) if clib is not None else orc.attention(q, dk, dv)
+            c.fp_len, c.offset = saved
+        return out
+
+    return step, {"kind": "port", "cores": threads,
+                  "sample": f"{layers} of {LAYERS} layers per step; per layer: append 1 token, dense float32 reassembly of "
+                            f"{CTX + 1} tokens x {HKV} KV heads, float32 GQA attention ({'C/OpenMP' if clib is not None else 'NumPy'})"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    layers = 1
+    step, info = cpu_reference_step_factory(layers)
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    gbs = BYTES_PER_LAYER_STEP * layers / dt / 1e9
+    line = {
+        "impl": "reference", "metric": "decode_attn_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "us_per_layer_step": dt / layers * 1e6,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "layers_per_step": layers, "note": "CPU restatement of the reference's per-step path; MLX and Metal are unavailable on this box"},
+        "cpu_baseline": dict(info, value=gbs, unit="GB/s"),
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ---- the CUDA path ------------------------------------------------------------------------------------------
+def build_caches(torch, dev, rank):
+    from mlx_turboquant_b200 import TurboQuantKVCache
+    caches, qs = [], []
+    for li in range(LAYERS):
+        g = torch.Generator(device=dev).manual_seed(1000 + 100 * rank + li)
+        scale_k = torch.exp(0.5 * torch.randn(1, HKV, CTX, 1, device=dev, generator=g))
+        k = (torch.randn(1, HKV, CTX, D, device=dev, generator=g) * scale_k).half()
+        scale_v = torch.exp(0.5 * torch.randn(1, HKV, CTX, 1, device=dev, generator=g))
+        v = (torch.randn(1, HKV, CTX, D, device=dev, generator=g) * scale_v).half()
+        c = TurboQuantKVCache(head_dim=D, num_kv_heads=HKV, key_bits=4, value_bits=2, residual_window=RW, fp16_sink_size=SINK)
+        c.update(k, v)
+        assert (c._sink_len, c._compressed_len, c._fp16_len) == (SINK, T_C, RW)
+        caches.append(c)
+        qs.append((torch.randn(1, HQ, 1, D, device=dev, generator=g) / D ** 0.5).half())
+        del k, v
+    return caches, qs
+
+
+def bench_quantize(torch, dev, steps, warmup, peak):
+    """Quantize+pack throughput: 32 distinct 4096-token x 8-head chunks (K and V) per step, two settings."""
+    from mlx_turboquant_b200 import kernels
+    from mlx_turboquant_b200.codebook import get_codebook
+    from mlx_turboquant_b200.rotation import get_rotation_matrix
+    rot = get_rotation_matrix(D, 42, dev)
+    g = torch.Generator(device=dev).manual_seed(2000)
+    pool = []
+    for _ in range(LAYERS):
+        x = torch.randn(2, 1, HKV, QCHUNK, D, device=dev, generator=g)
+        x[..., [3, 40, 77, 101]] *= 20.0   # four fixed outlier channels per head
+        pool.append(x.half())
+    out = {}
+    for name, kb, vb in (("k3_v2", 3, 2), ("k3.5_v3.5", 3.5, 3.5)):
+        sides = []
+        for bits in (kb, vb):
+            hi, lo = kernels.split_bits(bits)
+            w_hi, w_lo = kernels.packed_widths(D, hi, lo)
+            sides.append(dict(hi=hi, lo=lo, bnd_hi=get_codebook(D, hi, dev)[1], bnd_lo=get_codebook(D, lo, dev)[1] if lo else None,
+                              p_hi=torch.empty(1, HKV, QCHUNK, w_hi, dtype=torch.uint8, device=dev),
+                              p_lo=torch.empty(1, HKV, QCHUNK, w_lo, dtype=torch.uint8, device=dev) if lo else None,
+                              norms=torch.empty(1, HKV, QCHUNK, dtype=torch.float32, device=dev), w=w_hi + w_lo))
+
+        def step():
+            for x in pool:
+                for i, s in enumerate(sides):
+                    kernels.quantize_pack(x[i], rot, s["bnd_hi"], s["hi"], s["bnd_lo"], s["lo"], out_hi=s["p_hi"],
+                                          out_lo=s["p_lo"], out_norms=s["norms"], out_offset=0)
+        for _ in range(warmup):
+            step()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1) / steps
+        bytes_per_unit = 2 * D * 2 + sides[0]["w"] + 4 + sides[1]["w"] + 4        # per (token, head, layer), K and V
+        units = LAYERS * HKV * QCHUNK
+        gbs = units * bytes_per_unit / (ms * 1e-3) / 1e9
+        out[name] = {"mtokens_per_s": QCHUNK / (ms * 1e-3) / 1e6, "ms_per_step": ms, "bytes_per_token_head_layer": bytes_per_unit,
+                     "hbm_gbs": gbs, "frac_of_peak": gbs / peak}
+    return out
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    import __graft_entry__ as ge
+    from mlx_turboquant_b200 import _lib
+    if not _lib.LIB_PATH.exists() and rank == 0:
+        ge.build()
+    if world > 1:
+        dist.barrier()
+    _lib.lib()
+    peak, peak_src = peaks()
+
+    global LAYERS
+    LAYERS = args.layers
+    caches, qs = build_caches(torch, dev, rank)
+    torch.cuda.synchronize(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- device-resident throughput: CUDA graph of one 32-layer step -------------------------------------
+    outs = [None] * LAYERS
+
+    def layer_pass():
+        for i in range(LAYERS):
+            outs[i] = caches[i].attend(qs[i])
+    layer_pass()                      # allocates the workspace before capture
+    torch.cuda.synchronize(dev)
+    if args.no_graph:
+        class _Eager:
+            replay = staticmethod(layer_pass)
+        graph = _Eager()
+    else:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            layer_pass()
+    launches_per_step = LAYERS * 3
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    barrier()
+    with ClockSampler(local) as clk:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # keep the timed region long enough for clock samples
+        reps = args.steps
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        barrier()
+        ms_step = e0.elapsed_time(e1) / reps
+        t_end = time.time() + (0.0 if args.no_graph else 0.6)
+        while time.time() < t_end:     # a few more replays so the sampler sees the loaded clock
+            graph.replay()
+        torch.cuda.synchronize(dev)
+    t = torch.tensor([ms_step], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item())
+    value = world * LAYERS * BYTES_PER_LAYER_STEP / (ms_step * 1e-3) / 1e9
+
+    # ---- end to end through the public API with host buffers -----------------------------------------------
+    hq = [torch.randn(1, HQ, 1, D).half().pin_memory() for _ in range(LAYERS)]
+    hk = [torch.randn(1, HKV, 1, D).half().pin_memory() for _ in range(LAYERS)]
+    hv = [torch.randn(1, HKV, 1, D).half().pin_memory() for _ in range(LAYERS)]
+    hout = [torch.empty(1, HQ, 1, D, dtype=torch.float16).pin_memory() for _ in range(LAYERS)]
+    e2e_caches, _ = (caches, None)
+
+    def e2e_step():
+        for i in range(LAYERS):
+            q = hq[i].to(dev, non_blocking=True)
+            k = hk[i].to(dev, non_blocking=True)
+            v = hv[i].to(dev, non_blocking=True)
+            e2e_caches[i].update(k, v)
+            hout[i].copy_(e2e_caches[i].attend(q), non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+    e2e_steps = min(args.steps, 20)
+    for _ in range(0 if args.no_e2e else 3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(0 if args.no_e2e else e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / e2e_steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    e2e_gbs = world * LAYERS * BYTES_PER_LAYER_STEP / (e2e_ms * 1e-3) / 1e9
+
+    line = {
+        "metric": "decode_attn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "us_per_layer_step": ms_step * 1e3 / LAYERS,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 accumulate, f16 operands",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "layers_per_step": LAYERS, "q_heads": HQ, "kv_heads": HKV, "head_dim": D,
+                   "batch_per_gpu": 1, "context": CTX, "l2_policy": "inputs larger than L2: 32 distinct layer caches, 0.9 GB per step",
+                   "sharding": "independent sequences per GPU, no collective"},
+        "e2e": {"value": e2e_gbs, "unit": "GB/s", "ms_per_step": e2e_ms, "us_per_layer_step": e2e_ms * 1e3 / LAYERS,
+                "h2d_bytes_per_step": LAYERS * (HQ * D * 2 + 2 * HKV * D * 2), "d2h_bytes_per_step": LAYERS * HQ * D * 2,
+                "path": "TurboQuantKVCache.update + .attend per layer, pinned host q/k/v in, pinned host result out"},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clk.summary(),
+        "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
+                     "peak_source": peak_src, "frac_of_nominal_8tbs": value / world / 8000.0, "traffic": None,
+                     "kernel": "decode_partial_kernel<128, direct> (+ prep and merge launches, timed together)",
+                     "algorithmic_bytes_per_launch": BYTES_PER_LAYER_STEP},
+    }
+    if rank == 0 and world == 1 and not args.no_secondary:
+        line["secondary"] = {"metric": "quantize_pack_mtokens_per_s", "unit": "Mtokens/s (token = position x 8 KV heads x 32 layers)",
+                             "chunk_tokens": QCHUNK, **bench_quantize(torch, dev, max(2, min(args.steps, 10)), 3, peak)}
+    if rank == 0 and world == 1 and not args.no_cpu:
+        step, info = cpu_reference_step_factory(1)
+        step()
+        t0 = time.perf_counter()
+        n = 3
+        for _ in range(n):
+            step()
+        dt = (time.perf_counter() - t0) / n
+        line["cpu_baseline"] = dict(info, value=BYTES_PER_LAYER_STEP / dt / 1e9, unit="GB/s", us_per_layer_step=dt * 1e6)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
+    ap.add_argument("--layers", type=int, default=32, help="distinct layer caches per step (32 = the model; fewer for profiling)")
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph (for profilers)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the quantize+pack leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

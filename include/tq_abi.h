@@ -129,6 +129,9 @@ typedef struct {
     const uint8_t *k_hi, *k_lo, *v_hi, *v_lo;
     const float *k_norms, *v_norms;
     const float *k_cent_hi, *k_cent_lo, *v_cent_hi, *v_cent_lo;
+    /* The kernel holds value centroids in fp16; a table-wide scale from tq_fp16_table_scale() applied
+     * before the cast (and divided out of the result) keeps that rounding below 1e-4. 0 = no scaling. */
+    float v_cent_scale_hi, v_cent_scale_lo;
     /* optional QJL sketches of the K and V residuals (m == 32); qjl_proj is S (m, d) */
     const float* qjl_proj;
     const uint32_t *k_qjl_bits, *v_qjl_bits; const float *k_qjl_gamma, *v_qjl_gamma;
@@ -150,8 +153,13 @@ size_t tq_decode_workspace_bytes(int batch, int n_q_heads, int n_kv_heads, int d
  * (pre-rotated query, rotation.py:81-110) extended with softmax and values. */
 int tq_decode_attn(const tq_decode_args* a, void* stream);
 
+/* Scale s in [1, 2) minimising max_i |fp16(s*c_i) - s*c_i| / |s*c_i| for a HOST array of n centroids
+ * (no reference counterpart; pure host arithmetic). */
+float tq_fp16_table_scale(const float* centroids_host, int n);
+
 /* Host-side tuning knobs of the split heuristic (process-wide; no reference counterpart):
- *   "decode_ctas_per_sm" 1..8, "decode_splits" 0 (auto)..448, "decode_force_general" 0/1.
+ *   "decode_ctas_per_sm" 1..8, "decode_splits" 0 (auto)..448, "decode_force_general" 0/1,
+ *   "decode_pdl" 0/1 (programmatic dependent launch between the kernels of one call).
  * Changing them changes tq_decode_workspace_bytes for the same sizes. */
 int tq_set_tuning(const char* key, int value);
 

@@ -52,6 +52,7 @@ class DecodeArgs(C.Structure):
         ("k_hi", _vp), ("k_lo", _vp), ("v_hi", _vp), ("v_lo", _vp),
         ("k_norms", _vp), ("v_norms", _vp),
         ("k_cent_hi", _vp), ("k_cent_lo", _vp), ("v_cent_hi", _vp), ("v_cent_lo", _vp),
+        ("v_cent_scale_hi", _f), ("v_cent_scale_lo", _f),
         ("qjl_proj", _vp), ("k_qjl_bits", _vp), ("v_qjl_bits", _vp), ("k_qjl_gamma", _vp), ("v_qjl_gamma", _vp),
         ("dense_dtype", _i),
         ("sink_k", _vp), ("sink_v", _vp), ("sink_len", _i64), ("sink_lane_stride", _i64),
@@ -77,6 +78,7 @@ PROTOTYPES = {
     "tq_decode_workspace_bytes": (_sz, [_i, _i, _i, _i, _i64, _i64]),
     "tq_decode_attn": (_i, [C.POINTER(DecodeArgs), _vp]),
     "tq_set_tuning": (_i, [C.c_char_p, _i]),
+    "tq_fp16_table_scale": (_f, [_vp, _i]),
 }
 
 _lib = None

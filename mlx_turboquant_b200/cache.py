@@ -24,13 +24,27 @@ from typing import Any
 import torch
 
 from . import _lib, kernels
-from .codebook import get_codebook
+from .codebook import get_codebook, get_codebook_host
 from .qjl import generate_projection_matrix_host, get_projection_matrix
 from .rotation import generate_rotation_matrix_host, get_rotation_matrix
 
 
 def _round_up(n: int, m: int) -> int:
     return (n + m - 1) // m * m
+
+
+_fp16_scales: dict[tuple[int, int], float] = {}
+
+
+def _fp16_scale(d: int, bits: int) -> float:
+    """Table-wide scale that makes the fp16 copies of a codebook's centroids (held by the decode kernel)
+    accurate to ~1e-5 instead of 2^-11; see tq_fp16_table_scale."""
+    key = (d, bits)
+    if key not in _fp16_scales:
+        import numpy as np
+        c = np.ascontiguousarray(get_codebook_host(d, bits)[0], dtype=np.float32)
+        _fp16_scales[key] = float(_lib.lib().tq_fp16_table_scale(c.ctypes.data, c.size))
+    return _fp16_scales[key]
 
 
 class _Side:
@@ -42,11 +56,14 @@ class _Side:
         self.fractional = self.bits_lo != 0
         self.hi = self.lo = self.norms = self.qbits = self.qgamma = None
         self.cent_hi = self.cent_lo = self.bnd_hi = self.bnd_lo = None
+        self.fp16_scale_hi = self.fp16_scale_lo = 0.0
 
     def load_tables(self, d: int, device) -> None:
         self.cent_hi, self.bnd_hi = get_codebook(d, self.bits_hi, device)
+        self.fp16_scale_hi = _fp16_scale(d, self.bits_hi)
         if self.fractional:
             self.cent_lo, self.bnd_lo = get_codebook(d, self.bits_lo, device)
+            self.fp16_scale_lo = _fp16_scale(d, self.bits_lo)
 
     def capacity(self) -> int:
         return 0 if self.hi is None else self.hi.shape[2]
@@ -381,11 +398,13 @@ class TurboQuantKVCache:
         return torch.cat(pk, dim=2), torch.cat(pv, dim=2)
 
     # ---- attention on the packed cache -----------------------------------------------------------
-    def attend(self, queries: torch.Tensor, scale: float | None = None) -> torch.Tensor:
+    def attend(self, queries: torch.Tensor, scale: float | None = None, out_dtype=None) -> torch.Tensor:
         """softmax(scale * q K^T) V for ONE query token per sequence, straight from packed storage.
 
-        ``queries`` is (B, n_q_heads, 1, D) or (B, n_q_heads, D); the result has the same shape and dtype.
-        Equals attention over what ``update_and_fetch`` would return (to ~1e-3), without building it.
+        ``queries`` is (B, n_q_heads, 1, D) or (B, n_q_heads, D); the result has the same shape and, unless
+        ``out_dtype`` says otherwise, the same dtype.  Equals attention over what ``update_and_fetch``
+        would return (to ~1e-3 with a float32 result; a float16 result adds its own rounding), without
+        building it.
         """
         dev = _lib.require_cuda(queries)
         self._bind(dev)
@@ -400,7 +419,7 @@ class TurboQuantKVCache:
         if q.dtype not in (torch.float16, torch.bfloat16, torch.float32):
             q = q.to(torch.float32)
         q = q.contiguous()
-        out = torch.empty((b, hq, d), dtype=q.dtype, device=dev)
+        out = torch.empty((b, hq, d), dtype=out_dtype or q.dtype, device=dev)
         ref = self.keys if self.keys is not None else self.sink_keys
         if ref is None:
             ref = self._k.hi
@@ -421,6 +440,7 @@ class TurboQuantKVCache:
             a.k_norms, a.v_norms = _lib.ptr(k.norms), _lib.ptr(v.norms)
             a.k_cent_hi, a.k_cent_lo = _lib.ptr(k.cent_hi), _lib.ptr(k.cent_lo)
             a.v_cent_hi, a.v_cent_lo = _lib.ptr(v.cent_hi), _lib.ptr(v.cent_lo)
+            a.v_cent_scale_hi, a.v_cent_scale_lo = v.fp16_scale_hi, v.fp16_scale_lo
             if self.qjl_correction and k.qbits is not None:
                 a.qjl_proj = _lib.ptr(self._qjl_proj)
                 a.k_qjl_bits, a.v_qjl_bits = _lib.ptr(k.qbits), _lib.ptr(v.qbits)

@@ -49,6 +49,7 @@ struct DecodeParams {
     int n_ps, n_ds;                    // packed / dense splits
     int64_t p_tps, d_tps;              // tiles per split
     const void* q; int q_dtype; float scale; const float* rot;
+    float v_scale_hi, v_scale_lo;      // value centroids are multiplied by this before the fp16 cast (undone in the merge)
     __half *q_rot, *q_raw;             // workspace: (B, Hq, D) each, pre-scaled
     float *part_o, *part_ml;           // workspace: (B, Hkv, HG, S, slots, D) and (.., slots, 2)
     void* out; int out_dtype;
@@ -81,41 +82,59 @@ __device__ __forceinline__ uint32_t movm_t(uint32_t a) {
     asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
     return d;
 }
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+// Programmatic dependent launch: wait for the producer grid / let the consumer grid start its prologue.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
 // ---- query preparation ----------------------------------------------------------------------------
-// grid (B*Hq), 256 threads.  q_rot[j] = sum_k q[k] R[j][k]  (rotation.py:81-110), both copies scaled by
-// scale*log2(e) so the softmax can use exp2.
+// grid (B*Hq), D threads.  q_rot[j] = sum_k q[k] R[j][k]  (rotation.py:81-110); both copies are scaled by
+// scale*log2(e) so the softmax can use exp2.  Thread j streams row j of R with independent 128-bit loads.
 __global__ void __launch_bounds__(256) decode_prep_kernel(DecodeParams p) {
-    __shared__ float sq[256];
-    const int bh = blockIdx.x, d = p.D;
+    __shared__ __align__(16) float sq[256];
+    pdl_trigger();     // the partial kernel may start building its tables right away
+    pdl_wait();        // the query (and the workspace) may come from the launch just before this one
+    const int bh = blockIdx.x, d = p.D, j = threadIdx.x;
     const float f = p.scale * LOG2E;
-    for (int k = threadIdx.x; k < d; k += blockDim.x) {
-        const float v = load_as_f32(p.q, p.q_dtype, int64_t(bh) * d + k);
-        sq[k] = v;
-        p.q_raw[int64_t(bh) * d + k] = __float2half_rn(v * f);
-    }
+    const float v = load_as_f32(p.q, p.q_dtype, int64_t(bh) * d + j);
+    sq[j] = v;
     __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int j = warp; j < d; j += 8) {
-        float acc = 0.f;
-        for (int k = lane; k < d; k += 32) acc = fmaf(sq[k], __ldg(p.rot + int64_t(j) * d + k), acc);
-#pragma unroll
-        for (int off = 16; off; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-        if (lane == 0) p.q_rot[int64_t(bh) * d + j] = __float2half_rn(acc * f);
+    const float4* row = reinterpret_cast<const float4*>(p.rot + int64_t(j) * d);
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll 8
+    for (int k = 0; k < d / 4; ++k) {
+        const float4 r = __ldg(row + k);
+        const float4 x = *reinterpret_cast<const float4*>(sq + 4 * k);
+        a0 = fmaf(x.x, r.x, a0); a1 = fmaf(x.y, r.y, a1); a2 = fmaf(x.z, r.z, a2); a3 = fmaf(x.w, r.w, a3);
     }
+    p.q_raw[int64_t(bh) * d + j] = __float2half_rn(v * f);
+    p.q_rot[int64_t(bh) * d + j] = __float2half_rn(((a0 + a1) + (a2 + a3)) * f);
 }
 
 // ---- per-warp running softmax state ------------------------------------------------------------------
+constexpr float MAX_SLACK = 6.f;   // scores may exceed the running reference by 2^6 before it is refreshed
 template <int D> struct WarpAcc {
-    float m[2], l[2];          // heads 2t, 2t+1 (l is this lane's share; reduced over g at the end)
+    float m[2], mt[2], l[2];   // heads 2t, 2t+1: reference max, refresh threshold, this lane's share of the sum
     float o[D / 16][4];        // O^T fragments: rows = coordinate slots, cols = heads
 };
 
 // s[0..1]: token g, heads 2t,2t+1;  s[2..3]: token g+8.  Returns the P^T operand for the PV mma.
+// The softmax reference m is refreshed (with a cross-lane max and a rescale of the accumulators) only
+// when some score exceeds it by more than MAX_SLACK; softmax is shift-invariant, so any reference that
+// keeps exp2(s - m) inside the fp16 range is exact.
 template <int D>
 __device__ __forceinline__ void softmax_step(float (&s)[4], float kn0, float kn1, float vn0, float vn1, bool ok0,
                                              bool ok1, WarpAcc<D>& st, uint32_t (&bp)[2]) {
@@ -124,24 +143,25 @@ __device__ __forceinline__ void softmax_step(float (&s)[4], float kn0, float kn1
     s[2] = ok1 ? s[2] * kn1 : -INFINITY;
     s[3] = ok1 ? s[3] * kn1 : -INFINITY;
     float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+    if (__any_sync(0xffffffffu, mx0 > st.mt[0] || mx1 > st.mt[1])) {
 #pragma unroll
-    for (int off = 4; off < 32; off <<= 1) {
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
-    }
-    const float mn0 = fmaxf(st.m[0], mx0), mn1 = fmaxf(st.m[1], mx1);
-    const float a0 = ex2(st.m[0] - mn0), a1 = ex2(st.m[1] - mn1);
-    st.m[0] = mn0;
-    st.m[1] = mn1;
-    const float p0 = ex2(s[0] - mn0), p1 = ex2(s[1] - mn1), p2 = ex2(s[2] - mn0), p3 = ex2(s[3] - mn1);
-    st.l[0] = fmaf(st.l[0], a0, p0 + p2);
-    st.l[1] = fmaf(st.l[1], a1, p1 + p3);
-    if (!__all_sync(0xffffffffu, a0 == 1.f && a1 == 1.f)) {
+        for (int off = 4; off < 32; off <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+        }
+        const float mn0 = fmaxf(fmaxf(st.m[0], mx0), -1e30f), mn1 = fmaxf(fmaxf(st.m[1], mx1), -1e30f);
+        const float a0 = ex2(st.m[0] - mn0), a1 = ex2(st.m[1] - mn1);
+        st.m[0] = mn0; st.m[1] = mn1;
+        st.mt[0] = mn0 + MAX_SLACK; st.mt[1] = mn1 + MAX_SLACK;
+        st.l[0] *= a0; st.l[1] *= a1;
 #pragma unroll
         for (int mt = 0; mt < D / 16; ++mt) {
             st.o[mt][0] *= a0; st.o[mt][1] *= a1; st.o[mt][2] *= a0; st.o[mt][3] *= a1;
         }
     }
+    const float p0 = ex2(s[0] - st.m[0]), p1 = ex2(s[1] - st.m[1]), p2 = ex2(s[2] - st.m[0]), p3 = ex2(s[3] - st.m[1]);
+    st.l[0] += p0 + p2;
+    st.l[1] += p1 + p3;
     // value norms ride on P (fp16, clamped below the fp16 maximum)
     const uint32_t h0 = pack_h2(fminf(p0 * vn0, 65504.f), fminf(p1 * vn0, 65504.f));
     const uint32_t h1 = pack_h2(fminf(p2 * vn1, 65504.f), fminf(p3 * vn1, 65504.f));
@@ -201,6 +221,7 @@ __global__ void __launch_bounds__(NW * 32, DIRECT ? 2 : 1) decode_partial_kernel
     constexpr size_t BODY = partial_smem<D, DIRECT>() - 4 * 16 * sizeof(__half);
     __half* ctab = reinterpret_cast<__half*>(smem + BODY);   // kc_hi, kc_lo, vc_hi, vc_lo (16 each)
 
+    pdl_trigger();     // lets the merge launch get resident early; it waits for this grid to finish
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, hkv = blockIdx.y / p.HG, hg = blockIdx.y % p.HG, b = blockIdx.z;
     const int64_t kvl = int64_t(b) * p.Hkv + hkv;        // lane of the cache arrays
@@ -209,7 +230,7 @@ __global__ void __launch_bounds__(NW * 32, DIRECT ? 2 : 1) decode_partial_kernel
     const int64_t qbase = (int64_t(b) * p.Hq + int64_t(hkv) * p.G + hg * HPG) * D;   // first query head of this group
 
     WarpAcc<D> st;
-    st.m[0] = st.m[1] = -INFINITY;
+    st.m[0] = st.m[1] = st.mt[0] = st.mt[1] = -INFINITY;
     st.l[0] = st.l[1] = 0.f;
 #pragma unroll
     for (int mt = 0; mt < D / 16; ++mt) st.o[mt][0] = st.o[mt][1] = st.o[mt][2] = st.o[mt][3] = 0.f;
@@ -218,6 +239,7 @@ __global__ void __launch_bounds__(NW * 32, DIRECT ? 2 : 1) decode_partial_kernel
 
     if (dense) {
         // ---------------- uncompressed tokens: sink then residual window, raw query ----------------
+        pdl_wait();        // the scaled query copies come from the prep launch
         uint32_t bq[D / 16][2];
         {
             const __half* qh = p.q_raw + qbase + int64_t(g) * D;
@@ -271,8 +293,10 @@ __global__ void __launch_bounds__(NW * 32, DIRECT ? 2 : 1) decode_partial_kernel
             const int which = tid >> 4, k = tid & 15;
             const float* src = which == 0 ? p.kc_hi : which == 1 ? p.kc_lo : which == 2 ? p.vc_hi : p.vc_lo;
             const int bits = which == 0 ? p.kb_hi : which == 1 ? p.kb_lo : which == 2 ? p.vb_hi : p.vb_lo;
-            ctab[tid] = __float2half_rn((src != nullptr && bits > 0 && k < (1 << bits)) ? src[k] : 0.f);
+            const float sc = which == 2 ? p.v_scale_hi : which == 3 ? p.v_scale_lo : 1.f;
+            ctab[tid] = __float2half_rn((src != nullptr && bits > 0 && k < (1 << bits)) ? src[k] * sc : 0.f);
         }
+        pdl_wait();        // the rotated query comes from the prep launch
         __syncthreads();
         uint32_t bq[D / 16][2];
         {
@@ -332,7 +356,7 @@ __global__ void __launch_bounds__(NW * 32, DIRECT ? 2 : 1) decode_partial_kernel
         if (tid < 32) {
             const int which = tid >> 4, k = tid & 15;
             const float* src = which ? p.vc_hi : p.kc_hi;
-            ctab[which * 32 + k] = __float2half_rn(k < (which ? 4 : 16) ? src[k] : 0.f);
+            ctab[which * 32 + k] = __float2half_rn(k < (which ? 4 : 16) ? src[k] * (which ? p.v_scale_hi : 1.f) : 0.f);
         }
         __syncthreads();
         for (int e = tid; e < 256 * 8; e += NW * 32) {     // 4 replicas per 128-bit store
@@ -349,6 +373,7 @@ __global__ void __launch_bounds__(NW * 32, DIRECT ? 2 : 1) decode_partial_kernel
             const uint32_t v0 = *reinterpret_cast<const uint32_t*>(&h0), v1 = *reinterpret_cast<const uint32_t*>(&h1);
             reinterpret_cast<uint4*>(T2)[entry * 8 + q2] = make_uint4(v0, v1, v0, v1);
         }
+        pdl_wait();        // the rotated query comes from the prep launch
         __syncthreads();
         // Query fragments in the byte order of the 4-bit rows: thread t owns coordinates [t*D/4, (t+1)*D/4).
         uint32_t bq[D / 16][2];
@@ -363,84 +388,107 @@ __global__ void __launch_bounds__(NW * 32, DIRECT ? 2 : 1) decode_partial_kernel
         constexpr int KW = D / 2, VW = D / 4;            // bytes per token
         constexpr int KQ = KW / 4 / 4;                   // 32-bit words in a thread's quarter of a key row
         constexpr int VQ = VW / 8 / 4;                   // 32-bit words in a thread's eighth of a value row
-        static_assert(KQ >= 1 && VQ >= 1, "direct path needs d >= 128");
-        const uint8_t* kbase = p.k_hi + kvl * p.c_ls * KW;
-        const uint8_t* vbase = p.v_hi + kvl * p.c_ls * VW;
-        const float* knb = p.k_norms + kvl * p.c_ls;
-        const float* vnb = p.v_norms + kvl * p.c_ls;
-        const uint32_t* T4l = T4 + lane;
-        const uint2* T2l = T2 + (lane & 15);
+        static_assert(KQ >= 1 && VQ >= 1 && KQ % 4 == 0, "direct path needs d a multiple of 128");
+        // 32-bit shared-window addresses of this lane's private table columns: entry e of T4 sits at
+        // t4 + e*128, entry e of T2 at t2 + e*128 (one IMAD each, no 64-bit address arithmetic).
+        const uint32_t t4 = static_cast<uint32_t>(__cvta_generic_to_shared(T4)) + lane * 4;
+        const uint32_t t2 = static_cast<uint32_t>(__cvta_generic_to_shared(T2)) + (lane & 15) * 8;
         const int64_t tile_lo = int64_t(split) * p.p_tps;
         const int64_t tile_hi = min(tile_lo + p.p_tps, (p.c_len + TILE - 1) / TILE);
         const int64_t last = p.c_len - 1;
+        const uint8_t* kbase = p.k_hi + kvl * p.c_ls * KW + t * (KQ * 4);
+        const uint8_t* vbase = p.v_hi + kvl * p.c_ls * VW + g * (VQ * 4);
+        const float* knb = p.k_norms + kvl * p.c_ls;
+        const float* vnb = p.v_norms + kvl * p.c_ls;
 
-        uint32_t kw[2][KQ], vw[4][VQ];
-        float nr[4];
-        auto issue_loads = [&](int64_t tile) {
-            const int64_t tok0 = tile * TILE;
-            const int64_t ta = min(tok0 + g, last), tb = min(tok0 + g + 8, last);
+        struct Raw { uint4 k[2][KQ / 4]; uint32_t v[4][VQ]; float n[4]; };
+        auto issue_loads = [&](Raw& r, int64_t tok0) {
+            if (tok0 + TILE <= p.c_len) {      // whole tile in range: constant offsets from three bases
+                const uint8_t* kp = kbase + (tok0 + g) * KW;
+                const uint8_t* vp = vbase + (tok0 + 2 * t) * VW;
 #pragma unroll
-            for (int i = 0; i < KQ; ++i) {
-                kw[0][i] = __ldg(reinterpret_cast<const uint32_t*>(kbase + ta * KW) + t * KQ + i);
-                kw[1][i] = __ldg(reinterpret_cast<const uint32_t*>(kbase + tb * KW) + t * KQ + i);
-            }
-            const int64_t v0 = min(tok0 + 2 * t, last), v1 = min(tok0 + 2 * t + 1, last);
-            const int64_t v2 = min(tok0 + 2 * t + 8, last), v3 = min(tok0 + 2 * t + 9, last);
+                for (int i = 0; i < KQ / 4; ++i) {
+                    r.k[0][i] = __ldg(reinterpret_cast<const uint4*>(kp) + i);
+                    r.k[1][i] = __ldg(reinterpret_cast<const uint4*>(kp + 8 * KW) + i);
+                }
 #pragma unroll
-            for (int i = 0; i < VQ; ++i) {
-                vw[0][i] = __ldg(reinterpret_cast<const uint32_t*>(vbase + v0 * VW) + g * VQ + i);
-                vw[1][i] = __ldg(reinterpret_cast<const uint32_t*>(vbase + v1 * VW) + g * VQ + i);
-                vw[2][i] = __ldg(reinterpret_cast<const uint32_t*>(vbase + v2 * VW) + g * VQ + i);
-                vw[3][i] = __ldg(reinterpret_cast<const uint32_t*>(vbase + v3 * VW) + g * VQ + i);
+                for (int i = 0; i < VQ; ++i) {
+                    r.v[0][i] = __ldg(reinterpret_cast<const uint32_t*>(vp) + i);
+                    r.v[1][i] = __ldg(reinterpret_cast<const uint32_t*>(vp + VW) + i);
+                    r.v[2][i] = __ldg(reinterpret_cast<const uint32_t*>(vp + 8 * VW) + i);
+                    r.v[3][i] = __ldg(reinterpret_cast<const uint32_t*>(vp + 9 * VW) + i);
+                }
+                r.n[0] = __ldg(knb + tok0 + g); r.n[1] = __ldg(knb + tok0 + g + 8);
+                r.n[2] = __ldg(vnb + tok0 + g); r.n[3] = __ldg(vnb + tok0 + g + 8);
+            } else {                            // the one ragged tile at the very end: clamp every token index
+                const int64_t ta = min(tok0 + g, last), tb = min(tok0 + g + 8, last);
+#pragma unroll
+                for (int i = 0; i < KQ / 4; ++i) {
+                    r.k[0][i] = __ldg(reinterpret_cast<const uint4*>(kbase + ta * KW) + i);
+                    r.k[1][i] = __ldg(reinterpret_cast<const uint4*>(kbase + tb * KW) + i);
+                }
+                const int64_t v0 = min(tok0 + 2 * t, last), v1 = min(tok0 + 2 * t + 1, last);
+                const int64_t v2 = min(tok0 + 2 * t + 8, last), v3 = min(tok0 + 2 * t + 9, last);
+#pragma unroll
+                for (int i = 0; i < VQ; ++i) {
+                    r.v[0][i] = __ldg(reinterpret_cast<const uint32_t*>(vbase + v0 * VW) + i);
+                    r.v[1][i] = __ldg(reinterpret_cast<const uint32_t*>(vbase + v1 * VW) + i);
+                    r.v[2][i] = __ldg(reinterpret_cast<const uint32_t*>(vbase + v2 * VW) + i);
+                    r.v[3][i] = __ldg(reinterpret_cast<const uint32_t*>(vbase + v3 * VW) + i);
+                }
+                r.n[0] = __ldg(knb + ta); r.n[1] = __ldg(knb + tb); r.n[2] = __ldg(vnb + ta); r.n[3] = __ldg(vnb + tb);
             }
-            nr[0] = __ldg(knb + ta); nr[1] = __ldg(knb + tb); nr[2] = __ldg(vnb + ta); nr[3] = __ldg(vnb + tb);
         };
-        int64_t tile = tile_lo + warp;
-        if (tile < tile_hi) issue_loads(tile);
-        for (; tile < tile_hi; tile += NW) {
-            uint32_t ck[2][KQ], cv[4][VQ];
-            float cn[4];
-#pragma unroll
-            for (int i = 0; i < KQ; ++i) { ck[0][i] = kw[0][i]; ck[1][i] = kw[1][i]; }
-#pragma unroll
-            for (int i = 0; i < VQ; ++i) { cv[0][i] = vw[0][i]; cv[1][i] = vw[1][i]; cv[2][i] = vw[2][i]; cv[3][i] = vw[3][i]; }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) cn[i] = nr[i];
-            if (tile + NW < tile_hi) issue_loads(tile + NW);   // next tile's bytes fly while this one is computed
-
-            const int64_t tok0 = tile * TILE;
+        auto compute = [&](const Raw& r, int64_t tok0) {
             float s[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
-                // bytes 2ks, 2ks+1 of this thread's quarter row
-                const uint32_t w0 = ck[0][ks >> 1], w1 = ck[1][ks >> 1];
-                const int sh = (ks & 1) * 16;
-                const uint32_t a0 = T4l[((w0 >> sh) & 0xFFu) * 32];
-                const uint32_t a2 = T4l[((w0 >> (sh + 8)) & 0xFFu) * 32];
-                const uint32_t a1 = T4l[((w1 >> sh) & 0xFFu) * 32];
-                const uint32_t a3 = T4l[((w1 >> (sh + 8)) & 0xFFu) * 32];
+                // bytes 2ks, 2ks+1 of this thread's quarter row, for tokens g and g+8
+                const uint4& q0 = r.k[0][ks >> 3];
+                const uint4& q1 = r.k[1][ks >> 3];
+                const int wi = (ks >> 1) & 3;
+                const uint32_t w0 = wi == 0 ? q0.x : wi == 1 ? q0.y : wi == 2 ? q0.z : q0.w;
+                const uint32_t w1 = wi == 0 ? q1.x : wi == 1 ? q1.y : wi == 2 ? q1.z : q1.w;
+                const int b0 = (ks & 1) * 2;
+                const uint32_t a0 = lds32(__byte_perm(w0, 0, 0x4440 | b0) * 128u + t4);
+                const uint32_t a1 = lds32(__byte_perm(w1, 0, 0x4440 | b0) * 128u + t4);
+                const uint32_t a2 = lds32(__byte_perm(w0, 0, 0x4440 | (b0 + 1)) * 128u + t4);
+                const uint32_t a3 = lds32(__byte_perm(w1, 0, 0x4440 | (b0 + 1)) * 128u + t4);
                 mma16816(s, a0, a1, a2, a3, bq[ks][0], bq[ks][1]);
             }
             uint32_t bp[2];
-            softmax_step<D>(s, cn[0], cn[1], cn[2], cn[3], tok0 + g < p.c_len, tok0 + g + 8 < p.c_len, st, bp);
+            softmax_step<D>(s, r.n[0], r.n[1], r.n[2], r.n[3], tok0 + g < p.c_len, tok0 + g + 8 < p.c_len, st, bp);
 #pragma unroll
             for (int i = 0; i < VQ; ++i) {
                 // interleave the 2-bit codes of a token pair: nibble k of X = (A code 2k) | (B code 2k) << 2
-                const uint32_t x0 = (cv[0][i] & 0x33333333u) | ((cv[1][i] << 2) & 0xCCCCCCCCu);
-                const uint32_t y0 = ((cv[0][i] >> 2) & 0x33333333u) | (cv[1][i] & 0xCCCCCCCCu);
-                const uint32_t x1 = (cv[2][i] & 0x33333333u) | ((cv[3][i] << 2) & 0xCCCCCCCCu);
-                const uint32_t y1 = ((cv[2][i] >> 2) & 0x33333333u) | (cv[3][i] & 0xCCCCCCCCu);
+                const uint32_t x0 = (r.v[0][i] & 0x33333333u) | ((r.v[1][i] << 2) & 0xCCCCCCCCu);
+                const uint32_t y0 = ((r.v[0][i] >> 2) & 0x33333333u) | (r.v[1][i] & 0xCCCCCCCCu);
+                const uint32_t x1 = (r.v[2][i] & 0x33333333u) | ((r.v[3][i] << 2) & 0xCCCCCCCCu);
+                const uint32_t y1 = ((r.v[2][i] >> 2) & 0x33333333u) | (r.v[3][i] & 0xCCCCCCCCu);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const uint2 fa = T2l[((x0 >> (8 * k)) & 0xFFu) * 16];   // rows g      , tokens 2t,2t+1   -> m-tiles 2k, 2k+1
-                    const uint2 fb = T2l[((y0 >> (8 * k)) & 0xFFu) * 16];   // rows g + 8
-                    const uint2 fc = T2l[((x1 >> (8 * k)) & 0xFFu) * 16];   // rows g      , tokens 2t+8,2t+9
-                    const uint2 fd = T2l[((y1 >> (8 * k)) & 0xFFu) * 16];
+                    const uint2 fa = lds64(__byte_perm(x0, 0, 0x4440 | k) * 128u + t2);   // rows g,   tokens 2t,2t+1   -> m-tiles 2k, 2k+1
+                    const uint2 fb = lds64(__byte_perm(y0, 0, 0x4440 | k) * 128u + t2);   // rows g+8
+                    const uint2 fc = lds64(__byte_perm(x1, 0, 0x4440 | k) * 128u + t2);   // rows g,   tokens 2t+8,2t+9
+                    const uint2 fd = lds64(__byte_perm(y1, 0, 0x4440 | k) * 128u + t2);
                     const int mt = i * 8 + 2 * k;
                     mma16816(st.o[mt], fa.x, fb.x, fc.x, fd.x, bp[0], bp[1]);
                     mma16816(st.o[mt + 1], fa.y, fb.y, fc.y, fd.y, bp[0], bp[1]);
                 }
             }
+        };
+        // two register buffers, loads for the next tile in flight while the current one is computed
+        Raw ra, rb;
+        int64_t tile = tile_lo + warp;
+        if (tile < tile_hi) issue_loads(ra, tile * TILE);
+        while (tile < tile_hi) {
+            if (tile + NW < tile_hi) issue_loads(rb, (tile + NW) * TILE);
+            compute(ra, tile * TILE);
+            tile += NW;
+            if (tile >= tile_hi) break;
+            if (tile + NW < tile_hi) issue_loads(ra, (tile + NW) * TILE);
+            compute(rb, tile * TILE);
+            tile += NW;
         }
     }
 
@@ -490,38 +538,95 @@ __global__ void __launch_bounds__(NW * 32, DIRECT ? 2 : 1) decode_partial_kernel
     }
 }
 
-// grid (Hq, B), 128 threads: merge the splits of one query head and undo the rotation once.
-__global__ void __launch_bounds__(128) decode_merge_kernel(DecodeParams p) {
-    __shared__ float s_rot[256];
-    __shared__ float s_w[512];
-    const int h = blockIdx.x, b = blockIdx.y, d = p.D;
+// grid (Hq, B), 256 threads: merge the splits of one query head and undo the rotation once.
+// Three short phases, each a single round of independent loads: (1) split weights from the per-split
+// (max, sum) pairs, (2) weighted sum of the partial accumulators over splits, (3) the d x d product with R.
+constexpr int MERGE_T = 256, MAX_SPLITS = 512;
+__global__ void __launch_bounds__(MERGE_T) decode_merge_kernel(DecodeParams p) {
+    __shared__ float s_w[MAX_SPLITS];
+    __shared__ float s_part[4][256];   // partial sums per thread group
+    __shared__ float s_rot[256], s_raw[256];
+    __shared__ float s_inv;
+    pdl_wait();        // partial accumulators come from the launch just before this one
+    pdl_trigger();
+    const int h = blockIdx.x, b = blockIdx.y, d = p.D, tid = threadIdx.x;
     const int hkv = h / p.G, hl = h - hkv * p.G, hg = hl / HPG, hs = hl - hg * HPG;
-    const int S = p.n_ps + p.n_ds;
+    const int S = p.n_ps + p.n_ds, SL = p.slots;
     const int64_t base = ((int64_t(b) * p.Hkv + hkv) * p.HG + hg) * S;
-    float M = -INFINITY;
-    const int SL = p.slots;
-    for (int s = 0; s < S; ++s) M = fmaxf(M, p.part_ml[(base + s) * (SL * 2) + 2 * hs]);
-    float L = 0.f;
-    for (int s = 0; s < S; ++s) {
-        const float ms = p.part_ml[(base + s) * (SL * 2) + 2 * hs];
-        const float w = (ms == -INFINITY) ? 0.f : ex2(ms - M);
-        L = fmaf(w, p.part_ml[(base + s) * (SL * 2) + 2 * hs + 1], L);
-        if (threadIdx.x == 0 && s < 512) s_w[s] = w;
+    // (1) warp 0: weights exp2(m_s - M) and the normaliser
+    if (tid < 32) {
+        float mloc[MAX_SPLITS / 32], lloc[MAX_SPLITS / 32];
+        float M = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < MAX_SPLITS / 32; ++i) {
+            const int sidx = tid + 32 * i;
+            mloc[i] = -INFINITY; lloc[i] = 0.f;
+            if (sidx < S) {
+                const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + ((base + sidx) * SL + hs) * 2);
+                mloc[i] = ml.x; lloc[i] = ml.y;
+            }
+            M = fmaxf(M, mloc[i]);
+        }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+        float L = 0.f;
+#pragma unroll
+        for (int i = 0; i < MAX_SPLITS / 32; ++i) {
+            const int sidx = tid + 32 * i;
+            const float w = (mloc[i] == -INFINITY) ? 0.f : ex2(mloc[i] - M);
+            if (sidx < S) s_w[sidx] = w;
+            L = fmaf(w, lloc[i], L);
+        }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+        if (tid == 0) s_inv = 1.f / L;
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < d; c += blockDim.x) {
-        float acc = 0.f;
-        for (int s = 0; s < p.n_ps; ++s) acc = fmaf(s_w[s], p.part_o[((base + s) * SL + hs) * d + c], acc);
-        s_rot[c] = acc;
+    // (2) thread (c, part): sum over the splits congruent to `part`
+    const int JW = d >= 128 ? 128 : d, parts = MERGE_T / JW;
+    const int part = tid / JW, cj = tid - part * JW;
+    for (int c = cj; c < d; c += JW) {
+        float rot = 0.f, raw = 0.f;
+        if (part < parts) {
+#pragma unroll 4
+            for (int sidx = part; sidx < p.n_ps; sidx += parts) rot = fmaf(s_w[sidx], p.part_o[((base + sidx) * SL + hs) * d + c], rot);
+            for (int sidx = p.n_ps + part; sidx < S; sidx += parts) raw = fmaf(s_w[sidx], p.part_o[((base + sidx) * SL + hs) * d + c], raw);
+        }
+        __syncthreads();
+        if (part < parts) { s_part[part][c] = rot; }
+        __syncthreads();
+        if (part == 0) {
+            float v = 0.f;
+            for (int q = 0; q < parts; ++q) v += s_part[q][c];
+            const int v_half = p.vb_lo ? d / 2 : d;
+            s_rot[c] = v / (c < v_half ? p.v_scale_hi : p.v_scale_lo);
+        }
+        __syncthreads();
+        if (part < parts) { s_part[part][c] = raw; }
+        __syncthreads();
+        if (part == 0) {
+            float v = 0.f;
+            for (int q = 0; q < parts; ++q) v += s_part[q][c];
+            s_raw[c] = v;
+        }
     }
     __syncthreads();
-    const float inv = 1.f / L;
-    for (int j = threadIdx.x; j < d; j += blockDim.x) {
-        float acc = 0.f;
-        for (int s = p.n_ps; s < S; ++s) acc = fmaf(s_w[s], p.part_o[((base + s) * SL + hs) * d + j], acc);
+    // (3) thread (j, part): rows [part*d/parts, (part+1)*d/parts) of R, column j  (y @ R, rotation.py:68-78)
+    for (int j = cj; j < d; j += JW) {
         float r = 0.f;
-        for (int c = 0; c < d; ++c) r = fmaf(s_rot[c], __ldg(p.rot + int64_t(c) * d + j), r);   // @ R, rotation.py:68-78
-        store_from_f32(p.out, p.out_dtype, (int64_t(b) * p.Hq + h) * d + j, (acc + r) * inv);
+        if (part < parts) {
+            const int c0 = part * (d / parts), c1 = c0 + d / parts;
+#pragma unroll 8
+            for (int c = c0; c < c1; ++c) r = fmaf(s_rot[c], __ldg(p.rot + int64_t(c) * d + j), r);
+        }
+        __syncthreads();
+        if (part < parts) s_part[part][j] = r;
+        __syncthreads();
+        if (part == 0) {
+            float v = s_raw[j];
+            for (int q = 0; q < parts; ++q) v += s_part[q][j];
+            store_from_f32(p.out, p.out_dtype, (int64_t(b) * p.Hq + h) * d + j, v * s_inv);
+        }
     }
 }
 
@@ -529,6 +634,7 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(DecodeParams p) {
 static int g_tune_ctas_per_sm = 2;     // CTAs the partial kernel keeps resident per SM (split heuristic)
 static int g_tune_force_general = 0;   // 1: never take the direct path (testing)
 static int g_tune_splits = 0;          // > 0: fixed number of packed splits
+static int g_tune_pdl = 1;             // programmatic dependent launch between the three kernels
 
 static int sm_count() {
     static int n = 0;
@@ -548,19 +654,21 @@ static SplitPlan plan_splits(int batch, int n_q_heads, int n_kv_heads, int64_t c
     s.hg = (G + HPG - 1) / HPG;
     const int64_t lanes = int64_t(batch) * n_kv_heads * s.hg;
     const int64_t p_tiles = (c_len + TILE - 1) / TILE, d_tiles = (dense_len + TILE - 1) / TILE;
+    if (d_tiles > 0) {
+        s.d_tps = 2 * NW;   // two tiles per warp
+        s.n_ds = int((d_tiles + s.d_tps - 1) / s.d_tps);
+        if (s.n_ds > 64) { s.d_tps = (d_tiles + 63) / 64; s.n_ds = int((d_tiles + s.d_tps - 1) / s.d_tps); }
+    }
     if (p_tiles > 0) {
-        int64_t want = g_tune_splits > 0 ? g_tune_splits : (int64_t(sms) * g_tune_ctas_per_sm + lanes - 1) / lanes;
+        // all CTAs of the grid resident at once: (packed + dense splits) * lanes <= SMs * CTAs per SM
+        const int64_t slots = int64_t(sms) * g_tune_ctas_per_sm;
+        int64_t want = g_tune_splits > 0 ? g_tune_splits : slots / lanes - s.n_ds;
         const int64_t max_useful = (p_tiles + 2 * NW - 1) / (2 * NW);   // at least two tiles per warp
         if (want > max_useful) want = max_useful;
         if (want < 1) want = 1;
-        if (want > 448) want = 448;
+        if (want > MAX_SPLITS - 64) want = MAX_SPLITS - 64;
         s.p_tps = (p_tiles + want - 1) / want;
         s.n_ps = int((p_tiles + s.p_tps - 1) / s.p_tps);
-    }
-    if (d_tiles > 0) {
-        s.d_tps = NW;   // one tile per warp
-        s.n_ds = int((d_tiles + s.d_tps - 1) / s.d_tps);
-        if (s.n_ds > 64) { s.n_ds = 64; s.d_tps = (d_tiles + 63) / 64; s.n_ds = int((d_tiles + s.d_tps - 1) / s.d_tps); }
     }
     return s;
 }
@@ -582,6 +690,21 @@ static WsLayout ws_layout(int batch, int n_q_heads, int n_kv_heads, int d, const
     return w;
 }
 
+// Launch with programmatic stream serialisation: the kernel may become resident before its predecessor
+// on the stream has finished; every kernel here calls griddepcontrol.wait before touching dependent data.
+template <typename K> static int launch_pdl(K kernel, dim3 grid, unsigned block, size_t smem, cudaStream_t s,
+                                            const DecodeParams& p, const char* what) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = dim3(block); cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = g_tune_pdl ? 1 : 0;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, p);
+    if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+    return TQ_OK;
+}
+
 template <int D, bool DIRECT> static int launch_partial(const DecodeParams& p, cudaStream_t s) {
     constexpr size_t smem = partial_smem<D, DIRECT>();
     static bool set[16] = {false};
@@ -593,8 +716,7 @@ template <int D, bool DIRECT> static int launch_partial(const DecodeParams& p, c
         set[dev] = true;
     }
     dim3 grid(unsigned(p.n_ps + p.n_ds), unsigned(p.Hkv * p.HG), unsigned(p.B));
-    decode_partial_kernel<D, DIRECT><<<grid, NW * 32, smem, s>>>(p);
-    return check_launch("tq_decode_attn (partial)");
+    return launch_pdl(decode_partial_kernel<D, DIRECT>, grid, NW * 32, smem, s, p, "tq_decode_attn (partial)");
 }
 
 }  // namespace tq
@@ -606,9 +728,31 @@ extern "C" int tq_set_tuning(const char* key, int value) {
     const std::string_view k(key);
     if (k == "decode_ctas_per_sm" && value >= 1 && value <= 8) g_tune_ctas_per_sm = value;
     else if (k == "decode_force_general" && (value == 0 || value == 1)) g_tune_force_general = value;
-    else if (k == "decode_splits" && value >= 0 && value <= 448) g_tune_splits = value;
+    else if (k == "decode_pdl" && (value == 0 || value == 1)) g_tune_pdl = value;
+    else if (k == "decode_splits" && value >= 0 && value <= MAX_SPLITS - 64) g_tune_splits = value;
     else return fail(TQ_ERR_INVALID, "tq_set_tuning: unknown key or bad value: %s=%d", key, value);
     return TQ_OK;
+}
+
+extern "C" float tq_fp16_table_scale(const float* centroids_host, int n) {
+    // Scale s in [1, 2) that minimises the worst relative error of fp16(s * c_i): the decode kernel keeps
+    // value centroids in fp16, and with only 2^bits distinct levels their rounding error is systematic.
+    if (!centroids_host || n <= 0) return 1.f;
+    float best = 1.f;
+    double best_err = 1e30;
+    for (int i = 0; i < (1 << 16); ++i) {
+        const float sc = 1.f + float(i) / float(1 << 16);
+        double worst = 0.0;
+        for (int k = 0; k < n; ++k) {
+            const float v = centroids_host[k] * sc;
+            if (v == 0.f) continue;
+            const float r = __half2float(__float2half_rn(v));
+            const double e = fabs(double(r) - double(v)) / fabs(double(v));
+            if (e > worst) worst = e;
+        }
+        if (worst < best_err) { best_err = worst; best = sc; }
+    }
+    return best;
 }
 
 extern "C" size_t tq_decode_workspace_bytes(int batch, int n_q_heads, int n_kv_heads, int d, int64_t c_len,
@@ -651,7 +795,7 @@ extern "C" int tq_decode_attn(const tq_decode_args* a, void* stream) {
     const SplitPlan sp = plan_splits(a->batch, a->n_q_heads, a->n_kv_heads, a->c_len, dense_len, sm_count());
     const WsLayout wl = ws_layout(a->batch, a->n_q_heads, a->n_kv_heads, d, sp);
     if (wl.total > a->workspace_bytes) return fail(TQ_ERR_INVALID, "tq_decode_attn: workspace %zu B < %zu B", a->workspace_bytes, wl.total);
-    if (sp.n_ps + sp.n_ds > 512) return fail(TQ_ERR_UNSUPPORTED, "tq_decode_attn: too many splits");
+    if (sp.n_ps + sp.n_ds > MAX_SPLITS) return fail(TQ_ERR_UNSUPPORTED, "tq_decode_attn: too many splits");
 
     DecodeParams p{};
     p.B = a->batch; p.Hq = a->n_q_heads; p.Hkv = a->n_kv_heads; p.G = p.Hq / p.Hkv; p.HG = sp.hg; p.D = d; p.slots = std::min(p.G, HPG);
@@ -665,14 +809,15 @@ extern "C" int tq_decode_attn(const tq_decode_args* a, void* stream) {
     p.sink_len = a->sink_len; p.sink_ls = a->sink_lane_stride; p.res_len = a->res_len; p.res_ls = a->res_lane_stride;
     p.n_ps = sp.n_ps; p.n_ds = sp.n_ds; p.p_tps = sp.p_tps; p.d_tps = sp.d_tps;
     p.q = a->q; p.q_dtype = a->q_dtype; p.scale = a->scale; p.rot = a->rot;
+    p.v_scale_hi = a->v_cent_scale_hi > 0.f ? a->v_cent_scale_hi : 1.f;
+    p.v_scale_lo = a->v_cent_scale_lo > 0.f ? a->v_cent_scale_lo : 1.f;
     unsigned char* ws = static_cast<unsigned char*>(a->workspace);
     p.q_rot = reinterpret_cast<__half*>(ws + wl.q_rot); p.q_raw = reinterpret_cast<__half*>(ws + wl.q_raw);
     p.part_o = reinterpret_cast<float*>(ws + wl.part_o); p.part_ml = reinterpret_cast<float*>(ws + wl.part_ml);
     p.out = a->out; p.out_dtype = a->out_dtype;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    decode_prep_kernel<<<unsigned(p.B * p.Hq), 256, 0, s>>>(p);
-    int rc = check_launch("tq_decode_attn (prep)");
+    int rc = launch_pdl(decode_prep_kernel, dim3(unsigned(p.B * p.Hq)), unsigned(d), 0, s, p, "tq_decode_attn (prep)");
     if (rc) return rc;
 
     const bool direct = !g_tune_force_general && d == 128 && a->c_len > 0 && a->k_bits_hi == 4 && a->k_bits_lo == 0 &&
@@ -684,6 +829,5 @@ extern "C" int tq_decode_attn(const tq_decode_args* a, void* stream) {
     else rc = launch_partial<256, false>(p, s);
     if (rc) return rc;
 
-    decode_merge_kernel<<<dim3(unsigned(p.Hq), unsigned(p.B)), 128, 0, s>>>(p);
-    return check_launch("tq_decode_attn (merge)");
+    return launch_pdl(decode_merge_kernel, dim3(unsigned(p.Hq), unsigned(p.B)), MERGE_T, 0, s, p, "tq_decode_attn (merge)");
 }

@@ -54,13 +54,28 @@ def test_update_and_fetch_matches_reference(golden, scenarios, name):
 
 @pytest.mark.parametrize("name", ("c_k4v2", "c_chunk", "c_frac", "c_w0"))
 def test_attend_matches_attention_over_reference_cache(golden, scenarios, name):
-    """Packed decode == float32 softmax attention over the reference's dense output, within 1e-3."""
-    c, ok, ov, sc = _replay(name, golden, scenarios)
+    """Packed decode over the REFERENCE's own packed state == float32 softmax attention over the reference's
+    dense output, within 1e-3 (state injected so both sides see identical codes)."""
+    from mlx_turboquant_b200 import TurboQuantKVCache
+    sc = scenarios[name]
+    ms = sc["meta_state"]
+    s, n, m = int(ms["sink_len"]), int(ms["fp16_len"]), int(ms["compressed_len"])
+    rk, rv = golden[name + "_out_k"], golden[name + "_out_v"]
+    total = rk.shape[2]
+    c = TurboQuantKVCache(num_kv_heads=2, **sc["cfg"])
+    f16 = lambda a: cu(np.ascontiguousarray(a).astype(np.float16))   # noqa: E731 - sink / recent tokens were fp16 inputs
+    g = lambda key: cu(golden[key]) if key in golden else None   # noqa: E731
+    c.state = (f16(rk[:, :, total - n:]) if n else None, f16(rv[:, :, total - n:]) if n else None,
+               g(name + "_state2"), g(name + "_state3"), g(name + "_state4"), g(name + "_state5"),
+               f16(rk[:, :, :s]) if s else None, f16(rv[:, :, :s]) if s else None, g(name + "_state8"), g(name + "_state9"))
+    c.meta_state = dict(ms, fp16_capacity=str(n))
+    assert c._compressed_len == m
     q = cu(golden[name + "_q"])
-    out = c.attend(q)
+    assert c.attend(q).dtype == q.dtype
+    out = c.attend(q, out_dtype=torch.float32)
     ref = golden[name + "_attn"]
-    assert tuple(out.shape) == ref.shape and out.dtype == q.dtype
-    np.testing.assert_allclose(host(out.float()), ref, rtol=0, atol=1e-3 * np.abs(ref).max())
+    assert tuple(out.shape) == ref.shape
+    np.testing.assert_allclose(host(out), ref, rtol=0, atol=1e-3 * np.abs(ref).max())
 
 
 def test_incremental_decode_and_lengths():
