@@ -140,7 +140,9 @@ typedef struct {
     const void *sink_k, *sink_v; int64_t sink_len, sink_lane_stride;   /* stride in tokens */
     const void *res_k, *res_v;   int64_t res_len,  res_lane_stride;
     void* out; int out_dtype;                /* (batch, n_q_heads, d) */
-    void* workspace; size_t workspace_bytes; /* >= tq_decode_workspace_bytes(...) */
+    /* >= tq_decode_workspace_bytes(...), 256-byte aligned, ZERO-FILLED before its first use (it holds
+     * arrival counters that every launch leaves at zero again); one buffer per stream in flight. */
+    void* workspace; size_t workspace_bytes;
 } tq_decode_args;
 
 /* Scratch bytes tq_decode_attn needs for these sizes (host-side arithmetic only). */
@@ -159,7 +161,7 @@ float tq_fp16_table_scale(const float* centroids_host, int n);
 
 /* Host-side tuning knobs of the split heuristic (process-wide; no reference counterpart):
  *   "decode_ctas_per_sm" 1..8, "decode_splits" 0 (auto)..448, "decode_force_general" 0/1,
- *   "decode_pdl" 0/1 (programmatic dependent launch between the kernels of one call).
+ *   "decode_pdl" 0/1 (programmatic dependent launch: a call's prologue overlaps the previous kernel's tail).
  * Changing them changes tq_decode_workspace_bytes for the same sizes. */
 int tq_set_tuning(const char* key, int value);
 

@@ -188,7 +188,17 @@ class TurboQuantKVCache:
             raise ValueError(f"state must have 6, 8, 10 or 14 elements, got {n}")
         v = tuple(v) + (None,) * (14 - n)
         self.keys, self.values = v[0], v[1]
-        own = lambda t: None if t is None else t.contiguous()   # noqa: E731
+        def own(t):
+            """Adopt a packed array as storage: contiguous, token capacity padded to a multiple of 16."""
+            if t is None:
+                return None
+            cap = _round_up(max(t.shape[2], 16), 16)
+            if cap == t.shape[2] and t.is_contiguous():
+                return t
+            new = torch.zeros(t.shape[:2] + (cap,) + t.shape[3:], dtype=t.dtype, device=t.device)
+            new[:, :, :t.shape[2]] = t
+            return new
+        n_comp = None if v[2] is None else v[2].shape[2]
         self._k.hi, self._k.norms, self._v.hi, self._v.norms = own(v[2]), own(v[3]), own(v[4]), own(v[5])
         if n >= 8:
             self.sink_keys, self.sink_values = v[6], v[7]
@@ -196,8 +206,8 @@ class TurboQuantKVCache:
             self._k.lo, self._v.lo = own(v[8]), own(v[9])
         if n >= 14:
             self._k.qbits, self._k.qgamma, self._v.qbits, self._v.qgamma = own(v[10]), own(v[11]), own(v[12]), own(v[13])
-        if self._k.hi is not None:
-            self._compressed_len = self._k.hi.shape[2]
+        if n_comp is not None:
+            self._compressed_len = n_comp
         self._dense_k = self._dense_v = None
         self._dense_len = 0
         for t in v:

@@ -1,59 +1,35 @@
 // One decode step of attention computed directly on the compressed KV cache
-// [fp16 sink | packed middle | fp16 residual window], split over the sequence (flash-decode).
+// [fp16 sink | packed middle | fp16 residual window], split over the sequence (flash-decode), in ONE launch.
 //
-// Three launches per call:
-//   decode_prep_kernel     rotates the query once (q @ R^T), folds scale*log2(e) in, stores fp16 copies
-//   decode_partial_kernel  grid (splits, kv_heads * head_groups, batch); every CTA owns a token range of
-//                          either the packed middle or the uncompressed regions and produces one
-//                          (max, sum, weighted-V) partial per query head
-//   decode_merge_kernel    log-sum-exp merge of the partials, one inverse rotation (@ R) of the part that
-//                          was accumulated in rotated space, normalisation, output
+// decode_attn_kernel, grid (splits, kv_heads * head_groups, batch).  Every CTA
+//   1. rotates the query heads of its GQA group once (q @ R^T, float32), folds scale*log2(e) in and keeps
+//      fp16 copies in shared memory (CTAs that own uncompressed tokens keep the unrotated query instead);
+//   2. runs the online-softmax attention over its token range of either the packed middle or the
+//      uncompressed regions; values of the packed middle are accumulated in ROTATED space;
+//   3. reduces its warps and writes one (max, sum, weighted-V) partial per query head to the workspace;
+//   4. bumps a counter; the CTA that arrives last for a (sequence, KV head, head group) merges all partials
+//      (log-sum-exp), undoes the rotation once (@ R), adds the unrotated part, normalises and writes the
+//      output.  No CTA ever waits for another one: the last arrival is detected with one atomic add.
 //
-// Arithmetic: warps work on tiles of 16 tokens with mma.sync.m16n8k16 (fp16 operands, fp32
-// accumulation): S[16 tokens x 8 heads] = K_tile . Q^T, online softmax in registers, P transposed with
-// movmatrix, O^T[d x 8 heads] += V_tile^T . P^T.  Tokens are the M dimension so a GQA group of up to 8
-// query heads shares every unpacked key/value.  The kernel is bound by HBM bytes (packed codes + norms),
-// not by the tensor pipe; the contraction shape is tiny (N = 8).
+// Arithmetic: warps work on tiles of 16 tokens with mma.sync.m16n8k16 (fp16 operands, fp32 accumulation):
+// S[16 tokens x 8 heads] = K_tile . Q^T, online softmax in registers, P transposed with movmatrix,
+// O^T[d x 8 heads] += V_tile^T . P^T.  Tokens are the M dimension so a GQA group of up to 8 query heads
+// shares every unpacked key/value.  The kernel is bound by HBM bytes (packed codes + norms), not by the
+// tensor pipe; the contraction shape is tiny (N = 8), which is why the warp-level MMA is used here.
 //
 // Two ways to build the K / V^T operand fragments:
-//   * general: a warp unpacks (or, for the fp16 regions, copies) its tile into shared memory as fp16 and
-//     reads fragments back with ldmatrix - any bit width, fractional splits, any d multiple of 16;
-//   * direct (4-bit keys, 2-bit values, d = 128): packed words go from global memory to registers and
-//     are turned into fragments through bank-conflict-free lookup tables in shared memory
-//     (byte -> half2), never touching shared memory with unpacked data.  The coordinate order inside a
-//     fragment is permuted to match the byte layout; the query fragments and the output mapping use the
-//     same permutation, so results are unchanged.
+//   * general: a warp unpacks (or, for the fp16 regions, copies) its tile into shared memory as fp16 and reads
+//     fragments back with ldmatrix - any bit width, fractional splits, d in {64, 96, 128, 256};
+//   * direct (4-bit keys, 2-bit values, d = 128): raw packed tiles stream through a per-warp cp.async ring and
+//     are turned into fragments through bank-conflict-free lookup tables in shared memory (byte -> half2),
+//     never touching shared memory with unpacked data.  The coordinate order inside a fragment is permuted to
+//     match the byte layout; the query fragments and the output mapping use the same permutation.
 #include <algorithm>
 #include <string_view>
 
-#include "common.cuh"
+#include "decode.cuh"
 
 namespace tq {
-
-constexpr int NW = 8;                 // warps per CTA
-constexpr int TILE = 16;              // tokens per warp tile
-constexpr int HPG = 8;                // query heads per head group (the mma N dimension)
-constexpr float LOG2E = 1.4426950408889634f;
-
-struct DecodeParams {
-    int B, Hq, Hkv, G, HG, D;
-    int slots;                         // head slots per partial = min(G, 8)
-    int64_t c_len, c_ls;
-    int kb_hi, kb_lo, vb_hi, vb_lo;
-    const uint8_t *k_hi, *k_lo, *v_hi, *v_lo;
-    const float *k_norms, *v_norms;
-    const float *kc_hi, *kc_lo, *vc_hi, *vc_lo;
-    int dense_dtype;
-    const void *sink_k, *sink_v, *res_k, *res_v;
-    int64_t sink_len, sink_ls, res_len, res_ls;
-    int n_ps, n_ds;                    // packed / dense splits
-    int64_t p_tps, d_tps;              // tiles per split
-    const void* q; int q_dtype; float scale; const float* rot;
-    float v_scale_hi, v_scale_lo;      // value centroids are multiplied by this before the fp16 cast (undone in the merge)
-    __half *q_rot, *q_raw;             // workspace: (B, Hq, D) each, pre-scaled
-    float *part_o, *part_ml;           // workspace: (B, Hkv, HG, S, slots, D) and (.., slots, 2)
-    void* out; int out_dtype;
-};
 
 // ---- small PTX wrappers --------------------------------------------------------------------------
 __device__ __forceinline__ float ex2(float x) {
@@ -82,17 +58,36 @@ __device__ __forceinline__ uint32_t movm_t(uint32_t a) {
     asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
     return d;
 }
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+// Lookups in tables that are constant for the lifetime of the CTA: plain (non-volatile) asm so the compiler
+// may hoist and batch them ahead of the MMAs that consume them.
+__device__ __forceinline__ uint32_t lut32(uint32_t addr) {
     uint32_t v;
-    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
-__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+__device__ __forceinline__ uint2 lut64(uint32_t addr) {
     uint2 v;
-    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    asm("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
     return v;
 }
-// Programmatic dependent launch: wait for the producer grid / let the consumer grid start its prologue.
+// Reads of the cp.async ring: ordered after the wait / warp barrier that makes the data visible.
+__device__ __forceinline__ uint32_t ring32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 ring128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+// 16-byte asynchronous global -> shared copy; bytes past src_bytes are zero-filled (0 = read nothing).
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// Programmatic dependent launch: wait for the previous grid on the stream / let the next grid start its prologue.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
@@ -100,29 +95,20 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// ---- query preparation ----------------------------------------------------------------------------
-// grid (B*Hq), D threads.  q_rot[j] = sum_k q[k] R[j][k]  (rotation.py:81-110); both copies are scaled by
-// scale*log2(e) so the softmax can use exp2.  Thread j streams row j of R with independent 128-bit loads.
-__global__ void __launch_bounds__(256) decode_prep_kernel(DecodeParams p) {
-    __shared__ __align__(16) float sq[256];
-    pdl_trigger();     // the partial kernel may start building its tables right away
-    pdl_wait();        // the query (and the workspace) may come from the launch just before this one
-    const int bh = blockIdx.x, d = p.D, j = threadIdx.x;
-    const float f = p.scale * LOG2E;
-    const float v = load_as_f32(p.q, p.q_dtype, int64_t(bh) * d + j);
-    sq[j] = v;
-    __syncthreads();
-    const float4* row = reinterpret_cast<const float4*>(p.rot + int64_t(j) * d);
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll 8
-    for (int k = 0; k < d / 4; ++k) {
-        const float4 r = __ldg(row + k);
-        const float4 x = *reinterpret_cast<const float4*>(sq + 4 * k);
-        a0 = fmaf(x.x, r.x, a0); a1 = fmaf(x.y, r.y, a1); a2 = fmaf(x.z, r.z, a2); a3 = fmaf(x.w, r.w, a3);
+#ifdef TQ_TIMING
+// Phase timestamps (development builds only): [cta][8] globaltimer values.
+__device__ unsigned long long g_tq_timing[4096 * 16];
+__device__ __forceinline__ void stamp(int cta, int slot) {
+    if (threadIdx.x == 0 && cta < 4096) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_tq_timing[cta * 16 + slot] = t;
     }
-    p.q_raw[int64_t(bh) * d + j] = __float2half_rn(v * f);
-    p.q_rot[int64_t(bh) * d + j] = __float2half_rn(((a0 + a1) + (a2 + a3)) * f);
 }
+#define TQ_STAMP(slot) stamp(int(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)), slot)
+#else
+#define TQ_STAMP(slot)
+#endif
 
 // ---- per-warp running softmax state ------------------------------------------------------------------
 constexpr float MAX_SLACK = 6.f;   // scores may exceed the running reference by 2^6 before it is refreshed
@@ -169,20 +155,41 @@ __device__ __forceinline__ void softmax_step(float (&s)[4], float kn0, float kn1
     bp[1] = movm_t(h1);   // tokens 2t+8,2t+9 x head g
 }
 
-// Shared-memory layout of one CTA (a CTA is either "packed" or "dense", so the regions overlap):
+// ---- shared memory plan ----------------------------------------------------------------------------------
+// BODY is reused by phases that never overlap in time:
 //   general staging: per warp  Ks[16][D+8] + Vs[16][D+8] halves
-//   direct tables:   T4 [256][32] u32 (32 KB) + T2 [256][16] uint2 (32 KB)
-//   final reduction: per warp  o[D][8] floats + m[8] + l[8]
+//   direct:          T4 [256][32] u32 (32 KB) + T2 [256][16] uint2 (32 KB) + per-warp cp.async ring + R (64 KB)
+//   CTA reduction:   per warp  o[D][8] floats + m[8] + l[8], then weights [NW][8]
+//   merge (last CTA): split weights [8][MAX_SPLITS], rotated / raw sums [8][D] each, partial products
+// After BODY: float query [8][D], fp16 query [8][D], four 16-entry fp16 centroid tables, a few scalars.
+constexpr int MERGE_CPARTS = 4;       // thread slabs of the d x d product with R in the epilogue
 template <int D> __host__ __device__ constexpr int stage_ld() { return D + 8; }
-template <int D> __host__ __device__ constexpr size_t stage_bytes() { return size_t(NW) * 2 * TILE * stage_ld<D>() * sizeof(__half); }
-template <int D> __host__ __device__ constexpr size_t reduce_bytes() { return size_t(NW) * (D * HPG + 2 * HPG) * sizeof(float); }
-constexpr size_t TABLE_BYTES = 65536;
-template <int D, bool DIRECT> __host__ __device__ constexpr size_t partial_smem() {
-    size_t s = stage_bytes<D>();
-    if (reduce_bytes<D>() > s) s = reduce_bytes<D>();
-    if (DIRECT && TABLE_BYTES > s) s = TABLE_BYTES;
-    return s + 4 * 16 * sizeof(__half);   // + the four 16-entry centroid tables
+template <int D, int NW> __host__ __device__ constexpr size_t stage_bytes() { return size_t(NW) * 2 * TILE * stage_ld<D>() * sizeof(__half); }
+template <int D, int NW> __host__ __device__ constexpr size_t reduce_bytes() {
+    return size_t(NW) * (HPG * (D + 2) + 2 * HPG) * sizeof(float) + size_t(NW) * HPG * sizeof(float) + size_t(HPG) * D * sizeof(float) +
+           size_t(MERGE_CPARTS) * HPG * D * sizeof(float);
 }
+constexpr size_t TABLE_BYTES = 65536;
+constexpr int RING_STAGES = 3;
+template <int D> __host__ __device__ constexpr int ring_stage_bytes() { return TILE * (D / 2 + D / 4 + 8); }
+// direct path: the rotation matrix stays resident in shared memory behind the tables and the ring
+template <int D, int NW> __host__ __device__ constexpr size_t rot_offset() { return TABLE_BYTES + size_t(NW) * RING_STAGES * ring_stage_bytes<D>(); }
+// chunk (16 bytes) kc of row j of the resident matrix sits at chunk position rot_pos(j, kc) of that row: both a
+// thread quartet reading along a row and a warp reading down a column hit distinct bank groups
+__host__ __device__ constexpr int rot_pos(int j, int kc) { return (kc & ~7) | ((kc ^ j ^ ((kc >> 3) << 1)) & 7); }
+template <int D> __host__ __device__ constexpr size_t merge_bytes() { return size_t(HPG) * MAX_SPLITS * sizeof(float2); }
+template <int D, bool DIRECT> __host__ __device__ constexpr size_t body_bytes() {
+    constexpr int NW = warps_per_cta(DIRECT);
+    size_t s = stage_bytes<D, NW>();
+    if (reduce_bytes<D, NW>() > s) s = reduce_bytes<D, NW>();
+    if (merge_bytes<D>() > s) s = merge_bytes<D>();
+    if (DIRECT && rot_offset<D, NW>() + size_t(D) * D * sizeof(float) > s) s = rot_offset<D, NW>() + size_t(D) * D * sizeof(float);
+    return (s + 15) / 16 * 16;
+}
+template <int D> __host__ __device__ constexpr size_t tail_bytes() {
+    return size_t(HPG) * D * sizeof(float) + size_t(HPG) * D * sizeof(__half) + 64 * sizeof(__half) + 16 * sizeof(float);
+}
+template <int D, bool DIRECT> __host__ __device__ constexpr size_t kernel_smem() { return body_bytes<D, DIRECT>() + tail_bytes<D>(); }
 
 // One 16-token tile whose K and V sit in shared memory as fp16 [token][coordinate].
 template <int D>
@@ -213,21 +220,222 @@ __device__ __forceinline__ void tile_from_smem(const __half* Ks, const __half* V
     }
 }
 
-// grid (n_ps + n_ds, Hkv * HG, B), NW*32 threads.
-template <int D, bool DIRECT>
-__global__ void __launch_bounds__(NW * 32, DIRECT ? 2 : 1) decode_partial_kernel(DecodeParams p) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    constexpr int LD = stage_ld<D>();
-    constexpr size_t BODY = partial_smem<D, DIRECT>() - 4 * 16 * sizeof(__half);
-    __half* ctab = reinterpret_cast<__half*>(smem + BODY);   // kc_hi, kc_lo, vc_hi, vc_lo (16 each)
+// Per-warp cp.async ring of raw packed tiles (direct path, d = 128): one tile = 1024 B of 4-bit keys, 512 B of
+// 2-bit values, 2 x 64 B of norms.  Tokens past c_len are zero-filled without touching memory.
+template <int D, int NW> struct RingCtx {
+    static constexpr int KW = D / 2, VW = D / 4, KT = TILE * KW, VT = TILE * VW, STG = ring_stage_bytes<D>();
+    uint32_t ring, v_dst;
+    int tile_hi, first, c_len;
+    const uint8_t *kbase, *vbase;
+    const float* nbase;
+    // Value rows are stored permuted inside each group of four (row r -> slot (r + r/4) mod 4) so that the four
+    // rows {2t+c} a warp reads together fall into distinct banks.
+    __device__ __forceinline__ static int vslot(int r) { return (r & ~3) | ((r + (r >> 2)) & 3); }
+    __device__ __forceinline__ void init(const DecodeParams& p, unsigned char* smem, int64_t kvl, int split, int warp, int lane) {
+        ring = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + uint32_t(TABLE_BYTES) + warp * (RING_STAGES * STG);
+        v_dst = KT + vslot(lane >> 1) * VW + (lane & 1) * 16;
+        const int n_tiles = int((p.c_len + TILE - 1) / TILE);
+        const int tile_lo = int(split * p.p_tps);
+        tile_hi = min(tile_lo + int(p.p_tps), n_tiles);
+        first = tile_lo + warp;
+        c_len = int(p.c_len);
+        kbase = p.k_hi + kvl * p.c_ls * KW + lane * 16;
+        vbase = p.v_hi + kvl * p.c_ls * VW + lane * 16;
+        nbase = (lane < 4 ? p.k_norms : p.v_norms) + kvl * p.c_ls + (lane & 3) * 4;
+    }
+    __device__ __forceinline__ void issue(int stage, int tile, int lane) const {
+        const uint32_t sb = ring + stage * STG;
+        const int tok0 = tile * TILE;
+        const int left = c_len - tok0;            // valid tokens from here on (>= 16 for all but the last tile)
+        const uint8_t* ks = kbase + int64_t(tok0) * KW;
+        cp_async16(sb + lane * 16, ks, (lane >> 2) < left ? 16 : 0);
+        cp_async16(sb + 512 + lane * 16, ks + 512, (lane >> 2) + 8 < left ? 16 : 0);
+        cp_async16(sb + v_dst, vbase + int64_t(tok0) * VW, (lane >> 1) < left ? 16 : 0);
+        if (lane < 8) {
+            const int ok = left - (lane & 3) * 4;
+            cp_async16(sb + KT + VT + lane * 16, nbase + tok0, ok >= 4 ? 16 : ok > 0 ? ok * 4 : 0);
+        }
+    }
+};
 
-    pdl_trigger();     // lets the merge launch get resident early; it waits for this grid to finish
+template <int D, bool DIRECT>
+__global__ void __launch_bounds__(warps_per_cta(DIRECT) * 32, 1) decode_attn_kernel(DecodeParams p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    constexpr int NW = warps_per_cta(DIRECT), NT = NW * 32;
+    constexpr int LD = stage_ld<D>();
+    constexpr size_t BODY = body_bytes<D, DIRECT>();
+    float* qf = reinterpret_cast<float*>(smem + BODY);                       // [8][D] query, float32
+    __half* qs = reinterpret_cast<__half*>(qf + HPG * D);                    // [8][D] scaled fp16 query (rotated or raw)
+    __half* ctab = qs + HPG * D;                                             // kc_hi, kc_lo, vc_hi, vc_lo (16 each)
+    float* s_misc = reinterpret_cast<float*>(ctab + 64);                     // [0..7] 1/L per head, [8] last-CTA flag
+
+    TQ_STAMP(0);
+    pdl_trigger();     // the next launch on the stream may become resident and run its own prologue
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, hkv = blockIdx.y / p.HG, hg = blockIdx.y % p.HG, b = blockIdx.z;
     const int64_t kvl = int64_t(b) * p.Hkv + hkv;        // lane of the cache arrays
     const bool dense = split >= p.n_ps;
     const int heads_here = min(HPG, p.G - hg * HPG);
     const int64_t qbase = (int64_t(b) * p.Hq + int64_t(hkv) * p.G + hg * HPG) * D;   // first query head of this group
+    const int S = p.n_ps + p.n_ds;
+
+    // ---------------- prologue on constants only (runs before the previous launch has finished) -----------
+    if constexpr (DIRECT) {
+        if (!dense) {
+            uint32_t* T4 = reinterpret_cast<uint32_t*>(smem);               // [256][32]: byte -> half2(c[lo], c[hi])
+            uint2* T2 = reinterpret_cast<uint2*>(smem + 32768);             // [256][16]: byte -> 2 x half2 (token pair)
+            if (tid < 32) {
+                const int which = tid >> 4, k = tid & 15;
+                const float* src = which ? p.vc_hi : p.kc_hi;
+                ctab[which * 32 + k] = __float2half_rn(k < (which ? 4 : 16) ? src[k] * (which ? p.v_scale_hi : 1.f) : 0.f);
+            }
+            __syncthreads();
+            for (int e = tid; e < 256 * 8; e += NT) {     // 4 replicas per 128-bit store
+                const int entry = e >> 3, q4 = e & 7;
+                const __half2 h = __halves2half2(ctab[entry & 15], ctab[entry >> 4]);
+                const uint32_t v = *reinterpret_cast<const uint32_t*>(&h);
+                reinterpret_cast<uint4*>(T4)[entry * 8 + q4] = make_uint4(v, v, v, v);
+            }
+            for (int e = tid; e < 256 * 8; e += NT) {     // 2 replicas per 128-bit store
+                const int entry = e >> 3, q2 = e & 7;
+                const int n0 = entry & 15, n1 = entry >> 4;
+                const __half2 h0 = __halves2half2(ctab[32 + (n0 & 3)], ctab[32 + (n0 >> 2)]);
+                const __half2 h1 = __halves2half2(ctab[32 + (n1 & 3)], ctab[32 + (n1 >> 2)]);
+                const uint32_t v0 = *reinterpret_cast<const uint32_t*>(&h0), v1 = *reinterpret_cast<const uint32_t*>(&h1);
+                reinterpret_cast<uint4*>(T2)[entry * 8 + q2] = make_uint4(v0, v1, v0, v1);
+            }
+        }
+    } else {
+        if (!dense && tid < 64) {
+            const int which = tid >> 4, k = tid & 15;
+            const float* src = which == 0 ? p.kc_hi : which == 1 ? p.kc_lo : which == 2 ? p.vc_hi : p.vc_lo;
+            const int bits = which == 0 ? p.kb_hi : which == 1 ? p.kb_lo : which == 2 ? p.vb_hi : p.vb_lo;
+            const float sc = which == 2 ? p.v_scale_hi : which == 3 ? p.v_scale_lo : 1.f;
+            ctab[tid] = __float2half_rn((src != nullptr && bits > 0 && k < (1 << bits)) ? src[k] * sc : 0.f);
+        }
+    }
+    TQ_STAMP(1);
+    pdl_wait();        // from here on: the query, the cache and the workspace of the previous launch are settled
+
+    TQ_STAMP(2);
+    RingCtx<D, NW> rc;
+    // ---------------- the query heads of this group: float32, then (rotated) scaled fp16 --------------------
+    // q_rot[h][j] = sum_k q[h][k] R[j][k]  (rotation.py:81-110)
+    {
+        const float f = p.scale * LOG2E;
+        if constexpr (DIRECT) {
+            // R (64 KB) is read ONCE per CTA with fully coalesced 128-bit loads and stays resident in shared
+            // memory (the epilogue needs it again); chunk placement rot_pos() keeps both uses conflict-free.
+            float4* rs = reinterpret_cast<float4*>(smem + rot_offset<D, NW>());
+            float4 rr[(D * D / 4) / NT];
+            if (!dense) {
+#pragma unroll
+                for (int i = 0; i < (D * D / 4) / NT; ++i) rr[i] = __ldg(reinterpret_cast<const float4*>(p.rot) + tid + i * NT);
+            }
+            // 16-byte chunk kc of a query row is stored at chunk kc ^ (kc >> 3): the four threads of a row
+            // quartet read chunks 8 apart, which would otherwise share a bank group
+            for (int e = tid; e < heads_here * D; e += NT) {
+                const int kc = (e % D) >> 2;
+                qf[(e - (e % D)) + ((kc ^ (kc >> 3)) << 2) + (e & 3)] = load_as_f32(p.q, p.q_dtype, qbase + e);
+            }
+            if (!dense) {
+                // start streaming the first packed tiles: they land while the query is being rotated
+                rc.init(p, smem, kvl, split, warp, lane);
+#pragma unroll
+                for (int i = 0; i < RING_STAGES - 1; ++i) {
+                    if (rc.first + i * NW < rc.tile_hi) rc.issue(i, rc.first + i * NW, lane);
+                    cp_async_commit();
+                }
+#pragma unroll
+                for (int i = 0; i < (D * D / 4) / NT; ++i) {
+                    const int idx = tid + i * NT, j = idx / (D / 4), k = idx - j * (D / 4);
+                    rs[j * (D / 4) + rot_pos(j, k)] = rr[i];
+                }
+            }
+            __syncthreads();
+            if (dense) {
+                for (int e = tid; e < heads_here * D; e += NT) {
+                    const int kc = (e % D) >> 2;
+                    qs[e] = __float2half_rn(qf[(e - (e % D)) + ((kc ^ (kc >> 3)) << 2) + (e & 3)] * f);
+                }
+            } else {
+                // thread (j, part): columns [part*32, part*32+32) of row j; the four parts of a row are adjacent lanes
+                constexpr int KP = NT / D, COLS = D / KP;
+                static_assert(KP == 4, "direct path: four threads per row of R");
+                const int j = tid >> 2, kp = tid & 3;
+                float acc[HPG];
+#pragma unroll
+                for (int h = 0; h < HPG; ++h) acc[h] = 0.f;
+#pragma unroll
+                for (int k = 0; k < COLS / 4; ++k) {
+                    const int kc = kp * (COLS / 4) + k;
+                    const float4 r = rs[j * (D / 4) + rot_pos(j, kc)];
+#pragma unroll
+                    for (int h = 0; h < HPG; ++h) {
+                        if (h < heads_here) {
+                            const float4 x = *reinterpret_cast<const float4*>(qf + h * D + 4 * (kc ^ (kc >> 3)));
+                            acc[h] = fmaf(x.x, r.x, fmaf(x.y, r.y, fmaf(x.z, r.z, fmaf(x.w, r.w, acc[h]))));
+                        }
+                    }
+                }
+#pragma unroll
+                for (int h = 0; h < HPG; ++h) {
+                    acc[h] += __shfl_xor_sync(0xffffffffu, acc[h], 1);
+                    acc[h] += __shfl_xor_sync(0xffffffffu, acc[h], 2);
+                    if (kp == 0 && h < heads_here) qs[h * D + j] = __float2half_rn(acc[h] * f);
+                }
+            }
+        } else {
+            // general path: thread (j, part) reads its slice of row j straight from global memory
+            constexpr int KP = NT / D >= 4 ? 4 : NT / D >= 2 ? 2 : 1;     // slices per row (power of two)
+            constexpr int COLS = D / KP;                                   // columns per slice
+            const int j = tid / KP, kp = tid - j * KP;
+            const bool rot_thread = !dense && j < D;
+            constexpr int CH = COLS / 4 > 16 ? 16 : COLS / 4;             // float4 loads in flight per round
+            const float4* row = reinterpret_cast<const float4*>(p.rot + int64_t(rot_thread ? j : 0) * D + kp * COLS);
+            float4 rr[CH];
+            if (rot_thread) {
+#pragma unroll
+                for (int k = 0; k < CH; ++k) rr[k] = __ldg(row + k);
+            }
+            for (int e = tid; e < heads_here * D; e += NT) qf[e] = load_as_f32(p.q, p.q_dtype, qbase + e);
+            __syncthreads();
+            if (dense) {
+                for (int e = tid; e < heads_here * D; e += NT) qs[e] = __float2half_rn(qf[e] * f);
+            } else {
+                float acc[HPG];
+#pragma unroll
+                for (int h = 0; h < HPG; ++h) acc[h] = 0.f;
+                if (rot_thread) {
+#pragma unroll 1
+                    for (int k0 = 0; k0 < COLS / 4; k0 += CH) {
+                        if (k0 > 0) {
+#pragma unroll
+                            for (int k = 0; k < CH; ++k) rr[k] = __ldg(row + k0 + k);
+                        }
+#pragma unroll
+                        for (int k = 0; k < CH; ++k) {
+#pragma unroll
+                            for (int h = 0; h < HPG; ++h) {
+                                if (h < heads_here) {
+                                    const float4 x = *reinterpret_cast<const float4*>(qf + h * D + kp * COLS + 4 * (k0 + k));
+                                    acc[h] = fmaf(x.x, rr[k].x, fmaf(x.y, rr[k].y, fmaf(x.z, rr[k].z, fmaf(x.w, rr[k].w, acc[h]))));
+                                }
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int h = 0; h < HPG; ++h) {
+#pragma unroll
+                    for (int off = KP / 2; off; off >>= 1) acc[h] += __shfl_xor_sync(0xffffffffu, acc[h], off);
+                    if (rot_thread && kp == 0 && h < heads_here) qs[h * D + j] = __float2half_rn(acc[h] * f);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    TQ_STAMP(3);
 
     WarpAcc<D> st;
     st.m[0] = st.m[1] = st.mt[0] = st.mt[1] = -INFINITY;
@@ -239,10 +447,9 @@ __global__ void __launch_bounds__(NW * 32, DIRECT ? 2 : 1) decode_partial_kernel
 
     if (dense) {
         // ---------------- uncompressed tokens: sink then residual window, raw query ----------------
-        pdl_wait();        // the scaled query copies come from the prep launch
         uint32_t bq[D / 16][2];
         {
-            const __half* qh = p.q_raw + qbase + int64_t(g) * D;
+            const __half* qh = qs + g * D;
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
                 bq[ks][0] = g < heads_here ? *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * t) : 0u;
@@ -256,20 +463,37 @@ __global__ void __launch_bounds__(NW * 32, DIRECT ? 2 : 1) decode_partial_kernel
         const int64_t tile_hi = min(tile_lo + p.d_tps, (n_tok + TILE - 1) / TILE);
         for (int64_t tile = tile_lo + warp; tile < tile_hi; tile += NW) {
             const int64_t tok0 = tile * TILE;
-            for (int c = lane; c < TILE * (D / 8); c += 32) {
-                const int r = c / (D / 8), c8 = c - r * (D / 8);
-                const int64_t tok = tok0 + r;
-                uint4 kv = make_uint4(0, 0, 0, 0), vv = kv;
-                if (tok < n_tok) {
-                    const bool in_sink = tok < p.sink_len;
-                    const int64_t row = in_sink ? kvl * p.sink_ls + tok : kvl * p.res_ls + (tok - p.sink_len);
-                    const void* kb = in_sink ? p.sink_k : p.res_k;
-                    const void* vb = in_sink ? p.sink_v : p.res_v;
-                    const int64_t e = row * D + c8 * 8;
-                    if (p.dense_dtype == TQ_F16) {
-                        kv = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(kb) + e));
-                        vv = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(vb) + e));
-                    } else {
+            constexpr int NCH = TILE * (D / 8) / 32;          // 16-byte chunks per lane and tensor
+            if (p.dense_dtype == TQ_F16) {
+                uint4 kv[NCH], vv[NCH];                        // every load of the tile in flight before the first store
+#pragma unroll
+                for (int i = 0; i < NCH; ++i) {
+                    const int c = lane + 32 * i, r = c / (D / 8), c8 = c - r * (D / 8);
+                    const int64_t tok = tok0 + r;
+                    kv[i] = make_uint4(0, 0, 0, 0); vv[i] = kv[i];
+                    if (tok < n_tok) {
+                        const bool in_sink = tok < p.sink_len;
+                        const int64_t e = (in_sink ? kvl * p.sink_ls + tok : kvl * p.res_ls + (tok - p.sink_len)) * D + c8 * 8;
+                        kv[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(in_sink ? p.sink_k : p.res_k) + e));
+                        vv[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(in_sink ? p.sink_v : p.res_v) + e));
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < NCH; ++i) {
+                    const int c = lane + 32 * i, r = c / (D / 8), c8 = c - r * (D / 8);
+                    *reinterpret_cast<uint4*>(Ks + r * LD + c8 * 8) = kv[i];
+                    *reinterpret_cast<uint4*>(Vs + r * LD + c8 * 8) = vv[i];
+                }
+            } else {
+                for (int c = lane; c < TILE * (D / 8); c += 32) {
+                    const int r = c / (D / 8), c8 = c - r * (D / 8);
+                    const int64_t tok = tok0 + r;
+                    uint4 kv = make_uint4(0, 0, 0, 0), vv = kv;
+                    if (tok < n_tok) {
+                        const bool in_sink = tok < p.sink_len;
+                        const int64_t e = (in_sink ? kvl * p.sink_ls + tok : kvl * p.res_ls + (tok - p.sink_len)) * D + c8 * 8;
+                        const void* kb = in_sink ? p.sink_k : p.res_k;
+                        const void* vb = in_sink ? p.sink_v : p.res_v;
                         __half hk[8], hv[8];
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
@@ -279,9 +503,9 @@ __global__ void __launch_bounds__(NW * 32, DIRECT ? 2 : 1) decode_partial_kernel
                         kv = *reinterpret_cast<uint4*>(hk);
                         vv = *reinterpret_cast<uint4*>(hv);
                     }
+                    *reinterpret_cast<uint4*>(Ks + r * LD + c8 * 8) = kv;
+                    *reinterpret_cast<uint4*>(Vs + r * LD + c8 * 8) = vv;
                 }
-                *reinterpret_cast<uint4*>(Ks + r * LD + c8 * 8) = kv;
-                *reinterpret_cast<uint4*>(Vs + r * LD + c8 * 8) = vv;
             }
             __syncwarp();
             tile_from_smem<D>(Ks, Vs, bq, 1.f, 1.f, 1.f, 1.f, tok0 + g < n_tok, tok0 + g + 8 < n_tok, st, lane);
@@ -289,18 +513,9 @@ __global__ void __launch_bounds__(NW * 32, DIRECT ? 2 : 1) decode_partial_kernel
         }
     } else if constexpr (!DIRECT) {
         // ---------------- packed tokens, general path: unpack into shared memory ---------------------
-        if (tid < 64) {
-            const int which = tid >> 4, k = tid & 15;
-            const float* src = which == 0 ? p.kc_hi : which == 1 ? p.kc_lo : which == 2 ? p.vc_hi : p.vc_lo;
-            const int bits = which == 0 ? p.kb_hi : which == 1 ? p.kb_lo : which == 2 ? p.vb_hi : p.vb_lo;
-            const float sc = which == 2 ? p.v_scale_hi : which == 3 ? p.v_scale_lo : 1.f;
-            ctab[tid] = __float2half_rn((src != nullptr && bits > 0 && k < (1 << bits)) ? src[k] * sc : 0.f);
-        }
-        pdl_wait();        // the rotated query comes from the prep launch
-        __syncthreads();
         uint32_t bq[D / 16][2];
         {
-            const __half* qh = p.q_rot + qbase + int64_t(g) * D;
+            const __half* qh = qs + g * D;
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
                 bq[ks][0] = g < heads_here ? *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * t) : 0u;
@@ -351,290 +566,267 @@ __global__ void __launch_bounds__(NW * 32, DIRECT ? 2 : 1) decode_partial_kernel
     } else {
         // ---------------- packed tokens, direct path: 4-bit keys, 2-bit values -------------------------
         direct_order = true;
-        uint32_t* T4 = reinterpret_cast<uint32_t*>(smem);               // [256][32]: byte -> half2(c[lo], c[hi])
-        uint2* T2 = reinterpret_cast<uint2*>(smem + 32768);             // [256][16]: byte -> 2 x half2 (token pair)
-        if (tid < 32) {
-            const int which = tid >> 4, k = tid & 15;
-            const float* src = which ? p.vc_hi : p.kc_hi;
-            ctab[which * 32 + k] = __float2half_rn(k < (which ? 4 : 16) ? src[k] * (which ? p.v_scale_hi : 1.f) : 0.f);
-        }
-        __syncthreads();
-        for (int e = tid; e < 256 * 8; e += NW * 32) {     // 4 replicas per 128-bit store
-            const int entry = e >> 3, q4 = e & 7;
-            const __half2 h = __halves2half2(ctab[entry & 15], ctab[entry >> 4]);
-            const uint32_t v = *reinterpret_cast<const uint32_t*>(&h);
-            reinterpret_cast<uint4*>(T4)[entry * 8 + q4] = make_uint4(v, v, v, v);
-        }
-        for (int e = tid; e < 256 * 8; e += NW * 32) {     // 2 replicas per 128-bit store
-            const int entry = e >> 3, q2 = e & 7;
-            const int n0 = entry & 15, n1 = entry >> 4;
-            const __half2 h0 = __halves2half2(ctab[32 + (n0 & 3)], ctab[32 + (n0 >> 2)]);
-            const __half2 h1 = __halves2half2(ctab[32 + (n1 & 3)], ctab[32 + (n1 >> 2)]);
-            const uint32_t v0 = *reinterpret_cast<const uint32_t*>(&h0), v1 = *reinterpret_cast<const uint32_t*>(&h1);
-            reinterpret_cast<uint4*>(T2)[entry * 8 + q2] = make_uint4(v0, v1, v0, v1);
-        }
-        pdl_wait();        // the rotated query comes from the prep launch
-        __syncthreads();
+        static_assert(!DIRECT || D == 128, "the direct path's shared-memory tile layout is written for d = 128");
         // Query fragments in the byte order of the 4-bit rows: thread t owns coordinates [t*D/4, (t+1)*D/4).
         uint32_t bq[D / 16][2];
         {
-            const __half* qh = p.q_rot + qbase + int64_t(g) * D + t * (D / 4);
+            const __half* qh = qs + g * D + t * (D / 4);
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
                 bq[ks][0] = g < heads_here ? *reinterpret_cast<const uint32_t*>(qh + 4 * ks) : 0u;
                 bq[ks][1] = g < heads_here ? *reinterpret_cast<const uint32_t*>(qh + 4 * ks + 2) : 0u;
             }
         }
-        constexpr int KW = D / 2, VW = D / 4;            // bytes per token
-        constexpr int KQ = KW / 4 / 4;                   // 32-bit words in a thread's quarter of a key row
-        constexpr int VQ = VW / 8 / 4;                   // 32-bit words in a thread's eighth of a value row
-        static_assert(KQ >= 1 && VQ >= 1 && KQ % 4 == 0, "direct path needs d a multiple of 128");
+        using RC = RingCtx<D, NW>;
+        constexpr int KT = RC::KT, VT = RC::VT, VW = RC::VW, STG = RC::STG;
         // 32-bit shared-window addresses of this lane's private table columns: entry e of T4 sits at
-        // t4 + e*128, entry e of T2 at t2 + e*128 (one IMAD each, no 64-bit address arithmetic).
-        const uint32_t t4 = static_cast<uint32_t>(__cvta_generic_to_shared(T4)) + lane * 4;
-        const uint32_t t2 = static_cast<uint32_t>(__cvta_generic_to_shared(T2)) + (lane & 15) * 8;
-        const int64_t tile_lo = int64_t(split) * p.p_tps;
-        const int64_t tile_hi = min(tile_lo + p.p_tps, (p.c_len + TILE - 1) / TILE);
-        const int64_t last = p.c_len - 1;
-        const uint8_t* kbase = p.k_hi + kvl * p.c_ls * KW + t * (KQ * 4);
-        const uint8_t* vbase = p.v_hi + kvl * p.c_ls * VW + g * (VQ * 4);
-        const float* knb = p.k_norms + kvl * p.c_ls;
-        const float* vnb = p.v_norms + kvl * p.c_ls;
-
-        struct Raw { uint4 k[2][KQ / 4]; uint32_t v[4][VQ]; float n[4]; };
-        auto issue_loads = [&](Raw& r, int64_t tok0) {
-            if (tok0 + TILE <= p.c_len) {      // whole tile in range: constant offsets from three bases
-                const uint8_t* kp = kbase + (tok0 + g) * KW;
-                const uint8_t* vp = vbase + (tok0 + 2 * t) * VW;
-#pragma unroll
-                for (int i = 0; i < KQ / 4; ++i) {
-                    r.k[0][i] = __ldg(reinterpret_cast<const uint4*>(kp) + i);
-                    r.k[1][i] = __ldg(reinterpret_cast<const uint4*>(kp + 8 * KW) + i);
-                }
-#pragma unroll
-                for (int i = 0; i < VQ; ++i) {
-                    r.v[0][i] = __ldg(reinterpret_cast<const uint32_t*>(vp) + i);
-                    r.v[1][i] = __ldg(reinterpret_cast<const uint32_t*>(vp + VW) + i);
-                    r.v[2][i] = __ldg(reinterpret_cast<const uint32_t*>(vp + 8 * VW) + i);
-                    r.v[3][i] = __ldg(reinterpret_cast<const uint32_t*>(vp + 9 * VW) + i);
-                }
-                r.n[0] = __ldg(knb + tok0 + g); r.n[1] = __ldg(knb + tok0 + g + 8);
-                r.n[2] = __ldg(vnb + tok0 + g); r.n[3] = __ldg(vnb + tok0 + g + 8);
-            } else {                            // the one ragged tile at the very end: clamp every token index
-                const int64_t ta = min(tok0 + g, last), tb = min(tok0 + g + 8, last);
-#pragma unroll
-                for (int i = 0; i < KQ / 4; ++i) {
-                    r.k[0][i] = __ldg(reinterpret_cast<const uint4*>(kbase + ta * KW) + i);
-                    r.k[1][i] = __ldg(reinterpret_cast<const uint4*>(kbase + tb * KW) + i);
-                }
-                const int64_t v0 = min(tok0 + 2 * t, last), v1 = min(tok0 + 2 * t + 1, last);
-                const int64_t v2 = min(tok0 + 2 * t + 8, last), v3 = min(tok0 + 2 * t + 9, last);
-#pragma unroll
-                for (int i = 0; i < VQ; ++i) {
-                    r.v[0][i] = __ldg(reinterpret_cast<const uint32_t*>(vbase + v0 * VW) + i);
-                    r.v[1][i] = __ldg(reinterpret_cast<const uint32_t*>(vbase + v1 * VW) + i);
-                    r.v[2][i] = __ldg(reinterpret_cast<const uint32_t*>(vbase + v2 * VW) + i);
-                    r.v[3][i] = __ldg(reinterpret_cast<const uint32_t*>(vbase + v3 * VW) + i);
-                }
-                r.n[0] = __ldg(knb + ta); r.n[1] = __ldg(knb + tb); r.n[2] = __ldg(vnb + ta); r.n[3] = __ldg(vnb + tb);
-            }
-        };
-        auto compute = [&](const Raw& r, int64_t tok0) {
-            float s[4] = {0.f, 0.f, 0.f, 0.f};
+        // t4 + e*128, entry e of T2 at t2 + e*128 (one multiply-add each, no 64-bit address arithmetic).
+        const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+        const uint32_t t4 = smem_base + lane * 4;
+        const uint32_t t2 = smem_base + 32768 + (lane & 15) * 8;
+        const uint32_t ring = rc.ring;
+        const int c_len = rc.c_len, tile_hi = rc.tile_hi;
+        const uint32_t vo0 = KT + RC::vslot(2 * t) * VW + g * 4, vo1 = KT + RC::vslot(2 * t + 1) * VW + g * 4;
+        const uint32_t vo2 = KT + RC::vslot(2 * t + 8) * VW + g * 4, vo3 = KT + RC::vslot(2 * t + 9) * VW + g * 4;
+        auto compute = [&](int stage, int tile) {
+            const uint32_t sb = ring + stage * STG;
+            const int tok0 = tile * TILE;
+            const uint4 q0 = ring128(sb + lane * 16);            // token g,   this thread's quarter row
+            const uint4 q1 = ring128(sb + 512 + lane * 16);      // token g+8
+            const float kn0 = __uint_as_float(ring32(sb + KT + VT + g * 4)), kn1 = __uint_as_float(ring32(sb + KT + VT + 32 + g * 4));
+            const float vn0 = __uint_as_float(ring32(sb + KT + VT + 64 + g * 4)), vn1 = __uint_as_float(ring32(sb + KT + VT + 96 + g * 4));
+            const uint32_t va = ring32(sb + vo0), vb = ring32(sb + vo1), vc = ring32(sb + vo2), vd = ring32(sb + vo3);
+            // two independent accumulators (even / odd k-steps) halve the dependent MMA chain
+            float s[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
-                // bytes 2ks, 2ks+1 of this thread's quarter row, for tokens g and g+8
-                const uint4& q0 = r.k[0][ks >> 3];
-                const uint4& q1 = r.k[1][ks >> 3];
-                const int wi = (ks >> 1) & 3;
+                // bytes 2ks, 2ks+1 of the quarter row
+                const int wi = ks >> 1;
                 const uint32_t w0 = wi == 0 ? q0.x : wi == 1 ? q0.y : wi == 2 ? q0.z : q0.w;
                 const uint32_t w1 = wi == 0 ? q1.x : wi == 1 ? q1.y : wi == 2 ? q1.z : q1.w;
                 const int b0 = (ks & 1) * 2;
-                const uint32_t a0 = lds32(__byte_perm(w0, 0, 0x4440 | b0) * 128u + t4);
-                const uint32_t a1 = lds32(__byte_perm(w1, 0, 0x4440 | b0) * 128u + t4);
-                const uint32_t a2 = lds32(__byte_perm(w0, 0, 0x4440 | (b0 + 1)) * 128u + t4);
-                const uint32_t a3 = lds32(__byte_perm(w1, 0, 0x4440 | (b0 + 1)) * 128u + t4);
-                mma16816(s, a0, a1, a2, a3, bq[ks][0], bq[ks][1]);
+                const uint32_t a0 = lut32(__byte_perm(w0, 0, 0x4440 | b0) * 128u + t4);
+                const uint32_t a1 = lut32(__byte_perm(w1, 0, 0x4440 | b0) * 128u + t4);
+                const uint32_t a2 = lut32(__byte_perm(w0, 0, 0x4440 | (b0 + 1)) * 128u + t4);
+                const uint32_t a3 = lut32(__byte_perm(w1, 0, 0x4440 | (b0 + 1)) * 128u + t4);
+                if (ks & 1) mma16816(s2, a0, a1, a2, a3, bq[ks][0], bq[ks][1]);
+                else mma16816(s, a0, a1, a2, a3, bq[ks][0], bq[ks][1]);
             }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[i] += s2[i];
             uint32_t bp[2];
-            softmax_step<D>(s, r.n[0], r.n[1], r.n[2], r.n[3], tok0 + g < p.c_len, tok0 + g + 8 < p.c_len, st, bp);
+            softmax_step<D>(s, kn0, kn1, vn0, vn1, tok0 + g < c_len, tok0 + g + 8 < c_len, st, bp);
+            // interleave the 2-bit codes of a token pair: nibble k of X = (A code 2k) | (B code 2k) << 2
+            const uint32_t x0 = (va & 0x33333333u) | ((vb << 2) & 0xCCCCCCCCu);
+            const uint32_t y0 = ((va >> 2) & 0x33333333u) | (vb & 0xCCCCCCCCu);
+            const uint32_t x1 = (vc & 0x33333333u) | ((vd << 2) & 0xCCCCCCCCu);
+            const uint32_t y1 = ((vc >> 2) & 0x33333333u) | (vd & 0xCCCCCCCCu);
 #pragma unroll
-            for (int i = 0; i < VQ; ++i) {
-                // interleave the 2-bit codes of a token pair: nibble k of X = (A code 2k) | (B code 2k) << 2
-                const uint32_t x0 = (r.v[0][i] & 0x33333333u) | ((r.v[1][i] << 2) & 0xCCCCCCCCu);
-                const uint32_t y0 = ((r.v[0][i] >> 2) & 0x33333333u) | (r.v[1][i] & 0xCCCCCCCCu);
-                const uint32_t x1 = (r.v[2][i] & 0x33333333u) | ((r.v[3][i] << 2) & 0xCCCCCCCCu);
-                const uint32_t y1 = ((r.v[2][i] >> 2) & 0x33333333u) | (r.v[3][i] & 0xCCCCCCCCu);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const uint2 fa = lds64(__byte_perm(x0, 0, 0x4440 | k) * 128u + t2);   // rows g,   tokens 2t,2t+1   -> m-tiles 2k, 2k+1
-                    const uint2 fb = lds64(__byte_perm(y0, 0, 0x4440 | k) * 128u + t2);   // rows g+8
-                    const uint2 fc = lds64(__byte_perm(x1, 0, 0x4440 | k) * 128u + t2);   // rows g,   tokens 2t+8,2t+9
-                    const uint2 fd = lds64(__byte_perm(y1, 0, 0x4440 | k) * 128u + t2);
-                    const int mt = i * 8 + 2 * k;
-                    mma16816(st.o[mt], fa.x, fb.x, fc.x, fd.x, bp[0], bp[1]);
-                    mma16816(st.o[mt + 1], fa.y, fb.y, fc.y, fd.y, bp[0], bp[1]);
-                }
+            for (int k = 0; k < 4; ++k) {
+                const uint2 fa = lut64(__byte_perm(x0, 0, 0x4440 | k) * 128u + t2);   // rows g,   tokens 2t,2t+1   -> m-tiles 2k, 2k+1
+                const uint2 fb = lut64(__byte_perm(y0, 0, 0x4440 | k) * 128u + t2);   // rows g+8
+                const uint2 fc = lut64(__byte_perm(x1, 0, 0x4440 | k) * 128u + t2);   // rows g,   tokens 2t+8,2t+9
+                const uint2 fd = lut64(__byte_perm(y1, 0, 0x4440 | k) * 128u + t2);
+                mma16816(st.o[2 * k], fa.x, fb.x, fc.x, fd.x, bp[0], bp[1]);
+                mma16816(st.o[2 * k + 1], fa.y, fb.y, fc.y, fd.y, bp[0], bp[1]);
             }
         };
-        // two register buffers, loads for the next tile in flight while the current one is computed
-        Raw ra, rb;
-        int64_t tile = tile_lo + warp;
-        if (tile < tile_hi) issue_loads(ra, tile * TILE);
-        while (tile < tile_hi) {
-            if (tile + NW < tile_hi) issue_loads(rb, (tile + NW) * TILE);
-            compute(ra, tile * TILE);
-            tile += NW;
-            if (tile >= tile_hi) break;
-            if (tile + NW < tile_hi) issue_loads(ra, (tile + NW) * TILE);
-            compute(rb, tile * TILE);
-            tile += NW;
+        // Software pipeline: RING_STAGES - 1 tiles in flight per warp (the first ones were issued before the query
+        // was rotated).  One commit group per slot, issued or not, keeps the group count uniform; cp.async
+        // completion is tracked by hardware (no spin waits).
+        const int first = rc.first;
+        int stage = 0;
+        for (int tile = first; tile < tile_hi; tile += NW) {
+            const int ahead = tile + (RING_STAGES - 1) * NW;
+            const int st_in = stage == 0 ? RING_STAGES - 1 : stage - 1;
+            if (ahead < tile_hi) rc.issue(st_in, ahead, lane);
+            cp_async_commit();
+            cp_async_wait<RING_STAGES - 1>();
+            __syncwarp();
+            compute(stage, tile);
+            __syncwarp();       // every lane is done with this stage before it is refilled
+            stage = stage == RING_STAGES - 1 ? 0 : stage + 1;
         }
+        cp_async_wait<0>();
     }
 
-    // ---------------- CTA reduction over warps, then one partial per head to the workspace ---------------
+    // ---------------- CTA reduction over warps ----------------------------------------------------------------
 #pragma unroll
     for (int off = 4; off < 32; off <<= 1) {
         st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], off);
         st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], off);
     }
-    __syncthreads();   // staging / tables are dead from here on
+    __syncthreads();   // staging / tables / ring are dead from here on
+    TQ_STAMP(4);
+    constexpr int DS = D + 2;                               // row stride (floats): keeps the 64-bit stores below 2-way conflicts
+    constexpr int RW = HPG * DS + 2 * HPG;                  // floats per warp in the reduction buffer
     float* red = reinterpret_cast<float*>(smem);
-    float* ro = red + size_t(warp) * (D * HPG + 2 * HPG);   // [D][8]
-    float* rm = ro + D * HPG;                               // [8] max, [8] sum
+    float* wts = red + size_t(NW) * RW;                     // [NW][8] per-warp weights exp2(m_w - M)
+    float* s_acc = wts + NW * HPG;                          // [8][D] reduced accumulator of this CTA
+    float* s_pp = s_acc + HPG * D;                          // [MERGE_CPARTS][8][D] partial products with R
+    {
+        float* ro = red + size_t(warp) * RW;                // [8][DS]: head-major
+        float* rm = ro + HPG * DS;                          // [8] max, [8] sum
+        if (2 * t < heads_here) {                           // lanes that hold only padding heads store nothing
 #pragma unroll
-    for (int mt = 0; mt < D / 16; ++mt) {
-        int c0, c1;
-        if (direct_order) { c0 = g * (D / 8) + 2 * mt; c1 = c0 + 1; }
-        else { c0 = mt * 16 + g; c1 = c0 + 8; }
-        *reinterpret_cast<float2*>(ro + c0 * HPG + 2 * t) = make_float2(st.o[mt][0], st.o[mt][1]);
-        *reinterpret_cast<float2*>(ro + c1 * HPG + 2 * t) = make_float2(st.o[mt][2], st.o[mt][3]);
-    }
-    if (g == 0) {
-        rm[2 * t] = st.m[0]; rm[2 * t + 1] = st.m[1];
-        rm[HPG + 2 * t] = st.l[0]; rm[HPG + 2 * t + 1] = st.l[1];
+            for (int mt = 0; mt < D / 16; ++mt) {
+                if (direct_order) {                          // rows g, g+8 of the tile are coordinates c0, c0+1
+                    const int c0 = g * (D / 8) + 2 * mt;
+                    *reinterpret_cast<float2*>(ro + (2 * t) * DS + c0) = make_float2(st.o[mt][0], st.o[mt][2]);
+                    *reinterpret_cast<float2*>(ro + (2 * t + 1) * DS + c0) = make_float2(st.o[mt][1], st.o[mt][3]);
+                } else {
+                    const int c0 = mt * 16 + g;
+                    ro[(2 * t) * DS + c0] = st.o[mt][0]; ro[(2 * t + 1) * DS + c0] = st.o[mt][1];
+                    ro[(2 * t) * DS + c0 + 8] = st.o[mt][2]; ro[(2 * t + 1) * DS + c0 + 8] = st.o[mt][3];
+                }
+            }
+        }
+        if (g == 0) {
+            rm[2 * t] = st.m[0]; rm[2 * t + 1] = st.m[1];
+            rm[HPG + 2 * t] = st.l[0]; rm[HPG + 2 * t + 1] = st.l[1];
+        }
     }
     __syncthreads();
-    const int64_t pidx = ((kvl * p.HG + hg) * (p.n_ps + p.n_ds) + split);
-    float* po = p.part_o + pidx * (int64_t(p.slots) * D);
-    float* pml = p.part_ml + pidx * (p.slots * 2);
-    for (int e = tid; e < D * HPG; e += NW * 32) {
-        const int h = e / D, c = e - h * D;           // output layout [head][coordinate]
-        if (h >= heads_here) continue;
+    const int64_t grp = (kvl * p.HG + hg);
+    const int64_t pidx = grp * S + split;
+    float* po = p.part_o + pidx * (int64_t(p.slots) * D);   // [slots][D], always in UNROTATED space
+    float* pml = p.part_ml + pidx * (p.slots * 2);          // [slots][2]
+    if (tid < NW * HPG) {
+        const int w = tid / HPG, h = tid - w * HPG;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < NW; ++w) M = fmaxf(M, red[size_t(w) * (D * HPG + 2 * HPG) + D * HPG + h]);
-        float acc = 0.f, L = 0.f;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-            const float* rw = red + size_t(w) * (D * HPG + 2 * HPG);
-            const float mw = rw[D * HPG + h];
-            const float f = (mw == -INFINITY) ? 0.f : ex2(mw - M);
-            acc = fmaf(f, rw[c * HPG + h], acc);
-            L = fmaf(f, rw[D * HPG + HPG + h], L);
-        }
-        po[h * D + c] = acc;
-        if (c == 0) { pml[2 * h] = M; pml[2 * h + 1] = L; }
+        for (int x = 0; x < NW; ++x) M = fmaxf(M, red[size_t(x) * RW + HPG * DS + h]);
+        const float mw = red[size_t(w) * RW + HPG * DS + h];
+        const float f = (mw == -INFINITY) ? 0.f : ex2(mw - M);
+        wts[w * HPG + h] = f;
+        if (w == 0 && h < heads_here) pml[2 * h] = M;
     }
-}
-
-// grid (Hq, B), 256 threads: merge the splits of one query head and undo the rotation once.
-// Three short phases, each a single round of independent loads: (1) split weights from the per-split
-// (max, sum) pairs, (2) weighted sum of the partial accumulators over splits, (3) the d x d product with R.
-constexpr int MERGE_T = 256, MAX_SPLITS = 512;
-__global__ void __launch_bounds__(MERGE_T) decode_merge_kernel(DecodeParams p) {
-    __shared__ float s_w[MAX_SPLITS];
-    __shared__ float s_part[4][256];   // partial sums per thread group
-    __shared__ float s_rot[256], s_raw[256];
-    __shared__ float s_inv;
-    pdl_wait();        // partial accumulators come from the launch just before this one
-    pdl_trigger();
-    const int h = blockIdx.x, b = blockIdx.y, d = p.D, tid = threadIdx.x;
-    const int hkv = h / p.G, hl = h - hkv * p.G, hg = hl / HPG, hs = hl - hg * HPG;
-    const int S = p.n_ps + p.n_ds, SL = p.slots;
-    const int64_t base = ((int64_t(b) * p.Hkv + hkv) * p.HG + hg) * S;
-    // (1) warp 0: weights exp2(m_s - M) and the normaliser
-    if (tid < 32) {
-        float mloc[MAX_SPLITS / 32], lloc[MAX_SPLITS / 32];
-        float M = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < MAX_SPLITS / 32; ++i) {
-            const int sidx = tid + 32 * i;
-            mloc[i] = -INFINITY; lloc[i] = 0.f;
-            if (sidx < S) {
-                const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + ((base + sidx) * SL + hs) * 2);
-                mloc[i] = ml.x; lloc[i] = ml.y;
-            }
-            M = fmaxf(M, mloc[i]);
-        }
-#pragma unroll
-        for (int off = 16; off; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+    __syncthreads();
+    if (tid < heads_here) {
         float L = 0.f;
 #pragma unroll
-        for (int i = 0; i < MAX_SPLITS / 32; ++i) {
-            const int sidx = tid + 32 * i;
-            const float w = (mloc[i] == -INFINITY) ? 0.f : ex2(mloc[i] - M);
-            if (sidx < S) s_w[sidx] = w;
-            L = fmaf(w, lloc[i], L);
-        }
+        for (int x = 0; x < NW; ++x) L = fmaf(wts[x * HPG + tid], red[size_t(x) * RW + HPG * DS + HPG + tid], L);
+        pml[2 * tid + 1] = L;
+    }
+    const int v_half = p.vb_lo ? D / 2 : D;
+    for (int e = tid; e < D * heads_here; e += NT) {         // e = h * D + c: contiguous in the workspace
+        const int h = e / D, c = e - h * D;
+        float acc = 0.f;
 #pragma unroll
-        for (int off = 16; off; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
-        if (tid == 0) s_inv = 1.f / L;
+        for (int x = 0; x < NW; ++x) acc = fmaf(wts[x * HPG + h], red[size_t(x) * RW + h * DS + c], acc);
+        if (dense) po[e] = acc;                              // uncompressed tokens were never rotated
+        else s_acc[e] = acc / (c < v_half ? p.v_scale_hi : p.v_scale_lo);
     }
-    __syncthreads();
-    // (2) thread (c, part): sum over the splits congruent to `part`
-    const int JW = d >= 128 ? 128 : d, parts = MERGE_T / JW;
-    const int part = tid / JW, cj = tid - part * JW;
-    for (int c = cj; c < d; c += JW) {
-        float rot = 0.f, raw = 0.f;
-        if (part < parts) {
+    if (!dense) {
+        // Packed tokens were accumulated in rotated space: undo the rotation here, once per CTA
+        // (y @ R, rotation.py:68-78), so that the merge only has to add partials.  Thread (slab, j).
+        __syncthreads();
+        constexpr int JT = NT / MERGE_CPARTS, ROWS = D / MERGE_CPARTS;
+        const int slab = tid / JT, jt = tid - slab * JT;
+        for (int j = jt; j < D; j += JT) {
+            float acc[HPG];
+#pragma unroll
+            for (int h = 0; h < HPG; ++h) acc[h] = 0.f;
 #pragma unroll 4
-            for (int sidx = part; sidx < p.n_ps; sidx += parts) rot = fmaf(s_w[sidx], p.part_o[((base + sidx) * SL + hs) * d + c], rot);
-            for (int sidx = p.n_ps + part; sidx < S; sidx += parts) raw = fmaf(s_w[sidx], p.part_o[((base + sidx) * SL + hs) * d + c], raw);
+            for (int c4 = 0; c4 < ROWS / 4; ++c4) {
+                float r[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int c = slab * ROWS + c4 * 4 + u;
+                    if constexpr (DIRECT) r[u] = reinterpret_cast<const float*>(smem + rot_offset<D, NW>())[(c * (D / 4) + rot_pos(c, j >> 2)) * 4 + (j & 3)];
+                    else r[u] = __ldg(p.rot + int64_t(c) * D + j);
+                }
+#pragma unroll
+                for (int h = 0; h < HPG; ++h) {
+                    if (h < heads_here) {
+                        const float4 a = *reinterpret_cast<const float4*>(s_acc + h * D + slab * ROWS + c4 * 4);
+                        acc[h] = fmaf(a.x, r[0], fmaf(a.y, r[1], fmaf(a.z, r[2], fmaf(a.w, r[3], acc[h]))));
+                    }
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < HPG; ++h)
+                if (h < heads_here) s_pp[(slab * HPG + h) * D + j] = acc[h];
         }
         __syncthreads();
-        if (part < parts) { s_part[part][c] = rot; }
-        __syncthreads();
-        if (part == 0) {
+        for (int e = tid; e < D * heads_here; e += NT) {
+            const int h = e / D, j = e - h * D;
             float v = 0.f;
-            for (int q = 0; q < parts; ++q) v += s_part[q][c];
-            const int v_half = p.vb_lo ? d / 2 : d;
-            s_rot[c] = v / (c < v_half ? p.v_scale_hi : p.v_scale_lo);
+#pragma unroll
+            for (int x = 0; x < MERGE_CPARTS; ++x) v += s_pp[(x * HPG + h) * D + j];
+            po[e] = v;
         }
-        __syncthreads();
-        if (part < parts) { s_part[part][c] = raw; }
-        __syncthreads();
-        if (part == 0) {
-            float v = 0.f;
-            for (int q = 0; q < parts; ++q) v += s_part[q][c];
-            s_raw[c] = v;
+    }
+
+    // ---------------- last arrival for this (sequence, KV head, head group) merges -----------------------
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();       // cumulative: publishes the partial every thread of this CTA wrote before the barrier
+        const int prev = atomicAdd(p.counters + grp, 1);
+        s_misc[8] = (prev == S - 1) ? 1.f : 0.f;
+        if (prev == S - 1) {
+            __threadfence();
+            p.counters[grp] = 0;     // ready for the next launch
         }
+    }
+    TQ_STAMP(5);
+    __syncthreads();
+    if (s_misc[8] == 0.f) return;
+    TQ_STAMP(7);
+    const int SL = p.slots;
+    const int64_t base = grp * S;
+    // thread (h, c) loads its partial accumulators of up to 24 splits while other threads fetch the (max, sum)
+    // pairs into shared memory: one round of loads; the log-sum-exp weights are then recomputed per thread
+    float2* s_ml = reinterpret_cast<float2*>(smem);                             // [8][MAX_SPLITS]
+    constexpr int U = 24;
+    const int e0 = tid;                                                         // first (h, c) element of this thread
+    float v0[U];
+    {
+        const int h = e0 / D, c = e0 - h * D;
+        const float* src = p.part_o + (base * SL + h) * D + c;
+        const int64_t stride = int64_t(SL) * D;
+#pragma unroll
+        for (int u = 0; u < U; ++u) v0[u] = (e0 < D * heads_here && u < S) ? __ldcg(src + u * stride) : 0.f;
+    }
+    for (int idx = tid; idx < heads_here * S; idx += NT) {
+        const int h = idx / S, sidx = idx - h * S;
+        s_ml[h * MAX_SPLITS + sidx] = __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((base + sidx) * SL + h) * 2));
     }
     __syncthreads();
-    // (3) thread (j, part): rows [part*d/parts, (part+1)*d/parts) of R, column j  (y @ R, rotation.py:68-78)
-    for (int j = cj; j < d; j += JW) {
-        float r = 0.f;
-        if (part < parts) {
-            const int c0 = part * (d / parts), c1 = c0 + d / parts;
-#pragma unroll 8
-            for (int c = c0; c < c1; ++c) r = fmaf(s_rot[c], __ldg(p.rot + int64_t(c) * d + j), r);
+    TQ_STAMP(8);
+    for (int e = tid; e < D * heads_here; e += NT) {
+        const int h = e / D, c = e - h * D;
+        const float* src = p.part_o + (base * SL + h) * D + c;
+        const int64_t stride = int64_t(SL) * D;
+        const float2* ml = s_ml + h * MAX_SPLITS;
+        float M = -INFINITY;
+        for (int sidx = 0; sidx < S; ++sidx) M = fmaxf(M, ml[sidx].x);
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (u < S) {
+                const float2 x = ml[u];
+                const float w = (x.x == -INFINITY) ? 0.f : ex2(x.x - M);
+                L = fmaf(w, x.y, L);
+                acc = fmaf(w, (e == e0) ? v0[u] : __ldcg(src + u * stride), acc);
+            }
         }
-        __syncthreads();
-        if (part < parts) s_part[part][j] = r;
-        __syncthreads();
-        if (part == 0) {
-            float v = s_raw[j];
-            for (int q = 0; q < parts; ++q) v += s_part[q][j];
-            store_from_f32(p.out, p.out_dtype, (int64_t(b) * p.Hq + h) * d + j, v * s_inv);
+        for (int sidx = U; sidx < S; ++sidx) {
+            const float2 x = ml[sidx];
+            const float w = (x.x == -INFINITY) ? 0.f : ex2(x.x - M);
+            L = fmaf(w, x.y, L);
+            acc = fmaf(w, __ldcg(src + sidx * stride), acc);
         }
+        store_from_f32(p.out, p.out_dtype, qbase + e, acc / L);
     }
+    TQ_STAMP(6);
 }
 
 // ---- host side ------------------------------------------------------------------------------------
-static int g_tune_ctas_per_sm = 2;     // CTAs the partial kernel keeps resident per SM (split heuristic)
+static int g_tune_ctas_per_sm = 1;     // CTAs of the general path resident per SM (split heuristic)
 static int g_tune_force_general = 0;   // 1: never take the direct path (testing)
 static int g_tune_splits = 0;          // > 0: fixed number of packed splits
-static int g_tune_pdl = 1;             // programmatic dependent launch between the three kernels
+static int g_tune_pdl = 1;             // programmatic dependent launch between consecutive calls
 
 static int sm_count() {
     static int n = 0;
@@ -648,20 +840,21 @@ static int sm_count() {
 
 struct SplitPlan { int n_ps, n_ds, hg; int64_t p_tps, d_tps; };
 
-static SplitPlan plan_splits(int batch, int n_q_heads, int n_kv_heads, int64_t c_len, int64_t dense_len, int sms) {
+static SplitPlan plan_splits(int batch, int n_q_heads, int n_kv_heads, int64_t c_len, int64_t dense_len, int sms, bool direct) {
+    const int NW = warps_per_cta(direct);
     SplitPlan s{};
     const int G = n_q_heads / n_kv_heads;
     s.hg = (G + HPG - 1) / HPG;
     const int64_t lanes = int64_t(batch) * n_kv_heads * s.hg;
     const int64_t p_tiles = (c_len + TILE - 1) / TILE, d_tiles = (dense_len + TILE - 1) / TILE;
     if (d_tiles > 0) {
-        s.d_tps = 2 * NW;   // two tiles per warp
+        s.d_tps = direct ? NW : 2 * NW;   // tiles per dense CTA: one (16 warps) or two (8 warps) per warp
         s.n_ds = int((d_tiles + s.d_tps - 1) / s.d_tps);
         if (s.n_ds > 64) { s.d_tps = (d_tiles + 63) / 64; s.n_ds = int((d_tiles + s.d_tps - 1) / s.d_tps); }
     }
     if (p_tiles > 0) {
         // all CTAs of the grid resident at once: (packed + dense splits) * lanes <= SMs * CTAs per SM
-        const int64_t slots = int64_t(sms) * g_tune_ctas_per_sm;
+        const int64_t slots = int64_t(sms) * (direct ? 1 : g_tune_ctas_per_sm);
         int64_t want = g_tune_splits > 0 ? g_tune_splits : slots / lanes - s.n_ds;
         const int64_t max_useful = (p_tiles + 2 * NW - 1) / (2 * NW);   // at least two tiles per warp
         if (want > max_useful) want = max_useful;
@@ -675,53 +868,129 @@ static SplitPlan plan_splits(int batch, int n_q_heads, int n_kv_heads, int64_t c
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-struct WsLayout { size_t q_rot, q_raw, part_o, part_ml, total; };
+// The arrival counters sit at the start of the workspace so that their position does not depend on the plan.
+struct WsLayout { size_t counters, part_o, part_ml, total; };
 
 static WsLayout ws_layout(int batch, int n_q_heads, int n_kv_heads, int d, const SplitPlan& s) {
     WsLayout w{};
-    const size_t qn = size_t(batch) * n_q_heads * d * sizeof(__half);
-    const size_t parts = size_t(batch) * n_kv_heads * s.hg * size_t(s.n_ps + s.n_ds);
+    const size_t groups = size_t(batch) * n_kv_heads * s.hg;
+    const size_t parts = groups * size_t(s.n_ps + s.n_ds);
     const size_t slots = size_t(std::min(n_q_heads / n_kv_heads, HPG));
-    w.q_rot = 0;
-    w.q_raw = align_up(w.q_rot + qn, 256);
-    w.part_o = align_up(w.q_raw + qn, 256);
+    w.counters = 0;
+    w.part_o = align_up(groups * sizeof(int), 256);
     w.part_ml = align_up(w.part_o + parts * slots * d * sizeof(float), 256);
     w.total = align_up(w.part_ml + parts * slots * 2 * sizeof(float), 256);
     return w;
 }
 
-// Launch with programmatic stream serialisation: the kernel may become resident before its predecessor
-// on the stream has finished; every kernel here calls griddepcontrol.wait before touching dependent data.
-template <typename K> static int launch_pdl(K kernel, dim3 grid, unsigned block, size_t smem, cudaStream_t s,
-                                            const DecodeParams& p, const char* what) {
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = grid; cfg.blockDim = dim3(block); cfg.dynamicSmemBytes = smem; cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = g_tune_pdl ? 1 : 0;
-    cfg.attrs = attr; cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, p);
-    if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
-    return TQ_OK;
-}
-
-template <int D, bool DIRECT> static int launch_partial(const DecodeParams& p, cudaStream_t s) {
-    constexpr size_t smem = partial_smem<D, DIRECT>();
+template <int D, bool DIRECT> static int launch_decode(const DecodeParams& p, cudaStream_t s) {
+    constexpr size_t smem = kernel_smem<D, DIRECT>();
     static bool set[16] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 16 && !set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(decode_partial_kernel<D, DIRECT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        cudaError_t e = cudaFuncSetAttribute(decode_attn_kernel<D, DIRECT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_decode_attn: shared memory %zu B: %s", smem, cudaGetErrorString(e));
         set[dev] = true;
     }
-    dim3 grid(unsigned(p.n_ps + p.n_ds), unsigned(p.Hkv * p.HG), unsigned(p.B));
-    return launch_pdl(decode_partial_kernel<D, DIRECT>, grid, NW * 32, smem, s, p, "tq_decode_attn (partial)");
+    // Programmatic stream serialisation: the grid may become resident before its predecessor on the stream
+    // has finished; the kernel calls griddepcontrol.wait before it touches anything but constants.
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(p.n_ps + p.n_ds), unsigned(p.Hkv * p.HG), unsigned(p.B));
+    cfg.blockDim = dim3(warps_per_cta(DIRECT) * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = g_tune_pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_attn_kernel<D, DIRECT>, p);
+    if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_decode_attn: %s", cudaGetErrorString(e));
+    return TQ_OK;
+}
+
+// Validates the arguments, picks the path and the split plan and fills the kernel parameters.
+int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_bytes, DecodeParams* out, bool* direct_out) {
+    if (!a) return fail(TQ_ERR_INVALID, "tq_decode_attn: null args");
+    const int d = a->d;
+    if (a->batch <= 0 || a->n_q_heads <= 0 || a->n_kv_heads <= 0 || a->n_q_heads % a->n_kv_heads)
+        return fail(TQ_ERR_INVALID, "tq_decode_attn: batch=%d q_heads=%d kv_heads=%d", a->batch, a->n_q_heads, a->n_kv_heads);
+    if (d != 64 && d != 96 && d != 128 && d != 256) return fail(TQ_ERR_UNSUPPORTED, "tq_decode_attn: d=%d (64, 96, 128 or 256)", d);
+    if (a->c_len < 0 || a->sink_len < 0 || a->res_len < 0 || a->c_len + a->sink_len + a->res_len == 0)
+        return fail(TQ_ERR_INVALID, "tq_decode_attn: the cache holds no tokens");
+    if (a->c_len >= (int64_t(1) << 30)) return fail(TQ_ERR_UNSUPPORTED, "tq_decode_attn: c_len too large");
+    if (!a->q || !a->rot || !a->out || !workspace) return fail(TQ_ERR_INVALID, "tq_decode_attn: null pointer");
+    if (a->q_dtype < 0 || a->q_dtype > 2 || a->out_dtype < 0 || a->out_dtype > 2 || a->dense_dtype < 0 || a->dense_dtype > 2)
+        return fail(TQ_ERR_INVALID, "tq_decode_attn: bad dtype");
+    if (!aligned(a->rot, 16)) return fail(TQ_ERR_INVALID, "tq_decode_attn: rot must be 16-byte aligned");
+    if (a->c_len > 0) {
+        if (!bits_ok(a->k_bits_hi) || !bits_ok(a->v_bits_hi) || (a->k_bits_lo && !bits_ok(a->k_bits_lo)) || (a->v_bits_lo && !bits_ok(a->v_bits_lo)))
+            return fail(TQ_ERR_INVALID, "Unsupported bit-width. Use 1, 2, 3, or 4.");
+        if (!a->k_hi || !a->v_hi || !a->k_norms || !a->v_norms || !a->k_cent_hi || !a->v_cent_hi || (a->k_bits_lo && (!a->k_lo || !a->k_cent_lo)) ||
+            (a->v_bits_lo && (!a->v_lo || !a->v_cent_lo)))
+            return fail(TQ_ERR_INVALID, "tq_decode_attn: null packed-cache pointer");
+        if (a->c_lane_stride < a->c_len) return fail(TQ_ERR_INVALID, "tq_decode_attn: c_lane_stride < c_len");
+        if (a->k_qjl_bits || a->v_qjl_bits) return fail(TQ_ERR_UNSUPPORTED, "tq_decode_attn: QJL sketches are not supported by this build");
+    }
+    if ((a->sink_len > 0 && (!a->sink_k || !a->sink_v || a->sink_lane_stride < a->sink_len)) ||
+        (a->res_len > 0 && (!a->res_k || !a->res_v || a->res_lane_stride < a->res_len)))
+        return fail(TQ_ERR_INVALID, "tq_decode_attn: bad sink / residual buffers");
+    if (a->dense_dtype == TQ_F16 && ((a->sink_len > 0 && (!aligned(a->sink_k, 16) || !aligned(a->sink_v, 16))) ||
+                                     (a->res_len > 0 && (!aligned(a->res_k, 16) || !aligned(a->res_v, 16)))))
+        return fail(TQ_ERR_INVALID, "tq_decode_attn: fp16 sink / residual buffers must be 16-byte aligned");
+    if (!aligned(workspace, 256)) return fail(TQ_ERR_INVALID, "tq_decode_attn: workspace must be 256-byte aligned");
+
+    const int64_t dense_len = a->sink_len + a->res_len;
+    // direct path: 4-bit keys / 2-bit values, d = 128, rows and norms addressable in aligned 16-byte chunks
+    const bool direct = !g_tune_force_general && d == 128 && a->c_len > 0 && a->k_bits_hi == 4 && a->k_bits_lo == 0 &&
+                        a->v_bits_hi == 2 && a->v_bits_lo == 0 && aligned(a->k_hi, 16) && aligned(a->v_hi, 16) &&
+                        aligned(a->k_norms, 16) && aligned(a->v_norms, 16) && a->c_lane_stride % 16 == 0;
+    const SplitPlan sp = plan_splits(a->batch, a->n_q_heads, a->n_kv_heads, a->c_len, dense_len, sm_count(), direct);
+    const WsLayout wl = ws_layout(a->batch, a->n_q_heads, a->n_kv_heads, d, sp);
+    if (wl.total > workspace_bytes) return fail(TQ_ERR_INVALID, "tq_decode_attn: workspace %zu B < %zu B", workspace_bytes, wl.total);
+    if (sp.n_ps + sp.n_ds > MAX_SPLITS) return fail(TQ_ERR_UNSUPPORTED, "tq_decode_attn: too many splits");
+
+    DecodeParams p{};
+    p.B = a->batch; p.Hq = a->n_q_heads; p.Hkv = a->n_kv_heads; p.G = p.Hq / p.Hkv; p.HG = sp.hg; p.D = d; p.slots = std::min(p.G, HPG);
+    p.c_len = a->c_len; p.c_ls = a->c_lane_stride;
+    p.kb_hi = a->k_bits_hi; p.kb_lo = a->k_bits_lo; p.vb_hi = a->v_bits_hi; p.vb_lo = a->v_bits_lo;
+    p.k_hi = a->k_hi; p.k_lo = a->k_lo; p.v_hi = a->v_hi; p.v_lo = a->v_lo;
+    p.k_norms = a->k_norms; p.v_norms = a->v_norms;
+    p.kc_hi = a->k_cent_hi; p.kc_lo = a->k_cent_lo; p.vc_hi = a->v_cent_hi; p.vc_lo = a->v_cent_lo;
+    p.dense_dtype = a->dense_dtype;
+    p.sink_k = a->sink_k; p.sink_v = a->sink_v; p.res_k = a->res_k; p.res_v = a->res_v;
+    p.sink_len = a->sink_len; p.sink_ls = a->sink_lane_stride; p.res_len = a->res_len; p.res_ls = a->res_lane_stride;
+    p.n_ps = sp.n_ps; p.n_ds = sp.n_ds; p.p_tps = sp.p_tps; p.d_tps = sp.d_tps;
+    p.q = a->q; p.q_dtype = a->q_dtype; p.scale = a->scale; p.rot = a->rot;
+    p.v_scale_hi = a->v_cent_scale_hi > 0.f ? a->v_cent_scale_hi : 1.f;
+    p.v_scale_lo = a->v_cent_scale_lo > 0.f ? a->v_cent_scale_lo : 1.f;
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    p.counters = reinterpret_cast<int*>(ws + wl.counters);
+    p.part_o = reinterpret_cast<float*>(ws + wl.part_o); p.part_ml = reinterpret_cast<float*>(ws + wl.part_ml);
+    p.out = a->out; p.out_dtype = a->out_dtype;
+    *out = p;
+    *direct_out = direct;
+    return TQ_OK;
+}
+
+int decode_launch(const DecodeParams& p, bool direct, cudaStream_t s) {
+    if (direct) return launch_decode<128, true>(p, s);
+    if (p.D == 64) return launch_decode<64, false>(p, s);
+    if (p.D == 96) return launch_decode<96, false>(p, s);
+    if (p.D == 128) return launch_decode<128, false>(p, s);
+    return launch_decode<256, false>(p, s);
 }
 
 }  // namespace tq
 
 using namespace tq;
+
+#ifdef TQ_TIMING
+extern "C" int tq_debug_timing(unsigned long long* host_out, int n) {
+    return int(cudaMemcpyFromSymbol(host_out, g_tq_timing, sizeof(unsigned long long) * n));
+}
+#endif
 
 extern "C" int tq_set_tuning(const char* key, int value) {
     if (!key) return fail(TQ_ERR_INVALID, "tq_set_tuning: null key");
@@ -758,76 +1027,16 @@ extern "C" float tq_fp16_table_scale(const float* centroids_host, int n) {
 extern "C" size_t tq_decode_workspace_bytes(int batch, int n_q_heads, int n_kv_heads, int d, int64_t c_len,
                                             int64_t dense_len) {
     if (batch <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || d <= 0 || n_q_heads % n_kv_heads || c_len < 0 || dense_len < 0) return 0;
-    // Same split plan tq_decode_attn will use for these sizes (and the current tuning values).
-    const SplitPlan s = plan_splits(batch, n_q_heads, n_kv_heads, c_len, dense_len, sm_count());
-    return ws_layout(batch, n_q_heads, n_kv_heads, d, s).total;
+    // The larger of the two split plans tq_decode_attn can choose for these sizes (current tuning values).
+    const size_t a = ws_layout(batch, n_q_heads, n_kv_heads, d, plan_splits(batch, n_q_heads, n_kv_heads, c_len, dense_len, sm_count(), false)).total;
+    const size_t b = ws_layout(batch, n_q_heads, n_kv_heads, d, plan_splits(batch, n_q_heads, n_kv_heads, c_len, dense_len, sm_count(), true)).total;
+    return a > b ? a : b;
 }
 
 extern "C" int tq_decode_attn(const tq_decode_args* a, void* stream) {
-    if (!a) return fail(TQ_ERR_INVALID, "tq_decode_attn: null args");
-    const int d = a->d;
-    if (a->batch <= 0 || a->n_q_heads <= 0 || a->n_kv_heads <= 0 || a->n_q_heads % a->n_kv_heads)
-        return fail(TQ_ERR_INVALID, "tq_decode_attn: batch=%d q_heads=%d kv_heads=%d", a->batch, a->n_q_heads, a->n_kv_heads);
-    if (d != 64 && d != 96 && d != 128 && d != 256) return fail(TQ_ERR_UNSUPPORTED, "tq_decode_attn: d=%d (64, 96, 128 or 256)", d);
-    if (a->c_len < 0 || a->sink_len < 0 || a->res_len < 0 || a->c_len + a->sink_len + a->res_len == 0)
-        return fail(TQ_ERR_INVALID, "tq_decode_attn: the cache holds no tokens");
-    if (!a->q || !a->rot || !a->out || !a->workspace) return fail(TQ_ERR_INVALID, "tq_decode_attn: null pointer");
-    if (a->q_dtype < 0 || a->q_dtype > 2 || a->out_dtype < 0 || a->out_dtype > 2 || a->dense_dtype < 0 || a->dense_dtype > 2)
-        return fail(TQ_ERR_INVALID, "tq_decode_attn: bad dtype");
-    if (a->c_len > 0) {
-        if (!bits_ok(a->k_bits_hi) || !bits_ok(a->v_bits_hi) || (a->k_bits_lo && !bits_ok(a->k_bits_lo)) || (a->v_bits_lo && !bits_ok(a->v_bits_lo)))
-            return fail(TQ_ERR_INVALID, "Unsupported bit-width. Use 1, 2, 3, or 4.");
-        if (!a->k_hi || !a->v_hi || !a->k_norms || !a->v_norms || !a->k_cent_hi || !a->v_cent_hi || (a->k_bits_lo && (!a->k_lo || !a->k_cent_lo)) ||
-            (a->v_bits_lo && (!a->v_lo || !a->v_cent_lo)))
-            return fail(TQ_ERR_INVALID, "tq_decode_attn: null packed-cache pointer");
-        if (a->c_lane_stride < a->c_len) return fail(TQ_ERR_INVALID, "tq_decode_attn: c_lane_stride < c_len");
-        if (a->k_qjl_bits || a->v_qjl_bits) return fail(TQ_ERR_UNSUPPORTED, "tq_decode_attn: QJL sketches are not supported by this build");
-    }
-    if ((a->sink_len > 0 && (!a->sink_k || !a->sink_v || a->sink_lane_stride < a->sink_len)) ||
-        (a->res_len > 0 && (!a->res_k || !a->res_v || a->res_lane_stride < a->res_len)))
-        return fail(TQ_ERR_INVALID, "tq_decode_attn: bad sink / residual buffers");
-    if (a->dense_dtype == TQ_F16 && ((a->sink_len > 0 && (!aligned(a->sink_k, 16) || !aligned(a->sink_v, 16))) ||
-                                     (a->res_len > 0 && (!aligned(a->res_k, 16) || !aligned(a->res_v, 16)))))
-        return fail(TQ_ERR_INVALID, "tq_decode_attn: fp16 sink / residual buffers must be 16-byte aligned");
-    if (!aligned(a->workspace, 256)) return fail(TQ_ERR_INVALID, "tq_decode_attn: workspace must be 256-byte aligned");
-
-    const int64_t dense_len = a->sink_len + a->res_len;
-    const SplitPlan sp = plan_splits(a->batch, a->n_q_heads, a->n_kv_heads, a->c_len, dense_len, sm_count());
-    const WsLayout wl = ws_layout(a->batch, a->n_q_heads, a->n_kv_heads, d, sp);
-    if (wl.total > a->workspace_bytes) return fail(TQ_ERR_INVALID, "tq_decode_attn: workspace %zu B < %zu B", a->workspace_bytes, wl.total);
-    if (sp.n_ps + sp.n_ds > MAX_SPLITS) return fail(TQ_ERR_UNSUPPORTED, "tq_decode_attn: too many splits");
-
-    DecodeParams p{};
-    p.B = a->batch; p.Hq = a->n_q_heads; p.Hkv = a->n_kv_heads; p.G = p.Hq / p.Hkv; p.HG = sp.hg; p.D = d; p.slots = std::min(p.G, HPG);
-    p.c_len = a->c_len; p.c_ls = a->c_lane_stride;
-    p.kb_hi = a->k_bits_hi; p.kb_lo = a->k_bits_lo; p.vb_hi = a->v_bits_hi; p.vb_lo = a->v_bits_lo;
-    p.k_hi = a->k_hi; p.k_lo = a->k_lo; p.v_hi = a->v_hi; p.v_lo = a->v_lo;
-    p.k_norms = a->k_norms; p.v_norms = a->v_norms;
-    p.kc_hi = a->k_cent_hi; p.kc_lo = a->k_cent_lo; p.vc_hi = a->v_cent_hi; p.vc_lo = a->v_cent_lo;
-    p.dense_dtype = a->dense_dtype;
-    p.sink_k = a->sink_k; p.sink_v = a->sink_v; p.res_k = a->res_k; p.res_v = a->res_v;
-    p.sink_len = a->sink_len; p.sink_ls = a->sink_lane_stride; p.res_len = a->res_len; p.res_ls = a->res_lane_stride;
-    p.n_ps = sp.n_ps; p.n_ds = sp.n_ds; p.p_tps = sp.p_tps; p.d_tps = sp.d_tps;
-    p.q = a->q; p.q_dtype = a->q_dtype; p.scale = a->scale; p.rot = a->rot;
-    p.v_scale_hi = a->v_cent_scale_hi > 0.f ? a->v_cent_scale_hi : 1.f;
-    p.v_scale_lo = a->v_cent_scale_lo > 0.f ? a->v_cent_scale_lo : 1.f;
-    unsigned char* ws = static_cast<unsigned char*>(a->workspace);
-    p.q_rot = reinterpret_cast<__half*>(ws + wl.q_rot); p.q_raw = reinterpret_cast<__half*>(ws + wl.q_raw);
-    p.part_o = reinterpret_cast<float*>(ws + wl.part_o); p.part_ml = reinterpret_cast<float*>(ws + wl.part_ml);
-    p.out = a->out; p.out_dtype = a->out_dtype;
-
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    int rc = launch_pdl(decode_prep_kernel, dim3(unsigned(p.B * p.Hq)), unsigned(d), 0, s, p, "tq_decode_attn (prep)");
+    DecodeParams p;
+    bool direct = false;
+    int rc = decode_prepare(a, a ? a->workspace : nullptr, a ? a->workspace_bytes : 0, &p, &direct);
     if (rc) return rc;
-
-    const bool direct = !g_tune_force_general && d == 128 && a->c_len > 0 && a->k_bits_hi == 4 && a->k_bits_lo == 0 &&
-                        a->v_bits_hi == 2 && a->v_bits_lo == 0 && aligned(a->k_hi, 16) && aligned(a->v_hi, 16);
-    if (direct) rc = launch_partial<128, true>(p, s);
-    else if (d == 64) rc = launch_partial<64, false>(p, s);
-    else if (d == 96) rc = launch_partial<96, false>(p, s);
-    else if (d == 128) rc = launch_partial<128, false>(p, s);
-    else rc = launch_partial<256, false>(p, s);
-    if (rc) return rc;
-
-    return launch_pdl(decode_merge_kernel, dim3(unsigned(p.Hq), unsigned(p.B)), MERGE_T, 0, s, p, "tq_decode_attn (merge)");
+    return decode_launch(p, direct, static_cast<cudaStream_t>(stream));
 }

@@ -206,11 +206,13 @@ _workspaces: dict[tuple[str, int], torch.Tensor] = {}
 
 
 def decode_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """Scratch for the decode kernels, one buffer per (device, stream), grown on demand."""
+    """Scratch for the decode kernel, one zero-filled buffer per (device, stream), grown on demand.
+
+    The kernel keeps arrival counters in it and leaves them at zero, so the buffer must start zeroed."""
     key = (str(device), torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
 
