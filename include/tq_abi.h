@@ -93,6 +93,11 @@ typedef struct {
  * metal_quantize_4bit (kernels.py:363-409). */
 int tq_quantize_pack(const tq_quantize_args* a, void* stream);
 
+/* fp16 rows with d = 128 take a tensor-core (tcgen05) kernel whose inter-warp waits are bounded; if one ever
+ * timed out the kernel drains, and this returns the code of the first such wait (0 = none) for the current
+ * device.  Synchronises the device; no reference counterpart. */
+int tq_device_status(void);
+
 /* ---- dequantize: unpack -> centroid -> inverse rotation -> scale ------------------------- */
 
 typedef struct {

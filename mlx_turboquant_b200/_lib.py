@@ -79,6 +79,7 @@ PROTOTYPES = {
     "tq_decode_attn": (_i, [C.POINTER(DecodeArgs), _vp]),
     "tq_set_tuning": (_i, [C.c_char_p, _i]),
     "tq_fp16_table_scale": (_f, [_vp, _i]),
+    "tq_device_status": (_i, []),
 }
 
 _lib = None

@@ -1,8 +1,431 @@
-// Tensor-core (tcgen05) quantize kernel for fp16 rows, d = 128.  Placeholder dispatcher: reports
-// "not handled" so the caller takes the general CUDA-core path.
+// Fused quantize kernel on the 5th-generation tensor cores (tcgen05 + TMEM) for fp16 rows with d = 128:
+//   norm -> rotation (128 x 128 x 128 contraction per tile of 128 rows) -> Lloyd-Max boundary search -> bit-pack.
+//
+// The rotation has to be float32-accurate (a code flips whenever a rotated value crosses a boundary), so the
+// fp16 rows are used UN-normalised as exact MMA operands and R is split into two fp16 matrices,
+// R = R_hi + 2^-11 * R_lo; both products are exact in the fp32 accumulators, and the normalisation by the
+// row norm is applied afterwards.  Per tile: 2 x 8 tcgen05.mma (M = 128, N = 128, K = 16) into two TMEM
+// accumulators, double-buffered so that the epilogue of tile i overlaps the loads and MMAs of tile i+1.
+//
+// Warp roles in a persistent CTA (one per SM, 544 threads):
+//   warps 0-7   epilogue: thread <-> one row (TMEM lane) and one half of the coordinates; tcgen05.ld, boundary
+//               search through a 513-bin lookup table (bin -> nearest boundary + count below it; exact, see
+//               build_bins), packing, 128-bit stores
+//   warp  8     allocates TMEM, issues the MMAs (one elected thread) and commits them to mbarriers
+//   warps 9-16  producers: 128-bit global loads of the rows, sum of squares for the norm, stores into the
+//               128-byte-swizzled K-major shared-memory layout the MMA descriptors expect
+// Every mbarrier wait is bounded: on a timeout the kernel raises a status word, drains and frees its TMEM.
+#include <algorithm>
+#include <cstdlib>
+
 #include "common.cuh"
 
-int tq_quantize_pack_tc(const tq_quantize_args*, cudaStream_t, bool* handled) {
+namespace tq {
+
+namespace tc {
+
+constexpr int D = 128, TM = 128;                 // head_dim, rows per tile
+constexpr int A_STAGES = 3, ACC_STAGES = 2;
+constexpr int N_EPI = 256, N_PROD = 256;         // threads per role
+constexpr int NT = N_EPI + 32 + N_PROD;          // 544
+constexpr int KBLK_BYTES = TM * 128;             // one 64-column K-block of a 128-row operand: 16 KB
+constexpr int OPER_BYTES = 2 * KBLK_BYTES;       // 32 KB per operand tile
+constexpr int NBINS = 516;                       // 513 used + guard
+constexpr uint32_t WAIT_LIMIT = 4u << 20;        // bounded spin: a few hundred milliseconds at most
+
+// shared memory map (bytes)
+constexpr int OFF_A = 0;                                   // A_STAGES x 32 KB, 1024-byte aligned
+constexpr int OFF_RHI = OFF_A + A_STAGES * OPER_BYTES;     // 32 KB
+constexpr int OFF_RLO = OFF_RHI + OPER_BYTES;              // 32 KB
+constexpr int OFF_BINS = OFF_RLO + OPER_BYTES;             // 2 tables x NBINS x 8 B
+constexpr int OFF_BND = OFF_BINS + 2 * NBINS * 8;          // 2 x 16 floats: raw boundaries (slow path)
+constexpr int OFF_NSQ = OFF_BND + 128;                     // A_STAGES x 2 x 128 floats: partial sums of squares
+constexpr int OFF_BAR = OFF_NSQ + A_STAGES * 2 * TM * 4;   // mbarriers
+constexpr int OFF_MISC = OFF_BAR + 16 * 8;                 // tmem base, abort flag
+constexpr int SMEM_BYTES = OFF_MISC + 64;
+
+struct Params {
+    const __half* x; int64_t n_lanes, n_rows, x_lane_stride, x_row_stride;
+    const float* rot;
+    const float* bnd_hi; const float* bnd_lo; int bits_hi, bits_lo;
+    uint8_t* p_hi; uint8_t* p_lo; float* norms; int64_t out_lane_stride;
+    int64_t n_tiles;
+    int* status;
+};
+
+__device__ int g_status = 0;   // 0 ok, otherwise the code of the first wait that timed out
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false after WAIT_LIMIT polls (or when another role already gave up).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = code;
+    atomicCAS(&g_status, 0, code);
+    return false;
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    const uint32_t zero = 0;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(zero), "r"(zero), "r"(zero), "r"(zero) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile in shared memory, 128-byte swizzle: row r of K-block b at  b*16 KB + r*128 B, its 16-byte
+// chunk c stored at chunk position c ^ (r & 7).  Descriptor for the 16-column slab `ks` (0..3) of K-block b.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t tile_addr, int kblk, int ks) {
+    const uint32_t addr = tile_addr + kblk * KBLK_BYTES + ks * 32;
+    uint64_t d = 0;
+    d |= uint64_t((addr >> 4) & 0x3FFF);          // start address
+    d |= uint64_t(1) << 16;                       // leading byte offset (ignored for swizzled K-major)
+    d |= uint64_t(1024 >> 4) << 32;               // stride byte offset: 8 rows x 128 B
+    d |= uint64_t(1) << 46;                       // descriptor version (Blackwell)
+    d |= uint64_t(2) << 61;                       // SWIZZLE_128B
+    return d;
+}
+// kind::f16: fp16 A and B, fp32 accumulate, both K-major, N = 128, M = 128
+constexpr uint32_t IDESC = (1u << 4) | (uint32_t(D >> 3) << 17) | (uint32_t(TM >> 4) << 24);
+
+// Lookup table for the boundary search.  Bin k covers normalised values around (k - 256) / 256 (width 1/256);
+// entry = (boundary to test, number of boundaries below the bin's neighbourhood) where the neighbourhood is the
+// bin widened by one bin on each side, so that a bin index that is off by one through rounding still gives the
+// exact count.  A neighbourhood holding two boundaries is marked (NaN) and handled by the plain counting loop.
+__device__ void build_bins(float2* bins, const float* bnd, int n_bnd, int tid, int nthreads) {
+    for (int k = tid; k < NBINS; k += nthreads) {
+        const float lo = (float(k) - 256.f - 1.5f) / 256.f, hi = (float(k) - 256.f + 1.5f) / 256.f;
+        int below = 0, inside = 0;
+        float b_in = INFINITY;
+        for (int i = 0; i < n_bnd; ++i) {
+            const float b = bnd[i];
+            if (b < lo) ++below;
+            else if (b <= hi) { ++inside; b_in = b; }
+        }
+        bins[k] = make_float2(inside > 1 ? __int_as_float(0x7fc00000) : b_in, __int_as_float(below));
+    }
+}
+
+__device__ __forceinline__ uint32_t code_of(float yp, float rinv, float rbin, const float2* bins, const float* raw_bnd, int n_bnd) {
+    // bin index from the mantissa of (y * 256 + 256 + 2^23): exact rounding to nearest, no convert instruction
+    const float tt = fmaf(yp, rbin, 8388608.f + 256.f);
+    const uint32_t k = min(__float_as_uint(tt) & 0x3FFu, uint32_t(NBINS - 1));
+    const float2 e = bins[k];
+    const float y = yp * rinv;
+    uint32_t c = __float_as_uint(e.y) + (y > e.x ? 1u : 0u);     // strict >, codebook.py:220-223
+    if (e.x != e.x) {                                            // rare: two boundaries close together
+        c = 0;
+        for (int i = 0; i < n_bnd; ++i) c += (y > raw_bnd[i]) ? 1u : 0u;
+    }
+    return c;
+}
+
+struct EpiCtx {
+    const Params& p; unsigned char* smem; uint32_t tmem_base, bar_accfull, bar_accfree, bar_afree;
+    volatile int* abort_flag; int64_t total_rows; int warp, lane;
+};
+
+template <int BITS>
+__device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
+    const Params& p = e.p;
+    const int quad = e.warp & 3, half = e.warp >> 2, row_in_tile = quad * 32 + e.lane;
+    const bool second = p.bits_lo && half;
+    const float2* bins = reinterpret_cast<const float2*>(e.smem + OFF_BINS) + (second ? NBINS : 0);
+    const float* raw_bnd = reinterpret_cast<const float*>(e.smem + OFF_BND) + (second ? 16 : 0);
+    constexpr int n_bnd = (1 << BITS) - 1;
+    constexpr int WBYTES = 64 * BITS / 8;                       // bytes this thread produces per row
+    int it = 0;
+    for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
+        const int a = it % ACC_STAGES, s = it % A_STAGES;
+        if (!mbar_wait(e.bar_accfull + 8 * a, (it / ACC_STAGES) & 1, e.abort_flag, 3)) break;
+        tc_fence_after();
+        const float* nsq = reinterpret_cast<const float*>(e.smem + OFF_NSQ) + s * 2 * TM;
+        const float nrm = sqrtf(nsq[row_in_tile] + nsq[TM + row_in_tile]);
+        mbar_arrive(e.bar_afree + 8 * s);                       // norm slots of this stage are free again
+        const float rinv = 1.f / fmaxf(nrm, 1e-10f);            // cache.py:237-238 guards the zero vector the same way
+        const float rbin = rinv * 256.f;
+        const int64_t row = tile * TM + row_in_tile;
+        const bool live = row < e.total_rows;
+        int64_t orow = 0;
+        if (live) {
+            const int64_t o = row / p.n_rows, r = row - o * p.n_rows;
+            orow = o * p.out_lane_stride + r;
+            if (half == 0) p.norms[orow] = nrm;
+        }
+        const uint32_t t_hi = e.tmem_base + (uint32_t(quad * 32) << 16) + a * 256 + half * 64;
+        uint32_t words[8];                                      // up to 64 codes x 4 bits
+#pragma unroll
+        for (int i = 0; i < 8; ++i) words[i] = 0;
+#pragma unroll
+        for (int cb = 0; cb < 2; ++cb) {                        // 32 coordinates at a time
+            uint32_t vh[32], vl[32];
+            tmem_ld32(t_hi + cb * 32, vh);
+            tmem_ld32(t_hi + 128 + cb * 32, vl);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const float yp = fmaf(__uint_as_float(vl[i]), 1.f / 2048.f, __uint_as_float(vh[i]));
+                const uint32_t c = code_of(yp, rinv, rbin, bins, raw_bnd, n_bnd);
+                const int j = cb * 32 + i;                      // coordinate inside this half
+                if (BITS == 4) words[j >> 3] |= c << (4 * (j & 7));
+                else if (BITS == 2) words[j >> 4] |= c << (2 * (j & 15));
+                else if (BITS == 1) words[j >> 5] |= c << (j & 31);
+                else {                                          // 3 bits: 8 codes -> 24 bits, little-endian stream
+                    const int bit = 3 * j, w = bit >> 5, sh = bit & 31;
+                    words[w] |= c << sh;
+                    if (sh > 29) words[w + 1] |= c >> (32 - sh);
+                }
+            }
+        }
+        tc_fence_before();
+        mbar_arrive(e.bar_accfree + 8 * a);                     // accumulators may be overwritten
+        if (live) {
+            const bool frac = p.bits_lo != 0;
+            uint8_t* dst = second ? p.p_lo + orow * WBYTES : p.p_hi + orow * (frac ? WBYTES : 2 * WBYTES) + (frac ? 0 : half * WBYTES);
+            if ((WBYTES & 15) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                for (int i = 0; i < WBYTES / 16; ++i)
+                    reinterpret_cast<uint4*>(dst)[i] = make_uint4(words[4 * i], words[4 * i + 1], words[4 * i + 2], words[4 * i + 3]);
+            } else if ((WBYTES & 7) == 0 && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+#pragma unroll
+                for (int i = 0; i < WBYTES / 8; ++i) reinterpret_cast<uint2*>(dst)[i] = make_uint2(words[2 * i], words[2 * i + 1]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < WBYTES; ++i) dst[i] = uint8_t(words[i >> 2] >> (8 * (i & 3)));
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(NT, 1) quantize_tc_kernel(Params p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const uint32_t sbase = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 4);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
+    // barriers: full[A_STAGES] (producers -> MMA), a_free[A_STAGES] (MMA commit + epilogue's norm read -> producers),
+    //           acc_full[ACC_STAGES] (MMA commit -> epilogue), acc_free[ACC_STAGES] (epilogue -> MMA)
+    const uint32_t bar_full = sbase + OFF_BAR, bar_afree = bar_full + 8 * A_STAGES;
+    const uint32_t bar_accfull = bar_afree + 8 * A_STAGES, bar_accfree = bar_accfull + 8 * ACC_STAGES;
+
+    if (sbase & 1023u) {                  // the swizzled operand tiles need 1024-byte alignment (uniform across the CTA)
+        if (tid == 0) atomicCAS(&g_status, 0, 9);
+        return;
+    }
+    if (tid == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < A_STAGES; ++s) { mbar_init(bar_full + 8 * s, N_PROD); mbar_init(bar_afree + 8 * s, 1 + N_EPI); }
+        for (int a = 0; a < ACC_STAGES; ++a) { mbar_init(bar_accfull + 8 * a, 1); mbar_init(bar_accfree + 8 * a, N_EPI); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // R -> fp16 hi / lo operand tiles (swizzled K-major): B[n = j][k] = R[j][k]
+    for (int idx = tid; idx < D * (D / 8); idx += NT) {
+        const int j = idx / (D / 8), c = idx - j * (D / 8);      // row j, 16-byte chunk c (8 halves) of the row
+        const float4 f0 = __ldg(reinterpret_cast<const float4*>(p.rot + j * D + c * 8));
+        const float4 f1 = __ldg(reinterpret_cast<const float4*>(p.rot + j * D + c * 8 + 4));
+        const float v[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+        __align__(16) __half hi[8], lo[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            hi[i] = __float2half_rn(v[i]);
+            lo[i] = __float2half_rn((v[i] - __half2float(hi[i])) * 2048.f);
+        }
+        const int kblk = c >> 3, cc = c & 7;
+        const int off = kblk * KBLK_BYTES + j * 128 + ((cc ^ (j & 7)) << 4);
+        *reinterpret_cast<uint4*>(smem + OFF_RHI + off) = *reinterpret_cast<const uint4*>(hi);
+        *reinterpret_cast<uint4*>(smem + OFF_RLO + off) = *reinterpret_cast<const uint4*>(lo);
+    }
+    {
+        float* raw = reinterpret_cast<float*>(smem + OFF_BND);
+        if (tid < 32) {
+            const int side = tid >> 4, i = tid & 15;
+            const float* src = side ? p.bnd_lo : p.bnd_hi;
+            const int nb = (1 << (side ? p.bits_lo : p.bits_hi)) - 1;
+            raw[tid] = (src != nullptr && i < nb) ? src[i] : INFINITY;
+        }
+        __syncthreads();
+        build_bins(reinterpret_cast<float2*>(smem + OFF_BINS), raw, (1 << p.bits_hi) - 1, tid, NT);
+        if (p.bits_lo) build_bins(reinterpret_cast<float2*>(smem + OFF_BINS) + NBINS, raw + 16, (1 << p.bits_lo) - 1, tid, NT);
+    }
+    if (warp == 8) {                      // one warp owns the TMEM allocation: 2 stages x (hi + lo) x 128 columns
+        tmem_alloc(sbase + OFF_MISC, 512);
+        tmem_relinquish();
+    }
+    fence_proxy_async();                  // the operand tiles written above are read by the tensor core
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int64_t total_rows = p.n_lanes * p.n_rows;
+
+    if (warp < 8) {
+        // ======================= epilogue: row = 32*(warp%4) + lane, coordinate half = warp/4 =======================
+        const int bits = (p.bits_lo && (warp >> 2)) ? p.bits_lo : p.bits_hi;
+        EpiCtx e{p, smem, tmem_base, bar_accfull, bar_accfree, bar_afree, abort_flag, total_rows, warp, lane};
+        if (bits == 4) epilogue_loop<4>(e);
+        else if (bits == 3) epilogue_loop<3>(e);
+        else if (bits == 2) epilogue_loop<2>(e);
+        else epilogue_loop<1>(e);
+    } else if (warp == 8) {
+        // ======================= MMA issue: one elected thread =======================
+        if (lane == 0) {
+            int it = 0;
+            for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
+                const int a = it % ACC_STAGES, s = it % A_STAGES;
+                if (it >= ACC_STAGES && !mbar_wait(bar_accfree + 8 * a, ((it / ACC_STAGES) - 1) & 1, abort_flag, 2)) break;
+                if (!mbar_wait(bar_full + 8 * s, (it / A_STAGES) & 1, abort_flag, 1)) break;
+                tc_fence_after();
+                const uint32_t a_tile = sbase + OFF_A + s * OPER_BYTES;
+                const uint32_t d_hi = tmem_base + a * 256, d_lo = d_hi + 128;
+#pragma unroll
+                for (int kb = 0; kb < 2; ++kb) {
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint64_t da = smem_desc(a_tile, kb, ks);
+                        const uint32_t acc = (kb | ks) ? 1u : 0u;
+                        umma_f16(d_hi, da, smem_desc(sbase + OFF_RHI, kb, ks), IDESC, acc);
+                        umma_f16(d_lo, da, smem_desc(sbase + OFF_RLO, kb, ks), IDESC, acc);
+                    }
+                }
+                umma_commit(bar_afree + 8 * s);      // rows of this stage consumed: producers may refill it
+                umma_commit(bar_accfull + 8 * a);    // both accumulators complete: epilogue may read them
+            }
+        }
+        __syncwarp();
+    } else {
+        // ======================= producers: thread = (K-block, row) =======================
+        const int pt = tid - (N_EPI + 32);
+        const int kblk = pt >> 7, r = pt & 127;
+        int it = 0;
+        for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
+            const int s = it % A_STAGES;
+            const int64_t row = tile * TM + r;
+            uint4 v[8];
+            if (row < total_rows) {
+                const int64_t o = row / p.n_rows, rr = row - o * p.n_rows;
+                const uint4* src = reinterpret_cast<const uint4*>(p.x + o * p.x_lane_stride + rr * p.x_row_stride + kblk * 64);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) v[c] = __ldg(src + c);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) v[c] = make_uint4(0, 0, 0, 0);
+            }
+            float ss = 0.f;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const __half2* h = reinterpret_cast<const __half2*>(&v[c]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __half22float2(h[i]);
+                    ss = fmaf(f.x, f.x, ss);
+                    ss = fmaf(f.y, f.y, ss);
+                }
+            }
+            // the stage and its norm slots must be free: MMAs of tile it - A_STAGES done, its epilogue has read the norms
+            if (it >= A_STAGES && !mbar_wait(bar_afree + 8 * s, ((it / A_STAGES) - 1) & 1, abort_flag, 4)) break;
+            unsigned char* dst = smem + OFF_A + s * OPER_BYTES + kblk * KBLK_BYTES + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = v[c];
+            reinterpret_cast<float*>(smem + OFF_NSQ)[(s * 2 + kblk) * TM + r] = ss;
+            fence_proxy_async();                     // generic-proxy stores -> visible to the tensor core
+            mbar_arrive(bar_full + 8 * s);
+        }
+    }
+    // ---- teardown: every loop above is bounded, so every thread gets here ----
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+    if (tid == 0 && *abort_flag && p.status) *p.status = *abort_flag;
+}
+
+}  // namespace tc
+
+}  // namespace tq
+
+using namespace tq;
+
+// Takes the call when it fits the tensor-core kernel: fp16 rows, d = 128, 16-byte aligned rows, no QJL sketch,
+// no rotated-row output.  Otherwise reports "not handled" and the caller uses the general CUDA-core kernel.
+int tq_quantize_pack_tc(const tq_quantize_args* q, cudaStream_t s, bool* handled) {
     *handled = false;
-    return TQ_OK;
+    if (q->d != tc::D || q->x_dtype != TQ_F16 || q->qjl_bits || q->y_out) return TQ_OK;
+    if (!aligned(q->x, 16) || q->x_row_stride % 8 || q->x_lane_stride % 8 || !aligned(q->rot, 16)) return TQ_OK;
+    static int disabled = -1;
+    if (disabled < 0) {
+        const char* e = getenv("TQ_DISABLE_TC");
+        disabled = (e && e[0] == '1') ? 1 : 0;
+    }
+    if (disabled) return TQ_OK;
+    const int64_t total = q->n_lanes * q->n_rows;
+    if (total < 4 * tc::TM) return TQ_OK;            // tiny inputs: not worth a persistent launch
+    static bool attr_set[16] = {false};
+    static int sms[16] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 16) return TQ_OK;
+    if (!attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(tc::quantize_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+        if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_quantize_pack: shared memory %d B: %s", tc::SMEM_BYTES, cudaGetErrorString(e));
+        if (cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms[dev] <= 0) sms[dev] = 148;
+        attr_set[dev] = true;
+    }
+    tc::Params p{};
+    p.x = static_cast<const __half*>(q->x);
+    p.n_lanes = q->n_lanes; p.n_rows = q->n_rows; p.x_lane_stride = q->x_lane_stride; p.x_row_stride = q->x_row_stride;
+    p.rot = q->rot; p.bnd_hi = q->bnd_hi; p.bnd_lo = q->bnd_lo; p.bits_hi = q->bits_hi; p.bits_lo = q->bits_lo;
+    p.p_hi = q->packed_hi; p.p_lo = q->packed_lo; p.norms = q->norms; p.out_lane_stride = q->out_lane_stride;
+    p.n_tiles = (total + tc::TM - 1) / tc::TM;
+    p.status = nullptr;
+    const unsigned grid = unsigned(std::min<int64_t>(p.n_tiles, sms[dev]));
+    tc::quantize_tc_kernel<<<grid, tc::NT, tc::SMEM_BYTES, s>>>(p);
+    *handled = true;
+    return check_launch("tq_quantize_pack (tensor core)");
+}
+
+// 0 if no tensor-core quantize launch on the current device has reported a timed-out wait, else its code.
+// Synchronises the device.
+extern "C" int tq_device_status(void) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, tc::g_status, sizeof(int)) != cudaSuccess) return -1;
+    return v;
 }

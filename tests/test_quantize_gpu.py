@@ -199,3 +199,50 @@ def test_fused_qk_scores_shapes(oracle, tables, tq, tkv, d, bits):
     fn = {2: kernels.fused_qk_scores_2bit, 3: kernels.fused_qk_scores_3bit, 4: kernels.fused_qk_scores_4bit}[bits]
     s = fn(cu(oracle.rotate_fwd(q, rot)), cu(packed), cu(norms), get_codebook(d, bits)[0], d)
     np.testing.assert_allclose(host(s), ref, atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("kb,lanes,rows", ((4, 8, 1000), (2, 8, 1024), (3, 3, 700), (3.5, 4, 1153), (2.5, 2, 4096), (4, 1, 513)))
+def test_tensor_core_quantize_path(oracle, tables, kb, lanes, rows):
+    """fp16, d = 128 rows go through the tcgen05 kernel (>= 512 rows): same parity bar as the general kernel,
+    ragged last tile, strided lanes (rows taken from a larger buffer), every packed width."""
+    from mlx_turboquant_b200 import _lib, kernels
+    from mlx_turboquant_b200.codebook import get_codebook
+    from mlx_turboquant_b200.rotation import get_rotation_matrix
+    d = 128
+    rs = np.random.RandomState(int(kb * 10) + rows)
+    hi, lo = kernels.split_bits(kb)
+    buf = cu(kv_like(rs, (1, lanes, rows + 40, d)))
+    x = buf[:, :, 16:16 + rows]                                   # lane stride != rows * d
+    x[0, 0, 5] = 0                                                # zero row
+    xh = host(x)
+    bh = get_codebook(d, hi)[1]
+    bl = get_codebook(d, lo)[1] if lo else None
+    ph, pl, norms = kernels.quantize_pack(x, get_rotation_matrix(d), bh, hi, bl, lo)
+    assert _lib.lib().tq_device_status() == 0
+    rot = oracle.rotation_matrix(d)
+    if lo:
+        rh, rl, rn, ry = oracle.split_quantize(xh, rot, tables[(d, hi)][1], hi, tables[(d, lo)][1], lo)
+        f2 = code_mismatch_report(host(pl), rl, lo, 64, ry[..., 64:], tables[(d, lo)][1])
+        assert tuple(pl.shape) == rl.shape and f2[0] < 1e-4 and f2[1] <= 1 and f2[2] < 1e-6, f2
+        f1 = code_mismatch_report(host(ph), rh, hi, 64, ry[..., :64], tables[(d, hi)][1])
+    else:
+        rh, rn, ry = oracle.mse_quantize(xh, rot, tables[(d, hi)][1], hi)
+        f1 = code_mismatch_report(host(ph), rh, hi, d, ry, tables[(d, hi)][1])
+    assert tuple(ph.shape) == rh.shape and f1[0] < 1e-4 and f1[1] <= 1 and f1[2] < 1e-6, f1
+    np.testing.assert_allclose(host(norms), rn, rtol=2e-6)
+    assert host(norms)[0, 0, 5] == 0
+
+
+def test_tensor_core_and_general_kernels_agree(tables):
+    """Same rows through both kernels (float32 copy forces the general one): codes differ only on boundaries."""
+    from mlx_turboquant_b200 import kernels
+    from mlx_turboquant_b200.codebook import get_codebook
+    from mlx_turboquant_b200.rotation import get_rotation_matrix
+    rs = np.random.RandomState(77)
+    x = cu(kv_like(rs, (1, 8, 4096, 128)))
+    b = get_codebook(128, 3)[1]
+    rot = get_rotation_matrix(128)
+    p1, _, n1 = kernels.quantize_pack(x, rot, b, 3)
+    p2, _, n2 = kernels.quantize_pack(x.float(), rot, b, 3)
+    np.testing.assert_allclose(host(n1), host(n2), rtol=2e-6)
+    assert (host(p1) != host(p2)).mean() < 1e-4
