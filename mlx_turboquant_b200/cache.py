@@ -300,9 +300,12 @@ class TurboQuantKVCache:
                 return
             self._drain_chunk(self._fp16_len - self.residual_window)
             return
+        # The reference drains one chunk per loop iteration while fp16_len >= residual_window + chunk_size; tokens
+        # are quantized independently, so all those chunks go to the GPU as one launch with the same result.
         threshold = self.residual_window + self.chunk_size
-        while self._fp16_len >= threshold:
-            self._drain_chunk(self.chunk_size)
+        if self._fp16_len >= threshold:
+            n_chunks = (self._fp16_len - self.residual_window) // self.chunk_size
+            self._drain_chunk(n_chunks * self.chunk_size)
 
     def _route_sink(self, keys, values):
         """Peel the tokens that belong to the permanent sink off the head of the batch (cache.py:577-618)."""

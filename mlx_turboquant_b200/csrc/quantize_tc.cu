@@ -7,12 +7,12 @@
 // row norm is applied afterwards.  Per tile: 2 x 8 tcgen05.mma (M = 128, N = 128, K = 16) into two TMEM
 // accumulators, double-buffered so that the epilogue of tile i overlaps the loads and MMAs of tile i+1.
 //
-// Warp roles in a persistent CTA (one per SM, 544 threads):
-//   warps 0-7   epilogue: thread <-> one row (TMEM lane) and one half of the coordinates; tcgen05.ld, boundary
+// Warp roles in a persistent CTA (one per SM, 800 threads):
+//   warps 0-15  epilogue: thread <-> one row (TMEM lane) and one quarter of the coordinates; tcgen05.ld, boundary
 //               search through a 513-bin lookup table (bin -> nearest boundary + count below it; exact, see
 //               build_bins), packing, 128-bit stores
-//   warp  8     allocates TMEM, issues the MMAs (one elected thread) and commits them to mbarriers
-//   warps 9-16  producers: 128-bit global loads of the rows, sum of squares for the norm, stores into the
+//   warp  16    allocates TMEM, issues the MMAs (one elected thread) and commits them to mbarriers
+//   warps 17-24 producers: 128-bit global loads of the rows, sum of squares for the norm, stores into the
 //               128-byte-swizzled K-major shared-memory layout the MMA descriptors expect
 // Every mbarrier wait is bounded: on a timeout the kernel raises a status word, drains and frees its TMEM.
 #include <algorithm>
@@ -26,8 +26,10 @@ namespace tc {
 
 constexpr int D = 128, TM = 128;                 // head_dim, rows per tile
 constexpr int A_STAGES = 3, ACC_STAGES = 2;
-constexpr int N_EPI = 256, N_PROD = 256;         // threads per role
-constexpr int NT = N_EPI + 32 + N_PROD;          // 544
+constexpr int N_EPI = 512, N_PROD = 256;         // threads per role
+constexpr int EPI_WARPS = N_EPI / 32;            // 16: TMEM lane quadrant = warp % 4, coordinate quarter = warp / 4
+constexpr int NT = N_EPI + 32 + N_PROD;          // 800
+constexpr int BIN_REP = 4;                       // copies of every lookup-table entry (lane & 3 picks one): fewer bank conflicts
 constexpr int KBLK_BYTES = TM * 128;             // one 64-column K-block of a 128-row operand: 16 KB
 constexpr int OPER_BYTES = 2 * KBLK_BYTES;       // 32 KB per operand tile
 constexpr int NBINS = 516;                       // 513 used + guard
@@ -37,8 +39,8 @@ constexpr uint32_t WAIT_LIMIT = 4u << 20;        // bounded spin: a few hundred 
 constexpr int OFF_A = 0;                                   // A_STAGES x 32 KB, 1024-byte aligned
 constexpr int OFF_RHI = OFF_A + A_STAGES * OPER_BYTES;     // 32 KB
 constexpr int OFF_RLO = OFF_RHI + OPER_BYTES;              // 32 KB
-constexpr int OFF_BINS = OFF_RLO + OPER_BYTES;             // 2 tables x NBINS x 8 B
-constexpr int OFF_BND = OFF_BINS + 2 * NBINS * 8;          // 2 x 16 floats: raw boundaries (slow path)
+constexpr int OFF_BINS = OFF_RLO + OPER_BYTES;             // 2 tables x NBINS x BIN_REP x 8 B
+constexpr int OFF_BND = OFF_BINS + 2 * NBINS * BIN_REP * 8; // 2 x 16 floats: raw boundaries (slow path)
 constexpr int OFF_NSQ = OFF_BND + 128;                     // A_STAGES x 2 x 128 floats: partial sums of squares
 constexpr int OFF_BAR = OFF_NSQ + A_STAGES * 2 * TM * 4;   // mbarriers
 constexpr int OFF_MISC = OFF_BAR + 16 * 8;                 // tmem base, abort flag
@@ -54,6 +56,21 @@ struct Params {
 };
 
 __device__ int g_status = 0;   // 0 ok, otherwise the code of the first wait that timed out
+
+#ifdef TQ_TIMING
+// Development builds only: globaltimer stamps of CTA 0, [role][iteration][slot].
+__device__ unsigned long long g_tc_timing[3 * 64 * 4 + 8];
+__device__ __forceinline__ void tstamp(int idx) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_tc_timing[idx] = t;
+}
+#define TC_STAMP(cond, role, it, slot) do { if ((cond) && blockIdx.x == 0 && (it) < 64) tstamp(((role) * 64 + (it)) * 4 + (slot)); } while (0)
+#define TC_STAMP0(cond, slot) do { if ((cond) && blockIdx.x == 0) tstamp(3 * 64 * 4 + (slot)); } while (0)
+#else
+#define TC_STAMP(cond, role, it, slot)
+#define TC_STAMP0(cond, slot)
+#endif
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -108,6 +125,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // K-major operand tile in shared memory, 128-byte swizzle: row r of K-block b at  b*16 KB + r*128 B, its 16-byte
@@ -139,21 +163,25 @@ __device__ void build_bins(float2* bins, const float* bnd, int n_bnd, int tid, i
             if (b < lo) ++below;
             else if (b <= hi) { ++inside; b_in = b; }
         }
-        bins[k] = make_float2(inside > 1 ? __int_as_float(0x7fc00000) : b_in, __int_as_float(below));
+        const float2 e = make_float2(inside > 1 ? __int_as_float(0x7fc00000) : b_in, __int_as_float(below));
+#pragma unroll
+        for (int r = 0; r < BIN_REP; ++r) bins[k * BIN_REP + r] = e;
     }
 }
 
-__device__ __forceinline__ uint32_t code_of(float yp, float rinv, float rbin, const float2* bins, const float* raw_bnd, int n_bnd) {
+// Fast path of the boundary search: one table lookup and one compare.  `slow` is raised when the bin is marked.
+__device__ __forceinline__ uint32_t code_of(float yp, float rinv, float rbin, const float2* bins, bool& slow) {
     // bin index from the mantissa of (y * 256 + 256 + 2^23): exact rounding to nearest, no convert instruction
     const float tt = fmaf(yp, rbin, 8388608.f + 256.f);
     const uint32_t k = min(__float_as_uint(tt) & 0x3FFu, uint32_t(NBINS - 1));
-    const float2 e = bins[k];
-    const float y = yp * rinv;
-    uint32_t c = __float_as_uint(e.y) + (y > e.x ? 1u : 0u);     // strict >, codebook.py:220-223
-    if (e.x != e.x) {                                            // rare: two boundaries close together
-        c = 0;
-        for (int i = 0; i < n_bnd; ++i) c += (y > raw_bnd[i]) ? 1u : 0u;
-    }
+    const float2 e = bins[k * BIN_REP];
+    slow |= (e.x != e.x);
+    return __float_as_uint(e.y) + ((yp * rinv) > e.x ? 1u : 0u);     // strict >, codebook.py:220-223
+}
+// Plain counting loop, kept out of line: only reached when two boundaries share a bin neighbourhood.
+__device__ __noinline__ uint32_t code_slow(float y, const float* raw_bnd, int n_bnd) {
+    uint32_t c = 0;
+    for (int i = 0; i < n_bnd; ++i) c += (y > raw_bnd[i]) ? 1u : 0u;
     return c;
 }
 
@@ -165,17 +193,19 @@ struct EpiCtx {
 template <int BITS>
 __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
     const Params& p = e.p;
-    const int quad = e.warp & 3, half = e.warp >> 2, row_in_tile = quad * 32 + e.lane;
-    const bool second = p.bits_lo && half;
-    const float2* bins = reinterpret_cast<const float2*>(e.smem + OFF_BINS) + (second ? NBINS : 0);
+    const int quad = e.warp & 3, quarter = e.warp >> 2, row_in_tile = quad * 32 + e.lane;
+    const bool second = p.bits_lo && quarter >= 2;              // fractional mode: coordinates [64, 128) use the low-bit codebook
+    const float2* bins = reinterpret_cast<const float2*>(e.smem + OFF_BINS) + (second ? NBINS * BIN_REP : 0) + (e.lane & (BIN_REP - 1));
     const float* raw_bnd = reinterpret_cast<const float*>(e.smem + OFF_BND) + (second ? 16 : 0);
     constexpr int n_bnd = (1 << BITS) - 1;
-    constexpr int WBYTES = 64 * BITS / 8;                       // bytes this thread produces per row
+    constexpr int WBYTES = 32 * BITS / 8;                       // bytes this thread produces per row (32 coordinates)
     int it = 0;
     for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
         const int a = it % ACC_STAGES, s = it % A_STAGES;
+        TC_STAMP(e.warp == 0 && e.lane == 0, 2, it, 0);
         if (!mbar_wait(e.bar_accfull + 8 * a, (it / ACC_STAGES) & 1, e.abort_flag, 3)) break;
         tc_fence_after();
+        TC_STAMP(e.warp == 0 && e.lane == 0, 2, it, 1);
         const float* nsq = reinterpret_cast<const float*>(e.smem + OFF_NSQ) + s * 2 * TM;
         const float nrm = sqrtf(nsq[row_in_tile] + nsq[TM + row_in_tile]);
         mbar_arrive(e.bar_afree + 8 * s);                       // norm slots of this stage are free again
@@ -187,23 +217,33 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
         if (live) {
             const int64_t o = row / p.n_rows, r = row - o * p.n_rows;
             orow = o * p.out_lane_stride + r;
-            if (half == 0) p.norms[orow] = nrm;
+            if (quarter == 0) p.norms[orow] = nrm;
         }
-        const uint32_t t_hi = e.tmem_base + (uint32_t(quad * 32) << 16) + a * 256 + half * 64;
-        uint32_t words[8];                                      // up to 64 codes x 4 bits
+        const uint32_t t_hi = e.tmem_base + (uint32_t(quad * 32) << 16) + a * 256 + quarter * 32;
+        uint32_t words[4];                                      // 32 codes x at most 4 bits
 #pragma unroll
-        for (int i = 0; i < 8; ++i) words[i] = 0;
+        for (int i = 0; i < 4; ++i) words[i] = 0;
 #pragma unroll
-        for (int cb = 0; cb < 2; ++cb) {                        // 32 coordinates at a time
-            uint32_t vh[32], vl[32];
-            tmem_ld32(t_hi + cb * 32, vh);
-            tmem_ld32(t_hi + 128 + cb * 32, vl);
+        for (int cb = 0; cb < 2; ++cb) {                        // 16 coordinates at a time
+            uint32_t vh[16], vl[16];
+            tmem_ld16(t_hi + cb * 16, vh);
+            tmem_ld16(t_hi + 128 + cb * 16, vl);
             tmem_ld_wait();
+            bool slow = false;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
+            for (int i = 0; i < 16; ++i) {
                 const float yp = fmaf(__uint_as_float(vl[i]), 1.f / 2048.f, __uint_as_float(vh[i]));
-                const uint32_t c = code_of(yp, rinv, rbin, bins, raw_bnd, n_bnd);
-                const int j = cb * 32 + i;                      // coordinate inside this half
+                vh[i] = __float_as_uint(yp);
+                vl[i] = code_of(yp, rinv, rbin, bins, slow);
+            }
+            if (__any_sync(0xffffffffu, slow)) {                // never taken with the shipped codebooks
+#pragma unroll
+                for (int i = 0; i < 16; ++i) vl[i] = code_slow(__uint_as_float(vh[i]) * rinv, raw_bnd, n_bnd);
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const uint32_t c = vl[i];
+                const int j = cb * 16 + i;                      // coordinate inside this quarter
                 if (BITS == 4) words[j >> 3] |= c << (4 * (j & 7));
                 else if (BITS == 2) words[j >> 4] |= c << (2 * (j & 15));
                 else if (BITS == 1) words[j >> 5] |= c << (j & 31);
@@ -216,9 +256,12 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
         }
         tc_fence_before();
         mbar_arrive(e.bar_accfree + 8 * a);                     // accumulators may be overwritten
+        TC_STAMP(e.warp == 0 && e.lane == 0, 2, it, 2);
         if (live) {
             const bool frac = p.bits_lo != 0;
-            uint8_t* dst = second ? p.p_lo + orow * WBYTES : p.p_hi + orow * (frac ? WBYTES : 2 * WBYTES) + (frac ? 0 : half * WBYTES);
+            // integer mode: the row holds 4 quarters; fractional mode: packed_hi and packed_lo hold 2 quarters each
+            uint8_t* dst = second ? p.p_lo + orow * (2 * WBYTES) + (quarter - 2) * WBYTES
+                                  : p.p_hi + orow * ((frac ? 2 : 4) * WBYTES) + quarter * WBYTES;
             if ((WBYTES & 15) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
                 for (int i = 0; i < WBYTES / 16; ++i)
@@ -226,6 +269,9 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
             } else if ((WBYTES & 7) == 0 && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
 #pragma unroll
                 for (int i = 0; i < WBYTES / 8; ++i) reinterpret_cast<uint2*>(dst)[i] = make_uint2(words[2 * i], words[2 * i + 1]);
+            } else if ((WBYTES & 3) == 0 && (reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
+#pragma unroll
+                for (int i = 0; i < WBYTES / 4; ++i) reinterpret_cast<uint32_t*>(dst)[i] = words[i];
             } else {
 #pragma unroll
                 for (int i = 0; i < WBYTES; ++i) dst[i] = uint8_t(words[i >> 2] >> (8 * (i & 3)));
@@ -245,6 +291,7 @@ __global__ void __launch_bounds__(NT, 1) quantize_tc_kernel(Params p) {
     const uint32_t bar_full = sbase + OFF_BAR, bar_afree = bar_full + 8 * A_STAGES;
     const uint32_t bar_accfull = bar_afree + 8 * A_STAGES, bar_accfree = bar_accfull + 8 * ACC_STAGES;
 
+    TC_STAMP0(tid == 0, 0);
     if (sbase & 1023u) {                  // the swizzled operand tiles need 1024-byte alignment (uniform across the CTA)
         if (tid == 0) atomicCAS(&g_status, 0, 9);
         return;
@@ -282,9 +329,9 @@ __global__ void __launch_bounds__(NT, 1) quantize_tc_kernel(Params p) {
         }
         __syncthreads();
         build_bins(reinterpret_cast<float2*>(smem + OFF_BINS), raw, (1 << p.bits_hi) - 1, tid, NT);
-        if (p.bits_lo) build_bins(reinterpret_cast<float2*>(smem + OFF_BINS) + NBINS, raw + 16, (1 << p.bits_lo) - 1, tid, NT);
+        if (p.bits_lo) build_bins(reinterpret_cast<float2*>(smem + OFF_BINS) + NBINS * BIN_REP, raw + 16, (1 << p.bits_lo) - 1, tid, NT);
     }
-    if (warp == 8) {                      // one warp owns the TMEM allocation: 2 stages x (hi + lo) x 128 columns
+    if (warp == EPI_WARPS) {              // one warp owns the TMEM allocation: 2 stages x (hi + lo) x 128 columns
         tmem_alloc(sbase + OFF_MISC, 512);
         tmem_relinquish();
     }
@@ -294,24 +341,27 @@ __global__ void __launch_bounds__(NT, 1) quantize_tc_kernel(Params p) {
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int64_t total_rows = p.n_lanes * p.n_rows;
+    TC_STAMP0(tid == 0, 1);
 
-    if (warp < 8) {
-        // ======================= epilogue: row = 32*(warp%4) + lane, coordinate half = warp/4 =======================
-        const int bits = (p.bits_lo && (warp >> 2)) ? p.bits_lo : p.bits_hi;
+    if (warp < EPI_WARPS) {
+        // ======================= epilogue: row = 32*(warp%4) + lane, coordinate quarter = warp/4 =======================
+        const int bits = (p.bits_lo && (warp >> 3)) ? p.bits_lo : p.bits_hi;
         EpiCtx e{p, smem, tmem_base, bar_accfull, bar_accfree, bar_afree, abort_flag, total_rows, warp, lane};
         if (bits == 4) epilogue_loop<4>(e);
         else if (bits == 3) epilogue_loop<3>(e);
         else if (bits == 2) epilogue_loop<2>(e);
         else epilogue_loop<1>(e);
-    } else if (warp == 8) {
+    } else if (warp == EPI_WARPS) {
         // ======================= MMA issue: one elected thread =======================
         if (lane == 0) {
             int it = 0;
             for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
                 const int a = it % ACC_STAGES, s = it % A_STAGES;
                 if (it >= ACC_STAGES && !mbar_wait(bar_accfree + 8 * a, ((it / ACC_STAGES) - 1) & 1, abort_flag, 2)) break;
+                TC_STAMP(true, 1, it, 0);
                 if (!mbar_wait(bar_full + 8 * s, (it / A_STAGES) & 1, abort_flag, 1)) break;
                 tc_fence_after();
+                TC_STAMP(true, 1, it, 1);
                 const uint32_t a_tile = sbase + OFF_A + s * OPER_BYTES;
                 const uint32_t d_hi = tmem_base + a * 256, d_lo = d_hi + 128;
 #pragma unroll
@@ -326,52 +376,67 @@ __global__ void __launch_bounds__(NT, 1) quantize_tc_kernel(Params p) {
                 }
                 umma_commit(bar_afree + 8 * s);      // rows of this stage consumed: producers may refill it
                 umma_commit(bar_accfull + 8 * a);    // both accumulators complete: epilogue may read them
+                TC_STAMP(true, 1, it, 2);
             }
         }
         __syncwarp();
     } else {
-        // ======================= producers: thread = (K-block, row) =======================
+        // ======================= producers =======================
+        // Warp pw owns rows [16*pw, 16*pw + 16) of the tile; one warp-wide 128-bit load covers two whole rows
+        // (lane = 16*(row & 1) + chunk), i.e. 512 contiguous bytes when rows are contiguous.
         const int pt = tid - (N_EPI + 32);
-        const int kblk = pt >> 7, r = pt & 127;
+        const int pw = pt >> 5, chunk = lane & 15, rsub = lane >> 4;
+        const int kblk = chunk >> 3, cc = chunk & 7;
         int it = 0;
         for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
             const int s = it % A_STAGES;
-            const int64_t row = tile * TM + r;
             uint4 v[8];
-            if (row < total_rows) {
-                const int64_t o = row / p.n_rows, rr = row - o * p.n_rows;
-                const uint4* src = reinterpret_cast<const uint4*>(p.x + o * p.x_lane_stride + rr * p.x_row_stride + kblk * 64);
 #pragma unroll
-                for (int c = 0; c < 8; ++c) v[c] = __ldg(src + c);
-            } else {
-#pragma unroll
-                for (int c = 0; c < 8; ++c) v[c] = make_uint4(0, 0, 0, 0);
-            }
-            float ss = 0.f;
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const __half2* h = reinterpret_cast<const __half2*>(&v[c]);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 f = __half22float2(h[i]);
-                    ss = fmaf(f.x, f.x, ss);
-                    ss = fmaf(f.y, f.y, ss);
+            for (int i = 0; i < 8; ++i) {
+                const int64_t row = tile * TM + pw * 16 + i * 2 + rsub;
+                v[i] = make_uint4(0, 0, 0, 0);
+                if (row < total_rows) {
+                    const int64_t o = row / p.n_rows, rr = row - o * p.n_rows;
+                    v[i] = __ldg(reinterpret_cast<const uint4*>(p.x + o * p.x_lane_stride + rr * p.x_row_stride) + chunk);
                 }
             }
+            TC_STAMP(pt == 0, 0, it, 0);
+            float ss[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const __half2* h = reinterpret_cast<const __half2*>(&v[i]);
+                float a = 0.f;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float2 f = __half22float2(h[u]);
+                    a = fmaf(f.x, f.x, a);
+                    a = fmaf(f.y, f.y, a);
+                }
+#pragma unroll
+                for (int off = 8; off; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+                ss[i] = a;
+            }
+            TC_STAMP(pt == 0, 0, it, 1);
             // the stage and its norm slots must be free: MMAs of tile it - A_STAGES done, its epilogue has read the norms
             if (it >= A_STAGES && !mbar_wait(bar_afree + 8 * s, ((it / A_STAGES) - 1) & 1, abort_flag, 4)) break;
-            unsigned char* dst = smem + OFF_A + s * OPER_BYTES + kblk * KBLK_BYTES + r * 128;
+            TC_STAMP(pt == 0, 0, it, 2);
+            unsigned char* stage = smem + OFF_A + s * OPER_BYTES + kblk * KBLK_BYTES;
+            float* nsq = reinterpret_cast<float*>(smem + OFF_NSQ) + s * 2 * TM;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = v[c];
-            reinterpret_cast<float*>(smem + OFF_NSQ)[(s * 2 + kblk) * TM + r] = ss;
+            for (int i = 0; i < 8; ++i) {
+                const int r = pw * 16 + i * 2 + rsub;
+                *reinterpret_cast<uint4*>(stage + r * 128 + ((cc ^ (r & 7)) << 4)) = v[i];
+                if (chunk == 0) { nsq[r] = ss[i]; nsq[TM + r] = 0.f; }
+            }
             fence_proxy_async();                     // generic-proxy stores -> visible to the tensor core
             mbar_arrive(bar_full + 8 * s);
+            TC_STAMP(pt == 0, 0, it, 3);
         }
     }
     // ---- teardown: every loop above is bounded, so every thread gets here ----
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) {
+    if (warp == EPI_WARPS) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
@@ -424,6 +489,12 @@ int tq_quantize_pack_tc(const tq_quantize_args* q, cudaStream_t s, bool* handled
 
 // 0 if no tensor-core quantize launch on the current device has reported a timed-out wait, else its code.
 // Synchronises the device.
+#ifdef TQ_TIMING
+extern "C" int tq_debug_tc_timing(unsigned long long* host_out, int n) {
+    return int(cudaMemcpyFromSymbol(host_out, tc::g_tc_timing, sizeof(unsigned long long) * n));
+}
+#endif
+
 extern "C" int tq_device_status(void) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, tc::g_status, sizeof(int)) != cudaSuccess) return -1;
