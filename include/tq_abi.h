@@ -160,6 +160,16 @@ size_t tq_decode_workspace_bytes(int batch, int n_q_heads, int n_kv_heads, int d
  * (pre-rotated query, rotation.py:81-110) extended with softmax and values. */
 int tq_decode_attn(const tq_decode_args* a, void* stream);
 
+/* Same computation as tq_decode_attn for callers that can neither lend a workspace nor allocate one at call
+ * time (a process that gave the whole device to its own memory pool at start-up; a step loop that cannot afford
+ * a driver allocation).  It has no counterpart in the reference.  `workspace` / `workspace_bytes` in the
+ * arguments are ignored: scratch comes from a TQ_DECODE_STATIC_SCRATCH_BYTES array inside the library, present
+ * on every GPU that loads it.  Sizes that need more are refused with TQ_ERR_UNSUPPORTED.  The first call on a
+ * device looks the array's address up (do it outside stream capture).  All calls on a device share the array:
+ * order them on one stream, calls that overlap on the GPU race.  Allocates nothing. */
+#define TQ_DECODE_STATIC_SCRATCH_BYTES (8u << 20)
+int tq_decode_attn_static(const tq_decode_args* a, void* stream);
+
 /* Scale s in [1, 2) minimising max_i |fp16(s*c_i) - s*c_i| / |s*c_i| for a HOST array of n centroids
  * (no reference counterpart; pure host arithmetic). */
 float tq_fp16_table_scale(const float* centroids_host, int n);

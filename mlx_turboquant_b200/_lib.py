@@ -77,6 +77,7 @@ PROTOTYPES = {
     "tq_qk_scores": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _vp, _vp]),
     "tq_decode_workspace_bytes": (_sz, [_i, _i, _i, _i, _i64, _i64]),
     "tq_decode_attn": (_i, [C.POINTER(DecodeArgs), _vp]),
+    "tq_decode_attn_static": (_i, [C.POINTER(DecodeArgs), _vp]),
     "tq_set_tuning": (_i, [C.c_char_p, _i]),
     "tq_fp16_table_scale": (_f, [_vp, _i]),
     "tq_device_status": (_i, []),
