@@ -43,6 +43,9 @@ LAYERS, HQ, HKV, D, CTX, SINK, RW = 32, 32, 8, 128, 32768, 128, 128
 T_C = CTX - SINK - RW
 # algorithmic bytes of one layer-step: packed codes + norms, fp16 sink/recent tokens, query in, result out
 BYTES_PER_LAYER_STEP = HKV * T_C * (D * 4 // 8 + 4 + D * 2 // 8 + 4) + HKV * (SINK + RW) * 2 * D * 2 + HQ * D * 4
+# DRAM bytes (read + write) of one decode launch on this workload, from the ncu capture summarised in
+# profiles/decode_attn_kernel_c1_k4v2_ctx32768.md (it equals the algorithmic bytes within 1.5 %: nothing is re-read)
+NCU_DRAM_BYTES_PER_LAUNCH = 28545152
 WORKLOAD = "llama31_8b_layer_decode_attn_ctx32768_k4v2_sink128_rw128"
 # quantize+pack: 4096-token chunks x 8 KV heads, K and V, fp16 in; bytes per (token, head): read 2*D*2, write codes + norms
 QCHUNK = 4096
@@ -193,7 +196,7 @@ def build_caches(torch, dev, rank):
     return caches, qs
 
 
-def bench_quantize(torch, dev, steps, warmup, peak):
+def bench_quantize(torch, dev, steps, warmup, peak, pool_size=8):
     """Prefill compression throughput: 131072 new tokens x 8 KV heads per layer, chunk_size 4096, residual window
     128 -> the cache drains 31 chunks (126976 tokens) per layer and side, issued as one fused launch each.
     One step = 32 layers (8 distinct fp16 K/V input sets of 0.5 GB each, cycled: every launch reads far more
@@ -205,7 +208,7 @@ def bench_quantize(torch, dev, steps, warmup, peak):
     n_tok = (131072 - RW) // QCHUNK * QCHUNK          # tokens that leave the fp16 buffer: 126976
     g = torch.Generator(device=dev).manual_seed(2000)
     pool = []
-    for _ in range(8):
+    for _ in range(pool_size):
         x = torch.randn(2, 1, HKV, n_tok, D, device=dev, generator=g, dtype=torch.float16)
         x[..., [3, 40, 77, 101]] *= 20.0              # four fixed outlier channels per head
         pool.append(x)
@@ -258,7 +261,7 @@ def run_b200(args):
         dist.init_process_group("nccl", device_id=dev)
 
     import __graft_entry__ as ge
-    from mlx_turboquant_b200 import _lib
+    from mlx_turboquant_b200 import _lib, sharding
     if not _lib.LIB_PATH.exists() and rank == 0:
         ge.build()
     if world > 1:
@@ -268,7 +271,10 @@ def run_b200(args):
 
     global LAYERS
     LAYERS = args.layers
-    caches, qs = build_caches(torch, dev, rank)
+    # weak scaling: `world` independent sequences, dealt one per rank; no rank reads another rank's lanes
+    plan = sharding.plan_lanes(world, HKV, world, rank, split_heads=False)
+    assert (plan.seq_end - plan.seq_begin, plan.head_end - plan.head_begin) == (1, HKV)
+    caches, qs = build_caches(torch, dev, plan.seq_begin)
     torch.cuda.synchronize(dev)
 
     def barrier():
@@ -310,10 +316,7 @@ def run_b200(args):
         while time.time() < t_end:     # a few more replays so the sampler sees the loaded clock
             graph.replay()
         torch.cuda.synchronize(dev)
-    t = torch.tensor([ms_step], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item())
+    ms_step = sharding.job_time_ms(ms_step, dev)
     value = world * LAYERS * BYTES_PER_LAYER_STEP / (ms_step * 1e-3) / 1e9
 
     # ---- end to end through the public API with host buffers -----------------------------------------------
@@ -341,11 +344,8 @@ def run_b200(args):
         e2e_step()
     e1.record()
     barrier()
-    t = torch.tensor([e0.elapsed_time(e1) / e2e_steps], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item())
-    e2e_gbs = world * LAYERS * BYTES_PER_LAYER_STEP / (e2e_ms * 1e-3) / 1e9
+    e2e_ms = sharding.job_time_ms(e0.elapsed_time(e1) / e2e_steps, dev)
+    e2e_gbs = None if args.no_e2e else world * LAYERS * BYTES_PER_LAYER_STEP / (e2e_ms * 1e-3) / 1e9
 
     line = {
         "metric": "decode_attn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
@@ -361,13 +361,14 @@ def run_b200(args):
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clk.summary(),
         "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
-                     "peak_source": peak_src, "frac_of_nominal_8tbs": value / world / 8000.0, "traffic": None,
+                     "peak_source": peak_src, "frac_of_nominal_8tbs": value / world / 8000.0,
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH if LAYERS == 32 else None, "traffic_unit": "bytes per launch (ncu, one capture)",
                      "kernel": "decode_attn_kernel<128, direct> (one launch per layer: query rotation, packed attention, merge)",
                      "algorithmic_bytes_per_launch": BYTES_PER_LAYER_STEP},
     }
     if rank == 0 and world == 1 and not args.no_secondary:
         line["secondary"] = {"metric": "quantize_pack_mtokens_per_s", "unit": "Mtokens/s (token = position x 8 KV heads x 32 layers)",
-                             "chunk_tokens": QCHUNK, **bench_quantize(torch, dev, 3, 3, peak)}
+                             "chunk_tokens": QCHUNK, **bench_quantize(torch, dev, 3, 3, peak, args.quantize_pool)}
     if rank == 0 and world == 1 and not args.no_cpu:
         step, info = cpu_reference_step_factory(1)
         step()
@@ -393,6 +394,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph (for profilers)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--quantize-pool", type=int, default=8, help="distinct 0.5 GB fp16 K/V input sets the quantize leg cycles through")
     ap.add_argument("--no-secondary", action="store_true", help="skip the quantize+pack leg")
     args = ap.parse_args()
     if args.impl == "reference":
