@@ -148,6 +148,11 @@ typedef struct {
     /* >= tq_decode_workspace_bytes(...), 256-byte aligned, ZERO-FILLED before its first use (it holds
      * arrival counters that every launch leaves at zero again); one buffer per stream in flight. */
     void* workspace; size_t workspace_bytes;
+    /* Optional HOST copies of k_cent_hi (2^k_bits_hi floats) and v_cent_hi (2^v_bits_hi floats), or NULL.  With
+     * them the 4-bit-key / 2-bit-value kernel receives the centroids inside its launch parameters and starts
+     * building its tables without a round trip to device memory first.  Must hold the same values as the
+     * device arrays; read during the call only. */
+    const float *k_cent_hi_host, *v_cent_hi_host;
 } tq_decode_args;
 
 /* Scratch bytes tq_decode_attn needs for these sizes (host-side arithmetic only). */

@@ -59,6 +59,7 @@ class DecodeArgs(C.Structure):
         ("res_k", _vp), ("res_v", _vp), ("res_len", _i64), ("res_lane_stride", _i64),
         ("out", _vp), ("out_dtype", _i),
         ("workspace", _vp), ("workspace_bytes", _sz),
+        ("k_cent_hi_host", _vp), ("v_cent_hi_host", _vp),
     ]
 
 

@@ -19,6 +19,8 @@ written against the reference keeps working.  What differs is where the work hap
 from __future__ import annotations
 
 import ctypes as C
+
+import numpy as np
 from typing import Any
 
 import torch
@@ -56,10 +58,12 @@ class _Side:
         self.fractional = self.bits_lo != 0
         self.hi = self.lo = self.norms = self.qbits = self.qgamma = None
         self.cent_hi = self.cent_lo = self.bnd_hi = self.bnd_lo = None
+        self.cent_hi_host = None                 # float32 host copy of cent_hi (kept alive: its address is handed to the library)
         self.fp16_scale_hi = self.fp16_scale_lo = 0.0
 
     def load_tables(self, d: int, device) -> None:
         self.cent_hi, self.bnd_hi = get_codebook(d, self.bits_hi, device)
+        self.cent_hi_host = np.ascontiguousarray(get_codebook_host(d, self.bits_hi)[0], dtype=np.float32)
         self.fp16_scale_hi = _fp16_scale(d, self.bits_hi)
         if self.fractional:
             self.cent_lo, self.bnd_lo = get_codebook(d, self.bits_lo, device)
@@ -454,6 +458,8 @@ class TurboQuantKVCache:
             a.k_cent_hi, a.k_cent_lo = _lib.ptr(k.cent_hi), _lib.ptr(k.cent_lo)
             a.v_cent_hi, a.v_cent_lo = _lib.ptr(v.cent_hi), _lib.ptr(v.cent_lo)
             a.v_cent_scale_hi, a.v_cent_scale_lo = v.fp16_scale_hi, v.fp16_scale_lo
+            if k.cent_hi_host is not None and v.cent_hi_host is not None:
+                a.k_cent_hi_host, a.v_cent_hi_host = k.cent_hi_host.ctypes.data, v.cent_hi_host.ctypes.data
             if self.qjl_correction and k.qbits is not None:
                 a.qjl_proj = _lib.ptr(self._qjl_proj)
                 a.k_qjl_bits, a.v_qjl_bits = _lib.ptr(k.qbits), _lib.ptr(v.qbits)

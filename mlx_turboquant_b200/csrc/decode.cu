@@ -1,275 +1,70 @@
 // One decode step of attention computed directly on the compressed KV cache
 // [fp16 sink | packed middle | fp16 residual window], split over the sequence (flash-decode), in ONE launch.
 //
+// This file: the host side (argument checks, split plan, workspace layout, launch) and the GENERAL kernel, which
+// handles every bit width (1-4, fractional splits) and d in {64, 96, 128, 256}.  4-bit keys with 2-bit values at
+// d = 128 take the specialised kernel of decode_direct.cu instead.
+//
 // decode_attn_kernel, grid (splits, kv_heads * head_groups, batch).  Every CTA
 //   1. rotates the query heads of its GQA group once (q @ R^T, float32), folds scale*log2(e) in and keeps
 //      fp16 copies in shared memory (CTAs that own uncompressed tokens keep the unrotated query instead);
 //   2. runs the online-softmax attention over its token range of either the packed middle or the
 //      uncompressed regions; values of the packed middle are accumulated in ROTATED space;
-//   3. reduces its warps and writes one (max, sum, weighted-V) partial per query head to the workspace;
+//   3. reduces its warps, undoes the rotation of its partial (@ R) and writes one (max, sum, weighted-V)
+//      partial per query head to the workspace;
 //   4. bumps a counter; the CTA that arrives last for a (sequence, KV head, head group) merges all partials
-//      (log-sum-exp), undoes the rotation once (@ R), adds the unrotated part, normalises and writes the
-//      output.  No CTA ever waits for another one: the last arrival is detected with one atomic add.
+//      (log-sum-exp), normalises and writes the output.  No CTA ever waits for another one: the last arrival
+//      is detected with one atomic add.
 //
 // Arithmetic: warps work on tiles of 16 tokens with mma.sync.m16n8k16 (fp16 operands, fp32 accumulation):
 // S[16 tokens x 8 heads] = K_tile . Q^T, online softmax in registers, P transposed with movmatrix,
 // O^T[d x 8 heads] += V_tile^T . P^T.  Tokens are the M dimension so a GQA group of up to 8 query heads
-// shares every unpacked key/value.  The kernel is bound by HBM bytes (packed codes + norms), not by the
-// tensor pipe; the contraction shape is tiny (N = 8), which is why the warp-level MMA is used here.
-//
-// Two ways to build the K / V^T operand fragments:
-//   * general: a warp unpacks (or, for the fp16 regions, copies) its tile into shared memory as fp16 and reads
-//     fragments back with ldmatrix - any bit width, fractional splits, d in {64, 96, 128, 256};
-//   * direct (4-bit keys, 2-bit values, d = 128): raw packed tiles stream through a per-warp cp.async ring and
-//     are turned into fragments through bank-conflict-free lookup tables in shared memory (byte -> half2),
-//     never touching shared memory with unpacked data.  The coordinate order inside a fragment is permuted to
-//     match the byte layout; the query fragments and the output mapping use the same permutation.
+// shares every unpacked key/value.  A warp unpacks (or, for the fp16 regions, copies) its tile into shared
+// memory as fp16 and reads the operand fragments back with ldmatrix.
 #include <algorithm>
 #include <string_view>
 
-#include "decode.cuh"
+#include "decode_dev.cuh"
 
 namespace tq {
 
-// ---- small PTX wrappers --------------------------------------------------------------------------
-__device__ __forceinline__ float ex2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* smem_ptr) {
-    uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem_ptr));
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* smem_ptr) {
-    uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem_ptr));
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ uint32_t movm_t(uint32_t a) {
-    uint32_t d;
-    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
-    return d;
-}
-// Lookups in tables that are constant for the lifetime of the CTA: plain (non-volatile) asm so the compiler
-// may hoist and batch them ahead of the MMAs that consume them.
-__device__ __forceinline__ uint32_t lut32(uint32_t addr) {
-    uint32_t v;
-    asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint2 lut64(uint32_t addr) {
-    uint2 v;
-    asm("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-    return v;
-}
-// Reads of the cp.async ring: ordered after the wait / warp barrier that makes the data visible.
-__device__ __forceinline__ uint32_t ring32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
-    return v;
-}
-__device__ __forceinline__ uint4 ring128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
-    return v;
-}
-// 16-byte asynchronous global -> shared copy; bytes past src_bytes are zero-filled (0 = read nothing).
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-// Programmatic dependent launch: wait for the previous grid on the stream / let the next grid start its prologue.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
-    __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
-
-#ifdef TQ_TIMING
-// Phase timestamps (development builds only): [cta][8] globaltimer values.
-__device__ unsigned long long g_tq_timing[4096 * 16];
-__device__ __forceinline__ void stamp(int cta, int slot) {
-    if (threadIdx.x == 0 && cta < 4096) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        g_tq_timing[cta * 16 + slot] = t;
-    }
-}
-#define TQ_STAMP(slot) stamp(int(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)), slot)
-#else
-#define TQ_STAMP(slot)
-#endif
-
-// ---- per-warp running softmax state ------------------------------------------------------------------
-constexpr float MAX_SLACK = 6.f;   // scores may exceed the running reference by 2^6 before it is refreshed
-template <int D> struct WarpAcc {
-    float m[2], mt[2], l[2];   // heads 2t, 2t+1: reference max, refresh threshold, this lane's share of the sum
-    float o[D / 16][4];        // O^T fragments: rows = coordinate slots, cols = heads
-};
-
-// s[0..1]: token g, heads 2t,2t+1;  s[2..3]: token g+8.  Returns the P^T operand for the PV mma.
-// The softmax reference m is refreshed (with a cross-lane max and a rescale of the accumulators) only
-// when some score exceeds it by more than MAX_SLACK; softmax is shift-invariant, so any reference that
-// keeps exp2(s - m) inside the fp16 range is exact.
-template <int D>
-__device__ __forceinline__ void softmax_step(float (&s)[4], float kn0, float kn1, float vn0, float vn1, bool ok0,
-                                             bool ok1, WarpAcc<D>& st, uint32_t (&bp)[2]) {
-    s[0] = ok0 ? s[0] * kn0 : -INFINITY;
-    s[1] = ok0 ? s[1] * kn0 : -INFINITY;
-    s[2] = ok1 ? s[2] * kn1 : -INFINITY;
-    s[3] = ok1 ? s[3] * kn1 : -INFINITY;
-    float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
-    if (__any_sync(0xffffffffu, mx0 > st.mt[0] || mx1 > st.mt[1])) {
-#pragma unroll
-        for (int off = 4; off < 32; off <<= 1) {
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
-        }
-        const float mn0 = fmaxf(fmaxf(st.m[0], mx0), -1e30f), mn1 = fmaxf(fmaxf(st.m[1], mx1), -1e30f);
-        const float a0 = ex2(st.m[0] - mn0), a1 = ex2(st.m[1] - mn1);
-        st.m[0] = mn0; st.m[1] = mn1;
-        st.mt[0] = mn0 + MAX_SLACK; st.mt[1] = mn1 + MAX_SLACK;
-        st.l[0] *= a0; st.l[1] *= a1;
-#pragma unroll
-        for (int mt = 0; mt < D / 16; ++mt) {
-            st.o[mt][0] *= a0; st.o[mt][1] *= a1; st.o[mt][2] *= a0; st.o[mt][3] *= a1;
-        }
-    }
-    const float p0 = ex2(s[0] - st.m[0]), p1 = ex2(s[1] - st.m[1]), p2 = ex2(s[2] - st.m[0]), p3 = ex2(s[3] - st.m[1]);
-    st.l[0] += p0 + p2;
-    st.l[1] += p1 + p3;
-    // value norms ride on P (fp16, clamped below the fp16 maximum)
-    const uint32_t h0 = pack_h2(fminf(p0 * vn0, 65504.f), fminf(p1 * vn0, 65504.f));
-    const uint32_t h1 = pack_h2(fminf(p2 * vn1, 65504.f), fminf(p3 * vn1, 65504.f));
-    bp[0] = movm_t(h0);   // tokens 2t,2t+1   x head g
-    bp[1] = movm_t(h1);   // tokens 2t+8,2t+9 x head g
-}
+constexpr int GNW = 8;                 // warps per CTA of the general kernel
 
 // ---- shared memory plan ----------------------------------------------------------------------------------
 // BODY is reused by phases that never overlap in time:
-//   general staging: per warp  Ks[16][D+8] + Vs[16][D+8] halves
-//   direct:          T4 [256][32] u32 (32 KB) + T2 [256][16] uint2 (32 KB) + per-warp cp.async ring + R (64 KB)
+//   staging:         per warp  Ks[16][D+8] + Vs[16][D+8] halves
 //   CTA reduction:   per warp  o[D][8] floats + m[8] + l[8], then weights [NW][8]
-//   merge (last CTA): split weights [8][MAX_SPLITS], rotated / raw sums [8][D] each, partial products
+//   merge (last CTA): split weights [8][MAX_SPLITS]
 // After BODY: float query [8][D], fp16 query [8][D], four 16-entry fp16 centroid tables, a few scalars.
 constexpr int MERGE_CPARTS = 4;       // thread slabs of the d x d product with R in the epilogue
-template <int D> __host__ __device__ constexpr int stage_ld() { return D + 8; }
 template <int D, int NW> __host__ __device__ constexpr size_t stage_bytes() { return size_t(NW) * 2 * TILE * stage_ld<D>() * sizeof(__half); }
 template <int D, int NW> __host__ __device__ constexpr size_t reduce_bytes() {
     return size_t(NW) * (HPG * (D + 2) + 2 * HPG) * sizeof(float) + size_t(NW) * HPG * sizeof(float) + size_t(HPG) * D * sizeof(float) +
            size_t(MERGE_CPARTS) * HPG * D * sizeof(float);
 }
-constexpr size_t TABLE_BYTES = 65536;
-constexpr int RING_STAGES = 3;
-template <int D> __host__ __device__ constexpr int ring_stage_bytes() { return TILE * (D / 2 + D / 4 + 8); }
-// direct path: the rotation matrix stays resident in shared memory behind the tables and the ring
-template <int D, int NW> __host__ __device__ constexpr size_t rot_offset() { return TABLE_BYTES + size_t(NW) * RING_STAGES * ring_stage_bytes<D>(); }
-// chunk (16 bytes) kc of row j of the resident matrix sits at chunk position rot_pos(j, kc) of that row: both a
-// thread quartet reading along a row and a warp reading down a column hit distinct bank groups
-__host__ __device__ constexpr int rot_pos(int j, int kc) { return (kc & ~7) | ((kc ^ j ^ ((kc >> 3) << 1)) & 7); }
 template <int D> __host__ __device__ constexpr size_t merge_bytes() { return size_t(HPG) * MAX_SPLITS * sizeof(float2); }
-template <int D, bool DIRECT> __host__ __device__ constexpr size_t body_bytes() {
-    constexpr int NW = warps_per_cta(DIRECT);
-    size_t s = stage_bytes<D, NW>();
-    if (reduce_bytes<D, NW>() > s) s = reduce_bytes<D, NW>();
+template <int D> __host__ __device__ constexpr size_t body_bytes() {
+    size_t s = stage_bytes<D, GNW>();
+    if (reduce_bytes<D, GNW>() > s) s = reduce_bytes<D, GNW>();
     if (merge_bytes<D>() > s) s = merge_bytes<D>();
-    if (DIRECT && rot_offset<D, NW>() + size_t(D) * D * sizeof(float) > s) s = rot_offset<D, NW>() + size_t(D) * D * sizeof(float);
     return (s + 15) / 16 * 16;
 }
 template <int D> __host__ __device__ constexpr size_t tail_bytes() {
     return size_t(HPG) * D * sizeof(float) + size_t(HPG) * D * sizeof(__half) + 64 * sizeof(__half) + 16 * sizeof(float);
 }
-template <int D, bool DIRECT> __host__ __device__ constexpr size_t kernel_smem() { return body_bytes<D, DIRECT>() + tail_bytes<D>(); }
+template <int D> __host__ __device__ constexpr size_t kernel_smem() { return body_bytes<D>() + tail_bytes<D>(); }
 
-// One 16-token tile whose K and V sit in shared memory as fp16 [token][coordinate].
 template <int D>
-__device__ __forceinline__ void tile_from_smem(const __half* Ks, const __half* Vs, const uint32_t (&bq)[D / 16][2],
-                                               float kn0, float kn1, float vn0, float vn1, bool ok0, bool ok1,
-                                               WarpAcc<D>& st, int lane) {
-    constexpr int LD = stage_ld<D>();
-    float s[4] = {0.f, 0.f, 0.f, 0.f};
-    {
-        const __half* base = Ks + (lane & 15) * LD + (lane >> 4) * 8;
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-            uint32_t a[4];
-            ldsm_x4(a, base + ks * 16);
-            mma16816(s, a[0], a[1], a[2], a[3], bq[ks][0], bq[ks][1]);
-        }
-    }
-    uint32_t bp[2];
-    softmax_step<D>(s, kn0, kn1, vn0, vn1, ok0, ok1, st, bp);
-    {
-        const __half* base = Vs + ((lane & 7) + ((lane >> 4) & 1) * 8) * LD + ((lane >> 3) & 1) * 8;
-#pragma unroll
-        for (int mt = 0; mt < D / 16; ++mt) {
-            uint32_t a[4];
-            ldsm_x4_t(a, base + mt * 16);
-            mma16816(st.o[mt], a[0], a[1], a[2], a[3], bp[0], bp[1]);
-        }
-    }
-}
-
-// Per-warp cp.async ring of raw packed tiles (direct path, d = 128): one tile = 1024 B of 4-bit keys, 512 B of
-// 2-bit values, 2 x 64 B of norms.  Tokens past c_len are zero-filled without touching memory.
-template <int D, int NW> struct RingCtx {
-    static constexpr int KW = D / 2, VW = D / 4, KT = TILE * KW, VT = TILE * VW, STG = ring_stage_bytes<D>();
-    uint32_t ring, v_dst;
-    int tile_hi, first, c_len;
-    const uint8_t *kbase, *vbase;
-    const float* nbase;
-    // Value rows are stored permuted inside each group of four (row r -> slot (r + r/4) mod 4) so that the four
-    // rows {2t+c} a warp reads together fall into distinct banks.
-    __device__ __forceinline__ static int vslot(int r) { return (r & ~3) | ((r + (r >> 2)) & 3); }
-    __device__ __forceinline__ void init(const DecodeParams& p, unsigned char* smem, int64_t kvl, int split, int warp, int lane) {
-        ring = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + uint32_t(TABLE_BYTES) + warp * (RING_STAGES * STG);
-        v_dst = KT + vslot(lane >> 1) * VW + (lane & 1) * 16;
-        const int n_tiles = int((p.c_len + TILE - 1) / TILE);
-        const int tile_lo = int(split * p.p_tps);
-        tile_hi = min(tile_lo + int(p.p_tps), n_tiles);
-        first = tile_lo + warp;
-        c_len = int(p.c_len);
-        kbase = p.k_hi + kvl * p.c_ls * KW + lane * 16;
-        vbase = p.v_hi + kvl * p.c_ls * VW + lane * 16;
-        nbase = (lane < 4 ? p.k_norms : p.v_norms) + kvl * p.c_ls + (lane & 3) * 4;
-    }
-    __device__ __forceinline__ void issue(int stage, int tile, int lane) const {
-        const uint32_t sb = ring + stage * STG;
-        const int tok0 = tile * TILE;
-        const int left = c_len - tok0;            // valid tokens from here on (>= 16 for all but the last tile)
-        const uint8_t* ks = kbase + int64_t(tok0) * KW;
-        cp_async16(sb + lane * 16, ks, (lane >> 2) < left ? 16 : 0);
-        cp_async16(sb + 512 + lane * 16, ks + 512, (lane >> 2) + 8 < left ? 16 : 0);
-        cp_async16(sb + v_dst, vbase + int64_t(tok0) * VW, (lane >> 1) < left ? 16 : 0);
-        if (lane < 8) {
-            const int ok = left - (lane & 3) * 4;
-            cp_async16(sb + KT + VT + lane * 16, nbase + tok0, ok >= 4 ? 16 : ok > 0 ? ok * 4 : 0);
-        }
-    }
-};
-
-template <int D, bool DIRECT>
-__global__ void __launch_bounds__(warps_per_cta(DIRECT) * 32, 1) decode_attn_kernel(DecodeParams p) {
+__global__ void __launch_bounds__(GNW * 32, 1) decode_attn_kernel(DecodeParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
-    constexpr int NW = warps_per_cta(DIRECT), NT = NW * 32;
+    constexpr int NW = GNW, NT = NW * 32;
     constexpr int LD = stage_ld<D>();
-    constexpr size_t BODY = body_bytes<D, DIRECT>();
+    constexpr size_t BODY = body_bytes<D>();
     float* qf = reinterpret_cast<float*>(smem + BODY);                       // [8][D] query, float32
     __half* qs = reinterpret_cast<__half*>(qf + HPG * D);                    // [8][D] scaled fp16 query (rotated or raw)
     __half* ctab = qs + HPG * D;                                             // kc_hi, kc_lo, vc_hi, vc_lo (16 each)
     float* s_misc = reinterpret_cast<float*>(ctab + 64);                     // [0..7] 1/L per head, [8] last-CTA flag
 
-    TQ_STAMP(0);
     pdl_trigger();     // the next launch on the stream may become resident and run its own prologue
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, hkv = blockIdx.y / p.HG, hg = blockIdx.y % p.HG, b = blockIdx.z;
@@ -280,112 +75,20 @@ __global__ void __launch_bounds__(warps_per_cta(DIRECT) * 32, 1) decode_attn_ker
     const int S = p.n_ps + p.n_ds;
 
     // ---------------- prologue on constants only (runs before the previous launch has finished) -----------
-    if constexpr (DIRECT) {
-        if (!dense) {
-            uint32_t* T4 = reinterpret_cast<uint32_t*>(smem);               // [256][32]: byte -> half2(c[lo], c[hi])
-            uint2* T2 = reinterpret_cast<uint2*>(smem + 32768);             // [256][16]: byte -> 2 x half2 (token pair)
-            if (tid < 32) {
-                const int which = tid >> 4, k = tid & 15;
-                const float* src = which ? p.vc_hi : p.kc_hi;
-                ctab[which * 32 + k] = __float2half_rn(k < (which ? 4 : 16) ? src[k] * (which ? p.v_scale_hi : 1.f) : 0.f);
-            }
-            __syncthreads();
-            for (int e = tid; e < 256 * 8; e += NT) {     // 4 replicas per 128-bit store
-                const int entry = e >> 3, q4 = e & 7;
-                const __half2 h = __halves2half2(ctab[entry & 15], ctab[entry >> 4]);
-                const uint32_t v = *reinterpret_cast<const uint32_t*>(&h);
-                reinterpret_cast<uint4*>(T4)[entry * 8 + q4] = make_uint4(v, v, v, v);
-            }
-            for (int e = tid; e < 256 * 8; e += NT) {     // 2 replicas per 128-bit store
-                const int entry = e >> 3, q2 = e & 7;
-                const int n0 = entry & 15, n1 = entry >> 4;
-                const __half2 h0 = __halves2half2(ctab[32 + (n0 & 3)], ctab[32 + (n0 >> 2)]);
-                const __half2 h1 = __halves2half2(ctab[32 + (n1 & 3)], ctab[32 + (n1 >> 2)]);
-                const uint32_t v0 = *reinterpret_cast<const uint32_t*>(&h0), v1 = *reinterpret_cast<const uint32_t*>(&h1);
-                reinterpret_cast<uint4*>(T2)[entry * 8 + q2] = make_uint4(v0, v1, v0, v1);
-            }
-        }
-    } else {
-        if (!dense && tid < 64) {
-            const int which = tid >> 4, k = tid & 15;
-            const float* src = which == 0 ? p.kc_hi : which == 1 ? p.kc_lo : which == 2 ? p.vc_hi : p.vc_lo;
-            const int bits = which == 0 ? p.kb_hi : which == 1 ? p.kb_lo : which == 2 ? p.vb_hi : p.vb_lo;
-            const float sc = which == 2 ? p.v_scale_hi : which == 3 ? p.v_scale_lo : 1.f;
-            ctab[tid] = __float2half_rn((src != nullptr && bits > 0 && k < (1 << bits)) ? src[k] * sc : 0.f);
-        }
+    if (!dense && tid < 64) {
+        const int which = tid >> 4, k = tid & 15;
+        const float* src = which == 0 ? p.kc_hi : which == 1 ? p.kc_lo : which == 2 ? p.vc_hi : p.vc_lo;
+        const int bits = which == 0 ? p.kb_hi : which == 1 ? p.kb_lo : which == 2 ? p.vb_hi : p.vb_lo;
+        const float sc = which == 2 ? p.v_scale_hi : which == 3 ? p.v_scale_lo : 1.f;
+        ctab[tid] = __float2half_rn((src != nullptr && bits > 0 && k < (1 << bits)) ? src[k] * sc : 0.f);
     }
-    TQ_STAMP(1);
     pdl_wait();        // from here on: the query, the cache and the workspace of the previous launch are settled
 
-    TQ_STAMP(2);
-    RingCtx<D, NW> rc;
     // ---------------- the query heads of this group: float32, then (rotated) scaled fp16 --------------------
     // q_rot[h][j] = sum_k q[h][k] R[j][k]  (rotation.py:81-110)
     {
         const float f = p.scale * LOG2E;
-        if constexpr (DIRECT) {
-            // R (64 KB) is read ONCE per CTA with fully coalesced 128-bit loads and stays resident in shared
-            // memory (the epilogue needs it again); chunk placement rot_pos() keeps both uses conflict-free.
-            float4* rs = reinterpret_cast<float4*>(smem + rot_offset<D, NW>());
-            float4 rr[(D * D / 4) / NT];
-            if (!dense) {
-#pragma unroll
-                for (int i = 0; i < (D * D / 4) / NT; ++i) rr[i] = __ldg(reinterpret_cast<const float4*>(p.rot) + tid + i * NT);
-            }
-            // 16-byte chunk kc of a query row is stored at chunk kc ^ (kc >> 3): the four threads of a row
-            // quartet read chunks 8 apart, which would otherwise share a bank group
-            for (int e = tid; e < heads_here * D; e += NT) {
-                const int kc = (e % D) >> 2;
-                qf[(e - (e % D)) + ((kc ^ (kc >> 3)) << 2) + (e & 3)] = load_as_f32(p.q, p.q_dtype, qbase + e);
-            }
-            if (!dense) {
-                // start streaming the first packed tiles: they land while the query is being rotated
-                rc.init(p, smem, kvl, split, warp, lane);
-#pragma unroll
-                for (int i = 0; i < RING_STAGES - 1; ++i) {
-                    if (rc.first + i * NW < rc.tile_hi) rc.issue(i, rc.first + i * NW, lane);
-                    cp_async_commit();
-                }
-#pragma unroll
-                for (int i = 0; i < (D * D / 4) / NT; ++i) {
-                    const int idx = tid + i * NT, j = idx / (D / 4), k = idx - j * (D / 4);
-                    rs[j * (D / 4) + rot_pos(j, k)] = rr[i];
-                }
-            }
-            __syncthreads();
-            if (dense) {
-                for (int e = tid; e < heads_here * D; e += NT) {
-                    const int kc = (e % D) >> 2;
-                    qs[e] = __float2half_rn(qf[(e - (e % D)) + ((kc ^ (kc >> 3)) << 2) + (e & 3)] * f);
-                }
-            } else {
-                // thread (j, part): columns [part*32, part*32+32) of row j; the four parts of a row are adjacent lanes
-                constexpr int KP = NT / D, COLS = D / KP;
-                static_assert(KP == 4, "direct path: four threads per row of R");
-                const int j = tid >> 2, kp = tid & 3;
-                float acc[HPG];
-#pragma unroll
-                for (int h = 0; h < HPG; ++h) acc[h] = 0.f;
-#pragma unroll
-                for (int k = 0; k < COLS / 4; ++k) {
-                    const int kc = kp * (COLS / 4) + k;
-                    const float4 r = rs[j * (D / 4) + rot_pos(j, kc)];
-#pragma unroll
-                    for (int h = 0; h < HPG; ++h) {
-                        if (h < heads_here) {
-                            const float4 x = *reinterpret_cast<const float4*>(qf + h * D + 4 * (kc ^ (kc >> 3)));
-                            acc[h] = fmaf(x.x, r.x, fmaf(x.y, r.y, fmaf(x.z, r.z, fmaf(x.w, r.w, acc[h]))));
-                        }
-                    }
-                }
-#pragma unroll
-                for (int h = 0; h < HPG; ++h) {
-                    acc[h] += __shfl_xor_sync(0xffffffffu, acc[h], 1);
-                    acc[h] += __shfl_xor_sync(0xffffffffu, acc[h], 2);
-                    if (kp == 0 && h < heads_here) qs[h * D + j] = __float2half_rn(acc[h] * f);
-                }
-            }
-        } else {
+        {
             // general path: thread (j, part) reads its slice of row j straight from global memory
             constexpr int KP = NT / D >= 4 ? 4 : NT / D >= 2 ? 2 : 1;     // slices per row (power of two)
             constexpr int COLS = D / KP;                                   // columns per slice
@@ -435,7 +138,6 @@ __global__ void __launch_bounds__(warps_per_cta(DIRECT) * 32, 1) decode_attn_ker
         }
     }
     __syncthreads();
-    TQ_STAMP(3);
 
     WarpAcc<D> st;
     st.m[0] = st.m[1] = st.mt[0] = st.mt[1] = -INFINITY;
@@ -443,87 +145,23 @@ __global__ void __launch_bounds__(warps_per_cta(DIRECT) * 32, 1) decode_attn_ker
 #pragma unroll
     for (int mt = 0; mt < D / 16; ++mt) st.o[mt][0] = st.o[mt][1] = st.o[mt][2] = st.o[mt][3] = 0.f;
 
-    bool direct_order = false;   // which coordinate permutation the accumulators use
-
+    uint32_t bq[D / 16][2];
+    {
+        const __half* qh = qs + g * D;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            bq[ks][0] = g < heads_here ? *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * t) : 0u;
+            bq[ks][1] = g < heads_here ? *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * t + 8) : 0u;
+        }
+    }
+    __half* Ks = reinterpret_cast<__half*>(smem) + size_t(warp) * 2 * TILE * LD;
+    __half* Vs = Ks + TILE * LD;
     if (dense) {
         // ---------------- uncompressed tokens: sink then residual window, raw query ----------------
-        uint32_t bq[D / 16][2];
-        {
-            const __half* qh = qs + g * D;
-#pragma unroll
-            for (int ks = 0; ks < D / 16; ++ks) {
-                bq[ks][0] = g < heads_here ? *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * t) : 0u;
-                bq[ks][1] = g < heads_here ? *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * t + 8) : 0u;
-            }
-        }
-        __half* Ks = reinterpret_cast<__half*>(smem) + size_t(warp) * 2 * TILE * LD;
-        __half* Vs = Ks + TILE * LD;
-        const int64_t n_tok = p.sink_len + p.res_len;
         const int64_t tile_lo = int64_t(split - p.n_ps) * p.d_tps;
-        const int64_t tile_hi = min(tile_lo + p.d_tps, (n_tok + TILE - 1) / TILE);
-        for (int64_t tile = tile_lo + warp; tile < tile_hi; tile += NW) {
-            const int64_t tok0 = tile * TILE;
-            constexpr int NCH = TILE * (D / 8) / 32;          // 16-byte chunks per lane and tensor
-            if (p.dense_dtype == TQ_F16) {
-                uint4 kv[NCH], vv[NCH];                        // every load of the tile in flight before the first store
-#pragma unroll
-                for (int i = 0; i < NCH; ++i) {
-                    const int c = lane + 32 * i, r = c / (D / 8), c8 = c - r * (D / 8);
-                    const int64_t tok = tok0 + r;
-                    kv[i] = make_uint4(0, 0, 0, 0); vv[i] = kv[i];
-                    if (tok < n_tok) {
-                        const bool in_sink = tok < p.sink_len;
-                        const int64_t e = (in_sink ? kvl * p.sink_ls + tok : kvl * p.res_ls + (tok - p.sink_len)) * D + c8 * 8;
-                        kv[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(in_sink ? p.sink_k : p.res_k) + e));
-                        vv[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(in_sink ? p.sink_v : p.res_v) + e));
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < NCH; ++i) {
-                    const int c = lane + 32 * i, r = c / (D / 8), c8 = c - r * (D / 8);
-                    *reinterpret_cast<uint4*>(Ks + r * LD + c8 * 8) = kv[i];
-                    *reinterpret_cast<uint4*>(Vs + r * LD + c8 * 8) = vv[i];
-                }
-            } else {
-                for (int c = lane; c < TILE * (D / 8); c += 32) {
-                    const int r = c / (D / 8), c8 = c - r * (D / 8);
-                    const int64_t tok = tok0 + r;
-                    uint4 kv = make_uint4(0, 0, 0, 0), vv = kv;
-                    if (tok < n_tok) {
-                        const bool in_sink = tok < p.sink_len;
-                        const int64_t e = (in_sink ? kvl * p.sink_ls + tok : kvl * p.res_ls + (tok - p.sink_len)) * D + c8 * 8;
-                        const void* kb = in_sink ? p.sink_k : p.res_k;
-                        const void* vb = in_sink ? p.sink_v : p.res_v;
-                        __half hk[8], hv[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            hk[i] = __float2half_rn(load_as_f32(kb, p.dense_dtype, e + i));
-                            hv[i] = __float2half_rn(load_as_f32(vb, p.dense_dtype, e + i));
-                        }
-                        kv = *reinterpret_cast<uint4*>(hk);
-                        vv = *reinterpret_cast<uint4*>(hv);
-                    }
-                    *reinterpret_cast<uint4*>(Ks + r * LD + c8 * 8) = kv;
-                    *reinterpret_cast<uint4*>(Vs + r * LD + c8 * 8) = vv;
-                }
-            }
-            __syncwarp();
-            tile_from_smem<D>(Ks, Vs, bq, 1.f, 1.f, 1.f, 1.f, tok0 + g < n_tok, tok0 + g + 8 < n_tok, st, lane);
-            __syncwarp();
-        }
-    } else if constexpr (!DIRECT) {
-        // ---------------- packed tokens, general path: unpack into shared memory ---------------------
-        uint32_t bq[D / 16][2];
-        {
-            const __half* qh = qs + g * D;
-#pragma unroll
-            for (int ks = 0; ks < D / 16; ++ks) {
-                bq[ks][0] = g < heads_here ? *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * t) : 0u;
-                bq[ks][1] = g < heads_here ? *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * t + 8) : 0u;
-            }
-        }
-        __half* Ks = reinterpret_cast<__half*>(smem) + size_t(warp) * 2 * TILE * LD;
-        __half* Vs = Ks + TILE * LD;
+        dense_tiles<D, NW>(p, kvl, tile_lo, tile_lo + p.d_tps, Ks, Vs, bq, st, warp, lane);
+    } else {
+        // ---------------- packed tokens: unpack into shared memory ---------------------
         const int k_half = p.kb_lo ? D / 2 : D, v_half = p.vb_lo ? D / 2 : D;
         const int kw_hi = packed_bytes(k_half, p.kb_hi), kw_lo = p.kb_lo ? packed_bytes(D - k_half, p.kb_lo) : 0;
         const int vw_hi = packed_bytes(v_half, p.vb_hi), vw_lo = p.vb_lo ? packed_bytes(D - v_half, p.vb_lo) : 0;
@@ -563,91 +201,6 @@ __global__ void __launch_bounds__(warps_per_cta(DIRECT) * 32, 1) decode_attn_ker
             tile_from_smem<D>(Ks, Vs, bq, kn0, kn1, vn0, vn1, ok0, ok1, st, lane);
             __syncwarp();
         }
-    } else {
-        // ---------------- packed tokens, direct path: 4-bit keys, 2-bit values -------------------------
-        direct_order = true;
-        static_assert(!DIRECT || D == 128, "the direct path's shared-memory tile layout is written for d = 128");
-        // Query fragments in the byte order of the 4-bit rows: thread t owns coordinates [t*D/4, (t+1)*D/4).
-        uint32_t bq[D / 16][2];
-        {
-            const __half* qh = qs + g * D + t * (D / 4);
-#pragma unroll
-            for (int ks = 0; ks < D / 16; ++ks) {
-                bq[ks][0] = g < heads_here ? *reinterpret_cast<const uint32_t*>(qh + 4 * ks) : 0u;
-                bq[ks][1] = g < heads_here ? *reinterpret_cast<const uint32_t*>(qh + 4 * ks + 2) : 0u;
-            }
-        }
-        using RC = RingCtx<D, NW>;
-        constexpr int KT = RC::KT, VT = RC::VT, VW = RC::VW, STG = RC::STG;
-        // 32-bit shared-window addresses of this lane's private table columns: entry e of T4 sits at
-        // t4 + e*128, entry e of T2 at t2 + e*128 (one multiply-add each, no 64-bit address arithmetic).
-        const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
-        const uint32_t t4 = smem_base + lane * 4;
-        const uint32_t t2 = smem_base + 32768 + (lane & 15) * 8;
-        const uint32_t ring = rc.ring;
-        const int c_len = rc.c_len, tile_hi = rc.tile_hi;
-        const uint32_t vo0 = KT + RC::vslot(2 * t) * VW + g * 4, vo1 = KT + RC::vslot(2 * t + 1) * VW + g * 4;
-        const uint32_t vo2 = KT + RC::vslot(2 * t + 8) * VW + g * 4, vo3 = KT + RC::vslot(2 * t + 9) * VW + g * 4;
-        auto compute = [&](int stage, int tile) {
-            const uint32_t sb = ring + stage * STG;
-            const int tok0 = tile * TILE;
-            const uint4 q0 = ring128(sb + lane * 16);            // token g,   this thread's quarter row
-            const uint4 q1 = ring128(sb + 512 + lane * 16);      // token g+8
-            const float kn0 = __uint_as_float(ring32(sb + KT + VT + g * 4)), kn1 = __uint_as_float(ring32(sb + KT + VT + 32 + g * 4));
-            const float vn0 = __uint_as_float(ring32(sb + KT + VT + 64 + g * 4)), vn1 = __uint_as_float(ring32(sb + KT + VT + 96 + g * 4));
-            const uint32_t va = ring32(sb + vo0), vb = ring32(sb + vo1), vc = ring32(sb + vo2), vd = ring32(sb + vo3);
-            // two independent accumulators (even / odd k-steps) halve the dependent MMA chain
-            float s[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int ks = 0; ks < D / 16; ++ks) {
-                // bytes 2ks, 2ks+1 of the quarter row
-                const int wi = ks >> 1;
-                const uint32_t w0 = wi == 0 ? q0.x : wi == 1 ? q0.y : wi == 2 ? q0.z : q0.w;
-                const uint32_t w1 = wi == 0 ? q1.x : wi == 1 ? q1.y : wi == 2 ? q1.z : q1.w;
-                const int b0 = (ks & 1) * 2;
-                const uint32_t a0 = lut32(__byte_perm(w0, 0, 0x4440 | b0) * 128u + t4);
-                const uint32_t a1 = lut32(__byte_perm(w1, 0, 0x4440 | b0) * 128u + t4);
-                const uint32_t a2 = lut32(__byte_perm(w0, 0, 0x4440 | (b0 + 1)) * 128u + t4);
-                const uint32_t a3 = lut32(__byte_perm(w1, 0, 0x4440 | (b0 + 1)) * 128u + t4);
-                if (ks & 1) mma16816(s2, a0, a1, a2, a3, bq[ks][0], bq[ks][1]);
-                else mma16816(s, a0, a1, a2, a3, bq[ks][0], bq[ks][1]);
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) s[i] += s2[i];
-            uint32_t bp[2];
-            softmax_step<D>(s, kn0, kn1, vn0, vn1, tok0 + g < c_len, tok0 + g + 8 < c_len, st, bp);
-            // interleave the 2-bit codes of a token pair: nibble k of X = (A code 2k) | (B code 2k) << 2
-            const uint32_t x0 = (va & 0x33333333u) | ((vb << 2) & 0xCCCCCCCCu);
-            const uint32_t y0 = ((va >> 2) & 0x33333333u) | (vb & 0xCCCCCCCCu);
-            const uint32_t x1 = (vc & 0x33333333u) | ((vd << 2) & 0xCCCCCCCCu);
-            const uint32_t y1 = ((vc >> 2) & 0x33333333u) | (vd & 0xCCCCCCCCu);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const uint2 fa = lut64(__byte_perm(x0, 0, 0x4440 | k) * 128u + t2);   // rows g,   tokens 2t,2t+1   -> m-tiles 2k, 2k+1
-                const uint2 fb = lut64(__byte_perm(y0, 0, 0x4440 | k) * 128u + t2);   // rows g+8
-                const uint2 fc = lut64(__byte_perm(x1, 0, 0x4440 | k) * 128u + t2);   // rows g,   tokens 2t+8,2t+9
-                const uint2 fd = lut64(__byte_perm(y1, 0, 0x4440 | k) * 128u + t2);
-                mma16816(st.o[2 * k], fa.x, fb.x, fc.x, fd.x, bp[0], bp[1]);
-                mma16816(st.o[2 * k + 1], fa.y, fb.y, fc.y, fd.y, bp[0], bp[1]);
-            }
-        };
-        // Software pipeline: RING_STAGES - 1 tiles in flight per warp (the first ones were issued before the query
-        // was rotated).  One commit group per slot, issued or not, keeps the group count uniform; cp.async
-        // completion is tracked by hardware (no spin waits).
-        const int first = rc.first;
-        int stage = 0;
-        for (int tile = first; tile < tile_hi; tile += NW) {
-            const int ahead = tile + (RING_STAGES - 1) * NW;
-            const int st_in = stage == 0 ? RING_STAGES - 1 : stage - 1;
-            if (ahead < tile_hi) rc.issue(st_in, ahead, lane);
-            cp_async_commit();
-            cp_async_wait<RING_STAGES - 1>();
-            __syncwarp();
-            compute(stage, tile);
-            __syncwarp();       // every lane is done with this stage before it is refilled
-            stage = stage == RING_STAGES - 1 ? 0 : stage + 1;
-        }
-        cp_async_wait<0>();
     }
 
     // ---------------- CTA reduction over warps ----------------------------------------------------------------
@@ -657,7 +210,6 @@ __global__ void __launch_bounds__(warps_per_cta(DIRECT) * 32, 1) decode_attn_ker
         st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], off);
     }
     __syncthreads();   // staging / tables / ring are dead from here on
-    TQ_STAMP(4);
     constexpr int DS = D + 2;                               // row stride (floats): keeps the 64-bit stores below 2-way conflicts
     constexpr int RW = HPG * DS + 2 * HPG;                  // floats per warp in the reduction buffer
     float* red = reinterpret_cast<float*>(smem);
@@ -670,15 +222,9 @@ __global__ void __launch_bounds__(warps_per_cta(DIRECT) * 32, 1) decode_attn_ker
         if (2 * t < heads_here) {                           // lanes that hold only padding heads store nothing
 #pragma unroll
             for (int mt = 0; mt < D / 16; ++mt) {
-                if (direct_order) {                          // rows g, g+8 of the tile are coordinates c0, c0+1
-                    const int c0 = g * (D / 8) + 2 * mt;
-                    *reinterpret_cast<float2*>(ro + (2 * t) * DS + c0) = make_float2(st.o[mt][0], st.o[mt][2]);
-                    *reinterpret_cast<float2*>(ro + (2 * t + 1) * DS + c0) = make_float2(st.o[mt][1], st.o[mt][3]);
-                } else {
-                    const int c0 = mt * 16 + g;
-                    ro[(2 * t) * DS + c0] = st.o[mt][0]; ro[(2 * t + 1) * DS + c0] = st.o[mt][1];
-                    ro[(2 * t) * DS + c0 + 8] = st.o[mt][2]; ro[(2 * t + 1) * DS + c0 + 8] = st.o[mt][3];
-                }
+                const int c0 = mt * 16 + g;
+                ro[(2 * t) * DS + c0] = st.o[mt][0]; ro[(2 * t + 1) * DS + c0] = st.o[mt][1];
+                ro[(2 * t) * DS + c0 + 8] = st.o[mt][2]; ro[(2 * t + 1) * DS + c0 + 8] = st.o[mt][3];
             }
         }
         if (g == 0) {
@@ -733,8 +279,7 @@ __global__ void __launch_bounds__(warps_per_cta(DIRECT) * 32, 1) decode_attn_ker
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int c = slab * ROWS + c4 * 4 + u;
-                    if constexpr (DIRECT) r[u] = reinterpret_cast<const float*>(smem + rot_offset<D, NW>())[(c * (D / 4) + rot_pos(c, j >> 2)) * 4 + (j & 3)];
-                    else r[u] = __ldg(p.rot + int64_t(c) * D + j);
+                    r[u] = __ldg(p.rot + int64_t(c) * D + j);
                 }
 #pragma unroll
                 for (int h = 0; h < HPG; ++h) {
@@ -769,10 +314,8 @@ __global__ void __launch_bounds__(warps_per_cta(DIRECT) * 32, 1) decode_attn_ker
             p.counters[grp] = 0;     // ready for the next launch
         }
     }
-    TQ_STAMP(5);
     __syncthreads();
     if (s_misc[8] == 0.f) return;
-    TQ_STAMP(7);
     const int SL = p.slots;
     const int64_t base = grp * S;
     // thread (h, c) loads its partial accumulators of up to 24 splits while other threads fetch the (max, sum)
@@ -793,7 +336,6 @@ __global__ void __launch_bounds__(warps_per_cta(DIRECT) * 32, 1) decode_attn_ker
         s_ml[h * MAX_SPLITS + sidx] = __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((base + sidx) * SL + h) * 2));
     }
     __syncthreads();
-    TQ_STAMP(8);
     for (int e = tid; e < D * heads_here; e += NT) {
         const int h = e / D, c = e - h * D;
         const float* src = p.part_o + (base * SL + h) * D + c;
@@ -819,7 +361,6 @@ __global__ void __launch_bounds__(warps_per_cta(DIRECT) * 32, 1) decode_attn_ker
         }
         store_from_f32(p.out, p.out_dtype, qbase + e, acc / L);
     }
-    TQ_STAMP(6);
 }
 
 // ---- host side ------------------------------------------------------------------------------------
@@ -841,7 +382,7 @@ static int sm_count() {
 struct SplitPlan { int n_ps, n_ds, hg; int64_t p_tps, d_tps; };
 
 static SplitPlan plan_splits(int batch, int n_q_heads, int n_kv_heads, int64_t c_len, int64_t dense_len, int sms, bool direct) {
-    const int NW = warps_per_cta(direct);
+    const int NW = direct ? DIRECT_WARPS : GNW;
     SplitPlan s{};
     const int G = n_q_heads / n_kv_heads;
     s.hg = (G + HPG - 1) / HPG;
@@ -883,13 +424,13 @@ static WsLayout ws_layout(int batch, int n_q_heads, int n_kv_heads, int d, const
     return w;
 }
 
-template <int D, bool DIRECT> static int launch_decode(const DecodeParams& p, cudaStream_t s) {
-    constexpr size_t smem = kernel_smem<D, DIRECT>();
+template <int D> static int launch_decode(const DecodeParams& p, cudaStream_t s) {
+    constexpr size_t smem = kernel_smem<D>();
     static bool set[16] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 16 && !set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(decode_attn_kernel<D, DIRECT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        cudaError_t e = cudaFuncSetAttribute(decode_attn_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_decode_attn: shared memory %zu B: %s", smem, cudaGetErrorString(e));
         set[dev] = true;
     }
@@ -897,7 +438,7 @@ template <int D, bool DIRECT> static int launch_decode(const DecodeParams& p, cu
     // has finished; the kernel calls griddepcontrol.wait before it touches anything but constants.
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(unsigned(p.n_ps + p.n_ds), unsigned(p.Hkv * p.HG), unsigned(p.B));
-    cfg.blockDim = dim3(warps_per_cta(DIRECT) * 32);
+    cfg.blockDim = dim3(GNW * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
@@ -905,7 +446,7 @@ template <int D, bool DIRECT> static int launch_decode(const DecodeParams& p, cu
     attr[0].val.programmaticStreamSerializationAllowed = g_tune_pdl ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_attn_kernel<D, DIRECT>, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_attn_kernel<D>, p);
     if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_decode_attn: %s", cudaGetErrorString(e));
     return TQ_OK;
 }
@@ -945,7 +486,7 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
     // direct path: 4-bit keys / 2-bit values, d = 128, rows and norms addressable in aligned 16-byte chunks
     const bool direct = !g_tune_force_general && d == 128 && a->c_len > 0 && a->k_bits_hi == 4 && a->k_bits_lo == 0 &&
                         a->v_bits_hi == 2 && a->v_bits_lo == 0 && aligned(a->k_hi, 16) && aligned(a->v_hi, 16) &&
-                        aligned(a->k_norms, 16) && aligned(a->v_norms, 16) && a->c_lane_stride % 16 == 0;
+                        aligned(a->k_norms, 16) && aligned(a->v_norms, 16) && a->c_lane_stride % 16 == 0 && direct_supported();
     const SplitPlan sp = plan_splits(a->batch, a->n_q_heads, a->n_kv_heads, a->c_len, dense_len, sm_count(), direct);
     const WsLayout wl = ws_layout(a->batch, a->n_q_heads, a->n_kv_heads, d, sp);
     if (wl.total > workspace_bytes) return fail(TQ_ERR_INVALID, "tq_decode_attn: workspace %zu B < %zu B", workspace_bytes, wl.total);
@@ -969,28 +510,29 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
     p.counters = reinterpret_cast<int*>(ws + wl.counters);
     p.part_o = reinterpret_cast<float*>(ws + wl.part_o); p.part_ml = reinterpret_cast<float*>(ws + wl.part_ml);
     p.out = a->out; p.out_dtype = a->out_dtype;
+    p.pdl = g_tune_pdl;
+    p.cent_by_value = 0;
+    if (direct && a->k_cent_hi_host && a->v_cent_hi_host) {
+        p.cent_by_value = 1;
+        for (int i = 0; i < 16; ++i) p.kc16[i] = a->k_cent_hi_host[i];
+        for (int i = 0; i < 4; ++i) p.vc4[i] = a->v_cent_hi_host[i];
+    }
     *out = p;
     *direct_out = direct;
     return TQ_OK;
 }
 
 int decode_launch(const DecodeParams& p, bool direct, cudaStream_t s) {
-    if (direct) return launch_decode<128, true>(p, s);
-    if (p.D == 64) return launch_decode<64, false>(p, s);
-    if (p.D == 96) return launch_decode<96, false>(p, s);
-    if (p.D == 128) return launch_decode<128, false>(p, s);
-    return launch_decode<256, false>(p, s);
+    if (direct) return launch_decode_direct(p, s);
+    if (p.D == 64) return launch_decode<64>(p, s);
+    if (p.D == 96) return launch_decode<96>(p, s);
+    if (p.D == 128) return launch_decode<128>(p, s);
+    return launch_decode<256>(p, s);
 }
 
 }  // namespace tq
 
 using namespace tq;
-
-#ifdef TQ_TIMING
-extern "C" int tq_debug_timing(unsigned long long* host_out, int n) {
-    return int(cudaMemcpyFromSymbol(host_out, g_tq_timing, sizeof(unsigned long long) * n));
-}
-#endif
 
 extern "C" int tq_set_tuning(const char* key, int value) {
     if (!key) return fail(TQ_ERR_INVALID, "tq_set_tuning: null key");

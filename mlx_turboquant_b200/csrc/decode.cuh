@@ -5,7 +5,7 @@
 
 namespace tq {
 
-__host__ __device__ constexpr int warps_per_cta(bool direct) { return direct ? 16 : 8; }   // warps per CTA
+constexpr int DIRECT_WARPS = 16;     // warps per CTA of the 4-bit-key / 2-bit-value kernel
 constexpr int TILE = 16;              // tokens per warp tile
 constexpr int HPG = 8;                // query heads per head group (the mma N dimension)
 constexpr int MAX_SPLITS = 512;
@@ -29,11 +29,20 @@ struct DecodeParams {
     float *part_o, *part_ml;           // workspace: (B, Hkv, HG, S, slots, D) and (B, Hkv, HG, S, slots, 2)
     int* counters;                     // workspace: (B, Hkv, HG) arrival counters, zero between launches
     void* out; int out_dtype;
+    int pdl;                           // launch with programmatic stream serialisation
+    int cent_by_value;                 // kc16 / vc4 below hold the key / value centroids (host copies were given)
+    float kc16[16], vc4[4];
 };
 
 // Validates the arguments, picks the path and the split plan and fills the kernel parameters for the given
 // scratch buffer (which must be zero-filled before its first use; the kernel leaves its counters at zero).
 int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_bytes, DecodeParams* out, bool* direct_out);
 int decode_launch(const DecodeParams& p, bool direct, cudaStream_t s);
+
+// decode_direct.cu: the kernel for 4-bit keys / 2-bit values at d = 128.  direct_supported() checks once per
+// device (one tiny synchronous probe launch on first use) that the kernel's shared-memory plan fits the device.
+bool direct_supported();
+int launch_decode_direct(const DecodeParams& p, cudaStream_t s);
+int decode_status_host();          // code of the first bounded wait that ran out on this device (0 = none), -1 on error
 
 }  // namespace tq

@@ -1,0 +1,210 @@
+// Device-side building blocks shared by the decode-attention kernels: PTX wrappers, the per-warp online-softmax
+// state, and the 16-token tile step on fp16 operands staged in shared memory.
+#pragma once
+
+#include "decode.cuh"
+
+namespace tq {
+
+// ---- small PTX wrappers --------------------------------------------------------------------------
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* smem_ptr) {
+    uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem_ptr));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* smem_ptr) {
+    uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem_ptr));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t movm_t(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+// Lookups in tables that are constant for the lifetime of the CTA: plain (non-volatile) asm so the compiler
+// may hoist and batch them ahead of the MMAs that consume them.
+__device__ __forceinline__ uint32_t lut32(uint32_t addr) {
+    uint32_t v;
+    asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lut64(uint32_t addr) {
+    uint2 v;
+    asm("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+// Reads of the cp.async ring: ordered after the wait / warp barrier that makes the data visible.
+__device__ __forceinline__ uint32_t ring32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 ring128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+// 16-byte asynchronous global -> shared copy; bytes past src_bytes are zero-filled (0 = read nothing).
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// Programmatic dependent launch: wait for the previous grid on the stream / let the next grid start its prologue.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// ---- per-warp running softmax state ------------------------------------------------------------------
+constexpr float MAX_SLACK = 6.f;   // scores may exceed the running reference by 2^6 before it is refreshed
+template <int D> struct WarpAcc {
+    float m[2], mt[2], l[2];   // heads 2t, 2t+1: reference max, refresh threshold, this lane's share of the sum
+    float o[D / 16][4];        // O^T fragments: rows = coordinate slots, cols = heads
+};
+
+// s[0..1]: token g, heads 2t,2t+1;  s[2..3]: token g+8.  Returns the P^T operand for the PV mma.
+// The softmax reference m is refreshed (with a cross-lane max and a rescale of the accumulators) only
+// when some score exceeds it by more than MAX_SLACK; softmax is shift-invariant, so any reference that
+// keeps exp2(s - m) inside the fp16 range is exact.
+template <int D>
+__device__ __forceinline__ void softmax_step(float (&s)[4], float kn0, float kn1, float vn0, float vn1, bool ok0,
+                                             bool ok1, WarpAcc<D>& st, uint32_t (&bp)[2]) {
+    s[0] = ok0 ? s[0] * kn0 : -INFINITY;
+    s[1] = ok0 ? s[1] * kn0 : -INFINITY;
+    s[2] = ok1 ? s[2] * kn1 : -INFINITY;
+    s[3] = ok1 ? s[3] * kn1 : -INFINITY;
+    float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+    if (__any_sync(0xffffffffu, mx0 > st.mt[0] || mx1 > st.mt[1])) {
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+        }
+        const float mn0 = fmaxf(fmaxf(st.m[0], mx0), -1e30f), mn1 = fmaxf(fmaxf(st.m[1], mx1), -1e30f);
+        const float a0 = ex2(st.m[0] - mn0), a1 = ex2(st.m[1] - mn1);
+        st.m[0] = mn0; st.m[1] = mn1;
+        st.mt[0] = mn0 + MAX_SLACK; st.mt[1] = mn1 + MAX_SLACK;
+        st.l[0] *= a0; st.l[1] *= a1;
+#pragma unroll
+        for (int mt = 0; mt < D / 16; ++mt) {
+            st.o[mt][0] *= a0; st.o[mt][1] *= a1; st.o[mt][2] *= a0; st.o[mt][3] *= a1;
+        }
+    }
+    const float p0 = ex2(s[0] - st.m[0]), p1 = ex2(s[1] - st.m[1]), p2 = ex2(s[2] - st.m[0]), p3 = ex2(s[3] - st.m[1]);
+    st.l[0] += p0 + p2;
+    st.l[1] += p1 + p3;
+    // value norms ride on P (fp16, clamped below the fp16 maximum)
+    const uint32_t h0 = pack_h2(fminf(p0 * vn0, 65504.f), fminf(p1 * vn0, 65504.f));
+    const uint32_t h1 = pack_h2(fminf(p2 * vn1, 65504.f), fminf(p3 * vn1, 65504.f));
+    bp[0] = movm_t(h0);   // tokens 2t,2t+1   x head g
+    bp[1] = movm_t(h1);   // tokens 2t+8,2t+9 x head g
+}
+
+template <int D> __host__ __device__ constexpr int stage_ld() { return D + 8; }
+
+// One 16-token tile whose K and V sit in shared memory as fp16 [token][coordinate].
+template <int D>
+__device__ __forceinline__ void tile_from_smem(const __half* Ks, const __half* Vs, const uint32_t (&bq)[D / 16][2],
+                                               float kn0, float kn1, float vn0, float vn1, bool ok0, bool ok1,
+                                               WarpAcc<D>& st, int lane) {
+    constexpr int LD = stage_ld<D>();
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+        const __half* base = Ks + (lane & 15) * LD + (lane >> 4) * 8;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            uint32_t a[4];
+            ldsm_x4(a, base + ks * 16);
+            mma16816(s, a[0], a[1], a[2], a[3], bq[ks][0], bq[ks][1]);
+        }
+    }
+    uint32_t bp[2];
+    softmax_step<D>(s, kn0, kn1, vn0, vn1, ok0, ok1, st, bp);
+    {
+        const __half* base = Vs + ((lane & 7) + ((lane >> 4) & 1) * 8) * LD + ((lane >> 3) & 1) * 8;
+#pragma unroll
+        for (int mt = 0; mt < D / 16; ++mt) {
+            uint32_t a[4];
+            ldsm_x4_t(a, base + mt * 16);
+            mma16816(st.o[mt], a[0], a[1], a[2], a[3], bp[0], bp[1]);
+        }
+    }
+}
+
+// Attention over the uncompressed tokens [sink | residual window] of cache lane kvl with the unrotated query:
+// this warp takes tiles tile_lo + warp, + NW, ... below tile_hi; Ks / Vs are its fp16 staging buffers.
+template <int D, int NW>
+__device__ __forceinline__ void dense_tiles(const DecodeParams& p, int64_t kvl, int64_t tile_lo, int64_t tile_hi_in, __half* Ks, __half* Vs,
+                                            const uint32_t (&bq)[D / 16][2], WarpAcc<D>& st, int warp, int lane) {
+    constexpr int LD = stage_ld<D>();
+    const int g = lane >> 2;
+    const int64_t n_tok = p.sink_len + p.res_len;
+    const int64_t tile_hi = min(tile_hi_in, (n_tok + TILE - 1) / TILE);
+    for (int64_t tile = tile_lo + warp; tile < tile_hi; tile += NW) {
+        const int64_t tok0 = tile * TILE;
+        constexpr int NCH = TILE * (D / 8) / 32;          // 16-byte chunks per lane and tensor
+        if (p.dense_dtype == TQ_F16) {
+            uint4 kv[NCH], vv[NCH];                        // every load of the tile in flight before the first store
+#pragma unroll
+            for (int i = 0; i < NCH; ++i) {
+                const int c = lane + 32 * i, r = c / (D / 8), c8 = c - r * (D / 8);
+                const int64_t tok = tok0 + r;
+                kv[i] = make_uint4(0, 0, 0, 0); vv[i] = kv[i];
+                if (tok < n_tok) {
+                    const bool in_sink = tok < p.sink_len;
+                    const int64_t e = (in_sink ? kvl * p.sink_ls + tok : kvl * p.res_ls + (tok - p.sink_len)) * D + c8 * 8;
+                    kv[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(in_sink ? p.sink_k : p.res_k) + e));
+                    vv[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(in_sink ? p.sink_v : p.res_v) + e));
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < NCH; ++i) {
+                const int c = lane + 32 * i, r = c / (D / 8), c8 = c - r * (D / 8);
+                *reinterpret_cast<uint4*>(Ks + r * LD + c8 * 8) = kv[i];
+                *reinterpret_cast<uint4*>(Vs + r * LD + c8 * 8) = vv[i];
+            }
+        } else {
+            for (int c = lane; c < TILE * (D / 8); c += 32) {
+                const int r = c / (D / 8), c8 = c - r * (D / 8);
+                const int64_t tok = tok0 + r;
+                uint4 kv = make_uint4(0, 0, 0, 0), vv = kv;
+                if (tok < n_tok) {
+                    const bool in_sink = tok < p.sink_len;
+                    const int64_t e = (in_sink ? kvl * p.sink_ls + tok : kvl * p.res_ls + (tok - p.sink_len)) * D + c8 * 8;
+                    const void* kb = in_sink ? p.sink_k : p.res_k;
+                    const void* vb = in_sink ? p.sink_v : p.res_v;
+                    __half hk[8], hv[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        hk[i] = __float2half_rn(load_as_f32(kb, p.dense_dtype, e + i));
+                        hv[i] = __float2half_rn(load_as_f32(vb, p.dense_dtype, e + i));
+                    }
+                    kv = *reinterpret_cast<uint4*>(hk);
+                    vv = *reinterpret_cast<uint4*>(hv);
+                }
+                *reinterpret_cast<uint4*>(Ks + r * LD + c8 * 8) = kv;
+                *reinterpret_cast<uint4*>(Vs + r * LD + c8 * 8) = vv;
+            }
+        }
+        __syncwarp();
+        tile_from_smem<D>(Ks, Vs, bq, 1.f, 1.f, 1.f, 1.f, tok0 + g < n_tok, tok0 + g + 8 < n_tok, st, lane);
+        __syncwarp();
+    }
+}
+
+}  // namespace tq

@@ -495,8 +495,10 @@ extern "C" int tq_debug_tc_timing(unsigned long long* host_out, int n) {
 }
 #endif
 
+namespace tq { int decode_status_host(); }   // decode_direct.cu
+
 extern "C" int tq_device_status(void) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, tc::g_status, sizeof(int)) != cudaSuccess) return -1;
-    return v;
+    return v ? v : decode_status_host();
 }
