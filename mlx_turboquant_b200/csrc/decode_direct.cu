@@ -217,8 +217,8 @@ __global__ void __launch_bounds__(NT, 1) decode_direct_kernel(DecodeParams p) {
         __syncthreads();
         DD_STAMP(9);
         // tables: slot e at LUT_BASE + e * 256: +0 32 copies of half2(kc[e & 15], kc[e >> 4]);
-        // +128 16 copies of {half2 pair for nibble e & 15, half2 pair for nibble e >> 4}, nibble n = (code A) | (code B) << 2;
-        // copies r with (r & 2) serve lanes that read the token pair in swapped order and pair (c[n >> 2], c[n & 3]) instead
+        // +128 16 copies of the value entry (two half2: one per coordinate, each pairing the two tokens); copies r with
+        // (r & 2) serve lanes that read the token pair in swapped order
         uint4* lut = reinterpret_cast<uint4*>(gp(LUT_BASE));
         for (int idx = tid; idx < 256 * 16; idx += NT) {
             const int e = idx >> 4, q = idx & 15;
@@ -228,11 +228,12 @@ __global__ void __launch_bounds__(NT, 1) decode_direct_kernel(DecodeParams p) {
                 const uint32_t u = *reinterpret_cast<const uint32_t*>(&h);
                 v = make_uint4(u, u, u, u);
             } else {
+                // entry e: low nibble = two adjacent 2-bit codes of the first word read, high nibble = the same two
+                // coordinates of the second word; tokens (A, B) = (first, second), or (second, first) for swapped copies
                 const bool sw = (q & 1) != 0;            // copies 2(q-8), 2(q-8)+1: bit 1 of the copy index is (q & 1)
-                const int n0 = e & 15, n1 = e >> 4;
-                const __half a0 = ctab[16 + (n0 & 3)], b0 = ctab[16 + (n0 >> 2)], a1 = ctab[16 + (n1 & 3)], b1 = ctab[16 + (n1 >> 2)];
-                const __half2 h0 = sw ? __halves2half2(b0, a0) : __halves2half2(a0, b0);
-                const __half2 h1 = sw ? __halves2half2(b1, a1) : __halves2half2(a1, b1);
+                const int na = sw ? e >> 4 : e & 15, nb = sw ? e & 15 : e >> 4;
+                const __half2 h0 = __halves2half2(ctab[16 + (na & 3)], ctab[16 + (nb & 3)]);      // first coordinate: (token A, token B)
+                const __half2 h1 = __halves2half2(ctab[16 + (na >> 2)], ctab[16 + (nb >> 2)]);    // second coordinate
                 const uint32_t u0 = *reinterpret_cast<const uint32_t*>(&h0), u1 = *reinterpret_cast<const uint32_t*>(&h1);
                 v = make_uint4(u0, u1, u0, u1);
             }
@@ -424,19 +425,19 @@ __global__ void __launch_bounds__(NT, 1) decode_direct_kernel(DecodeParams p) {
             for (int i = 0; i < 4; ++i) s[i] += s2[i];
             uint32_t bp[2];
             softmax_direct(s, kn0, kn1, vn0, vn1, tok0 + TILE > c_len, tok0 + g < c_len, tok0 + g + 8 < c_len, st, bp);
-            // interleave the 2-bit codes of a token pair: nibble k of X = (first word, code 2k) | (second word, code 2k) << 2
-            const uint32_t x0 = (va & 0x33333333u) | ((vb << 2) & 0xCCCCCCCCu);
-            const uint32_t y0 = ((va >> 2) & 0x33333333u) | (vb & 0xCCCCCCCCu);
-            const uint32_t x1 = (vc & 0x33333333u) | ((vd << 2) & 0xCCCCCCCCu);
-            const uint32_t y1 = ((vc >> 2) & 0x33333333u) | (vd & 0xCCCCCCCCu);
+            // pair the nibbles (two adjacent coordinates) of the two tokens: byte j of Z0 = (first word, nibble 2j) |
+            // (second word, nibble 2j) << 4, Z1 the odd nibbles.  One 64-bit lookup then yields the two operand registers
+            // that sit next to each other in the MMA (rows g and g+8 = the two coordinates, token pair in each).
+            const uint32_t z0 = (va & 0x0F0F0F0Fu) | ((vb << 4) & 0xF0F0F0F0u), z1 = ((va >> 4) & 0x0F0F0F0Fu) | (vb & 0xF0F0F0F0u);
+            const uint32_t w0 = (vc & 0x0F0F0F0Fu) | ((vd << 4) & 0xF0F0F0F0u), w1 = ((vc >> 4) & 0x0F0F0F0Fu) | (vd & 0xF0F0F0F0u);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const uint2 fa = lut64(__byte_perm(x0, c2, 0x7604 | (k << 4)));   // rows g,   tokens 2t,2t+1   -> m-tiles 2k, 2k+1
-                const uint2 fb = lut64(__byte_perm(y0, c2, 0x7604 | (k << 4)));   // rows g+8
-                const uint2 fc = lut64(__byte_perm(x1, c2, 0x7604 | (k << 4)));   // rows g,   tokens 2t+8,2t+9
-                const uint2 fd = lut64(__byte_perm(y1, c2, 0x7604 | (k << 4)));
-                mma16816(st.o[2 * k], fa.x, fb.x, fc.x, fd.x, bp[0], bp[1]);
-                mma16816(st.o[2 * k + 1], fa.y, fb.y, fc.y, fd.y, bp[0], bp[1]);
+                const uint2 e01 = lut64(__byte_perm(z0, c2, 0x7604 | (k << 4)));   // m-tile 2k:   tokens 2t, 2t+1
+                const uint2 e23 = lut64(__byte_perm(w0, c2, 0x7604 | (k << 4)));   //             tokens 2t+8, 2t+9
+                const uint2 f01 = lut64(__byte_perm(z1, c2, 0x7604 | (k << 4)));   // m-tile 2k+1
+                const uint2 f23 = lut64(__byte_perm(w1, c2, 0x7604 | (k << 4)));
+                mma16816(st.o[2 * k], e01.x, e01.y, e23.x, e23.y, bp[0], bp[1]);
+                mma16816(st.o[2 * k + 1], f01.x, f01.y, f23.x, f23.y, bp[0], bp[1]);
             }
         };
         // Up to five tiles per warp in flight; a stage is refilled (by one lane) as soon as the warp is done with it.
