@@ -156,6 +156,8 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if "WORLD_SIZE" in os.environ:      # torchrun pins OMP_NUM_THREADS to 1; this arm is a CPU job and takes the whole host
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     layers = 1
     step, info = cpu_reference_step_factory(layers)
     for _ in range(args.warmup):
@@ -320,17 +322,14 @@ def run_b200(args):
     value = world * LAYERS * BYTES_PER_LAYER_STEP / (ms_step * 1e-3) / 1e9
 
     # ---- end to end through the public API with host buffers -----------------------------------------------
-    hq = [torch.randn(1, HQ, 1, D).half().pin_memory() for _ in range(LAYERS)]
-    hk = [torch.randn(1, HKV, 1, D).half().pin_memory() for _ in range(LAYERS)]
-    hv = [torch.randn(1, HKV, 1, D).half().pin_memory() for _ in range(LAYERS)]
+    # one pinned staging buffer per layer holds the step's query, key and value heads: one host -> device copy
+    hx = [torch.randn(1, HQ + 2 * HKV, 1, D).half().pin_memory() for _ in range(LAYERS)]
     hout = [torch.empty(1, HQ, 1, D, dtype=torch.float16).pin_memory() for _ in range(LAYERS)]
     e2e_caches, _ = (caches, None)
 
     def e2e_step():
         for i in range(LAYERS):
-            q = hq[i].to(dev, non_blocking=True)
-            k = hk[i].to(dev, non_blocking=True)
-            v = hv[i].to(dev, non_blocking=True)
+            q, k, v = hx[i].to(dev, non_blocking=True).split((HQ, HKV, HKV), dim=1)
             e2e_caches[i].update(k, v)
             hout[i].copy_(e2e_caches[i].attend(q), non_blocking=True)
         torch.cuda.current_stream(dev).synchronize()

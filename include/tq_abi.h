@@ -121,6 +121,15 @@ int tq_dequantize(const tq_dequantize_args* a, void* stream);
 int tq_qk_scores(const float* q_rot, const uint8_t* packed, const float* norms, const float* centroids,
                  int bits, int d, int64_t t_q, int64_t t_kv, float* out, void* stream);
 
+/* ---- uncompressed token buffers ------------------------------------------------------------ */
+
+/* Appends t_new rows per lane to the key AND value buffers of the residual window (or the sink) in one launch:
+ * dst[(lane * dst_lane_stride + dst_row0 + r)] = src[(lane * src_lane_stride + r)], rows of row_bytes bytes
+ * (a multiple of 16; all pointers 16-byte aligned).  The slice assignments of update_and_fetch
+ * (cache.py:632-672, 577-618). */
+int tq_append_tokens(const void* k_new, const void* v_new, void* k_buf, void* v_buf, int64_t lanes, int64_t t_new,
+                     int64_t row_bytes, int64_t src_lane_stride, int64_t dst_lane_stride, int64_t dst_row0, void* stream);
+
 /* ---- decode attention over [fp16 sink | packed middle | fp16 residual] ------------------- */
 
 typedef struct {

@@ -76,6 +76,7 @@ PROTOTYPES = {
     "tq_quantize_pack": (_i, [C.POINTER(QuantizeArgs), _vp]),
     "tq_dequantize": (_i, [C.POINTER(DequantizeArgs), _vp]),
     "tq_qk_scores": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _vp, _vp]),
+    "tq_append_tokens": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _vp]),
     "tq_decode_workspace_bytes": (_sz, [_i, _i, _i, _i, _i64, _i64]),
     "tq_decode_attn": (_i, [C.POINTER(DecodeArgs), _vp]),
     "tq_decode_attn_static": (_i, [C.POINTER(DecodeArgs), _vp]),
@@ -143,5 +144,13 @@ def ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
+try:
+    _raw_stream = torch._C._cuda_getCurrentRawStream      # the stream handle as an int, without building a Stream object
+except AttributeError:                                    # pragma: no cover - older / newer torch
+    _raw_stream = None
+
+
 def stream_ptr(device: torch.device) -> int:
+    if _raw_stream is not None:
+        return _raw_stream(device.index if device.index is not None else torch.cuda.current_device())
     return torch.cuda.current_stream(device).cuda_stream

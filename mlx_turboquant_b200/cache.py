@@ -133,6 +133,8 @@ class TurboQuantKVCache:
         self._compressed_len = 0
         self._dense_k = self._dense_v = None       # lazily dequantized middle, float32
         self._dense_len = 0
+        self._dargs = self._dargs_key = self._ws_key = None     # decode argument block kept between attend() calls
+        self._ws_need = 0
         self.offset = 0
 
     # ---- constants -------------------------------------------------------------------------------
@@ -323,10 +325,29 @@ class TurboQuantKVCache:
             b, h, _, d = keys.shape
             self.sink_keys = torch.zeros((b, h, self.fp16_sink_size, d), dtype=keys.dtype, device=keys.device)
             self.sink_values = torch.zeros((b, h, self.fp16_sink_size, d), dtype=values.dtype, device=values.device)
-        self.sink_keys[:, :, self.offset:self.offset + n_sink] = keys[:, :, :n_sink]
-        self.sink_values[:, :, self.offset:self.offset + n_sink] = values[:, :, :n_sink]
+        if n_sink == t_new:
+            self._append(self.sink_keys, self.sink_values, keys, values, self.offset)
+        else:
+            self.sink_keys[:, :, self.offset:self.offset + n_sink] = keys[:, :, :n_sink]
+            self.sink_values[:, :, self.offset:self.offset + n_sink] = values[:, :, :n_sink]
         self._sink_len = self.offset + n_sink
         return keys[:, :, n_sink:], values[:, :, n_sink:]
+
+    @staticmethod
+    def _append(k_buf, v_buf, k_new, v_new, row0: int) -> None:
+        """k_buf[:, :, row0:row0+T] = k_new (same for values): one library launch when the layout allows it."""
+        t_new = k_new.shape[2]
+        if (k_new.is_contiguous() and v_new.is_contiguous() and k_new.dtype == k_buf.dtype and v_new.dtype == v_buf.dtype
+                and k_buf.dtype == v_buf.dtype and (k_buf.shape[3] * k_buf.element_size()) % 16 == 0):
+            b, h, cap, d = k_buf.shape
+            rc = _lib.lib().tq_append_tokens(k_new.data_ptr(), v_new.data_ptr(), k_buf.data_ptr(), v_buf.data_ptr(), b * h, t_new,
+                                            d * k_buf.element_size(), t_new, cap, row0, _lib.stream_ptr(k_buf.device))
+            if rc == 0:
+                return
+            if rc != -2:                      # anything but "layout not supported" is an error
+                _lib.check(rc)
+        k_buf[:, :, row0:row0 + t_new] = k_new
+        v_buf[:, :, row0:row0 + t_new] = v_new
 
     def update(self, keys: torch.Tensor, values: torch.Tensor) -> None:
         """Append new tokens (B, H, T, D) and compress what leaves the residual window.
@@ -356,8 +377,7 @@ class TurboQuantKVCache:
                 nk[:, :, :self._fp16_len] = self.keys[:, :, :self._fp16_len]
                 nv[:, :, :self._fp16_len] = self.values[:, :, :self._fp16_len]
                 self.keys, self.values, self._fp16_capacity = nk, nv, new_cap
-            self.keys[:, :, self._fp16_len:new_len] = keys_rest
-            self.values[:, :, self._fp16_len:new_len] = values_rest
+            self._append(self.keys, self.values, keys_rest, values_rest, self._fp16_len)
             self._fp16_len = new_len
         self.offset += t_total
         self._compress_old_tokens()
@@ -437,18 +457,40 @@ class TurboQuantKVCache:
             q = q.to(torch.float32)
         q = q.contiguous()
         out = torch.empty((b, hq, d), dtype=out_dtype or q.dtype, device=dev)
+        k, v = self._k, self._v
+        # Everything but the query, the result and the three lengths only changes when a buffer is (re)allocated:
+        # the filled-in argument block is kept and revalidated by the buffers' addresses.
+        key = (b, hq, q.dtype, out.dtype, scale, _lib.ptr(k.hi), _lib.ptr(v.hi), _lib.ptr(self.keys), _lib.ptr(self.sink_keys),
+               _lib.ptr(k.qbits), k.capacity(), self._fp16_capacity)
+        a = self._dargs
+        if a is None or key != self._dargs_key:
+            a = self._fill_decode_args(b, hq, q.dtype, out.dtype, scale)
+            self._dargs, self._dargs_key, self._ws_key = a, key, None
+        a.q, a.out = q.data_ptr(), out.data_ptr()
+        a.c_len, a.sink_len, a.res_len = self._compressed_len, self._sink_len, self._fp16_len
+        dense_len = self._sink_len + self._fp16_len
+        ws_key = (self._compressed_len, (dense_len + 15) >> 4)        # the split plan depends on whole 16-token tiles only
+        if ws_key != self._ws_key:
+            self._ws_need = _lib.lib().tq_decode_workspace_bytes(b, hq, a.n_kv_heads, d, self._compressed_len, ws_key[1] << 4)
+            self._ws_key = ws_key
+        ws = kernels.decode_workspace(dev, self._ws_need)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        _lib.check(_lib.lib().tq_decode_attn(C.byref(a), _lib.stream_ptr(dev)))
+        return out if squeeze else out.reshape(b, hq, 1, d)
+
+    def _fill_decode_args(self, b: int, hq: int, q_dtype, out_dtype, scale) -> "_lib.DecodeArgs":
+        d = self.head_dim
         ref = self.keys if self.keys is not None else self.sink_keys
         if ref is None:
             ref = self._k.hi
         hkv = ref.shape[1]
         a = _lib.DecodeArgs()
         a.batch, a.n_q_heads, a.n_kv_heads, a.d = b, hq, hkv, d
-        a.q, a.q_dtype = q.data_ptr(), _lib.dtype_code(q.dtype)
+        a.q_dtype = _lib.dtype_code(q_dtype)
         a.scale = float(d ** -0.5 if scale is None else scale)
         a.rot = self._rotation.data_ptr()
         k, v = self._k, self._v
-        a.c_len = self._compressed_len
-        if self._compressed_len > 0:
+        if k.hi is not None:
             a.c_lane_stride = k.hi.shape[2]
             if v.hi.shape[2] != k.hi.shape[2]:
                 raise RuntimeError("key and value packed storage have different capacities")
@@ -465,23 +507,19 @@ class TurboQuantKVCache:
                 a.k_qjl_bits, a.v_qjl_bits = _lib.ptr(k.qbits), _lib.ptr(v.qbits)
                 a.k_qjl_gamma, a.v_qjl_gamma = _lib.ptr(k.qgamma), _lib.ptr(v.qgamma)
         dense_dtype = None
-        if self._sink_len > 0:
+        if self.sink_keys is not None:
             a.sink_k, a.sink_v = self.sink_keys.data_ptr(), self.sink_values.data_ptr()
-            a.sink_len, a.sink_lane_stride = self._sink_len, self.sink_keys.shape[2]
+            a.sink_lane_stride = self.sink_keys.shape[2]
             dense_dtype = self.sink_keys.dtype
-        if self._fp16_len > 0:
+        if self.keys is not None:
             a.res_k, a.res_v = self.keys.data_ptr(), self.values.data_ptr()
-            a.res_len, a.res_lane_stride = self._fp16_len, self.keys.shape[2]
+            a.res_lane_stride = self.keys.shape[2]
             if dense_dtype is not None and dense_dtype != self.keys.dtype:
                 raise RuntimeError("sink and recent-token buffers have different dtypes")
             dense_dtype = self.keys.dtype
         a.dense_dtype = _lib.dtype_code(dense_dtype) if dense_dtype is not None else _lib.TQ_F16
-        a.out, a.out_dtype = out.data_ptr(), _lib.dtype_code(out.dtype)
-        need = _lib.lib().tq_decode_workspace_bytes(b, hq, hkv, d, self._compressed_len, self._sink_len + self._fp16_len)
-        ws = kernels.decode_workspace(dev, need)
-        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
-        _lib.check(_lib.lib().tq_decode_attn(C.byref(a), _lib.stream_ptr(dev)))
-        return out if squeeze else out.reshape(b, hq, 1, d)
+        a.out_dtype = _lib.dtype_code(out_dtype)
+        return a
 
     def make_mask(self, N: int, offset: int = 0, return_array: bool = False, window_size: int | None = None) -> Any | None:
         """``None`` for a single-token step, ``"causal"`` otherwise; sliding windows are rejected (cache.py:708-724)."""

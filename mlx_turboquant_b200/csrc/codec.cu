@@ -2,6 +2,8 @@
 //
 // pack / unpack move 32 codes per thread with 128-bit loads or stores when the buffers allow
 // it, and fall back to a one-group-per-thread kernel for ragged sizes or unaligned pointers.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace tq {
@@ -296,4 +298,43 @@ extern "C" int tq_quantize_from_rotated(const float* y, int64_t n, int d, const 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     quantize_rotated_kernel<<<blocks_for(n * (d / 8), 256), 256, 0, s>>>(y, n, d, bnd_hi, bits_hi, bnd_lo, bits_lo, packed_hi, packed_lo);
     return check_launch("tq_quantize_from_rotated");
+}
+
+// ---- append rows to the uncompressed token buffers ------------------------------------------------------
+namespace tq {
+// One launch copies the new rows of keys AND values: thread -> (tensor, lane, row, 16-byte chunk).
+__global__ void append_rows_kernel(const uint4* __restrict__ k_new, const uint4* __restrict__ v_new, uint4* __restrict__ k_buf,
+                                   uint4* __restrict__ v_buf, int64_t lanes, int64_t t_new, int chunks, int64_t src_ls, int64_t dst_ls,
+                                   int64_t dst_row0) {
+    const int64_t total = 2 * lanes * t_new * chunks;
+    for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
+        const int c = int(i % chunks);
+        int64_t r = i / chunks;
+        const int64_t row = r % t_new; r /= t_new;
+        const int64_t lane = r % lanes;
+        const bool is_v = r >= lanes;
+        const uint4* src = (is_v ? v_new : k_new) + (lane * src_ls + row) * chunks + c;
+        uint4* dst = (is_v ? v_buf : k_buf) + (lane * dst_ls + dst_row0 + row) * chunks + c;
+        *dst = __ldg(src);
+    }
+}
+}  // namespace tq
+
+extern "C" int tq_append_tokens(const void* k_new, const void* v_new, void* k_buf, void* v_buf, int64_t lanes, int64_t t_new,
+                                int64_t row_bytes, int64_t src_lane_stride, int64_t dst_lane_stride, int64_t dst_row0, void* stream) {
+    using namespace tq;
+    if (lanes < 0 || t_new < 0 || row_bytes <= 0 || dst_row0 < 0 || src_lane_stride < t_new || dst_lane_stride < dst_row0 + t_new)
+        return fail(TQ_ERR_INVALID, "tq_append_tokens: bad sizes");
+    if (lanes == 0 || t_new == 0) return TQ_OK;
+    if (!k_new || !v_new || !k_buf || !v_buf) return fail(TQ_ERR_INVALID, "tq_append_tokens: null pointer");
+    if (row_bytes % 16 || !aligned(k_new, 16) || !aligned(v_new, 16) || !aligned(k_buf, 16) || !aligned(v_buf, 16))
+        return fail(TQ_ERR_UNSUPPORTED, "tq_append_tokens: rows must be multiples of 16 bytes at 16-byte aligned addresses");
+    const int chunks = int(row_bytes / 16);
+    const int64_t total = 2 * lanes * t_new * chunks;
+    const int threads = 256;
+    const unsigned blocks = unsigned(std::min<int64_t>((total + threads - 1) / threads, 148 * 8));
+    append_rows_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(k_new), static_cast<const uint4*>(v_new), static_cast<uint4*>(k_buf), static_cast<uint4*>(v_buf),
+        lanes, t_new, chunks, src_lane_stride, dst_lane_stride, dst_row0);
+    return check_launch("tq_append_tokens");
 }

@@ -202,14 +202,14 @@ def fused_qk_scores_2bit(q_rot, packed_k, norms_k, centroids, D):
     return _fused_qk(q_rot, packed_k, norms_k, centroids, D, 2)
 
 
-_workspaces: dict[tuple[str, int], torch.Tensor] = {}
+_workspaces: dict[tuple[int | None, int], torch.Tensor] = {}
 
 
 def decode_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     """Scratch for the decode kernel, one zero-filled buffer per (device, stream), grown on demand.
 
     The kernel keeps arrival counters in it and leaves them at zero, so the buffer must start zeroed."""
-    key = (str(device), torch.cuda.current_stream(device).cuda_stream)
+    key = (device.index, _lib.stream_ptr(device))
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
