@@ -9,8 +9,8 @@
 //
 // Warp roles in a persistent CTA (one per SM, 800 threads):
 //   warps 0-15  epilogue: thread <-> one row (TMEM lane) and one quarter of the coordinates; tcgen05.ld, boundary
-//               search through a 513-bin lookup table (bin -> nearest boundary + count below it; exact, see
-//               build_bins), packing, 128-bit stores
+//               search (up to 3 bits: binary search over boundaries held in registers; 4 bits: a 513-bin lookup
+//               table, bin -> nearest boundary + count below it; both exact, see build_bins), packing, 128-bit stores
 //   warp  16    allocates TMEM, issues the MMAs (one elected thread) and commits them to mbarriers
 //   warps 17-24 producers: 128-bit global loads of the rows, sum of squares for the norm, stores into the
 //               128-byte-swizzled K-major shared-memory layout the MMA descriptors expect
@@ -152,31 +152,67 @@ constexpr uint32_t IDESC = (1u << 4) | (uint32_t(D >> 3) << 17) | (uint32_t(TM >
 // Lookup table for the boundary search.  Bin k covers normalised values around (k - 256) / 256 (width 1/256);
 // entry = (boundary to test, number of boundaries below the bin's neighbourhood) where the neighbourhood is the
 // bin widened by one bin on each side, so that a bin index that is off by one through rounding still gives the
-// exact count.  A neighbourhood holding two boundaries is marked (NaN) and handled by the plain counting loop.
+// exact count.  A neighbourhood holding two boundaries is marked (a flag bit in the count) and handled by the plain
+// counting loop.
+constexpr int MARKED = 0x100;
+#ifndef TQ_DIRECT_MAX_BITS
+#define TQ_DIRECT_MAX_BITS 3
+#endif
+constexpr int DIRECT_MAX_BITS = TQ_DIRECT_MAX_BITS;   // up to this width the boundaries are searched in registers, above it through the
+                                                      // bin table (at 4 bits the register search costs more issue slots than the table's bank conflicts)
 __device__ void build_bins(float2* bins, const float* bnd, int n_bnd, int tid, int nthreads) {
     for (int k = tid; k < NBINS; k += nthreads) {
         const float lo = (float(k) - 256.f - 1.5f) / 256.f, hi = (float(k) - 256.f + 1.5f) / 256.f;
         int below = 0, inside = 0;
-        float b_in = INFINITY;
+        float b_in = 2.0f;                    // no boundary near this bin: |y| <= 1 never exceeds the sentinel
         for (int i = 0; i < n_bnd; ++i) {
             const float b = bnd[i];
             if (b < lo) ++below;
             else if (b <= hi) { ++inside; b_in = b; }
         }
-        const float2 e = make_float2(inside > 1 ? __int_as_float(0x7fc00000) : b_in, __int_as_float(below));
+        const float2 e = make_float2(b_in, __int_as_float(inside > 1 ? (below | MARKED) : below));
 #pragma unroll
         for (int r = 0; r < BIN_REP; ++r) bins[k * BIN_REP + r] = e;
     }
 }
 
-// Fast path of the boundary search: one table lookup and one compare.  `slow` is raised when the bin is marked.
-__device__ __forceinline__ uint32_t code_of(float yp, float rinv, float rbin, const float2* bins, bool& slow) {
-    // bin index from the mantissa of (y * 256 + 256 + 2^23): exact rounding to nearest, no convert instruction
+// Fast path of the boundary search: one table lookup and one compare.  The counts looked up are OR-ed into `seen`;
+// if the flag bit of a marked bin shows up there the group is redone with the counting loop.
+__device__ __forceinline__ uint32_t code_of(float yp, float rinv, float rbin, const float2* bins, uint32_t& seen) {
+    // bin index from the mantissa of (y * 256 + 256 + 2^23): exact rounding to nearest, no convert instruction.
+    // |y| <= 1 keeps the index below 513; NaN and infinity give index 0 (ten low mantissa bits are zero).
     const float tt = fmaf(yp, rbin, 8388608.f + 256.f);
-    const uint32_t k = min(__float_as_uint(tt) & 0x3FFu, uint32_t(NBINS - 1));
+    const uint32_t k = __float_as_uint(tt) & 0x3FFu;
     const float2 e = bins[k * BIN_REP];
-    slow |= (e.x != e.x);
+    seen |= __float_as_uint(e.y);
     return __float_as_uint(e.y) + ((yp * rinv) > e.x ? 1u : 0u);     // strict >, codebook.py:220-223
+}
+// Up to three bits: the boundaries live in registers and a binary search (one compare per bit) counts how many the
+// value exceeds - the same number the counting loop gives for a non-decreasing boundary list, NaN included (0).
+template <int BITS>
+__device__ __forceinline__ uint32_t code_direct(float y, const float (&b)[15]) {
+    if (BITS == 4) {
+        const bool p1 = y > b[7];
+        const bool p2 = y > (p1 ? b[11] : b[3]);
+        const float l2 = p2 ? b[5] : b[1], h2 = p2 ? b[13] : b[9];
+        const bool p3 = y > (p1 ? h2 : l2);
+        // fourth level: boundary 8 p1 + 4 p2 + 2 p3
+        const float c0 = p3 ? b[2] : b[0], c1 = p3 ? b[6] : b[4], c2 = p3 ? b[10] : b[8], c3 = p3 ? b[14] : b[12];
+        const float d0 = p2 ? c1 : c0, d1 = p2 ? c3 : c2;
+        const bool p4 = y > (p1 ? d1 : d0);
+        return (p1 ? 8u : 0u) + (p2 ? 4u : 0u) + (p3 ? 2u : 0u) + (p4 ? 1u : 0u);
+    }
+    if (BITS == 1) return y > b[0] ? 1u : 0u;
+    if (BITS == 2) {
+        const bool p1 = y > b[1];
+        const bool p2 = y > (p1 ? b[2] : b[0]);
+        return (p1 ? 2u : 0u) + (p2 ? 1u : 0u);
+    }
+    const bool p1 = y > b[3];
+    const bool p2 = y > (p1 ? b[5] : b[1]);
+    const float lo = p2 ? b[2] : b[0], hi = p2 ? b[6] : b[4];
+    const bool p3 = y > (p1 ? hi : lo);
+    return (p1 ? 4u : 0u) + (p2 ? 2u : 0u) + (p3 ? 1u : 0u);
 }
 // Plain counting loop, kept out of line: only reached when two boundaries share a bin neighbourhood.
 __device__ __noinline__ uint32_t code_slow(float y, const float* raw_bnd, int n_bnd) {
@@ -199,6 +235,13 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
     const float* raw_bnd = reinterpret_cast<const float*>(e.smem + OFF_BND) + (second ? 16 : 0);
     constexpr int n_bnd = (1 << BITS) - 1;
     constexpr int WBYTES = 32 * BITS / 8;                       // bytes this thread produces per row (32 coordinates)
+    float bnd[15];
+#pragma unroll
+    for (int i = 0; i < 15; ++i) bnd[i] = raw_bnd[i < n_bnd ? i : 0];
+    // the tile stride in (lane, row) form
+    const int64_t stride_rows = int64_t(gridDim.x) * TM;
+    const int64_t step_o = stride_rows / p.n_rows, step_r = stride_rows - step_o * p.n_rows;
+    int64_t lane_o = 0, lane_r = 0;
     int it = 0;
     for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
         const int a = it % ACC_STAGES, s = it % A_STAGES;
@@ -215,9 +258,12 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
         const bool live = row < e.total_rows;
         int64_t orow = 0;
         if (live) {
-            const int64_t o = row / p.n_rows, r = row - o * p.n_rows;
-            orow = o * p.out_lane_stride + r;
+            // lane (cache row o) and row inside it: one division at the start, then advanced by the grid stride
+            if (it == 0) { lane_o = row / p.n_rows; lane_r = row - lane_o * p.n_rows; }
+            orow = lane_o * p.out_lane_stride + lane_r;
             if (quarter == 0) p.norms[orow] = nrm;
+            lane_r += step_r; lane_o += step_o;
+            if (lane_r >= p.n_rows) { lane_r -= p.n_rows; ++lane_o; }
         }
         const uint32_t t_hi = e.tmem_base + (uint32_t(quad * 32) << 16) + a * 256 + quarter * 32;
         uint32_t words[4];                                      // 32 codes x at most 4 bits
@@ -229,16 +275,24 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
             tmem_ld16(t_hi + cb * 16, vh);
             tmem_ld16(t_hi + 128 + cb * 16, vl);
             tmem_ld_wait();
-            bool slow = false;
+            if (BITS <= DIRECT_MAX_BITS) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float yp = fmaf(__uint_as_float(vl[i]), 1.f / 2048.f, __uint_as_float(vh[i]));
-                vh[i] = __float_as_uint(yp);
-                vl[i] = code_of(yp, rinv, rbin, bins, slow);
-            }
-            if (__any_sync(0xffffffffu, slow)) {                // never taken with the shipped codebooks
+                for (int i = 0; i < 16; ++i) {
+                    const float yp = fmaf(__uint_as_float(vl[i]), 1.f / 2048.f, __uint_as_float(vh[i]));
+                    vl[i] = code_direct<BITS>(yp * rinv, bnd);
+                }
+            } else {
+                uint32_t seen = 0;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) vl[i] = code_slow(__uint_as_float(vh[i]) * rinv, raw_bnd, n_bnd);
+                for (int i = 0; i < 16; ++i) {
+                    const float yp = fmaf(__uint_as_float(vl[i]), 1.f / 2048.f, __uint_as_float(vh[i]));
+                    vh[i] = __float_as_uint(yp);
+                    vl[i] = code_of(yp, rinv, rbin, bins, seen);
+                }
+                if (__any_sync(0xffffffffu, (seen & MARKED) != 0)) {     // never taken with the shipped codebooks
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) vl[i] = code_slow(__uint_as_float(vh[i]) * rinv, raw_bnd, n_bnd);
+                }
             }
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
@@ -387,6 +441,12 @@ __global__ void __launch_bounds__(NT, 1) quantize_tc_kernel(Params p) {
         const int pt = tid - (N_EPI + 32);
         const int pw = pt >> 5, chunk = lane & 15, rsub = lane >> 4;
         const int kblk = chunk >> 3, cc = chunk & 7;
+        // (lane, row) of this thread's first row of the tile, advanced by the grid stride: no 64-bit division per row
+        const bool wide = p.n_rows >= TM;            // a tile then spans at most two lanes
+        const int64_t stride_rows = int64_t(gridDim.x) * TM;
+        const int64_t step_o = stride_rows / p.n_rows, step_r = stride_rows - step_o * p.n_rows;
+        int64_t base_o = (int64_t(blockIdx.x) * TM + pw * 16 + rsub) / p.n_rows;
+        int64_t base_r = (int64_t(blockIdx.x) * TM + pw * 16 + rsub) - base_o * p.n_rows;
         int it = 0;
         for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
             const int s = it % A_STAGES;
@@ -396,10 +456,18 @@ __global__ void __launch_bounds__(NT, 1) quantize_tc_kernel(Params p) {
                 const int64_t row = tile * TM + pw * 16 + i * 2 + rsub;
                 v[i] = make_uint4(0, 0, 0, 0);
                 if (row < total_rows) {
-                    const int64_t o = row / p.n_rows, rr = row - o * p.n_rows;
+                    int64_t o, rr;
+                    if (wide) {
+                        o = base_o; rr = base_r + i * 2;
+                        if (rr >= p.n_rows) { rr -= p.n_rows; ++o; }
+                    } else {
+                        o = row / p.n_rows; rr = row - o * p.n_rows;
+                    }
                     v[i] = __ldg(reinterpret_cast<const uint4*>(p.x + o * p.x_lane_stride + rr * p.x_row_stride) + chunk);
                 }
             }
+            base_r += step_r; base_o += step_o;
+            if (base_r >= p.n_rows) { base_r -= p.n_rows; ++base_o; }
             TC_STAMP(pt == 0, 0, it, 0);
             float ss[8];
 #pragma unroll
