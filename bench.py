@@ -250,6 +250,45 @@ def bench_quantize(torch, dev, steps, warmup, peak, pool_size=8):
     return out
 
 
+def bench_c3(torch, dev, steps, warmup, peak):
+    """Phi-3.5-mini-shaped layer with the QJL sketch: 32 query = 32 KV heads, head_dim 96, batch 16, context 8192 =
+    128 sink + 7936 packed (4-bit keys, 2-bit values, sign sketches) + 128 recent.  One launch = one layer-step;
+    four layer caches (1.8 GB) are cycled."""
+    from mlx_turboquant_b200 import TurboQuantKVCache
+    b, h, d, ctx = 16, 32, 96, 8192
+    t_c = ctx - SINK - RW
+    bytes_step = b * h * t_c * (d // 2 + 4 + d // 4 + 4 + 2 * (4 + 4)) + b * h * (SINK + RW) * 2 * d * 2 + b * h * d * 4
+    caches, qs = [], []
+    for li in range(4):
+        g = torch.Generator(device=dev).manual_seed(3000 + li)
+        k = (torch.randn(b, h, ctx, d, device=dev, generator=g) * torch.exp(0.5 * torch.randn(b, h, ctx, 1, device=dev, generator=g))).half()
+        v = (torch.randn(b, h, ctx, d, device=dev, generator=g) * torch.exp(0.5 * torch.randn(b, h, ctx, 1, device=dev, generator=g))).half()
+        c = TurboQuantKVCache(head_dim=d, num_kv_heads=h, key_bits=4, value_bits=2, residual_window=RW, fp16_sink_size=SINK,
+                              qjl_correction=True)
+        c.update(k, v)
+        assert (c._sink_len, c._compressed_len, c._fp16_len) == (SINK, t_c, RW)
+        caches.append(c)
+        qs.append((torch.randn(b, h, 1, d, device=dev, generator=g) / d ** 0.5).half())
+        del k, v
+    def step():
+        for c, q in zip(caches, qs):
+            c.attend(q)
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    us = e0.elapsed_time(e1) * 1e3 / (steps * len(caches))
+    gbs = bytes_step / (us * 1e-6) / 1e9
+    return {"workload": "phi35mini_layer_decode_attn_b16_ctx8192_k4v2_qjl_sink128_rw128", "us_per_layer_step": us,
+            "algorithmic_bytes_per_launch": bytes_step, "hbm_gbs": gbs, "frac_of_peak": gbs / peak,
+            "kernel": "decode_attn_kernel<96, qjl> (general kernel: unpack to shared memory, ldmatrix)"}
+
+
 def run_b200(args):
     import torch
     import torch.distributed as dist
@@ -368,6 +407,7 @@ def run_b200(args):
     if rank == 0 and world == 1 and not args.no_secondary:
         line["secondary"] = {"metric": "quantize_pack_mtokens_per_s", "unit": "Mtokens/s (token = position x 8 KV heads x 32 layers)",
                              "chunk_tokens": QCHUNK, **bench_quantize(torch, dev, 3, 3, peak, args.quantize_pool)}
+        line["secondary"]["decode_qjl_d96_b16"] = bench_c3(torch, dev, 5, 3, peak)
     if rank == 0 and world == 1 and not args.no_cpu:
         step, info = cpu_reference_step_factory(1)
         step()

@@ -146,7 +146,9 @@ typedef struct {
     /* The kernel holds value centroids in fp16; a table-wide scale from tq_fp16_table_scale() applied
      * before the cast (and divided out of the result) keeps that rounding below 1e-4. 0 = no scaling. */
     float v_cent_scale_hi, v_cent_scale_lo;
-    /* optional QJL sketches of the K and V residuals (m == 32); qjl_proj is S (m, d) */
+    /* optional QJL sketches of the K and V residuals (m == 32); qjl_proj is S (m, d).  All five or none: the
+     * scores gain (sqrt(pi/2)/d) gamma_k sign_k.(S q), the output (sqrt(pi/2)/d) (sum_t p_t gamma_v sign_v) @ S,
+     * which is attention over the reference's corrected dense K / V (cache.py:396-427, qjl.py:70-94). */
     const float* qjl_proj;
     const uint32_t *k_qjl_bits, *v_qjl_bits; const float *k_qjl_gamma, *v_qjl_gamma;
     /* uncompressed regions, (lanes, cap, d) of dense_dtype; *_len valid tokens */

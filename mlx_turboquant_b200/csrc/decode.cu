@@ -38,8 +38,10 @@ constexpr int GNW = 8;                 // warps per CTA of the general kernel
 // After BODY: float query [8][D], fp16 query [8][D], four 16-entry fp16 centroid tables, a few scalars.
 constexpr int MERGE_CPARTS = 4;       // thread slabs of the d x d product with R in the epilogue
 template <int D, int NW> __host__ __device__ constexpr size_t stage_bytes() { return size_t(NW) * 2 * TILE * stage_ld<D>() * sizeof(__half); }
+constexpr int QM = 32;                // QJL projections per sketch (one 32-bit sign word per token)
+constexpr float QJL_C = 1.2533141373155003f;   // sqrt(pi / 2), qjl.py:91-92
 template <int D, int NW> __host__ __device__ constexpr size_t reduce_bytes() {
-    return size_t(NW) * (HPG * (D + 2) + 2 * HPG) * sizeof(float) + size_t(NW) * HPG * sizeof(float) + size_t(HPG) * D * sizeof(float) +
+    return size_t(NW) * (HPG * (D + 2) + 2 * HPG + HPG * QM) * sizeof(float) + size_t(HPG) * QM * sizeof(float) + size_t(NW) * HPG * sizeof(float) + size_t(HPG) * D * sizeof(float) +
            size_t(MERGE_CPARTS) * HPG * D * sizeof(float);
 }
 template <int D> __host__ __device__ constexpr size_t merge_bytes() { return size_t(HPG) * MAX_SPLITS * sizeof(float2); }
@@ -50,11 +52,20 @@ template <int D> __host__ __device__ constexpr size_t body_bytes() {
     return (s + 15) / 16 * 16;
 }
 template <int D> __host__ __device__ constexpr size_t tail_bytes() {
-    return size_t(HPG) * D * sizeof(float) + size_t(HPG) * D * sizeof(__half) + 64 * sizeof(__half) + 16 * sizeof(float);
+    return size_t(HPG) * D * sizeof(float) + size_t(HPG) * D * sizeof(__half) + 64 * sizeof(__half) + 16 * sizeof(float) +
+           size_t(HPG) * QM * sizeof(__half);
 }
 template <int D> __host__ __device__ constexpr size_t kernel_smem() { return body_bytes<D>() + tail_bytes<D>(); }
 
-template <int D>
+// half2 of two signs (+1 for a set bit, -1 otherwise) from bit 0 of a and bit 0 of b
+__device__ __forceinline__ uint32_t sign_pair(uint32_t a, uint32_t b) { return 0xBC00BC00u ^ ((a & 1u) << 15) ^ ((b & 1u) << 31); }
+
+// QJL: the cache also keeps, per packed token, the signs of 32 random projections S r of the quantization residual r
+// and its norm gamma; the reference adds  (sqrt(pi/2) / d) * gamma * (signs @ S)  to the dequantized vector
+// (cache.py:396-427, qjl.py:70-94).  In attention that is
+//   scores:  += (c/d) gamma_k[t] * sum_p sign_p(t) (S q)[p]            -> one more small MMA on +-1 operands
+//   output:  += (c/d) (sum_t p_t gamma_v[t] signs(t)) @ S               -> 32 more accumulator rows, applied at the end
+template <int D, bool QJL>
 __global__ void __launch_bounds__(GNW * 32, 1) decode_attn_kernel(DecodeParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int NW = GNW, NT = NW * 32;
@@ -64,6 +75,7 @@ __global__ void __launch_bounds__(GNW * 32, 1) decode_attn_kernel(DecodeParams p
     __half* qs = reinterpret_cast<__half*>(qf + HPG * D);                    // [8][D] scaled fp16 query (rotated or raw)
     __half* ctab = qs + HPG * D;                                             // kc_hi, kc_lo, vc_hi, vc_lo (16 each)
     float* s_misc = reinterpret_cast<float*>(ctab + 64);                     // [0..7] 1/L per head, [8] last-CTA flag
+    __half* us = reinterpret_cast<__half*>(s_misc + 16);                     // [8][32] fp16 (S q) * scale * log2(e)  (QJL)
 
     pdl_trigger();     // the next launch on the stream may become resident and run its own prologue
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
@@ -136,6 +148,15 @@ __global__ void __launch_bounds__(GNW * 32, 1) decode_attn_kernel(DecodeParams p
                 }
             }
         }
+        if (QJL && !dense) {
+            // (S q)[h][p] for the unrotated query, already in the log2 domain; thread (h, p)
+            const int h = tid >> 5, pp = tid & 31;
+            float acc = 0.f;
+            if (h < heads_here) {
+                for (int k = 0; k < D; ++k) acc = fmaf(qf[h * D + k], __ldg(p.qjl_proj + pp * D + k), acc);
+            }
+            us[h * QM + pp] = __float2half_rn(acc * f);
+        }
     }
     __syncthreads();
 
@@ -153,6 +174,14 @@ __global__ void __launch_bounds__(GNW * 32, 1) decode_attn_kernel(DecodeParams p
             bq[ks][0] = g < heads_here ? *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * t) : 0u;
             bq[ks][1] = g < heads_here ? *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * t + 8) : 0u;
         }
+    }
+    uint32_t bu[QM / 16][2];          // (S q) fragments, B operand: k = sketch index, n = head
+    float zacc[QM / 16][4];           // sketch rows of the output, this warp's share
+#pragma unroll
+    for (int ks = 0; ks < QM / 16; ++ks) {
+        bu[ks][0] = (QJL && g < heads_here) ? *reinterpret_cast<const uint32_t*>(us + g * QM + ks * 16 + 2 * t) : 0u;
+        bu[ks][1] = (QJL && g < heads_here) ? *reinterpret_cast<const uint32_t*>(us + g * QM + ks * 16 + 2 * t + 8) : 0u;
+        zacc[ks][0] = zacc[ks][1] = zacc[ks][2] = zacc[ks][3] = 0.f;
     }
     __half* Ks = reinterpret_cast<__half*>(smem) + size_t(warp) * 2 * TILE * LD;
     __half* Vs = Ks + TILE * LD;
@@ -198,7 +227,60 @@ __global__ void __launch_bounds__(GNW * 32, 1) decode_attn_kernel(DecodeParams p
             const float kn0 = __ldg(p.k_norms + n0), kn1 = __ldg(p.k_norms + n1);
             const float vn0 = __ldg(p.v_norms + n0), vn1 = __ldg(p.v_norms + n1);
             __syncwarp();
-            tile_from_smem<D>(Ks, Vs, bq, kn0, kn1, vn0, vn1, ok0, ok1, st, lane);
+            if (!QJL) {
+                tile_from_smem<D>(Ks, Vs, bq, kn0, kn1, vn0, vn1, ok0, ok1, st, lane);
+            } else {
+                // scores: MSE part scaled by the key norm plus the sketch part scaled by (c/d) gamma
+                float s[4] = {0.f, 0.f, 0.f, 0.f}, sq[4] = {0.f, 0.f, 0.f, 0.f};
+                {
+                    const __half* base = Ks + (lane & 15) * LD + (lane >> 4) * 8;
+#pragma unroll
+                    for (int ks = 0; ks < D / 16; ++ks) {
+                        uint32_t a[4];
+                        ldsm_x4(a, base + ks * 16);
+                        mma16816(s, a[0], a[1], a[2], a[3], bq[ks][0], bq[ks][1]);
+                    }
+                }
+                const uint32_t zk0 = ok0 ? __ldg(p.k_qbits + n0) : 0u, zk1 = ok1 ? __ldg(p.k_qbits + n1) : 0u;
+                const float gk0 = ok0 ? __ldg(p.k_qgamma + n0) * (QJL_C / D) : 0.f, gk1 = ok1 ? __ldg(p.k_qgamma + n1) * (QJL_C / D) : 0.f;
+#pragma unroll
+                for (int ks = 0; ks < QM / 16; ++ks) {
+                    const int sh = ks * 16 + 2 * t;
+                    mma16816(sq, sign_pair(zk0 >> sh, zk0 >> (sh + 1)), sign_pair(zk1 >> sh, zk1 >> (sh + 1)),
+                             sign_pair(zk0 >> (sh + 8), zk0 >> (sh + 9)), sign_pair(zk1 >> (sh + 8), zk1 >> (sh + 9)), bu[ks][0], bu[ks][1]);
+                }
+                s[0] = fmaf(s[0], kn0, sq[0] * gk0); s[1] = fmaf(s[1], kn0, sq[1] * gk0);
+                s[2] = fmaf(s[2], kn1, sq[2] * gk1); s[3] = fmaf(s[3], kn1, sq[3] * gk1);
+                uint32_t bp[2];
+                float pr[4];
+                softmax_step<D>(s, 1.f, 1.f, vn0, vn1, ok0, ok1, st, bp, pr);
+                {
+                    const __half* base = Vs + ((lane & 7) + ((lane >> 4) & 1) * 8) * LD + ((lane >> 3) & 1) * 8;
+#pragma unroll
+                    for (int mt = 0; mt < D / 16; ++mt) {
+                        uint32_t a[4];
+                        ldsm_x4_t(a, base + mt * 16);
+                        mma16816(st.o[mt], a[0], a[1], a[2], a[3], bp[0], bp[1]);
+                    }
+                }
+                // sketch rows of the output: z[p][h] += sum_t sign_p(t) * (p_t * gamma_v[t]); P^T operand as for the values
+                const float gv0 = ok0 ? __ldg(p.v_qgamma + n0) : 0.f, gv1 = ok1 ? __ldg(p.v_qgamma + n1) : 0.f;
+                const uint32_t bz0 = movm_t(pack_h2(fminf(pr[0] * gv0, 65504.f), fminf(pr[1] * gv0, 65504.f)));
+                const uint32_t bz1 = movm_t(pack_h2(fminf(pr[2] * gv1, 65504.f), fminf(pr[3] * gv1, 65504.f)));
+                const int64_t nb = kvl * p.c_ls + tok0;
+                uint32_t zv[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int tk = 2 * t + (u & 1) + (u >> 1) * 8;                    // tokens 2t, 2t+1, 2t+8, 2t+9
+                    zv[u] = tok0 + tk < p.c_len ? __ldg(p.v_qbits + nb + tk) : 0u;
+                }
+#pragma unroll
+                for (int mt = 0; mt < QM / 16; ++mt) {
+                    const int r0 = mt * 16 + g;                                         // sketch rows r0 and r0 + 8
+                    mma16816(zacc[mt], sign_pair(zv[0] >> r0, zv[1] >> r0), sign_pair(zv[0] >> (r0 + 8), zv[1] >> (r0 + 8)),
+                             sign_pair(zv[2] >> r0, zv[3] >> r0), sign_pair(zv[2] >> (r0 + 8), zv[3] >> (r0 + 8)), bz0, bz1);
+                }
+            }
             __syncwarp();
         }
     }
@@ -211,10 +293,11 @@ __global__ void __launch_bounds__(GNW * 32, 1) decode_attn_kernel(DecodeParams p
     }
     __syncthreads();   // staging / tables / ring are dead from here on
     constexpr int DS = D + 2;                               // row stride (floats): keeps the 64-bit stores below 2-way conflicts
-    constexpr int RW = HPG * DS + 2 * HPG;                  // floats per warp in the reduction buffer
+    constexpr int RW = HPG * DS + 2 * HPG + HPG * QM;       // floats per warp in the reduction buffer: o, (m, l), sketch rows
     float* red = reinterpret_cast<float*>(smem);
     float* wts = red + size_t(NW) * RW;                     // [NW][8] per-warp weights exp2(m_w - M)
-    float* s_acc = wts + NW * HPG;                          // [8][D] reduced accumulator of this CTA
+    float* s_z = wts + NW * HPG;                            // [8][32] reduced sketch rows of this CTA
+    float* s_acc = s_z + HPG * QM;                          // [8][D] reduced accumulator of this CTA
     float* s_pp = s_acc + HPG * D;                          // [MERGE_CPARTS][8][D] partial products with R
     {
         float* ro = red + size_t(warp) * RW;                // [8][DS]: head-major
@@ -230,6 +313,14 @@ __global__ void __launch_bounds__(GNW * 32, 1) decode_attn_kernel(DecodeParams p
         if (g == 0) {
             rm[2 * t] = st.m[0]; rm[2 * t + 1] = st.m[1];
             rm[HPG + 2 * t] = st.l[0]; rm[HPG + 2 * t + 1] = st.l[1];
+        }
+        if (QJL) {
+            float* rz = rm + 2 * HPG;                        // [8 heads][32 sketch rows]
+#pragma unroll
+            for (int mt = 0; mt < QM / 16; ++mt) {
+                rz[(2 * t) * QM + mt * 16 + g] = zacc[mt][0]; rz[(2 * t + 1) * QM + mt * 16 + g] = zacc[mt][1];
+                rz[(2 * t) * QM + mt * 16 + g + 8] = zacc[mt][2]; rz[(2 * t + 1) * QM + mt * 16 + g + 8] = zacc[mt][3];
+            }
         }
     }
     __syncthreads();
@@ -262,6 +353,13 @@ __global__ void __launch_bounds__(GNW * 32, 1) decode_attn_kernel(DecodeParams p
         for (int x = 0; x < NW; ++x) acc = fmaf(wts[x * HPG + h], red[size_t(x) * RW + h * DS + c], acc);
         if (dense) po[e] = acc;                              // uncompressed tokens were never rotated
         else s_acc[e] = acc / (c < v_half ? p.v_scale_hi : p.v_scale_lo);
+    }
+    if (QJL && !dense && tid < HPG * QM) {
+        const int h = tid / QM, pp = tid - h * QM;
+        float acc = 0.f;
+#pragma unroll
+        for (int x = 0; x < NW; ++x) acc = fmaf(wts[x * HPG + h], red[size_t(x) * RW + HPG * DS + 2 * HPG + h * QM + pp], acc);
+        s_z[tid] = acc * (QJL_C / D);
     }
     if (!dense) {
         // Packed tokens were accumulated in rotated space: undo the rotation here, once per CTA
@@ -299,6 +397,10 @@ __global__ void __launch_bounds__(GNW * 32, 1) decode_attn_kernel(DecodeParams p
             float v = 0.f;
 #pragma unroll
             for (int x = 0; x < MERGE_CPARTS; ++x) v += s_pp[(x * HPG + h) * D + j];
+            if (QJL) {                                       // (c/d) * z @ S, in unrotated space (qjl.py:89-92)
+#pragma unroll 8
+                for (int pp = 0; pp < QM; ++pp) v = fmaf(s_z[h * QM + pp], __ldg(p.qjl_proj + pp * D + j), v);
+            }
             po[e] = v;
         }
     }
@@ -424,13 +526,13 @@ static WsLayout ws_layout(int batch, int n_q_heads, int n_kv_heads, int d, const
     return w;
 }
 
-template <int D> static int launch_decode(const DecodeParams& p, cudaStream_t s) {
+template <int D, bool QJL> static int launch_decode(const DecodeParams& p, cudaStream_t s) {
     constexpr size_t smem = kernel_smem<D>();
     static bool set[16] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 16 && !set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(decode_attn_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        cudaError_t e = cudaFuncSetAttribute(decode_attn_kernel<D, QJL>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_decode_attn: shared memory %zu B: %s", smem, cudaGetErrorString(e));
         set[dev] = true;
     }
@@ -446,7 +548,7 @@ template <int D> static int launch_decode(const DecodeParams& p, cudaStream_t s)
     attr[0].val.programmaticStreamSerializationAllowed = g_tune_pdl ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_attn_kernel<D>, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_attn_kernel<D, QJL>, p);
     if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_decode_attn: %s", cudaGetErrorString(e));
     return TQ_OK;
 }
@@ -472,7 +574,10 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
             (a->v_bits_lo && (!a->v_lo || !a->v_cent_lo)))
             return fail(TQ_ERR_INVALID, "tq_decode_attn: null packed-cache pointer");
         if (a->c_lane_stride < a->c_len) return fail(TQ_ERR_INVALID, "tq_decode_attn: c_lane_stride < c_len");
-        if (a->k_qjl_bits || a->v_qjl_bits) return fail(TQ_ERR_UNSUPPORTED, "tq_decode_attn: QJL sketches are not supported by this build");
+        if (a->k_qjl_bits || a->v_qjl_bits || a->k_qjl_gamma || a->v_qjl_gamma) {
+            if (!a->k_qjl_bits || !a->v_qjl_bits || !a->k_qjl_gamma || !a->v_qjl_gamma || !a->qjl_proj)
+                return fail(TQ_ERR_INVALID, "tq_decode_attn: QJL needs the projection matrix and both sides' sign words and residual norms");
+        }
     }
     if ((a->sink_len > 0 && (!a->sink_k || !a->sink_v || a->sink_lane_stride < a->sink_len)) ||
         (a->res_len > 0 && (!a->res_k || !a->res_v || a->res_lane_stride < a->res_len)))
@@ -485,7 +590,7 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
     const int64_t dense_len = a->sink_len + a->res_len;
     // direct path: 4-bit keys / 2-bit values, d = 128, rows and norms addressable in aligned 16-byte chunks
     const bool direct = !g_tune_force_general && d == 128 && a->c_len > 0 && a->k_bits_hi == 4 && a->k_bits_lo == 0 &&
-                        a->v_bits_hi == 2 && a->v_bits_lo == 0 && aligned(a->k_hi, 16) && aligned(a->v_hi, 16) &&
+                        a->v_bits_hi == 2 && a->v_bits_lo == 0 && !a->k_qjl_bits && aligned(a->k_hi, 16) && aligned(a->v_hi, 16) &&
                         aligned(a->k_norms, 16) && aligned(a->v_norms, 16) && a->c_lane_stride % 16 == 0 && direct_supported();
     const SplitPlan sp = plan_splits(a->batch, a->n_q_heads, a->n_kv_heads, a->c_len, dense_len, sm_count(), direct);
     const WsLayout wl = ws_layout(a->batch, a->n_q_heads, a->n_kv_heads, d, sp);
@@ -500,6 +605,9 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
     p.k_norms = a->k_norms; p.v_norms = a->v_norms;
     p.kc_hi = a->k_cent_hi; p.kc_lo = a->k_cent_lo; p.vc_hi = a->v_cent_hi; p.vc_lo = a->v_cent_lo;
     p.dense_dtype = a->dense_dtype;
+    if (a->c_len > 0 && a->k_qjl_bits) {
+        p.qjl_proj = a->qjl_proj; p.k_qbits = a->k_qjl_bits; p.v_qbits = a->v_qjl_bits; p.k_qgamma = a->k_qjl_gamma; p.v_qgamma = a->v_qjl_gamma;
+    }
     p.sink_k = a->sink_k; p.sink_v = a->sink_v; p.res_k = a->res_k; p.res_v = a->res_v;
     p.sink_len = a->sink_len; p.sink_ls = a->sink_lane_stride; p.res_len = a->res_len; p.res_ls = a->res_lane_stride;
     p.n_ps = sp.n_ps; p.n_ds = sp.n_ds; p.p_tps = sp.p_tps; p.d_tps = sp.d_tps;
@@ -524,10 +632,11 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
 
 int decode_launch(const DecodeParams& p, bool direct, cudaStream_t s) {
     if (direct) return launch_decode_direct(p, s);
-    if (p.D == 64) return launch_decode<64>(p, s);
-    if (p.D == 96) return launch_decode<96>(p, s);
-    if (p.D == 128) return launch_decode<128>(p, s);
-    return launch_decode<256>(p, s);
+    const bool qjl = p.qjl_proj != nullptr;
+    if (p.D == 64) return qjl ? launch_decode<64, true>(p, s) : launch_decode<64, false>(p, s);
+    if (p.D == 96) return qjl ? launch_decode<96, true>(p, s) : launch_decode<96, false>(p, s);
+    if (p.D == 128) return qjl ? launch_decode<128, true>(p, s) : launch_decode<128, false>(p, s);
+    return qjl ? launch_decode<256, true>(p, s) : launch_decode<256, false>(p, s);
 }
 
 }  // namespace tq

@@ -19,6 +19,9 @@ struct DecodeParams {
     const uint8_t *k_hi, *k_lo, *v_hi, *v_lo;
     const float *k_norms, *v_norms;
     const float *kc_hi, *kc_lo, *vc_hi, *vc_lo;
+    const float* qjl_proj;             // S (32, D), or null: no QJL sketches
+    const uint32_t *k_qbits, *v_qbits; // sign words of the residual sketches, one per packed token
+    const float *k_qgamma, *v_qgamma;  // residual norms
     int dense_dtype;
     const void *sink_k, *sink_v, *res_k, *res_v;
     int64_t sink_len, sink_ls, res_len, res_ls;

@@ -83,7 +83,7 @@ template <int D> struct WarpAcc {
 // keeps exp2(s - m) inside the fp16 range is exact.
 template <int D>
 __device__ __forceinline__ void softmax_step(float (&s)[4], float kn0, float kn1, float vn0, float vn1, bool ok0,
-                                             bool ok1, WarpAcc<D>& st, uint32_t (&bp)[2]) {
+                                             bool ok1, WarpAcc<D>& st, uint32_t (&bp)[2], float* p_out = nullptr) {
     s[0] = ok0 ? s[0] * kn0 : -INFINITY;
     s[1] = ok0 ? s[1] * kn0 : -INFINITY;
     s[2] = ok1 ? s[2] * kn1 : -INFINITY;
@@ -108,6 +108,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[4], float kn0, float kn1
     const float p0 = ex2(s[0] - st.m[0]), p1 = ex2(s[1] - st.m[1]), p2 = ex2(s[2] - st.m[0]), p3 = ex2(s[3] - st.m[1]);
     st.l[0] += p0 + p2;
     st.l[1] += p1 + p3;
+    if (p_out) { p_out[0] = p0; p_out[1] = p1; p_out[2] = p2; p_out[3] = p3; }
     // value norms ride on P (fp16, clamped below the fp16 maximum)
     const uint32_t h0 = pack_h2(fminf(p0 * vn0, 65504.f), fminf(p1 * vn0, 65504.f));
     const uint32_t h1 = pack_h2(fminf(p2 * vn1, 65504.f), fminf(p3 * vn1, 65504.f));

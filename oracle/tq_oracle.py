@@ -286,6 +286,7 @@ class KVCacheOracle:
         self.rw, self.sink_size, self.chunk = residual_window, fp16_sink_size, chunk_size
         self.rot = rotation_matrix(head_dim, rotation_seed)
         self.proj = projection_matrix(head_dim, qjl_n_proj) if qjl_correction else None
+        self.sketch = {}          # name -> (sign words uint32 (B,H,T_c), residual norms float32 (B,H,T_c)) when QJL is on
         self.sink_k = self.sink_v = None
         self.sink_len = 0
         self.k = self.v = None            # recent-token buffer, valid [:fp_len]
@@ -307,6 +308,12 @@ class KVCacheOracle:
             pl = None
             dq = mse_dequantize(ph, n, self.rot, self.tables[b][0], b, self.d)
         if self.proj is not None:
+            # the reference applies the sketch and forgets it (cache.py:396-427); the signs and norms are kept here as
+            # well, as 32-bit words and float32, so that tests can hand a kernel exactly the state the correction used
+            r = np.asarray(x).astype(F32) - np.asarray(dq).astype(F32)
+            sg, gm = qjl_quantize(r.reshape(-1, self.d), self.proj)
+            words = (sg.astype(np.uint64) << np.arange(sg.shape[1], dtype=np.uint64)).sum(axis=1).astype(np.uint32)
+            self._last_sketch = (words.reshape(r.shape[:-1]), gm.astype(F32).reshape(r.shape[:-1]))
             dq = qjl_correct(x, dq, self.proj)
         return ph, pl, n, dq
 
@@ -321,6 +328,10 @@ class KVCacheOracle:
         self.fp_len = rem
         for name, x, bits in (("k", old_k, self.key_bits), ("v", old_v, self.value_bits)):
             ph, pl, nr, dq = self._side(x, bits)
+            if self.proj is not None:
+                w, g = self._last_sketch
+                prev = self.sketch.get(name)
+                self.sketch[name] = (w, g) if prev is None else (np.concatenate([prev[0], w], axis=2), np.concatenate([prev[1], g], axis=2))
             if self.comp[name] is None:
                 self.comp[name] = [ph, pl, nr]
                 dense = dq

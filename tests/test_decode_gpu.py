@@ -13,7 +13,7 @@ from gpu_util import cu, host, host_tables, kv_like
 pytestmark = pytest.mark.gpu
 
 
-def _case(oracle, rs, b, hq, hkv, t, d, kb, vb, rw, sink, chunk=0, dtype=np.float16):
+def _case(oracle, rs, b, hq, hkv, t, d, kb, vb, rw, sink, chunk=0, dtype=np.float16, qjl=False):
     """Build the cache with the oracle on the CPU and hand its exact state (packed codes, norms, sink and
     recent tokens) to a GPU cache, so the comparison isolates the attention arithmetic: packed codes are
     only bit-exact given identical rotated inputs, and one code that rounds the other way on a boundary
@@ -21,14 +21,19 @@ def _case(oracle, rs, b, hq, hkv, t, d, kb, vb, rw, sink, chunk=0, dtype=np.floa
     from mlx_turboquant_b200 import TurboQuantKVCache
     k, v = kv_like(rs, (b, hkv, t, d), dtype), kv_like(rs, (b, hkv, t, d), dtype)
     q = (rs.randn(b, hq, 1, d) / np.sqrt(d)).astype(dtype)
-    ref_c = oracle.KVCacheOracle(d, host_tables(d), kb, vb, rw, fp16_sink_size=sink, chunk_size=chunk)
+    ref_c = oracle.KVCacheOracle(d, host_tables(d), kb, vb, rw, fp16_sink_size=sink, chunk_size=chunk, qjl_correction=qjl)
     rk, rv = ref_c.update_and_fetch(k, v)
     c = TurboQuantKVCache(head_dim=d, num_kv_heads=hkv, key_bits=kb, value_bits=vb, residual_window=rw,
-                          fp16_sink_size=sink, chunk_size=chunk)
+                          fp16_sink_size=sink, chunk_size=chunk, qjl_correction=qjl)
     g = lambda a: None if a is None else cu(a)   # noqa: E731
     ck, cv = (ref_c.comp["k"] or [None] * 3), (ref_c.comp["v"] or [None] * 3)
-    c.state = (g(ref_c.k), g(ref_c.v), g(ck[0]), g(ck[2]), g(cv[0]), g(cv[2]), g(ref_c.sink_k), g(ref_c.sink_v),
-               g(ck[1]), g(cv[1]))
+    state = (g(ref_c.k), g(ref_c.v), g(ck[0]), g(ck[2]), g(cv[0]), g(cv[2]), g(ref_c.sink_k), g(ref_c.sink_v),
+             g(ck[1]), g(cv[1]))
+    if qjl:
+        sk, sv = ref_c.sketch.get("k", (None, None)), ref_c.sketch.get("v", (None, None))
+        i32 = lambda a: None if a is None else cu(a.view(np.int32))   # noqa: E731  (sign words travel as int32)
+        state = state + (i32(sk[0]), g(sk[1]), i32(sv[0]), g(sv[1]))
+    c.state = state
     c.meta_state = {"offset": str(ref_c.offset), "compressed_len": str(ref_c.comp_len), "sink_len": str(ref_c.sink_len),
                     "fp16_len": str(ref_c.fp_len), "fp16_capacity": str(0 if ref_c.k is None else ref_c.k.shape[2])}
     return c, cu(q), oracle.attention(q, rk, rv)
@@ -144,4 +149,15 @@ def test_benchmark_shape_against_gpu_dense_attention():
     vv = dv.float().repeat_interleave(hq // hkv, dim=1)
     p = torch.softmax((q.float() @ kk.transpose(-1, -2)) * d ** -0.5, dim=-1)
     ref = (p @ vv).cpu().numpy()
+    _check(c.attend(q, out_dtype=torch.float32), ref)
+
+
+@pytest.mark.parametrize("d,hq,hkv", ((96, 4, 4), (128, 8, 2), (64, 4, 1)))
+def test_qjl_sketch_in_packed_attention(oracle, d, hq, hkv):
+    """QJL on: attention over packed codes plus sign sketches equals attention over the reference's corrected dense
+    K / V (cache.py:396-427).  The sketch forces the general kernel also for 4-bit keys / 2-bit values at d = 128."""
+    rs = np.random.RandomState(1000 + d)
+    c, q, ref = _case(oracle, rs, 2, hq, hkv, 777, d, 4, 2, 32, 16, qjl=True)
+    _check(c.attend(q, out_dtype=torch.float32), ref)
+    c, q, ref = _case(oracle, rs, 1, hq, hkv, 300, d, 3.5, 3.5, 16, 0, chunk=64, qjl=True)
     _check(c.attend(q, out_dtype=torch.float32), ref)
