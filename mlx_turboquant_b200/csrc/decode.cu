@@ -53,7 +53,7 @@ template <int D> __host__ __device__ constexpr size_t body_bytes() {
 }
 template <int D> __host__ __device__ constexpr size_t tail_bytes() {
     return size_t(HPG) * D * sizeof(float) + size_t(HPG) * D * sizeof(__half) + 64 * sizeof(__half) + 16 * sizeof(float) +
-           size_t(HPG) * QM * sizeof(__half);
+           size_t(HPG) * QM * sizeof(__half) + 256 * sizeof(uint32_t) + 256 * sizeof(uint2);
 }
 template <int D> __host__ __device__ constexpr size_t kernel_smem() { return body_bytes<D>() + tail_bytes<D>(); }
 
@@ -76,6 +76,8 @@ __global__ void __launch_bounds__(GNW * 32, 1) decode_attn_kernel(DecodeParams p
     __half* ctab = qs + HPG * D;                                             // kc_hi, kc_lo, vc_hi, vc_lo (16 each)
     float* s_misc = reinterpret_cast<float*>(ctab + 64);                     // [0..7] 1/L per head, [8] last-CTA flag
     __half* us = reinterpret_cast<__half*>(s_misc + 16);                     // [8][32] fp16 (S q) * scale * log2(e)  (QJL)
+    uint32_t* t4 = reinterpret_cast<uint32_t*>(us + HPG * QM);               // [256] byte of two 4-bit codes -> half2 of key centroids
+    uint2* t2 = reinterpret_cast<uint2*>(t4 + 256);                          // [256] byte of four 2-bit codes -> 4 value centroids
 
     pdl_trigger();     // the next launch on the stream may become resident and run its own prologue
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
@@ -93,6 +95,18 @@ __global__ void __launch_bounds__(GNW * 32, 1) decode_attn_kernel(DecodeParams p
         const int bits = which == 0 ? p.kb_hi : which == 1 ? p.kb_lo : which == 2 ? p.vb_hi : p.vb_lo;
         const float sc = which == 2 ? p.v_scale_hi : which == 3 ? p.v_scale_lo : 1.f;
         ctab[tid] = __float2half_rn((src != nullptr && bits > 0 && k < (1 << bits)) ? src[k] * sc : 0.f);
+    }
+    // whole-byte tables for the two commonest widths (4-bit keys, 2-bit values, not fractional): a tile is then
+    // unpacked a 32-bit word at a time instead of a code at a time
+    const bool fast_k = !dense && p.kb_hi == 4 && p.kb_lo == 0 && p.words_ok, fast_v = !dense && p.vb_hi == 2 && p.vb_lo == 0 && p.words_ok;
+    if (fast_k || fast_v) {
+        __syncthreads();
+        const int e = tid;      // NT == 256 entries
+        const __half2 hk = __halves2half2(ctab[e & 15], ctab[e >> 4]);
+        t4[e] = *reinterpret_cast<const uint32_t*>(&hk);
+        const __half2 v01 = __halves2half2(ctab[32 + (e & 3)], ctab[32 + ((e >> 2) & 3)]);
+        const __half2 v23 = __halves2half2(ctab[32 + ((e >> 4) & 3)], ctab[32 + (e >> 6)]);
+        t2[e] = make_uint2(*reinterpret_cast<const uint32_t*>(&v01), *reinterpret_cast<const uint32_t*>(&v23));
     }
     pdl_wait();        // from here on: the query, the cache and the workspace of the previous launch are settled
 
@@ -198,7 +212,36 @@ __global__ void __launch_bounds__(GNW * 32, 1) decode_attn_kernel(DecodeParams p
         const int64_t tile_hi = min(tile_lo + p.p_tps, (p.c_len + TILE - 1) / TILE);
         for (int64_t tile = tile_lo + warp; tile < tile_hi; tile += NW) {
             const int64_t tok0 = tile * TILE;
-            {
+            if (fast_k) {
+                // 16 rows of D/2 bytes are contiguous: word i of the tile = row (4 i) / (D/2), bytes (4 i) % (D/2) ...
+                const uint32_t* src = reinterpret_cast<const uint32_t*>(p.k_hi + (kvl * p.c_ls + tok0) * (D / 2));
+#pragma unroll
+                for (int j = 0; j < (TILE * D / 2 / 4) / 32; ++j) {
+                    const int i = lane + 32 * j, r = (4 * i) / (D / 2), cb = 4 * i - r * (D / 2);
+                    const uint32_t w = tok0 + r < p.c_len ? __ldg(src + i) : 0u;
+                    uint4 o;
+                    o.x = t4[w & 255u]; o.y = t4[(w >> 8) & 255u]; o.z = t4[(w >> 16) & 255u]; o.w = t4[w >> 24];
+                    if (tok0 + r >= p.c_len) o = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(Ks + r * LD + 2 * cb) = o;
+                }
+            }
+            if (fast_v) {
+                const uint32_t* src = reinterpret_cast<const uint32_t*>(p.v_hi + (kvl * p.c_ls + tok0) * (D / 4));
+#pragma unroll
+                for (int j = 0; j < (TILE * D / 4 / 4 + 31) / 32; ++j) {
+                    const int i = lane + 32 * j, r = (4 * i) / (D / 4), cb = 4 * i - r * (D / 4);
+                    if (i < TILE * D / 4 / 4) {
+                        const bool live = tok0 + r < p.c_len;
+                        const uint32_t w = live ? __ldg(src + i) : 0u;
+                        const uint2 a = t2[w & 255u], b = t2[(w >> 8) & 255u], c = t2[(w >> 16) & 255u], e = t2[w >> 24];
+                        uint4 o0 = make_uint4(a.x, a.y, b.x, b.y), o1 = make_uint4(c.x, c.y, e.x, e.y);
+                        if (!live) { o0 = make_uint4(0, 0, 0, 0); o1 = o0; }
+                        *reinterpret_cast<uint4*>(Vs + r * LD + 4 * cb) = o0;
+                        *reinterpret_cast<uint4*>(Vs + r * LD + 4 * cb + 8) = o1;
+                    }
+                }
+            }
+            if (!fast_k || !fast_v) {
                 const int r = lane >> 1, hr = lane & 1;
                 const int64_t tok = tok0 + r;
                 const bool live = tok < p.c_len;
@@ -218,8 +261,8 @@ __global__ void __launch_bounds__(GNW * 32, 1) decode_attn_kernel(DecodeParams p
                         kk = __halves2half2(k0, k1);
                         vv = __halves2half2(v0, v1);
                     }
-                    *reinterpret_cast<__half2*>(Ks + r * LD + j) = kk;
-                    *reinterpret_cast<__half2*>(Vs + r * LD + j) = vv;
+                    if (!fast_k) *reinterpret_cast<__half2*>(Ks + r * LD + j) = kk;
+                    if (!fast_v) *reinterpret_cast<__half2*>(Vs + r * LD + j) = vv;
                 }
             }
             const bool ok0 = tok0 + g < p.c_len, ok1 = tok0 + g + 8 < p.c_len;
@@ -619,6 +662,7 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
     p.part_o = reinterpret_cast<float*>(ws + wl.part_o); p.part_ml = reinterpret_cast<float*>(ws + wl.part_ml);
     p.out = a->out; p.out_dtype = a->out_dtype;
     p.pdl = g_tune_pdl;
+    p.words_ok = (a->c_len > 0 && aligned(a->k_hi, 4) && aligned(a->v_hi, 4)) ? 1 : 0;   // packed rows readable as 32-bit words
     p.cent_by_value = 0;
     if (direct && a->k_cent_hi_host && a->v_cent_hi_host) {
         p.cent_by_value = 1;

@@ -33,6 +33,7 @@ struct DecodeParams {
     int* counters;                     // workspace: (B, Hkv, HG) arrival counters, zero between launches
     void* out; int out_dtype;
     int pdl;                           // launch with programmatic stream serialisation
+    int words_ok;                      // packed key / value rows start on 4-byte boundaries
     int cent_by_value;                 // kc16 / vc4 below hold the key / value centroids (host copies were given)
     float kc16[16], vc4[4];
 };
