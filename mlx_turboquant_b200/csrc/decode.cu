@@ -66,7 +66,7 @@ __device__ __forceinline__ uint32_t sign_pair(uint32_t a, uint32_t b) { return 0
 //   scores:  += (c/d) gamma_k[t] * sum_p sign_p(t) (S q)[p]            -> one more small MMA on +-1 operands
 //   output:  += (c/d) (sum_t p_t gamma_v[t] signs(t)) @ S               -> 32 more accumulator rows, applied at the end
 template <int D, bool QJL>
-__global__ void __launch_bounds__(GNW * 32, 1) decode_attn_kernel(DecodeParams p) {
+__global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel(DecodeParams p) {
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int NW = GNW, NT = NW * 32;
     constexpr int LD = stage_ld<D>();
@@ -509,7 +509,7 @@ __global__ void __launch_bounds__(GNW * 32, 1) decode_attn_kernel(DecodeParams p
 }
 
 // ---- host side ------------------------------------------------------------------------------------
-static int g_tune_ctas_per_sm = 1;     // CTAs of the general path resident per SM (split heuristic)
+static int g_tune_ctas_per_sm = 2;     // CTAs of the general path resident per SM at d <= 128 (split heuristic)
 static int g_tune_force_general = 0;   // 1: never take the direct path (testing)
 static int g_tune_splits = 0;          // > 0: fixed number of packed splits
 static int g_tune_pdl = 1;             // programmatic dependent launch between consecutive calls
