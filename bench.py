@@ -44,8 +44,8 @@ T_C = CTX - SINK - RW
 # algorithmic bytes of one layer-step: packed codes + norms, fp16 sink/recent tokens, query in, result out
 BYTES_PER_LAYER_STEP = HKV * T_C * (D * 4 // 8 + 4 + D * 2 // 8 + 4) + HKV * (SINK + RW) * 2 * D * 2 + HQ * D * 4
 # DRAM bytes (read + write) of one decode launch on this workload, from the ncu capture summarised in
-# profiles/decode_attn_kernel_c1_k4v2_ctx32768.md (it equals the algorithmic bytes within 1.5 %: nothing is re-read)
-NCU_DRAM_BYTES_PER_LAUNCH = 28545152
+# profiles/decode_direct_kernel_c1_k4v2_ctx32768.md (it equals the algorithmic bytes within 1 %: nothing is re-read)
+NCU_DRAM_BYTES_PER_LAUNCH = 28248064
 WORKLOAD = "llama31_8b_layer_decode_attn_ctx32768_k4v2_sink128_rw128"
 # quantize+pack: 4096-token chunks x 8 KV heads, K and V, fp16 in; bytes per (token, head): read 2*D*2, write codes + norms
 QCHUNK = 4096
@@ -401,7 +401,7 @@ def run_b200(args):
         "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
                      "peak_source": peak_src, "frac_of_nominal_8tbs": value / world / 8000.0,
                      "traffic": NCU_DRAM_BYTES_PER_LAUNCH if LAYERS == 32 else None, "traffic_unit": "bytes per launch (ncu, one capture)",
-                     "kernel": "decode_attn_kernel<128, direct> (one launch per layer: query rotation, packed attention, merge)",
+                     "kernel": "decode_direct_kernel<4> (one launch per layer: query rotation, packed attention, merge)",
                      "algorithmic_bytes_per_launch": BYTES_PER_LAYER_STEP},
     }
     if rank == 0 and world == 1 and not args.no_secondary:
