@@ -93,9 +93,10 @@ typedef struct {
  * metal_quantize_4bit (kernels.py:363-409). */
 int tq_quantize_pack(const tq_quantize_args* a, void* stream);
 
-/* fp16 rows with d = 128 take a tensor-core (tcgen05) kernel whose inter-warp waits are bounded; if one ever
- * timed out the kernel drains, and this returns the code of the first such wait (0 = none) for the current
- * device.  Synchronises the device; no reference counterpart. */
+/* The tensor-core quantize kernel (fp16 rows, d = 128) and the 4-bit-key / 2-bit-value decode kernel wait on
+ * mbarriers with an iteration limit; if a wait ever runs out the kernel drains and finishes, and this returns the
+ * code of the first such wait on the current device (quantize 1-9, decode 101-103; 0 = none).  Synchronises the
+ * device; no reference counterpart. */
 int tq_device_status(void);
 
 /* ---- dequantize: unpack -> centroid -> inverse rotation -> scale ------------------------- */
