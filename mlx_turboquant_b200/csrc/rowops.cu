@@ -220,23 +220,43 @@ __global__ void __launch_bounds__(NT) rowops_kernel(RowArgs a) {
     }
     // ---- QJL sketch of the residual, in rotated space: (x - xhat) @ S^T = |x| * (y - yhat) @ (S R^T)^T ----
     if (want_qjl_q) {
-        for (int mi = 0; mi < BM / 8; ++mi) {
-            const int m = warp * (BM / 8) + mi;
-            const int64_t row = row0 + m;
-            if (row >= total_rows) continue;   // warp-uniform
-            const float* e = es + m * (d + 1);
-            float dot = 0.f, ee = 0.f;
-            for (int k = 0; k < d; ++k) dot = fmaf(e[k], __ldg(a.qjl_proj_rot + lane * d + k), dot);
-            for (int k = lane; k < d; k += 32) ee = fmaf(e[k], e[k], ee);
+        // S R^T (32 x d) moves into the dead operand tile, rows padded to d + 1 floats so that lane p reading column k
+        // of its own row hits bank (p + k) mod 32; each warp then sketches its eight rows with one pass over k
+        float* sp = xs;                                      // [32][d + 1]: fits, 32 (d + 1) <= d * XS_LD for every d
+        for (int e = tid; e < 32 * d; e += NT) {
+            const int pp = e / d, k = e - pp * d;
+            sp[pp * (d + 1) + k] = __ldg(a.qjl_proj_rot + e);
+        }
+        __syncthreads();
+        constexpr int RPW = BM / (NT / 32);                  // rows per warp: 8
+        float dot[RPW], ee[RPW];
 #pragma unroll
-            for (int off = 16; off; off >>= 1) ee += __shfl_xor_sync(0xffffffffu, ee, off);
+        for (int mi = 0; mi < RPW; ++mi) dot[mi] = ee[mi] = 0.f;
+        const float* srow = sp + lane * (d + 1);
+        const float* e0 = es + size_t(warp) * RPW * (d + 1);
+        for (int k = 0; k < d; ++k) {
+            const float sv = srow[k];
+#pragma unroll
+            for (int mi = 0; mi < RPW; ++mi) dot[mi] = fmaf(e0[mi * (d + 1) + k], sv, dot[mi]);     // e: broadcast read
+        }
+        for (int k = lane; k < d; k += 32) {
+#pragma unroll
+            for (int mi = 0; mi < RPW; ++mi) { const float v = e0[mi * (d + 1) + k]; ee[mi] = fmaf(v, v, ee[mi]); }
+        }
+#pragma unroll
+        for (int mi = 0; mi < RPW; ++mi) {
+            const int m = warp * RPW + mi;
+            const int64_t row = row0 + m;
+            float en = ee[mi];
+#pragma unroll
+            for (int off = 16; off; off >>= 1) en += __shfl_xor_sync(0xffffffffu, en, off);
             const float nrm = rown[m];
-            uint32_t bits = __ballot_sync(0xffffffffu, dot >= 0.f);
+            uint32_t bits = __ballot_sync(0xffffffffu, dot[mi] >= 0.f);
             if (nrm == 0.f) bits = 0xffffffffu;   // zero row: the reference's residual is exactly 0, and 0 >= 0
-            if (lane == 0) {
+            if (lane == 0 && row < total_rows) {
                 const int64_t o = row / a.n_rows, r = row - o * a.n_rows;
                 a.qjl_bits_out[o * a.q_lane_stride + r] = bits;
-                a.qjl_gamma_out[o * a.q_lane_stride + r] = nrm * sqrtf(ee);
+                a.qjl_gamma_out[o * a.q_lane_stride + r] = nrm * sqrtf(en);
             }
         }
     }
