@@ -554,7 +554,9 @@ static SplitPlan plan_splits(int batch, int n_q_heads, int n_kv_heads, int64_t c
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// The arrival counters sit at the start of the workspace so that their position does not depend on the plan.
+// The arrival counters sit at the start of the workspace, in an area of fixed size: calls of different shapes that
+// share a workspace must never see one another's partials where they expect counters left at zero.
+constexpr size_t COUNTER_AREA = 65536;      // 16384 (sequence, KV head, head group) triples; beyond that the area grows
 struct WsLayout { size_t counters, part_o, part_ml, total; };
 
 static WsLayout ws_layout(int batch, int n_q_heads, int n_kv_heads, int d, const SplitPlan& s) {
@@ -563,7 +565,7 @@ static WsLayout ws_layout(int batch, int n_q_heads, int n_kv_heads, int d, const
     const size_t parts = groups * size_t(s.n_ps + s.n_ds);
     const size_t slots = size_t(std::min(n_q_heads / n_kv_heads, HPG));
     w.counters = 0;
-    w.part_o = align_up(groups * sizeof(int), 256);
+    w.part_o = align_up(std::max(groups * sizeof(int), COUNTER_AREA), 256);
     w.part_ml = align_up(w.part_o + parts * slots * d * sizeof(float), 256);
     w.total = align_up(w.part_ml + parts * slots * 2 * sizeof(float), 256);
     return w;
@@ -733,5 +735,10 @@ extern "C" int tq_decode_attn(const tq_decode_args* a, void* stream) {
     bool direct = false;
     int rc = decode_prepare(a, a ? a->workspace : nullptr, a ? a->workspace_bytes : 0, &p, &direct);
     if (rc) return rc;
+    const size_t counter_bytes = size_t(p.B) * p.Hkv * p.HG * sizeof(int);
+    if (counter_bytes > COUNTER_AREA) {        // more triples than the fixed area holds: clear them for this call
+        cudaError_t e = cudaMemsetAsync(p.counters, 0, counter_bytes, static_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_decode_attn: clearing counters: %s", cudaGetErrorString(e));
+    }
     return decode_launch(p, direct, static_cast<cudaStream_t>(stream));
 }

@@ -161,3 +161,14 @@ def test_qjl_sketch_in_packed_attention(oracle, d, hq, hkv):
     _check(c.attend(q, out_dtype=torch.float32), ref)
     c, q, ref = _case(oracle, rs, 1, hq, hkv, 300, d, 3.5, 3.5, 16, 0, chunk=64, qjl=True)
     _check(c.attend(q, out_dtype=torch.float32), ref)
+
+
+def test_calls_of_different_shapes_share_a_workspace(oracle):
+    """The scratch buffer is shared by every cache on a stream: a call with few (sequence, KV head) lanes followed by a
+    call with many must not find the first call's partials where it expects zeroed arrival counters."""
+    rs = np.random.RandomState(77)
+    small = _case(oracle, rs, 1, 4, 1, 3000, 128, 4, 2, 32, 8)
+    big = _case(oracle, rs, 6, 32, 32, 400, 64, 4, 2, 16, 4)
+    for _ in range(2):
+        for c, q, ref in (small, big, small):
+            _check(c.attend(q, out_dtype=torch.float32), ref)
