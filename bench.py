@@ -180,20 +180,23 @@ def run_reference(args):
 
 
 # ---- the CUDA path ------------------------------------------------------------------------------------------
-def build_caches(torch, dev, rank):
+def build_caches(torch, dev, seq, heads=(0, HKV)):
+    """Layer caches of sequence `seq`; `heads` = the KV heads this rank owns (all of them unless heads are split)."""
     from mlx_turboquant_b200 import TurboQuantKVCache
+    h0, h1 = heads
     caches, qs = [], []
     for li in range(LAYERS):
-        g = torch.Generator(device=dev).manual_seed(1000 + 100 * rank + li)
+        g = torch.Generator(device=dev).manual_seed(1000 + 100 * seq + li)
         scale_k = torch.exp(0.5 * torch.randn(1, HKV, CTX, 1, device=dev, generator=g))
         k = (torch.randn(1, HKV, CTX, D, device=dev, generator=g) * scale_k).half()
         scale_v = torch.exp(0.5 * torch.randn(1, HKV, CTX, 1, device=dev, generator=g))
         v = (torch.randn(1, HKV, CTX, D, device=dev, generator=g) * scale_v).half()
-        c = TurboQuantKVCache(head_dim=D, num_kv_heads=HKV, key_bits=4, value_bits=2, residual_window=RW, fp16_sink_size=SINK)
-        c.update(k, v)
+        c = TurboQuantKVCache(head_dim=D, num_kv_heads=h1 - h0, key_bits=4, value_bits=2, residual_window=RW, fp16_sink_size=SINK)
+        c.update(k[:, h0:h1].contiguous(), v[:, h0:h1].contiguous())
         assert (c._sink_len, c._compressed_len, c._fp16_len) == (SINK, T_C, RW)
         caches.append(c)
-        qs.append((torch.randn(1, HQ, 1, D, device=dev, generator=g) / D ** 0.5).half())
+        q = (torch.randn(1, HQ, 1, D, device=dev, generator=g) / D ** 0.5).half()
+        qs.append(q[:, h0 * (HQ // HKV):h1 * (HQ // HKV)].contiguous())
         del k, v
     return caches, qs
 
@@ -312,10 +315,21 @@ def run_b200(args):
 
     global LAYERS
     LAYERS = args.layers
-    # weak scaling: `world` independent sequences, dealt one per rank; no rank reads another rank's lanes
-    plan = sharding.plan_lanes(world, HKV, world, rank, split_heads=False)
-    assert (plan.seq_end - plan.seq_begin, plan.head_end - plan.head_begin) == (1, HKV)
-    caches, qs = build_caches(torch, dev, plan.seq_begin)
+    if args.split_heads and world > 1:
+        # strong scaling of ONE sequence: its KV heads dealt to the ranks; per layer the (1, H_q / world, 1, D) outputs
+        # are all-gathered (the only collective on the path), unless --no-gather
+        plan = sharding.plan_lanes(1, HKV, world, rank, split_heads=True)
+        caches, qs = build_caches(torch, dev, 0, (plan.head_begin, plan.head_end))
+        n_seq = 1
+    else:
+        # weak scaling: `world` independent sequences, dealt one per rank; no rank reads another rank's lanes
+        plan = sharding.plan_lanes(world, HKV, world, rank, split_heads=False)
+        assert (plan.seq_end - plan.seq_begin, plan.head_end - plan.head_begin) == (1, HKV)
+        caches, qs = build_caches(torch, dev, plan.seq_begin)
+        n_seq = world
+    split = args.split_heads and world > 1
+    if split:
+        args.no_e2e = True            # the host-buffer leg is defined for whole sequences per GPU
     torch.cuda.synchronize(dev)
 
     def barrier():
@@ -329,9 +343,11 @@ def run_b200(args):
     def layer_pass():
         for i in range(LAYERS):
             outs[i] = caches[i].attend(qs[i])
+            if split and not args.no_gather:
+                outs[i] = sharding.gather_heads(outs[i])
     layer_pass()                      # allocates the workspace before capture
     torch.cuda.synchronize(dev)
-    if args.no_graph:
+    if args.no_graph or split:        # collectives are launched eagerly
         class _Eager:
             replay = staticmethod(layer_pass)
         graph = _Eager()
@@ -353,12 +369,18 @@ def run_b200(args):
         e1.record()
         barrier()
         ms_step = e0.elapsed_time(e1) / reps
-        t_end = time.time() + (0.0 if args.no_graph else 0.6)
-        while time.time() < t_end:     # a few more replays so the sampler sees the loaded clock
-            graph.replay()
+        # a few more replays so the sampler sees the loaded clock; a fixed count when the step holds collectives
+        # (every rank must issue the same number of them), wall-clock bounded otherwise
+        if split and not args.no_gather:
+            for _ in range(200):
+                graph.replay()
+        else:
+            t_end = time.time() + (0.0 if args.no_graph else 0.6)
+            while time.time() < t_end:
+                graph.replay()
         torch.cuda.synchronize(dev)
     ms_step = sharding.job_time_ms(ms_step, dev)
-    value = world * LAYERS * BYTES_PER_LAYER_STEP / (ms_step * 1e-3) / 1e9
+    value = n_seq * LAYERS * BYTES_PER_LAYER_STEP / (ms_step * 1e-3) / 1e9
 
     # ---- end to end through the public API with host buffers -----------------------------------------------
     # one pinned staging buffer per layer holds the step's query, key and value heads: one host -> device copy
@@ -383,16 +405,17 @@ def run_b200(args):
     e1.record()
     barrier()
     e2e_ms = sharding.job_time_ms(e0.elapsed_time(e1) / e2e_steps, dev)
-    e2e_gbs = None if args.no_e2e else world * LAYERS * BYTES_PER_LAYER_STEP / (e2e_ms * 1e-3) / 1e9
+    e2e_gbs = None if args.no_e2e else n_seq * LAYERS * BYTES_PER_LAYER_STEP / (e2e_ms * 1e-3) / 1e9
 
     line = {
         "metric": "decode_attn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "us_per_layer_step": ms_step * 1e3 / LAYERS,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 accumulate, f16 operands",
+        "higher_is_better": True, "scaling": "strong" if split else "weak", "vs_baseline": None, "dtype": "f32 accumulate, f16 operands",
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "layers_per_step": LAYERS, "q_heads": HQ, "kv_heads": HKV, "head_dim": D,
                    "batch_per_gpu": 1, "context": CTX, "l2_policy": "inputs larger than L2: 32 distinct layer caches, 0.9 GB per step",
-                   "sharding": "independent sequences per GPU, no collective"},
+                   "sharding": ("one sequence, KV heads split over the GPUs, " + ("no gather" if args.no_gather else "outputs all-gathered per layer (NCCL)"))
+                   if split else "independent sequences per GPU, no collective"},
         "e2e": {"value": e2e_gbs, "unit": "GB/s", "ms_per_step": e2e_ms, "us_per_layer_step": e2e_ms * 1e3 / LAYERS,
                 "h2d_bytes_per_step": LAYERS * (HQ * D * 2 + 2 * HKV * D * 2), "d2h_bytes_per_step": LAYERS * HQ * D * 2,
                 "path": "TurboQuantKVCache.update + .attend per layer, pinned host q/k/v in, pinned host result out"},
@@ -434,6 +457,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--quantize-pool", type=int, default=8, help="distinct 0.5 GB fp16 K/V input sets the quantize leg cycles through")
+    ap.add_argument("--split-heads", action="store_true", help="N > 1: shard ONE sequence by KV head (strong scaling) instead of one sequence per GPU")
+    ap.add_argument("--no-gather", action="store_true", help="with --split-heads: leave every GPU with its own heads' outputs")
     ap.add_argument("--no-secondary", action="store_true", help="skip the quantize+pack leg")
     args = ap.parse_args()
     if args.impl == "reference":
