@@ -14,9 +14,16 @@
 //   warp  16    allocates TMEM, issues the MMAs (one elected thread) and commits them to mbarriers
 //   warps 17-24 producers: 128-bit global loads of the rows, sum of squares for the norm, stores into the
 //               128-byte-swizzled K-major shared-memory layout the MMA descriptors expect
+// Two ways to fill the operand stages.  TMA (the default when the driver offers tensor maps): one thread issues two
+// cp.async.bulk.tensor copies per tile with the 128-byte swizzle the MMA descriptors expect - three stages of rows
+// in flight per SM at no register cost - and warps 17-24 only read the tile back from shared memory for the norms.
+// Otherwise warps 17-24 load the rows themselves (one tile's worth of registers in flight).
 // Every mbarrier wait is bounded: on a timeout the kernel raises a status word, drains and frees its TMEM.
 #include <algorithm>
 #include <cstdlib>
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
 
 #include "common.cuh"
 
@@ -29,6 +36,7 @@ constexpr int A_STAGES = 3, ACC_STAGES = 2;
 constexpr int N_EPI = 512, N_PROD = 256;         // threads per role
 constexpr int EPI_WARPS = N_EPI / 32;            // 16: TMEM lane quadrant = warp % 4, coordinate quarter = warp / 4
 constexpr int NT = N_EPI + 32 + N_PROD;          // 800
+constexpr int NT_TMA = NT + 32;                  // one more warp: its first lane feeds the operand stages by TMA
 constexpr int BIN_REP = 4;                       // copies of every lookup-table entry (lane & 3 picks one): fewer bank conflicts
 constexpr int KBLK_BYTES = TM * 128;             // one 64-column K-block of a 128-row operand: 16 KB
 constexpr int OPER_BYTES = 2 * KBLK_BYTES;       // 32 KB per operand tile
@@ -43,7 +51,7 @@ constexpr int OFF_BINS = OFF_RLO + OPER_BYTES;             // 2 tables x NBINS x
 constexpr int OFF_BND = OFF_BINS + 2 * NBINS * BIN_REP * 8; // 2 x 16 floats: raw boundaries (slow path)
 constexpr int OFF_NSQ = OFF_BND + 128;                     // A_STAGES x 2 x 128 floats: partial sums of squares
 constexpr int OFF_BAR = OFF_NSQ + A_STAGES * 2 * TM * 4;   // mbarriers
-constexpr int OFF_MISC = OFF_BAR + 16 * 8;                 // tmem base, abort flag
+constexpr int OFF_MISC = OFF_BAR + 16 * 8;                 // tmem base, abort flag (barriers: 3 + 3 + 2 + 2 + 3 norm-ready)
 constexpr int SMEM_BYTES = OFF_MISC + 64;
 
 struct Params {
@@ -52,6 +60,7 @@ struct Params {
     const float* bnd_hi; const float* bnd_lo; int bits_hi, bits_lo;
     uint8_t* p_hi; uint8_t* p_lo; float* norms; int64_t out_lane_stride;
     int64_t n_tiles;
+    int64_t tiles_per_lane;      // TMA variant: tiles never cross cache lanes; tile = lane * tiles_per_lane + tile in lane
     int* status;
 };
 
@@ -96,6 +105,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Tiled TMA load of a (64 columns x 128 rows x 1 lane) box; the innermost coordinate is 0 or 64 halves (0 or 128 bytes).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
@@ -222,11 +239,11 @@ __device__ __noinline__ uint32_t code_slow(float y, const float* raw_bnd, int n_
 }
 
 struct EpiCtx {
-    const Params& p; unsigned char* smem; uint32_t tmem_base, bar_accfull, bar_accfree, bar_afree;
+    const Params& p; unsigned char* smem; uint32_t tmem_base, bar_accfull, bar_accfree, bar_afree, bar_nrm;
     volatile int* abort_flag; int64_t total_rows; int warp, lane;
 };
 
-template <int BITS>
+template <int BITS, bool TMA>
 __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
     const Params& p = e.p;
     const int quad = e.warp & 3, quarter = e.warp >> 2, row_in_tile = quad * 32 + e.lane;
@@ -238,15 +255,19 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
     float bnd[15];
 #pragma unroll
     for (int i = 0; i < 15; ++i) bnd[i] = raw_bnd[i < n_bnd ? i : 0];
-    // the tile stride in (lane, row) form
+    // the tile stride in (lane, row) form.  TMA variant: a tile is (lane, tile in lane), rows past the lane's end are
+    // zero-filled by the copy and dropped here; otherwise tiles run over the flattened rows of all lanes.
     const int64_t stride_rows = int64_t(gridDim.x) * TM;
-    const int64_t step_o = stride_rows / p.n_rows, step_r = stride_rows - step_o * p.n_rows;
+    const int64_t step_o = TMA ? int64_t(gridDim.x) / p.tiles_per_lane : stride_rows / p.n_rows;
+    const int64_t step_r = TMA ? (int64_t(gridDim.x) - step_o * p.tiles_per_lane) * TM : stride_rows - step_o * p.n_rows;
+    const int64_t wrap_r = TMA ? p.tiles_per_lane * TM : p.n_rows;
     int64_t lane_o = 0, lane_r = 0;
     int it = 0;
     for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
         const int a = it % ACC_STAGES, s = it % A_STAGES;
         TC_STAMP(e.warp == 0 && e.lane == 0, 2, it, 0);
         if (!mbar_wait(e.bar_accfull + 8 * a, (it / ACC_STAGES) & 1, e.abort_flag, 3)) break;
+        if (TMA && !mbar_wait(e.bar_nrm + 8 * s, (it / A_STAGES) & 1, e.abort_flag, 5)) break;     // sums of squares written
         tc_fence_after();
         TC_STAMP(e.warp == 0 && e.lane == 0, 2, it, 1);
         const float* nsq = reinterpret_cast<const float*>(e.smem + OFF_NSQ) + s * 2 * TM;
@@ -254,17 +275,18 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
         mbar_arrive(e.bar_afree + 8 * s);                       // norm slots of this stage are free again
         const float rinv = 1.f / fmaxf(nrm, 1e-10f);            // cache.py:237-238 guards the zero vector the same way
         const float rbin = rinv * 256.f;
-        const int64_t row = tile * TM + row_in_tile;
-        const bool live = row < e.total_rows;
+        if (it == 0) {      // one division at the start, then advanced by the grid stride
+            if (TMA) { lane_o = tile / p.tiles_per_lane; lane_r = (tile - lane_o * p.tiles_per_lane) * TM + row_in_tile; }
+            else { const int64_t row = tile * TM + row_in_tile; lane_o = row / p.n_rows; lane_r = row - lane_o * p.n_rows; }
+        }
+        const bool live = TMA ? lane_r < p.n_rows : tile * TM + row_in_tile < e.total_rows;
         int64_t orow = 0;
         if (live) {
-            // lane (cache row o) and row inside it: one division at the start, then advanced by the grid stride
-            if (it == 0) { lane_o = row / p.n_rows; lane_r = row - lane_o * p.n_rows; }
             orow = lane_o * p.out_lane_stride + lane_r;
             if (quarter == 0) p.norms[orow] = nrm;
-            lane_r += step_r; lane_o += step_o;
-            if (lane_r >= p.n_rows) { lane_r -= p.n_rows; ++lane_o; }
         }
+        lane_r += step_r; lane_o += step_o;
+        if (lane_r >= wrap_r + (TMA ? row_in_tile : 0)) { lane_r -= wrap_r; ++lane_o; }
         const uint32_t t_hi = e.tmem_base + (uint32_t(quad * 32) << 16) + a * 256 + quarter * 32;
         uint32_t words[4];                                      // 32 codes x at most 4 bits
 #pragma unroll
@@ -334,7 +356,9 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
     }
 }
 
-__global__ void __launch_bounds__(NT, 1) quantize_tc_kernel(Params p) {
+template <bool TMA>
+__global__ void __launch_bounds__(TMA ? NT_TMA : NT, 1) quantize_tc_kernel(Params p, const __grid_constant__ CUtensorMap tmap) {
+    constexpr int NTHREADS = TMA ? NT_TMA : NT;
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t sbase = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -344,6 +368,7 @@ __global__ void __launch_bounds__(NT, 1) quantize_tc_kernel(Params p) {
     //           acc_full[ACC_STAGES] (MMA commit -> epilogue), acc_free[ACC_STAGES] (epilogue -> MMA)
     const uint32_t bar_full = sbase + OFF_BAR, bar_afree = bar_full + 8 * A_STAGES;
     const uint32_t bar_accfull = bar_afree + 8 * A_STAGES, bar_accfree = bar_accfull + 8 * ACC_STAGES;
+    const uint32_t bar_nrm = bar_accfree + 8 * ACC_STAGES;       // TMA variant: sums of squares of a stage are written
 
     TC_STAMP0(tid == 0, 0);
     if (sbase & 1023u) {                  // the swizzled operand tiles need 1024-byte alignment (uniform across the CTA)
@@ -352,12 +377,18 @@ __global__ void __launch_bounds__(NT, 1) quantize_tc_kernel(Params p) {
     }
     if (tid == 0) {
         *abort_flag = 0;
-        for (int s = 0; s < A_STAGES; ++s) { mbar_init(bar_full + 8 * s, N_PROD); mbar_init(bar_afree + 8 * s, 1 + N_EPI); }
+        for (int s = 0; s < A_STAGES; ++s) {
+            // TMA: one arrival (the issuing thread, with the byte count) fills a stage; it is free again once the MMAs have
+            // committed, the epilogue has read the norms and the norm warps have read the rows
+            mbar_init(bar_full + 8 * s, TMA ? 1 : N_PROD);
+            mbar_init(bar_afree + 8 * s, TMA ? 1 + N_EPI + N_PROD : 1 + N_EPI);
+            mbar_init(bar_nrm + 8 * s, N_PROD);
+        }
         for (int a = 0; a < ACC_STAGES; ++a) { mbar_init(bar_accfull + 8 * a, 1); mbar_init(bar_accfree + 8 * a, N_EPI); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // R -> fp16 hi / lo operand tiles (swizzled K-major): B[n = j][k] = R[j][k]
-    for (int idx = tid; idx < D * (D / 8); idx += NT) {
+    for (int idx = tid; idx < D * (D / 8); idx += NTHREADS) {
         const int j = idx / (D / 8), c = idx - j * (D / 8);      // row j, 16-byte chunk c (8 halves) of the row
         const float4 f0 = __ldg(reinterpret_cast<const float4*>(p.rot + j * D + c * 8));
         const float4 f1 = __ldg(reinterpret_cast<const float4*>(p.rot + j * D + c * 8 + 4));
@@ -382,8 +413,8 @@ __global__ void __launch_bounds__(NT, 1) quantize_tc_kernel(Params p) {
             raw[tid] = (src != nullptr && i < nb) ? src[i] : INFINITY;
         }
         __syncthreads();
-        build_bins(reinterpret_cast<float2*>(smem + OFF_BINS), raw, (1 << p.bits_hi) - 1, tid, NT);
-        if (p.bits_lo) build_bins(reinterpret_cast<float2*>(smem + OFF_BINS) + NBINS * BIN_REP, raw + 16, (1 << p.bits_lo) - 1, tid, NT);
+        build_bins(reinterpret_cast<float2*>(smem + OFF_BINS), raw, (1 << p.bits_hi) - 1, tid, NTHREADS);
+        if (p.bits_lo) build_bins(reinterpret_cast<float2*>(smem + OFF_BINS) + NBINS * BIN_REP, raw + 16, (1 << p.bits_lo) - 1, tid, NTHREADS);
     }
     if (warp == EPI_WARPS) {              // one warp owns the TMEM allocation: 2 stages x (hi + lo) x 128 columns
         tmem_alloc(sbase + OFF_MISC, 512);
@@ -400,11 +431,11 @@ __global__ void __launch_bounds__(NT, 1) quantize_tc_kernel(Params p) {
     if (warp < EPI_WARPS) {
         // ======================= epilogue: row = 32*(warp%4) + lane, coordinate quarter = warp/4 =======================
         const int bits = (p.bits_lo && (warp >> 3)) ? p.bits_lo : p.bits_hi;
-        EpiCtx e{p, smem, tmem_base, bar_accfull, bar_accfree, bar_afree, abort_flag, total_rows, warp, lane};
-        if (bits == 4) epilogue_loop<4>(e);
-        else if (bits == 3) epilogue_loop<3>(e);
-        else if (bits == 2) epilogue_loop<2>(e);
-        else epilogue_loop<1>(e);
+        EpiCtx e{p, smem, tmem_base, bar_accfull, bar_accfree, bar_afree, bar_nrm, abort_flag, total_rows, warp, lane};
+        if (bits == 4) epilogue_loop<4, TMA>(e);
+        else if (bits == 3) epilogue_loop<3, TMA>(e);
+        else if (bits == 2) epilogue_loop<2, TMA>(e);
+        else epilogue_loop<1, TMA>(e);
     } else if (warp == EPI_WARPS) {
         // ======================= MMA issue: one elected thread =======================
         if (lane == 0) {
@@ -434,6 +465,50 @@ __global__ void __launch_bounds__(NT, 1) quantize_tc_kernel(Params p) {
             }
         }
         __syncwarp();
+    } else if (TMA && warp == EPI_WARPS + 1 + N_PROD / 32) {
+        // ======================= TMA issue: one thread keeps the operand stages full =======================
+        if (lane == 0) {
+            int64_t o = int64_t(blockIdx.x) / p.tiles_per_lane, tl = int64_t(blockIdx.x) - o * p.tiles_per_lane;
+            const int64_t so = int64_t(gridDim.x) / p.tiles_per_lane, st = int64_t(gridDim.x) - so * p.tiles_per_lane;
+            int it = 0;
+            for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
+                const int s = it % A_STAGES;
+                if (it >= A_STAGES && !mbar_wait(bar_afree + 8 * s, ((it / A_STAGES) - 1) & 1, abort_flag, 6)) break;
+                const uint32_t a_tile = sbase + OFF_A + s * OPER_BYTES;
+                mbar_expect_tx(bar_full + 8 * s, OPER_BYTES);
+                tma_load_3d(a_tile, &tmap, 0, int(tl * TM), int(o), bar_full + 8 * s);                    // columns 0..63
+                tma_load_3d(a_tile + KBLK_BYTES, &tmap, 64, int(tl * TM), int(o), bar_full + 8 * s);      // columns 64..127
+                o += so; tl += st;
+                if (tl >= p.tiles_per_lane) { tl -= p.tiles_per_lane; ++o; }
+            }
+        }
+        __syncwarp();
+    } else if (TMA) {
+        // ======================= norm warps: sum of squares of every row, read back from the stage =======================
+        // warp nw: K-block nw & 1 (64 columns), rows 32 (nw >> 1) + lane: eight consecutive rows hit eight different
+        // 16-byte columns of the swizzled tile, so the 128-bit reads are free of bank conflicts
+        const int nw = warp - (EPI_WARPS + 1), kblk = nw & 1, r = (nw >> 1) * 32 + lane;
+        int it = 0;
+        for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
+            const int s = it % A_STAGES;
+            if (!mbar_wait(bar_full + 8 * s, (it / A_STAGES) & 1, abort_flag, 7)) break;
+            const unsigned char* rowp = smem + OFF_A + s * OPER_BYTES + kblk * KBLK_BYTES + r * 128;
+            float a = 0.f;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint4 v = *reinterpret_cast<const uint4*>(rowp + ((c ^ (r & 7)) << 4));
+                const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float2 f = __half22float2(h[u]);
+                    a = fmaf(f.x, f.x, a);
+                    a = fmaf(f.y, f.y, a);
+                }
+            }
+            reinterpret_cast<float*>(smem + OFF_NSQ)[s * 2 * TM + kblk * TM + r] = a;
+            mbar_arrive(bar_nrm + 8 * s);        // release: the epilogue reads the sums after waiting on this barrier
+            mbar_arrive(bar_afree + 8 * s);      // this thread is done reading the stage
+        }
     } else {
         // ======================= producers =======================
         // Warp pw owns rows [16*pw, 16*pw + 16) of the tile; one warp-wide 128-bit load covers two whole rows
@@ -537,7 +612,8 @@ int tq_quantize_pack_tc(const tq_quantize_args* q, cudaStream_t s, bool* handled
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 16) return TQ_OK;
     if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(tc::quantize_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(tc::quantize_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::quantize_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
         if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_quantize_pack: shared memory %d B: %s", tc::SMEM_BYTES, cudaGetErrorString(e));
         if (cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms[dev] <= 0) sms[dev] = 148;
         attr_set[dev] = true;
@@ -547,10 +623,47 @@ int tq_quantize_pack_tc(const tq_quantize_args* q, cudaStream_t s, bool* handled
     p.n_lanes = q->n_lanes; p.n_rows = q->n_rows; p.x_lane_stride = q->x_lane_stride; p.x_row_stride = q->x_row_stride;
     p.rot = q->rot; p.bnd_hi = q->bnd_hi; p.bnd_lo = q->bnd_lo; p.bits_hi = q->bits_hi; p.bits_lo = q->bits_lo;
     p.p_hi = q->packed_hi; p.p_lo = q->packed_lo; p.norms = q->norms; p.out_lane_stride = q->out_lane_stride;
-    p.n_tiles = (total + tc::TM - 1) / tc::TM;
     p.status = nullptr;
-    const unsigned grid = unsigned(std::min<int64_t>(p.n_tiles, sms[dev]));
-    tc::quantize_tc_kernel<<<grid, tc::NT, tc::SMEM_BYTES, s>>>(p);
+
+    // Tensor map over the rows as (column, row, lane): boxes of 64 columns x 128 rows x 1 lane land in shared memory in
+    // the 128-byte-swizzled layout the MMA descriptors describe; rows past a lane's end read as zeros.
+    CUtensorMap tmap{};
+    bool use_tma = false;
+    static int tma_off = -1;
+    if (tma_off < 0) {
+        const char* e = getenv("TQ_DISABLE_TMA");
+        tma_off = (e && e[0] == '1') ? 1 : 0;
+    }
+    static PFN_cuTensorMapEncodeTiled encode = nullptr;
+    static bool looked_up = false;
+    if (!looked_up) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+            encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
+        looked_up = true;
+    }
+    if (!tma_off && encode && q->n_rows < (int64_t(1) << 31) && q->n_lanes < (int64_t(1) << 31)) {
+        const cuuint64_t dims[3] = {cuuint64_t(tc::D), cuuint64_t(q->n_rows), cuuint64_t(q->n_lanes)};
+        const cuuint64_t strides[2] = {cuuint64_t(q->x_row_stride) * 2, cuuint64_t(q->x_lane_stride) * 2};     // bytes, multiples of 16
+        const cuuint32_t box[3] = {64, cuuint32_t(tc::TM), 1};
+        const cuuint32_t estr[3] = {1, 1, 1};
+        const CUresult r = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(q->x), dims, strides, box, estr,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        use_tma = (r == CUDA_SUCCESS);
+    }
+    if (use_tma) {
+        p.tiles_per_lane = (q->n_rows + tc::TM - 1) / tc::TM;
+        p.n_tiles = q->n_lanes * p.tiles_per_lane;
+        const unsigned grid = unsigned(std::min<int64_t>(p.n_tiles, sms[dev]));
+        tc::quantize_tc_kernel<true><<<grid, tc::NT_TMA, tc::SMEM_BYTES, s>>>(p, tmap);
+    } else {
+        p.tiles_per_lane = 0;
+        p.n_tiles = (total + tc::TM - 1) / tc::TM;
+        const unsigned grid = unsigned(std::min<int64_t>(p.n_tiles, sms[dev]));
+        tc::quantize_tc_kernel<false><<<grid, tc::NT, tc::SMEM_BYTES, s>>>(p, tmap);
+    }
     *handled = true;
     return check_launch("tq_quantize_pack (tensor core)");
 }
