@@ -36,7 +36,8 @@ constexpr int A_STAGES = 3, ACC_STAGES = 2;
 constexpr int N_EPI = 512, N_PROD = 256;         // threads per role
 constexpr int EPI_WARPS = N_EPI / 32;            // 16: TMEM lane quadrant = warp % 4, coordinate quarter = warp / 4
 constexpr int NT = N_EPI + 32 + N_PROD;          // 800
-constexpr int NT_TMA = NT + 32;                  // one more warp: its first lane feeds the operand stages by TMA
+constexpr int N_NORM = 128;                       // TMA variant: threads that read the rows back for the norms (one row each)
+constexpr int NT_TMA = N_EPI + 32 + N_NORM + 32; // 704: the last warp's first lane feeds the operand stages by TMA
 constexpr int BIN_REP = 4;                       // copies of every lookup-table entry (lane & 3 picks one): fewer bank conflicts
 constexpr int KBLK_BYTES = TM * 128;             // one 64-column K-block of a 128-row operand: 16 KB
 constexpr int OPER_BYTES = 2 * KBLK_BYTES;       // 32 KB per operand tile
@@ -381,8 +382,8 @@ __global__ void __launch_bounds__(TMA ? NT_TMA : NT, 1) quantize_tc_kernel(Param
             // TMA: one arrival (the issuing thread, with the byte count) fills a stage; it is free again once the MMAs have
             // committed, the epilogue has read the norms and the norm warps have read the rows
             mbar_init(bar_full + 8 * s, TMA ? 1 : N_PROD);
-            mbar_init(bar_afree + 8 * s, TMA ? 1 + N_EPI + N_PROD : 1 + N_EPI);
-            mbar_init(bar_nrm + 8 * s, N_PROD);
+            mbar_init(bar_afree + 8 * s, TMA ? 1 + N_EPI + N_NORM : 1 + N_EPI);
+            mbar_init(bar_nrm + 8 * s, N_NORM);
         }
         for (int a = 0; a < ACC_STAGES; ++a) { mbar_init(bar_accfull + 8 * a, 1); mbar_init(bar_accfree + 8 * a, N_EPI); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -465,7 +466,7 @@ __global__ void __launch_bounds__(TMA ? NT_TMA : NT, 1) quantize_tc_kernel(Param
             }
         }
         __syncwarp();
-    } else if (TMA && warp == EPI_WARPS + 1 + N_PROD / 32) {
+    } else if (TMA && warp == EPI_WARPS + 1 + N_NORM / 32) {
         // ======================= TMA issue: one thread keeps the operand stages full =======================
         if (lane == 0) {
             int64_t o = int64_t(blockIdx.x) / p.tiles_per_lane, tl = int64_t(blockIdx.x) - o * p.tiles_per_lane;
@@ -485,27 +486,30 @@ __global__ void __launch_bounds__(TMA ? NT_TMA : NT, 1) quantize_tc_kernel(Param
         __syncwarp();
     } else if (TMA) {
         // ======================= norm warps: sum of squares of every row, read back from the stage =======================
-        // warp nw: K-block nw & 1 (64 columns), rows 32 (nw >> 1) + lane: eight consecutive rows hit eight different
-        // 16-byte columns of the swizzled tile, so the 128-bit reads are free of bank conflicts
-        const int nw = warp - (EPI_WARPS + 1), kblk = nw & 1, r = (nw >> 1) * 32 + lane;
+        // thread -> row 32 nw + lane, both 64-column blocks: eight consecutive rows hit eight different 16-byte columns
+        // of the swizzled tile, so the 128-bit reads are free of bank conflicts
+        const int nw = warp - (EPI_WARPS + 1), r = nw * 32 + lane;
         int it = 0;
         for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
             const int s = it % A_STAGES;
             if (!mbar_wait(bar_full + 8 * s, (it / A_STAGES) & 1, abort_flag, 7)) break;
-            const unsigned char* rowp = smem + OFF_A + s * OPER_BYTES + kblk * KBLK_BYTES + r * 128;
-            float a = 0.f;
+            const unsigned char* rowp = smem + OFF_A + s * OPER_BYTES + r * 128;
+            float a = 0.f, b = 0.f;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 const uint4 v = *reinterpret_cast<const uint4*>(rowp + ((c ^ (r & 7)) << 4));
+                const uint4 w = *reinterpret_cast<const uint4*>(rowp + KBLK_BYTES + ((c ^ (r & 7)) << 4));
                 const __half2* h = reinterpret_cast<const __half2*>(&v);
+                const __half2* g = reinterpret_cast<const __half2*>(&w);
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
-                    const float2 f = __half22float2(h[u]);
-                    a = fmaf(f.x, f.x, a);
-                    a = fmaf(f.y, f.y, a);
+                    const float2 f = __half22float2(h[u]), e = __half22float2(g[u]);
+                    a = fmaf(f.x, f.x, a); a = fmaf(f.y, f.y, a);
+                    b = fmaf(e.x, e.x, b); b = fmaf(e.y, e.y, b);
                 }
             }
-            reinterpret_cast<float*>(smem + OFF_NSQ)[s * 2 * TM + kblk * TM + r] = a;
+            float* nsq = reinterpret_cast<float*>(smem + OFF_NSQ) + s * 2 * TM;
+            nsq[r] = a; nsq[TM + r] = b;
             mbar_arrive(bar_nrm + 8 * s);        // release: the epilogue reads the sums after waiting on this barrier
             mbar_arrive(bar_afree + 8 * s);      // this thread is done reading the stage
         }
