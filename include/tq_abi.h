@@ -193,7 +193,8 @@ float tq_fp16_table_scale(const float* centroids_host, int n);
 
 /* Host-side tuning knobs of the split heuristic (process-wide; no reference counterpart):
  *   "decode_ctas_per_sm" 1..8, "decode_splits" 0 (auto)..448, "decode_force_general" 0/1,
- *   "decode_pdl" 0/1 (programmatic dependent launch: a call's prologue overlaps the previous kernel's tail).
+ *   "decode_pdl" 0/1 (programmatic dependent launch: a call's prologue overlaps the previous kernel's tail),
+ *   "quantize_tma" 0/1 (tensor-core quantize kernel: rows fetched by tiled TMA copies, or by loads in producer warps).
  * Changing them changes tq_decode_workspace_bytes for the same sizes. */
 int tq_set_tuning(const char* key, int value);
 

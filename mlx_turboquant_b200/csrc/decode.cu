@@ -28,6 +28,8 @@
 
 namespace tq {
 
+void set_quantize_tma(int on);      // quantize_tc.cu
+
 constexpr int GNW = 8;                 // warps per CTA of the general kernel
 
 // ---- shared memory plan ----------------------------------------------------------------------------------
@@ -696,6 +698,7 @@ extern "C" int tq_set_tuning(const char* key, int value) {
     else if (k == "decode_force_general" && (value == 0 || value == 1)) g_tune_force_general = value;
     else if (k == "decode_pdl" && (value == 0 || value == 1)) g_tune_pdl = value;
     else if (k == "decode_splits" && value >= 0 && value <= MAX_SPLITS - 64) g_tune_splits = value;
+    else if (k == "quantize_tma" && (value == 0 || value == 1)) set_quantize_tma(value);
     else return fail(TQ_ERR_INVALID, "tq_set_tuning: unknown key or bad value: %s=%d", key, value);
     return TQ_OK;
 }

@@ -178,6 +178,7 @@ constexpr int MARKED = 0x100;
 #endif
 constexpr int DIRECT_MAX_BITS = TQ_DIRECT_MAX_BITS;   // up to this width the boundaries are searched in registers, above it through the
                                                       // bin table (at 4 bits the register search costs more issue slots than the table's bank conflicts)
+static_assert(DIRECT_MAX_BITS <= 3, "the register search is written for at most seven boundaries");
 __device__ void build_bins(float2* bins, const float* bnd, int n_bnd, int tid, int nthreads) {
     for (int k = tid; k < NBINS; k += nthreads) {
         const float lo = (float(k) - 256.f - 1.5f) / 256.f, hi = (float(k) - 256.f + 1.5f) / 256.f;
@@ -194,43 +195,28 @@ __device__ void build_bins(float2* bins, const float* bnd, int n_bnd, int tid, i
     }
 }
 
-// Fast path of the boundary search: one table lookup and one compare.  The counts looked up are OR-ed into `seen`;
-// if the flag bit of a marked bin shows up there the group is redone with the counting loop.
-__device__ __forceinline__ uint32_t code_of(float yp, float rinv, float rbin, const float2* bins, uint32_t& seen) {
-    // bin index from the mantissa of (y * 256 + 256 + 2^23): exact rounding to nearest, no convert instruction.
-    // |y| <= 1 keeps the index below 513; NaN and infinity give index 0 (ten low mantissa bits are zero).
-    const float tt = fmaf(yp, rbin, 8388608.f + 256.f);
-    const uint32_t k = __float_as_uint(tt) & 0x3FFu;
-    const float2 e = bins[k * BIN_REP];
-    seen |= __float_as_uint(e.y);
-    return __float_as_uint(e.y) + ((yp * rinv) > e.x ? 1u : 0u);     // strict >, codebook.py:220-223
-}
-// Up to three bits: the boundaries live in registers and a binary search (one compare per bit) counts how many the
-// value exceeds - the same number the counting loop gives for a non-decreasing boundary list, NaN included (0).
+// Up to three bits the code is never formed: the boundaries live in registers, a binary search (one compare per bit)
+// decides how many of them the value exceeds - the number the counting loop gives for a non-decreasing boundary
+// list, NaN included (0) - and each level's outcome adds its bit, already shifted into place, to the group word
+// (eight codes per group, so a code never straddles two words while it is being built).
 template <int BITS>
-__device__ __forceinline__ uint32_t code_direct(float y, const float (&b)[15]) {
-    if (BITS == 4) {
-        const bool p1 = y > b[7];
-        const bool p2 = y > (p1 ? b[11] : b[3]);
-        const float l2 = p2 ? b[5] : b[1], h2 = p2 ? b[13] : b[9];
-        const bool p3 = y > (p1 ? h2 : l2);
-        // fourth level: boundary 8 p1 + 4 p2 + 2 p3
-        const float c0 = p3 ? b[2] : b[0], c1 = p3 ? b[6] : b[4], c2 = p3 ? b[10] : b[8], c3 = p3 ? b[14] : b[12];
-        const float d0 = p2 ? c1 : c0, d1 = p2 ? c3 : c2;
-        const bool p4 = y > (p1 ? d1 : d0);
-        return (p1 ? 8u : 0u) + (p2 ? 4u : 0u) + (p3 ? 2u : 0u) + (p4 ? 1u : 0u);
-    }
-    if (BITS == 1) return y > b[0] ? 1u : 0u;
-    if (BITS == 2) {
+__device__ __forceinline__ void add_code(uint32_t& grp, float y, const float (&b)[15], int sh) {
+    if (BITS == 1) {
+        if (y > b[0]) grp += 1u << sh;
+    } else if (BITS == 2) {
         const bool p1 = y > b[1];
         const bool p2 = y > (p1 ? b[2] : b[0]);
-        return (p1 ? 2u : 0u) + (p2 ? 1u : 0u);
+        if (p1) grp += 2u << sh;
+        if (p2) grp += 1u << sh;
+    } else {
+        const bool p1 = y > b[3];
+        const bool p2 = y > (p1 ? b[5] : b[1]);
+        const float lo = p2 ? b[2] : b[0], hi = p2 ? b[6] : b[4];
+        const bool p3 = y > (p1 ? hi : lo);
+        if (p1) grp += 4u << sh;
+        if (p2) grp += 2u << sh;
+        if (p3) grp += 1u << sh;
     }
-    const bool p1 = y > b[3];
-    const bool p2 = y > (p1 ? b[5] : b[1]);
-    const float lo = p2 ? b[2] : b[0], hi = p2 ? b[6] : b[4];
-    const bool p3 = y > (p1 ? hi : lo);
-    return (p1 ? 4u : 0u) + (p2 ? 2u : 0u) + (p3 ? 1u : 0u);
 }
 // Plain counting loop, kept out of line: only reached when two boundaries share a bin neighbourhood.
 __device__ __noinline__ uint32_t code_slow(float y, const float* raw_bnd, int n_bnd) {
@@ -289,9 +275,9 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
         lane_r += step_r; lane_o += step_o;
         if (lane_r >= wrap_r + (TMA ? row_in_tile : 0)) { lane_r -= wrap_r; ++lane_o; }
         const uint32_t t_hi = e.tmem_base + (uint32_t(quad * 32) << 16) + a * 256 + quarter * 32;
-        uint32_t words[4];                                      // 32 codes x at most 4 bits
+        uint32_t words[4], groups[4];                           // 32 codes x at most 4 bits; eight codes per group
 #pragma unroll
-        for (int i = 0; i < 4; ++i) words[i] = 0;
+        for (int i = 0; i < 4; ++i) words[i] = groups[i] = 0;
 #pragma unroll
         for (int cb = 0; cb < 2; ++cb) {                        // 16 coordinates at a time
             uint32_t vh[16], vl[16];
@@ -302,33 +288,44 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const float yp = fmaf(__uint_as_float(vl[i]), 1.f / 2048.f, __uint_as_float(vh[i]));
-                    vl[i] = code_direct<BITS>(yp * rinv, bnd);
+                    add_code<BITS>(groups[cb * 2 + (i >> 3)], yp * rinv, bnd, BITS * (i & 7));
                 }
             } else {
+                // table path: count-below times 16^k goes in with one multiply-add, the compare adds its bit in place
                 uint32_t seen = 0;
+                const uint32_t w0 = words[cb * 2], w1 = words[cb * 2 + 1];      // restored if the group has to be redone
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const float yp = fmaf(__uint_as_float(vl[i]), 1.f / 2048.f, __uint_as_float(vh[i]));
                     vh[i] = __float_as_uint(yp);
-                    vl[i] = code_of(yp, rinv, rbin, bins, seen);
+                    // bin index from the mantissa of (y * 256 + 256 + 2^23): exact rounding to nearest, no convert instruction.
+                    // |y| <= 1 keeps the index below 513; NaN and infinity give index 0 (ten low mantissa bits are zero).
+                    const float tt = fmaf(yp, rbin, 8388608.f + 256.f);
+                    const float2 en = bins[(__float_as_uint(tt) & 0x3FFu) * BIN_REP];
+                    seen |= __float_as_uint(en.y);
+                    uint32_t& w = words[cb * 2 + (i >> 3)];
+                    w += __float_as_uint(en.y) * (1u << (4 * (i & 7)));
+                    if ((yp * rinv) > en.x) w += 1u << (4 * (i & 7));          // strict >, codebook.py:220-223
                 }
-                if (__any_sync(0xffffffffu, (seen & MARKED) != 0)) {     // never taken with the shipped codebooks
+                if (__any_sync(0xffffffffu, (seen & MARKED) != 0)) {     // a marked bin was hit: redo the group with the counting loop
+                    words[cb * 2] = w0; words[cb * 2 + 1] = w1;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) vl[i] = code_slow(__uint_as_float(vh[i]) * rinv, raw_bnd, n_bnd);
+                    for (int i = 0; i < 16; ++i)
+                        words[cb * 2 + (i >> 3)] |= code_slow(__uint_as_float(vh[i]) * rinv, raw_bnd, n_bnd) << (4 * (i & 7));
                 }
             }
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const uint32_t c = vl[i];
-                const int j = cb * 16 + i;                      // coordinate inside this quarter
-                if (BITS == 4) words[j >> 3] |= c << (4 * (j & 7));
-                else if (BITS == 2) words[j >> 4] |= c << (2 * (j & 15));
-                else if (BITS == 1) words[j >> 5] |= c << (j & 31);
-                else {                                          // 3 bits: 8 codes -> 24 bits, little-endian stream
-                    const int bit = 3 * j, w = bit >> 5, sh = bit & 31;
-                    words[w] |= c << sh;
-                    if (sh > 29) words[w + 1] |= c >> (32 - sh);
-                }
+        }
+        if (BITS <= DIRECT_MAX_BITS) {
+            // groups[g] holds codes 8g .. 8g+7 in 8 * BITS bits: lay them out as the little-endian bit stream
+            if (BITS == 3) {
+                words[0] = groups[0] | (groups[1] << 24);
+                words[1] = (groups[1] >> 8) | (groups[2] << 16);
+                words[2] = (groups[2] >> 16) | (groups[3] << 8);
+            } else if (BITS == 2) {
+                words[0] = groups[0] | (groups[1] << 16);
+                words[1] = groups[2] | (groups[3] << 16);
+            } else {
+                words[0] = groups[0] | (groups[1] << 8) | (groups[2] << 16) | (groups[3] << 24);
             }
         }
         tc_fence_before();
@@ -596,6 +593,9 @@ __global__ void __launch_bounds__(TMA ? NT_TMA : NT, 1) quantize_tc_kernel(Param
 
 using namespace tq;
 
+static int g_quantize_tma = 1;     // tq_set_tuning("quantize_tma", 0 / 1)
+namespace tq { void set_quantize_tma(int on) { g_quantize_tma = on ? 1 : 0; } }
+
 // Takes the call when it fits the tensor-core kernel: fp16 rows, d = 128, 16-byte aligned rows, no QJL sketch,
 // no rotated-row output.  Otherwise reports "not handled" and the caller uses the general CUDA-core kernel.
 int tq_quantize_pack_tc(const tq_quantize_args* q, cudaStream_t s, bool* handled) {
@@ -633,11 +633,12 @@ int tq_quantize_pack_tc(const tq_quantize_args* q, cudaStream_t s, bool* handled
     // the 128-byte-swizzled layout the MMA descriptors describe; rows past a lane's end read as zeros.
     CUtensorMap tmap{};
     bool use_tma = false;
-    static int tma_off = -1;
-    if (tma_off < 0) {
+    static int env_off = -1;
+    if (env_off < 0) {
         const char* e = getenv("TQ_DISABLE_TMA");
-        tma_off = (e && e[0] == '1') ? 1 : 0;
+        env_off = (e && e[0] == '1') ? 1 : 0;
     }
+    const bool tma_off = env_off || !g_quantize_tma;
     static PFN_cuTensorMapEncodeTiled encode = nullptr;
     static bool looked_up = false;
     if (!looked_up) {

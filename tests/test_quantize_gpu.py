@@ -246,3 +246,32 @@ def test_tensor_core_and_general_kernels_agree(tables):
     p2, _, n2 = kernels.quantize_pack(x.float(), rot, b, 3)
     np.testing.assert_allclose(host(n1), host(n2), rtol=2e-6)
     assert (host(p1) != host(p2)).mean() < 1e-4
+
+
+def test_tensor_core_quantize_tma_and_producer_loads_agree(tables):
+    """The two ways the tcgen05 kernel fetches its rows (tiled TMA copies; loads in producer warps) feed the same
+    arithmetic: same codes and norms, on contiguous rows and on rows sliced out of a larger buffer with a ragged tail."""
+    from mlx_turboquant_b200 import kernels
+    from mlx_turboquant_b200.codebook import get_codebook
+    from mlx_turboquant_b200.rotation import get_rotation_matrix
+    rs = np.random.RandomState(5)
+    rot = get_rotation_matrix(128)
+    buf = cu(kv_like(rs, (2, 3, 1500, 128)))
+    for x in (buf, buf[:, :, 7:7 + 1153]):
+        for kb in (4, 3, 2, 3.5):
+            hi, lo = kernels.split_bits(kb)
+            bh = get_codebook(128, hi)[1]
+            bl = get_codebook(128, lo)[1] if lo else None
+            a = kernels.quantize_pack(x, rot, bh, hi, bl, lo)
+            kernels.set_tuning("quantize_tma", 0)
+            try:
+                b = kernels.quantize_pack(x, rot, bh, hi, bl, lo)
+            finally:
+                kernels.set_tuning("quantize_tma", 1)
+            for u, v in zip(a, b):                          # (codes hi, codes lo, norms)
+                if u is None:
+                    assert v is None
+                elif u.dtype == torch.uint8:
+                    assert (u != v).float().mean() < 1e-5       # the sums of squares are added in a different order: a norm
+                else:                                           # may differ in its last bit and tip a value over a boundary
+                    torch.testing.assert_close(u, v, rtol=2e-6, atol=0)
