@@ -38,7 +38,7 @@ constexpr int EPI_WARPS = N_EPI / 32;            // 16: TMEM lane quadrant = war
 constexpr int NT = N_EPI + 32 + N_PROD;          // 800
 constexpr int N_NORM = 128;                       // TMA variant: threads that read the rows back for the norms (one row each)
 constexpr int NT_TMA = N_EPI + 32 + N_NORM + 32; // 704: the last warp's first lane feeds the operand stages by TMA
-constexpr int BIN_REP = 4;                       // copies of every lookup-table entry (lane & 3 picks one): fewer bank conflicts
+constexpr int BIN_REP = 8;                       // copies of every lookup-table entry (lane & 7 picks one): fewer bank conflicts
 constexpr int KBLK_BYTES = TM * 128;             // one 64-column K-block of a 128-row operand: 16 KB
 constexpr int OPER_BYTES = 2 * KBLK_BYTES;       // 32 KB per operand tile
 constexpr int NBINS = 516;                       // 513 used + guard
@@ -48,8 +48,8 @@ constexpr uint32_t WAIT_LIMIT = 4u << 20;        // bounded spin: a few hundred 
 constexpr int OFF_A = 0;                                   // A_STAGES x 32 KB, 1024-byte aligned
 constexpr int OFF_RHI = OFF_A + A_STAGES * OPER_BYTES;     // 32 KB
 constexpr int OFF_RLO = OFF_RHI + OPER_BYTES;              // 32 KB
-constexpr int OFF_BINS = OFF_RLO + OPER_BYTES;             // 2 tables x NBINS x BIN_REP x 8 B
-constexpr int OFF_BND = OFF_BINS + 2 * NBINS * BIN_REP * 8; // 2 x 16 floats: raw boundaries (slow path)
+constexpr int OFF_BINS = OFF_RLO + OPER_BYTES;             // NBINS x BIN_REP x 8 B: the table of the 4-bit codebook (only bits_hi can be 4)
+constexpr int OFF_BND = OFF_BINS + NBINS * BIN_REP * 8;    // 2 x 16 floats: raw boundaries
 constexpr int OFF_NSQ = OFF_BND + 128;                     // A_STAGES x 2 x 128 floats: partial sums of squares
 constexpr int OFF_BAR = OFF_NSQ + A_STAGES * 2 * TM * 4;   // mbarriers
 constexpr int OFF_MISC = OFF_BAR + 16 * 8;                 // tmem base, abort flag (barriers: 3 + 3 + 2 + 2 + 3 norm-ready)
@@ -235,7 +235,7 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
     const Params& p = e.p;
     const int quad = e.warp & 3, quarter = e.warp >> 2, row_in_tile = quad * 32 + e.lane;
     const bool second = p.bits_lo && quarter >= 2;              // fractional mode: coordinates [64, 128) use the low-bit codebook
-    const float2* bins = reinterpret_cast<const float2*>(e.smem + OFF_BINS) + (second ? NBINS * BIN_REP : 0) + (e.lane & (BIN_REP - 1));
+    const float2* bins = reinterpret_cast<const float2*>(e.smem + OFF_BINS) + (e.lane & (BIN_REP - 1));      // 4-bit side only
     const float* raw_bnd = reinterpret_cast<const float*>(e.smem + OFF_BND) + (second ? 16 : 0);
     constexpr int n_bnd = (1 << BITS) - 1;
     constexpr int WBYTES = 32 * BITS / 8;                       // bytes this thread produces per row (32 coordinates)
@@ -411,8 +411,7 @@ __global__ void __launch_bounds__(TMA ? NT_TMA : NT, 1) quantize_tc_kernel(Param
             raw[tid] = (src != nullptr && i < nb) ? src[i] : INFINITY;
         }
         __syncthreads();
-        build_bins(reinterpret_cast<float2*>(smem + OFF_BINS), raw, (1 << p.bits_hi) - 1, tid, NTHREADS);
-        if (p.bits_lo) build_bins(reinterpret_cast<float2*>(smem + OFF_BINS) + NBINS * BIN_REP, raw + 16, (1 << p.bits_lo) - 1, tid, NTHREADS);
+        if (p.bits_hi > DIRECT_MAX_BITS) build_bins(reinterpret_cast<float2*>(smem + OFF_BINS), raw, (1 << p.bits_hi) - 1, tid, NTHREADS);
     }
     if (warp == EPI_WARPS) {              // one warp owns the TMEM allocation: 2 stages x (hi + lo) x 128 columns
         tmem_alloc(sbase + OFF_MISC, 512);
@@ -601,6 +600,7 @@ namespace tq { void set_quantize_tma(int on) { g_quantize_tma = on ? 1 : 0; } }
 int tq_quantize_pack_tc(const tq_quantize_args* q, cudaStream_t s, bool* handled) {
     *handled = false;
     if (q->d != tc::D || q->x_dtype != TQ_F16 || q->qjl_bits || q->y_out) return TQ_OK;
+    if (q->bits_lo > tc::DIRECT_MAX_BITS) return TQ_OK;      // the kernel keeps one bin table: only the high-bit half may need it
     if (!aligned(q->x, 16) || q->x_row_stride % 8 || q->x_lane_stride % 8 || !aligned(q->rot, 16)) return TQ_OK;
     static int disabled = -1;
     if (disabled < 0) {
