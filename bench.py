@@ -292,6 +292,109 @@ def bench_c3(torch, dev, steps, warmup, peak):
             "kernel": "decode_attn_kernel<96, qjl> (general kernel: unpack to shared memory, ldmatrix)"}
 
 
+def run_c4(args):
+    """`--workload c4`: end-to-end batched decoding of a random-init Llama-3.1-8B-shaped model (32 layers, hidden 4096,
+    32 query / 8 KV heads, head_dim 128, SwiGLU 14336, vocabulary 128256, bf16 weights N(0, 0.02)) through compressed
+    caches (4-bit keys, 2-bit values, 128-token sink, 128 recent tokens).  `--c4-batch` sequences in total, dealt evenly
+    to the GPUs (every GPU holds the full weights; no collective); each sequence starts from a `--c4-prompt`-token
+    context.  The context's cache contents are seeded synthetic K/V fed through `cache.update` in 4096-token pieces
+    (a real prefill of 2 M random tokens would produce K/V of the same kind at a cost that is not what this config
+    measures).  One STEP = one new token for every sequence: embedding, 32 x (projections, RoPE, cache.update,
+    cache.attend, output projection, SwiGLU), logits, greedy pick.  GEMMs and element-wise work are torch library calls;
+    `update` and `attend` are this repository's kernels."""
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    from mlx_turboquant_b200 import _lib, apply_turboquant, sharding
+    from mlx_turboquant_b200.consumer import LlamaShaped, ModelArgs
+    _lib.lib()
+    peak, peak_src = peaks()
+    assert args.c4_batch % world == 0
+    b, prompt, piece = args.c4_batch // world, args.c4_prompt, 4096
+    margs = ModelArgs(num_hidden_layers=args.layers)
+    model = LlamaShaped(margs, dtype=torch.bfloat16, device=dev, seed=0)
+    apply_turboquant(model, key_bits=4, value_bits=2, residual_window=RW, fp16_sink_size=SINK, auto_detect_outliers=False)
+    caches = model.make_cache()
+    for li, c in enumerate(caches):
+        g = torch.Generator(device=dev).manual_seed(4000 + 64 * rank + li)
+        for s0 in range(0, prompt, piece):
+            n = min(piece, prompt - s0)
+            kv = []
+            for _ in range(2):
+                x = torch.randn(b, HKV, n, D, device=dev, generator=g, dtype=torch.bfloat16)
+                kv.append(x * torch.exp(0.5 * torch.randn(b, HKV, n, 1, device=dev, generator=g)).to(torch.bfloat16))
+            c.update(kv[0], kv[1])
+        del kv, x
+    tok = torch.randint(0, margs.vocab_size, (b, 1), device=dev, generator=torch.Generator(device=dev).manual_seed(5000 + rank))
+
+    def step(t):
+        return model(t, cache=caches, packed=True)[:, -1].argmax(-1, keepdim=True)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        tok = step(tok)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        e0.record()
+        for _ in range(args.steps):
+            tok = step(tok)
+        e1.record()
+        barrier()
+    ms_step = sharding.job_time_ms(e0.elapsed_time(e1) / args.steps, dev)
+
+    # the attention share: the same caches, `attend` alone (one launch per layer)
+    c0 = caches[0]
+    q = (torch.randn(b, HQ, 1, D, device=dev) / D ** 0.5).to(torch.bfloat16)
+    for c in caches:
+        c.attend(q)
+    torch.cuda.synchronize(dev)
+    e0.record()
+    reps = 3
+    for _ in range(reps):
+        for c in caches:
+            c.attend(q)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    attn_us = e0.elapsed_time(e1) * 1e3 / (reps * len(caches))
+    attn_bytes = (b * HKV * c0._compressed_len * (D // 2 + 4 + D // 4 + 4) + b * HKV * (c0._sink_len + c0._fp16_len) * 2 * D * 2
+                  + b * HQ * D * 4)
+    attn_gbs = attn_bytes / (attn_us * 1e-6) / 1e9
+    weight_bytes = sum(p.numel() * p.element_size() for p in model.parameters()) - model.embed_tokens.weight.numel() * 2
+    line = {
+        "metric": "e2e_decode_tokens_per_s", "value": args.c4_batch * 1e3 / ms_step, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16 weights and activations; attention f32 accumulate over packed 4-bit keys / 2-bit values",
+        "data": "synthetic",
+        "config": {"workload": "llama31_8b_shaped_batched_decode_k4v2_sink128_rw128", "layers": args.layers, "batch_total": args.c4_batch,
+                   "batch_per_gpu": b, "context_at_start": prompt, "context_at_end": caches[0].offset,
+                   "prompt": "cache contents from seeded synthetic K/V (no prefill pass)", "l2_policy": "inputs larger than L2",
+                   "sharding": "sequences dealt to the GPUs, full weights on each, no collective"},
+        "gpu_launches": 2 * args.layers * args.steps,
+        "clocks": clk.summary(),
+        "attention": {"us_per_layer_step": attn_us, "algorithmic_bytes_per_launch": attn_bytes, "hbm_gbs": attn_gbs, "frac_of_peak": attn_gbs / peak,
+                      "peak": peak, "peak_source": peak_src, "share_of_step": attn_us * args.layers / (ms_step * 1e3)},
+        "hbm_floor_ms_per_step": (attn_bytes * args.layers + weight_bytes) / (peak * 1e9) * 1e3,
+        "cache_bytes_per_gpu": sum(c.nbytes for c in caches), "weight_bytes_read_per_step": weight_bytes,
+    }
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_b200(args):
     import torch
     import torch.distributed as dist
@@ -460,9 +563,15 @@ def main():
     ap.add_argument("--split-heads", action="store_true", help="N > 1: shard ONE sequence by KV head (strong scaling) instead of one sequence per GPU")
     ap.add_argument("--no-gather", action="store_true", help="with --split-heads: leave every GPU with its own heads' outputs")
     ap.add_argument("--no-secondary", action="store_true", help="skip the quantize+pack leg")
+    ap.add_argument("--workload", default="c1", choices=("c1", "c4"), help="c1: the headline layer-decode benchmark; c4: end-to-end "
+                    "batched decoding of a Llama-3.1-8B-shaped model through compressed caches (about 75 GB on the device at the defaults)")
+    ap.add_argument("--c4-batch", type=int, default=64, help="c4: sequences in total over all GPUs")
+    ap.add_argument("--c4-prompt", type=int, default=32768, help="c4: context length every sequence starts from")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "c4":
+        run_c4(args)
     else:
         run_b200(args)
 

@@ -290,7 +290,16 @@ class TurboQuantKVCache:
                                   out_hi=side.hi, out_lo=side.lo, out_norms=side.norms,
                                   out_offset=self._compressed_len, qjl=self._qjl_args(side))
         rem = self._fp16_len - n
-        if rem > 0:
+        # A long prefill leaves buffers sized for the whole prompt; once most of it is packed they are swapped for
+        # buffers of the size a fresh cache would get for what remains (batch 64 x 32K tokens: 17 GB per layer otherwise).
+        small_cap = max(rem, self.residual_window * 2) + 256
+        if self._fp16_capacity > 4 * small_cap:
+            nk = torch.zeros((b, h, small_cap, d), dtype=self.keys.dtype, device=dev)
+            nv = torch.zeros((b, h, small_cap, d), dtype=self.values.dtype, device=dev)
+            if rem > 0:
+                self._append(nk, nv, self.keys[:, :, n:self._fp16_len], self.values[:, :, n:self._fp16_len], 0)
+            self.keys, self.values, self._fp16_capacity = nk, nv, small_cap
+        elif rem > 0:
             for buf in (self.keys, self.values):
                 tail = buf[:, :, n:self._fp16_len]
                 buf[:, :, :rem] = tail.clone() if n < rem else tail

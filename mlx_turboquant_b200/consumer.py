@@ -1,0 +1,164 @@
+"""A minimal Llama-shaped consumer of the cache protocol: the caller on the far side of the hot path.
+
+The reference never runs attention itself; mlx-lm's Llama ``Attention.__call__`` does
+(docs/attention_source_dump.txt:70-98): project, RoPE at ``cache.offset``, ``cache.update_and_fetch``,
+softmax attention, output projection.  This module restates that caller on torch so the cache can be
+exercised end to end: RMSNorm, rotary embedding (non-traditional layout, base ``rope_theta``), grouped-query
+attention, SwiGLU, tied to nothing but ``torch`` library calls (GEMMs and the dense prefill attention are
+library work, not part of the compressed path).  Two ways through the cache:
+
+* dense (the reference's only way): ``keys, values = cache.update_and_fetch(k, v)`` then softmax attention;
+* packed: for one new token per sequence, ``cache.update(k, v)`` then ``cache.attend(q)`` - attention straight
+  from packed storage.  Multi-token calls (prefill) always take the dense way.
+
+``generate`` is the greedy loop of the reference's command line (cli.py:81-104) without its tokenizer.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+
+@dataclass
+class ModelArgs:
+    """Field names follow the Hugging Face / mlx-lm config the reference reads (patch.py:13-86)."""
+
+    hidden_size: int = 4096
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    intermediate_size: int = 14336
+    rope_theta: float = 500000.0
+    vocab_size: int = 128256
+    rms_norm_eps: float = 1e-5
+
+
+def _rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * weight
+
+
+def rope(x: torch.Tensor, offset: int, theta: float) -> torch.Tensor:
+    """Rotary embedding, half-split layout (``traditional=False``), positions ``offset ... offset+L-1``.
+
+    ``x`` is (B, H, L, D); computed in float32 and cast back.
+    """
+    _, _, L, D = x.shape
+    half = D // 2
+    inv = theta ** (-torch.arange(0, half, device=x.device, dtype=torch.float32) / half)
+    ang = torch.arange(offset, offset + L, device=x.device, dtype=torch.float32)[:, None] * inv[None, :]
+    cos, sin = ang.cos(), ang.sin()
+    xf = x.float()
+    a, b = xf[..., :half], xf[..., half:]
+    return torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1).to(x.dtype)
+
+
+class Attention(torch.nn.Module):
+    def __init__(self, args: ModelArgs, dtype, device):
+        super().__init__()
+        self.n_heads, self.n_kv_heads, self.head_dim = args.num_attention_heads, args.num_key_value_heads, args.head_dim
+        self.scale = self.head_dim ** -0.5
+        self.rope_theta = args.rope_theta
+        kw = dict(bias=False, dtype=dtype, device=device)
+        # one fused projection for q, k and v (same arithmetic as three separate matrices)
+        self.qkv_proj = torch.nn.Linear(args.hidden_size, (self.n_heads + 2 * self.n_kv_heads) * self.head_dim, **kw)
+        self.o_proj = torch.nn.Linear(self.n_heads * self.head_dim, args.hidden_size, **kw)
+
+    def forward(self, x: torch.Tensor, cache=None, packed: bool = True) -> torch.Tensor:
+        B, L, _ = x.shape
+        hq, hkv, d = self.n_heads, self.n_kv_heads, self.head_dim
+        qkv = self.qkv_proj(x).view(B, L, hq + 2 * hkv, d).transpose(1, 2)            # (B, heads, L, d)
+        queries, keys, values = qkv[:, :hq], qkv[:, hq:hq + hkv], qkv[:, hq + hkv:]
+        offset = cache.offset if cache is not None else 0                               # read before the update
+        queries, keys = rope(queries, offset, self.rope_theta), rope(keys, offset, self.rope_theta)
+        if cache is not None and packed and L == 1 and hasattr(cache, "attend"):
+            cache.update(keys.contiguous(), values.contiguous())
+            out = cache.attend(queries.contiguous(), self.scale)                       # (B, hq, 1, d)
+        else:
+            if cache is not None:
+                keys, values = cache.update_and_fetch(keys.contiguous(), values.contiguous())
+            q = queries.float() if keys.dtype == torch.float32 else queries
+            T = keys.shape[2]
+            if L == 1:
+                mask = None
+            else:                                                                       # causal, aligned to the end
+                pos = torch.arange(T - L, T, device=x.device)
+                mask = torch.arange(T, device=x.device)[None, :] <= pos[:, None]
+            out = F.scaled_dot_product_attention(q, keys.to(q.dtype), values.to(q.dtype), attn_mask=mask, scale=self.scale,
+                                                 enable_gqa=hq != hkv).to(x.dtype)
+        return self.o_proj(out.transpose(1, 2).reshape(B, L, hq * d))
+
+
+class Block(torch.nn.Module):
+    def __init__(self, args: ModelArgs, dtype, device):
+        super().__init__()
+        kw = dict(bias=False, dtype=dtype, device=device)
+        self.eps = args.rms_norm_eps
+        self.self_attn = Attention(args, dtype, device)
+        self.gate_up_proj = torch.nn.Linear(args.hidden_size, 2 * args.intermediate_size, **kw)
+        self.down_proj = torch.nn.Linear(args.intermediate_size, args.hidden_size, **kw)
+        self.input_layernorm = torch.nn.Parameter(torch.ones(args.hidden_size, dtype=dtype, device=device))
+        self.post_attention_layernorm = torch.nn.Parameter(torch.ones(args.hidden_size, dtype=dtype, device=device))
+
+    def forward(self, x, cache=None, packed=True):
+        h = x + self.self_attn(_rms_norm(x, self.input_layernorm, self.eps), cache, packed)
+        gate, up = self.gate_up_proj(_rms_norm(h, self.post_attention_layernorm, self.eps)).chunk(2, dim=-1)
+        return h + self.down_proj(F.silu(gate) * up)
+
+
+class LlamaShaped(torch.nn.Module):
+    """Random-init decoder with Llama-3.1 structure; ``model(tokens, cache=[...])`` like an mlx-lm model."""
+
+    def __init__(self, args: ModelArgs | None = None, dtype=torch.bfloat16, device="cuda", seed: int = 0, std: float = 0.02):
+        super().__init__()
+        self.args = args or ModelArgs()
+        a = self.args
+        self.embed_tokens = torch.nn.Embedding(a.vocab_size, a.hidden_size, dtype=dtype, device=device)
+        self.layers = torch.nn.ModuleList(Block(a, dtype, device) for _ in range(a.num_hidden_layers))
+        self.norm = torch.nn.Parameter(torch.ones(a.hidden_size, dtype=dtype, device=device))
+        self.lm_head = torch.nn.Linear(a.hidden_size, a.vocab_size, bias=False, dtype=dtype, device=device)
+        g = torch.Generator(device=device).manual_seed(seed)
+        with torch.no_grad():
+            for p in self.parameters():
+                if p.dim() > 1:
+                    p.normal_(0.0, std, generator=g)
+
+    def make_cache(self):
+        """Default (uncompressed) caches; ``apply_turboquant`` replaces this on the instance."""
+        from .patch import KVCache
+        return [KVCache() for _ in self.layers]
+
+    @torch.no_grad()
+    def forward(self, tokens: torch.Tensor, cache=None, packed: bool = True, last_only: bool = False) -> torch.Tensor:
+        h = self.embed_tokens(tokens)
+        for i, layer in enumerate(self.layers):
+            h = layer(h, cache[i] if cache is not None else None, packed)
+        if last_only:
+            h = h[:, -1:]
+        return self.lm_head(_rms_norm(h, self.norm, self.args.rms_norm_eps))
+
+
+@torch.no_grad()
+def generate(model: LlamaShaped, prompt: torch.Tensor, max_new_tokens: int, cache=None, packed: bool = True,
+             prefill_chunk: int = 0) -> torch.Tensor:
+    """Greedy decoding: prefill ``prompt`` (B, T), then one token per step; returns (B, max_new_tokens).
+
+    ``prefill_chunk`` > 0 feeds the prompt in pieces of that many tokens (bounded activation memory).
+    """
+    cache = cache if cache is not None else model.make_cache()
+    T = prompt.shape[1]
+    step = prefill_chunk if prefill_chunk > 0 else T
+    logits = None
+    for s in range(0, T, step):
+        logits = model(prompt[:, s:s + step], cache=cache, packed=packed, last_only=True)
+    out = []
+    tok = logits[:, -1].argmax(-1, keepdim=True)
+    for i in range(max_new_tokens):
+        out.append(tok)
+        if i + 1 < max_new_tokens:
+            tok = model(tok, cache=cache, packed=packed, last_only=True)[:, -1].argmax(-1, keepdim=True)
+    return torch.cat(out, dim=1)

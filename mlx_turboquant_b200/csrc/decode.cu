@@ -212,15 +212,67 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
         const int vw_hi = packed_bytes(v_half, p.vb_hi), vw_lo = p.vb_lo ? packed_bytes(D - v_half, p.vb_lo) : 0;
         const int64_t tile_lo = int64_t(split) * p.p_tps;
         const int64_t tile_hi = min(tile_lo + p.p_tps, (p.c_len + TILE - 1) / TILE);
-        for (int64_t tile = tile_lo + warp; tile < tile_hi; tile += NW) {
+        // Word-at-a-time path: the packed words of tile i+1 are loaded (into registers) before tile i is unpacked, and a
+        // tile's norms / sketches are requested before its unpacking starts, so global latency overlaps shared-memory work.
+        constexpr int KWPL = (TILE * D / 2 / 4) / 32, VWPL = (TILE * D / 4 / 4 + 31) / 32;     // words per lane: keys, values
+        constexpr bool PREFETCH = D <= 128;                                                     // (register budget)
+        uint32_t kw[KWPL], vw[VWPL];
+        auto load_words = [&](int64_t tile, uint32_t (&kd)[KWPL], uint32_t (&vd)[VWPL]) {
             const int64_t tok0 = tile * TILE;
+            const bool in = tile < tile_hi;
             if (fast_k) {
                 // 16 rows of D/2 bytes are contiguous: word i of the tile = row (4 i) / (D/2), bytes (4 i) % (D/2) ...
                 const uint32_t* src = reinterpret_cast<const uint32_t*>(p.k_hi + (kvl * p.c_ls + tok0) * (D / 2));
 #pragma unroll
-                for (int j = 0; j < (TILE * D / 2 / 4) / 32; ++j) {
+                for (int j = 0; j < KWPL; ++j) {
+                    const int i = lane + 32 * j, r = (4 * i) / (D / 2);
+                    kd[j] = (in && tok0 + r < p.c_len) ? __ldg(src + i) : 0u;
+                }
+            }
+            if (fast_v) {
+                const uint32_t* src = reinterpret_cast<const uint32_t*>(p.v_hi + (kvl * p.c_ls + tok0) * (D / 4));
+#pragma unroll
+                for (int j = 0; j < VWPL; ++j) {
+                    const int i = lane + 32 * j, r = (4 * i) / (D / 4);
+                    vd[j] = (in && i < TILE * D / 4 / 4 && tok0 + r < p.c_len) ? __ldg(src + i) : 0u;
+                }
+            }
+        };
+        if (PREFETCH) load_words(tile_lo + warp, kw, vw);
+        for (int64_t tile = tile_lo + warp; tile < tile_hi; tile += NW) {
+            const int64_t tok0 = tile * TILE;
+            const bool ok0 = tok0 + g < p.c_len, ok1 = tok0 + g + 8 < p.c_len;
+            const int64_t n0 = kvl * p.c_ls + (ok0 ? tok0 + g : 0), n1 = kvl * p.c_ls + (ok1 ? tok0 + g + 8 : 0);
+            const float kn0 = __ldg(p.k_norms + n0), kn1 = __ldg(p.k_norms + n1);
+            const float vn0 = __ldg(p.v_norms + n0), vn1 = __ldg(p.v_norms + n1);
+            uint32_t zk0 = 0, zk1 = 0, zv[4] = {0, 0, 0, 0};
+            float gk0 = 0.f, gk1 = 0.f, gv0 = 0.f, gv1 = 0.f;
+            if (QJL) {
+                zk0 = ok0 ? __ldg(p.k_qbits + n0) : 0u; zk1 = ok1 ? __ldg(p.k_qbits + n1) : 0u;
+                gk0 = ok0 ? __ldg(p.k_qgamma + n0) * (QJL_C / D) : 0.f; gk1 = ok1 ? __ldg(p.k_qgamma + n1) * (QJL_C / D) : 0.f;
+                gv0 = ok0 ? __ldg(p.v_qgamma + n0) : 0.f; gv1 = ok1 ? __ldg(p.v_qgamma + n1) : 0.f;
+                const int64_t nb = kvl * p.c_ls + tok0;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int tk = 2 * t + (u & 1) + (u >> 1) * 8;                    // tokens 2t, 2t+1, 2t+8, 2t+9
+                    zv[u] = tok0 + tk < p.c_len ? __ldg(p.v_qbits + nb + tk) : 0u;
+                }
+            }
+            uint32_t kc[KWPL], vc[VWPL];
+            if (PREFETCH) {
+#pragma unroll
+                for (int j = 0; j < KWPL; ++j) kc[j] = kw[j];
+#pragma unroll
+                for (int j = 0; j < VWPL; ++j) vc[j] = vw[j];
+                load_words(tile + NW, kw, vw);          // next tile of this warp (zeros past the end)
+            } else {
+                load_words(tile, kc, vc);
+            }
+            if (fast_k) {
+#pragma unroll
+                for (int j = 0; j < KWPL; ++j) {
                     const int i = lane + 32 * j, r = (4 * i) / (D / 2), cb = 4 * i - r * (D / 2);
-                    const uint32_t w = tok0 + r < p.c_len ? __ldg(src + i) : 0u;
+                    const uint32_t w = kc[j];
                     uint4 o;
                     o.x = t4[w & 255u]; o.y = t4[(w >> 8) & 255u]; o.z = t4[(w >> 16) & 255u]; o.w = t4[w >> 24];
                     if (tok0 + r >= p.c_len) o = make_uint4(0, 0, 0, 0);
@@ -228,13 +280,12 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
                 }
             }
             if (fast_v) {
-                const uint32_t* src = reinterpret_cast<const uint32_t*>(p.v_hi + (kvl * p.c_ls + tok0) * (D / 4));
 #pragma unroll
-                for (int j = 0; j < (TILE * D / 4 / 4 + 31) / 32; ++j) {
+                for (int j = 0; j < VWPL; ++j) {
                     const int i = lane + 32 * j, r = (4 * i) / (D / 4), cb = 4 * i - r * (D / 4);
                     if (i < TILE * D / 4 / 4) {
                         const bool live = tok0 + r < p.c_len;
-                        const uint32_t w = live ? __ldg(src + i) : 0u;
+                        const uint32_t w = vc[j];
                         const uint2 a = t2[w & 255u], b = t2[(w >> 8) & 255u], c = t2[(w >> 16) & 255u], e = t2[w >> 24];
                         uint4 o0 = make_uint4(a.x, a.y, b.x, b.y), o1 = make_uint4(c.x, c.y, e.x, e.y);
                         if (!live) { o0 = make_uint4(0, 0, 0, 0); o1 = o0; }
@@ -267,10 +318,6 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
                     if (!fast_v) *reinterpret_cast<__half2*>(Vs + r * LD + j) = vv;
                 }
             }
-            const bool ok0 = tok0 + g < p.c_len, ok1 = tok0 + g + 8 < p.c_len;
-            const int64_t n0 = kvl * p.c_ls + (ok0 ? tok0 + g : 0), n1 = kvl * p.c_ls + (ok1 ? tok0 + g + 8 : 0);
-            const float kn0 = __ldg(p.k_norms + n0), kn1 = __ldg(p.k_norms + n1);
-            const float vn0 = __ldg(p.v_norms + n0), vn1 = __ldg(p.v_norms + n1);
             __syncwarp();
             if (!QJL) {
                 tile_from_smem<D>(Ks, Vs, bq, kn0, kn1, vn0, vn1, ok0, ok1, st, lane);
@@ -286,8 +333,6 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
                         mma16816(s, a[0], a[1], a[2], a[3], bq[ks][0], bq[ks][1]);
                     }
                 }
-                const uint32_t zk0 = ok0 ? __ldg(p.k_qbits + n0) : 0u, zk1 = ok1 ? __ldg(p.k_qbits + n1) : 0u;
-                const float gk0 = ok0 ? __ldg(p.k_qgamma + n0) * (QJL_C / D) : 0.f, gk1 = ok1 ? __ldg(p.k_qgamma + n1) * (QJL_C / D) : 0.f;
 #pragma unroll
                 for (int ks = 0; ks < QM / 16; ++ks) {
                     const int sh = ks * 16 + 2 * t;
@@ -309,16 +354,8 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
                     }
                 }
                 // sketch rows of the output: z[p][h] += sum_t sign_p(t) * (p_t * gamma_v[t]); P^T operand as for the values
-                const float gv0 = ok0 ? __ldg(p.v_qgamma + n0) : 0.f, gv1 = ok1 ? __ldg(p.v_qgamma + n1) : 0.f;
                 const uint32_t bz0 = movm_t(pack_h2(fminf(pr[0] * gv0, 65504.f), fminf(pr[1] * gv0, 65504.f)));
                 const uint32_t bz1 = movm_t(pack_h2(fminf(pr[2] * gv1, 65504.f), fminf(pr[3] * gv1, 65504.f)));
-                const int64_t nb = kvl * p.c_ls + tok0;
-                uint32_t zv[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int tk = 2 * t + (u & 1) + (u >> 1) * 8;                    // tokens 2t, 2t+1, 2t+8, 2t+9
-                    zv[u] = tok0 + tk < p.c_len ? __ldg(p.v_qbits + nb + tk) : 0u;
-                }
 #pragma unroll
                 for (int mt = 0; mt < QM / 16; ++mt) {
                     const int r0 = mt * 16 + g;                                         // sketch rows r0 and r0 + 8
