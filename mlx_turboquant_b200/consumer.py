@@ -38,23 +38,28 @@ class ModelArgs:
 
 
 def _rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    return F.rms_norm(x, (x.shape[-1],), weight, eps)
+
+
+def rope_tables(offset: int, length: int, dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """(cos | cos) and (-sin | sin) rows, float32 (length, dim), for positions ``offset ... offset+length-1``."""
+    half = dim // 2
+    inv = theta ** (-torch.arange(0, half, device=device, dtype=torch.float32) / half)
+    ang = torch.arange(offset, offset + length, device=device, dtype=torch.float32)[:, None] * inv[None, :]
+    cos, sin = ang.cos(), ang.sin()
+    return torch.cat([cos, cos], dim=-1), torch.cat([-sin, sin], dim=-1)
+
+
+def apply_rope(x: torch.Tensor, tables) -> torch.Tensor:
+    """Half-split rotary embedding (``traditional=False``): (a, b) -> (a cos - b sin, b cos + a sin), in float32."""
+    cos2, sin2 = tables
     xf = x.float()
-    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * weight
+    return torch.addcmul(xf * cos2, torch.roll(xf, x.shape[-1] // 2, dims=-1), sin2).to(x.dtype)
 
 
 def rope(x: torch.Tensor, offset: int, theta: float) -> torch.Tensor:
-    """Rotary embedding, half-split layout (``traditional=False``), positions ``offset ... offset+L-1``.
-
-    ``x`` is (B, H, L, D); computed in float32 and cast back.
-    """
-    _, _, L, D = x.shape
-    half = D // 2
-    inv = theta ** (-torch.arange(0, half, device=x.device, dtype=torch.float32) / half)
-    ang = torch.arange(offset, offset + L, device=x.device, dtype=torch.float32)[:, None] * inv[None, :]
-    cos, sin = ang.cos(), ang.sin()
-    xf = x.float()
-    a, b = xf[..., :half], xf[..., half:]
-    return torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1).to(x.dtype)
+    """Rotary embedding of ``x`` (B, H, L, D) at positions ``offset ... offset+L-1``."""
+    return apply_rope(x, rope_tables(offset, x.shape[2], x.shape[3], theta, x.device))
 
 
 class Attention(torch.nn.Module):
@@ -68,13 +73,19 @@ class Attention(torch.nn.Module):
         self.qkv_proj = torch.nn.Linear(args.hidden_size, (self.n_heads + 2 * self.n_kv_heads) * self.head_dim, **kw)
         self.o_proj = torch.nn.Linear(self.n_heads * self.head_dim, args.hidden_size, **kw)
 
-    def forward(self, x: torch.Tensor, cache=None, packed: bool = True) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, cache=None, packed: bool = True, rope_memo: dict | None = None) -> torch.Tensor:
         B, L, _ = x.shape
         hq, hkv, d = self.n_heads, self.n_kv_heads, self.head_dim
         qkv = self.qkv_proj(x).view(B, L, hq + 2 * hkv, d).transpose(1, 2)            # (B, heads, L, d)
-        queries, keys, values = qkv[:, :hq], qkv[:, hq:hq + hkv], qkv[:, hq + hkv:]
         offset = cache.offset if cache is not None else 0                               # read before the update
-        queries, keys = rope(queries, offset, self.rope_theta), rope(keys, offset, self.rope_theta)
+        # queries and keys sit at the same positions: one pass over both; the tables are shared by layers at one offset
+        tables = rope_memo.get((offset, L)) if rope_memo is not None else None
+        if tables is None:
+            tables = rope_tables(offset, L, d, self.rope_theta, x.device)
+            if rope_memo is not None:
+                rope_memo[(offset, L)] = tables
+        qk = apply_rope(qkv[:, :hq + hkv], tables)
+        queries, keys, values = qk[:, :hq], qk[:, hq:], qkv[:, hq + hkv:]
         if cache is not None and packed and L == 1 and hasattr(cache, "attend"):
             cache.update(keys.contiguous(), values.contiguous())
             out = cache.attend(queries.contiguous(), self.scale)                       # (B, hq, 1, d)
@@ -104,8 +115,8 @@ class Block(torch.nn.Module):
         self.input_layernorm = torch.nn.Parameter(torch.ones(args.hidden_size, dtype=dtype, device=device))
         self.post_attention_layernorm = torch.nn.Parameter(torch.ones(args.hidden_size, dtype=dtype, device=device))
 
-    def forward(self, x, cache=None, packed=True):
-        h = x + self.self_attn(_rms_norm(x, self.input_layernorm, self.eps), cache, packed)
+    def forward(self, x, cache=None, packed=True, rope_memo=None):
+        h = x + self.self_attn(_rms_norm(x, self.input_layernorm, self.eps), cache, packed, rope_memo)
         gate, up = self.gate_up_proj(_rms_norm(h, self.post_attention_layernorm, self.eps)).chunk(2, dim=-1)
         return h + self.down_proj(F.silu(gate) * up)
 
@@ -135,8 +146,9 @@ class LlamaShaped(torch.nn.Module):
     @torch.no_grad()
     def forward(self, tokens: torch.Tensor, cache=None, packed: bool = True, last_only: bool = False) -> torch.Tensor:
         h = self.embed_tokens(tokens)
+        rope_memo = {}
         for i, layer in enumerate(self.layers):
-            h = layer(h, cache[i] if cache is not None else None, packed)
+            h = layer(h, cache[i] if cache is not None else None, packed, rope_memo)
         if last_only:
             h = h[:, -1:]
         return self.lm_head(_rms_norm(h, self.norm, self.args.rms_norm_eps))

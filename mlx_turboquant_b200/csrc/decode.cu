@@ -578,13 +578,28 @@ static SplitPlan plan_splits(int batch, int n_q_heads, int n_kv_heads, int64_t c
         if (s.n_ds > 64) { s.d_tps = (d_tiles + 63) / 64; s.n_ds = int((d_tiles + s.d_tps - 1) / s.d_tps); }
     }
     if (p_tiles > 0) {
-        // all CTAs of the grid resident at once: (packed + dense splits) * lanes <= SMs * CTAs per SM
+        // Splits per lane.  While the whole grid fits on the device at once ((packed + dense splits) * lanes <= SMs * CTAs
+        // per SM) more splits are better.  Past that point CTAs queue: the estimate is total work over the slots plus half
+        // of one packed CTA for the ragged end, in units of one tile, with a CTA's fixed cost (tables, query rotation,
+        // reduction, merge) counted as so many tiles.  No CTA waits for another, so residency is not required.
         const int64_t slots = int64_t(sms) * (direct ? 1 : g_tune_ctas_per_sm);
-        int64_t want = g_tune_splits > 0 ? g_tune_splits : slots / lanes - s.n_ds;
-        const int64_t max_useful = (p_tiles + 2 * NW - 1) / (2 * NW);   // at least two tiles per warp
-        if (want > max_useful) want = max_useful;
-        if (want < 1) want = 1;
-        if (want > MAX_SPLITS - 64) want = MAX_SPLITS - 64;
+        const double fixed_p = direct ? 146.0 : 80.0, fixed_d = direct ? 100.0 : 40.0;
+        int64_t max_useful = (p_tiles + 2 * NW - 1) / (2 * NW);   // at least two tiles per warp
+        if (max_useful > MAX_SPLITS - 64) max_useful = MAX_SPLITS - 64;
+        if (max_useful < 1) max_useful = 1;
+        int64_t want = 1;
+        if (g_tune_splits > 0) {
+            want = std::min<int64_t>(g_tune_splits, max_useful);
+        } else {
+            double best = 0.0;
+            for (int64_t w = 1; w <= max_useful; ++w) {
+                const double cta = fixed_p + double(p_tiles) / double(w);
+                double t = cta;
+                if (lanes * (w + s.n_ds) > slots)
+                    t = (double(lanes * w) * cta + double(lanes * s.n_ds) * fixed_d) / double(slots) + 0.5 * cta;
+                if (w == 1 || t < best) { best = t; want = w; }
+            }
+        }
         s.p_tps = (p_tiles + want - 1) / want;
         s.n_ps = int((p_tiles + s.p_tps - 1) / s.p_tps);
     }
