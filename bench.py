@@ -443,8 +443,22 @@ def run_b200(args):
     # ---- device-resident throughput: CUDA graph of one 32-layer step -------------------------------------
     outs = [None] * LAYERS
 
+    fused = None
+    if split and args.fused_gather:
+        # every rank's result buffers (one slot per layer) mapped into every rank: the kernel's merge step stores this rank's
+        # heads into all of them and the consumer waits on an arrival counter - no collective on the path
+        g_heads = HQ // HKV
+        fused = sharding.FusedGather(1, HQ, D, torch.float16, n_buffers=LAYERS, head_offset=plan.head_begin * g_heads,
+                                     n_local_heads=(plan.head_end - plan.head_begin) * g_heads,
+                                     n_local_kv_heads=plan.head_end - plan.head_begin, device=dev)
+
     def layer_pass():
         for i in range(LAYERS):
+            if fused is not None:
+                caches[i].attend(qs[i], gather=fused.slot(i))
+                fused.wait(i)
+                outs[i] = fused.result(i)
+                continue
             outs[i] = caches[i].attend(qs[i])
             if split and not args.no_gather:
                 outs[i] = sharding.gather_heads(outs[i])
@@ -517,7 +531,8 @@ def run_b200(args):
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "layers_per_step": LAYERS, "q_heads": HQ, "kv_heads": HKV, "head_dim": D,
                    "batch_per_gpu": 1, "context": CTX, "l2_policy": "inputs larger than L2: 32 distinct layer caches, 0.9 GB per step",
-                   "sharding": ("one sequence, KV heads split over the GPUs, " + ("no gather" if args.no_gather else "outputs all-gathered per layer (NCCL)"))
+                   "sharding": ("one sequence, KV heads split over the GPUs, " + ("no gather" if args.no_gather else "outputs stored into every GPU's buffer by the kernel's merge step (peer stores + arrival counters)"
+                                                                                  if args.fused_gather else "outputs all-gathered per layer (NCCL)"))
                    if split else "independent sequences per GPU, no collective"},
         "e2e": {"value": e2e_gbs, "unit": "GB/s", "ms_per_step": e2e_ms, "us_per_layer_step": e2e_ms * 1e3 / LAYERS,
                 "h2d_bytes_per_step": LAYERS * (HQ * D * 2 + 2 * HKV * D * 2), "d2h_bytes_per_step": LAYERS * HQ * D * 2,
@@ -545,6 +560,13 @@ def run_b200(args):
         line["cpu_baseline"] = dict(info, value=BYTES_PER_LAYER_STEP / dt / 1e9, unit="GB/s", us_per_layer_step=dt * 1e6)
     if rank == 0:
         print(json.dumps(line))
+    if fused is not None:
+        line_status = _lib.lib().tq_device_status()
+        if line_status:
+            print(f"rank {rank}: device status {line_status} (a bounded wait ran out)", file=sys.stderr)
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        fused.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -562,6 +584,8 @@ def main():
     ap.add_argument("--quantize-pool", type=int, default=8, help="distinct 0.5 GB fp16 K/V input sets the quantize leg cycles through")
     ap.add_argument("--split-heads", action="store_true", help="N > 1: shard ONE sequence by KV head (strong scaling) instead of one sequence per GPU")
     ap.add_argument("--no-gather", action="store_true", help="with --split-heads: leave every GPU with its own heads' outputs")
+    ap.add_argument("--fused-gather", action="store_true", help="with --split-heads: the decode kernel stores its heads into every GPU's "
+                    "result buffer (peer-mapped memory) instead of an NCCL all-gather")
     ap.add_argument("--no-secondary", action="store_true", help="skip the quantize+pack leg")
     ap.add_argument("--workload", default="c1", choices=("c1", "c4"), help="c1: the headline layer-decode benchmark; c4: end-to-end "
                     "batched decoding of a Llama-3.1-8B-shaped model through compressed caches (about 75 GB on the device at the defaults)")

@@ -95,7 +95,7 @@ int tq_quantize_pack(const tq_quantize_args* a, void* stream);
 
 /* The tensor-core quantize kernel (fp16 rows, d = 128) and the 4-bit-key / 2-bit-value decode kernel wait on
  * mbarriers with an iteration limit; if a wait ever runs out the kernel drains and finishes, and this returns the
- * code of the first such wait on the current device (quantize 1-9, decode 101-103; 0 = none).  Synchronises the
+ * code of the first such wait on the current device (quantize 1-9, decode 101-103, gather wait 201; 0 = none).  Synchronises the
  * device; no reference counterpart. */
 int tq_device_status(void);
 
@@ -133,6 +133,8 @@ int tq_append_tokens(const void* k_new, const void* v_new, void* k_buf, void* v_
 
 /* ---- decode attention over [fp16 sink | packed middle | fp16 residual] ------------------- */
 
+struct tq_peer_gather;
+
 typedef struct {
     int batch, n_q_heads, n_kv_heads, d;
     const void* q; int q_dtype;              /* (batch, n_q_heads, d): one query token */
@@ -165,7 +167,26 @@ typedef struct {
      * building its tables without a round trip to device memory first.  Must hold the same values as the
      * device arrays; read during the call only. */
     const float *k_cent_hi_host, *v_cent_hi_host;
+    /* Optional fused gather of the result for head-sharded decoding (see tq_peer_gather below), or NULL: `out` then
+     * is not written; every peer's buffer is. */
+    const struct tq_peer_gather* gather;
 } tq_decode_args;
+
+/* Fused output gather (no reference counterpart; the reference is single-device).  When one sequence's KV heads are
+ * dealt to several GPUs of a node (one process per GPU), the consumer usually needs all heads' outputs on every GPU.
+ * Instead of a collective after the kernel, the kernel's merge step stores each result element into EVERY peer's
+ * output buffer (plain stores through peer-mapped addresses) and then adds 1 to every peer's arrival counter with
+ * release semantics at system scope, once per (sequence, KV head, head group) it merged.  The consumer orders
+ * tq_gather_wait(counter, target) on its stream before the first kernel that reads the buffer.  Nothing reads peer
+ * memory.  out[r] is rank r's buffer (batch, heads_total, d) of out_dtype, as an address valid on THIS device (the
+ * caller's own buffer at its own rank); the call's heads land at head index head_offset ... + n_q_heads - 1. */
+#define TQ_MAX_PEERS 8
+typedef struct tq_peer_gather {
+    int n_peers;                                   /* 1 ... TQ_MAX_PEERS */
+    int heads_total, head_offset;
+    void* out[TQ_MAX_PEERS];
+    unsigned long long* arrivals[TQ_MAX_PEERS];    /* one 64-bit counter per buffer per rank; only ever incremented */
+} tq_peer_gather;
 
 /* Scratch bytes tq_decode_attn needs for these sizes (host-side arithmetic only). */
 size_t tq_decode_workspace_bytes(int batch, int n_q_heads, int n_kv_heads, int d, int64_t c_len,
@@ -186,6 +207,25 @@ int tq_decode_attn(const tq_decode_args* a, void* stream);
  * order them on one stream, calls that overlap on the GPU race.  Allocates nothing. */
 #define TQ_DECODE_STATIC_SCRATCH_BYTES (8u << 20)
 int tq_decode_attn_static(const tq_decode_args* a, void* stream);
+
+/* How many times one tq_decode_attn call with these sizes increments each peer's arrival counter
+ * (= batch * n_kv_heads * head groups; host arithmetic). */
+int64_t tq_gather_arrivals_per_call(int batch, int n_q_heads, int n_kv_heads);
+
+/* Enqueues a one-warp kernel that returns once *arrivals >= target (an acquire load at system scope in a loop with
+ * a back-off, about two seconds at most).  If the limit is reached the kernel records status 201 for
+ * tq_device_status() and returns; the stream continues and the buffer's contents are not to be trusted. */
+int tq_gather_wait(const unsigned long long* arrivals, unsigned long long target, void* stream);
+
+/* Device buffers that other processes on the node can map (CUDA IPC), for the outputs and counters above.
+ * create: cudaMalloc + zero fill on the current device, returns the address and a 64-byte handle to pass to the peers
+ * by any host channel; open: maps a peer's buffer into this process for kernels on the CURRENT device (refused with
+ * TQ_ERR_UNSUPPORTED when the current device cannot address peer_device's memory); close / destroy undo them.  These
+ * four are the only calls of the library that allocate, and only when asked. */
+int tq_peer_buffer_create(size_t bytes, void** ptr, unsigned char handle[64]);
+int tq_peer_buffer_open(const unsigned char handle[64], int peer_device, void** ptr);
+int tq_peer_buffer_close(void* ptr);
+int tq_peer_buffer_destroy(void* ptr);
 
 /* Scale s in [1, 2) minimising max_i |fp16(s*c_i) - s*c_i| / |s*c_i| for a HOST array of n centroids
  * (no reference counterpart; pure host arithmetic). */

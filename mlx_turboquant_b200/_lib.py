@@ -43,6 +43,17 @@ class DequantizeArgs(C.Structure):
     ]
 
 
+TQ_MAX_PEERS = 8
+
+
+class PeerGather(C.Structure):
+    """tq_peer_gather: every rank's output buffer and arrival counter, as addresses valid on this device."""
+    _fields_ = [
+        ("n_peers", _i), ("heads_total", _i), ("head_offset", _i),
+        ("out", _vp * TQ_MAX_PEERS), ("arrivals", _vp * TQ_MAX_PEERS),
+    ]
+
+
 class DecodeArgs(C.Structure):
     _fields_ = [
         ("batch", _i), ("n_q_heads", _i), ("n_kv_heads", _i), ("d", _i),
@@ -60,6 +71,7 @@ class DecodeArgs(C.Structure):
         ("out", _vp), ("out_dtype", _i),
         ("workspace", _vp), ("workspace_bytes", _sz),
         ("k_cent_hi_host", _vp), ("v_cent_hi_host", _vp),
+        ("gather", C.POINTER(PeerGather)),
     ]
 
 
@@ -83,6 +95,12 @@ PROTOTYPES = {
     "tq_set_tuning": (_i, [C.c_char_p, _i]),
     "tq_fp16_table_scale": (_f, [_vp, _i]),
     "tq_device_status": (_i, []),
+    "tq_gather_arrivals_per_call": (_i64, [_i, _i, _i]),
+    "tq_gather_wait": (_i, [_vp, C.c_ulonglong, _vp]),
+    "tq_peer_buffer_create": (_i, [_sz, C.POINTER(_vp), C.c_char_p]),
+    "tq_peer_buffer_open": (_i, [C.c_char_p, _i, C.POINTER(_vp)]),
+    "tq_peer_buffer_close": (_i, [_vp]),
+    "tq_peer_buffer_destroy": (_i, [_vp]),
 }
 
 _lib = None

@@ -444,13 +444,14 @@ class TurboQuantKVCache:
         return torch.cat(pk, dim=2), torch.cat(pv, dim=2)
 
     # ---- attention on the packed cache -----------------------------------------------------------
-    def attend(self, queries: torch.Tensor, scale: float | None = None, out_dtype=None) -> torch.Tensor:
+    def attend(self, queries: torch.Tensor, scale: float | None = None, out_dtype=None, gather=None) -> torch.Tensor | None:
         """softmax(scale * q K^T) V for ONE query token per sequence, straight from packed storage.
 
         ``queries`` is (B, n_q_heads, 1, D) or (B, n_q_heads, D); the result has the same shape and, unless
         ``out_dtype`` says otherwise, the same dtype.  Equals attention over what ``update_and_fetch``
         would return (to ~1e-3 with a float32 result; a float16 result adds its own rounding), without
-        building it.
+        building it.  With ``gather`` (a slot of ``sharding.FusedGather``: this rank holds some of the heads) the
+        kernel stores the result into every rank's gather buffer instead and nothing is returned.
         """
         dev = _lib.require_cuda(queries)
         self._bind(dev)
@@ -465,17 +466,19 @@ class TurboQuantKVCache:
         if q.dtype not in (torch.float16, torch.bfloat16, torch.float32):
             q = q.to(torch.float32)
         q = q.contiguous()
-        out = torch.empty((b, hq, d), dtype=out_dtype or q.dtype, device=dev)
+        out = None if gather is not None else torch.empty((b, hq, d), dtype=out_dtype or q.dtype, device=dev)
+        out_dt = (out_dtype or q.dtype) if out is None else out.dtype
         k, v = self._k, self._v
         # Everything but the query, the result and the three lengths only changes when a buffer is (re)allocated:
         # the filled-in argument block is kept and revalidated by the buffers' addresses.
-        key = (b, hq, q.dtype, out.dtype, scale, _lib.ptr(k.hi), _lib.ptr(v.hi), _lib.ptr(self.keys), _lib.ptr(self.sink_keys),
+        key = (b, hq, q.dtype, out_dt, scale, _lib.ptr(k.hi), _lib.ptr(v.hi), _lib.ptr(self.keys), _lib.ptr(self.sink_keys),
                _lib.ptr(k.qbits), k.capacity(), self._fp16_capacity)
         a = self._dargs
         if a is None or key != self._dargs_key:
-            a = self._fill_decode_args(b, hq, q.dtype, out.dtype, scale)
+            a = self._fill_decode_args(b, hq, q.dtype, out_dt, scale)
             self._dargs, self._dargs_key, self._ws_key = a, key, None
-        a.q, a.out = q.data_ptr(), out.data_ptr()
+        a.q, a.out = q.data_ptr(), (None if out is None else out.data_ptr())
+        a.gather = C.pointer(gather) if gather is not None else None
         a.c_len, a.sink_len, a.res_len = self._compressed_len, self._sink_len, self._fp16_len
         dense_len = self._sink_len + self._fp16_len
         ws_key = (self._compressed_len, (dense_len + 15) >> 4)        # the split plan depends on whole 16-token tiles only
@@ -485,6 +488,8 @@ class TurboQuantKVCache:
         ws = kernels.decode_workspace(dev, self._ws_need)
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
         _lib.check(_lib.lib().tq_decode_attn(C.byref(a), _lib.stream_ptr(dev)))
+        if out is None:
+            return None
         return out if squeeze else out.reshape(b, hq, 1, d)
 
     def _fill_decode_args(self, b: int, hq: int, q_dtype, out_dtype, scale) -> "_lib.DecodeArgs":

@@ -24,6 +24,8 @@
 #include <algorithm>
 #include <string_view>
 
+#include <cstring>
+
 #include "decode_dev.cuh"
 
 namespace tq {
@@ -543,8 +545,11 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
             L = fmaf(w, x.y, L);
             acc = fmaf(w, __ldcg(src + sidx * stride), acc);
         }
-        store_from_f32(p.out, p.out_dtype, qbase + e, acc / L);
+        // fused gather: the group's first head in the peers' (batch, heads_total, d) buffers
+        const int64_t gbase = (int64_t(blockIdx.z) * p.heads_total + p.head_offset + int64_t(blockIdx.y / p.HG) * p.G + (blockIdx.y % p.HG) * HPG) * D;
+        store_result(p, qbase + e, gbase + e, acc / L);
     }
+    signal_peers(p);
 }
 
 // ---- host side ------------------------------------------------------------------------------------
@@ -662,7 +667,7 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
     if (a->c_len < 0 || a->sink_len < 0 || a->res_len < 0 || a->c_len + a->sink_len + a->res_len == 0)
         return fail(TQ_ERR_INVALID, "tq_decode_attn: the cache holds no tokens");
     if (a->c_len >= (int64_t(1) << 30)) return fail(TQ_ERR_UNSUPPORTED, "tq_decode_attn: c_len too large");
-    if (!a->q || !a->rot || !a->out || !workspace) return fail(TQ_ERR_INVALID, "tq_decode_attn: null pointer");
+    if (!a->q || !a->rot || (!a->out && !a->gather) || !workspace) return fail(TQ_ERR_INVALID, "tq_decode_attn: null pointer");
     if (a->q_dtype < 0 || a->q_dtype > 2 || a->out_dtype < 0 || a->out_dtype > 2 || a->dense_dtype < 0 || a->dense_dtype > 2)
         return fail(TQ_ERR_INVALID, "tq_decode_attn: bad dtype");
     if (!aligned(a->rot, 16)) return fail(TQ_ERR_INVALID, "tq_decode_attn: rot must be 16-byte aligned");
@@ -717,6 +722,18 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
     p.counters = reinterpret_cast<int*>(ws + wl.counters);
     p.part_o = reinterpret_cast<float*>(ws + wl.part_o); p.part_ml = reinterpret_cast<float*>(ws + wl.part_ml);
     p.out = a->out; p.out_dtype = a->out_dtype;
+    p.n_peers = 0; p.heads_total = a->n_q_heads; p.head_offset = 0;
+    if (a->gather) {
+        const tq_peer_gather* gth = a->gather;
+        if (gth->n_peers < 1 || gth->n_peers > TQ_MAX_PEERS || gth->head_offset < 0 || gth->heads_total < gth->head_offset + a->n_q_heads)
+            return fail(TQ_ERR_INVALID, "tq_decode_attn: gather: n_peers %d, heads %d + %d of %d", gth->n_peers, gth->head_offset, a->n_q_heads,
+                        gth->heads_total);
+        for (int r = 0; r < gth->n_peers; ++r)
+            if (!gth->out[r] || !gth->arrivals[r] || !aligned(gth->arrivals[r], 8))
+                return fail(TQ_ERR_INVALID, "tq_decode_attn: gather: null or misaligned buffer of peer %d", r);
+        p.n_peers = gth->n_peers; p.heads_total = gth->heads_total; p.head_offset = gth->head_offset;
+        for (int r = 0; r < gth->n_peers; ++r) { p.peer_out[r] = gth->out[r]; p.peer_arrivals[r] = gth->arrivals[r]; }
+    }
     p.pdl = g_tune_pdl;
     p.words_ok = (a->c_len > 0 && aligned(a->k_hi, 4) && aligned(a->v_hi, 4)) ? 1 : 0;   // packed rows readable as 32-bit words
     p.cent_by_value = 0;
@@ -753,6 +770,60 @@ extern "C" int tq_set_tuning(const char* key, int value) {
     else if (k == "quantize_tma" && (value == 0 || value == 1)) set_quantize_tma(value);
     else return fail(TQ_ERR_INVALID, "tq_set_tuning: unknown key or bad value: %s=%d", key, value);
     return TQ_OK;
+}
+
+extern "C" int tq_gather_wait(const unsigned long long* arrivals, unsigned long long target, void* stream) {
+    if (!arrivals || !aligned(arrivals, 8)) return fail(TQ_ERR_INVALID, "tq_gather_wait: null or misaligned counter");
+    return launch_gather_wait(arrivals, target, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int64_t tq_gather_arrivals_per_call(int batch, int n_q_heads, int n_kv_heads) {
+    if (batch <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads) return 0;
+    const int G = n_q_heads / n_kv_heads;
+    return int64_t(batch) * n_kv_heads * ((G + HPG - 1) / HPG);     // one merging CTA per (sequence, KV head, head group)
+}
+
+// ---- peer-visible buffers (CUDA IPC) -----------------------------------------------------------------
+extern "C" int tq_peer_buffer_create(size_t bytes, void** ptr, unsigned char handle[64]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    if (!ptr || !handle || bytes == 0) return fail(TQ_ERR_INVALID, "tq_peer_buffer_create: bad arguments");
+    void* d = nullptr;
+    cudaError_t e = cudaMalloc(&d, bytes);
+    if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_peer_buffer_create: cudaMalloc(%zu): %s", bytes, cudaGetErrorString(e));
+    cudaIpcMemHandle_t h;
+    if ((e = cudaMemset(d, 0, bytes)) != cudaSuccess || (e = cudaIpcGetMemHandle(&h, d)) != cudaSuccess) {
+        cudaFree(d);
+        return fail(TQ_ERR_LAUNCH, "tq_peer_buffer_create: %s", cudaGetErrorString(e));
+    }
+    std::memcpy(handle, &h, 64);
+    *ptr = d;
+    return TQ_OK;
+}
+
+extern "C" int tq_peer_buffer_open(const unsigned char handle[64], int peer_device, void** ptr) {
+    if (!ptr || !handle) return fail(TQ_ERR_INVALID, "tq_peer_buffer_open: bad arguments");
+    int dev = 0, can = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess && dev != peer_device) e = cudaDeviceCanAccessPeer(&can, dev, peer_device);
+    if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_peer_buffer_open: %s", cudaGetErrorString(e));
+    if (dev != peer_device && !can) return fail(TQ_ERR_UNSUPPORTED, "tq_peer_buffer_open: device %d cannot address device %d", dev, peer_device);
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, 64);
+    void* d = nullptr;
+    e = cudaIpcOpenMemHandle(&d, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_peer_buffer_open: %s", cudaGetErrorString(e));
+    *ptr = d;
+    return TQ_OK;
+}
+
+extern "C" int tq_peer_buffer_close(void* ptr) {
+    cudaError_t e = ptr ? cudaIpcCloseMemHandle(ptr) : cudaSuccess;
+    return e == cudaSuccess ? TQ_OK : fail(TQ_ERR_LAUNCH, "tq_peer_buffer_close: %s", cudaGetErrorString(e));
+}
+
+extern "C" int tq_peer_buffer_destroy(void* ptr) {
+    cudaError_t e = ptr ? cudaFree(ptr) : cudaSuccess;
+    return e == cudaSuccess ? TQ_OK : fail(TQ_ERR_LAUNCH, "tq_peer_buffer_destroy: %s", cudaGetErrorString(e));
 }
 
 extern "C" float tq_fp16_table_scale(const float* centroids_host, int n) {

@@ -36,6 +36,11 @@ struct DecodeParams {
     int words_ok;                      // packed key / value rows start on 4-byte boundaries
     int cent_by_value;                 // kc16 / vc4 below hold the key / value centroids (host copies were given)
     float kc16[16], vc4[4];
+    // fused gather (n_peers > 0): results go to every peer's buffer at head index head_offset + local head, then
+    // every peer's arrival counter is incremented once per merging CTA
+    int n_peers, heads_total, head_offset;
+    void* peer_out[TQ_MAX_PEERS];
+    unsigned long long* peer_arrivals[TQ_MAX_PEERS];
 };
 
 // Validates the arguments, picks the path and the split plan and fills the kernel parameters for the given
@@ -47,6 +52,7 @@ int decode_launch(const DecodeParams& p, bool direct, cudaStream_t s);
 // device (one tiny synchronous probe launch on first use) that the kernel's shared-memory plan fits the device.
 bool direct_supported();
 int launch_decode_direct(const DecodeParams& p, cudaStream_t s);
+int launch_gather_wait(const unsigned long long* arrivals, unsigned long long target, cudaStream_t s);
 int decode_status_host();          // code of the first bounded wait that ran out on this device (0 = none), -1 on error
 
 }  // namespace tq

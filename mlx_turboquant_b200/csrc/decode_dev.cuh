@@ -72,6 +72,27 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
 
 // ---- per-warp running softmax state ------------------------------------------------------------------
 constexpr float MAX_SLACK = 6.f;   // scores may exceed the running reference by 2^6 before it is refreshed
+// ---- result stores ---------------------------------------------------------------------------------
+// One element of the result: into the caller's buffer, or (fused gather) into the same place of every peer's buffer.
+// `gather_head` is the global index of the group's first head: sequence * heads_total + head_offset + local head.
+__device__ __forceinline__ void store_result(const DecodeParams& p, int64_t local_idx, int64_t gather_idx, float v) {
+    if (p.n_peers == 0) {
+        store_from_f32(p.out, p.out_dtype, local_idx, v);
+        return;
+    }
+    for (int r = 0; r < p.n_peers; ++r) store_from_f32(p.peer_out[r], p.out_dtype, gather_idx, v);
+}
+// After the result stores of a merging CTA; every thread of the CTA calls it.  The barrier orders all threads' stores
+// before thread 0's fence at system scope (cumulative), which orders them before the counter increments the peers poll.
+__device__ __forceinline__ void signal_peers(const DecodeParams& p) {
+    if (p.n_peers == 0) return;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        for (int r = 0; r < p.n_peers; ++r) atomicAdd_system(p.peer_arrivals[r], 1ULL);
+    }
+}
+
 template <int D> struct WarpAcc {
     float m[2], mt[2], l[2];   // heads 2t, 2t+1: reference max, refresh threshold, this lane's share of the sum
     float o[D / 16][4];        // O^T fragments: rows = coordinate slots, cols = heads

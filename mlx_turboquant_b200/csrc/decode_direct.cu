@@ -67,7 +67,7 @@ static_assert(NW * HPG * D * 4 <= NW * 3 * STG, "partial products must fit in th
 static_assert(LUT_BASE + uint32_t(NW) * 2 * TILE * stage_ld<D>() * 2 <= BARS, "dense staging must end before the barriers");
 
 constexpr uint32_t WAIT_LIMIT = 4u << 20;
-constexpr int ERR_RING = 101, ERR_LAYOUT = 103;
+constexpr int ERR_RING = 101, ERR_LAYOUT = 103, ERR_GATHER_WAIT = 201;
 
 __device__ int g_status = 0;
 __device__ unsigned g_probe_base = 0;
@@ -652,10 +652,26 @@ __global__ void __launch_bounds__(NT, 1) decode_direct_kernel(DecodeParams p) {
             float v = s_ad[e];
 #pragma unroll
             for (int x = 0; x < NW; ++x) v += s_pp[(x * HPG + h) * D + j];
-            store_from_f32(p.out, p.out_dtype, qbase + e, v * s_il[h]);
+            // fused gather: the group's first head in the peers' (batch, heads_total, d) buffers
+            const int64_t gbase = (int64_t(blockIdx.z) * p.heads_total + p.head_offset + int64_t(blockIdx.y / p.HG) * p.G + (blockIdx.y % p.HG) * HPG) * D;
+            store_result(p, qbase + e, gbase + e, v * s_il[h]);
         }
     }
+    signal_peers(p);
     DD_STAMP(6);
+}
+
+// Consumer side of the fused gather: returns once the arrival counter (written by the peers' merge steps) has reached
+// `target`.  The counter lives in this GPU's own memory; the poll is bounded (about two seconds), then a status is left.
+__global__ void gather_wait_kernel(const unsigned long long* arrivals, unsigned long long target) {
+    if (threadIdx.x != 0) return;
+    for (int it = 0; it < 2000000; ++it) {
+        unsigned long long v;
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(arrivals) : "memory");
+        if (v >= target) return;
+        __nanosleep(it < 64 ? 32 : 512);
+    }
+    atomicCAS(&g_status, 0, ERR_GATHER_WAIT);
 }
 
 static unsigned probe_smem_base() {
@@ -716,6 +732,13 @@ template <int NH> static int launch_nh(const DecodeParams& p, cudaStream_t s) {
 
 int launch_decode_direct(const DecodeParams& p, cudaStream_t s) {
     return p.slots <= 4 ? launch_nh<4>(p, s) : launch_nh<8>(p, s);
+}
+
+int launch_gather_wait(const unsigned long long* arrivals, unsigned long long target, cudaStream_t s) {
+    dd::gather_wait_kernel<<<1, 32, 0, s>>>(arrivals, target);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_gather_wait: %s", cudaGetErrorString(e));
+    return TQ_OK;
 }
 
 int decode_status_host() {

@@ -11,6 +11,10 @@ with no data-path collective.  Two plans:
   ranks; each rank then holds the caches of its KV heads only and the per-head outputs are
   gathered once per step (``gather_heads``), the only collective on the path.
 
+  ``FusedGather`` is the same exchange without a collective: the decode kernel's merge step stores each
+  rank's heads straight into every rank's output buffer (peer-mapped device memory, plain stores) and bumps an
+  arrival counter the consumer waits on.
+
 ``job_time_ms`` is the barrier-free max over ranks that multi-GPU timings must use.
 """
 
@@ -18,8 +22,12 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import ctypes as C
+
 import torch
 import torch.distributed as dist
+
+from . import _lib
 
 
 @dataclass(frozen=True)
@@ -77,6 +85,111 @@ def gather_heads(local_out: torch.Tensor, group: dist.ProcessGroup | None = None
     parts = [torch.empty_like(local_out) for _ in range(world)]
     dist.all_gather(parts, local_out.contiguous(), group=group)
     return torch.cat(parts, dim=1)
+
+
+class _DeviceView:
+    """A span of raw device memory that ``torch.as_tensor`` can wrap (CUDA array interface, version 2)."""
+
+    def __init__(self, address: int, shape: tuple[int, ...], typestr: str):
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (address, False), "version": 2,
+                                         "strides": None}
+
+
+_TYPESTR = {torch.float16: ("<f2", 2), torch.float32: ("<f4", 4), torch.bfloat16: (None, 2)}
+
+
+class FusedGather:
+    """Every rank's output buffers and arrival counters, mapped into every rank (ranks = GPUs of one node).
+
+    ``n_buffers`` independent slots (one per layer in flight is the usual choice), each a full-size result
+    ``(batch, heads_total, d)`` of ``dtype`` plus one 64-bit arrival counter.  A decode call given ``slot(i)`` writes
+    its heads into slot ``i`` of every rank; ``wait(i)`` then orders the current stream behind the arrival of all
+    ranks' heads in the local copy, after which ``result(i)`` is complete.  Counters only grow: ``wait`` tracks how
+    many calls slot ``i`` has seen.  Every rank must make the same calls on the same slots.
+
+    A slot may be rewritten by a peer as soon as that peer has passed its own ``wait`` on a LATER call that this rank
+    issues after reading the slot, which holds when a rank reads ``result(i)`` before it launches its next decode
+    call (stream order) and slots are reused no sooner than every other call.
+    """
+
+    def __init__(self, batch: int, heads_total: int, d: int, dtype: torch.dtype, n_buffers: int, head_offset: int,
+                 n_local_heads: int, n_local_kv_heads: int, device: torch.device, group: dist.ProcessGroup | None = None):
+        if dtype not in _TYPESTR:
+            raise TypeError(f"unsupported result dtype {dtype}")
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > _lib.TQ_MAX_PEERS:
+            raise ValueError(f"at most {_lib.TQ_MAX_PEERS} ranks")
+        self.shape, self.dtype, self.n_buffers, self.device = (batch, heads_total, d), dtype, n_buffers, device
+        elem = _TYPESTR[dtype][1]
+        self._slot_bytes = (batch * heads_total * d * elem + 255) // 256 * 256
+        self._ctr_off = n_buffers * self._slot_bytes
+        total = self._ctr_off + (n_buffers * 8 + 255) // 256 * 256
+        lib = _lib.lib()
+        with torch.cuda.device(device):
+            base = C.c_void_p()
+            handle = C.create_string_buffer(64)
+            _lib.check(lib.tq_peer_buffer_create(total, C.byref(base), handle))
+            self._own = base.value
+            mine = (device.index if device.index is not None else torch.cuda.current_device(), bytes(handle.raw))
+            everyone = [None] * self.world
+            dist.all_gather_object(everyone, mine, group=group)
+            self._bases, self._opened = [], []
+            for r, (peer_dev, h) in enumerate(everyone):
+                if r == self.rank:
+                    self._bases.append(self._own)
+                    continue
+                p = C.c_void_p()
+                _lib.check(lib.tq_peer_buffer_open(h, peer_dev, C.byref(p)))
+                self._bases.append(p.value)
+                self._opened.append(p.value)
+        self._structs = []
+        for i in range(n_buffers):
+            g = _lib.PeerGather()
+            g.n_peers, g.heads_total, g.head_offset = self.world, heads_total, head_offset
+            for r, b in enumerate(self._bases):
+                g.out[r] = b + i * self._slot_bytes
+                g.arrivals[r] = b + self._ctr_off + 8 * i
+            self._structs.append(g)
+        self._per_call = self.world * int(lib.tq_gather_arrivals_per_call(batch, n_local_heads, n_local_kv_heads))
+        self._calls = [0] * n_buffers
+        self._results = [self._view(i) for i in range(n_buffers)]
+        if dist.get_world_size(group) > 1:
+            dist.barrier(group=group)          # nobody writes before everybody has mapped everybody
+
+    def _view(self, i: int) -> torch.Tensor:
+        b, h, d = self.shape
+        addr = self._own + i * self._slot_bytes
+        typestr = _TYPESTR[self.dtype][0]
+        if typestr is None:                    # bfloat16 has no array-interface code: wrap as int16, reinterpret
+            t = torch.as_tensor(_DeviceView(addr, (b, h, d), "<i2"), device=self.device).view(torch.bfloat16)
+        else:
+            t = torch.as_tensor(_DeviceView(addr, (b, h, d), typestr), device=self.device)
+        return t
+
+    def slot(self, i: int) -> "_lib.PeerGather":
+        """The argument for ``TurboQuantKVCache.attend(..., gather=...)``; counts one more call on slot ``i``."""
+        self._calls[i] += 1
+        return self._structs[i]
+
+    def wait(self, i: int) -> None:
+        """Order the current stream behind the arrival of every rank's heads for the latest call on slot ``i``."""
+        addr = self._own + self._ctr_off + 8 * i
+        _lib.check(_lib.lib().tq_gather_wait(addr, self._calls[i] * self._per_call, _lib.stream_ptr(self.device)))
+
+    def result(self, i: int) -> torch.Tensor:
+        """(batch, heads_total, d) view of this rank's copy of slot ``i`` (complete once ``wait(i)`` has run)."""
+        return self._results[i]
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free this rank's (call on every rank, after a barrier and a device sync)."""
+        lib = _lib.lib()
+        with torch.cuda.device(self.device):
+            for p in self._opened:
+                lib.tq_peer_buffer_close(p)
+            self._opened = []
+            if self._own:
+                lib.tq_peer_buffer_destroy(self._own)
+                self._own = 0
 
 
 def job_time_ms(local_ms: float, device: torch.device | None = None, group: dist.ProcessGroup | None = None) -> float:
