@@ -464,7 +464,7 @@ def run_b200(args):
                 outs[i] = sharding.gather_heads(outs[i])
     layer_pass()                      # allocates the workspace before capture
     torch.cuda.synchronize(dev)
-    if args.no_graph or split:        # collectives are launched eagerly
+    if args.no_graph or (split and fused is None):        # collectives are launched eagerly
         class _Eager:
             replay = staticmethod(layer_pass)
         graph = _Eager()

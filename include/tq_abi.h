@@ -212,10 +212,14 @@ int tq_decode_attn_static(const tq_decode_args* a, void* stream);
  * (= batch * n_kv_heads * head groups; host arithmetic). */
 int64_t tq_gather_arrivals_per_call(int batch, int n_q_heads, int n_kv_heads);
 
-/* Enqueues a one-warp kernel that returns once *arrivals >= target (an acquire load at system scope in a loop with
- * a back-off, about two seconds at most).  If the limit is reached the kernel records status 201 for
- * tq_device_status() and returns; the stream continues and the buffer's contents are not to be trusted. */
-int tq_gather_wait(const unsigned long long* arrivals, unsigned long long target, void* stream);
+/* Enqueues a one-warp kernel that returns once *arrivals has reached its target (an acquire load at system scope in
+ * a loop with a back-off, about two seconds at most).  consumed == NULL: the target is `count` (the caller keeps track
+ * of how many arrivals all calls so far add up to).  Otherwise the target is *consumed + count and the kernel moves
+ * *consumed (a counter in this GPU's memory, zero at the start, touched by nothing else) up to it: the arguments are
+ * then the same for every step and the launch can be captured in a CUDA graph.  If the limit is reached the kernel
+ * records status 201 for tq_device_status() and returns; the stream continues and the buffer's contents are not to
+ * be trusted. */
+int tq_gather_wait(const unsigned long long* arrivals, unsigned long long* consumed, unsigned long long count, void* stream);
 
 /* Device buffers that other processes on the node can map (CUDA IPC), for the outputs and counters above.
  * create: cudaMalloc + zero fill on the current device, returns the address and a 64-byte handle to pass to the peers

@@ -96,7 +96,7 @@ PROTOTYPES = {
     "tq_fp16_table_scale": (_f, [_vp, _i]),
     "tq_device_status": (_i, []),
     "tq_gather_arrivals_per_call": (_i64, [_i, _i, _i]),
-    "tq_gather_wait": (_i, [_vp, C.c_ulonglong, _vp]),
+    "tq_gather_wait": (_i, [_vp, _vp, C.c_ulonglong, _vp]),
     "tq_peer_buffer_create": (_i, [_sz, C.POINTER(_vp), C.c_char_p]),
     "tq_peer_buffer_open": (_i, [C.c_char_p, _i, C.POINTER(_vp)]),
     "tq_peer_buffer_close": (_i, [_vp]),

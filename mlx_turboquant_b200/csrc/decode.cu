@@ -772,9 +772,9 @@ extern "C" int tq_set_tuning(const char* key, int value) {
     return TQ_OK;
 }
 
-extern "C" int tq_gather_wait(const unsigned long long* arrivals, unsigned long long target, void* stream) {
-    if (!arrivals || !aligned(arrivals, 8)) return fail(TQ_ERR_INVALID, "tq_gather_wait: null or misaligned counter");
-    return launch_gather_wait(arrivals, target, static_cast<cudaStream_t>(stream));
+extern "C" int tq_gather_wait(const unsigned long long* arrivals, unsigned long long* consumed, unsigned long long count, void* stream) {
+    if (!arrivals || !aligned(arrivals, 8) || !aligned(consumed, 8)) return fail(TQ_ERR_INVALID, "tq_gather_wait: null or misaligned counter");
+    return launch_gather_wait(arrivals, consumed, count, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int64_t tq_gather_arrivals_per_call(int batch, int n_q_heads, int n_kv_heads) {

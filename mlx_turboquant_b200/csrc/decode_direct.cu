@@ -662,9 +662,13 @@ __global__ void __launch_bounds__(NT, 1) decode_direct_kernel(DecodeParams p) {
 }
 
 // Consumer side of the fused gather: returns once the arrival counter (written by the peers' merge steps) has reached
-// `target`.  The counter lives in this GPU's own memory; the poll is bounded (about two seconds), then a status is left.
-__global__ void gather_wait_kernel(const unsigned long long* arrivals, unsigned long long target) {
+// its target: `count` itself, or, with a `consumed` counter, *consumed + count, after which *consumed moves up by count
+// (the launch parameters then never change, so the launch can sit in a CUDA graph).  Both counters live in this GPU's
+// own memory; the poll is bounded (about two seconds), then a status is left.
+__global__ void gather_wait_kernel(const unsigned long long* arrivals, unsigned long long* consumed, unsigned long long count) {
     if (threadIdx.x != 0) return;
+    const unsigned long long target = consumed ? *consumed + count : count;
+    if (consumed) *consumed = target;                       // also after a time-out: later waits keep their meaning
     for (int it = 0; it < 2000000; ++it) {
         unsigned long long v;
         asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(arrivals) : "memory");
@@ -734,8 +738,8 @@ int launch_decode_direct(const DecodeParams& p, cudaStream_t s) {
     return p.slots <= 4 ? launch_nh<4>(p, s) : launch_nh<8>(p, s);
 }
 
-int launch_gather_wait(const unsigned long long* arrivals, unsigned long long target, cudaStream_t s) {
-    dd::gather_wait_kernel<<<1, 32, 0, s>>>(arrivals, target);
+int launch_gather_wait(const unsigned long long* arrivals, unsigned long long* consumed, unsigned long long count, cudaStream_t s) {
+    dd::gather_wait_kernel<<<1, 32, 0, s>>>(arrivals, consumed, count);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_gather_wait: %s", cudaGetErrorString(e));
     return TQ_OK;

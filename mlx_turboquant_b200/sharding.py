@@ -104,8 +104,10 @@ class FusedGather:
     ``n_buffers`` independent slots (one per layer in flight is the usual choice), each a full-size result
     ``(batch, heads_total, d)`` of ``dtype`` plus one 64-bit arrival counter.  A decode call given ``slot(i)`` writes
     its heads into slot ``i`` of every rank; ``wait(i)`` then orders the current stream behind the arrival of all
-    ranks' heads in the local copy, after which ``result(i)`` is complete.  Counters only grow: ``wait`` tracks how
-    many calls slot ``i`` has seen.  Every rank must make the same calls on the same slots.
+    ranks' heads in the local copy, after which ``result(i)`` is complete.  Counters only grow; a second, local counter
+    per slot remembers how many arrivals earlier waits consumed, so both launches take the same arguments every step and
+    a step can be captured in a CUDA graph.  Every rank must make the same calls on the same slots, one ``wait(i)`` per
+    decode call on slot ``i``.
 
     A slot may be rewritten by a peer as soon as that peer has passed its own ``wait`` on a LATER call that this rank
     issues after reading the slot, which holds when a rank reads ``result(i)`` before it launches its next decode
@@ -123,7 +125,8 @@ class FusedGather:
         elem = _TYPESTR[dtype][1]
         self._slot_bytes = (batch * heads_total * d * elem + 255) // 256 * 256
         self._ctr_off = n_buffers * self._slot_bytes
-        total = self._ctr_off + (n_buffers * 8 + 255) // 256 * 256
+        self._used_off = self._ctr_off + (n_buffers * 8 + 255) // 256 * 256          # local "consumed" counters
+        total = self._used_off + (n_buffers * 8 + 255) // 256 * 256
         lib = _lib.lib()
         with torch.cuda.device(device):
             base = C.c_void_p()
@@ -151,7 +154,6 @@ class FusedGather:
                 g.arrivals[r] = b + self._ctr_off + 8 * i
             self._structs.append(g)
         self._per_call = self.world * int(lib.tq_gather_arrivals_per_call(batch, n_local_heads, n_local_kv_heads))
-        self._calls = [0] * n_buffers
         self._results = [self._view(i) for i in range(n_buffers)]
         if dist.get_world_size(group) > 1:
             dist.barrier(group=group)          # nobody writes before everybody has mapped everybody
@@ -167,14 +169,13 @@ class FusedGather:
         return t
 
     def slot(self, i: int) -> "_lib.PeerGather":
-        """The argument for ``TurboQuantKVCache.attend(..., gather=...)``; counts one more call on slot ``i``."""
-        self._calls[i] += 1
+        """The argument for ``TurboQuantKVCache.attend(..., gather=...)``."""
         return self._structs[i]
 
     def wait(self, i: int) -> None:
-        """Order the current stream behind the arrival of every rank's heads for the latest call on slot ``i``."""
-        addr = self._own + self._ctr_off + 8 * i
-        _lib.check(_lib.lib().tq_gather_wait(addr, self._calls[i] * self._per_call, _lib.stream_ptr(self.device)))
+        """Order the current stream behind the arrival of every rank's heads for one more decode call on slot ``i``."""
+        _lib.check(_lib.lib().tq_gather_wait(self._own + self._ctr_off + 8 * i, self._own + self._used_off + 8 * i, self._per_call,
+                                             _lib.stream_ptr(self.device)))
 
     def result(self, i: int) -> torch.Tensor:
         """(batch, heads_total, d) view of this rank's copy of slot ``i`` (complete once ``wait(i)`` has run)."""

@@ -48,7 +48,7 @@ def test_two_emulated_ranks_fill_both_buffers(d, kb, vb, ctx):
                 gs.arrivals[j] = ctrs.data_ptr() + 8 * j
             assert caches[r].attend(q[:, r * hq_loc:(r + 1) * hq_loc].contiguous(), gather=gs) is None
         for j in range(world):
-            _lib.check(_lib.lib().tq_gather_wait(ctrs.data_ptr() + 8 * j, rep * world * per_call, _lib.stream_ptr(q.device)))
+            _lib.check(_lib.lib().tq_gather_wait(ctrs.data_ptr() + 8 * j, None, rep * world * per_call, _lib.stream_ptr(q.device)))
         torch.cuda.synchronize()
         assert ctrs.tolist() == [rep * world * per_call] * world
         for j in range(world):
@@ -74,7 +74,7 @@ def test_gather_argument_errors():
     with pytest.raises(ValueError):
         caches[0].attend(q, gather=gs)
     with pytest.raises(ValueError):
-        _lib.check(_lib.lib().tq_gather_wait(None, 1, _lib.stream_ptr(q.device)))
+        _lib.check(_lib.lib().tq_gather_wait(None, None, 1, _lib.stream_ptr(q.device)))
 
 
 def test_fused_gather_object_single_rank():
@@ -96,6 +96,18 @@ def test_fused_gather_object_single_rank():
             torch.cuda.synchronize()
             assert torch.equal(fg.result(i).reshape(1, 8, 1, 128), want)
             fg.result(i).zero_()
+        # the pair of launches takes the same arguments every time: capture once, replay
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            caches[0].attend(q, gather=fg.slot(1))
+            fg.wait(1)
+        for _ in range(3):
+            fg.result(1).zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(fg.result(1).reshape(1, 8, 1, 128), want)
+        from mlx_turboquant_b200 import _lib
+        assert _lib.lib().tq_device_status() == 0
         fg.close()
     finally:
         if own_group:
