@@ -98,6 +98,8 @@ int tq_quantize_pack(const tq_quantize_args* a, void* stream);
  * code of the first such wait on the current device (quantize 1-9, decode 101-103, gather wait 201; 0 = none).  Synchronises the
  * device; no reference counterpart. */
 int tq_device_status(void);
+/* Back to 0 (after the caller has dealt with a reported time-out). */
+int tq_device_status_clear(void);
 
 /* ---- dequantize: unpack -> centroid -> inverse rotation -> scale ------------------------- */
 
@@ -238,7 +240,8 @@ float tq_fp16_table_scale(const float* centroids_host, int n);
 /* Host-side tuning knobs of the split heuristic (process-wide; no reference counterpart):
  *   "decode_ctas_per_sm" 1..8, "decode_splits" 0 (auto)..448, "decode_force_general" 0/1,
  *   "decode_pdl" 0/1 (programmatic dependent launch: a call's prologue overlaps the previous kernel's tail),
- *   "quantize_tma" 0/1 (tensor-core quantize kernel: rows fetched by tiled TMA copies, or by loads in producer warps).
+ *   "quantize_tma" 0/1 (tensor-core quantize kernel: rows fetched by tiled TMA copies, or by loads in producer warps),
+ *   "gather_wait_polls" 1000..4000000 (polls of tq_gather_wait before it gives up; default 2000000, some two seconds).
  * Changing them changes tq_decode_workspace_bytes for the same sizes. */
 int tq_set_tuning(const char* key, int value);
 

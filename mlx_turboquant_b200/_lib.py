@@ -95,6 +95,7 @@ PROTOTYPES = {
     "tq_set_tuning": (_i, [C.c_char_p, _i]),
     "tq_fp16_table_scale": (_f, [_vp, _i]),
     "tq_device_status": (_i, []),
+    "tq_device_status_clear": (_i, []),
     "tq_gather_arrivals_per_call": (_i64, [_i, _i, _i]),
     "tq_gather_wait": (_i, [_vp, _vp, C.c_ulonglong, _vp]),
     "tq_peer_buffer_create": (_i, [_sz, C.POINTER(_vp), C.c_char_p]),

@@ -554,6 +554,7 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
 
 // ---- host side ------------------------------------------------------------------------------------
 static int g_tune_ctas_per_sm = 2;     // CTAs of the general path resident per SM at d <= 128 (split heuristic)
+static int g_tune_wait_polls = 2000000;  // polls of tq_gather_wait before it gives up (about 1.2 us each: some two seconds)
 static int g_tune_force_general = 0;   // 1: never take the direct path (testing)
 static int g_tune_splits = 0;          // > 0: fixed number of packed splits
 static int g_tune_pdl = 1;             // programmatic dependent launch between consecutive calls
@@ -768,13 +769,14 @@ extern "C" int tq_set_tuning(const char* key, int value) {
     else if (k == "decode_pdl" && (value == 0 || value == 1)) g_tune_pdl = value;
     else if (k == "decode_splits" && value >= 0 && value <= MAX_SPLITS - 64) g_tune_splits = value;
     else if (k == "quantize_tma" && (value == 0 || value == 1)) set_quantize_tma(value);
+    else if (k == "gather_wait_polls" && value >= 1000 && value <= 4000000) g_tune_wait_polls = value;
     else return fail(TQ_ERR_INVALID, "tq_set_tuning: unknown key or bad value: %s=%d", key, value);
     return TQ_OK;
 }
 
 extern "C" int tq_gather_wait(const unsigned long long* arrivals, unsigned long long* consumed, unsigned long long count, void* stream) {
     if (!arrivals || !aligned(arrivals, 8) || !aligned(consumed, 8)) return fail(TQ_ERR_INVALID, "tq_gather_wait: null or misaligned counter");
-    return launch_gather_wait(arrivals, consumed, count, static_cast<cudaStream_t>(stream));
+    return launch_gather_wait(arrivals, consumed, count, g_tune_wait_polls, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int64_t tq_gather_arrivals_per_call(int batch, int n_q_heads, int n_kv_heads) {

@@ -52,7 +52,7 @@ int decode_launch(const DecodeParams& p, bool direct, cudaStream_t s);
 // device (one tiny synchronous probe launch on first use) that the kernel's shared-memory plan fits the device.
 bool direct_supported();
 int launch_decode_direct(const DecodeParams& p, cudaStream_t s);
-int launch_gather_wait(const unsigned long long* arrivals, unsigned long long* consumed, unsigned long long count, cudaStream_t s);
+int launch_gather_wait(const unsigned long long* arrivals, unsigned long long* consumed, unsigned long long count, int max_polls, cudaStream_t s);
 int decode_status_host();          // code of the first bounded wait that ran out on this device (0 = none), -1 on error
 
 }  // namespace tq

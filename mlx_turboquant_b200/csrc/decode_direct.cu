@@ -665,11 +665,11 @@ __global__ void __launch_bounds__(NT, 1) decode_direct_kernel(DecodeParams p) {
 // its target: `count` itself, or, with a `consumed` counter, *consumed + count, after which *consumed moves up by count
 // (the launch parameters then never change, so the launch can sit in a CUDA graph).  Both counters live in this GPU's
 // own memory; the poll is bounded (about two seconds), then a status is left.
-__global__ void gather_wait_kernel(const unsigned long long* arrivals, unsigned long long* consumed, unsigned long long count) {
+__global__ void gather_wait_kernel(const unsigned long long* arrivals, unsigned long long* consumed, unsigned long long count, int max_polls) {
     if (threadIdx.x != 0) return;
     const unsigned long long target = consumed ? *consumed + count : count;
     if (consumed) *consumed = target;                       // also after a time-out: later waits keep their meaning
-    for (int it = 0; it < 2000000; ++it) {
+    for (int it = 0; it < max_polls; ++it) {
         unsigned long long v;
         asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(arrivals) : "memory");
         if (v >= target) return;
@@ -738,11 +738,16 @@ int launch_decode_direct(const DecodeParams& p, cudaStream_t s) {
     return p.slots <= 4 ? launch_nh<4>(p, s) : launch_nh<8>(p, s);
 }
 
-int launch_gather_wait(const unsigned long long* arrivals, unsigned long long* consumed, unsigned long long count, cudaStream_t s) {
-    dd::gather_wait_kernel<<<1, 32, 0, s>>>(arrivals, consumed, count);
+int launch_gather_wait(const unsigned long long* arrivals, unsigned long long* consumed, unsigned long long count, int max_polls, cudaStream_t s) {
+    dd::gather_wait_kernel<<<1, 32, 0, s>>>(arrivals, consumed, count, max_polls);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_gather_wait: %s", cudaGetErrorString(e));
     return TQ_OK;
+}
+
+int decode_status_clear() {
+    const int zero = 0;
+    return cudaMemcpyToSymbol(dd::g_status, &zero, sizeof(int)) == cudaSuccess ? 0 : -1;
 }
 
 int decode_status_host() {

@@ -681,10 +681,16 @@ extern "C" int tq_debug_tc_timing(unsigned long long* host_out, int n) {
 }
 #endif
 
-namespace tq { int decode_status_host(); }   // decode_direct.cu
+namespace tq { int decode_status_host(); int decode_status_clear(); }   // decode_direct.cu
 
 extern "C" int tq_device_status(void) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, tc::g_status, sizeof(int)) != cudaSuccess) return -1;
     return v ? v : decode_status_host();
+}
+
+extern "C" int tq_device_status_clear(void) {
+    const int zero = 0;
+    if (cudaMemcpyToSymbol(tc::g_status, &zero, sizeof(int)) != cudaSuccess) return -1;
+    return decode_status_clear();
 }

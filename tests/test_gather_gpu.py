@@ -112,3 +112,26 @@ def test_fused_gather_object_single_rank():
     finally:
         if own_group:
             dist.destroy_process_group()
+
+
+def test_wait_that_nothing_satisfies_gives_up_and_reports():
+    """A counter nobody increments: the wait ends by itself after its poll limit, leaves status 201, and the stream,
+    the context and later waits keep working."""
+    from mlx_turboquant_b200 import _lib, kernels
+    lib = _lib.lib()
+    assert lib.tq_device_status() == 0
+    ctr = torch.zeros(2, dtype=torch.int64, device="cuda")             # [arrivals, consumed]
+    kernels.set_tuning("gather_wait_polls", 20000)                      # some 25 ms
+    try:
+        _lib.check(lib.tq_gather_wait(ctr.data_ptr(), ctr.data_ptr() + 8, 3, _lib.stream_ptr(ctr.device)))
+        torch.cuda.synchronize()
+        assert lib.tq_device_status() == 201
+        assert ctr.tolist() == [0, 3]                                   # the consumed counter moved on all the same
+        assert lib.tq_device_status_clear() == 0 and lib.tq_device_status() == 0
+        ctr[0] = 5
+        _lib.check(lib.tq_gather_wait(ctr.data_ptr(), ctr.data_ptr() + 8, 2, _lib.stream_ptr(ctr.device)))   # 5 >= 3 + 2
+        torch.cuda.synchronize()
+        assert lib.tq_device_status() == 0 and ctr.tolist() == [5, 5]
+    finally:
+        kernels.set_tuning("gather_wait_polls", 2000000)
+        lib.tq_device_status_clear()
