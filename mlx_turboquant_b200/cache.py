@@ -444,14 +444,16 @@ class TurboQuantKVCache:
         return torch.cat(pk, dim=2), torch.cat(pv, dim=2)
 
     # ---- attention on the packed cache -----------------------------------------------------------
-    def attend(self, queries: torch.Tensor, scale: float | None = None, out_dtype=None, gather=None) -> torch.Tensor | None:
+    def attend(self, queries: torch.Tensor, scale: float | None = None, out_dtype=None, gather=None,
+               out: torch.Tensor | None = None) -> torch.Tensor | None:
         """softmax(scale * q K^T) V for ONE query token per sequence, straight from packed storage.
 
         ``queries`` is (B, n_q_heads, 1, D) or (B, n_q_heads, D); the result has the same shape and, unless
         ``out_dtype`` says otherwise, the same dtype.  Equals attention over what ``update_and_fetch``
         would return (to ~1e-3 with a float32 result; a float16 result adds its own rounding), without
         building it.  With ``gather`` (a slot of ``sharding.FusedGather``: this rank holds some of the heads) the
-        kernel stores the result into every rank's gather buffer instead and nothing is returned.
+        kernel stores the result into every rank's gather buffer instead and nothing is returned.  ``out`` (contiguous,
+        ``queries``' shape) receives the result in place of a fresh tensor.
         """
         dev = _lib.require_cuda(queries)
         self._bind(dev)
@@ -466,7 +468,13 @@ class TurboQuantKVCache:
         if q.dtype not in (torch.float16, torch.bfloat16, torch.float32):
             q = q.to(torch.float32)
         q = q.contiguous()
-        out = None if gather is not None else torch.empty((b, hq, d), dtype=out_dtype or q.dtype, device=dev)
+        given = out
+        if gather is not None:
+            out = None
+        elif out is None:
+            out = torch.empty((b, hq, d), dtype=out_dtype or q.dtype, device=dev)
+        elif out.device != dev or out.numel() != b * hq * d or not out.is_contiguous() or out.dtype not in _lib._DTYPES:
+            raise ValueError("out must be a contiguous float16 / bfloat16 / float32 tensor of the queries' shape on their device")
         out_dt = (out_dtype or q.dtype) if out is None else out.dtype
         k, v = self._k, self._v
         # Everything but the query, the result and the three lengths only changes when a buffer is (re)allocated:
@@ -490,6 +498,8 @@ class TurboQuantKVCache:
         _lib.check(_lib.lib().tq_decode_attn(C.byref(a), _lib.stream_ptr(dev)))
         if out is None:
             return None
+        if given is not None:
+            return given
         return out if squeeze else out.reshape(b, hq, 1, d)
 
     def _fill_decode_args(self, b: int, hq: int, q_dtype, out_dtype, scale) -> "_lib.DecodeArgs":

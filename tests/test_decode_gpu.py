@@ -172,3 +172,12 @@ def test_calls_of_different_shapes_share_a_workspace(oracle):
     for _ in range(2):
         for c, q, ref in (small, big, small):
             _check(c.attend(q, out_dtype=torch.float32), ref)
+
+
+def test_attend_into_a_given_tensor(oracle):
+    c, q, _ = _case(oracle, np.random.RandomState(77), 1, 8, 2, 700, 128, 4, 2, 32, 16)
+    want = c.attend(q)
+    out = torch.full_like(want, float("nan"))
+    assert c.attend(q, out=out) is out and torch.equal(out, want)
+    with pytest.raises(ValueError):
+        c.attend(q, out=torch.empty(3, device="cuda", dtype=torch.float16))
