@@ -55,9 +55,12 @@ template <int D> __host__ __device__ constexpr size_t body_bytes() {
     if (merge_bytes<D>() > s) s = merge_bytes<D>();
     return (s + 15) / 16 * 16;
 }
+// Copies of each entry of the whole-byte tables (lane l reads copy l mod TREP): random entries then spread over the
+// banks instead of piling up; as many as fit beside two resident CTAs.
+template <int D> __host__ __device__ constexpr int table_rep() { return D == 128 ? 8 : 16; }
 template <int D> __host__ __device__ constexpr size_t tail_bytes() {
     return size_t(HPG) * D * sizeof(float) + size_t(HPG) * D * sizeof(__half) + 64 * sizeof(__half) + 16 * sizeof(float) +
-           size_t(HPG) * QM * sizeof(__half) + 256 * sizeof(uint32_t) + 256 * sizeof(uint2);
+           size_t(HPG) * QM * sizeof(__half) + size_t(table_rep<D>()) * (256 * sizeof(uint32_t) + 256 * sizeof(uint2));
 }
 template <int D> __host__ __device__ constexpr size_t kernel_smem() { return body_bytes<D>() + tail_bytes<D>(); }
 
@@ -80,8 +83,9 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
     __half* ctab = qs + HPG * D;                                             // kc_hi, kc_lo, vc_hi, vc_lo (16 each)
     float* s_misc = reinterpret_cast<float*>(ctab + 64);                     // [0..7] 1/L per head, [8] last-CTA flag
     __half* us = reinterpret_cast<__half*>(s_misc + 16);                     // [8][32] fp16 (S q) * scale * log2(e)  (QJL)
-    uint32_t* t4 = reinterpret_cast<uint32_t*>(us + HPG * QM);               // [256] byte of two 4-bit codes -> half2 of key centroids
-    uint2* t2 = reinterpret_cast<uint2*>(t4 + 256);                          // [256] byte of four 2-bit codes -> 4 value centroids
+    constexpr int TREP = table_rep<D>();
+    uint2* t2 = reinterpret_cast<uint2*>(us + HPG * QM);                     // [256][TREP] byte of four 2-bit codes -> 4 value centroids
+    uint32_t* t4 = reinterpret_cast<uint32_t*>(t2 + 256 * TREP);             // [256][TREP] byte of two 4-bit codes -> half2 of key centroids
 
     pdl_trigger();     // the next launch on the stream may become resident and run its own prologue
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
@@ -105,12 +109,14 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
     const bool fast_k = !dense && p.kb_hi == 4 && p.kb_lo == 0 && p.words_ok, fast_v = !dense && p.vb_hi == 2 && p.vb_lo == 0 && p.words_ok;
     if (fast_k || fast_v) {
         __syncthreads();
-        const int e = tid;      // NT == 256 entries
-        const __half2 hk = __halves2half2(ctab[e & 15], ctab[e >> 4]);
-        t4[e] = *reinterpret_cast<const uint32_t*>(&hk);
-        const __half2 v01 = __halves2half2(ctab[32 + (e & 3)], ctab[32 + ((e >> 2) & 3)]);
-        const __half2 v23 = __halves2half2(ctab[32 + ((e >> 4) & 3)], ctab[32 + (e >> 6)]);
-        t2[e] = make_uint2(*reinterpret_cast<const uint32_t*>(&v01), *reinterpret_cast<const uint32_t*>(&v23));
+        for (int idx = tid; idx < 256 * TREP; idx += NT) {
+            const int e = idx / TREP;
+            const __half2 hk = __halves2half2(ctab[e & 15], ctab[e >> 4]);
+            t4[idx] = *reinterpret_cast<const uint32_t*>(&hk);
+            const __half2 v01 = __halves2half2(ctab[32 + (e & 3)], ctab[32 + ((e >> 2) & 3)]);
+            const __half2 v23 = __halves2half2(ctab[32 + ((e >> 4) & 3)], ctab[32 + (e >> 6)]);
+            t2[idx] = make_uint2(*reinterpret_cast<const uint32_t*>(&v01), *reinterpret_cast<const uint32_t*>(&v23));
+        }
     }
     pdl_wait();        // from here on: the query, the cache and the workspace of the previous launch are settled
 
@@ -216,6 +222,12 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
         const int64_t tile_hi = min(tile_lo + p.p_tps, (p.c_len + TILE - 1) / TILE);
         // Word-at-a-time path: the packed words of tile i+1 are loaded (into registers) before tile i is unpacked, and a
         // tile's norms / sketches are requested before its unpacking starts, so global latency overlaps shared-memory work.
+        constexpr int TSH = TREP == 16 ? 4 : 3;                                                 // log2(TREP)
+        const uint32_t my_copy = lane & (TREP - 1);
+        auto tix = [&](uint32_t w, int byte) -> uint32_t {      // index of this lane's copy of the entry for byte `byte` of w
+            const uint32_t field = byte * 8 >= TSH ? (w >> (byte * 8 - TSH)) : (w << (TSH - byte * 8));
+            return (field & (255u << TSH)) | my_copy;
+        };
         constexpr int KWPL = (TILE * D / 2 / 4) / 32, VWPL = (TILE * D / 4 / 4 + 31) / 32;     // words per lane: keys, values
         constexpr bool PREFETCH = D <= 128;                                                     // (register budget)
         uint32_t kw[KWPL], vw[VWPL];
@@ -276,7 +288,7 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
                     const int i = lane + 32 * j, r = (4 * i) / (D / 2), cb = 4 * i - r * (D / 2);
                     const uint32_t w = kc[j];
                     uint4 o;
-                    o.x = t4[w & 255u]; o.y = t4[(w >> 8) & 255u]; o.z = t4[(w >> 16) & 255u]; o.w = t4[w >> 24];
+                    o.x = t4[tix(w, 0)]; o.y = t4[tix(w, 1)]; o.z = t4[tix(w, 2)]; o.w = t4[tix(w, 3)];
                     if (tok0 + r >= p.c_len) o = make_uint4(0, 0, 0, 0);
                     *reinterpret_cast<uint4*>(Ks + r * LD + 2 * cb) = o;
                 }
@@ -288,7 +300,7 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
                     if (i < TILE * D / 4 / 4) {
                         const bool live = tok0 + r < p.c_len;
                         const uint32_t w = vc[j];
-                        const uint2 a = t2[w & 255u], b = t2[(w >> 8) & 255u], c = t2[(w >> 16) & 255u], e = t2[w >> 24];
+                        const uint2 a = t2[tix(w, 0)], b = t2[tix(w, 1)], c = t2[tix(w, 2)], e = t2[tix(w, 3)];
                         uint4 o0 = make_uint4(a.x, a.y, b.x, b.y), o1 = make_uint4(c.x, c.y, e.x, e.y);
                         if (!live) { o0 = make_uint4(0, 0, 0, 0); o1 = o0; }
                         *reinterpret_cast<uint4*>(Vs + r * LD + 4 * cb) = o0;
