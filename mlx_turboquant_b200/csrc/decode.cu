@@ -233,14 +233,14 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
         uint32_t kw[KWPL], vw[VWPL];
         auto load_words = [&](int64_t tile, uint32_t (&kd)[KWPL], uint32_t (&vd)[VWPL]) {
             const int64_t tok0 = tile * TILE;
-            const bool in = tile < tile_hi;
+            const int rows = tile < tile_hi ? int(min(int64_t(TILE), p.c_len - tok0)) : 0;     // rows of this tile inside the cache
             if (fast_k) {
                 // 16 rows of D/2 bytes are contiguous: word i of the tile = row (4 i) / (D/2), bytes (4 i) % (D/2) ...
                 const uint32_t* src = reinterpret_cast<const uint32_t*>(p.k_hi + (kvl * p.c_ls + tok0) * (D / 2));
 #pragma unroll
                 for (int j = 0; j < KWPL; ++j) {
                     const int i = lane + 32 * j, r = (4 * i) / (D / 2);
-                    kd[j] = (in && tok0 + r < p.c_len) ? __ldg(src + i) : 0u;
+                    kd[j] = r < rows ? __ldg(src + i) : 0u;
                 }
             }
             if (fast_v) {
@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
 #pragma unroll
                 for (int j = 0; j < VWPL; ++j) {
                     const int i = lane + 32 * j, r = (4 * i) / (D / 4);
-                    vd[j] = (in && i < TILE * D / 4 / 4 && tok0 + r < p.c_len) ? __ldg(src + i) : 0u;
+                    vd[j] = (i < TILE * D / 4 / 4 && r < rows) ? __ldg(src + i) : 0u;
                 }
             }
         };
@@ -288,8 +288,9 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
                     const int i = lane + 32 * j, r = (4 * i) / (D / 2), cb = 4 * i - r * (D / 2);
                     const uint32_t w = kc[j];
                     uint4 o;
+                    // rows past the end of the cache were loaded as zero words: they unpack to centroid 0, a finite value
+                    // that the softmax's mask (ok0 / ok1) keeps out of every sum
                     o.x = t4[tix(w, 0)]; o.y = t4[tix(w, 1)]; o.z = t4[tix(w, 2)]; o.w = t4[tix(w, 3)];
-                    if (tok0 + r >= p.c_len) o = make_uint4(0, 0, 0, 0);
                     *reinterpret_cast<uint4*>(Ks + r * LD + 2 * cb) = o;
                 }
             }
@@ -298,11 +299,9 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
                 for (int j = 0; j < VWPL; ++j) {
                     const int i = lane + 32 * j, r = (4 * i) / (D / 4), cb = 4 * i - r * (D / 4);
                     if (i < TILE * D / 4 / 4) {
-                        const bool live = tok0 + r < p.c_len;
                         const uint32_t w = vc[j];
                         const uint2 a = t2[tix(w, 0)], b = t2[tix(w, 1)], c = t2[tix(w, 2)], e = t2[tix(w, 3)];
-                        uint4 o0 = make_uint4(a.x, a.y, b.x, b.y), o1 = make_uint4(c.x, c.y, e.x, e.y);
-                        if (!live) { o0 = make_uint4(0, 0, 0, 0); o1 = o0; }
+                        const uint4 o0 = make_uint4(a.x, a.y, b.x, b.y), o1 = make_uint4(c.x, c.y, e.x, e.y);
                         *reinterpret_cast<uint4*>(Vs + r * LD + 4 * cb) = o0;
                         *reinterpret_cast<uint4*>(Vs + r * LD + 4 * cb + 8) = o1;
                     }
