@@ -66,6 +66,8 @@ template <int D> __host__ __device__ constexpr size_t kernel_smem() { return bod
 
 // half2 of two signs (+1 for a set bit, -1 otherwise) from bit 0 of a and bit 0 of b
 __device__ __forceinline__ uint32_t sign_pair(uint32_t a, uint32_t b) { return 0xBC00BC00u ^ ((a & 1u) << 15) ^ ((b & 1u) << 31); }
+// the same from one word that holds the two sign bits at positions 15 and 31
+__device__ __forceinline__ uint32_t sign_pair16(uint32_t x) { return 0xBC00BC00u ^ (x & 0x80008000u); }
 
 // QJL: the cache also keeps, per packed token, the signs of 32 random projections S r of the quantization residual r
 // and its norm gamma; the reference adds  (sqrt(pi/2) / d) * gamma * (signs @ S)  to the dequantized vector
@@ -203,8 +205,17 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
     float zacc[QM / 16][4];           // sketch rows of the output, this warp's share
 #pragma unroll
     for (int ks = 0; ks < QM / 16; ++ks) {
-        bu[ks][0] = (QJL && g < heads_here) ? *reinterpret_cast<const uint32_t*>(us + g * QM + ks * 16 + 2 * t) : 0u;
-        bu[ks][1] = (QJL && g < heads_here) ? *reinterpret_cast<const uint32_t*>(us + g * QM + ks * 16 + 2 * t + 8) : 0u;
+        // k-slot (ks, register hh, half e) of lane t stands for sketch index 4 t + 2 ks + hh + 16 e: the two halves of an
+        // operand register are then bits 16 apart in a token's sign word, and one shift + one logic op builds the register
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int pidx = 4 * t + 2 * ks + hh;
+            bu[ks][hh] = 0u;
+            if (QJL && g < heads_here) {
+                const __half2 u2 = __halves2half2(us[g * QM + pidx], us[g * QM + pidx + 16]);
+                bu[ks][hh] = *reinterpret_cast<const uint32_t*>(&u2);
+            }
+        }
         zacc[ks][0] = zacc[ks][1] = zacc[ks][2] = zacc[ks][3] = 0.f;
     }
     __half* Ks = reinterpret_cast<__half*>(smem) + size_t(warp) * 2 * TILE * LD;
@@ -346,11 +357,13 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
                         mma16816(s, a[0], a[1], a[2], a[3], bq[ks][0], bq[ks][1]);
                     }
                 }
+                {
+                    // signs of sketch indices 4 t + q (+ 16) of tokens g and g + 8: bits 12 + q and 28 + q after one shift
+                    const uint32_t zs0 = zk0 << (12 - 4 * t), zs1 = zk1 << (12 - 4 * t);
 #pragma unroll
-                for (int ks = 0; ks < QM / 16; ++ks) {
-                    const int sh = ks * 16 + 2 * t;
-                    mma16816(sq, sign_pair(zk0 >> sh, zk0 >> (sh + 1)), sign_pair(zk1 >> sh, zk1 >> (sh + 1)),
-                             sign_pair(zk0 >> (sh + 8), zk0 >> (sh + 9)), sign_pair(zk1 >> (sh + 8), zk1 >> (sh + 9)), bu[ks][0], bu[ks][1]);
+                    for (int ks = 0; ks < QM / 16; ++ks)
+                        mma16816(sq, sign_pair16(zs0 << (3 - 2 * ks)), sign_pair16(zs1 << (3 - 2 * ks)), sign_pair16(zs0 << (2 - 2 * ks)),
+                                 sign_pair16(zs1 << (2 - 2 * ks)), bu[ks][0], bu[ks][1]);
                 }
                 s[0] = fmaf(s[0], kn0, sq[0] * gk0); s[1] = fmaf(s[1], kn0, sq[1] * gk0);
                 s[2] = fmaf(s[2], kn1, sq[2] * gk1); s[3] = fmaf(s[3], kn1, sq[3] * gk1);
@@ -369,11 +382,14 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
                 // sketch rows of the output: z[p][h] += sum_t sign_p(t) * (p_t * gamma_v[t]); P^T operand as for the values
                 const uint32_t bz0 = movm_t(pack_h2(fminf(pr[0] * gv0, 65504.f), fminf(pr[1] * gv0, 65504.f)));
                 const uint32_t bz1 = movm_t(pack_h2(fminf(pr[2] * gv1, 65504.f), fminf(pr[3] * gv1, 65504.f)));
-#pragma unroll
-                for (int mt = 0; mt < QM / 16; ++mt) {
-                    const int r0 = mt * 16 + g;                                         // sketch rows r0 and r0 + 8
-                    mma16816(zacc[mt], sign_pair(zv[0] >> r0, zv[1] >> r0), sign_pair(zv[0] >> (r0 + 8), zv[1] >> (r0 + 8)),
-                             sign_pair(zv[2] >> r0, zv[3] >> r0), sign_pair(zv[2] >> (r0 + 8), zv[3] >> (r0 + 8)), bz0, bz1);
+                {
+                    // operand registers pair two tokens' signs of one sketch row: put the tokens' half-words side by side
+                    // (row r of token A at bit r, of token B at bit r + 16), then one shift + one logic op per register
+                    const uint32_t x01 = __byte_perm(zv[0], zv[1], 0x5410) << (7 - g), y01 = __byte_perm(zv[0], zv[1], 0x7632) << (7 - g);
+                    const uint32_t x23 = __byte_perm(zv[2], zv[3], 0x5410) << (7 - g), y23 = __byte_perm(zv[2], zv[3], 0x7632) << (7 - g);
+                    // rows g, g + 8 (from x) and 16 + g, 24 + g (from y); bit 15 - 8 = row g + 8 now, row g after 8 more
+                    mma16816(zacc[0], sign_pair16(x01 << 8), sign_pair16(x01), sign_pair16(x23 << 8), sign_pair16(x23), bz0, bz1);
+                    mma16816(zacc[1], sign_pair16(y01 << 8), sign_pair16(y01), sign_pair16(y23 << 8), sign_pair16(y23), bz0, bz1);
                 }
             }
             __syncwarp();
