@@ -230,6 +230,122 @@ struct EpiCtx {
     volatile int* abort_flag; int64_t total_rows; int warp, lane;
 };
 
+// One chunk of 16 coordinates (TMEM columns col .. col + 15 of the hi and lo accumulators) at BITS bits: the codes go into
+// g0 / g1 (eight codes each; plain 4-bit words on the table path).
+template <int BITS>
+__device__ __forceinline__ void epilogue_chunk(uint32_t taddr, float rinv, float rbin, const float (&bnd)[15], const float2* bins,
+                                               const float* raw_bnd, uint32_t& g0, uint32_t& g1) {
+    constexpr int n_bnd = (1 << BITS) - 1;
+    uint32_t vh[16], vl[16];
+    tmem_ld16(taddr, vh);
+    tmem_ld16(taddr + 128, vl);
+    tmem_ld_wait();
+    if (BITS <= DIRECT_MAX_BITS) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float yp = fmaf(__uint_as_float(vl[i]), 1.f / 2048.f, __uint_as_float(vh[i]));
+            add_code<BITS>(i < 8 ? g0 : g1, yp * rinv, bnd, BITS * (i & 7));
+        }
+    } else {
+        // table path: count-below times 16^k goes in with one multiply-add, the compare adds its bit in place
+        uint32_t seen = 0;
+        const uint32_t w0 = g0, w1 = g1;                                        // restored if the group has to be redone
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float yp = fmaf(__uint_as_float(vl[i]), 1.f / 2048.f, __uint_as_float(vh[i]));
+            vh[i] = __float_as_uint(yp);
+            // bin index from the mantissa of (y * 256 + 256 + 2^23): exact rounding to nearest, no convert instruction.
+            // |y| <= 1 keeps the index below 513; NaN and infinity give index 0 (ten low mantissa bits are zero).
+            const float tt = fmaf(yp, rbin, 8388608.f + 256.f);
+            const float2 en = bins[(__float_as_uint(tt) & 0x3FFu) * BIN_REP];
+            seen |= __float_as_uint(en.y);
+            uint32_t& w = i < 8 ? g0 : g1;
+            w += __float_as_uint(en.y) * (1u << (4 * (i & 7)));
+            if ((yp * rinv) > en.x) w += 1u << (4 * (i & 7));                  // strict >, codebook.py:220-223
+        }
+        if (__any_sync(0xffffffffu, (seen & MARKED) != 0)) {     // a marked bin was hit: redo the group with the counting loop
+            g0 = w0; g1 = w1;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                (i < 8 ? g0 : g1) |= code_slow(__uint_as_float(vh[i]) * rinv, raw_bnd, n_bnd) << (4 * (i & 7));
+        }
+    }
+}
+
+// 2 * BITS bytes: the sixteen codes of one chunk as the little-endian bit stream, stored at dst (2-byte aligned at least)
+template <int BITS>
+__device__ __forceinline__ void store_chunk(uint8_t* dst, uint32_t g0, uint32_t g1) {
+    if (BITS == 4) {
+        if ((reinterpret_cast<uintptr_t>(dst) & 7) == 0) *reinterpret_cast<uint2*>(dst) = make_uint2(g0, g1);
+        else { reinterpret_cast<uint16_t*>(dst)[0] = uint16_t(g0); reinterpret_cast<uint16_t*>(dst)[1] = uint16_t(g0 >> 16);
+               reinterpret_cast<uint16_t*>(dst)[2] = uint16_t(g1); reinterpret_cast<uint16_t*>(dst)[3] = uint16_t(g1 >> 16); }
+    } else if (BITS == 3) {
+        const uint32_t w0 = g0 | (g1 << 24), w1 = g1 >> 8;
+        reinterpret_cast<uint16_t*>(dst)[0] = uint16_t(w0); reinterpret_cast<uint16_t*>(dst)[1] = uint16_t(w0 >> 16);
+        reinterpret_cast<uint16_t*>(dst)[2] = uint16_t(w1);
+    } else if (BITS == 2) {
+        const uint32_t w0 = g0 | (g1 << 16);
+        if ((reinterpret_cast<uintptr_t>(dst) & 3) == 0) *reinterpret_cast<uint32_t*>(dst) = w0;
+        else { reinterpret_cast<uint16_t*>(dst)[0] = uint16_t(w0); reinterpret_cast<uint16_t*>(dst)[1] = uint16_t(w0 >> 16); }
+    } else {
+        *reinterpret_cast<uint16_t*>(dst) = uint16_t(g0 | (g1 << 8));
+    }
+}
+
+// Fractional widths, balanced: every warp takes sixteen coordinates of the high-bit half and sixteen of the low-bit half
+// (coordinate quarter q: [16 q, 16 q + 16) and [64 + 16 q, 64 + 16 q + 16)), so no warp is left with only the
+// costlier width while the others wait at the accumulator barrier.
+template <int BH, int BL, bool TMA>
+__device__ __forceinline__ void epilogue_loop_frac(const EpiCtx& e) {
+    const Params& p = e.p;
+    const int quad = e.warp & 3, quarter = e.warp >> 2, row_in_tile = quad * 32 + e.lane;
+    const float2* bins = reinterpret_cast<const float2*>(e.smem + OFF_BINS) + (e.lane & (BIN_REP - 1));      // 4-bit side only
+    const float* raw_h = reinterpret_cast<const float*>(e.smem + OFF_BND);
+    const float* raw_l = raw_h + 16;
+    float bnd_h[15], bnd_l[15];
+#pragma unroll
+    for (int i = 0; i < 15; ++i) { bnd_h[i] = raw_h[i < (1 << BH) - 1 ? i : 0]; bnd_l[i] = raw_l[i < (1 << BL) - 1 ? i : 0]; }
+    const int64_t stride_rows = int64_t(gridDim.x) * TM;
+    const int64_t step_o = TMA ? int64_t(gridDim.x) / p.tiles_per_lane : stride_rows / p.n_rows;
+    const int64_t step_r = TMA ? (int64_t(gridDim.x) - step_o * p.tiles_per_lane) * TM : stride_rows - step_o * p.n_rows;
+    const int64_t wrap_r = TMA ? p.tiles_per_lane * TM : p.n_rows;
+    int64_t lane_o = 0, lane_r = 0;
+    int it = 0;
+    for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
+        const int a = it % ACC_STAGES, s = it % A_STAGES;
+        if (!mbar_wait(e.bar_accfull + 8 * a, (it / ACC_STAGES) & 1, e.abort_flag, 3)) break;
+        if (TMA && !mbar_wait(e.bar_nrm + 8 * s, (it / A_STAGES) & 1, e.abort_flag, 5)) break;     // sums of squares written
+        tc_fence_after();
+        const float* nsq = reinterpret_cast<const float*>(e.smem + OFF_NSQ) + s * 2 * TM;
+        const float nrm = sqrtf(nsq[row_in_tile] + nsq[TM + row_in_tile]);
+        mbar_arrive(e.bar_afree + 8 * s);                       // norm slots of this stage are free again
+        const float rinv = 1.f / fmaxf(nrm, 1e-10f);            // cache.py:237-238 guards the zero vector the same way
+        const float rbin = rinv * 256.f;
+        if (it == 0) {      // one division at the start, then advanced by the grid stride
+            if (TMA) { lane_o = tile / p.tiles_per_lane; lane_r = (tile - lane_o * p.tiles_per_lane) * TM + row_in_tile; }
+            else { const int64_t row = tile * TM + row_in_tile; lane_o = row / p.n_rows; lane_r = row - lane_o * p.n_rows; }
+        }
+        const bool live = TMA ? lane_r < p.n_rows : tile * TM + row_in_tile < e.total_rows;
+        int64_t orow = 0;
+        if (live) {
+            orow = lane_o * p.out_lane_stride + lane_r;
+            if (quarter == 0) p.norms[orow] = nrm;
+        }
+        lane_r += step_r; lane_o += step_o;
+        if (lane_r >= wrap_r + (TMA ? row_in_tile : 0)) { lane_r -= wrap_r; ++lane_o; }
+        const uint32_t t_row = e.tmem_base + (uint32_t(quad * 32) << 16) + a * 256;
+        uint32_t h0 = 0, h1 = 0, l0 = 0, l1 = 0;
+        epilogue_chunk<BH>(t_row + quarter * 16, rinv, rbin, bnd_h, bins, raw_h, h0, h1);
+        epilogue_chunk<BL>(t_row + 64 + quarter * 16, rinv, rbin, bnd_l, bins, raw_l, l0, l1);
+        tc_fence_before();
+        mbar_arrive(e.bar_accfree + 8 * a);                     // accumulators may be overwritten
+        if (live) {
+            store_chunk<BH>(p.p_hi + orow * (8 * BH) + quarter * (2 * BH), h0, h1);      // a row of the half: 64 codes = 8 * bits bytes
+            store_chunk<BL>(p.p_lo + orow * (8 * BL) + quarter * (2 * BL), l0, l1);
+        }
+    }
+}
+
 template <int BITS, bool TMA>
 __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
     const Params& p = e.p;
@@ -354,7 +470,9 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
     }
 }
 
-template <bool TMA>
+// FRAC: the balanced epilogue for the reference's fractional widths (bits_lo == bits_hi - 1); a kernel of its own so that the
+// integer-width kernel keeps its register allocation
+template <bool TMA, bool FRAC>
 __global__ void __launch_bounds__(TMA ? NT_TMA : NT, 1) quantize_tc_kernel(Params p, const __grid_constant__ CUtensorMap tmap) {
     constexpr int NTHREADS = TMA ? NT_TMA : NT;
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -429,7 +547,11 @@ __global__ void __launch_bounds__(TMA ? NT_TMA : NT, 1) quantize_tc_kernel(Param
         // ======================= epilogue: row = 32*(warp%4) + lane, coordinate quarter = warp/4 =======================
         const int bits = (p.bits_lo && (warp >> 3)) ? p.bits_lo : p.bits_hi;
         EpiCtx e{p, smem, tmem_base, bar_accfull, bar_accfree, bar_afree, bar_nrm, abort_flag, total_rows, warp, lane};
-        if (bits == 4) epilogue_loop<4, TMA>(e);
+        if (FRAC) {                                             // 3.5, 2.5, 1.5 bits
+            if (p.bits_hi == 4) epilogue_loop_frac<4, 3, TMA>(e);
+            else if (p.bits_hi == 3) epilogue_loop_frac<3, 2, TMA>(e);
+            else epilogue_loop_frac<2, 1, TMA>(e);
+        } else if (bits == 4) epilogue_loop<4, TMA>(e);
         else if (bits == 3) epilogue_loop<3, TMA>(e);
         else if (bits == 2) epilogue_loop<2, TMA>(e);
         else epilogue_loop<1, TMA>(e);
@@ -616,8 +738,10 @@ int tq_quantize_pack_tc(const tq_quantize_args* q, cudaStream_t s, bool* handled
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 16) return TQ_OK;
     if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(tc::quantize_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::quantize_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(tc::quantize_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::quantize_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::quantize_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::quantize_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
         if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_quantize_pack: shared memory %d B: %s", tc::SMEM_BYTES, cudaGetErrorString(e));
         if (cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms[dev] <= 0) sms[dev] = 148;
         attr_set[dev] = true;
@@ -658,16 +782,19 @@ int tq_quantize_pack_tc(const tq_quantize_args* q, cudaStream_t s, bool* handled
                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         use_tma = (r == CUDA_SUCCESS);
     }
+    const bool frac = q->bits_lo != 0 && q->bits_hi == q->bits_lo + 1;     // balanced epilogue of the fractional widths
     if (use_tma) {
         p.tiles_per_lane = (q->n_rows + tc::TM - 1) / tc::TM;
         p.n_tiles = q->n_lanes * p.tiles_per_lane;
         const unsigned grid = unsigned(std::min<int64_t>(p.n_tiles, sms[dev]));
-        tc::quantize_tc_kernel<true><<<grid, tc::NT_TMA, tc::SMEM_BYTES, s>>>(p, tmap);
+        if (frac) tc::quantize_tc_kernel<true, true><<<grid, tc::NT_TMA, tc::SMEM_BYTES, s>>>(p, tmap);
+        else tc::quantize_tc_kernel<true, false><<<grid, tc::NT_TMA, tc::SMEM_BYTES, s>>>(p, tmap);
     } else {
         p.tiles_per_lane = 0;
         p.n_tiles = (total + tc::TM - 1) / tc::TM;
         const unsigned grid = unsigned(std::min<int64_t>(p.n_tiles, sms[dev]));
-        tc::quantize_tc_kernel<false><<<grid, tc::NT, tc::SMEM_BYTES, s>>>(p, tmap);
+        if (frac) tc::quantize_tc_kernel<false, true><<<grid, tc::NT, tc::SMEM_BYTES, s>>>(p, tmap);
+        else tc::quantize_tc_kernel<false, false><<<grid, tc::NT, tc::SMEM_BYTES, s>>>(p, tmap);
     }
     *handled = true;
     return check_launch("tq_quantize_pack (tensor core)");

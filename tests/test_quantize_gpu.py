@@ -201,7 +201,7 @@ def test_fused_qk_scores_shapes(oracle, tables, tq, tkv, d, bits):
     np.testing.assert_allclose(host(s), ref, atol=1e-3, rtol=1e-3)
 
 
-@pytest.mark.parametrize("kb,lanes,rows", ((4, 8, 1000), (2, 8, 1024), (3, 3, 700), (3.5, 4, 1153), (2.5, 2, 4096), (4, 1, 513)))
+@pytest.mark.parametrize("kb,lanes,rows", ((4, 8, 1000), (2, 8, 1024), (3, 3, 700), (3.5, 4, 1153), (2.5, 2, 4096), (1.5, 3, 900), (4, 1, 513)))
 def test_tensor_core_quantize_path(oracle, tables, kb, lanes, rows):
     """fp16, d = 128 rows go through the tcgen05 kernel (>= 512 rows): same parity bar as the general kernel,
     ragged last tile, strided lanes (rows taken from a larger buffer), every packed width."""
