@@ -137,14 +137,24 @@ class FusedGather:
             everyone = [None] * self.world
             dist.all_gather_object(everyone, mine, group=group)
             self._bases, self._opened = [], []
+            failure = None
             for r, (peer_dev, h) in enumerate(everyone):
                 if r == self.rank:
                     self._bases.append(self._own)
                     continue
                 p = C.c_void_p()
-                _lib.check(lib.tq_peer_buffer_open(h, peer_dev, C.byref(p)))
+                rc = lib.tq_peer_buffer_open(h, peer_dev, C.byref(p))
+                if rc != 0:
+                    failure = f"rank {self.rank}: cannot map rank {r}'s buffer: " + lib.tq_last_error().decode("utf-8", "replace")
+                    break
                 self._bases.append(p.value)
                 self._opened.append(p.value)
+            # every rank learns of any rank's failure before anybody waits for anybody
+            reports = [None] * self.world
+            dist.all_gather_object(reports, failure, group=group)
+            if any(reports):
+                self.close()
+                raise RuntimeError("; ".join(m for m in reports if m))
         self._structs = []
         for i in range(n_buffers):
             g = _lib.PeerGather()
