@@ -75,7 +75,7 @@ typedef struct {
     int64_t n_lanes, n_rows;  /* lanes = batch*kv_heads, rows = tokens of this chunk */
     int64_t x_lane_stride, x_row_stride; /* elements */
     const float* rot;         /* (d, d) float32, row-major */
-    const float* bnd_hi; int bits_hi;    /* 2^bits_hi - 1 boundaries */
+    const float* bnd_hi; int bits_hi;    /* 2^bits_hi - 1 boundaries, non-decreasing (a codebook's are; the kernels search them) */
     const float* bnd_lo; int bits_lo;    /* 0 = integer mode */
     uint8_t* packed_hi;       /* row (o, r) at packed_hi + (o*out_lane_stride + r)*width_hi */
     uint8_t* packed_lo;       /* fractional mode only */

@@ -177,9 +177,11 @@ __global__ void __launch_bounds__(NT) rowops_kernel(RowArgs a) {
                     reinterpret_cast<float*>(a.out)[row * d + col] = y;
                 } else if (a.mode == MODE_QUANT) {
                     const int side = col >= half ? 1 : 0;
-                    const int nb = (1 << (side ? a.bits_lo : a.bits_hi)) - 1;
+                    // how many boundaries y strictly exceeds (codebook.py:220-223): for a non-decreasing list a binary
+                    // search gives the counting loop's answer with one compare per bit, NaN included (0)
                     uint32_t c = 0;
-                    for (int b = 0; b < nb; ++b) c += (y > tab[side * 16 + b]) ? 1u : 0u;   // strict >, codebook.py:220-223
+                    for (uint32_t st = 1u << ((side ? a.bits_lo : a.bits_hi) - 1); st; st >>= 1)
+                        if (y > tab[side * 16 + c + st - 1]) c += st;
                     cs[m * d + col] = uint8_t(c);
                     if (a.y_out) a.y_out[row * d + col] = y;
                     if (want_qjl_q) es[m * (d + 1) + col] = y - (side ? a.cent_lo : a.cent_hi)[c];
