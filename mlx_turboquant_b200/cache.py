@@ -476,6 +476,12 @@ class TurboQuantKVCache:
         elif out.device != dev or out.numel() != b * hq * d or not out.is_contiguous() or out.dtype not in _lib._DTYPES:
             raise ValueError("out must be a contiguous float16 / bfloat16 / float32 tensor of the queries' shape on their device")
         out_dt = (out_dtype or q.dtype) if out is None else out.dtype
+        if gather is not None and getattr(gather, "dtype", None) is not None:
+            if out_dtype is not None and out_dtype != gather.dtype:
+                raise ValueError(f"the gather buffers hold {gather.dtype}, not {out_dtype}")
+            out_dt = gather.dtype                                   # element size of the peers' buffers
+        if gather is not None and getattr(gather, "shape", None) is not None and gather.shape != (b, d):
+            raise ValueError(f"the gather buffers are for batch {gather.shape[0]}, head_dim {gather.shape[1]}; got {b}, {d}")
         k, v = self._k, self._v
         # Everything but the query, the result and the three lengths only changes when a buffer is (re)allocated:
         # the filled-in argument block is kept and revalidated by the buffers' addresses.

@@ -159,6 +159,7 @@ class FusedGather:
         for i in range(n_buffers):
             g = _lib.PeerGather()
             g.n_peers, g.heads_total, g.head_offset = self.world, heads_total, head_offset
+            g.dtype, g.shape = dtype, (batch, d)                    # (Python attributes: attend checks its call against them)
             for r, b in enumerate(self._bases):
                 g.out[r] = b + i * self._slot_bytes
                 g.arrivals[r] = b + self._ctr_off + 8 * i
