@@ -45,7 +45,7 @@ T_C = CTX - SINK - RW
 BYTES_PER_LAYER_STEP = HKV * T_C * (D * 4 // 8 + 4 + D * 2 // 8 + 4) + HKV * (SINK + RW) * 2 * D * 2 + HQ * D * 4
 # DRAM bytes (read + write) of one decode launch on this workload, from the ncu capture summarised in
 # profiles/decode_direct_kernel_c1_k4v2_ctx32768.md (it equals the algorithmic bytes within 1 %: nothing is re-read)
-NCU_DRAM_BYTES_PER_LAUNCH = 28248064
+NCU_DRAM_BYTES_PER_LAUNCH = 28250624
 WORKLOAD = "llama31_8b_layer_decode_attn_ctx32768_k4v2_sink128_rw128"
 # quantize+pack: 4096-token chunks x 8 KV heads, K and V, fp16 in; bytes per (token, head): read 2*D*2, write codes + norms
 QCHUNK = 4096
