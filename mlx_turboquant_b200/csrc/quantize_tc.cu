@@ -244,7 +244,7 @@ __device__ __forceinline__ void epilogue_chunk(uint32_t taddr, float rinv, float
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const float yp = fmaf(__uint_as_float(vl[i]), 1.f / 2048.f, __uint_as_float(vh[i]));
-            add_code<BITS>(i < 8 ? g0 : g1, yp * rinv, bnd, BITS * (i & 7));
+            add_code<BITS>(i < 8 ? g0 : g1, yp, bnd, BITS * (i & 7));                 // bnd: boundaries times the row's norm
         }
     } else {
         // table path: count-below times 16^k goes in with one multiply-add, the compare adds its bit in place
@@ -319,8 +319,13 @@ __device__ __forceinline__ void epilogue_loop_frac(const EpiCtx& e) {
         const float* nsq = reinterpret_cast<const float*>(e.smem + OFF_NSQ) + s * 2 * TM;
         const float nrm = sqrtf(nsq[row_in_tile] + nsq[TM + row_in_tile]);
         mbar_arrive(e.bar_afree + 8 * s);                       // norm slots of this stage are free again
-        const float rinv = 1.f / fmaxf(nrm, 1e-10f);            // cache.py:237-238 guards the zero vector the same way
+        const float nden = fmaxf(nrm, 1e-10f);                  // cache.py:237-238 guards the zero vector the same way
+        const float rinv = 1.f / nden;
         const float rbin = rinv * 256.f;
+        // register search: y / |x| > b is tested as y > b * |x| (one multiply per boundary and row instead of one per coordinate)
+        float sb_h[15], sb_l[15];
+#pragma unroll
+        for (int i = 0; i < 15; ++i) { sb_h[i] = bnd_h[i] * nden; sb_l[i] = bnd_l[i] * nden; }
         if (it == 0) {      // one division at the start, then advanced by the grid stride
             if (TMA) { lane_o = tile / p.tiles_per_lane; lane_r = (tile - lane_o * p.tiles_per_lane) * TM + row_in_tile; }
             else { const int64_t row = tile * TM + row_in_tile; lane_o = row / p.n_rows; lane_r = row - lane_o * p.n_rows; }
@@ -335,8 +340,8 @@ __device__ __forceinline__ void epilogue_loop_frac(const EpiCtx& e) {
         if (lane_r >= wrap_r + (TMA ? row_in_tile : 0)) { lane_r -= wrap_r; ++lane_o; }
         const uint32_t t_row = e.tmem_base + (uint32_t(quad * 32) << 16) + a * 256;
         uint32_t h0 = 0, h1 = 0, l0 = 0, l1 = 0;
-        epilogue_chunk<BH>(t_row + quarter * 16, rinv, rbin, bnd_h, bins, raw_h, h0, h1);
-        epilogue_chunk<BL>(t_row + 64 + quarter * 16, rinv, rbin, bnd_l, bins, raw_l, l0, l1);
+        epilogue_chunk<BH>(t_row + quarter * 16, rinv, rbin, sb_h, bins, raw_h, h0, h1);
+        epilogue_chunk<BL>(t_row + 64 + quarter * 16, rinv, rbin, sb_l, bins, raw_l, l0, l1);
         tc_fence_before();
         mbar_arrive(e.bar_accfree + 8 * a);                     // accumulators may be overwritten
         if (live) {
@@ -376,8 +381,13 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
         const float* nsq = reinterpret_cast<const float*>(e.smem + OFF_NSQ) + s * 2 * TM;
         const float nrm = sqrtf(nsq[row_in_tile] + nsq[TM + row_in_tile]);
         mbar_arrive(e.bar_afree + 8 * s);                       // norm slots of this stage are free again
-        const float rinv = 1.f / fmaxf(nrm, 1e-10f);            // cache.py:237-238 guards the zero vector the same way
+        const float nden = fmaxf(nrm, 1e-10f);                  // cache.py:237-238 guards the zero vector the same way
+        const float rinv = 1.f / nden;
         const float rbin = rinv * 256.f;
+        // register search: y / |x| > b is tested as y > b * |x| (one multiply per boundary and row instead of one per coordinate)
+        float sb[15];
+#pragma unroll
+        for (int i = 0; i < 15; ++i) sb[i] = bnd[i] * nden;
         if (it == 0) {      // one division at the start, then advanced by the grid stride
             if (TMA) { lane_o = tile / p.tiles_per_lane; lane_r = (tile - lane_o * p.tiles_per_lane) * TM + row_in_tile; }
             else { const int64_t row = tile * TM + row_in_tile; lane_o = row / p.n_rows; lane_r = row - lane_o * p.n_rows; }
@@ -404,7 +414,7 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const float yp = fmaf(__uint_as_float(vl[i]), 1.f / 2048.f, __uint_as_float(vh[i]));
-                    add_code<BITS>(groups[cb * 2 + (i >> 3)], yp * rinv, bnd, BITS * (i & 7));
+                    add_code<BITS>(groups[cb * 2 + (i >> 3)], yp, sb, BITS * (i & 7));
                 }
             } else {
                 // table path: count-below times 16^k goes in with one multiply-add, the compare adds its bit in place
