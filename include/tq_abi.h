@@ -9,7 +9,11 @@
  * Conventions
  *   - Every pointer is a caller-owned DEVICE pointer unless it is marked "host".
  *   - Every call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = legacy
- *     default stream) and allocates nothing.
+ *     default stream) and allocates nothing.  Exceptions, both once per device and both to be
+ *     made outside stream capture: tq_decode_tables_build synchronises (it also measures where
+ *     the device places dynamic shared memory), and so does the first tq_decode_attn on a device
+ *     when no tables were ever built there.
+ *   - Calls act on the device that is current when they are made; pointers must belong to it.
  *   - Return value: TQ_OK or a negative TQ_ERR_*; tq_last_error() gives the thread-local text.
  *     Nothing throws, aborts or traps.
  *   - "rows" are vectors of length d.  Row r of lane o lives at
@@ -31,7 +35,7 @@
 extern "C" {
 #endif
 
-#define TQ_ABI_VERSION 1
+#define TQ_ABI_VERSION 2
 
 enum { TQ_OK = 0, TQ_ERR_INVALID = -1, TQ_ERR_UNSUPPORTED = -2, TQ_ERR_LAUNCH = -3, TQ_ERR_TIMEOUT = -4 };
 enum { TQ_F16 = 0, TQ_BF16 = 1, TQ_F32 = 2 };
@@ -164,15 +168,31 @@ typedef struct {
     /* >= tq_decode_workspace_bytes(...), 256-byte aligned, ZERO-FILLED before its first use (it holds
      * arrival counters that every launch leaves at zero again); one buffer per stream in flight. */
     void* workspace; size_t workspace_bytes;
-    /* Optional HOST copies of k_cent_hi (2^k_bits_hi floats) and v_cent_hi (2^v_bits_hi floats), or NULL.  With
-     * them the 4-bit-key / 2-bit-value kernel receives the centroids inside its launch parameters and starts
-     * building its tables without a round trip to device memory first.  Must hold the same values as the
-     * device arrays; read during the call only. */
-    const float *k_cent_hi_host, *v_cent_hi_host;
     /* Optional fused gather of the result for head-sharded decoding (see tq_peer_gather below), or NULL: `out` then
      * is not written; every peer's buffer is. */
     const struct tq_peer_gather* gather;
+    /* Optional constants from tq_decode_tables_build for this (rot, k_cent_hi, v_cent_hi, v_cent_scale_hi), or NULL.
+     * With them the 4-bit-key / 2-bit-value kernel at d = 128 copies its lookup tables and the split rotation matrix
+     * instead of rebuilding them in every CTA of every launch; without them those shapes take the general kernel. */
+    const void* tables;
 } tq_decode_args;
+
+/* Ordering on the stream.  tq_decode_attn is launched with programmatic stream serialisation (unless the "decode_pdl"
+ * tuning knob is 0): its CTAs may become resident while the preceding kernel on the stream is still finishing.  Before
+ * that kernel has completed they read only rot, the centroid tables and `tables` (which the preceding kernel must not
+ * write) and ask for lines of the packed arrays in L2 (harmless whoever is writing them); q, the cache contents, the
+ * workspace and the output are touched only after the preceding kernel has completed and its writes are visible. */
+
+/* Bytes of the constants buffer for tq_decode_args.tables (host arithmetic); 0 when no kernel uses prebuilt constants
+ * for this shape (today: d = 128 with 4-bit keys and 2-bit values has one). */
+size_t tq_decode_tables_bytes(int d, int k_bits, int v_bits);
+/* Fills `tables` (device, 256-byte aligned, tq_decode_tables_bytes(...) bytes) from the rotation matrix (d, d), the key
+ * centroids (2^k_bits) and the value centroids (2^v_bits), all device float32, and the fp16 table scale the calls will
+ * use as v_cent_scale_hi (0 = 1).  Call once per (device, rotation, codebooks) at set-up, outside stream capture:
+ * it synchronises the stream.  No reference counterpart (the reference keeps rotation and codebooks as process-wide
+ * cached arrays, rotation.py:12, codebook.py:32; this is the same cache in the layout the kernel consumes). */
+int tq_decode_tables_build(int d, const float* rot, const float* k_cent, int k_bits, const float* v_cent, int v_bits,
+                           float v_cent_scale, void* tables, size_t bytes, void* stream);
 
 /* Fused output gather (no reference counterpart; the reference is single-device).  When one sequence's KV heads are
  * dealt to several GPUs of a node (one process per GPU), the consumer usually needs all heads' outputs on every GPU.
@@ -205,8 +225,11 @@ int tq_decode_attn(const tq_decode_args* a, void* stream);
  * a driver allocation).  It has no counterpart in the reference.  `workspace` / `workspace_bytes` in the
  * arguments are ignored: scratch comes from a TQ_DECODE_STATIC_SCRATCH_BYTES array inside the library, present
  * on every GPU that loads it.  Sizes that need more are refused with TQ_ERR_UNSUPPORTED.  The first call on a
- * device looks the array's address up (do it outside stream capture).  All calls on a device share the array:
- * order them on one stream, calls that overlap on the GPU race.  Allocates nothing. */
+ * device looks the array's address up (do it outside stream capture); under CUDA's default lazy module loading that
+ * is also when the driver reserves the array's bytes on the device, so a process that is about to give all remaining
+ * memory to its own pool makes the first call before it does (or runs with CUDA_MODULE_LOADING=EAGER); if the
+ * reservation fails the call says so (TQ_ERR_LAUNCH).  All calls on a device share the array: order them on one
+ * stream, calls that overlap on the GPU race.  Allocates nothing itself. */
 #define TQ_DECODE_STATIC_SCRATCH_BYTES (8u << 20)
 int tq_decode_attn_static(const tq_decode_args* a, void* stream);
 

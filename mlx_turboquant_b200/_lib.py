@@ -3,7 +3,7 @@
 The library is the only compute path of this package: there is no CPU or PyTorch
 fallback.  Importing this module never fails, but the first call that needs the
 library raises ``RuntimeError`` when the shared object has not been built
-(``python -c "import __graft_entry__ as g; g.build()"`` or ``build_ext.py``).
+(``python -c "import __graft_entry__ as g; g.build()"``).
 """
 
 from __future__ import annotations
@@ -70,8 +70,8 @@ class DecodeArgs(C.Structure):
         ("res_k", _vp), ("res_v", _vp), ("res_len", _i64), ("res_lane_stride", _i64),
         ("out", _vp), ("out_dtype", _i),
         ("workspace", _vp), ("workspace_bytes", _sz),
-        ("k_cent_hi_host", _vp), ("v_cent_hi_host", _vp),
         ("gather", C.POINTER(PeerGather)),
+        ("tables", _vp),
     ]
 
 
@@ -90,6 +90,8 @@ PROTOTYPES = {
     "tq_qk_scores": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _vp, _vp]),
     "tq_append_tokens": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _vp]),
     "tq_decode_workspace_bytes": (_sz, [_i, _i, _i, _i, _i64, _i64]),
+    "tq_decode_tables_bytes": (_sz, [_i, _i, _i]),
+    "tq_decode_tables_build": (_i, [_i, _vp, _vp, _i, _vp, _i, _f, _vp, _sz, _vp]),
     "tq_decode_attn": (_i, [C.POINTER(DecodeArgs), _vp]),
     "tq_decode_attn_static": (_i, [C.POINTER(DecodeArgs), _vp]),
     "tq_set_tuning": (_i, [C.c_char_p, _i]),
@@ -157,6 +159,21 @@ def require_cuda(*tensors: torch.Tensor) -> torch.device:
         elif t.device != dev:
             raise RuntimeError("tensors are on different devices")
     return dev
+
+
+def launch(dev: torch.device, name: str, *args) -> int:
+    """Call library function ``name`` with ``dev`` as the current CUDA device and return its status.
+
+    The library launches on the device that is current when it is called, and its per-device tables (SM count,
+    shared-memory plan, static scratch) are keyed on it; tensors on ``cuda:1`` handed over while ``cuda:0`` is current
+    would be dereferenced on the wrong GPU.  ``stream`` arguments must already belong to ``dev`` (``stream_ptr(dev)``).
+    """
+    fn = getattr(lib(), name)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx == torch.cuda.current_device():
+        return fn(*args)
+    with torch.cuda.device(idx):
+        return fn(*args)
 
 
 def ptr(t: torch.Tensor | None) -> int | None:

@@ -58,12 +58,10 @@ class _Side:
         self.fractional = self.bits_lo != 0
         self.hi = self.lo = self.norms = self.qbits = self.qgamma = None
         self.cent_hi = self.cent_lo = self.bnd_hi = self.bnd_lo = None
-        self.cent_hi_host = None                 # float32 host copy of cent_hi (kept alive: its address is handed to the library)
         self.fp16_scale_hi = self.fp16_scale_lo = 0.0
 
     def load_tables(self, d: int, device) -> None:
         self.cent_hi, self.bnd_hi = get_codebook(d, self.bits_hi, device)
-        self.cent_hi_host = np.ascontiguousarray(get_codebook_host(d, self.bits_hi)[0], dtype=np.float32)
         self.fp16_scale_hi = _fp16_scale(d, self.bits_hi)
         if self.fractional:
             self.cent_lo, self.bnd_lo = get_codebook(d, self.bits_lo, device)
@@ -135,17 +133,23 @@ class TurboQuantKVCache:
         self._dense_len = 0
         self._dargs = self._dargs_key = self._ws_key = None     # decode argument block kept between attend() calls
         self._ws_need = 0
+        self._tables = None         # prebuilt constants of the decode kernel (shared between caches of the same shape)
         self.offset = 0
 
     # ---- constants -------------------------------------------------------------------------------
     def _bind(self, device) -> None:
         if self._device is not None:
+            if device != self._device:
+                raise RuntimeError(f"this cache lives on {self._device}; got tensors on {device}")
             return
         self._device = device
         d = self.head_dim
         self._rotation = get_rotation_matrix(d, self.rotation_seed, device)
         self._k.load_tables(d, device)
         self._v.load_tables(d, device)
+        if not (self._k.fractional or self._v.fractional or self.qjl_correction):
+            self._tables = kernels.decode_tables(d, self.rotation_seed, self._rotation, self._k.cent_hi, self._k.bits_hi,
+                                                 self._v.cent_hi, self._v.bits_hi, self._v.fp16_scale_hi)
         if self.qjl_correction:
             self._qjl_proj = get_projection_matrix(d, self.qjl_n_proj, device=device)
             s = generate_projection_matrix_host(d, self.qjl_n_proj).astype("float64")
@@ -192,7 +196,13 @@ class TurboQuantKVCache:
         n = len(v)
         if n not in (6, 8, 10, 14):
             raise ValueError(f"state must have 6, 8, 10 or 14 elements, got {n}")
+        # every kernel dereferences these arrays as device memory: a checkpoint loaded on the CPU (or spread over
+        # several GPUs) is refused here rather than faulting at the next attend()
+        dev = _lib.require_cuda(*v)
+        if dev is not None and self._device is not None and dev != self._device:
+            raise RuntimeError(f"state tensors are on {dev}, this cache is bound to {self._device}")
         v = tuple(v) + (None,) * (14 - n)
+        self._dargs = self._dargs_key = self._ws_key = None     # the cached decode arguments pointed into the old arrays
         self.keys, self.values = v[0], v[1]
         def own(t):
             """Adopt a packed array as storage: contiguous, token capacity padded to a multiple of 16."""
@@ -216,10 +226,8 @@ class TurboQuantKVCache:
             self._compressed_len = n_comp
         self._dense_k = self._dense_v = None
         self._dense_len = 0
-        for t in v:
-            if t is not None and t.is_cuda:
-                self._bind(t.device)
-                break
+        if dev is not None:
+            self._bind(dev)
 
     @property
     def meta_state(self):
@@ -346,11 +354,12 @@ class TurboQuantKVCache:
     def _append(k_buf, v_buf, k_new, v_new, row0: int) -> None:
         """k_buf[:, :, row0:row0+T] = k_new (same for values): one library launch when the layout allows it."""
         t_new = k_new.shape[2]
+        _lib.require_cuda(k_buf, v_buf, k_new, v_new)
         if (k_new.is_contiguous() and v_new.is_contiguous() and k_new.dtype == k_buf.dtype and v_new.dtype == v_buf.dtype
                 and k_buf.dtype == v_buf.dtype and (k_buf.shape[3] * k_buf.element_size()) % 16 == 0):
             b, h, cap, d = k_buf.shape
-            rc = _lib.lib().tq_append_tokens(k_new.data_ptr(), v_new.data_ptr(), k_buf.data_ptr(), v_buf.data_ptr(), b * h, t_new,
-                                            d * k_buf.element_size(), t_new, cap, row0, _lib.stream_ptr(k_buf.device))
+            rc = _lib.launch(k_buf.device, "tq_append_tokens", k_new.data_ptr(), v_new.data_ptr(), k_buf.data_ptr(), v_buf.data_ptr(),
+                             b * h, t_new, d * k_buf.element_size(), t_new, cap, row0, _lib.stream_ptr(k_buf.device))
             if rc == 0:
                 return
             if rc != -2:                      # anything but "layout not supported" is an error
@@ -501,7 +510,7 @@ class TurboQuantKVCache:
             self._ws_key = ws_key
         ws = kernels.decode_workspace(dev, self._ws_need)
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
-        _lib.check(_lib.lib().tq_decode_attn(C.byref(a), _lib.stream_ptr(dev)))
+        _lib.check(_lib.launch(dev, "tq_decode_attn", C.byref(a), _lib.stream_ptr(dev)))
         if out is None:
             return None
         if given is not None:
@@ -530,8 +539,7 @@ class TurboQuantKVCache:
             a.k_cent_hi, a.k_cent_lo = _lib.ptr(k.cent_hi), _lib.ptr(k.cent_lo)
             a.v_cent_hi, a.v_cent_lo = _lib.ptr(v.cent_hi), _lib.ptr(v.cent_lo)
             a.v_cent_scale_hi, a.v_cent_scale_lo = v.fp16_scale_hi, v.fp16_scale_lo
-            if k.cent_hi_host is not None and v.cent_hi_host is not None:
-                a.k_cent_hi_host, a.v_cent_hi_host = k.cent_hi_host.ctypes.data, v.cent_hi_host.ctypes.data
+            a.tables = _lib.ptr(self._tables)
             if self.qjl_correction and k.qbits is not None:
                 a.qjl_proj = _lib.ptr(self._qjl_proj)
                 a.k_qjl_bits, a.v_qjl_bits = _lib.ptr(k.qbits), _lib.ptr(v.qbits)

@@ -157,8 +157,8 @@ def quantize_scalar(x: torch.Tensor, centroids: torch.Tensor, boundaries: torch.
     xf = x.to(torch.float32).contiguous()
     b = boundaries.to(torch.float32).contiguous()
     out = torch.empty(x.shape, dtype=torch.uint8, device=dev)
-    _lib.check(_lib.lib().tq_quantize_scalar(xf.data_ptr(), b.data_ptr(), b.numel(), out.data_ptr(), xf.numel(),
-                                             _lib.stream_ptr(dev)))
+    _lib.check(_lib.launch(dev, "tq_quantize_scalar", xf.data_ptr(), b.data_ptr(), b.numel(), out.data_ptr(), xf.numel(),
+                           _lib.stream_ptr(dev)))
     return out
 
 
@@ -168,6 +168,6 @@ def dequantize_scalar(indices: torch.Tensor, centroids: torch.Tensor) -> torch.T
     idx = indices.to(torch.uint8).contiguous()
     c = centroids.to(torch.float32).contiguous()
     out = torch.empty(indices.shape, dtype=torch.float32, device=dev)
-    _lib.check(_lib.lib().tq_dequantize_scalar(idx.data_ptr(), c.data_ptr(), c.numel(), out.data_ptr(), idx.numel(),
-                                               _lib.stream_ptr(dev)))
+    _lib.check(_lib.launch(dev, "tq_dequantize_scalar", idx.data_ptr(), c.data_ptr(), c.numel(), out.data_ptr(), idx.numel(),
+                           _lib.stream_ptr(dev)))
     return out

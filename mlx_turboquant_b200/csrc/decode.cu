@@ -186,11 +186,9 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
     }
     __syncthreads();
 
-    WarpAcc<D> st;
-    st.m[0] = st.m[1] = st.mt[0] = st.mt[1] = -INFINITY;
-    st.l[0] = st.l[1] = 0.f;
-#pragma unroll
-    for (int mt = 0; mt < D / 16; ++mt) st.o[mt][0] = st.o[mt][1] = st.o[mt][2] = st.o[mt][3] = 0.f;
+    constexpr int NZ = QJL ? QM / 16 : 0;
+    WarpAcc<D, NZ> st;
+    st.init();
 
     uint32_t bq[D / 16][2];
     {
@@ -202,7 +200,7 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
         }
     }
     uint32_t bu[QM / 16][2];          // (S q) fragments, B operand: k = sketch index, n = head
-    float zacc[QM / 16][4];           // sketch rows of the output, this warp's share
+    auto& zacc = st.z;                // sketch rows of the output, this warp's share (rescaled with the other accumulators)
 #pragma unroll
     for (int ks = 0; ks < QM / 16; ++ks) {
         // k-slot (ks, register hh, half e) of lane t stands for sketch index 4 t + 2 ks + hh + 16 e: the two halves of an
@@ -216,14 +214,13 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
                 bu[ks][hh] = *reinterpret_cast<const uint32_t*>(&u2);
             }
         }
-        zacc[ks][0] = zacc[ks][1] = zacc[ks][2] = zacc[ks][3] = 0.f;
     }
     __half* Ks = reinterpret_cast<__half*>(smem) + size_t(warp) * 2 * TILE * LD;
     __half* Vs = Ks + TILE * LD;
     if (dense) {
         // ---------------- uncompressed tokens: sink then residual window, raw query ----------------
         const int64_t tile_lo = int64_t(split - p.n_ps) * p.d_tps;
-        dense_tiles<D, NW>(p, kvl, tile_lo, tile_lo + p.d_tps, Ks, Vs, bq, st, warp, lane);
+        dense_tiles<D, NW, NZ>(p, kvl, tile_lo, tile_lo + p.d_tps, Ks, Vs, bq, st, warp, lane);
     } else {
         // ---------------- packed tokens: unpack into shared memory ---------------------
         const int k_half = p.kb_lo ? D / 2 : D, v_half = p.vb_lo ? D / 2 : D;
@@ -344,7 +341,7 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
             }
             __syncwarp();
             if (!QJL) {
-                tile_from_smem<D>(Ks, Vs, bq, kn0, kn1, vn0, vn1, ok0, ok1, st, lane);
+                tile_from_smem<D, NZ>(Ks, Vs, bq, kn0, kn1, vn0, vn1, ok0, ok1, st, lane);
             } else {
                 // scores: MSE part scaled by the key norm plus the sketch part scaled by (c/d) gamma
                 float s[4] = {0.f, 0.f, 0.f, 0.f}, sq[4] = {0.f, 0.f, 0.f, 0.f};
@@ -369,7 +366,7 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
                 s[2] = fmaf(s[2], kn1, sq[2] * gk1); s[3] = fmaf(s[3], kn1, sq[3] * gk1);
                 uint32_t bp[2];
                 float pr[4];
-                softmax_step<D>(s, 1.f, 1.f, vn0, vn1, ok0, ok1, st, bp, pr);
+                softmax_step<D, NZ>(s, 1.f, 1.f, vn0, vn1, ok0, ok1, st, bp, pr, fmaxf(gv0, gv1));
                 {
                     const __half* base = Vs + ((lane & 7) + ((lane >> 4) & 1) * 8) * LD + ((lane >> 3) & 1) * 8;
 #pragma unroll
@@ -380,8 +377,9 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
                     }
                 }
                 // sketch rows of the output: z[p][h] += sum_t sign_p(t) * (p_t * gamma_v[t]); P^T operand as for the values
-                const uint32_t bz0 = movm_t(pack_h2(fminf(pr[0] * gv0, 65504.f), fminf(pr[1] * gv0, 65504.f)));
-                const uint32_t bz1 = movm_t(pack_h2(fminf(pr[2] * gv1, 65504.f), fminf(pr[3] * gv1, 65504.f)));
+                // pr carries the value scale, which was chosen with the residual norms in view
+                const uint32_t bz0 = movm_t(pack_h2(pr[0] * gv0, pr[1] * gv0));
+                const uint32_t bz1 = movm_t(pack_h2(pr[2] * gv1, pr[3] * gv1));
                 {
                     // operand registers pair two tokens' signs of one sketch row: put the tokens' half-words side by side
                     // (row r of token A at bit r, of token B at bit r + 16), then one shift + one logic op per register
@@ -396,6 +394,7 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
         }
     }
 
+    st.finish();       // accumulators back to true scale (the value scale is per warp)
     // ---------------- CTA reduction over warps ----------------------------------------------------------------
 #pragma unroll
     for (int off = 4; off < 32; off <<= 1) {
@@ -721,7 +720,8 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
 
     const int64_t dense_len = a->sink_len + a->res_len;
     // direct path: 4-bit keys / 2-bit values, d = 128, rows and norms addressable in aligned 16-byte chunks
-    const bool direct = !g_tune_force_general && d == 128 && a->c_len > 0 && a->k_bits_hi == 4 && a->k_bits_lo == 0 &&
+    if (a->tables && !aligned(a->tables, 256)) return fail(TQ_ERR_INVALID, "tq_decode_attn: tables must be 256-byte aligned");
+    const bool direct = !g_tune_force_general && a->tables && d == 128 && a->c_len > 0 && a->k_bits_hi == 4 && a->k_bits_lo == 0 &&
                         a->v_bits_hi == 2 && a->v_bits_lo == 0 && !a->k_qjl_bits && aligned(a->k_hi, 16) && aligned(a->v_hi, 16) &&
                         aligned(a->k_norms, 16) && aligned(a->v_norms, 16) && a->c_lane_stride % 16 == 0 && direct_supported();
     const SplitPlan sp = plan_splits(a->batch, a->n_q_heads, a->n_kv_heads, a->c_len, dense_len, sm_count(), direct);
@@ -764,12 +764,7 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
     }
     p.pdl = g_tune_pdl;
     p.words_ok = (a->c_len > 0 && aligned(a->k_hi, 4) && aligned(a->v_hi, 4)) ? 1 : 0;   // packed rows readable as 32-bit words
-    p.cent_by_value = 0;
-    if (direct && a->k_cent_hi_host && a->v_cent_hi_host) {
-        p.cent_by_value = 1;
-        for (int i = 0; i < 16; ++i) p.kc16[i] = a->k_cent_hi_host[i];
-        for (int i = 0; i < 4; ++i) p.vc4[i] = a->v_cent_hi_host[i];
-    }
+    p.tables = direct ? a->tables : nullptr;
     *out = p;
     *direct_out = direct;
     return TQ_OK;
@@ -874,6 +869,19 @@ extern "C" float tq_fp16_table_scale(const float* centroids_host, int n) {
         if (worst < best_err) { best_err = worst; best = sc; }
     }
     return best;
+}
+
+extern "C" size_t tq_decode_tables_bytes(int d, int k_bits, int v_bits) {
+    return (d == 128 && k_bits == 4 && v_bits == 2) ? direct_tables_bytes() : 0;
+}
+
+extern "C" int tq_decode_tables_build(int d, const float* rot, const float* k_cent, int k_bits, const float* v_cent, int v_bits,
+                                      float v_cent_scale, void* tables, size_t bytes, void* stream) {
+    const size_t need = tq_decode_tables_bytes(d, k_bits, v_bits);
+    if (need == 0) return fail(TQ_ERR_UNSUPPORTED, "tq_decode_tables_build: no kernel uses prebuilt constants for d=%d at %d-bit keys / %d-bit values", d, k_bits, v_bits);
+    if (!rot || !k_cent || !v_cent || !tables) return fail(TQ_ERR_INVALID, "tq_decode_tables_build: null pointer");
+    if (!aligned(tables, 256) || bytes < need) return fail(TQ_ERR_INVALID, "tq_decode_tables_build: the buffer must be 256-byte aligned and hold %zu bytes", need);
+    return direct_tables_build(rot, k_cent, v_cent, v_cent_scale, tables, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" size_t tq_decode_workspace_bytes(int batch, int n_q_heads, int n_kv_heads, int d, int64_t c_len,

@@ -34,8 +34,7 @@ struct DecodeParams {
     void* out; int out_dtype;
     int pdl;                           // launch with programmatic stream serialisation
     int words_ok;                      // packed key / value rows start on 4-byte boundaries
-    int cent_by_value;                 // kc16 / vc4 below hold the key / value centroids (host copies were given)
-    float kc16[16], vc4[4];
+    const void* tables;                // prebuilt constants of the direct kernel (decode_direct.cu: DirectTables), or null
     // fused gather (n_peers > 0): results go to every peer's buffer at head index head_offset + local head, then
     // every peer's arrival counter is incremented once per merging CTA
     int n_peers, heads_total, head_offset;
@@ -51,6 +50,8 @@ int decode_launch(const DecodeParams& p, bool direct, cudaStream_t s);
 // decode_direct.cu: the kernel for 4-bit keys / 2-bit values at d = 128.  direct_supported() checks once per
 // device (one tiny synchronous probe launch on first use) that the kernel's shared-memory plan fits the device.
 bool direct_supported();
+size_t direct_tables_bytes();
+int direct_tables_build(const float* rot, const float* k_cent, const float* v_cent, float v_scale, void* tables, cudaStream_t s);
 int launch_decode_direct(const DecodeParams& p, cudaStream_t s);
 int launch_gather_wait(const unsigned long long* arrivals, unsigned long long* consumed, unsigned long long count, int max_polls, cudaStream_t s);
 int decode_status_host();          // code of the first bounded wait that ran out on this device (0 = none), -1 on error

@@ -93,46 +93,95 @@ __device__ __forceinline__ void signal_peers(const DecodeParams& p) {
     }
 }
 
-template <int D> struct WarpAcc {
+// NZ: extra accumulator tiles that share the softmax weights (the QJL sketch rows of the output).
+template <int D, int NZ = 0> struct WarpAcc {
     float m[2], mt[2], l[2];   // heads 2t, 2t+1: reference max, refresh threshold, this lane's share of the sum
-    float o[D / 16][4];        // O^T fragments: rows = coordinate slots, cols = heads
+    float vsc, vt;             // power-of-two scale applied to (weight * value norm) before the fp16 cast; norms above vt force a new one
+    float o[D / 16][4];        // O^T fragments: rows = coordinate slots, cols = heads; hold vsc * (true sums)
+    float z[NZ ? NZ : 1][4];
+    __device__ __forceinline__ void init() {
+        m[0] = m[1] = mt[0] = mt[1] = -INFINITY;
+        l[0] = l[1] = 0.f;
+        vsc = 1.f; vt = 0.f;   // the first tile with a non-zero value norm picks the scale
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+#pragma unroll
+        for (int i = 0; i < (NZ ? NZ : 1); ++i) z[i][0] = z[i][1] = z[i][2] = z[i][3] = 0.f;
+    }
+    // undo the value scale: afterwards o / z hold the true weighted sums
+    __device__ __forceinline__ void finish() {
+        const float r = 1.f / vsc;     // exact: vsc is a power of two
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) { o[i][0] *= r; o[i][1] *= r; o[i][2] *= r; o[i][3] *= r; }
+#pragma unroll
+        for (int i = 0; i < NZ; ++i) { z[i][0] *= r; z[i][1] *= r; z[i][2] *= r; z[i][3] *= r; }
+    }
 };
+
+// The softmax weights p = exp2(s - m) reach the value MMAs as fp16 operands p * |v| * vsc.  m is refreshed lazily, so
+// p <= 2^MAX_SLACK; vsc is a power of two chosen so that the largest value norm seen so far lands in [128, 256), which
+// keeps every operand below 2^14 whatever the norms' magnitude (the reference works in float32, cache.py:276-343) and
+// keeps small norms clear of the fp16 subnormals.  A norm above vt = 1023 / vsc forces a new scale; the accumulators are
+// rescaled like they are for a new maximum.
+constexpr float VSC_CAP = 1023.f;
+
+// The rare branch of the softmax step: new reference maxima and / or a new value scale.  vmax: the largest value norm of
+// the tile in this lane (lanes with the same g hold the same norms).
+template <int D, int NZ>
+__device__ __forceinline__ void softmax_refresh(float mx0, float mx1, float vmax, WarpAcc<D, NZ>& st) {
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+        vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
+    }
+    const float mn0 = fmaxf(fmaxf(st.m[0], mx0), -1e30f), mn1 = fmaxf(fmaxf(st.m[1], mx1), -1e30f);
+    float a0 = ex2(st.m[0] - mn0), a1 = ex2(st.m[1] - mn1);
+    st.m[0] = mn0; st.m[1] = mn1;
+    st.mt[0] = mn0 + MAX_SLACK; st.mt[1] = mn1 + MAX_SLACK;
+    st.l[0] *= a0; st.l[1] *= a1;
+    if (vmax > st.vt) {                                              // warp-uniform
+        int eb = (__float_as_int(vmax) >> 23) & 0xff;                // biased exponent of the largest norm
+        eb = min(max(eb, 16), 240);                                  // (subnormal, infinite and NaN norms: any finite scale)
+        const float nsc = __int_as_float((261 - eb) << 23);          // 2^(7 - floor(log2 vmax)): vmax * nsc in [128, 256)
+        const float r = nsc / st.vsc;
+        a0 *= r; a1 *= r;
+        st.vsc = nsc;
+        st.vt = VSC_CAP / nsc;
+    }
+#pragma unroll
+    for (int mt = 0; mt < D / 16; ++mt) {
+        st.o[mt][0] *= a0; st.o[mt][1] *= a1; st.o[mt][2] *= a0; st.o[mt][3] *= a1;
+    }
+#pragma unroll
+    for (int i = 0; i < NZ; ++i) {
+        st.z[i][0] *= a0; st.z[i][1] *= a1; st.z[i][2] *= a0; st.z[i][3] *= a1;
+    }
+}
 
 // s[0..1]: token g, heads 2t,2t+1;  s[2..3]: token g+8.  Returns the P^T operand for the PV mma.
 // The softmax reference m is refreshed (with a cross-lane max and a rescale of the accumulators) only
 // when some score exceeds it by more than MAX_SLACK; softmax is shift-invariant, so any reference that
-// keeps exp2(s - m) inside the fp16 range is exact.
-template <int D>
+// keeps exp2(s - m) inside the fp16 range is exact.  p_out (optional) receives the four weights times vsc.
+template <int D, int NZ>
 __device__ __forceinline__ void softmax_step(float (&s)[4], float kn0, float kn1, float vn0, float vn1, bool ok0,
-                                             bool ok1, WarpAcc<D>& st, uint32_t (&bp)[2], float* p_out = nullptr) {
+                                             bool ok1, WarpAcc<D, NZ>& st, uint32_t (&bp)[2], float* p_out = nullptr, float vx = 0.f) {
     s[0] = ok0 ? s[0] * kn0 : -INFINITY;
     s[1] = ok0 ? s[1] * kn0 : -INFINITY;
     s[2] = ok1 ? s[2] * kn1 : -INFINITY;
     s[3] = ok1 ? s[3] * kn1 : -INFINITY;
-    float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
-    if (__any_sync(0xffffffffu, mx0 > st.mt[0] || mx1 > st.mt[1])) {
-#pragma unroll
-        for (int off = 4; off < 32; off <<= 1) {
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
-        }
-        const float mn0 = fmaxf(fmaxf(st.m[0], mx0), -1e30f), mn1 = fmaxf(fmaxf(st.m[1], mx1), -1e30f);
-        const float a0 = ex2(st.m[0] - mn0), a1 = ex2(st.m[1] - mn1);
-        st.m[0] = mn0; st.m[1] = mn1;
-        st.mt[0] = mn0 + MAX_SLACK; st.mt[1] = mn1 + MAX_SLACK;
-        st.l[0] *= a0; st.l[1] *= a1;
-#pragma unroll
-        for (int mt = 0; mt < D / 16; ++mt) {
-            st.o[mt][0] *= a0; st.o[mt][1] *= a1; st.o[mt][2] *= a0; st.o[mt][3] *= a1;
-        }
-    }
+    vn0 = ok0 ? vn0 : 0.f; vn1 = ok1 ? vn1 : 0.f;
+    // vx: any other magnitude that will multiply the weights p_out (the QJL residual norms of the tile)
+    const float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]), vmax = fmaxf(fmaxf(vn0, vn1), vx);
+    if (__any_sync(0xffffffffu, mx0 > st.mt[0] || mx1 > st.mt[1] || vmax > st.vt)) softmax_refresh<D, NZ>(mx0, mx1, vmax, st);
     const float p0 = ex2(s[0] - st.m[0]), p1 = ex2(s[1] - st.m[1]), p2 = ex2(s[2] - st.m[0]), p3 = ex2(s[3] - st.m[1]);
     st.l[0] += p0 + p2;
     st.l[1] += p1 + p3;
-    if (p_out) { p_out[0] = p0; p_out[1] = p1; p_out[2] = p2; p_out[3] = p3; }
-    // value norms ride on P (fp16, clamped below the fp16 maximum)
-    const uint32_t h0 = pack_h2(fminf(p0 * vn0, 65504.f), fminf(p1 * vn0, 65504.f));
-    const uint32_t h1 = pack_h2(fminf(p2 * vn1, 65504.f), fminf(p3 * vn1, 65504.f));
+    if (p_out) { p_out[0] = p0 * st.vsc; p_out[1] = p1 * st.vsc; p_out[2] = p2 * st.vsc; p_out[3] = p3 * st.vsc; }
+    // value norms ride on P (fp16)
+    const float w0 = vn0 * st.vsc, w1 = vn1 * st.vsc;
+    const uint32_t h0 = pack_h2(p0 * w0, p1 * w0);
+    const uint32_t h1 = pack_h2(p2 * w1, p3 * w1);
     bp[0] = movm_t(h0);   // tokens 2t,2t+1   x head g
     bp[1] = movm_t(h1);   // tokens 2t+8,2t+9 x head g
 }
@@ -140,10 +189,10 @@ __device__ __forceinline__ void softmax_step(float (&s)[4], float kn0, float kn1
 template <int D> __host__ __device__ constexpr int stage_ld() { return D + 8; }
 
 // One 16-token tile whose K and V sit in shared memory as fp16 [token][coordinate].
-template <int D>
+template <int D, int NZ>
 __device__ __forceinline__ void tile_from_smem(const __half* Ks, const __half* Vs, const uint32_t (&bq)[D / 16][2],
                                                float kn0, float kn1, float vn0, float vn1, bool ok0, bool ok1,
-                                               WarpAcc<D>& st, int lane) {
+                                               WarpAcc<D, NZ>& st, int lane) {
     constexpr int LD = stage_ld<D>();
     float s[4] = {0.f, 0.f, 0.f, 0.f};
     {
@@ -156,7 +205,7 @@ __device__ __forceinline__ void tile_from_smem(const __half* Ks, const __half* V
         }
     }
     uint32_t bp[2];
-    softmax_step<D>(s, kn0, kn1, vn0, vn1, ok0, ok1, st, bp);
+    softmax_step<D, NZ>(s, kn0, kn1, vn0, vn1, ok0, ok1, st, bp);
     {
         const __half* base = Vs + ((lane & 7) + ((lane >> 4) & 1) * 8) * LD + ((lane >> 3) & 1) * 8;
 #pragma unroll
@@ -170,15 +219,16 @@ __device__ __forceinline__ void tile_from_smem(const __half* Ks, const __half* V
 
 // Attention over the uncompressed tokens [sink | residual window] of cache lane kvl with the unrotated query:
 // this warp takes tiles tile_lo + warp, + NW, ... below tile_hi; Ks / Vs are its fp16 staging buffers.
-template <int D, int NW>
+template <int D, int NW, int NZ>
 __device__ __forceinline__ void dense_tiles(const DecodeParams& p, int64_t kvl, int64_t tile_lo, int64_t tile_hi_in, __half* Ks, __half* Vs,
-                                            const uint32_t (&bq)[D / 16][2], WarpAcc<D>& st, int warp, int lane) {
+                                            const uint32_t (&bq)[D / 16][2], WarpAcc<D, NZ>& st, int warp, int lane) {
     constexpr int LD = stage_ld<D>();
     const int g = lane >> 2;
     const int64_t n_tok = p.sink_len + p.res_len;
     const int64_t tile_hi = min(tile_hi_in, (n_tok + TILE - 1) / TILE);
     for (int64_t tile = tile_lo + warp; tile < tile_hi; tile += NW) {
         const int64_t tok0 = tile * TILE;
+        float sck = 1.f, scv = 1.f;                       // staging scales of row lane >> 1 (keys, values)
         constexpr int NCH = TILE * (D / 8) / 32;          // 16-byte chunks per lane and tensor
         if (p.dense_dtype == TQ_F16) {
             uint4 kv[NCH], vv[NCH];                        // every load of the tile in flight before the first store
@@ -201,9 +251,34 @@ __device__ __forceinline__ void dense_tiles(const DecodeParams& p, int64_t kvl, 
                 *reinterpret_cast<uint4*>(Vs + r * LD + c8 * 8) = vv[i];
             }
         } else {
+            // float32 / bfloat16 tokens can lie outside the fp16 range: every token row is staged as fp16 under its own
+            // power-of-two scale (largest magnitude into [2^7, 2^8)); the scores and the softmax weights take the inverse
+            // scales where the packed tokens take their norms.  Lane pair (2r, 2r+1) scans row r of the tile.
+            {
+                const int r = lane >> 1, hf = lane & 1;
+                const int64_t tok = tok0 + r;
+                float mk = 0.f, mv = 0.f;
+                if (tok < n_tok) {
+                    const bool in_sink = tok < p.sink_len;
+                    const int64_t e = (in_sink ? kvl * p.sink_ls + tok : kvl * p.res_ls + (tok - p.sink_len)) * D + hf * (D / 2);
+                    const void* kb = in_sink ? p.sink_k : p.res_k;
+                    const void* vb = in_sink ? p.sink_v : p.res_v;
+                    for (int i = 0; i < D / 2; ++i) {
+                        mk = fmaxf(mk, fabsf(load_as_f32(kb, p.dense_dtype, e + i)));
+                        mv = fmaxf(mv, fabsf(load_as_f32(vb, p.dense_dtype, e + i)));
+                    }
+                }
+                mk = fmaxf(mk, __shfl_xor_sync(0xffffffffu, mk, 1));
+                mv = fmaxf(mv, __shfl_xor_sync(0xffffffffu, mv, 1));
+                // scale 2^(7 - floor(log2 max)); rows of zeros (and non-finite rows) keep scale 1
+                const int ek = (__float_as_int(mk) >> 23) & 0xff, ev = (__float_as_int(mv) >> 23) & 0xff;
+                sck = (ek >= 16 && ek <= 240) ? __int_as_float((261 - ek) << 23) : 1.f;
+                scv = (ev >= 16 && ev <= 240) ? __int_as_float((261 - ev) << 23) : 1.f;
+            }
             for (int c = lane; c < TILE * (D / 8); c += 32) {
                 const int r = c / (D / 8), c8 = c - r * (D / 8);
                 const int64_t tok = tok0 + r;
+                const float fk = __shfl_sync(0xffffffffu, sck, 2 * r), fv = __shfl_sync(0xffffffffu, scv, 2 * r);
                 uint4 kv = make_uint4(0, 0, 0, 0), vv = kv;
                 if (tok < n_tok) {
                     const bool in_sink = tok < p.sink_len;
@@ -213,8 +288,8 @@ __device__ __forceinline__ void dense_tiles(const DecodeParams& p, int64_t kvl, 
                     __half hk[8], hv[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        hk[i] = __float2half_rn(load_as_f32(kb, p.dense_dtype, e + i));
-                        hv[i] = __float2half_rn(load_as_f32(vb, p.dense_dtype, e + i));
+                        hk[i] = __float2half_rn(load_as_f32(kb, p.dense_dtype, e + i) * fk);
+                        hv[i] = __float2half_rn(load_as_f32(vb, p.dense_dtype, e + i) * fv);
                     }
                     kv = *reinterpret_cast<uint4*>(hk);
                     vv = *reinterpret_cast<uint4*>(hv);
@@ -224,7 +299,10 @@ __device__ __forceinline__ void dense_tiles(const DecodeParams& p, int64_t kvl, 
             }
         }
         __syncwarp();
-        tile_from_smem<D>(Ks, Vs, bq, 1.f, 1.f, 1.f, 1.f, tok0 + g < n_tok, tok0 + g + 8 < n_tok, st, lane);
+        // inverse scales of rows g and g + 8 (1 for fp16 tokens)
+        const float ik0 = 1.f / __shfl_sync(0xffffffffu, sck, 2 * g), ik1 = 1.f / __shfl_sync(0xffffffffu, sck, 2 * g + 16);
+        const float iv0 = 1.f / __shfl_sync(0xffffffffu, scv, 2 * g), iv1 = 1.f / __shfl_sync(0xffffffffu, scv, 2 * g + 16);
+        tile_from_smem<D, NZ>(Ks, Vs, bq, ik0, ik1, iv0, iv1, tok0 + g < n_tok, tok0 + g + 8 < n_tok, st, lane);
         __syncwarp();
     }
 }

@@ -11,11 +11,16 @@
 // Set-up.  Host code cannot use the array's name as a device address (it names a host-side stand-in; a kernel
 // given it would fault or touch the wrong memory), so the first call on each device, with that device current,
 // resolves the real address once with cudaGetSymbolAddress and keeps it.  Make that first call outside any
-// stream capture.
+// stream capture.  With CUDA's default lazy module loading that first look-up is also the moment the driver
+// loads this module and reserves the array's bytes on the device: a process that is about to hand all remaining
+// device memory to its own pool must make the first call (or set CUDA_MODULE_LOADING=EAGER) before it does so.
+// If the reservation fails the call reports it and allocates nothing else.
 //
 // Sharing.  All calls on a device use the same array and find in it whatever the previous call left.  The kernel
 // needs its arrival counters at zero; every call clears them on the caller's stream before the launch.  Two calls
 // that run on the GPU at the same time (different streams, no ordering) would race on the array: order them.
+#include <atomic>
+
 #include "decode.cuh"
 
 namespace tq {
@@ -23,17 +28,25 @@ namespace tq {
 static __device__ __align__(256) unsigned char g_decode_scratch[TQ_DECODE_STATIC_SCRATCH_BYTES];
 
 static int static_scratch_ptr(void** out) {
-    static void* ptrs[64] = {nullptr};
+    // one slot per device; filled at most once (compare-and-swap: concurrent first calls resolve the same address)
+    static std::atomic<void*> ptrs[64];
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= 64) return fail(TQ_ERR_LAUNCH, "tq_decode_attn_static: cudaGetDevice: %s", cudaGetErrorString(e));
-    if (ptrs[dev] == nullptr) {
-        void* p = nullptr;
+    void* p = ptrs[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
         e = cudaGetSymbolAddress(&p, g_decode_scratch);
+        if (e == cudaErrorMemoryAllocation) {
+            cudaGetLastError();
+            return fail(TQ_ERR_LAUNCH, "tq_decode_attn_static: the device has no room left for the library's %zu-byte scratch array "
+                        "(the module is loaded at the first call: make it before a memory pool takes the device, or set CUDA_MODULE_LOADING=EAGER)",
+                        size_t(TQ_DECODE_STATIC_SCRATCH_BYTES));
+        }
         if (e != cudaSuccess || p == nullptr) return fail(TQ_ERR_LAUNCH, "tq_decode_attn_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-        ptrs[dev] = p;
+        void* expected = nullptr;
+        ptrs[dev].compare_exchange_strong(expected, p, std::memory_order_acq_rel);
     }
-    *out = ptrs[dev];
+    *out = p;
     return TQ_OK;
 }
 

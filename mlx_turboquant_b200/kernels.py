@@ -44,7 +44,8 @@ def quantize_pack(x: torch.Tensor, rotation: torch.Tensor, boundaries_hi: torch.
     (lanes..., capacity, width) storage instead of allocating.  ``qjl`` = dict(proj_rot, cent_hi,
     cent_lo, bits, gamma) also emits the 1-bit sketch of the residual.
     """
-    dev = _lib.require_cuda(x, rotation, boundaries_hi)
+    q_bufs = () if qjl is None else (qjl.get("proj_rot"), qjl.get("cent_hi"), qjl.get("cent_lo"), qjl.get("bits"), qjl.get("gamma"))
+    dev = _lib.require_cuda(x, rotation, boundaries_hi, boundaries_lo, out_hi, out_lo, out_norms, *q_bufs)
     d = x.shape[-1]
     if x.dim() < 2:
         x = x.reshape(1, d)
@@ -89,7 +90,7 @@ def quantize_pack(x: torch.Tensor, rotation: torch.Tensor, boundaries_hi: torch.
         a.cent_lo = qjl["cent_lo"].data_ptr() if bits_lo else None
         a.qjl_bits = qjl["bits"].data_ptr() + out_offset * 4
         a.qjl_gamma = qjl["gamma"].data_ptr() + out_offset * 4
-    _lib.check(_lib.lib().tq_quantize_pack(C.byref(a), _lib.stream_ptr(dev)))
+    _lib.check(_lib.launch(dev, "tq_quantize_pack", C.byref(a), _lib.stream_ptr(dev)))
     if fresh:
         out_hi = out_hi.reshape(*lead, t, w_hi)
         out_lo = out_lo.reshape(*lead, t, w_lo) if bits_lo else None
@@ -119,7 +120,8 @@ def dequantize_rows(packed_hi: torch.Tensor, packed_lo: torch.Tensor | None, nor
     packed is (lanes..., cap, width); rows [in_offset, in_offset + n_rows) of every lane are expanded
     into ``out`` (lanes..., out_cap, d) starting at row ``out_offset`` (a fresh tensor if ``out`` is None).
     """
-    dev = _lib.require_cuda(packed_hi, norms, rotation, centroids_hi)
+    q_bufs = () if qjl is None else (qjl.get("proj"), qjl.get("bits"), qjl.get("gamma"))
+    dev = _lib.require_cuda(packed_hi, packed_lo, norms, rotation, centroids_hi, centroids_lo, out, *q_bufs)
     cap = packed_hi.shape[-2]
     t = cap - in_offset if n_rows is None else n_rows
     assert in_offset + t <= cap
@@ -150,7 +152,7 @@ def dequantize_rows(packed_hi: torch.Tensor, packed_lo: torch.Tensor | None, nor
     a.out = out.data_ptr() + out_offset * d * out.element_size()
     a.out_dtype = _lib.dtype_code(out.dtype)
     a.out_lane_stride, a.out_row_stride = out_cap * d, d
-    _lib.check(_lib.lib().tq_dequantize(C.byref(a), _lib.stream_ptr(dev)))
+    _lib.check(_lib.launch(dev, "tq_dequantize", C.byref(a), _lib.stream_ptr(dev)))
     return out
 
 
@@ -182,10 +184,9 @@ def _fused_qk(q_rot, packed_k, norms_k, centroids, D, bits):
     if t_q == 0 or t_kv == 0:
         return out
     q = q_rot.to(torch.float32).contiguous()
-    _lib.check(_lib.lib().tq_qk_scores(q.data_ptr(), packed_k.contiguous().data_ptr(),
-                                       norms_k.to(torch.float32).contiguous().data_ptr(),
-                                       centroids.to(torch.float32).contiguous().data_ptr(), bits, D, t_q, t_kv,
-                                       out.data_ptr(), _lib.stream_ptr(dev)))
+    pk, nk, ce = packed_k.contiguous(), norms_k.to(torch.float32).contiguous(), centroids.to(torch.float32).contiguous()
+    _lib.check(_lib.launch(dev, "tq_qk_scores", q.data_ptr(), pk.data_ptr(), nk.data_ptr(), ce.data_ptr(), bits, D, t_q, t_kv,
+                           out.data_ptr(), _lib.stream_ptr(dev)))
     return out
 
 
@@ -215,6 +216,30 @@ def decode_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
         ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
+
+
+_decode_tables: dict[tuple, torch.Tensor | None] = {}
+
+
+def decode_tables(d: int, seed: int, rotation: torch.Tensor, k_cent: torch.Tensor, k_bits: int, v_cent: torch.Tensor, v_bits: int,
+                  v_cent_scale: float) -> torch.Tensor | None:
+    """Constants of the decode kernel for this (device, head_dim, rotation seed, bit widths), built once and shared by every
+    cache that uses them: the image of the kernel's lookup tables and the rotation matrix split into fp16 halves in the
+    order the tensor-core rotation consumes (``tq_decode_tables_build``).  ``None`` when no kernel uses prebuilt
+    constants for the shape.  The first call for a key synchronises the stream; make it outside graph capture
+    (a cache does, the first time it sees a tensor)."""
+    dev = _lib.require_cuda(rotation, k_cent, v_cent)
+    key = (dev.index, d, seed, k_bits, v_bits, float(v_cent_scale), rotation.data_ptr(), k_cent.data_ptr(), v_cent.data_ptr())
+    if key not in _decode_tables:
+        need = int(_lib.lib().tq_decode_tables_bytes(d, k_bits, v_bits))
+        if need == 0:
+            _decode_tables[key] = None
+        else:
+            buf = torch.empty(need, dtype=torch.uint8, device=dev)
+            _lib.check(_lib.launch(dev, "tq_decode_tables_build", d, rotation.data_ptr(), k_cent.data_ptr(), k_bits, v_cent.data_ptr(),
+                                   v_bits, float(v_cent_scale), buf.data_ptr(), need, _lib.stream_ptr(dev)))
+            _decode_tables[key] = buf
+    return _decode_tables[key]
 
 
 def set_tuning(key: str, value: int) -> None:

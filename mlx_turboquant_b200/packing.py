@@ -27,7 +27,7 @@ def pack_indices(indices: torch.Tensor, bits: int) -> torch.Tensor:
     idx = indices.to(torch.uint8).contiguous()
     out = torch.empty(*indices.shape[:-1], d * bits // 8, dtype=torch.uint8, device=dev)
     n = idx.numel() // d if d else 0
-    _lib.check(_lib.lib().tq_pack(idx.data_ptr(), out.data_ptr(), n, d, bits, _lib.stream_ptr(dev)))
+    _lib.check(_lib.launch(dev, "tq_pack", idx.data_ptr(), out.data_ptr(), n, d, bits, _lib.stream_ptr(dev)))
     return out
 
 
@@ -41,7 +41,7 @@ def unpack_indices(packed: torch.Tensor, bits: int, d: int) -> torch.Tensor:
         raise ValueError(f"packed last dimension {p.shape[-1]} does not match d={d} at {bits} bits ({w})")
     out = torch.empty(*packed.shape[:-1], d, dtype=torch.uint8, device=dev)
     n = p.numel() // w if w else 0
-    _lib.check(_lib.lib().tq_unpack(p.data_ptr(), out.data_ptr(), n, d, bits, _lib.stream_ptr(dev)))
+    _lib.check(_lib.launch(dev, "tq_unpack", p.data_ptr(), out.data_ptr(), n, d, bits, _lib.stream_ptr(dev)))
     return out
 
 

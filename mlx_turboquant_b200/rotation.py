@@ -56,8 +56,8 @@ def _apply(x: torch.Tensor, rotation: torch.Tensor, inverse: bool) -> torch.Tens
         xc = xc.to(torch.float32)
     out = torch.empty(x.shape, dtype=torch.float32, device=dev)
     n = xc.numel() // d if d else 0
-    _lib.check(_lib.lib().tq_rotate(xc.data_ptr(), _lib.dtype_code(xc.dtype), rot.data_ptr(), out.data_ptr(),
-                                    n, d, 1 if inverse else 0, _lib.stream_ptr(dev)))
+    _lib.check(_lib.launch(dev, "tq_rotate", xc.data_ptr(), _lib.dtype_code(xc.dtype), rot.data_ptr(), out.data_ptr(),
+                           n, d, 1 if inverse else 0, _lib.stream_ptr(dev)))
     return out
 
 

@@ -98,6 +98,28 @@ class _DeviceView:
 _TYPESTR = {torch.float16: ("<f2", 2), torch.float32: ("<f4", 4), torch.bfloat16: (None, 2)}
 
 
+class SlotLedger:
+    """Reuse rule of the gather slots, as host-side bookkeeping: with more than one rank a peer may already be writing
+    call n + 1 into a slot while this rank still reads call n from it, unless the two calls use different slots.  So
+    more than one rank needs at least two slots, and the same slot may not take two decode calls in a row."""
+
+    def __init__(self, world: int, n_buffers: int):
+        if n_buffers < 1:
+            raise ValueError("n_buffers must be at least 1")
+        if world > 1 and n_buffers < 2:
+            raise ValueError("with more than one rank a gather needs at least two slots (n_buffers >= 2): a peer may "
+                             "overwrite a slot this rank is still reading")
+        self.world, self.n_buffers, self._last = world, n_buffers, None
+
+    def use(self, i: int) -> None:
+        if not 0 <= i < self.n_buffers:
+            raise IndexError(f"slot {i} of {self.n_buffers}")
+        if self.world > 1 and i == self._last:
+            raise RuntimeError(f"slot {i} was also the previous decode call's slot: a peer could overwrite the result "
+                               "while it is being read; alternate between slots")
+        self._last = i
+
+
 class FusedGather:
     """Every rank's output buffers and arrival counters, mapped into every rank (ranks = GPUs of one node).
 
@@ -121,6 +143,7 @@ class FusedGather:
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         if self.world > _lib.TQ_MAX_PEERS:
             raise ValueError(f"at most {_lib.TQ_MAX_PEERS} ranks")
+        self._ledger = SlotLedger(self.world, n_buffers)
         self.shape, self.dtype, self.n_buffers, self.device = (batch, heads_total, d), dtype, n_buffers, device
         elem = _TYPESTR[dtype][1]
         self._slot_bytes = (batch * heads_total * d * elem + 255) // 256 * 256
@@ -180,13 +203,15 @@ class FusedGather:
         return t
 
     def slot(self, i: int) -> "_lib.PeerGather":
-        """The argument for ``TurboQuantKVCache.attend(..., gather=...)``."""
+        """The argument for ``TurboQuantKVCache.attend(..., gather=...)``; call it once per decode call (it records the
+        slot's use and refuses the same slot twice in a row when there are peers)."""
+        self._ledger.use(i)
         return self._structs[i]
 
     def wait(self, i: int) -> None:
         """Order the current stream behind the arrival of every rank's heads for one more decode call on slot ``i``."""
-        _lib.check(_lib.lib().tq_gather_wait(self._own + self._ctr_off + 8 * i, self._own + self._used_off + 8 * i, self._per_call,
-                                             _lib.stream_ptr(self.device)))
+        _lib.check(_lib.launch(self.device, "tq_gather_wait", self._own + self._ctr_off + 8 * i, self._own + self._used_off + 8 * i,
+                               self._per_call, _lib.stream_ptr(self.device)))
 
     def result(self, i: int) -> torch.Tensor:
         """(batch, heads_total, d) view of this rank's copy of slot ``i`` (complete once ``wait(i)`` has run)."""

@@ -30,7 +30,7 @@ def test_header_symbols_are_exported(built):
 
 def test_version_and_argument_errors_without_gpu(built):
     lib = built.lib()
-    assert lib.tq_version() == 1
+    assert lib.tq_version() == 2
     # argument validation happens on the host before any CUDA call
     assert lib.tq_pack(None, None, 4, 128, 5, None) == -1
     assert b"Unsupported bit-width: 5" in lib.tq_last_error()

@@ -114,6 +114,32 @@ def test_decode_config1_against_oracle_two_kv_heads(oracle):
     assert np.abs(out - ref).max() <= 1e-3 * np.abs(ref).max()
 
 
+def test_decode_config3_against_oracle_two_heads(oracle):
+    """Phi-3.5-mini shape at its full 8192-token context (128 sink + 7936 packed + 128 recent), d = 96, 4-bit keys /
+    2-bit values with the QJL sketch, one sequence x two heads (MHA) so that the CPU oracle stays within seconds:
+    identical packed state and sketches, attention against the reference's corrected dense K / V."""
+    from mlx_turboquant_b200 import TurboQuantKVCache
+    rs = np.random.RandomState(23)
+    h, ctx, d = 2, 8192, 96
+    k, v = kv_like(rs, (1, h, ctx, d)), kv_like(rs, (1, h, ctx, d))
+    q = (rs.randn(1, h, 1, d) / np.sqrt(d)).astype(np.float16)
+    ref_c = oracle.KVCacheOracle(d, host_tables(d), 4, 2, 128, fp16_sink_size=128, qjl_correction=True)
+    rk, rv = ref_c.update_and_fetch(k, v)
+    assert (ref_c.sink_len, ref_c.comp_len, ref_c.fp_len) == (128, ctx - 256, 128)
+    ref = oracle.attention(q, rk, rv)
+    c = TurboQuantKVCache(head_dim=d, num_kv_heads=h, key_bits=4, value_bits=2, residual_window=128, fp16_sink_size=128,
+                          qjl_correction=True)
+    ck, cv = ref_c.comp["k"], ref_c.comp["v"]
+    sk, sv = ref_c.sketch["k"], ref_c.sketch["v"]
+    i32 = lambda a: cu(a.view(np.int32))   # noqa: E731
+    c.state = (cu(ref_c.k), cu(ref_c.v), cu(ck[0]), cu(ck[2]), cu(cv[0]), cu(cv[2]), cu(ref_c.sink_k), cu(ref_c.sink_v), None, None,
+               i32(sk[0]), cu(sk[1]), i32(sv[0]), cu(sv[1]))
+    c.meta_state = {"offset": str(ref_c.offset), "compressed_len": str(ref_c.comp_len), "sink_len": str(ref_c.sink_len),
+                    "fp16_len": str(ref_c.fp_len), "fp16_capacity": str(ref_c.k.shape[2])}
+    out = host(c.attend(cu(q), out_dtype=torch.float32))
+    assert np.abs(out - ref).max() <= 1e-3 * np.abs(ref).max()
+
+
 @pytest.mark.parametrize("kb", (3, 2, 3.5))
 def test_compression_config2_chunking_invariance(kb):
     """126,976 tokens x 8 heads drained as 31 chunks of 4096 in ONE launch give byte-identical codes and norms to 31

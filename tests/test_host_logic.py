@@ -181,3 +181,77 @@ def test_detect_outlier_layers_on_cpu_model():
 
     assert detect_outlier_layers(Tiny([1.0, 1.0, 10.0, 1.0])) == [2]
     assert detect_outlier_layers(Tiny([0.0, 0.0])) == []
+
+
+def test_library_calls_run_with_the_tensors_device_current(monkeypatch):
+    """A cache on cuda:1 used while cuda:0 is current: the launch helper makes cuda:1 current around the call (the
+    library launches on the current device).  Faked: no GPU is touched."""
+    import contextlib
+
+    import torch
+
+    from mlx_turboquant_b200 import _lib
+    state = {"current": 0, "seen": []}
+
+    class FakeLib:
+        def tq_pack(self, *args):
+            state["seen"].append((state["current"], args))
+            return 0
+
+    @contextlib.contextmanager
+    def fake_device(idx):
+        prev, state["current"] = state["current"], idx
+        try:
+            yield
+        finally:
+            state["current"] = prev
+
+    monkeypatch.setattr(_lib, "lib", lambda: FakeLib())
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: state["current"])
+    monkeypatch.setattr(torch.cuda, "device", fake_device)
+    assert _lib.launch(torch.device("cuda", 1), "tq_pack", 1, 2) == 0
+    assert _lib.launch(torch.device("cuda", 0), "tq_pack", 3) == 0
+    assert _lib.launch(torch.device("cuda"), "tq_pack", 4) == 0            # no index: the current device
+    assert [s[0] for s in state["seen"]] == [1, 0, 0] and state["current"] == 0
+
+
+def test_cpu_tensors_are_refused_before_any_launch():
+    """`cache.state = <checkpoint loaded on the CPU>` and CPU inputs raise instead of reaching a kernel."""
+    import torch
+
+    from mlx_turboquant_b200 import TurboQuantKVCache, _lib, kernels
+    c = TurboQuantKVCache(head_dim=128, num_kv_heads=2)
+    cpu_state = (torch.zeros(1, 2, 8, 128, dtype=torch.float16), torch.zeros(1, 2, 8, 128, dtype=torch.float16),
+                 torch.zeros(1, 2, 16, 64, dtype=torch.uint8), torch.zeros(1, 2, 16), torch.zeros(1, 2, 16, 32, dtype=torch.uint8),
+                 torch.zeros(1, 2, 16))
+    c._dargs, c._dargs_key, c._ws_key = object(), ("stale",), ("stale",)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        c.state = cpu_state
+    assert c._k.hi is None and c.keys is None                                # nothing was adopted
+    c.state = (None,) * 6                                                     # an empty state is fine and drops the cached arguments
+    assert c._dargs is None and c._dargs_key is None and c._ws_key is None
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        c.update(torch.zeros(1, 2, 1, 128), torch.zeros(1, 2, 1, 128))
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        c.attend(torch.zeros(1, 8, 1, 128))
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        kernels.quantize_pack(torch.zeros(4, 128), torch.eye(128), torch.zeros(15), 4)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        TurboQuantKVCache._append(torch.zeros(1, 2, 8, 128), torch.zeros(1, 2, 8, 128), torch.zeros(1, 2, 1, 128), torch.zeros(1, 2, 1, 128), 0)
+    assert _lib.require_cuda(None, None) is None
+
+
+def test_gather_slot_ledger():
+    from mlx_turboquant_b200.sharding import SlotLedger
+    with pytest.raises(ValueError):
+        SlotLedger(2, 1)
+    with pytest.raises(ValueError):
+        SlotLedger(1, 0)
+    one = SlotLedger(1, 1)                    # a single rank has no peer to race with
+    one.use(0); one.use(0)
+    led = SlotLedger(4, 3)
+    led.use(0); led.use(1); led.use(0); led.use(2)
+    with pytest.raises(RuntimeError, match="alternate"):
+        led.use(2)
+    with pytest.raises(IndexError):
+        led.use(3)

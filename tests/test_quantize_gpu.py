@@ -47,7 +47,8 @@ def test_mse_quantizer_against_reference_vectors(golden, tables, d, bits):
     np.testing.assert_allclose(host(qt.norms), golden[tag + "_norms"], rtol=2e-6)
     frac, step, dist = code_mismatch_report(host(qt.packed_indices), golden[tag + "_packed"], bits, d,
                                             golden[tag + "_y"], tables[(d, bits)][1])
-    assert frac < 1e-3 and step <= 1 and dist < 1e-6, (frac, step, dist)
+    # fewer than 1e-4 of the codes may differ (48 rows: at most one code), by one level, within 1e-6 of a boundary
+    assert frac <= max(1e-4, 1.0 / x.size) and step <= 1 and dist < 1e-6, (frac, step, dist)
     # dequantize the REFERENCE's packed bytes: isolates the dequantize kernel
     from mlx_turboquant_b200.quantizer import QuantizedTensor
     deq = host(q.dequantize(QuantizedTensor(cu(golden[tag + "_packed"]), cu(golden[tag + "_norms"]), bits, d)))
@@ -97,7 +98,8 @@ def test_fractional_quantize_dequantize(oracle, tables, dtype):
     np.testing.assert_allclose(host(n), rn, rtol=2e-6)
     f1 = code_mismatch_report(host(ph), rh, 4, 64, ry[..., :64], tables[(d, 4)][1])
     f2 = code_mismatch_report(host(pl), rl, 3, 64, ry[..., 64:], tables[(d, 3)][1])
-    assert f1[0] < 1e-3 and f1[1] <= 1 and f2[0] < 1e-3 and f2[1] <= 1
+    n_half = x.size // 2          # 2 x 3 x 77 x 64 codes per half: fewer than 1e-4 of them (at most two) may differ
+    assert f1[0] <= max(1e-4, 2.0 / n_half) and f1[1] <= 1 and f2[0] <= max(1e-4, 2.0 / n_half) and f2[1] <= 1
     deq = host(kernels.dequantize_rows(cu(rh), cu(rl), cu(rn), rot, c4, 4, c3, 3, d))
     ref = oracle.split_dequantize(rh, rl, rn, oracle.rotation_matrix(d), tables[(d, 4)][0], 4, tables[(d, 3)][0], 3, d)
     np.testing.assert_allclose(deq, ref, rtol=0, atol=2e-6 * np.abs(ref).max())

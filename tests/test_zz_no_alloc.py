@@ -37,6 +37,7 @@ def _args_for(cache, q, out, ws):
     a.res_k, a.res_v = cache.keys.data_ptr(), cache.values.data_ptr()
     a.res_len, a.res_lane_stride = cache._fp16_len, cache.keys.shape[2]
     a.out, a.out_dtype = out.data_ptr(), _lib.dtype_code(out.dtype)
+    a.tables = _lib.ptr(cache._tables)
     if ws is not None:
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
     return a
@@ -68,9 +69,9 @@ def test_static_scratch_matches_workspace_entry_point_twice_in_a_row():
             out = torch.full((b, hq, d), float("nan"), dtype=torch.float32, device="cuda")
             _lib.check(lib.tq_decode_attn_static(C.byref(_args_for(cache, q, out, None)), stream))
             torch.cuda.synchronize()
-            # same kernel, same split plan: identical up to the order in which partials are merged (none here)
-            err = (out - ref).abs().max().item() / ref.abs().max().item()
-            assert torch.isfinite(out).all() and err < 1e-3, err
+            # same kernel, same split plan, and partials are merged in a fixed order whichever CTA arrives last:
+            # the two entry points give the same bits
+            assert torch.isfinite(out).all() and torch.equal(out, ref)
         # and it still agrees with attention over the dense tensors the cache would hand out
         dk, dv = cache.update_and_fetch(cache.keys[:, :, :0], cache.values[:, :, :0])
         rep = hq // hkv
