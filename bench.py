@@ -253,6 +253,49 @@ def bench_quantize(torch, dev, steps, warmup, peak, pool_size=8):
     return out
 
 
+def bench_quantize_c3(torch, dev, steps, warmup, peak):
+    """Prefill compression of one Phi-3.5-mini-shaped layer with the QJL sketch: batch 16 x 32 KV heads x 7936 tokens of
+    head_dim 96 leave the fp16 buffer (context 8192, 128 sink, 128 recent), 4-bit keys and 2-bit values, one fused launch per
+    side writing codes, norms, sign words and residual norms.  Two distinct input sets (3.1 GB) are cycled."""
+    from mlx_turboquant_b200 import kernels
+    from mlx_turboquant_b200.codebook import get_codebook
+    from mlx_turboquant_b200.qjl import generate_projection_matrix_host
+    from mlx_turboquant_b200.rotation import generate_rotation_matrix_host, get_rotation_matrix
+    b, h, d, t = 16, 32, 96, 8192 - SINK - RW
+    rot = get_rotation_matrix(d, 42, dev)
+    prot = torch.from_numpy((generate_projection_matrix_host(d, 32).astype("float64") @ generate_rotation_matrix_host(d, 42).astype("float64").T)
+                            .astype("float32")).to(dev)
+    g = torch.Generator(device=dev).manual_seed(2100)
+    pool = [torch.randn(2, b, h, t, d, device=dev, generator=g, dtype=torch.float16) for _ in range(2)]
+    sides = []
+    for bits in (4, 2):
+        cent, bnd = get_codebook(d, bits, dev)
+        sides.append(dict(bits=bits, bnd=bnd, p=torch.empty(b, h, t, d * bits // 8, dtype=torch.uint8, device=dev),
+                          n=torch.empty(b, h, t, dtype=torch.float32, device=dev),
+                          q=dict(proj_rot=prot, cent_hi=cent, cent_lo=None, bits=torch.empty(b, h, t, dtype=torch.int32, device=dev),
+                                 gamma=torch.empty(b, h, t, dtype=torch.float32, device=dev))))
+
+    def step():
+        for x in pool:
+            for i, sd in enumerate(sides):
+                kernels.quantize_pack(x[i], rot, sd["bnd"], sd["bits"], out_hi=sd["p"], out_norms=sd["n"], out_offset=0, qjl=sd["q"])
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / (steps * len(pool))                  # per layer (K and V)
+    bytes_per_unit = 2 * d * 2 + (d * 4 // 8 + 4) + (d * 2 // 8 + 4) + 2 * (4 + 4)
+    gbs = b * h * t * bytes_per_unit / (ms * 1e-3) / 1e9
+    del pool
+    return {"workload": "phi35mini_layer_prefill_compress_b16_h32_d96_k4v2_qjl", "ms_per_layer": ms, "rows_per_side": b * h * t,
+            "bytes_per_token_head": bytes_per_unit, "hbm_gbs": gbs, "frac_of_peak": gbs / peak, "launches_per_layer": 2}
+
+
 def bench_c3(torch, dev, steps, warmup, peak):
     """Phi-3.5-mini-shaped layer with the QJL sketch: 32 query = 32 KV heads, head_dim 96, batch 16, context 8192 =
     128 sink + 7936 packed (4-bit keys, 2-bit values, sign sketches) + 128 recent.  One launch = one layer-step;
@@ -514,9 +557,7 @@ def run_b200(args):
     def e2e_step():
         xdev.copy_(hx, non_blocking=True)
         for i in range(LAYERS):
-            c = e2e_caches[i]
-            c.update(xk[i], xv[i])
-            c.attend(xq[i], out=xo[i])
+            e2e_caches[i].decode_step(xq[i], xk[i], xv[i], out=xo[i])
         hout.copy_(odev, non_blocking=True)
         torch.cuda.current_stream(dev).synchronize()
     e2e_steps = min(args.steps, 20)
@@ -544,7 +585,7 @@ def run_b200(args):
                    if split else "independent sequences per GPU, no collective"},
         "e2e": {"value": e2e_gbs, "unit": "GB/s", "ms_per_step": e2e_ms, "us_per_layer_step": e2e_ms * 1e3 / LAYERS,
                 "h2d_bytes_per_step": LAYERS * (HQ * D * 2 + 2 * HKV * D * 2), "d2h_bytes_per_step": LAYERS * HQ * D * 2,
-                "path": "per step: one pinned-host -> device copy of all layers' q/k/v, TurboQuantKVCache.update + .attend per layer, one device -> pinned-host copy of all layers' results"},
+                "path": "per step: one pinned-host -> device copy of all layers' q/k/v, TurboQuantKVCache.decode_step per layer (append + attention, one launch), one device -> pinned-host copy of all layers' results"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clk.summary(),
         "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
@@ -556,6 +597,7 @@ def run_b200(args):
     if rank == 0 and world == 1 and not args.no_secondary:
         line["secondary"] = {"metric": "quantize_pack_mtokens_per_s", "unit": "Mtokens/s (token = position x 8 KV heads x 32 layers)",
                              "chunk_tokens": QCHUNK, **bench_quantize(torch, dev, 3, 3, peak, args.quantize_pool)}
+        line["secondary"]["compress_qjl_d96_b16"] = bench_quantize_c3(torch, dev, 3, 2, peak)
         line["secondary"]["decode_qjl_d96_b16"] = bench_c3(torch, dev, 5, 3, peak)
     if rank == 0 and world == 1 and not args.no_cpu:
         step, info = cpu_reference_step_factory(1)

@@ -121,6 +121,15 @@ typedef struct {
  * (quantizer.py:87-109, cache.py:276-343, kernels.py:313-360). */
 int tq_dequantize(const tq_dequantize_args* a, void* stream);
 
+/* ---- QJL sketch ---------------------------------------------------------------------------- */
+
+/* qjl_quantize (qjl.py:47-67): signs[r][p] = (x[r] . S[p] >= 0) as one byte (0 / 1) each, gamma[r] = |x[r]|.
+ * x (n, d) float32, proj S (m, d) float32, d <= 256, any m. */
+int tq_qjl_quantize(const float* x, const float* proj, uint8_t* signs, float* gamma, int64_t n, int d, int m, void* stream);
+/* qjl_dequantize (qjl.py:70-94): out[r] = (sqrt(pi/2) / d) * gamma[r] * (z[r] @ S), z = +1 where signs != 0, else -1. */
+int tq_qjl_dequantize(const uint8_t* signs, const float* gamma, const float* proj, float* out, int64_t n, int d, int m,
+                      void* stream);
+
 /* ---- fused QK scores --------------------------------------------------------------------- */
 
 /* fused_qk_scores_{2,3,4}bit (kernels.py:558-629): out[q,k] = norms[k] * sum_j q_rot[q,j]*c[idx(k,j)];
@@ -220,6 +229,14 @@ size_t tq_decode_workspace_bytes(int batch, int n_q_heads, int n_kv_heads, int d
  * (pre-rotated query, rotation.py:81-110) extended with softmax and values. */
 int tq_decode_attn(const tq_decode_args* a, void* stream);
 
+/* One decode step in one launch: the new token's key and value rows (k_new, v_new: (batch, n_kv_heads, d) of dense_dtype,
+ * contiguous, 16-byte aligned) are stored at row res_len of res_k / res_v - which must be writable and have room,
+ * res_lane_stride > res_len - and attention runs over [sink | packed | res_len recent tokens | the new token].  a->res_len
+ * is the length BEFORE the call; the caller counts the token afterwards.  The append of update_and_fetch
+ * (cache.py:632-672) folded into the attention that follows it; the caller still decides when tokens leave the buffer
+ * for compression (tq_quantize_pack) and when a token belongs to the sink instead. */
+int tq_decode_step(const tq_decode_args* a, const void* k_new, const void* v_new, void* stream);
+
 /* Same computation as tq_decode_attn for callers that can neither lend a workspace nor allocate one at call
  * time (a process that gave the whole device to its own memory pool at start-up; a step loop that cannot afford
  * a driver allocation).  It has no counterpart in the reference.  `workspace` / `workspace_bytes` in the
@@ -263,7 +280,6 @@ float tq_fp16_table_scale(const float* centroids_host, int n);
 /* Host-side tuning knobs of the split heuristic (process-wide; no reference counterpart):
  *   "decode_ctas_per_sm" 1..8, "decode_splits" 0 (auto)..448, "decode_force_general" 0/1,
  *   "decode_pdl" 0/1 (programmatic dependent launch: a call's prologue overlaps the previous kernel's tail),
- *   "quantize_tma" 0/1 (tensor-core quantize kernel: rows fetched by tiled TMA copies, or by loads in producer warps),
  *   "gather_wait_polls" 1000..4000000 (polls of tq_gather_wait before it gives up; default 2000000, some two seconds).
  * Changing them changes tq_decode_workspace_bytes for the same sizes. */
 int tq_set_tuning(const char* key, int value);

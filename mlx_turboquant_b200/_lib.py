@@ -87,12 +87,15 @@ PROTOTYPES = {
     "tq_rotate": (_i, [_vp, _i, _vp, _vp, _i64, _i, _i, _vp]),
     "tq_quantize_pack": (_i, [C.POINTER(QuantizeArgs), _vp]),
     "tq_dequantize": (_i, [C.POINTER(DequantizeArgs), _vp]),
+    "tq_qjl_quantize": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _vp]),
+    "tq_qjl_dequantize": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _vp]),
     "tq_qk_scores": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i64, _i64, _vp, _vp]),
     "tq_append_tokens": (_i, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _vp]),
     "tq_decode_workspace_bytes": (_sz, [_i, _i, _i, _i, _i64, _i64]),
     "tq_decode_tables_bytes": (_sz, [_i, _i, _i]),
     "tq_decode_tables_build": (_i, [_i, _vp, _vp, _i, _vp, _i, _f, _vp, _sz, _vp]),
     "tq_decode_attn": (_i, [C.POINTER(DecodeArgs), _vp]),
+    "tq_decode_step": (_i, [C.POINTER(DecodeArgs), _vp, _vp, _vp]),
     "tq_decode_attn_static": (_i, [C.POINTER(DecodeArgs), _vp]),
     "tq_set_tuning": (_i, [C.c_char_p, _i]),
     "tq_fp16_table_scale": (_f, [_vp, _i]),

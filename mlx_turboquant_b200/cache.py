@@ -454,7 +454,7 @@ class TurboQuantKVCache:
 
     # ---- attention on the packed cache -----------------------------------------------------------
     def attend(self, queries: torch.Tensor, scale: float | None = None, out_dtype=None, gather=None,
-               out: torch.Tensor | None = None) -> torch.Tensor | None:
+               out: torch.Tensor | None = None, _new=None) -> torch.Tensor | None:
         """softmax(scale * q K^T) V for ONE query token per sequence, straight from packed storage.
 
         ``queries`` is (B, n_q_heads, 1, D) or (B, n_q_heads, D); the result has the same shape and, unless
@@ -471,7 +471,7 @@ class TurboQuantKVCache:
         if not squeeze and queries.shape[2] != 1:
             raise NotImplementedError("attend handles a single query token per sequence (decode step)")
         b, hq = queries.shape[0], queries.shape[1]
-        if self.empty():
+        if self.empty() and _new is None:
             raise ValueError("attend on an empty cache")
         q = queries.reshape(b, hq, d)
         if q.dtype not in (torch.float16, torch.bfloat16, torch.float32):
@@ -503,19 +503,47 @@ class TurboQuantKVCache:
         a.q, a.out = q.data_ptr(), (None if out is None else out.data_ptr())
         a.gather = C.pointer(gather) if gather is not None else None
         a.c_len, a.sink_len, a.res_len = self._compressed_len, self._sink_len, self._fp16_len
-        dense_len = self._sink_len + self._fp16_len
+        dense_len = self._sink_len + self._fp16_len + (0 if _new is None else 1)
         ws_key = (self._compressed_len, (dense_len + 15) >> 4)        # the split plan depends on whole 16-token tiles only
         if ws_key != self._ws_key:
             self._ws_need = _lib.lib().tq_decode_workspace_bytes(b, hq, a.n_kv_heads, d, self._compressed_len, ws_key[1] << 4)
             self._ws_key = ws_key
         ws = kernels.decode_workspace(dev, self._ws_need)
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
-        _lib.check(_lib.launch(dev, "tq_decode_attn", C.byref(a), _lib.stream_ptr(dev)))
+        if _new is None:
+            _lib.check(_lib.launch(dev, "tq_decode_attn", C.byref(a), _lib.stream_ptr(dev)))
+        else:      # append the token's rows and attend over them in the same launch
+            _lib.check(_lib.launch(dev, "tq_decode_step", C.byref(a), _new[0].data_ptr(), _new[1].data_ptr(), _lib.stream_ptr(dev)))
         if out is None:
             return None
         if given is not None:
             return given
         return out if squeeze else out.reshape(b, hq, 1, d)
+
+    def decode_step(self, queries: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, scale: float | None = None,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+        """One decode step: ``update(keys, values)`` followed by ``attend(queries)``, as ONE kernel launch when the new token
+        simply joins the recent-token buffer (no growth, no compression due, not a sink token, same dtype as the buffer):
+        the kernel stores the token's rows itself and attends over them.  Any other step takes the two calls."""
+        t_new = keys.shape[2] if keys.dim() == 4 else 0
+        fast = (t_new == 1 and self.keys is not None and self.offset >= self.fp16_sink_size
+                and self._fp16_len + 1 <= self._fp16_capacity and keys.dtype == self.keys.dtype and values.dtype == self.values.dtype
+                and keys.is_contiguous() and values.is_contiguous() and (queries.dim() == 3 or queries.shape[2] == 1))
+        if fast:
+            new_len = self._fp16_len + 1                     # would update() drain after this token?  (cache.py:497-533)
+            if self.chunk_size <= 0:
+                fast = new_len <= self.residual_window * 2
+            else:
+                fast = new_len < self.residual_window + self.chunk_size
+        if not fast:
+            self.update(keys, values)
+            return self.attend(queries, scale=scale, out=out)
+        if keys.device != self._device or values.device != self._device:
+            raise RuntimeError(f"this cache lives on {self._device}; got tensors on {keys.device}")
+        res = self.attend(queries, scale=scale, out=out, _new=(keys, values))
+        self._fp16_len += 1
+        self.offset += 1
+        return res
 
     def _fill_decode_args(self, b: int, hq: int, q_dtype, out_dtype, scale) -> "_lib.DecodeArgs":
         d = self.head_dim

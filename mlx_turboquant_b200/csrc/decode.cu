@@ -30,8 +30,6 @@
 
 namespace tq {
 
-void set_quantize_tma(int on);      // quantize_tc.cu
-
 constexpr int GNW = 8;                 // warps per CTA of the general kernel
 
 // ---- shared memory plan ----------------------------------------------------------------------------------
@@ -685,13 +683,22 @@ template <int D, bool QJL> static int launch_decode(const DecodeParams& p, cudaS
 }
 
 // Validates the arguments, picks the path and the split plan and fills the kernel parameters.
-int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_bytes, DecodeParams* out, bool* direct_out) {
+int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_bytes, DecodeParams* out, bool* direct_out,
+                   const void* k_new, const void* v_new) {
     if (!a) return fail(TQ_ERR_INVALID, "tq_decode_attn: null args");
+    const int n_new = k_new ? 1 : 0;
+    if (n_new) {
+        if (!v_new || !a->res_k || !a->res_v || a->res_lane_stride <= a->res_len)
+            return fail(TQ_ERR_INVALID, "tq_decode_step: the recent-token buffers have no room for the new token (%lld of %lld rows used)",
+                        (long long)a->res_len, (long long)a->res_lane_stride);
+        if (!aligned(k_new, 16) || !aligned(v_new, 16) || !aligned(a->res_k, 16) || !aligned(a->res_v, 16) || (a->d * (a->dense_dtype == TQ_F32 ? 4 : 2)) % 16)
+            return fail(TQ_ERR_INVALID, "tq_decode_step: new rows and recent-token buffers must be 16-byte aligned");
+    }
     const int d = a->d;
     if (a->batch <= 0 || a->n_q_heads <= 0 || a->n_kv_heads <= 0 || a->n_q_heads % a->n_kv_heads)
         return fail(TQ_ERR_INVALID, "tq_decode_attn: batch=%d q_heads=%d kv_heads=%d", a->batch, a->n_q_heads, a->n_kv_heads);
     if (d != 64 && d != 96 && d != 128 && d != 256) return fail(TQ_ERR_UNSUPPORTED, "tq_decode_attn: d=%d (64, 96, 128 or 256)", d);
-    if (a->c_len < 0 || a->sink_len < 0 || a->res_len < 0 || a->c_len + a->sink_len + a->res_len == 0)
+    if (a->c_len < 0 || a->sink_len < 0 || a->res_len < 0 || a->c_len + a->sink_len + a->res_len + n_new == 0)
         return fail(TQ_ERR_INVALID, "tq_decode_attn: the cache holds no tokens");
     if (a->c_len >= (int64_t(1) << 30)) return fail(TQ_ERR_UNSUPPORTED, "tq_decode_attn: c_len too large");
     if (!a->q || !a->rot || (!a->out && !a->gather) || !workspace) return fail(TQ_ERR_INVALID, "tq_decode_attn: null pointer");
@@ -711,14 +718,14 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
         }
     }
     if ((a->sink_len > 0 && (!a->sink_k || !a->sink_v || a->sink_lane_stride < a->sink_len)) ||
-        (a->res_len > 0 && (!a->res_k || !a->res_v || a->res_lane_stride < a->res_len)))
+        (a->res_len > 0 && (!a->res_k || !a->res_v || a->res_lane_stride < a->res_len + n_new)))
         return fail(TQ_ERR_INVALID, "tq_decode_attn: bad sink / residual buffers");
     if (a->dense_dtype == TQ_F16 && ((a->sink_len > 0 && (!aligned(a->sink_k, 16) || !aligned(a->sink_v, 16))) ||
                                      (a->res_len > 0 && (!aligned(a->res_k, 16) || !aligned(a->res_v, 16)))))
         return fail(TQ_ERR_INVALID, "tq_decode_attn: fp16 sink / residual buffers must be 16-byte aligned");
     if (!aligned(workspace, 256)) return fail(TQ_ERR_INVALID, "tq_decode_attn: workspace must be 256-byte aligned");
 
-    const int64_t dense_len = a->sink_len + a->res_len;
+    const int64_t dense_len = a->sink_len + a->res_len + n_new;
     // direct path: 4-bit keys / 2-bit values, d = 128, rows and norms addressable in aligned 16-byte chunks
     if (a->tables && !aligned(a->tables, 256)) return fail(TQ_ERR_INVALID, "tq_decode_attn: tables must be 256-byte aligned");
     const bool direct = !g_tune_force_general && a->tables && d == 128 && a->c_len > 0 && a->k_bits_hi == 4 && a->k_bits_lo == 0 &&
@@ -742,6 +749,7 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
     }
     p.sink_k = a->sink_k; p.sink_v = a->sink_v; p.res_k = a->res_k; p.res_v = a->res_v;
     p.sink_len = a->sink_len; p.sink_ls = a->sink_lane_stride; p.res_len = a->res_len; p.res_ls = a->res_lane_stride;
+    p.k_new = k_new; p.v_new = v_new; p.res_k_w = const_cast<void*>(a->res_k); p.res_v_w = const_cast<void*>(a->res_v);
     p.n_ps = sp.n_ps; p.n_ds = sp.n_ds; p.p_tps = sp.p_tps; p.d_tps = sp.d_tps;
     p.q = a->q; p.q_dtype = a->q_dtype; p.scale = a->scale; p.rot = a->rot;
     p.v_scale_hi = a->v_cent_scale_hi > 0.f ? a->v_cent_scale_hi : 1.f;
@@ -790,7 +798,6 @@ extern "C" int tq_set_tuning(const char* key, int value) {
     else if (k == "decode_force_general" && (value == 0 || value == 1)) g_tune_force_general = value;
     else if (k == "decode_pdl" && (value == 0 || value == 1)) g_tune_pdl = value;
     else if (k == "decode_splits" && value >= 0 && value <= MAX_SPLITS - 64) g_tune_splits = value;
-    else if (k == "quantize_tma" && (value == 0 || value == 1)) set_quantize_tma(value);
     else if (k == "gather_wait_polls" && value >= 1000 && value <= 4000000) g_tune_wait_polls = value;
     else return fail(TQ_ERR_INVALID, "tq_set_tuning: unknown key or bad value: %s=%d", key, value);
     return TQ_OK;
@@ -891,6 +898,20 @@ extern "C" size_t tq_decode_workspace_bytes(int batch, int n_q_heads, int n_kv_h
     const size_t a = ws_layout(batch, n_q_heads, n_kv_heads, d, plan_splits(batch, n_q_heads, n_kv_heads, c_len, dense_len, sm_count(), false)).total;
     const size_t b = ws_layout(batch, n_q_heads, n_kv_heads, d, plan_splits(batch, n_q_heads, n_kv_heads, c_len, dense_len, sm_count(), true)).total;
     return a > b ? a : b;
+}
+
+extern "C" int tq_decode_step(const tq_decode_args* a, const void* k_new, const void* v_new, void* stream) {
+    if (!k_new || !v_new) return fail(TQ_ERR_INVALID, "tq_decode_step: null new rows");
+    DecodeParams p;
+    bool direct = false;
+    int rc = decode_prepare(a, a ? a->workspace : nullptr, a ? a->workspace_bytes : 0, &p, &direct, k_new, v_new);
+    if (rc) return rc;
+    const size_t counter_bytes = size_t(p.B) * p.Hkv * p.HG * sizeof(int);
+    if (counter_bytes > COUNTER_AREA) {
+        cudaError_t e = cudaMemsetAsync(p.counters, 0, counter_bytes, static_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_decode_step: clearing counters: %s", cudaGetErrorString(e));
+    }
+    return decode_launch(p, direct, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int tq_decode_attn(const tq_decode_args* a, void* stream) {

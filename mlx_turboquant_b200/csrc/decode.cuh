@@ -25,6 +25,8 @@ struct DecodeParams {
     int dense_dtype;
     const void *sink_k, *sink_v, *res_k, *res_v;
     int64_t sink_len, sink_ls, res_len, res_ls;
+    const void *k_new, *v_new;         // one new row per cache lane to append at row res_len and attend to (or null)
+    void *res_k_w, *res_v_w;           // the recent-token buffers, writable (append)
     int n_ps, n_ds;                    // packed / dense splits
     int64_t p_tps, d_tps;              // tiles per split
     const void* q; int q_dtype; float scale; const float* rot;
@@ -44,7 +46,8 @@ struct DecodeParams {
 
 // Validates the arguments, picks the path and the split plan and fills the kernel parameters for the given
 // scratch buffer (which must be zero-filled before its first use; the kernel leaves its counters at zero).
-int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_bytes, DecodeParams* out, bool* direct_out);
+int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_bytes, DecodeParams* out, bool* direct_out,
+                   const void* k_new = nullptr, const void* v_new = nullptr);
 int decode_launch(const DecodeParams& p, bool direct, cudaStream_t s);
 
 // decode_direct.cu: the kernel for 4-bit keys / 2-bit values at d = 128.  direct_supported() checks once per

@@ -224,8 +224,30 @@ __device__ __forceinline__ void dense_tiles(const DecodeParams& p, int64_t kvl, 
                                             const uint32_t (&bq)[D / 16][2], WarpAcc<D, NZ>& st, int warp, int lane) {
     constexpr int LD = stage_ld<D>();
     const int g = lane >> 2;
-    const int64_t n_tok = p.sink_len + p.res_len;
+    // tokens [0, sink_len) sit in the sink, the next res_len in the recent-token buffer; a token that this very call appends
+    // (k_new / v_new: one row per lane) comes last and is read from where the caller left it
+    const int64_t n_tok = p.sink_len + p.res_len + (p.k_new ? 1 : 0);
     const int64_t tile_hi = min(tile_hi_in, (n_tok + TILE - 1) / TILE);
+    auto row_of = [&](int64_t tok, bool keys, int64_t& e) -> const void* {     // base pointer and element offset of a token's row
+        if (tok < p.sink_len) { e = (kvl * p.sink_ls + tok) * D; return keys ? p.sink_k : p.sink_v; }
+        const int64_t r = tok - p.sink_len;
+        if (r < p.res_len) { e = (kvl * p.res_ls + r) * D; return keys ? p.res_k : p.res_v; }
+        e = kvl * D;
+        return keys ? p.k_new : p.v_new;
+    };
+    if (p.k_new) {
+        // the warp that owns the new token's tile also stores the row at the end of the recent-token buffer (the caller's
+        // slice assignment, cache.py:632-672); CTAs of different head groups write the same bytes
+        const int64_t new_tile = (n_tok - 1) / TILE;
+        if (new_tile >= tile_lo && new_tile < tile_hi && (new_tile - tile_lo) % NW == warp) {
+            const int es = p.dense_dtype == TQ_F32 ? 4 : 2;
+            const int64_t dst = (kvl * p.res_ls + p.res_len) * D * es, src = kvl * D * es;
+            for (int c = lane; c < D * es / 16; c += 32) {
+                *reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.res_k_w) + dst + c * 16) = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(p.k_new) + src) + c);
+                *reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.res_v_w) + dst + c * 16) = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(p.v_new) + src) + c);
+            }
+        }
+    }
     for (int64_t tile = tile_lo + warp; tile < tile_hi; tile += NW) {
         const int64_t tok0 = tile * TILE;
         float sck = 1.f, scv = 1.f;                       // staging scales of row lane >> 1 (keys, values)
@@ -238,10 +260,11 @@ __device__ __forceinline__ void dense_tiles(const DecodeParams& p, int64_t kvl, 
                 const int64_t tok = tok0 + r;
                 kv[i] = make_uint4(0, 0, 0, 0); vv[i] = kv[i];
                 if (tok < n_tok) {
-                    const bool in_sink = tok < p.sink_len;
-                    const int64_t e = (in_sink ? kvl * p.sink_ls + tok : kvl * p.res_ls + (tok - p.sink_len)) * D + c8 * 8;
-                    kv[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(in_sink ? p.sink_k : p.res_k) + e));
-                    vv[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(in_sink ? p.sink_v : p.res_v) + e));
+                    int64_t e;
+                    const __half* kb = static_cast<const __half*>(row_of(tok, true, e));
+                    const __half* vb = static_cast<const __half*>(row_of(tok, false, e));
+                    kv[i] = __ldg(reinterpret_cast<const uint4*>(kb + e + c8 * 8));
+                    vv[i] = __ldg(reinterpret_cast<const uint4*>(vb + e + c8 * 8));
                 }
             }
 #pragma unroll
@@ -259,10 +282,10 @@ __device__ __forceinline__ void dense_tiles(const DecodeParams& p, int64_t kvl, 
                 const int64_t tok = tok0 + r;
                 float mk = 0.f, mv = 0.f;
                 if (tok < n_tok) {
-                    const bool in_sink = tok < p.sink_len;
-                    const int64_t e = (in_sink ? kvl * p.sink_ls + tok : kvl * p.res_ls + (tok - p.sink_len)) * D + hf * (D / 2);
-                    const void* kb = in_sink ? p.sink_k : p.res_k;
-                    const void* vb = in_sink ? p.sink_v : p.res_v;
+                    int64_t e;
+                    const void* kb = row_of(tok, true, e);
+                    const void* vb = row_of(tok, false, e);
+                    e += hf * (D / 2);
                     for (int i = 0; i < D / 2; ++i) {
                         mk = fmaxf(mk, fabsf(load_as_f32(kb, p.dense_dtype, e + i)));
                         mv = fmaxf(mv, fabsf(load_as_f32(vb, p.dense_dtype, e + i)));
@@ -281,10 +304,10 @@ __device__ __forceinline__ void dense_tiles(const DecodeParams& p, int64_t kvl, 
                 const float fk = __shfl_sync(0xffffffffu, sck, 2 * r), fv = __shfl_sync(0xffffffffu, scv, 2 * r);
                 uint4 kv = make_uint4(0, 0, 0, 0), vv = kv;
                 if (tok < n_tok) {
-                    const bool in_sink = tok < p.sink_len;
-                    const int64_t e = (in_sink ? kvl * p.sink_ls + tok : kvl * p.res_ls + (tok - p.sink_len)) * D + c8 * 8;
-                    const void* kb = in_sink ? p.sink_k : p.res_k;
-                    const void* vb = in_sink ? p.sink_v : p.res_v;
+                    int64_t e;
+                    const void* kb = row_of(tok, true, e);
+                    const void* vb = row_of(tok, false, e);
+                    e += c8 * 8;
                     __half hk[8], hv[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {

@@ -1,23 +1,35 @@
-// Fused quantize kernel on the 5th-generation tensor cores (tcgen05 + TMEM) for fp16 rows with d = 128:
-//   norm -> rotation (128 x 128 x 128 contraction per tile of 128 rows) -> Lloyd-Max boundary search -> bit-pack.
+// Fused quantize kernel on the 5th-generation tensor cores (tcgen05 + TMEM) for fp16 / bf16 rows with d in {64, 96, 128}:
+//   norm -> rotation (128 rows x d x d contraction per tile) -> Lloyd-Max boundary search -> bit-pack (+ QJL sketch).
 //
-// The rotation has to be float32-accurate (a code flips whenever a rotated value crosses a boundary), so the
-// fp16 rows are used UN-normalised as exact MMA operands and R is split into two fp16 matrices,
-// R = R_hi + 2^-11 * R_lo; both products are exact in the fp32 accumulators, and the normalisation by the
-// row norm is applied afterwards.  Per tile: 2 x 8 tcgen05.mma (M = 128, N = 128, K = 16) into two TMEM
-// accumulators, double-buffered so that the epilogue of tile i overlaps the loads and MMAs of tile i+1.
+// The rotation has to be float32-accurate (a code flips whenever a rotated value crosses a boundary), so the rows are
+// used UN-normalised as exact MMA operands and R is split into terms that are exact operands too:
+//   fp16 rows: R = R_hi + 2^-11 R_lo (fp16 each): one MMA of N = 2 d per k-step against [R_hi ; 2^11 R_lo] fills a
+//              high and a low accumulator (two chains of d / 16 dependent MMAs would take as long as one: a dependent
+//              step costs about 70 ns whatever its width); the epilogue adds them.  With the sketch on there is room
+//              for one accumulator per tile only: the low products are accumulated first and the first high MMA takes
+//              the accumulator scaled by 2^-11 (the instruction's scale-input-d).
+//   bf16 rows: R = R_1 + R_2 + R_3 (bf16 each, 24 bits together; bf16 has float32's exponent range, so no scaling) into
+//              one accumulator.
+// Every product is exact in the fp32 accumulator; the normalisation by the row norm is applied afterwards.
 //
-// Warp roles in a persistent CTA (one per SM, 800 threads):
-//   warps 0-15  epilogue: thread <-> one row (TMEM lane) and one quarter of the coordinates; tcgen05.ld, boundary
-//               search (up to 3 bits: binary search over boundaries held in registers; 4 bits: a 513-bin lookup
-//               table, bin -> nearest boundary + count below it; both exact, see build_bins), packing, 128-bit stores
-//   warp  16    allocates TMEM, issues the MMAs (one elected thread) and commits them to mbarriers
-//   warps 17-24 producers: 128-bit global loads of the rows, sum of squares for the norm, stores into the
-//               128-byte-swizzled K-major shared-memory layout the MMA descriptors expect
-// Two ways to fill the operand stages.  TMA (the default when the driver offers tensor maps): one thread issues two
-// cp.async.bulk.tensor copies per tile with the 128-byte swizzle the MMA descriptors expect - three stages of rows
-// in flight per SM at no register cost - and warps 17-24 only read the tile back from shared memory for the norms.
-// Otherwise warps 17-24 load the rows themselves (one tile's worth of registers in flight).
+// Warp roles in a persistent CTA (one per SM; 704 threads, 448 with the sketch on).  Epilogue warps come first (E of them),
+// then one MMA warp, four norm warps, one TMA warp:
+//   warps 0..E-1 epilogue; thread <-> one row (TMEM lane) and a share of its sixteen-coordinate chunks (tcgen05.ld).
+//                fp16 rows: all sixteen warps work on the same tile in step, a quarter of the row each, reading the
+//                high and the low accumulator and combining them; two accumulator stages, so the MMAs of the next tile
+//                run meanwhile.  bf16 rows: two groups of eight warps take alternate tiles (two stages each), half a row
+//                per thread.  With the QJL sketch on, a thread owns a whole row (E = 8: two groups of four warps, two
+//                stages each): it forms the quantization residual of every coordinate and accumulates its 32
+//                projections (the projection matrix is read from shared memory as warp-wide broadcasts).
+//                Up to 3 bits a binary search over boundaries (times the row's norm) held in registers adds its
+//                outcome bits straight into the packed word; at 4 bits one lookup in a 513-bin table (bin -> nearest
+//                boundary + count below; see build_bins).  Fractional widths: the threads of a row take chunks of
+//                either width, so they finish together.
+//   warp  E      allocates TMEM, issues the MMAs (one elected thread) and commits them to mbarriers
+//   next four    norms: read each tile back from shared memory for the rows' sums of squares
+//   last warp    one thread keeps the operand stages full with tiled TMA copies (cp.async.bulk.tensor, 3-D tensor map
+//                (column, row, lane), 128-byte swizzle as the MMA descriptors expect; rows past a lane's end and
+//                columns past d read as zeros)
 // Every mbarrier wait is bounded: on a timeout the kernel raises a status word, drains and frees its TMEM.
 #include <algorithm>
 #include <cstdlib>
@@ -31,56 +43,44 @@ namespace tq {
 
 namespace tc {
 
-constexpr int D = 128, TM = 128;                 // head_dim, rows per tile
-constexpr int A_STAGES = 3, ACC_STAGES = 2;
-constexpr int N_EPI = 512, N_PROD = 256;         // threads per role
-constexpr int EPI_WARPS = N_EPI / 32;            // 16: TMEM lane quadrant = warp % 4, coordinate quarter = warp / 4
-constexpr int NT = N_EPI + 32 + N_PROD;          // 800
-constexpr int N_NORM = 128;                       // TMA variant: threads that read the rows back for the norms (one row each)
-constexpr int NT_TMA = N_EPI + 32 + N_NORM + 32; // 704: the last warp's first lane feeds the operand stages by TMA
+constexpr int DMAX = 128, TM = 128;              // largest head_dim, rows per tile
+constexpr int A_STAGES_MAX = 3, ACC_STAGES = 4;
+constexpr int N_NORM = 128;                      // threads that read the rows back for the norms
+// epilogue warps: 16, or 8 with the QJL sketch on (its 32 running projections per thread need the registers); then the
+// MMA warp, the norm warps, the TMA warp
+__host__ __device__ constexpr int epi_warps(bool qjl) { return qjl ? 8 : 16; }
+__host__ __device__ constexpr int n_threads(bool qjl) { return epi_warps(qjl) * 32 + 32 + N_NORM + 32; }     // 704 / 448
 constexpr int BIN_REP = 8;                       // copies of every lookup-table entry (lane & 7 picks one): fewer bank conflicts
 constexpr int KBLK_BYTES = TM * 128;             // one 64-column K-block of a 128-row operand: 16 KB
 constexpr int OPER_BYTES = 2 * KBLK_BYTES;       // 32 KB per operand tile
 constexpr int NBINS = 516;                       // 513 used + guard
+constexpr int QM = 32;                           // projections of the QJL sketch
 constexpr uint32_t WAIT_LIMIT = 4u << 20;        // bounded spin: a few hundred milliseconds at most
 
-// shared memory map (bytes)
-constexpr int OFF_A = 0;                                   // A_STAGES x 32 KB, 1024-byte aligned
-constexpr int OFF_RHI = OFF_A + A_STAGES * OPER_BYTES;     // 32 KB
-constexpr int OFF_RLO = OFF_RHI + OPER_BYTES;              // 32 KB
-constexpr int OFF_BINS = OFF_RLO + OPER_BYTES;             // NBINS x BIN_REP x 8 B: the table of the 4-bit codebook (only bits_hi can be 4)
-constexpr int OFF_BND = OFF_BINS + NBINS * BIN_REP * 8;    // 2 x 16 floats: raw boundaries
-constexpr int OFF_NSQ = OFF_BND + 128;                     // A_STAGES x 2 x 128 floats: partial sums of squares
-constexpr int OFF_BAR = OFF_NSQ + A_STAGES * 2 * TM * 4;   // mbarriers
-constexpr int OFF_MISC = OFF_BAR + 16 * 8;                 // tmem base, abort flag (barriers: 3 + 3 + 2 + 2 + 3 norm-ready)
+// shared memory map (bytes).  fp16 rows: three row stages and two terms of R; bf16 rows: two row stages and three terms.
+constexpr int OFF_A = 0;                                   // stage s at s * 32 KB, 1024-byte aligned
+constexpr int OFF_R3 = OFF_A + 2 * OPER_BYTES;             // bf16: third term of R (fp16: the third row stage)
+constexpr int OFF_R1 = OFF_A + 3 * OPER_BYTES;             // R_hi / R_1
+constexpr int OFF_R2 = OFF_R1 + OPER_BYTES;                // R_lo / R_2
+constexpr int OFF_BINS = OFF_R2 + OPER_BYTES;              // NBINS x BIN_REP x 8 B: the table of the 4-bit codebook (only bits_hi can be 4)
+constexpr int OFF_PT = OFF_BINS + NBINS * BIN_REP * 8;     // QJL: (S R^T)^T, [d][32] floats
+constexpr int OFF_BND = OFF_PT + DMAX * QM * 4;            // 2 x 16 floats raw boundaries, 2 x 16 floats centroids
+constexpr int OFF_NSQ = OFF_BND + 256;                     // A_STAGES_MAX x 2 x 128 floats: partial sums of squares
+constexpr int OFF_BAR = OFF_NSQ + A_STAGES_MAX * 2 * TM * 4;   // mbarriers: 3 full, 3 a_free, 3 norm-ready, 4 acc_full, 4 acc_free
+constexpr int OFF_MISC = OFF_BAR + 24 * 8;                 // tmem base, abort flag
 constexpr int SMEM_BYTES = OFF_MISC + 64;
+static_assert(SMEM_BYTES <= 227 * 1024, "shared-memory plan");
 
 struct Params {
-    const __half* x; int64_t n_lanes, n_rows, x_lane_stride, x_row_stride;
+    int d, bf16, a_stages;
+    int64_t n_rows, n_tiles, tiles_per_lane;     // tiles never cross cache lanes; tile = lane * tiles_per_lane + tile in lane
     const float* rot;
     const float* bnd_hi; const float* bnd_lo; int bits_hi, bits_lo;
     uint8_t* p_hi; uint8_t* p_lo; float* norms; int64_t out_lane_stride;
-    int64_t n_tiles;
-    int64_t tiles_per_lane;      // TMA variant: tiles never cross cache lanes; tile = lane * tiles_per_lane + tile in lane
-    int* status;
+    const float* qjl_proj_rot; const float* cent_hi; const float* cent_lo; uint32_t* qjl_bits; float* qjl_gamma;
 };
 
 __device__ int g_status = 0;   // 0 ok, otherwise the code of the first wait that timed out
-
-#ifdef TQ_TIMING
-// Development builds only: globaltimer stamps of CTA 0, [role][iteration][slot].
-__device__ unsigned long long g_tc_timing[3 * 64 * 4 + 8];
-__device__ __forceinline__ void tstamp(int idx) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_tc_timing[idx] = t;
-}
-#define TC_STAMP(cond, role, it, slot) do { if ((cond) && blockIdx.x == 0 && (it) < 64) tstamp(((role) * 64 + (it)) * 4 + (slot)); } while (0)
-#define TC_STAMP0(cond, slot) do { if ((cond) && blockIdx.x == 0) tstamp(3 * 64 * 4 + (slot)); } while (0)
-#else
-#define TC_STAMP(cond, role, it, slot)
-#define TC_STAMP0(cond, slot)
-#endif
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -109,7 +109,7 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes) : "memory");
 }
-// Tiled TMA load of a (64 columns x 128 rows x 1 lane) box; the innermost coordinate is 0 or 64 halves (0 or 128 bytes).
+// Tiled TMA load of a (64 columns x 128 rows x 1 lane) box; the innermost coordinate is 0 or 64 elements (0 or 128 bytes).
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
@@ -123,6 +123,7 @@ __device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinq
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
+// D = A.B (+ D when accumulate != 0)
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     const uint32_t zero = 0;
     asm volatile(
@@ -130,8 +131,23 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint6
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(zero), "r"(zero), "r"(zero), "r"(zero) : "memory");
 }
+// D = A.B + 2^-11 D
+__device__ __forceinline__ void umma_f16_scaled11(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
+    const uint32_t zero = 0, one = 1;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p, 11;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(one), "r"(zero), "r"(zero), "r"(zero), "r"(zero) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -141,13 +157,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                    "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
                    "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                  : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -164,8 +173,10 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t tile_addr, int kblk, int 
     d |= uint64_t(2) << 61;                       // SWIZZLE_128B
     return d;
 }
-// kind::f16: fp16 A and B, fp32 accumulate, both K-major, N = 128, M = 128
-constexpr uint32_t IDESC = (1u << 4) | (uint32_t(D >> 3) << 17) | (uint32_t(TM >> 4) << 24);
+// kind::f16 instruction descriptor: fp32 accumulate, A and B both fp16 or both bf16, both K-major, M = 128, N = d
+__device__ __forceinline__ uint32_t make_idesc(int d, bool bf16) {
+    return (1u << 4) | (bf16 ? ((1u << 7) | (1u << 10)) : 0u) | (uint32_t(d >> 3) << 17) | (uint32_t(TM >> 4) << 24);
+}
 
 // Lookup table for the boundary search.  Bin k covers normalised values around (k - 256) / 256 (width 1/256);
 // entry = (boundary to test, number of boundaries below the bin's neighbourhood) where the neighbourhood is the
@@ -173,12 +184,6 @@ constexpr uint32_t IDESC = (1u << 4) | (uint32_t(D >> 3) << 17) | (uint32_t(TM >
 // exact count.  A neighbourhood holding two boundaries is marked (a flag bit in the count) and handled by the plain
 // counting loop.
 constexpr int MARKED = 0x100;
-#ifndef TQ_DIRECT_MAX_BITS
-#define TQ_DIRECT_MAX_BITS 3
-#endif
-constexpr int DIRECT_MAX_BITS = TQ_DIRECT_MAX_BITS;   // up to this width the boundaries are searched in registers, above it through the
-                                                      // bin table (at 4 bits the register search costs more issue slots than the table's bank conflicts)
-static_assert(DIRECT_MAX_BITS <= 3, "the register search is written for at most seven boundaries");
 __device__ void build_bins(float2* bins, const float* bnd, int n_bnd, int tid, int nthreads) {
     for (int k = tid; k < NBINS; k += nthreads) {
         const float lo = (float(k) - 256.f - 1.5f) / 256.f, hi = (float(k) - 256.f + 1.5f) / 256.f;
@@ -195,12 +200,12 @@ __device__ void build_bins(float2* bins, const float* bnd, int n_bnd, int tid, i
     }
 }
 
-// Up to three bits the code is never formed: the boundaries live in registers, a binary search (one compare per bit)
-// decides how many of them the value exceeds - the number the counting loop gives for a non-decreasing boundary
-// list, NaN included (0) - and each level's outcome adds its bit, already shifted into place, to the group word
-// (eight codes per group, so a code never straddles two words while it is being built).
+// Up to three bits the code is never formed: the boundaries (times the row's norm) live in registers, a binary search
+// (one compare per bit) decides how many of them the value exceeds - the number the counting loop gives for a
+// non-decreasing boundary list, NaN included (0) - and each level's outcome adds its bit, already shifted into place,
+// to the group word (eight codes per group, so a code never straddles two words while it is being built).
 template <int BITS>
-__device__ __forceinline__ void add_code(uint32_t& grp, float y, const float (&b)[15], int sh) {
+__device__ __forceinline__ void add_code(uint32_t& grp, float y, const float (&b)[7], int sh) {
     if (BITS == 1) {
         if (y > b[0]) grp += 1u << sh;
     } else if (BITS == 2) {
@@ -225,323 +230,347 @@ __device__ __noinline__ uint32_t code_slow(float y, const float* raw_bnd, int n_
     return c;
 }
 
-struct EpiCtx {
-    const Params& p; unsigned char* smem; uint32_t tmem_base, bar_accfull, bar_accfree, bar_afree, bar_nrm;
-    volatile int* abort_flag; int64_t total_rows; int warp, lane;
+// What a thread needs to know about its row while it walks the coordinates.
+struct RowCtx {
+    float rinv, rbin;              // 1 / max(|x|, 1e-10) and 256 times that
+    const float2* bins;            // this lane's copy of the 4-bit table
 };
 
-// One chunk of 16 coordinates (TMEM columns col .. col + 15 of the hi and lo accumulators) at BITS bits: the codes go into
-// g0 / g1 (eight codes each; plain 4-bit words on the table path).
+// Sixteen coordinates (TMEM columns taddr .. + 15) at BITS bits: the codes go into g0 / g1 (eight codes each, BITS bits
+// per code).  sb: boundaries times the row's norm (register search); raw: unscaled boundaries (table path's fallback).
 template <int BITS>
-__device__ __forceinline__ void epilogue_chunk(uint32_t taddr, float rinv, float rbin, const float (&bnd)[15], const float2* bins,
-                                               const float* raw_bnd, uint32_t& g0, uint32_t& g1) {
-    constexpr int n_bnd = (1 << BITS) - 1;
-    uint32_t vh[16], vl[16];
-    tmem_ld16(taddr, vh);
-    tmem_ld16(taddr + 128, vl);
-    tmem_ld_wait();
-    if (BITS <= DIRECT_MAX_BITS) {
+__device__ __forceinline__ void quantize16(const uint32_t* v, const RowCtx& rc, const float (&sb)[7], const float* raw, uint32_t& g0, uint32_t& g1) {
+    g0 = g1 = 0;
+    if (BITS <= 3) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const float yp = fmaf(__uint_as_float(vl[i]), 1.f / 2048.f, __uint_as_float(vh[i]));
-            add_code<BITS>(i < 8 ? g0 : g1, yp, bnd, BITS * (i & 7));                 // bnd: boundaries times the row's norm
-        }
+        for (int i = 0; i < 16; ++i) add_code<BITS>(i < 8 ? g0 : g1, __uint_as_float(v[i]), sb, BITS * (i & 7));
     } else {
         // table path: count-below times 16^k goes in with one multiply-add, the compare adds its bit in place
         uint32_t seen = 0;
-        const uint32_t w0 = g0, w1 = g1;                                        // restored if the group has to be redone
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-            const float yp = fmaf(__uint_as_float(vl[i]), 1.f / 2048.f, __uint_as_float(vh[i]));
-            vh[i] = __float_as_uint(yp);
+            const float yp = __uint_as_float(v[i]);
             // bin index from the mantissa of (y * 256 + 256 + 2^23): exact rounding to nearest, no convert instruction.
             // |y| <= 1 keeps the index below 513; NaN and infinity give index 0 (ten low mantissa bits are zero).
-            const float tt = fmaf(yp, rbin, 8388608.f + 256.f);
-            const float2 en = bins[(__float_as_uint(tt) & 0x3FFu) * BIN_REP];
+            const float tt = fmaf(yp, rc.rbin, 8388608.f + 256.f);
+            const float2 en = rc.bins[min(__float_as_uint(tt) & 0x3FFu, uint32_t(NBINS - 1)) * BIN_REP];     // (the clamp only matters for |y| > |x|, i.e. never)
             seen |= __float_as_uint(en.y);
             uint32_t& w = i < 8 ? g0 : g1;
             w += __float_as_uint(en.y) * (1u << (4 * (i & 7)));
-            if ((yp * rinv) > en.x) w += 1u << (4 * (i & 7));                  // strict >, codebook.py:220-223
+            if ((yp * rc.rinv) > en.x) w += 1u << (4 * (i & 7));                  // strict >, codebook.py:220-223
         }
         if (__any_sync(0xffffffffu, (seen & MARKED) != 0)) {     // a marked bin was hit: redo the group with the counting loop
-            g0 = w0; g1 = w1;
+            g0 = g1 = 0;
 #pragma unroll
             for (int i = 0; i < 16; ++i)
-                (i < 8 ? g0 : g1) |= code_slow(__uint_as_float(vh[i]) * rinv, raw_bnd, n_bnd) << (4 * (i & 7));
+                (i < 8 ? g0 : g1) |= code_slow(__uint_as_float(v[i]) * rc.rinv, raw, 15) << (4 * (i & 7));
         }
     }
 }
 
-// 2 * BITS bytes: the sixteen codes of one chunk as the little-endian bit stream, stored at dst (2-byte aligned at least)
-template <int BITS>
-__device__ __forceinline__ void store_chunk(uint8_t* dst, uint32_t g0, uint32_t g1) {
-    if (BITS == 4) {
-        if ((reinterpret_cast<uintptr_t>(dst) & 7) == 0) *reinterpret_cast<uint2*>(dst) = make_uint2(g0, g1);
-        else { reinterpret_cast<uint16_t*>(dst)[0] = uint16_t(g0); reinterpret_cast<uint16_t*>(dst)[1] = uint16_t(g0 >> 16);
-               reinterpret_cast<uint16_t*>(dst)[2] = uint16_t(g1); reinterpret_cast<uint16_t*>(dst)[3] = uint16_t(g1 >> 16); }
-    } else if (BITS == 3) {
-        const uint32_t w0 = g0 | (g1 << 24), w1 = g1 >> 8;
-        reinterpret_cast<uint16_t*>(dst)[0] = uint16_t(w0); reinterpret_cast<uint16_t*>(dst)[1] = uint16_t(w0 >> 16);
-        reinterpret_cast<uint16_t*>(dst)[2] = uint16_t(w1);
-    } else if (BITS == 2) {
-        const uint32_t w0 = g0 | (g1 << 16);
-        if ((reinterpret_cast<uintptr_t>(dst) & 3) == 0) *reinterpret_cast<uint32_t*>(dst) = w0;
-        else { reinterpret_cast<uint16_t*>(dst)[0] = uint16_t(w0); reinterpret_cast<uint16_t*>(dst)[1] = uint16_t(w0 >> 16); }
-    } else {
-        *reinterpret_cast<uint16_t*>(dst) = uint16_t(g0 | (g1 << 8));
+// Appends a group of eight codes (8 * BITS bits) to a row's bit stream held in words[]: group k sits at bit 8 * BITS * k.
+template <int BITS, int NW>
+__device__ __forceinline__ void put_group(uint32_t (&words)[NW], int k, uint32_t g) {
+    constexpr int GB = 8 * BITS;
+    const int bit = GB * k, w = bit >> 5, sh = bit & 31;                          // all compile-time after unrolling
+    words[w] |= g << sh;
+    if (sh + GB > 32 && w + 1 < NW) words[w + 1] |= g >> (32 - sh);
+}
+
+// nbytes of words[] to dst with the widest stores the address and the size allow (both known per row only)
+template <int NW>
+__device__ __forceinline__ void store_words(uint8_t* dst, const uint32_t (&words)[NW], int nbytes) {
+    const uint32_t al = uint32_t(reinterpret_cast<uintptr_t>(dst)) | uint32_t(nbytes);
+    if ((al & 15u) == 0) {
+#pragma unroll
+        for (int i = 0; i < NW / 4; ++i)
+            if (16 * i < nbytes) reinterpret_cast<uint4*>(dst)[i] = make_uint4(words[4 * i], words[4 * i + 1], words[4 * i + 2], words[4 * i + 3]);
+    } else if ((al & 7u) == 0) {
+#pragma unroll
+        for (int i = 0; i < NW / 2; ++i)
+            if (8 * i < nbytes) reinterpret_cast<uint2*>(dst)[i] = make_uint2(words[2 * i], words[2 * i + 1]);
+    } else if ((al & 3u) == 0) {
+#pragma unroll
+        for (int i = 0; i < NW; ++i)
+            if (4 * i < nbytes) reinterpret_cast<uint32_t*>(dst)[i] = words[i];
+    } else {                                                                      // rows of 6 or 18 bytes: 2-byte aligned
+#pragma unroll
+        for (int i = 0; i < 2 * NW; ++i)
+            if (2 * i < nbytes) reinterpret_cast<uint16_t*>(dst)[i] = uint16_t(words[i >> 1] >> (16 * (i & 1)));
     }
 }
 
-// Fractional widths, balanced: every warp takes sixteen coordinates of the high-bit half and sixteen of the low-bit half
-// (coordinate quarter q: [16 q, 16 q + 16) and [64 + 16 q, 64 + 16 q + 16)), so no warp is left with only the
-// costlier width while the others wait at the accumulator barrier.
-template <int BH, int BL, bool TMA>
-__device__ __forceinline__ void epilogue_loop_frac(const EpiCtx& e) {
+struct EpiCtx {
+    const Params& p; unsigned char* smem; uint32_t tmem_base, bar_accfull, bar_accfree, bar_afree, bar_nrm;
+    volatile int* abort_flag; int warp, lane;
+};
+
+// QJL: residual of sixteen coordinates (normalised rotated value minus its centroid) into the 32 projections and the
+// residual's sum of squares.  PT: [d][32] floats, read as warp-wide broadcasts.
+template <int BITS>
+__device__ __forceinline__ void sketch16(const uint32_t* v, uint32_t g0, uint32_t g1, float rinv, const float* cent, const float* PT, int col0,
+                                         float (&proj)[QM], float& ee) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const uint32_t code = ((i < 8 ? g0 : g1) >> (BITS * (i & 7))) & ((1u << BITS) - 1u);
+        const float e = fmaf(__uint_as_float(v[i]), rinv, -cent[code]);
+        ee = fmaf(e, e, ee);
+        const float4* row = reinterpret_cast<const float4*>(PT + (col0 + i) * QM);
+#pragma unroll
+        for (int q = 0; q < QM / 4; ++q) {
+            const float4 s = row[q];
+            proj[4 * q] = fmaf(e, s.x, proj[4 * q]); proj[4 * q + 1] = fmaf(e, s.y, proj[4 * q + 1]);
+            proj[4 * q + 2] = fmaf(e, s.z, proj[4 * q + 2]); proj[4 * q + 3] = fmaf(e, s.w, proj[4 * q + 3]);
+        }
+    }
+}
+
+// A run of a row's coordinates ([col0, col0 + 16 * nch) at BITS bits) in rolled steps of 32 coordinates; the step's codes
+// (32 * BITS bits) are assembled in registers and stored at once.  Keeping the loop rolled keeps its body within the
+// instruction cache.  SPLITACC: the high and low products sit in two accumulators lo_off columns apart and are combined
+// here (y = hi + 2^-11 lo), sixteen coordinates per pair of loads; otherwise one 32-column load per step.
+// NCH: the number of chunks when it is known at compile time (1 or 2: a single step whose shape folds), 0 = nch_rt.
+template <int BITS, bool QJL, bool SPLITACC, int NCH>
+__device__ __forceinline__ void quantize_part(uint32_t t_row, int col0, int nch_rt, int lo_off, const RowCtx& rc, const float (&sb)[7], const float* raw,
+                                              const float* cent, const float* PT, uint8_t* dst, bool live, float (&proj)[QM], float& ee) {
+    constexpr int NW = 2 * 16 * BITS / 32;                                          // words of a step: BITS
+    const int nch = NCH ? NCH : nch_rt;
+#pragma unroll 1
+    for (int c0 = 0; c0 < nch; c0 += 2) {
+        uint32_t v[32], w[NW];
+#pragma unroll
+        for (int i = 0; i < NW; ++i) w[i] = 0;
+        const int nc = min(2, nch - c0);                                            // a run may end on a half step
+        if (!SPLITACC && !QJL) {
+            tmem_ld32(t_row + col0 + c0 * 16, v);
+            tmem_ld_wait();
+        }
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            if (c < nc) {
+                uint32_t g0, g1;
+                uint32_t* vc = v + ((SPLITACC || QJL) ? 0 : 16 * c);
+                if (QJL && !SPLITACC) {                                         // (the sketch keeps 32 accumulators: sixteen columns at a time)
+                    tmem_ld16(t_row + col0 + (c0 + c) * 16, *reinterpret_cast<uint32_t (*)[16]>(v));
+                    tmem_ld_wait();
+                }
+                if (SPLITACC) {
+                    uint32_t (&hi)[16] = *reinterpret_cast<uint32_t (*)[16]>(v);
+                    uint32_t (&lo)[16] = *reinterpret_cast<uint32_t (*)[16]>(v + 16);
+                    tmem_ld16(t_row + col0 + (c0 + c) * 16, hi);
+                    tmem_ld16(t_row + lo_off + col0 + (c0 + c) * 16, lo);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(fmaf(__uint_as_float(v[16 + i]), 1.f / 2048.f, __uint_as_float(v[i])));
+                }
+                quantize16<BITS>(vc, rc, sb, raw, g0, g1);
+                put_group<BITS, NW>(w, 2 * c, g0);
+                put_group<BITS, NW>(w, 2 * c + 1, g1);
+                if constexpr (QJL) sketch16<BITS>(vc, g0, g1, rc.rinv, cent, PT, col0 + (c0 + c) * 16, proj, ee);
+            }
+        }
+        if (live) store_words<NW>(dst + c0 * 2 * BITS, w, nc * 2 * BITS);
+    }
+}
+
+// BH bits for coordinates [0, half), BL for [half, d) (BL == 0: BH for all of them, half = d).  Three shapes:
+//   fp16 rows (SPLITACC): two accumulators per tile (high and low products: two independent chains of MMAs instead of
+//     one twice as long) leave room for two stages, so all sixteen warps work on the same tile in step - thread <-> one
+//     row and a quarter of its sixteen-coordinate chunks (of either width) - while the MMAs of the next tile run.
+//   bf16 rows: one accumulator per tile, four stages; two groups of eight warps take alternate tiles (two stages each),
+//     a thread owns one row and half of its chunks.
+//   QJL sketch: a thread needs the whole row (32 running projections) and the registers for it: eight epilogue warps,
+//     two groups of four that take alternate tiles, one accumulator per tile, two stages per group.
+template <bool QJL, bool SPLITACC> struct EpiShape {
+    static constexpr int EW = epi_warps(QJL), NT = n_threads(QJL), N_EPI = EW * 32;
+    static constexpr int GROUPS = SPLITACC ? 1 : 2;                                 // groups of warps that take tiles in turn
+    static constexpr int WPG = EW / GROUPS;                                         // warps per group: 4 row quadrants x SPLIT shares of the columns
+    static constexpr int SPLIT = WPG / 4;
+    static constexpr int STAGES = SPLITACC ? 2 : 4;                                 // accumulator stages
+    static constexpr int STAGE_COLS = SPLITACC ? 2 * DMAX : DMAX;
+};
+// DC: head_dim when it is known at compile time (the chunk shares, row widths and store shapes then fold), 0 = read it
+// from the parameters.
+template <int BH, int BL, bool QJL, bool SPLITACC, int DC>
+__device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
+    using Sh = EpiShape<QJL, SPLITACC>;
     const Params& p = e.p;
-    const int quad = e.warp & 3, quarter = e.warp >> 2, row_in_tile = quad * 32 + e.lane;
-    const float2* bins = reinterpret_cast<const float2*>(e.smem + OFF_BINS) + (e.lane & (BIN_REP - 1));      // 4-bit side only
+    const int group = e.warp / Sh::WPG, quad = e.warp & 3, part = (e.warp % Sh::WPG) >> 2, row_in_tile = quad * 32 + e.lane;
+    const int d = DC ? DC : p.d, half = BL ? d / 2 : d;
+    const int nch_h = half / 16, nch_l = BL ? (d - half) / 16 : 0;                   // chunks of sixteen coordinates per bit width
+    // this thread's chunks: [h0, h1) of the first width, [l0, l1) of the second
+    // (share q of n chunks: [ceil(q n / SPLIT), ceil((q + 1) n / SPLIT)); the second width is dealt from the other end so
+    // that the shares of a fractional row add up evenly)
+    const int h0 = (part * nch_h + Sh::SPLIT - 1) / Sh::SPLIT, h1 = ((part + 1) * nch_h + Sh::SPLIT - 1) / Sh::SPLIT;
+    const int l0 = part * nch_l / Sh::SPLIT, l1 = (part + 1) * nch_l / Sh::SPLIT;
     const float* raw_h = reinterpret_cast<const float*>(e.smem + OFF_BND);
     const float* raw_l = raw_h + 16;
-    float bnd_h[15], bnd_l[15];
+    const float* cent_h = raw_h + 32;
+    const float* cent_l = raw_h + 48;
+    const float* PT = reinterpret_cast<const float*>(e.smem + OFF_PT);
+    RowCtx rc;
+    rc.bins = reinterpret_cast<const float2*>(e.smem + OFF_BINS) + (e.lane & (BIN_REP - 1));      // 4-bit side only
+    float bnd_h[7], bnd_l[7];
 #pragma unroll
-    for (int i = 0; i < 15; ++i) { bnd_h[i] = raw_h[i < (1 << BH) - 1 ? i : 0]; bnd_l[i] = raw_l[i < (1 << BL) - 1 ? i : 0]; }
-    const int64_t stride_rows = int64_t(gridDim.x) * TM;
-    const int64_t step_o = TMA ? int64_t(gridDim.x) / p.tiles_per_lane : stride_rows / p.n_rows;
-    const int64_t step_r = TMA ? (int64_t(gridDim.x) - step_o * p.tiles_per_lane) * TM : stride_rows - step_o * p.n_rows;
-    const int64_t wrap_r = TMA ? p.tiles_per_lane * TM : p.n_rows;
-    int64_t lane_o = 0, lane_r = 0;
-    int it = 0;
-    for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
-        const int a = it % ACC_STAGES, s = it % A_STAGES;
-        if (!mbar_wait(e.bar_accfull + 8 * a, (it / ACC_STAGES) & 1, e.abort_flag, 3)) break;
-        if (TMA && !mbar_wait(e.bar_nrm + 8 * s, (it / A_STAGES) & 1, e.abort_flag, 5)) break;     // sums of squares written
+    for (int i = 0; i < 7; ++i) { bnd_h[i] = raw_h[(BH <= 3 && i < (1 << BH) - 1) ? i : 0]; bnd_l[i] = raw_l[(BL >= 1 && BL <= 3 && i < (1 << BL) - 1) ? i : 0]; }
+    const uint32_t tpl = uint32_t(p.tiles_per_lane);
+    const int a_stages = p.a_stages;
+    const int nb_h = half * BH / 8, nb_l = BL ? (d - half) * BL / 8 : 0;            // bytes of a packed row (per width)
+    int s = group % a_stages;                                                       // operand stage of iteration `it`
+    // (cache lane, tile inside the lane) of the group's current tile, advanced by the group's tile stride: one division here
+    const uint32_t first_tile = blockIdx.x + uint32_t(group) * gridDim.x, stride_tiles = uint32_t(Sh::GROUPS) * gridDim.x;
+    uint32_t lane_o = first_tile / tpl, tl = first_tile - lane_o * tpl;
+    const uint32_t step_o = stride_tiles / tpl, step_t = stride_tiles - step_o * tpl;
+    for (int64_t tile = first_tile, it = group; tile < p.n_tiles; tile += stride_tiles, it += Sh::GROUPS) {
+        const int a = int(it % Sh::STAGES);
+        if (!mbar_wait(e.bar_accfull + 8 * a, uint32_t(it / Sh::STAGES) & 1u, e.abort_flag, 3)) break;
+        if (!mbar_wait(e.bar_nrm + 8 * s, uint32_t(it / a_stages) & 1u, e.abort_flag, 5)) break;     // sums of squares written
         tc_fence_after();
         const float* nsq = reinterpret_cast<const float*>(e.smem + OFF_NSQ) + s * 2 * TM;
         const float nrm = sqrtf(nsq[row_in_tile] + nsq[TM + row_in_tile]);
         mbar_arrive(e.bar_afree + 8 * s);                       // norm slots of this stage are free again
+        s = (s + Sh::GROUPS) % a_stages;
         const float nden = fmaxf(nrm, 1e-10f);                  // cache.py:237-238 guards the zero vector the same way
-        const float rinv = 1.f / nden;
-        const float rbin = rinv * 256.f;
+        rc.rinv = 1.f / nden;
+        rc.rbin = rc.rinv * 256.f;
         // register search: y / |x| > b is tested as y > b * |x| (one multiply per boundary and row instead of one per coordinate)
-        float sb_h[15], sb_l[15];
+        float sb_h[7], sb_l[7];
 #pragma unroll
-        for (int i = 0; i < 15; ++i) { sb_h[i] = bnd_h[i] * nden; sb_l[i] = bnd_l[i] * nden; }
-        if (it == 0) {      // one division at the start, then advanced by the grid stride
-            if (TMA) { lane_o = tile / p.tiles_per_lane; lane_r = (tile - lane_o * p.tiles_per_lane) * TM + row_in_tile; }
-            else { const int64_t row = tile * TM + row_in_tile; lane_o = row / p.n_rows; lane_r = row - lane_o * p.n_rows; }
+        for (int i = 0; i < 7; ++i) { sb_h[i] = bnd_h[i] * nden; sb_l[i] = bnd_l[i] * nden; }
+        const int64_t lane_r = int64_t(tl) * TM + row_in_tile;
+        const bool live = lane_r < p.n_rows;                    // rows past the lane's end were zero-filled by the copy
+        const int64_t orow = int64_t(lane_o) * p.out_lane_stride + lane_r;
+        lane_o += step_o; tl += step_t;
+        if (tl >= tpl) { tl -= tpl; ++lane_o; }
+        const uint32_t t_row = e.tmem_base + (uint32_t(quad * 32) << 16) + a * Sh::STAGE_COLS;
+        float proj[QM], ee = 0.f;
+        if (QJL) {
+#pragma unroll
+            for (int q = 0; q < QM; ++q) proj[q] = 0.f;
         }
-        const bool live = TMA ? lane_r < p.n_rows : tile * TM + row_in_tile < e.total_rows;
-        int64_t orow = 0;
-        if (live) {
-            orow = lane_o * p.out_lane_stride + lane_r;
-            if (quarter == 0) p.norms[orow] = nrm;
-        }
-        lane_r += step_r; lane_o += step_o;
-        if (lane_r >= wrap_r + (TMA ? row_in_tile : 0)) { lane_r -= wrap_r; ++lane_o; }
-        const uint32_t t_row = e.tmem_base + (uint32_t(quad * 32) << 16) + a * 256;
-        uint32_t h0 = 0, h1 = 0, l0 = 0, l1 = 0;
-        epilogue_chunk<BH>(t_row + quarter * 16, rinv, rbin, sb_h, bins, raw_h, h0, h1);
-        epilogue_chunk<BL>(t_row + 64 + quarter * 16, rinv, rbin, sb_l, bins, raw_l, l0, l1);
+        // with head_dim 128 and quarter shares every thread has two chunks of an integer width, or one of each fractional width
+        constexpr int NCH_H = (DC == 128 && Sh::SPLIT == 4) ? (BL ? 1 : 2) : 0, NCH_L = (DC == 128 && Sh::SPLIT == 4) ? 1 : 0;
+        quantize_part<BH, QJL, SPLITACC, NCH_H>(t_row, h0 * 16, h1 - h0, d, rc, sb_h, raw_h, cent_h, PT, p.p_hi + orow * nb_h + h0 * 2 * BH, live, proj, ee);
+        if (BL) quantize_part<(BL ? BL : 1), QJL, SPLITACC, NCH_L>(t_row, half + l0 * 16, l1 - l0, d, rc, sb_l, raw_l, cent_l, PT, p.p_lo + orow * nb_l + l0 * 2 * BL, live, proj, ee);
         tc_fence_before();
-        mbar_arrive(e.bar_accfree + 8 * a);                     // accumulators may be overwritten
-        if (live) {
-            store_chunk<BH>(p.p_hi + orow * (8 * BH) + quarter * (2 * BH), h0, h1);      // a row of the half: 64 codes = 8 * bits bytes
-            store_chunk<BL>(p.p_lo + orow * (8 * BL) + quarter * (2 * BL), l0, l1);
-        }
-    }
-}
-
-template <int BITS, bool TMA>
-__device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
-    const Params& p = e.p;
-    const int quad = e.warp & 3, quarter = e.warp >> 2, row_in_tile = quad * 32 + e.lane;
-    const bool second = p.bits_lo && quarter >= 2;              // fractional mode: coordinates [64, 128) use the low-bit codebook
-    const float2* bins = reinterpret_cast<const float2*>(e.smem + OFF_BINS) + (e.lane & (BIN_REP - 1));      // 4-bit side only
-    const float* raw_bnd = reinterpret_cast<const float*>(e.smem + OFF_BND) + (second ? 16 : 0);
-    constexpr int n_bnd = (1 << BITS) - 1;
-    constexpr int WBYTES = 32 * BITS / 8;                       // bytes this thread produces per row (32 coordinates)
-    float bnd[15];
+        mbar_arrive(e.bar_accfree + 8 * a);                     // the accumulator may be overwritten
+        if (live && part == 0) {
+            p.norms[orow] = nrm;
+            if (QJL) {
+                uint32_t zb = 0;
 #pragma unroll
-    for (int i = 0; i < 15; ++i) bnd[i] = raw_bnd[i < n_bnd ? i : 0];
-    // the tile stride in (lane, row) form.  TMA variant: a tile is (lane, tile in lane), rows past the lane's end are
-    // zero-filled by the copy and dropped here; otherwise tiles run over the flattened rows of all lanes.
-    const int64_t stride_rows = int64_t(gridDim.x) * TM;
-    const int64_t step_o = TMA ? int64_t(gridDim.x) / p.tiles_per_lane : stride_rows / p.n_rows;
-    const int64_t step_r = TMA ? (int64_t(gridDim.x) - step_o * p.tiles_per_lane) * TM : stride_rows - step_o * p.n_rows;
-    const int64_t wrap_r = TMA ? p.tiles_per_lane * TM : p.n_rows;
-    int64_t lane_o = 0, lane_r = 0;
-    int it = 0;
-    for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
-        const int a = it % ACC_STAGES, s = it % A_STAGES;
-        TC_STAMP(e.warp == 0 && e.lane == 0, 2, it, 0);
-        if (!mbar_wait(e.bar_accfull + 8 * a, (it / ACC_STAGES) & 1, e.abort_flag, 3)) break;
-        if (TMA && !mbar_wait(e.bar_nrm + 8 * s, (it / A_STAGES) & 1, e.abort_flag, 5)) break;     // sums of squares written
-        tc_fence_after();
-        TC_STAMP(e.warp == 0 && e.lane == 0, 2, it, 1);
-        const float* nsq = reinterpret_cast<const float*>(e.smem + OFF_NSQ) + s * 2 * TM;
-        const float nrm = sqrtf(nsq[row_in_tile] + nsq[TM + row_in_tile]);
-        mbar_arrive(e.bar_afree + 8 * s);                       // norm slots of this stage are free again
-        const float nden = fmaxf(nrm, 1e-10f);                  // cache.py:237-238 guards the zero vector the same way
-        const float rinv = 1.f / nden;
-        const float rbin = rinv * 256.f;
-        // register search: y / |x| > b is tested as y > b * |x| (one multiply per boundary and row instead of one per coordinate)
-        float sb[15];
-#pragma unroll
-        for (int i = 0; i < 15; ++i) sb[i] = bnd[i] * nden;
-        if (it == 0) {      // one division at the start, then advanced by the grid stride
-            if (TMA) { lane_o = tile / p.tiles_per_lane; lane_r = (tile - lane_o * p.tiles_per_lane) * TM + row_in_tile; }
-            else { const int64_t row = tile * TM + row_in_tile; lane_o = row / p.n_rows; lane_r = row - lane_o * p.n_rows; }
-        }
-        const bool live = TMA ? lane_r < p.n_rows : tile * TM + row_in_tile < e.total_rows;
-        int64_t orow = 0;
-        if (live) {
-            orow = lane_o * p.out_lane_stride + lane_r;
-            if (quarter == 0) p.norms[orow] = nrm;
-        }
-        lane_r += step_r; lane_o += step_o;
-        if (lane_r >= wrap_r + (TMA ? row_in_tile : 0)) { lane_r -= wrap_r; ++lane_o; }
-        const uint32_t t_hi = e.tmem_base + (uint32_t(quad * 32) << 16) + a * 256 + quarter * 32;
-        uint32_t words[4], groups[4];                           // 32 codes x at most 4 bits; eight codes per group
-#pragma unroll
-        for (int i = 0; i < 4; ++i) words[i] = groups[i] = 0;
-#pragma unroll
-        for (int cb = 0; cb < 2; ++cb) {                        // 16 coordinates at a time
-            uint32_t vh[16], vl[16];
-            tmem_ld16(t_hi + cb * 16, vh);
-            tmem_ld16(t_hi + 128 + cb * 16, vl);
-            tmem_ld_wait();
-            if (BITS <= DIRECT_MAX_BITS) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float yp = fmaf(__uint_as_float(vl[i]), 1.f / 2048.f, __uint_as_float(vh[i]));
-                    add_code<BITS>(groups[cb * 2 + (i >> 3)], yp, sb, BITS * (i & 7));
-                }
-            } else {
-                // table path: count-below times 16^k goes in with one multiply-add, the compare adds its bit in place
-                uint32_t seen = 0;
-                const uint32_t w0 = words[cb * 2], w1 = words[cb * 2 + 1];      // restored if the group has to be redone
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float yp = fmaf(__uint_as_float(vl[i]), 1.f / 2048.f, __uint_as_float(vh[i]));
-                    vh[i] = __float_as_uint(yp);
-                    // bin index from the mantissa of (y * 256 + 256 + 2^23): exact rounding to nearest, no convert instruction.
-                    // |y| <= 1 keeps the index below 513; NaN and infinity give index 0 (ten low mantissa bits are zero).
-                    const float tt = fmaf(yp, rbin, 8388608.f + 256.f);
-                    const float2 en = bins[(__float_as_uint(tt) & 0x3FFu) * BIN_REP];
-                    seen |= __float_as_uint(en.y);
-                    uint32_t& w = words[cb * 2 + (i >> 3)];
-                    w += __float_as_uint(en.y) * (1u << (4 * (i & 7)));
-                    if ((yp * rinv) > en.x) w += 1u << (4 * (i & 7));          // strict >, codebook.py:220-223
-                }
-                if (__any_sync(0xffffffffu, (seen & MARKED) != 0)) {     // a marked bin was hit: redo the group with the counting loop
-                    words[cb * 2] = w0; words[cb * 2 + 1] = w1;
-#pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        words[cb * 2 + (i >> 3)] |= code_slow(__uint_as_float(vh[i]) * rinv, raw_bnd, n_bnd) << (4 * (i & 7));
-                }
-            }
-        }
-        if (BITS <= DIRECT_MAX_BITS) {
-            // groups[g] holds codes 8g .. 8g+7 in 8 * BITS bits: lay them out as the little-endian bit stream
-            if (BITS == 3) {
-                words[0] = groups[0] | (groups[1] << 24);
-                words[1] = (groups[1] >> 8) | (groups[2] << 16);
-                words[2] = (groups[2] >> 16) | (groups[3] << 8);
-            } else if (BITS == 2) {
-                words[0] = groups[0] | (groups[1] << 16);
-                words[1] = groups[2] | (groups[3] << 16);
-            } else {
-                words[0] = groups[0] | (groups[1] << 8) | (groups[2] << 16) | (groups[3] << 24);
-            }
-        }
-        tc_fence_before();
-        mbar_arrive(e.bar_accfree + 8 * a);                     // accumulators may be overwritten
-        TC_STAMP(e.warp == 0 && e.lane == 0, 2, it, 2);
-        if (live) {
-            const bool frac = p.bits_lo != 0;
-            // integer mode: the row holds 4 quarters; fractional mode: packed_hi and packed_lo hold 2 quarters each
-            uint8_t* dst = second ? p.p_lo + orow * (2 * WBYTES) + (quarter - 2) * WBYTES
-                                  : p.p_hi + orow * ((frac ? 2 : 4) * WBYTES) + quarter * WBYTES;
-            if ((WBYTES & 15) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-                for (int i = 0; i < WBYTES / 16; ++i)
-                    reinterpret_cast<uint4*>(dst)[i] = make_uint4(words[4 * i], words[4 * i + 1], words[4 * i + 2], words[4 * i + 3]);
-            } else if ((WBYTES & 7) == 0 && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
-#pragma unroll
-                for (int i = 0; i < WBYTES / 8; ++i) reinterpret_cast<uint2*>(dst)[i] = make_uint2(words[2 * i], words[2 * i + 1]);
-            } else if ((WBYTES & 3) == 0 && (reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
-#pragma unroll
-                for (int i = 0; i < WBYTES / 4; ++i) reinterpret_cast<uint32_t*>(dst)[i] = words[i];
-            } else {
-#pragma unroll
-                for (int i = 0; i < WBYTES; ++i) dst[i] = uint8_t(words[i >> 2] >> (8 * (i & 3)));
+                for (int q = 0; q < QM; ++q) zb |= (proj[q] >= 0.f ? 1u : 0u) << q;
+                if (nrm == 0.f) zb = 0xffffffffu;               // zero row: the reference's residual is exactly 0, and 0 >= 0
+                p.qjl_bits[orow] = zb;
+                p.qjl_gamma[orow] = nrm * sqrtf(ee);            // |x - dequant(x)| = |x| |y_n - c| (the rotation is orthogonal)
             }
         }
     }
 }
 
-// FRAC: the balanced epilogue for the reference's fractional widths (bits_lo == bits_hi - 1); a kernel of its own so that the
-// integer-width kernel keeps its register allocation
-template <bool TMA, bool FRAC>
-__global__ void __launch_bounds__(TMA ? NT_TMA : NT, 1) quantize_tc_kernel(Params p, const __grid_constant__ CUtensorMap tmap) {
-    constexpr int NTHREADS = TMA ? NT_TMA : NT;
+// SPLITACC (fp16 rows without the sketch): high and low products in two accumulators, one MMA of N = 2 d per k-step
+// against [R_hi ; R_lo].  Otherwise one accumulator: fp16 low products first and the scale-input-d trick, bf16 three terms.
+template <bool QJL, bool SPLITACC, int DC>
+__global__ void __launch_bounds__(n_threads(QJL), 1) quantize_tc_kernel(Params p, const __grid_constant__ CUtensorMap tmap) {
+    using Sh = EpiShape<QJL, SPLITACC>;
+    constexpr int ACCS = Sh::STAGES, NT = Sh::NT, EPI_WARPS = Sh::EW, N_EPI = Sh::N_EPI;
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t sbase = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 4);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
-    // barriers: full[A_STAGES] (producers -> MMA), a_free[A_STAGES] (MMA commit + epilogue's norm read -> producers),
-    //           acc_full[ACC_STAGES] (MMA commit -> epilogue), acc_free[ACC_STAGES] (epilogue -> MMA)
-    const uint32_t bar_full = sbase + OFF_BAR, bar_afree = bar_full + 8 * A_STAGES;
-    const uint32_t bar_accfull = bar_afree + 8 * A_STAGES, bar_accfree = bar_accfull + 8 * ACC_STAGES;
-    const uint32_t bar_nrm = bar_accfree + 8 * ACC_STAGES;       // TMA variant: sums of squares of a stage are written
+    const int d = DC ? DC : p.d, a_stages = p.a_stages;
+    const bool bf16 = p.bf16 != 0;
+    // barriers: full[3] (TMA -> MMA, norms), a_free[3] (MMA commit + norm warps + the epilogue's norm read -> TMA),
+    //           nrm[3] (norm warps -> epilogue), acc_full[4] (MMA commit -> epilogue group), acc_free[4] (epilogue group -> MMA)
+    const uint32_t bar_full = sbase + OFF_BAR, bar_afree = bar_full + 8 * A_STAGES_MAX, bar_nrm = bar_afree + 8 * A_STAGES_MAX;
+    const uint32_t bar_accfull = bar_nrm + 8 * A_STAGES_MAX, bar_accfree = bar_accfull + 8 * ACC_STAGES;      // (ACCS of the 4 slots are used)
 
-    TC_STAMP0(tid == 0, 0);
     if (sbase & 1023u) {                  // the swizzled operand tiles need 1024-byte alignment (uniform across the CTA)
         if (tid == 0) atomicCAS(&g_status, 0, 9);
         return;
     }
     if (tid == 0) {
         *abort_flag = 0;
-        for (int s = 0; s < A_STAGES; ++s) {
-            // TMA: one arrival (the issuing thread, with the byte count) fills a stage; it is free again once the MMAs have
-            // committed, the epilogue has read the norms and the norm warps have read the rows
-            mbar_init(bar_full + 8 * s, TMA ? 1 : N_PROD);
-            mbar_init(bar_afree + 8 * s, TMA ? 1 + N_EPI + N_NORM : 1 + N_EPI);
+        for (int s = 0; s < A_STAGES_MAX; ++s) {
+            // one arrival (the issuing thread, with the byte count) fills a stage; it is free again once the MMAs have
+            // committed, the norm warps have read the rows and the tile's epilogue group has read the norms
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_afree + 8 * s, 1 + N_NORM + N_EPI / Sh::GROUPS);
             mbar_init(bar_nrm + 8 * s, N_NORM);
         }
-        for (int a = 0; a < ACC_STAGES; ++a) { mbar_init(bar_accfull + 8 * a, 1); mbar_init(bar_accfree + 8 * a, N_EPI); }
+        for (int a = 0; a < ACC_STAGES; ++a) { mbar_init(bar_accfull + 8 * a, 1); mbar_init(bar_accfree + 8 * a, N_EPI / Sh::GROUPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    // R -> fp16 hi / lo operand tiles (swizzled K-major): B[n = j][k] = R[j][k]
-    for (int idx = tid; idx < D * (D / 8); idx += NTHREADS) {
-        const int j = idx / (D / 8), c = idx - j * (D / 8);      // row j, 16-byte chunk c (8 halves) of the row
-        const float4 f0 = __ldg(reinterpret_cast<const float4*>(p.rot + j * D + c * 8));
-        const float4 f1 = __ldg(reinterpret_cast<const float4*>(p.rot + j * D + c * 8 + 4));
+    // R -> operand tiles (swizzled K-major): B[n = j][k] = R[j][k], rows j < d, 16-byte chunks c < d / 8
+    for (int idx = tid; idx < d * (d / 8); idx += NT) {
+        const int j = idx / (d / 8), c = idx - j * (d / 8);      // row j, chunk c (8 elements) of the row
+        const float4 f0 = __ldg(reinterpret_cast<const float4*>(p.rot + j * d + c * 8));
+        const float4 f1 = __ldg(reinterpret_cast<const float4*>(p.rot + j * d + c * 8 + 4));
         const float v[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
-        __align__(16) __half hi[8], lo[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            hi[i] = __float2half_rn(v[i]);
-            lo[i] = __float2half_rn((v[i] - __half2float(hi[i])) * 2048.f);
-        }
         const int kblk = c >> 3, cc = c & 7;
         const int off = kblk * KBLK_BYTES + j * 128 + ((cc ^ (j & 7)) << 4);
-        *reinterpret_cast<uint4*>(smem + OFF_RHI + off) = *reinterpret_cast<const uint4*>(hi);
-        *reinterpret_cast<uint4*>(smem + OFF_RLO + off) = *reinterpret_cast<const uint4*>(lo);
+        if (SPLITACC) {
+            // one operand of 2 d rows per K-block: row j = R_hi[j], row d + j = 2^11 R_lo[j] (K-blocks 32 KB apart)
+            __align__(16) __half hi[8], lo[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                hi[i] = __float2half_rn(v[i]);
+                lo[i] = __float2half_rn((v[i] - __half2float(hi[i])) * 2048.f);
+            }
+            const int jl = d + j;
+            *reinterpret_cast<uint4*>(smem + OFF_R1 + kblk * (2 * KBLK_BYTES) + j * 128 + ((cc ^ (j & 7)) << 4)) = *reinterpret_cast<const uint4*>(hi);
+            *reinterpret_cast<uint4*>(smem + OFF_R1 + kblk * (2 * KBLK_BYTES) + jl * 128 + ((cc ^ (jl & 7)) << 4)) = *reinterpret_cast<const uint4*>(lo);
+        } else if (!bf16) {
+            __align__(16) __half hi[8], lo[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                hi[i] = __float2half_rn(v[i]);
+                lo[i] = __float2half_rn((v[i] - __half2float(hi[i])) * 2048.f);
+            }
+            *reinterpret_cast<uint4*>(smem + OFF_R1 + off) = *reinterpret_cast<const uint4*>(hi);
+            *reinterpret_cast<uint4*>(smem + OFF_R2 + off) = *reinterpret_cast<const uint4*>(lo);
+        } else {
+            __align__(16) __nv_bfloat16 t1[8], t2[8], t3[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                t1[i] = __float2bfloat16_rn(v[i]);
+                const float r1 = v[i] - __bfloat162float(t1[i]);               // exact
+                t2[i] = __float2bfloat16_rn(r1);
+                t3[i] = __float2bfloat16_rn(r1 - __bfloat162float(t2[i]));     // exact remainder, 8 bits left at most
+            }
+            *reinterpret_cast<uint4*>(smem + OFF_R1 + off) = *reinterpret_cast<const uint4*>(t1);
+            *reinterpret_cast<uint4*>(smem + OFF_R2 + off) = *reinterpret_cast<const uint4*>(t2);
+            *reinterpret_cast<uint4*>(smem + OFF_R3 + off) = *reinterpret_cast<const uint4*>(t3);
+        }
     }
     {
         float* raw = reinterpret_cast<float*>(smem + OFF_BND);
-        if (tid < 32) {
-            const int side = tid >> 4, i = tid & 15;
-            const float* src = side ? p.bnd_lo : p.bnd_hi;
-            const int nb = (1 << (side ? p.bits_lo : p.bits_hi)) - 1;
-            raw[tid] = (src != nullptr && i < nb) ? src[i] : INFINITY;
+        if (tid < 64) {
+            const int which = tid >> 4, i = tid & 15;                    // 0 / 1: boundaries hi / lo, 2 / 3: centroids hi / lo
+            const int bits = (which & 1) ? p.bits_lo : p.bits_hi;
+            float val = which < 2 ? INFINITY : 0.f;
+            if (which < 2) {
+                const float* src = which ? p.bnd_lo : p.bnd_hi;
+                if (src != nullptr && bits > 0 && i < (1 << bits) - 1) val = src[i];
+            } else if (QJL) {
+                const float* src = (which & 1) ? p.cent_lo : p.cent_hi;
+                if (src != nullptr && bits > 0 && i < (1 << bits)) val = src[i];
+            }
+            raw[tid] = val;
+        }
+        if (QJL) {
+            // (S R^T) is (32, d): transposed so that one coordinate's 32 factors are 128 contiguous bytes
+            float* PT = reinterpret_cast<float*>(smem + OFF_PT);
+            for (int idx = tid; idx < QM * d; idx += NT) {
+                const int q = idx / d, j = idx - q * d;
+                PT[j * QM + q] = __ldg(p.qjl_proj_rot + idx);
+            }
         }
         __syncthreads();
-        if (p.bits_hi > DIRECT_MAX_BITS) build_bins(reinterpret_cast<float2*>(smem + OFF_BINS), raw, (1 << p.bits_hi) - 1, tid, NTHREADS);
+        if (p.bits_hi == 4) build_bins(reinterpret_cast<float2*>(smem + OFF_BINS), raw, 15, tid, NT);
     }
-    if (warp == EPI_WARPS) {              // one warp owns the TMEM allocation: 2 stages x (hi + lo) x 128 columns
+    if (warp == EPI_WARPS) {              // one warp owns the TMEM allocation: 4 stages x 128 columns
         tmem_alloc(sbase + OFF_MISC, 512);
         tmem_relinquish();
     }
@@ -550,162 +579,122 @@ __global__ void __launch_bounds__(TMA ? NT_TMA : NT, 1) quantize_tc_kernel(Param
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const int64_t total_rows = p.n_lanes * p.n_rows;
-    TC_STAMP0(tid == 0, 1);
+    const uint32_t oper_bytes = d > 64 ? OPER_BYTES : KBLK_BYTES;        // bytes one tile's copies deliver
 
     if (warp < EPI_WARPS) {
-        // ======================= epilogue: row = 32*(warp%4) + lane, coordinate quarter = warp/4 =======================
-        const int bits = (p.bits_lo && (warp >> 3)) ? p.bits_lo : p.bits_hi;
-        EpiCtx e{p, smem, tmem_base, bar_accfull, bar_accfree, bar_afree, bar_nrm, abort_flag, total_rows, warp, lane};
-        if (FRAC) {                                             // 3.5, 2.5, 1.5 bits
-            if (p.bits_hi == 4) epilogue_loop_frac<4, 3, TMA>(e);
-            else if (p.bits_hi == 3) epilogue_loop_frac<3, 2, TMA>(e);
-            else epilogue_loop_frac<2, 1, TMA>(e);
-        } else if (bits == 4) epilogue_loop<4, TMA>(e);
-        else if (bits == 3) epilogue_loop<3, TMA>(e);
-        else if (bits == 2) epilogue_loop<2, TMA>(e);
-        else epilogue_loop<1, TMA>(e);
+        // ======================= epilogue: row = 32 * (warp % 4) + lane; groups and column halves as in EpiShape =======================
+        EpiCtx e{p, smem, tmem_base, bar_accfull, bar_accfree, bar_afree, bar_nrm, abort_flag, warp, lane};
+        const int key = p.bits_hi * 8 + p.bits_lo;
+        switch (key) {
+            case 4 * 8 + 0: epilogue_loop<4, 0, QJL, SPLITACC, DC>(e); break;
+            case 3 * 8 + 0: epilogue_loop<3, 0, QJL, SPLITACC, DC>(e); break;
+            case 2 * 8 + 0: epilogue_loop<2, 0, QJL, SPLITACC, DC>(e); break;
+            case 1 * 8 + 0: epilogue_loop<1, 0, QJL, SPLITACC, DC>(e); break;
+            case 4 * 8 + 3: epilogue_loop<4, 3, QJL, SPLITACC, DC>(e); break;
+            case 3 * 8 + 2: epilogue_loop<3, 2, QJL, SPLITACC, DC>(e); break;
+            case 2 * 8 + 1: epilogue_loop<2, 1, QJL, SPLITACC, DC>(e); break;
+            default: break;               // the host only launches the combinations above
+        }
     } else if (warp == EPI_WARPS) {
         // ======================= MMA issue: one elected thread =======================
         if (lane == 0) {
+            const uint32_t idesc = make_idesc(SPLITACC ? 2 * d : d, bf16);
+            const int ksteps = d / 16;
             int it = 0;
             for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
-                const int a = it % ACC_STAGES, s = it % A_STAGES;
-                if (it >= ACC_STAGES && !mbar_wait(bar_accfree + 8 * a, ((it / ACC_STAGES) - 1) & 1, abort_flag, 2)) break;
-                TC_STAMP(true, 1, it, 0);
-                if (!mbar_wait(bar_full + 8 * s, (it / A_STAGES) & 1, abort_flag, 1)) break;
+                const int a = it % ACCS, s = it % a_stages;
+                if (it >= ACCS && !mbar_wait(bar_accfree + 8 * a, uint32_t((it / ACCS) - 1) & 1u, abort_flag, 2)) break;
+                if (!mbar_wait(bar_full + 8 * s, uint32_t(it / a_stages) & 1u, abort_flag, 1)) break;
                 tc_fence_after();
-                TC_STAMP(true, 1, it, 1);
                 const uint32_t a_tile = sbase + OFF_A + s * OPER_BYTES;
-                const uint32_t d_hi = tmem_base + a * 256, d_lo = d_hi + 128;
-#pragma unroll
-                for (int kb = 0; kb < 2; ++kb) {
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        const uint64_t da = smem_desc(a_tile, kb, ks);
-                        const uint32_t acc = (kb | ks) ? 1u : 0u;
-                        umma_f16(d_hi, da, smem_desc(sbase + OFF_RHI, kb, ks), IDESC, acc);
-                        umma_f16(d_lo, da, smem_desc(sbase + OFF_RLO, kb, ks), IDESC, acc);
+                const uint32_t d_acc = tmem_base + a * Sh::STAGE_COLS;
+                if (SPLITACC) {
+                    // columns [0, d): x.R_hi, columns [d, 2 d): 2^11 x.R_lo; the operand's K-blocks are 32 KB apart
+#ifdef EXP_TWO_MMA
+                    const uint32_t idesc1 = make_idesc(d, bf16);
+                    for (int ks = 0; ks < ksteps; ++ks) {
+                        const uint64_t da = smem_desc(a_tile, ks >> 2, ks & 3);
+                        const uint32_t rb = sbase + OFF_R1 + (ks >> 2) * KBLK_BYTES;
+                        umma_f16(d_acc, da, smem_desc(rb, ks >> 2, ks & 3), idesc1, ks ? 1u : 0u);
+                        umma_f16(d_acc + d, da, smem_desc(rb + d * 128, ks >> 2, ks & 3), idesc1, ks ? 1u : 0u);
                     }
+#else
+                    for (int ks = 0; ks < ksteps; ++ks)
+                        umma_f16(d_acc, smem_desc(a_tile, ks >> 2, ks & 3), smem_desc(sbase + OFF_R1 + (ks >> 2) * KBLK_BYTES, ks >> 2, ks & 3), idesc, ks ? 1u : 0u);
+#endif
+                } else if (!bf16) {
+                    for (int ks = 0; ks < ksteps; ++ks)            // 2^11-scaled low products first
+                        umma_f16(d_acc, smem_desc(a_tile, ks >> 2, ks & 3), smem_desc(sbase + OFF_R2, ks >> 2, ks & 3), idesc, ks ? 1u : 0u);
+                    umma_f16_scaled11(d_acc, smem_desc(a_tile, 0, 0), smem_desc(sbase + OFF_R1, 0, 0), idesc);    // acc = x.R_hi + 2^-11 acc
+                    for (int ks = 1; ks < ksteps; ++ks)
+                        umma_f16(d_acc, smem_desc(a_tile, ks >> 2, ks & 3), smem_desc(sbase + OFF_R1, ks >> 2, ks & 3), idesc, 1u);
+                } else {
+                    const int r_off[3] = {OFF_R3, OFF_R2, OFF_R1};   // smallest term first
+                    for (int term = 0; term < 3; ++term)
+                        for (int ks = 0; ks < ksteps; ++ks)
+                            umma_f16(d_acc, smem_desc(a_tile, ks >> 2, ks & 3), smem_desc(sbase + r_off[term], ks >> 2, ks & 3), idesc, (term | ks) ? 1u : 0u);
                 }
-                umma_commit(bar_afree + 8 * s);      // rows of this stage consumed: producers may refill it
-                umma_commit(bar_accfull + 8 * a);    // both accumulators complete: epilogue may read them
-                TC_STAMP(true, 1, it, 2);
+                umma_commit(bar_afree + 8 * s);      // rows of this stage consumed
+                umma_commit(bar_accfull + 8 * a);    // the accumulator is complete: its epilogue group may read it
             }
         }
         __syncwarp();
-    } else if (TMA && warp == EPI_WARPS + 1 + N_NORM / 32) {
+    } else if (warp == EPI_WARPS + 1 + N_NORM / 32) {
         // ======================= TMA issue: one thread keeps the operand stages full =======================
         if (lane == 0) {
-            int64_t o = int64_t(blockIdx.x) / p.tiles_per_lane, tl = int64_t(blockIdx.x) - o * p.tiles_per_lane;
-            const int64_t so = int64_t(gridDim.x) / p.tiles_per_lane, st = int64_t(gridDim.x) - so * p.tiles_per_lane;
+            const uint32_t tpl = uint32_t(p.tiles_per_lane);
             int it = 0;
             for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
-                const int s = it % A_STAGES;
-                if (it >= A_STAGES && !mbar_wait(bar_afree + 8 * s, ((it / A_STAGES) - 1) & 1, abort_flag, 6)) break;
+                const int s = it % a_stages;
+                if (it >= a_stages && !mbar_wait(bar_afree + 8 * s, uint32_t((it / a_stages) - 1) & 1u, abort_flag, 6)) break;
+                const uint32_t t32 = uint32_t(tile), o = t32 / tpl, tl = t32 - o * tpl;
                 const uint32_t a_tile = sbase + OFF_A + s * OPER_BYTES;
-                mbar_expect_tx(bar_full + 8 * s, OPER_BYTES);
-                tma_load_3d(a_tile, &tmap, 0, int(tl * TM), int(o), bar_full + 8 * s);                    // columns 0..63
-                tma_load_3d(a_tile + KBLK_BYTES, &tmap, 64, int(tl * TM), int(o), bar_full + 8 * s);      // columns 64..127
-                o += so; tl += st;
-                if (tl >= p.tiles_per_lane) { tl -= p.tiles_per_lane; ++o; }
+                mbar_expect_tx(bar_full + 8 * s, oper_bytes);
+                tma_load_3d(a_tile, &tmap, 0, int(tl * TM), int(o), bar_full + 8 * s);                              // columns 0..63
+                if (d > 64) tma_load_3d(a_tile + KBLK_BYTES, &tmap, 64, int(tl * TM), int(o), bar_full + 8 * s);    // columns 64..127 (zeros past d)
             }
         }
         __syncwarp();
-    } else if (TMA) {
+    } else {
         // ======================= norm warps: sum of squares of every row, read back from the stage =======================
         // thread -> row 32 nw + lane, both 64-column blocks: eight consecutive rows hit eight different 16-byte columns
         // of the swizzled tile, so the 128-bit reads are free of bank conflicts
         const int nw = warp - (EPI_WARPS + 1), r = nw * 32 + lane;
         int it = 0;
         for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
-            const int s = it % A_STAGES;
-            if (!mbar_wait(bar_full + 8 * s, (it / A_STAGES) & 1, abort_flag, 7)) break;
+            const int s = it % a_stages;
+            if (!mbar_wait(bar_full + 8 * s, uint32_t(it / a_stages) & 1u, abort_flag, 7)) break;
             const unsigned char* rowp = smem + OFF_A + s * OPER_BYTES + r * 128;
             float a = 0.f, b = 0.f;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 const uint4 v = *reinterpret_cast<const uint4*>(rowp + ((c ^ (r & 7)) << 4));
-                const uint4 w = *reinterpret_cast<const uint4*>(rowp + KBLK_BYTES + ((c ^ (r & 7)) << 4));
-                const __half2* h = reinterpret_cast<const __half2*>(&v);
-                const __half2* g = reinterpret_cast<const __half2*>(&w);
+                uint4 w = make_uint4(0, 0, 0, 0);
+                if (d > 64) w = *reinterpret_cast<const uint4*>(rowp + KBLK_BYTES + ((c ^ (r & 7)) << 4));
+                if (!bf16) {
+                    const __half2* h = reinterpret_cast<const __half2*>(&v);
+                    const __half2* g = reinterpret_cast<const __half2*>(&w);
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const float2 f = __half22float2(h[u]), e = __half22float2(g[u]);
-                    a = fmaf(f.x, f.x, a); a = fmaf(f.y, f.y, a);
-                    b = fmaf(e.x, e.x, b); b = fmaf(e.y, e.y, b);
+                    for (int u = 0; u < 4; ++u) {
+                        const float2 f = __half22float2(h[u]), e = __half22float2(g[u]);
+                        a = fmaf(f.x, f.x, a); a = fmaf(f.y, f.y, a);
+                        b = fmaf(e.x, e.x, b); b = fmaf(e.y, e.y, b);
+                    }
+                } else {
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+                    const __nv_bfloat162* g = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float2 f = __bfloat1622float2(h[u]), e = __bfloat1622float2(g[u]);
+                        a = fmaf(f.x, f.x, a); a = fmaf(f.y, f.y, a);
+                        b = fmaf(e.x, e.x, b); b = fmaf(e.y, e.y, b);
+                    }
                 }
             }
             float* nsq = reinterpret_cast<float*>(smem + OFF_NSQ) + s * 2 * TM;
             nsq[r] = a; nsq[TM + r] = b;
             mbar_arrive(bar_nrm + 8 * s);        // release: the epilogue reads the sums after waiting on this barrier
             mbar_arrive(bar_afree + 8 * s);      // this thread is done reading the stage
-        }
-    } else {
-        // ======================= producers =======================
-        // Warp pw owns rows [16*pw, 16*pw + 16) of the tile; one warp-wide 128-bit load covers two whole rows
-        // (lane = 16*(row & 1) + chunk), i.e. 512 contiguous bytes when rows are contiguous.
-        const int pt = tid - (N_EPI + 32);
-        const int pw = pt >> 5, chunk = lane & 15, rsub = lane >> 4;
-        const int kblk = chunk >> 3, cc = chunk & 7;
-        // (lane, row) of this thread's first row of the tile, advanced by the grid stride: no 64-bit division per row
-        const bool wide = p.n_rows >= TM;            // a tile then spans at most two lanes
-        const int64_t stride_rows = int64_t(gridDim.x) * TM;
-        const int64_t step_o = stride_rows / p.n_rows, step_r = stride_rows - step_o * p.n_rows;
-        int64_t base_o = (int64_t(blockIdx.x) * TM + pw * 16 + rsub) / p.n_rows;
-        int64_t base_r = (int64_t(blockIdx.x) * TM + pw * 16 + rsub) - base_o * p.n_rows;
-        int it = 0;
-        for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++it) {
-            const int s = it % A_STAGES;
-            uint4 v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int64_t row = tile * TM + pw * 16 + i * 2 + rsub;
-                v[i] = make_uint4(0, 0, 0, 0);
-                if (row < total_rows) {
-                    int64_t o, rr;
-                    if (wide) {
-                        o = base_o; rr = base_r + i * 2;
-                        if (rr >= p.n_rows) { rr -= p.n_rows; ++o; }
-                    } else {
-                        o = row / p.n_rows; rr = row - o * p.n_rows;
-                    }
-                    v[i] = __ldg(reinterpret_cast<const uint4*>(p.x + o * p.x_lane_stride + rr * p.x_row_stride) + chunk);
-                }
-            }
-            base_r += step_r; base_o += step_o;
-            if (base_r >= p.n_rows) { base_r -= p.n_rows; ++base_o; }
-            TC_STAMP(pt == 0, 0, it, 0);
-            float ss[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const __half2* h = reinterpret_cast<const __half2*>(&v[i]);
-                float a = 0.f;
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const float2 f = __half22float2(h[u]);
-                    a = fmaf(f.x, f.x, a);
-                    a = fmaf(f.y, f.y, a);
-                }
-#pragma unroll
-                for (int off = 8; off; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
-                ss[i] = a;
-            }
-            TC_STAMP(pt == 0, 0, it, 1);
-            // the stage and its norm slots must be free: MMAs of tile it - A_STAGES done, its epilogue has read the norms
-            if (it >= A_STAGES && !mbar_wait(bar_afree + 8 * s, ((it / A_STAGES) - 1) & 1, abort_flag, 4)) break;
-            TC_STAMP(pt == 0, 0, it, 2);
-            unsigned char* stage = smem + OFF_A + s * OPER_BYTES + kblk * KBLK_BYTES;
-            float* nsq = reinterpret_cast<float*>(smem + OFF_NSQ) + s * 2 * TM;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int r = pw * 16 + i * 2 + rsub;
-                *reinterpret_cast<uint4*>(stage + r * 128 + ((cc ^ (r & 7)) << 4)) = v[i];
-                if (chunk == 0) { nsq[r] = ss[i]; nsq[TM + r] = 0.f; }
-            }
-            fence_proxy_async();                     // generic-proxy stores -> visible to the tensor core
-            mbar_arrive(bar_full + 8 * s);
-            TC_STAMP(pt == 0, 0, it, 3);
         }
     }
     // ---- teardown: every loop above is bounded, so every thread gets here ----
@@ -715,7 +704,6 @@ __global__ void __launch_bounds__(TMA ? NT_TMA : NT, 1) quantize_tc_kernel(Param
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
-    if (tid == 0 && *abort_flag && p.status) *p.status = *abort_flag;
 }
 
 }  // namespace tc
@@ -724,16 +712,17 @@ __global__ void __launch_bounds__(TMA ? NT_TMA : NT, 1) quantize_tc_kernel(Param
 
 using namespace tq;
 
-static int g_quantize_tma = 1;     // tq_set_tuning("quantize_tma", 0 / 1)
-namespace tq { void set_quantize_tma(int on) { g_quantize_tma = on ? 1 : 0; } }
-
-// Takes the call when it fits the tensor-core kernel: fp16 rows, d = 128, 16-byte aligned rows, no QJL sketch,
-// no rotated-row output.  Otherwise reports "not handled" and the caller uses the general CUDA-core kernel.
+// Takes the call when it fits the tensor-core kernel: fp16 / bf16 rows, d in {64, 96, 128}, 16-byte aligned rows, no
+// rotated-row output, a bit-width pair the epilogue is compiled for.  Otherwise reports "not handled" and the caller uses
+// the general CUDA-core kernel.
 int tq_quantize_pack_tc(const tq_quantize_args* q, cudaStream_t s, bool* handled) {
     *handled = false;
-    if (q->d != tc::D || q->x_dtype != TQ_F16 || q->qjl_bits || q->y_out) return TQ_OK;
-    if (q->bits_lo > tc::DIRECT_MAX_BITS) return TQ_OK;      // the kernel keeps one bin table: only the high-bit half may need it
+    const int d = q->d;
+    if ((d != 64 && d != 96 && d != 128) || (q->x_dtype != TQ_F16 && q->x_dtype != TQ_BF16) || q->y_out) return TQ_OK;
+    const bool frac = q->bits_lo != 0;
+    if (frac && (q->bits_hi != q->bits_lo + 1)) return TQ_OK;                  // the reference's fractional widths only
     if (!aligned(q->x, 16) || q->x_row_stride % 8 || q->x_lane_stride % 8 || !aligned(q->rot, 16)) return TQ_OK;
+    if (q->n_rows >= (int64_t(1) << 31) || q->n_lanes >= (int64_t(1) << 31)) return TQ_OK;
     static int disabled = -1;
     if (disabled < 0) {
         const char* e = getenv("TQ_DISABLE_TC");
@@ -742,37 +731,21 @@ int tq_quantize_pack_tc(const tq_quantize_args* q, cudaStream_t s, bool* handled
     if (disabled) return TQ_OK;
     const int64_t total = q->n_lanes * q->n_rows;
     if (total < 4 * tc::TM) return TQ_OK;            // tiny inputs: not worth a persistent launch
+    const bool qjl = q->qjl_bits != nullptr;
     static bool attr_set[16] = {false};
     static int sms[16] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 16) return TQ_OK;
     if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(tc::quantize_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::quantize_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::quantize_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::quantize_tc_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(tc::quantize_tc_kernel<false, true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::quantize_tc_kernel<false, true, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::quantize_tc_kernel<false, false, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::quantize_tc_kernel<true, false, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES);
         if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_quantize_pack: shared memory %d B: %s", tc::SMEM_BYTES, cudaGetErrorString(e));
         if (cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms[dev] <= 0) sms[dev] = 148;
         attr_set[dev] = true;
     }
-    tc::Params p{};
-    p.x = static_cast<const __half*>(q->x);
-    p.n_lanes = q->n_lanes; p.n_rows = q->n_rows; p.x_lane_stride = q->x_lane_stride; p.x_row_stride = q->x_row_stride;
-    p.rot = q->rot; p.bnd_hi = q->bnd_hi; p.bnd_lo = q->bnd_lo; p.bits_hi = q->bits_hi; p.bits_lo = q->bits_lo;
-    p.p_hi = q->packed_hi; p.p_lo = q->packed_lo; p.norms = q->norms; p.out_lane_stride = q->out_lane_stride;
-    p.status = nullptr;
-
-    // Tensor map over the rows as (column, row, lane): boxes of 64 columns x 128 rows x 1 lane land in shared memory in
-    // the 128-byte-swizzled layout the MMA descriptors describe; rows past a lane's end read as zeros.
-    CUtensorMap tmap{};
-    bool use_tma = false;
-    static int env_off = -1;
-    if (env_off < 0) {
-        const char* e = getenv("TQ_DISABLE_TMA");
-        env_off = (e && e[0] == '1') ? 1 : 0;
-    }
-    const bool tma_off = env_off || !g_quantize_tma;
     static PFN_cuTensorMapEncodeTiled encode = nullptr;
     static bool looked_up = false;
     if (!looked_up) {
@@ -782,44 +755,41 @@ int tq_quantize_pack_tc(const tq_quantize_args* q, cudaStream_t s, bool* handled
             encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
         looked_up = true;
     }
-    if (!tma_off && encode && q->n_rows < (int64_t(1) << 31) && q->n_lanes < (int64_t(1) << 31)) {
-        const cuuint64_t dims[3] = {cuuint64_t(tc::D), cuuint64_t(q->n_rows), cuuint64_t(q->n_lanes)};
-        const cuuint64_t strides[2] = {cuuint64_t(q->x_row_stride) * 2, cuuint64_t(q->x_lane_stride) * 2};     // bytes, multiples of 16
-        const cuuint32_t box[3] = {64, cuuint32_t(tc::TM), 1};
-        const cuuint32_t estr[3] = {1, 1, 1};
-        const CUresult r = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(q->x), dims, strides, box, estr,
-                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        use_tma = (r == CUDA_SUCCESS);
-    }
-    const bool frac = q->bits_lo != 0 && q->bits_hi == q->bits_lo + 1;     // balanced epilogue of the fractional widths
-    if (use_tma) {
-        p.tiles_per_lane = (q->n_rows + tc::TM - 1) / tc::TM;
-        p.n_tiles = q->n_lanes * p.tiles_per_lane;
-        const unsigned grid = unsigned(std::min<int64_t>(p.n_tiles, sms[dev]));
-        if (frac) tc::quantize_tc_kernel<true, true><<<grid, tc::NT_TMA, tc::SMEM_BYTES, s>>>(p, tmap);
-        else tc::quantize_tc_kernel<true, false><<<grid, tc::NT_TMA, tc::SMEM_BYTES, s>>>(p, tmap);
-    } else {
-        p.tiles_per_lane = 0;
-        p.n_tiles = (total + tc::TM - 1) / tc::TM;
-        const unsigned grid = unsigned(std::min<int64_t>(p.n_tiles, sms[dev]));
-        if (frac) tc::quantize_tc_kernel<false, true><<<grid, tc::NT, tc::SMEM_BYTES, s>>>(p, tmap);
-        else tc::quantize_tc_kernel<false, false><<<grid, tc::NT, tc::SMEM_BYTES, s>>>(p, tmap);
-    }
+    if (!encode) return TQ_OK;
+    // Tensor map over the rows as (column, row, lane): boxes of 64 columns x 128 rows x 1 lane land in shared memory in
+    // the 128-byte-swizzled layout the MMA descriptors describe; rows past a lane's end and columns past d read as zeros.
+    CUtensorMap tmap{};
+    const cuuint64_t dims[3] = {cuuint64_t(d), cuuint64_t(q->n_rows), cuuint64_t(q->n_lanes)};
+    const cuuint64_t strides[2] = {cuuint64_t(q->x_row_stride) * 2, cuuint64_t(q->x_lane_stride ? q->x_lane_stride : q->x_row_stride * q->n_rows) * 2};   // bytes, multiples of 16
+    const cuuint32_t box[3] = {64, cuuint32_t(tc::TM), 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = encode(&tmap, q->x_dtype == TQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(q->x),
+                              dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return TQ_OK;
+
+    tc::Params p{};
+    p.d = d; p.bf16 = q->x_dtype == TQ_BF16 ? 1 : 0; p.a_stages = p.bf16 ? 2 : 3;
+    p.n_rows = q->n_rows;
+    p.tiles_per_lane = (q->n_rows + tc::TM - 1) / tc::TM;
+    p.n_tiles = q->n_lanes * p.tiles_per_lane;
+    if (p.n_tiles >= (int64_t(1) << 31)) return TQ_OK;
+    p.rot = q->rot; p.bnd_hi = q->bnd_hi; p.bnd_lo = q->bnd_lo; p.bits_hi = q->bits_hi; p.bits_lo = q->bits_lo;
+    p.p_hi = q->packed_hi; p.p_lo = q->packed_lo; p.norms = q->norms; p.out_lane_stride = q->out_lane_stride;
+    p.qjl_proj_rot = q->qjl_proj_rot; p.cent_hi = q->cent_hi; p.cent_lo = q->cent_lo; p.qjl_bits = q->qjl_bits; p.qjl_gamma = q->qjl_gamma;
+    const unsigned grid = unsigned(std::min<int64_t>(p.n_tiles, sms[dev]));
+    if (qjl) tc::quantize_tc_kernel<true, false, 0><<<grid, tc::n_threads(true), tc::SMEM_BYTES, s>>>(p, tmap);
+    else if (p.bf16) tc::quantize_tc_kernel<false, false, 0><<<grid, tc::n_threads(false), tc::SMEM_BYTES, s>>>(p, tmap);
+    else if (d == 128) tc::quantize_tc_kernel<false, true, 128><<<grid, tc::n_threads(false), tc::SMEM_BYTES, s>>>(p, tmap);
+    else tc::quantize_tc_kernel<false, true, 0><<<grid, tc::n_threads(false), tc::SMEM_BYTES, s>>>(p, tmap);
     *handled = true;
     return check_launch("tq_quantize_pack (tensor core)");
 }
 
-// 0 if no tensor-core quantize launch on the current device has reported a timed-out wait, else its code.
-// Synchronises the device.
-#ifdef TQ_TIMING
-extern "C" int tq_debug_tc_timing(unsigned long long* host_out, int n) {
-    return int(cudaMemcpyFromSymbol(host_out, tc::g_tc_timing, sizeof(unsigned long long) * n));
-}
-#endif
-
 namespace tq { int decode_status_host(); int decode_status_clear(); }   // decode_direct.cu
 
+// 0 if no kernel on the current device has reported a timed-out wait, else the code of the first one.
+// Synchronises the device.
 extern "C" int tq_device_status(void) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, tc::g_status, sizeof(int)) != cudaSuccess) return -1;

@@ -203,3 +203,41 @@ def test_qjl_correction_reduces_error_and_leaves_fp16_regions_alone():
     e_on = ((outs[True][:, :, mid] - x[:, :, mid]) ** 2).mean().item()
     assert e_on < e_off
     assert torch.equal(outs[True][:, :, :8], x[:, :, :8]) and torch.equal(outs[True][:, :, -16:], x[:, :, -16:])
+
+
+@pytest.mark.parametrize("kw", (dict(key_bits=4, value_bits=2, residual_window=8, fp16_sink_size=4),
+                                dict(key_bits=3.5, value_bits=3, residual_window=8, chunk_size=16),
+                                dict(key_bits=4, value_bits=2, residual_window=8, fp16_sink_size=4, qjl_correction=True)))
+@pytest.mark.parametrize("dtype", (torch.float16, torch.float32))
+def test_decode_step_equals_update_then_attend(kw, dtype):
+    """`decode_step` (the token's append folded into the attention launch) against `update` + `attend` on a twin cache,
+    token by token from an empty cache: through the sink, the first fills of the buffer, drains, and buffer growth.
+    Same bits out, same state afterwards."""
+    from mlx_turboquant_b200 import TurboQuantKVCache
+    d, hkv, hq, b = 128, 2, 8, 2
+    g = torch.Generator(device="cuda").manual_seed(5)
+    a, c = TurboQuantKVCache(head_dim=d, num_kv_heads=hkv, **kw), TurboQuantKVCache(head_dim=d, num_kv_heads=hkv, **kw)
+    pre = 300
+    k0 = torch.randn(b, hkv, pre, d, device="cuda", generator=g).to(dtype)
+    v0 = torch.randn(b, hkv, pre, d, device="cuda", generator=g).to(dtype)
+    for cache in (a, c):
+        cache.update(k0[:, :, :2], v0[:, :, :2])              # two tokens: still inside the sink
+    fused = 0
+    for i in range(2, 60):
+        q = (torch.randn(b, hq, 1, d, device="cuda", generator=g) / d ** 0.5).to(dtype)
+        k, v = k0[:, :, i:i + 1].contiguous(), v0[:, :, i:i + 1].contiguous()
+        before = a._fp16_len
+        out_a = a.decode_step(q, k, v)
+        c.update(k, v)
+        out_c = c.attend(q)
+        fused += int(a._fp16_len == before + 1 and a._compressed_len == c._compressed_len)
+        assert torch.equal(out_a, out_c), i
+        assert (a.offset, a._fp16_len, a._compressed_len, a._sink_len) == (c.offset, c._fp16_len, c._compressed_len, c._sink_len)
+    assert fused > 30                                          # most steps took the single launch
+    for x, y in zip(a.state, c.state):
+        assert (x is None) == (y is None)
+        if x is not None:
+            n = min(x.shape[2], y.shape[2])
+            if x.dtype == torch.uint8 or x.shape[2] == y.shape[2]:
+                assert torch.equal(x[:, :, :n], y[:, :, :n])
+    assert torch.equal(a.keys[:, :, :a._fp16_len], c.keys[:, :, :c._fp16_len])

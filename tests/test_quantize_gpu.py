@@ -206,7 +206,7 @@ def test_fused_qk_scores_shapes(oracle, tables, tq, tkv, d, bits):
 @pytest.mark.parametrize("kb,lanes,rows", ((4, 8, 1000), (2, 8, 1024), (3, 3, 700), (3.5, 4, 1153), (2.5, 2, 4096), (1.5, 3, 900), (4, 1, 513)))
 def test_tensor_core_quantize_path(oracle, tables, kb, lanes, rows):
     """fp16, d = 128 rows go through the tcgen05 kernel (>= 512 rows): same parity bar as the general kernel,
-    ragged last tile, strided lanes (rows taken from a larger buffer), every packed width."""
+    ragged last tile, strided lanes (rows taken from a larger buffer), every packed width (1.5 bits included)."""
     from mlx_turboquant_b200 import _lib, kernels
     from mlx_turboquant_b200.codebook import get_codebook
     from mlx_turboquant_b200.rotation import get_rotation_matrix
@@ -250,30 +250,95 @@ def test_tensor_core_and_general_kernels_agree(tables):
     assert (host(p1) != host(p2)).mean() < 1e-4
 
 
-def test_tensor_core_quantize_tma_and_producer_loads_agree(tables):
-    """The two ways the tcgen05 kernel fetches its rows (tiled TMA copies; loads in producer warps) feed the same
-    arithmetic: same codes and norms, on contiguous rows and on rows sliced out of a larger buffer with a ragged tail."""
-    from mlx_turboquant_b200 import kernels
+def _sign_words(signs):
+    """(…, 32) bool -> (…) uint32, bit i = sign i."""
+    w = np.zeros(signs.shape[:-1], dtype=np.uint32)
+    for i in range(32):
+        w |= signs[..., i].astype(np.uint32) << np.uint32(i)
+    return w
+
+
+@pytest.mark.parametrize("d", (64, 96, 128))
+@pytest.mark.parametrize("bf16", (False, True))
+@pytest.mark.parametrize("kb,qjl", ((4, False), (3, False), (2, False), (3.5, False), (2.5, False), (4, True), (2, True), (3.5, True)))
+def test_tensor_core_quantize_head_dims_dtypes_and_sketch(oracle, tables, d, bf16, kb, qjl):
+    """The tcgen05 kernel at every head_dim it takes (64, 96, 128), fp16 and bf16 rows, integer and fractional widths,
+    with and without the QJL sketch of the residual: codes against the oracle at the usual bar (fewer than 1e-4 differ,
+    by one level, within 1e-6 of a boundary), norms 2e-6; the sketch's sign words may differ only where a projection is
+    within rounding of zero (fewer than 1e-3 of the bits) and the residual norms agree to 1e-4.  Rows come out of a
+    larger buffer (lane stride != rows * d), the last tile is ragged, one row is zero."""
+    from mlx_turboquant_b200 import _lib, kernels
     from mlx_turboquant_b200.codebook import get_codebook
     from mlx_turboquant_b200.rotation import get_rotation_matrix
-    rs = np.random.RandomState(5)
-    rot = get_rotation_matrix(128)
-    buf = cu(kv_like(rs, (2, 3, 1500, 128)))
-    for x in (buf, buf[:, :, 7:7 + 1153]):
-        for kb in (4, 3, 2, 3.5):
-            hi, lo = kernels.split_bits(kb)
-            bh = get_codebook(128, hi)[1]
-            bl = get_codebook(128, lo)[1] if lo else None
-            a = kernels.quantize_pack(x, rot, bh, hi, bl, lo)
-            kernels.set_tuning("quantize_tma", 0)
-            try:
-                b = kernels.quantize_pack(x, rot, bh, hi, bl, lo)
-            finally:
-                kernels.set_tuning("quantize_tma", 1)
-            for u, v in zip(a, b):                          # (codes hi, codes lo, norms)
-                if u is None:
-                    assert v is None
-                elif u.dtype == torch.uint8:
-                    assert (u != v).float().mean() < 1e-5       # the sums of squares are added in a different order: a norm
-                else:                                           # may differ in its last bit and tip a value over a boundary
-                    torch.testing.assert_close(u, v, rtol=2e-6, atol=0)
+    lanes, rows = 3, 1153
+    rs = np.random.RandomState(int(kb * 10) + d + (7 if bf16 else 0) + (13 if qjl else 0))
+    hi, lo = kernels.split_bits(kb)
+    buf = cu(kv_like(rs, (1, lanes, rows + 40, d), np.float32))
+    buf = buf.to(torch.bfloat16) if bf16 else buf.half()
+    x = buf[:, :, 16:16 + rows]
+    x[0, 1, 5] = 0
+    xh = host(x.float())
+    (ch, bh), (cl, bl) = get_codebook(d, hi), (get_codebook(d, lo) if lo else (None, None))
+    rot = get_rotation_matrix(d)
+    sk = None
+    if qjl:
+        s_host = oracle.projection_matrix(d, 32)
+        prot = cu((s_host.astype(np.float64) @ oracle.rotation_matrix(d).astype(np.float64).T).astype(np.float32))
+        sk = dict(proj_rot=prot, cent_hi=ch, cent_lo=cl, bits=torch.zeros(1, lanes, rows, dtype=torch.int32, device="cuda"),
+                  gamma=torch.zeros(1, lanes, rows, dtype=torch.float32, device="cuda"))
+    out_hi = torch.zeros(1, lanes, rows, kernels.packed_widths(d, hi, lo)[0], dtype=torch.uint8, device="cuda")
+    out_lo = torch.zeros(1, lanes, rows, kernels.packed_widths(d, hi, lo)[1], dtype=torch.uint8, device="cuda") if lo else None
+    out_n = torch.zeros(1, lanes, rows, dtype=torch.float32, device="cuda")
+    kernels.quantize_pack(x, rot, bh, hi, bl, lo, out_hi=out_hi.view(lanes, rows, -1), out_lo=None if out_lo is None else out_lo.view(lanes, rows, -1),
+                          out_norms=out_n.view(lanes, rows), qjl=None if sk is None else dict(sk, bits=sk["bits"].view(lanes, rows), gamma=sk["gamma"].view(lanes, rows)))
+    assert _lib.lib().tq_device_status() == 0
+    orot = oracle.rotation_matrix(d)
+    half = d // 2
+    if lo:
+        rh, rl, rn, ry = oracle.split_quantize(xh, orot, tables[(d, hi)][1], hi, tables[(d, lo)][1], lo)
+        f2 = code_mismatch_report(host(out_lo), rl, lo, half, ry[..., half:], tables[(d, lo)][1])
+        assert tuple(out_lo.shape) == rl.shape and f2[0] < 1e-4 and f2[1] <= 1 and f2[2] < 1e-6, f2
+        f1 = code_mismatch_report(host(out_hi), rh, hi, half, ry[..., :half], tables[(d, hi)][1])
+    else:
+        rh, rn, ry = oracle.mse_quantize(xh, orot, tables[(d, hi)][1], hi)
+        f1 = code_mismatch_report(host(out_hi), rh, hi, d, ry, tables[(d, hi)][1])
+    assert tuple(out_hi.shape) == rh.shape and f1[0] < 1e-4 and f1[1] <= 1 and f1[2] < 1e-6, f1
+    np.testing.assert_allclose(host(out_n), rn, rtol=2e-6)
+    assert host(out_n)[0, 1, 5] == 0
+    if qjl:
+        # the oracle's sketch of the residual of ITS OWN codes; rows whose codes differ are left out of the comparison
+        if lo:
+            deq = oracle.split_dequantize(rh, rl, rn, orot, tables[(d, hi)][0], hi, tables[(d, lo)][0], lo, d)
+            same = (host(out_hi) == rh).all(-1) & (host(out_lo) == rl).all(-1)
+        else:
+            deq = oracle.mse_dequantize(rh, rn, orot, tables[(d, hi)][0], hi, d)
+            same = (host(out_hi) == rh).all(-1)
+        signs, gamma = oracle.qjl_quantize((xh - deq).reshape(-1, d), s_host)
+        words, gamma = _sign_words(signs).reshape(same.shape), gamma.reshape(same.shape)
+        got_w, got_g = host(sk["bits"]).view(np.uint32), host(sk["gamma"])
+        live = same & (rn > 0)
+        diff_bits = np.unpackbits((got_w[live] ^ words[live]).view(np.uint8)).sum()
+        assert live.mean() > 0.97 and diff_bits < 1e-3 * 32 * live.sum(), (live.mean(), diff_bits)
+        np.testing.assert_allclose(got_g[live], gamma[live], rtol=1e-4)
+        assert got_w[0, 1, 5] == 0xFFFFFFFF and got_g[0, 1, 5] == 0            # zero row: residual 0, 0 >= 0 on every projection
+
+
+
+@pytest.mark.parametrize("d,m", ((64, 32), (96, 32), (128, 128), (256, 256), (128, 40)))
+def test_qjl_kernels_against_oracle(oracle, d, m):
+    """The stand-alone sketch kernels (qjl.py:47-94) for the cache's 32 projections, TurboQuantProd's m = d and an odd m:
+    signs may differ only where a projection is within float32 rounding of zero, norms 1e-5, reconstruction 1e-4;
+    leading dimensions are kept, a ragged row count crosses CTA boundaries."""
+    from mlx_turboquant_b200.qjl import qjl_dequantize, qjl_quantize
+    rs = np.random.RandomState(d + m)
+    r = (rs.randn(3, 333, d) * 0.1).astype(np.float32)
+    r[1, 7] = 0
+    S = oracle.projection_matrix(d, m)
+    signs, gamma = qjl_quantize(cu(r), cu(S))
+    rs_, rg = oracle.qjl_quantize(r, S)
+    assert signs.dtype == torch.bool and tuple(signs.shape) == (3, 333, m) and tuple(gamma.shape) == (3, 333)
+    assert (host(signs) == rs_).mean() > 0.999 and host(signs)[1, 7].all()          # 0 >= 0 on every projection
+    np.testing.assert_allclose(host(gamma), rg, rtol=1e-5)
+    deq = qjl_dequantize(cu(rs_), cu(rg), cu(S), d)
+    ref = oracle.qjl_dequantize(rs_, rg, S, d)
+    np.testing.assert_allclose(host(deq), ref, rtol=1e-4, atol=1e-6 * np.abs(ref).max())
