@@ -237,6 +237,14 @@ int tq_decode_attn(const tq_decode_args* a, void* stream);
  * for compression (tq_quantize_pack) and when a token belongs to the sink instead. */
 int tq_decode_step(const tq_decode_args* a, const void* k_new, const void* v_new, void* stream);
 
+/* Causal attention for t_q query tokens per sequence - the LAST t_q tokens of the cache, appended by the caller
+ * beforehand: query i sits at position c_len + sink_len + res_len - t_q + i and sees every cached token up to and
+ * including itself.  a->q and a->out are (batch, n_q_heads, t_q, d); workspace, tables and gather are not used.  Caches
+ * with a QJL sketch are refused with TQ_ERR_UNSUPPORTED (their callers take the dense route).  Replaces dense
+ * reassembly (cache.py:674-706) + the consumer's masked attention for prefill chunks and multi-token steps; the
+ * reference only sketched it for packed keys (kernels.py:558-590, docs/FUSED_ATTENTION_DESIGN.md:281-283). */
+int tq_prefill_attn(const tq_decode_args* a, int t_q, void* stream);
+
 /* Same computation as tq_decode_attn for callers that can neither lend a workspace nor allocate one at call
  * time (a process that gave the whole device to its own memory pool at start-up; a step loop that cannot afford
  * a driver allocation).  It has no counterpart in the reference.  `workspace` / `workspace_bytes` in the

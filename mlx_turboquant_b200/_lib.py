@@ -96,6 +96,7 @@ PROTOTYPES = {
     "tq_decode_tables_build": (_i, [_i, _vp, _vp, _i, _vp, _i, _f, _vp, _sz, _vp]),
     "tq_decode_attn": (_i, [C.POINTER(DecodeArgs), _vp]),
     "tq_decode_step": (_i, [C.POINTER(DecodeArgs), _vp, _vp, _vp]),
+    "tq_prefill_attn": (_i, [C.POINTER(DecodeArgs), _i, _vp]),
     "tq_decode_attn_static": (_i, [C.POINTER(DecodeArgs), _vp]),
     "tq_set_tuning": (_i, [C.c_char_p, _i]),
     "tq_fp16_table_scale": (_f, [_vp, _i]),

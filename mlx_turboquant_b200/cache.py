@@ -455,9 +455,10 @@ class TurboQuantKVCache:
     # ---- attention on the packed cache -----------------------------------------------------------
     def attend(self, queries: torch.Tensor, scale: float | None = None, out_dtype=None, gather=None,
                out: torch.Tensor | None = None, _new=None) -> torch.Tensor | None:
-        """softmax(scale * q K^T) V for ONE query token per sequence, straight from packed storage.
+        """softmax(scale * q K^T) V straight from packed storage.
 
-        ``queries`` is (B, n_q_heads, 1, D) or (B, n_q_heads, D); the result has the same shape and, unless
+        ``queries`` is (B, n_q_heads, 1, D) or (B, n_q_heads, D) for a decode step, or (B, n_q_heads, T_q, D) for the last
+        T_q tokens of the cache (causal; see ``_attend_many``); the result has the same shape and, unless
         ``out_dtype`` says otherwise, the same dtype.  Equals attention over what ``update_and_fetch``
         would return (to ~1e-3 with a float32 result; a float16 result adds its own rounding), without
         building it.  With ``gather`` (a slot of ``sharding.FusedGather``: this rank holds some of the heads) the
@@ -469,7 +470,9 @@ class TurboQuantKVCache:
         d = self.head_dim
         squeeze = queries.dim() == 3
         if not squeeze and queries.shape[2] != 1:
-            raise NotImplementedError("attend handles a single query token per sequence (decode step)")
+            if gather is not None or _new is not None:
+                raise NotImplementedError("several query tokens per sequence: no fused gather, no fused append")
+            return self._attend_many(queries, scale, out_dtype, out)
         b, hq = queries.shape[0], queries.shape[1]
         if self.empty() and _new is None:
             raise ValueError("attend on an empty cache")
@@ -519,6 +522,31 @@ class TurboQuantKVCache:
         if given is not None:
             return given
         return out if squeeze else out.reshape(b, hq, 1, d)
+
+    def _attend_many(self, queries: torch.Tensor, scale, out_dtype, out) -> torch.Tensor:
+        """Causal attention for queries (B, n_q_heads, T_q, D) that are the LAST T_q tokens of the cache (call ``update``
+        with their keys and values first), straight from packed storage: query i sees every cached token up to and
+        including itself.  Equals causal attention over what ``update_and_fetch`` returns, without building it."""
+        dev = queries.device
+        d = self.head_dim
+        b, hq, tq = queries.shape[0], queries.shape[1], queries.shape[2]
+        if self.qjl_correction:
+            raise NotImplementedError("several query tokens over a cache with a QJL sketch: use update_and_fetch (dense route)")
+        if tq > self._sink_len + self._compressed_len + self._fp16_len:
+            raise ValueError("more query tokens than the cache holds: call update() with their keys and values first")
+        q = queries
+        if q.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+            q = q.to(torch.float32)
+        q = q.contiguous()
+        if out is None:
+            out = torch.empty((b, hq, tq, d), dtype=out_dtype or q.dtype, device=dev)
+        elif out.device != dev or tuple(out.shape) != (b, hq, tq, d) or not out.is_contiguous() or out.dtype not in _lib._DTYPES:
+            raise ValueError("out must be a contiguous float16 / bfloat16 / float32 tensor of the queries' shape on their device")
+        a = self._fill_decode_args(b, hq, q.dtype, out.dtype, scale)
+        a.q, a.out = q.data_ptr(), out.data_ptr()
+        a.c_len, a.sink_len, a.res_len = self._compressed_len, self._sink_len, self._fp16_len
+        _lib.check(_lib.launch(dev, "tq_prefill_attn", C.byref(a), tq, _lib.stream_ptr(dev)))
+        return out
 
     def decode_step(self, queries: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, scale: float | None = None,
                     out: torch.Tensor | None = None) -> torch.Tensor:

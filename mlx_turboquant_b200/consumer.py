@@ -86,9 +86,14 @@ class Attention(torch.nn.Module):
                 rope_memo[(offset, L)] = tables
         qk = apply_rope(qkv[:, :hq + hkv], tables)
         queries, keys, values = qk[:, :hq], qk[:, hq:], qkv[:, hq + hkv:]
-        if cache is not None and packed and L == 1 and hasattr(cache, "attend"):
-            cache.update(keys.contiguous(), values.contiguous())
-            out = cache.attend(queries.contiguous(), self.scale)                       # (B, hq, 1, d)
+        if cache is not None and packed and hasattr(cache, "attend") and (L == 1 or not getattr(cache, "qjl_correction", False)):
+            # attention straight from packed storage: one launch for a decode step (the token's append included), the
+            # causal multi-token kernel for prefill chunks (caches with a QJL sketch take the dense route there)
+            if L == 1:
+                out = cache.decode_step(queries.contiguous(), keys.contiguous(), values.contiguous(), self.scale)     # (B, hq, 1, d)
+            else:
+                cache.update(keys.contiguous(), values.contiguous())
+                out = cache.attend(queries.contiguous(), self.scale)                   # (B, hq, L, d)
         else:
             if cache is not None:
                 keys, values = cache.update_and_fetch(keys.contiguous(), values.contiguous())

@@ -37,13 +37,22 @@ class KVCache:
         self.update_and_fetch(keys, values)
 
     def attend(self, queries, scale=None):
-        d = queries.shape[-1]
-        q = queries.reshape(queries.shape[0], queries.shape[1], 1, d).float()
+        """Causal attention of the last ``T_q`` positions over everything stored (float32 arithmetic)."""
+        d, tq = queries.shape[-1], queries.shape[2] if queries.dim() == 4 else 1
+        q = queries.reshape(queries.shape[0], queries.shape[1], tq, d).float()
         rep = q.shape[1] // self.keys.shape[1]
         k = self.keys.float().repeat_interleave(rep, dim=1)
         v = self.values.float().repeat_interleave(rep, dim=1)
-        p = torch.softmax((q @ k.transpose(-1, -2)) * (d ** -0.5 if scale is None else scale), dim=-1)
-        return (p @ v).to(queries.dtype).reshape(queries.shape)
+        s = (q @ k.transpose(-1, -2)) * (d ** -0.5 if scale is None else scale)
+        if tq > 1:
+            t = k.shape[2]
+            pos = torch.arange(t - tq, t, device=s.device)
+            s = s.masked_fill(torch.arange(t, device=s.device)[None, :] > pos[:, None], float("-inf"))
+        return (torch.softmax(s, dim=-1) @ v).to(queries.dtype).reshape(queries.shape)
+
+    def decode_step(self, queries, keys, values, scale=None):
+        self.update(keys, values)
+        return self.attend(queries, scale)
 
     def make_mask(self, N, offset=0, return_array=False, window_size=None):
         return None if N == 1 and not return_array else "causal"

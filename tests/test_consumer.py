@@ -53,7 +53,7 @@ class _Recorder:
     """Wraps one layer's cache and keeps what the caller fed it and got back."""
 
     def __init__(self, inner):
-        self.inner, self.fed, self.queries, self.outs = inner, [], [], []
+        self.inner, self.fed, self.calls = inner, [], []
 
     def __getattr__(self, name):
         return getattr(self.inner, name)
@@ -68,8 +68,13 @@ class _Recorder:
 
     def attend(self, q, scale=None):
         out = self.inner.attend(q, scale)
-        self.queries.append(q.clone())
-        self.outs.append(out.clone())
+        self.calls.append((len(self.fed) - 1, q.clone(), out.clone()))
+        return out
+
+    def decode_step(self, q, k, v, scale=None):
+        self.fed.append((k.clone(), v.clone()))
+        out = self.inner.decode_step(q, k, v, scale)
+        self.calls.append((len(self.fed) - 1, q.clone(), out.clone()))
         return out
 
 
@@ -104,13 +109,14 @@ def test_packed_route_matches_dense_route_and_oracle(kb, vb, qjl):
     # layer 0's traffic through the oracle's cache: same inputs, attention in float32 over its dense output
     d = 128
     ref_c = oracle.KVCacheOracle(d, host_tables(d), kb, vb, 32, fp16_sink_size=16, chunk_size=0, qjl_correction=qjl)
-    for i, (k, v) in enumerate(rec.fed):
-        rk, rv = ref_c.update_and_fetch(host(k), host(v))
-        if i == 0:
-            continue                                                 # the prefill call went the dense way
-        ref = oracle.attention(host(rec.queries[i - 1]), rk, rv)
-        got = host(rec.outs[i - 1])
-        assert np.abs(got - ref).max() / np.abs(ref).max() < 1e-3
+    dense = [ref_c.update_and_fetch(host(k), host(v)) for (k, v) in rec.fed]
+    assert len(rec.calls) == (40 if qjl else 41)                     # with a sketch the prefill call goes the dense way
+    for (i, q, got) in rec.calls:
+        rk, rv = dense[i]
+        tq, tkv = q.shape[2], rk.shape[2]
+        ref = np.concatenate([oracle.attention(host(q)[:, :, j:j + 1], rk[:, :, :tkv - tq + j + 1], rv[:, :, :tkv - tq + j + 1])
+                              for j in range(tq)], axis=2)           # causal: query j sees the keys up to its own
+        assert np.abs(host(got) - ref).max() / np.abs(ref).max() < 1e-3
     assert ref_c.offset == 190 and ref_c.comp_len > 0
 
 
