@@ -335,16 +335,89 @@ def bench_c3(torch, dev, steps, warmup, peak):
             "kernel": "decode_attn_kernel<96, qjl> (general kernel: unpack to shared memory, ldmatrix)"}
 
 
+def bench_head_split(torch, dist, dev, world, rank, steps, warmup):
+    """N > 1: the headline workload as ONE sequence whose KV heads are dealt to the GPUs (strong scaling of a single
+    sequence), timed three ways in the same process group: every GPU keeps its own heads' outputs (no exchange); the
+    kernel's merge step stores its heads into every GPU's buffer and the next layer's kernel waits for the peers' heads in
+    its prologue (peer stores + arrival counters, no collective, one wait launch after the last layer); NCCL all-gather
+    after every layer.  Per mode: a CUDA graph of the 32 layer calls, device-timed, max over ranks."""
+    from mlx_turboquant_b200 import sharding
+    plan = sharding.plan_lanes(1, HKV, world, rank, split_heads=True)
+    caches, qs = build_caches(torch, dev, 0, (plan.head_begin, plan.head_end))
+    g_heads = HQ // HKV
+    n_kv = plan.head_end - plan.head_begin
+    fused = sharding.FusedGather(1, HQ, D, torch.float16, n_buffers=LAYERS, head_offset=plan.head_begin * g_heads,
+                                 n_local_heads=n_kv * g_heads, n_local_kv_heads=n_kv, device=dev)
+    gathered = [torch.empty(world, 1, n_kv * g_heads, 1, D, dtype=torch.float16, device=dev) for _ in range(LAYERS)]
+    outs = [None] * LAYERS
+
+    def no_gather():
+        for i in range(LAYERS):
+            outs[i] = caches[i].attend(qs[i])
+
+    def fused_gather():
+        for i in range(LAYERS):
+            caches[i].attend(qs[i], gather=fused.slot(i), after=fused.arrived(i - 1) if i else None)
+        fused.wait(LAYERS - 1)
+
+    def nccl_all_gather():
+        for i in range(LAYERS):
+            outs[i] = caches[i].attend(qs[i])
+            dist.all_gather_into_tensor(gathered[i], outs[i])
+
+    def sync():
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    res = {"workload": WORKLOAD + "_one_sequence_kv_heads_split", "kv_heads_per_gpu": n_kv, "layers_per_step": LAYERS,
+           "timing": "CUDA graph of the layer calls, CUDA events, max over ranks"}
+    for name, fn in (("no_gather", no_gather), ("fused_gather", fused_gather), ("nccl_all_gather", nccl_all_gather)):
+        fn()
+        sync()
+        launch = "graph"
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                fn()
+            run = graph.replay
+        except Exception:      # a collective that cannot be captured: launched eagerly
+            launch, run = "eager", fn
+        for _ in range(max(warmup, 3)):
+            run()
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            run()
+        e1.record()
+        sync()
+        ms = sharding.job_time_ms(e0.elapsed_time(e1) / steps, dev)
+        res[name] = {"us_per_layer_step": ms * 1e3 / LAYERS, "launch": launch,
+                     "hbm_gbs_all_gpus": LAYERS * BYTES_PER_LAYER_STEP / (ms * 1e-3) / 1e9}
+    res["fused_gather"]["over_no_gather_us"] = res["fused_gather"]["us_per_layer_step"] - res["no_gather"]["us_per_layer_step"]
+    res["nccl_all_gather"]["over_no_gather_us"] = res["nccl_all_gather"]["us_per_layer_step"] - res["no_gather"]["us_per_layer_step"]
+    # the fused path's result is the same bits as the collective's
+    want = gathered[LAYERS - 1].reshape(1, HQ, D)
+    res["fused_equals_all_gather"] = bool(torch.equal(fused.result(LAYERS - 1), want))
+    from mlx_turboquant_b200 import _lib
+    res["device_status"] = int(_lib.lib().tq_device_status())
+    sync()
+    fused.close()
+    return res
+
+
 def run_c4(args):
     """`--workload c4`: end-to-end batched decoding of a random-init Llama-3.1-8B-shaped model (32 layers, hidden 4096,
     32 query / 8 KV heads, head_dim 128, SwiGLU 14336, vocabulary 128256, bf16 weights N(0, 0.02)) through compressed
     caches (4-bit keys, 2-bit values, 128-token sink, 128 recent tokens).  `--c4-batch` sequences in total, dealt evenly
-    to the GPUs (every GPU holds the full weights; no collective); each sequence starts from a `--c4-prompt`-token
-    context.  The context's cache contents are seeded synthetic K/V fed through `cache.update` in 4096-token pieces
-    (a real prefill of 2 M random tokens would produce K/V of the same kind at a cost that is not what this config
-    measures).  One STEP = one new token for every sequence: embedding, 32 x (projections, RoPE, cache.update,
-    cache.attend, output projection, SwiGLU), logits, greedy pick.  GEMMs and element-wise work are torch library calls;
-    `update` and `attend` are this repository's kernels."""
+    to the GPUs (every GPU holds the full weights; no collective).  Every sequence has a prompt of `--c4-prompt` random
+    token ids, prefilled through the model in `--c4-prefill-chunk`-token pieces (attention of a piece runs straight from
+    packed storage); `--c4-prefill synthetic` instead fills the caches with seeded synthetic K/V of the same kind, for
+    quick runs.  Then `--steps` tokens are generated greedily; one STEP = one new token for every sequence: embedding,
+    32 x (projections, RoPE, cache.decode_step, output projection, SwiGLU), logits, arg-max.  GEMMs and element-wise work
+    are torch library calls replayed from CUDA graphs (consumer.GraphedDecoder); the cache calls are this repository's
+    kernels.  The timed region is the generation; the prefill is timed separately."""
     import torch
     import torch.distributed as dist
 
@@ -356,7 +429,7 @@ def run_c4(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     from mlx_turboquant_b200 import _lib, apply_turboquant, sharding
-    from mlx_turboquant_b200.consumer import LlamaShaped, ModelArgs
+    from mlx_turboquant_b200.consumer import GraphedDecoder, LlamaShaped, ModelArgs
     _lib.lib()
     peak, peak_src = peaks()
     assert args.c4_batch % world == 0
@@ -365,20 +438,43 @@ def run_c4(args):
     model = LlamaShaped(margs, dtype=torch.bfloat16, device=dev, seed=0)
     apply_turboquant(model, key_bits=4, value_bits=2, residual_window=RW, fp16_sink_size=SINK, auto_detect_outliers=False)
     caches = model.make_cache()
-    for li, c in enumerate(caches):
-        g = torch.Generator(device=dev).manual_seed(4000 + 64 * rank + li)
-        for s0 in range(0, prompt, piece):
-            n = min(piece, prompt - s0)
-            kv = []
-            for _ in range(2):
-                x = torch.randn(b, HKV, n, D, device=dev, generator=g, dtype=torch.bfloat16)
-                kv.append(x * torch.exp(0.5 * torch.randn(b, HKV, n, 1, device=dev, generator=g)).to(torch.bfloat16))
-            c.update(kv[0], kv[1])
-        del kv, x
-    tok = torch.randint(0, margs.vocab_size, (b, 1), device=dev, generator=torch.Generator(device=dev).manual_seed(5000 + rank))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    e0.record()
+    if args.c4_prefill == "model":
+        ids = torch.randint(0, margs.vocab_size, (b, prompt), device=dev, generator=torch.Generator(device=dev).manual_seed(4000 + rank))
+        logits = None
+        for s0 in range(0, prompt, args.c4_prefill_chunk):
+            logits = model(ids[:, s0:s0 + args.c4_prefill_chunk], cache=caches, packed=True, last_only=True)
+        tok = logits[:, -1].argmax(-1, keepdim=True)
+        del ids, logits
+    else:
+        for li, c in enumerate(caches):
+            g = torch.Generator(device=dev).manual_seed(4000 + 64 * rank + li)
+            for s0 in range(0, prompt, piece):
+                n = min(piece, prompt - s0)
+                kv = []
+                for _ in range(2):
+                    x = torch.randn(b, HKV, n, D, device=dev, generator=g, dtype=torch.bfloat16)
+                    kv.append(x * torch.exp(0.5 * torch.randn(b, HKV, n, 1, device=dev, generator=g)).to(torch.bfloat16))
+                c.update(kv[0], kv[1])
+            del kv, x
+        tok = torch.randint(0, margs.vocab_size, (b, 1), device=dev, generator=torch.Generator(device=dev).manual_seed(5000 + rank))
+    e1.record()
+    torch.cuda.synchronize(dev)
+    prefill_s = e0.elapsed_time(e1) * 1e-3
+    torch.cuda.empty_cache()
 
-    def step(t):
-        return model(t, cache=caches, packed=True)[:, -1].argmax(-1, keepdim=True)
+    if args.no_graph:
+        class _Eager:
+            tok = None
+
+            def step(self):
+                self.tok = model(self.tok, cache=caches, packed=True)[:, -1].argmax(-1, keepdim=True)
+        dec = _Eager()
+        dec.tok = tok
+    else:
+        dec = GraphedDecoder(model, caches, tok)
 
     def barrier():
         torch.cuda.synchronize(dev)
@@ -387,16 +483,17 @@ def run_c4(args):
             torch.cuda.synchronize(dev)
 
     for _ in range(max(args.warmup, 3)):
-        tok = step(tok)
+        dec.step()
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ctx0 = caches[0].offset
     with ClockSampler(local) as clk:
         e0.record()
         for _ in range(args.steps):
-            tok = step(tok)
+            dec.step()
         e1.record()
         barrier()
     ms_step = sharding.job_time_ms(e0.elapsed_time(e1) / args.steps, dev)
+    prefill_s = sharding.job_time_ms(prefill_s, dev)
 
     # the attention share: the same caches, `attend` alone (one launch per layer)
     c0 = caches[0]
@@ -416,20 +513,26 @@ def run_c4(args):
                   + b * HQ * D * 4)
     attn_gbs = attn_bytes / (attn_us * 1e-6) / 1e9
     weight_bytes = sum(p.numel() * p.element_size() for p in model.parameters()) - model.embed_tokens.weight.numel() * 2
+    floor_ms = (attn_bytes * args.layers + weight_bytes) / (peak * 1e9) * 1e3
     line = {
         "metric": "e2e_decode_tokens_per_s", "value": args.c4_batch * 1e3 / ms_step, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16 weights and activations; attention f32 accumulate over packed 4-bit keys / 2-bit values",
         "data": "synthetic",
         "config": {"workload": "llama31_8b_shaped_batched_decode_k4v2_sink128_rw128", "layers": args.layers, "batch_total": args.c4_batch,
-                   "batch_per_gpu": b, "context_at_start": prompt, "context_at_end": caches[0].offset,
-                   "prompt": "cache contents from seeded synthetic K/V (no prefill pass)", "l2_policy": "inputs larger than L2",
+                   "batch_per_gpu": b, "context_at_start": ctx0, "context_at_end": caches[0].offset,
+                   "prompt": ("random token ids prefilled through the model in %d-token pieces" % args.c4_prefill_chunk) if args.c4_prefill == "model"
+                   else "cache contents from seeded synthetic K/V (no prefill pass)",
+                   "decode_step": "eager" if args.no_graph else "library part replayed from CUDA graphs, cache calls eager",
+                   "l2_policy": "inputs larger than L2",
                    "sharding": "sequences dealt to the GPUs, full weights on each, no collective"},
-        "gpu_launches": 2 * args.layers * args.steps,
+        "gpu_launches": args.layers * args.steps,
         "clocks": clk.summary(),
+        "prefill": {"seconds": prefill_s, "tokens_per_s": args.c4_batch * prompt / prefill_s, "mode": args.c4_prefill},
         "attention": {"us_per_layer_step": attn_us, "algorithmic_bytes_per_launch": attn_bytes, "hbm_gbs": attn_gbs, "frac_of_peak": attn_gbs / peak,
                       "peak": peak, "peak_source": peak_src, "share_of_step": attn_us * args.layers / (ms_step * 1e3)},
-        "hbm_floor_ms_per_step": (attn_bytes * args.layers + weight_bytes) / (peak * 1e9) * 1e3,
+        "hbm_floor_ms_per_step": floor_ms, "step_over_floor": ms_step / floor_ms,
+        "weight_read_floor_ms_per_step": weight_bytes / (peak * 1e9) * 1e3,
         "cache_bytes_per_gpu": sum(c.nbytes for c in caches), "weight_bytes_read_per_step": weight_bytes,
     }
     if rank == 0:
@@ -599,6 +702,9 @@ def run_b200(args):
                              "chunk_tokens": QCHUNK, **bench_quantize(torch, dev, 3, 3, peak, args.quantize_pool)}
         line["secondary"]["compress_qjl_d96_b16"] = bench_quantize_c3(torch, dev, 3, 2, peak)
         line["secondary"]["decode_qjl_d96_b16"] = bench_c3(torch, dev, 5, 3, peak)
+    if world > 1 and not split and not args.no_secondary and HKV % world == 0:
+        hs = bench_head_split(torch, dist, dev, world, rank, args.steps, args.warmup)
+        line["secondary"] = {"head_split": hs}
     if rank == 0 and world == 1 and not args.no_cpu:
         step, info = cpu_reference_step_factory(1)
         step()
@@ -641,6 +747,9 @@ def main():
                     "batched decoding of a Llama-3.1-8B-shaped model through compressed caches (about 75 GB on the device at the defaults)")
     ap.add_argument("--c4-batch", type=int, default=64, help="c4: sequences in total over all GPUs")
     ap.add_argument("--c4-prompt", type=int, default=32768, help="c4: context length every sequence starts from")
+    ap.add_argument("--c4-prefill", default="model", choices=("model", "synthetic"), help="c4: prefill the prompt through the model, "
+                    "or fill the caches with synthetic K/V")
+    ap.add_argument("--c4-prefill-chunk", type=int, default=512, help="c4: prompt tokens per prefill call")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

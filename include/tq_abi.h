@@ -184,6 +184,17 @@ typedef struct {
      * With them the 4-bit-key / 2-bit-value kernel at d = 128 copies its lookup tables and the split rotation matrix
      * instead of rebuilding them in every CTA of every launch; without them those shapes take the general kernel. */
     const void* tables;
+    /* Optional (head-sharded decoding, see tq_peer_gather): before it reads q the kernel waits, bounded like
+     * tq_gather_wait and with the same status on expiry, until the gather of an EARLIER call on this stream (a
+     * different slot than this call's own `gather`) is complete on this GPU: every one of the await_words words of
+     * the landing buffer await_ll carries the epoch await_epochs[0].  It also writes the plain result to await_out
+     * (may be NULL).  This is the consumer side of the exchange folded into the next kernel's prologue: no wait
+     * launch between two decode calls (beyond 8192 words the library enqueues the wait launch itself).  NULL await_ll:
+     * no wait. */
+    const unsigned long long* await_ll;
+    const unsigned int* await_epochs;
+    int64_t await_words;
+    void* await_out;
 } tq_decode_args;
 
 /* Ordering on the stream.  tq_decode_attn is launched with programmatic stream serialisation (unless the "decode_pdl"
@@ -205,18 +216,24 @@ int tq_decode_tables_build(int d, const float* rot, const float* k_cent, int k_b
 
 /* Fused output gather (no reference counterpart; the reference is single-device).  When one sequence's KV heads are
  * dealt to several GPUs of a node (one process per GPU), the consumer usually needs all heads' outputs on every GPU.
- * Instead of a collective after the kernel, the kernel's merge step stores each result element into EVERY peer's
- * output buffer (plain stores through peer-mapped addresses) and then adds 1 to every peer's arrival counter with
- * release semantics at system scope, once per (sequence, KV head, head group) it merged.  The consumer orders
- * tq_gather_wait(counter, target) on its stream before the first kernel that reads the buffer.  Nothing reads peer
- * memory.  out[r] is rank r's buffer (batch, heads_total, d) of out_dtype, as an address valid on THIS device (the
- * caller's own buffer at its own rank); the call's heads land at head index head_offset ... + n_q_heads - 1. */
+ * Instead of a collective after the kernel, the kernel's merge step sends the heads it produced into EVERY peer's
+ * landing buffer through peer-mapped addresses, as 64-bit words {4 bytes of the result, 32-bit epoch} written with one
+ * store each: a word is complete when its epoch is, so no fence, flag or acknowledgement follows the data.  The epoch
+ * is the number of calls made into the slot so far; `epochs` (this GPU's own memory, zero at the start) holds it per
+ * (sequence, KV head, head group) of the call - tq_gather_groups(...) entries.  Every rank makes the same calls with
+ * the same sizes, so a gather is complete on a GPU once every word of its landing buffer carries that GPU's own
+ * epochs[0].  The consumer waits for that either inside the next decode call (await_* in tq_decode_args) or with
+ * tq_gather_wait on its stream; both also unpack the words into a plain (batch, heads_total, d) result.  Nothing reads
+ * peer memory.  ll[r] is rank r's landing buffer, batch * heads_total * d * sizeof(out element) / 4 words, 8-byte
+ * aligned, zero at the start, as an address valid on THIS device (the caller's own buffer at its own rank); the call's
+ * heads land at the place of head index head_offset ... + n_q_heads - 1.  A slot may take its next call only after
+ * every rank has consumed the previous one (use at least two slots in turn). */
 #define TQ_MAX_PEERS 8
 typedef struct tq_peer_gather {
     int n_peers;                                   /* 1 ... TQ_MAX_PEERS */
     int heads_total, head_offset;
-    void* out[TQ_MAX_PEERS];
-    unsigned long long* arrivals[TQ_MAX_PEERS];    /* one 64-bit counter per buffer per rank; only ever incremented */
+    unsigned long long* ll[TQ_MAX_PEERS];
+    unsigned int* epochs;
 } tq_peer_gather;
 
 /* Scratch bytes tq_decode_attn needs for these sizes (host-side arithmetic only). */
@@ -258,18 +275,19 @@ int tq_prefill_attn(const tq_decode_args* a, int t_q, void* stream);
 #define TQ_DECODE_STATIC_SCRATCH_BYTES (8u << 20)
 int tq_decode_attn_static(const tq_decode_args* a, void* stream);
 
-/* How many times one tq_decode_attn call with these sizes increments each peer's arrival counter
- * (= batch * n_kv_heads * head groups; host arithmetic). */
-int64_t tq_gather_arrivals_per_call(int batch, int n_q_heads, int n_kv_heads);
+/* Number of (sequence, KV head, head group) blocks one tq_decode_attn call with these sizes merges = entries of
+ * tq_peer_gather.epochs (host arithmetic). */
+int64_t tq_gather_groups(int batch, int n_q_heads, int n_kv_heads);
 
-/* Enqueues a one-warp kernel that returns once *arrivals has reached its target (an acquire load at system scope in
- * a loop with a back-off, about two seconds at most).  consumed == NULL: the target is `count` (the caller keeps track
- * of how many arrivals all calls so far add up to).  Otherwise the target is *consumed + count and the kernel moves
- * *consumed (a counter in this GPU's memory, zero at the start, touched by nothing else) up to it: the arguments are
- * then the same for every step and the launch can be captured in a CUDA graph.  If the limit is reached the kernel
- * records status 201 for tq_device_status() and returns; the stream continues and the buffer's contents are not to
- * be trusted. */
-int tq_gather_wait(const unsigned long long* arrivals, unsigned long long* consumed, unsigned long long count, void* stream);
+/* Enqueues a small kernel that returns once every one of the n_words words of the landing buffer `ll` carries the
+ * epoch epochs[0] - `epochs` being the tq_peer_gather array of this GPU, final by then because the producing call is
+ * earlier on the stream - and writes the 4-byte payloads to `out` (the plain result; may be NULL).  Relaxed loads at
+ * system scope in a loop with a back-off, about two seconds at most per word; if the limit is reached the kernel
+ * records status 201 for tq_device_status() and returns; the stream continues and the result is not to be trusted.
+ * The arguments are the same for every step, so the launch can be captured in a CUDA graph.  For consumers that are
+ * not this library's kernels; between two decode calls the await_* fields of tq_decode_args do the same without a
+ * launch. */
+int tq_gather_wait(const unsigned long long* ll, const unsigned int* epochs, int64_t n_words, void* out, void* stream);
 
 /* Device buffers that other processes on the node can map (CUDA IPC), for the outputs and counters above.
  * create: cudaMalloc + zero fill on the current device, returns the address and a 64-byte handle to pass to the peers
@@ -288,7 +306,7 @@ float tq_fp16_table_scale(const float* centroids_host, int n);
 /* Host-side tuning knobs of the split heuristic (process-wide; no reference counterpart):
  *   "decode_ctas_per_sm" 1..8, "decode_splits" 0 (auto)..448, "decode_force_general" 0/1,
  *   "decode_pdl" 0/1 (programmatic dependent launch: a call's prologue overlaps the previous kernel's tail),
- *   "gather_wait_polls" 1000..4000000 (polls of tq_gather_wait before it gives up; default 2000000, some two seconds).
+ *   "gather_wait_polls" 1000..4000000 (polls of one word of a gather before the wait gives up; default 2000000, some two seconds).
  * Changing them changes tq_decode_workspace_bytes for the same sizes. */
 int tq_set_tuning(const char* key, int value);
 

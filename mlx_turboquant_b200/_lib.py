@@ -47,10 +47,10 @@ TQ_MAX_PEERS = 8
 
 
 class PeerGather(C.Structure):
-    """tq_peer_gather: every rank's output buffer and arrival counter, as addresses valid on this device."""
+    """tq_peer_gather: every rank's landing buffer as addresses valid on this device, and this rank's epoch array."""
     _fields_ = [
         ("n_peers", _i), ("heads_total", _i), ("head_offset", _i),
-        ("out", _vp * TQ_MAX_PEERS), ("arrivals", _vp * TQ_MAX_PEERS),
+        ("ll", _vp * TQ_MAX_PEERS), ("epochs", _vp),
     ]
 
 
@@ -72,6 +72,7 @@ class DecodeArgs(C.Structure):
         ("workspace", _vp), ("workspace_bytes", _sz),
         ("gather", C.POINTER(PeerGather)),
         ("tables", _vp),
+        ("await_ll", _vp), ("await_epochs", _vp), ("await_words", _i64), ("await_out", _vp),
     ]
 
 
@@ -102,8 +103,8 @@ PROTOTYPES = {
     "tq_fp16_table_scale": (_f, [_vp, _i]),
     "tq_device_status": (_i, []),
     "tq_device_status_clear": (_i, []),
-    "tq_gather_arrivals_per_call": (_i64, [_i, _i, _i]),
-    "tq_gather_wait": (_i, [_vp, _vp, C.c_ulonglong, _vp]),
+    "tq_gather_groups": (_i64, [_i, _i, _i]),
+    "tq_gather_wait": (_i, [_vp, _vp, _i64, _vp, _vp]),
     "tq_peer_buffer_create": (_i, [_sz, C.POINTER(_vp), C.c_char_p]),
     "tq_peer_buffer_open": (_i, [C.c_char_p, _i, C.POINTER(_vp)]),
     "tq_peer_buffer_close": (_i, [_vp]),

@@ -454,7 +454,7 @@ class TurboQuantKVCache:
 
     # ---- attention on the packed cache -----------------------------------------------------------
     def attend(self, queries: torch.Tensor, scale: float | None = None, out_dtype=None, gather=None,
-               out: torch.Tensor | None = None, _new=None) -> torch.Tensor | None:
+               out: torch.Tensor | None = None, _new=None, after=None) -> torch.Tensor | None:
         """softmax(scale * q K^T) V straight from packed storage.
 
         ``queries`` is (B, n_q_heads, 1, D) or (B, n_q_heads, D) for a decode step, or (B, n_q_heads, T_q, D) for the last
@@ -463,14 +463,15 @@ class TurboQuantKVCache:
         would return (to ~1e-3 with a float32 result; a float16 result adds its own rounding), without
         building it.  With ``gather`` (a slot of ``sharding.FusedGather``: this rank holds some of the heads) the
         kernel stores the result into every rank's gather buffer instead and nothing is returned.  ``out`` (contiguous,
-        ``queries``' shape) receives the result in place of a fresh tensor.
+        ``queries``' shape) receives the result in place of a fresh tensor.  ``after`` (``FusedGather.arrived(j)`` of an
+        earlier call's slot) makes the kernel wait, before it reads the queries, until that gather is complete on this GPU.
         """
         dev = _lib.require_cuda(queries)
         self._bind(dev)
         d = self.head_dim
         squeeze = queries.dim() == 3
         if not squeeze and queries.shape[2] != 1:
-            if gather is not None or _new is not None:
+            if gather is not None or _new is not None or after is not None:
                 raise NotImplementedError("several query tokens per sequence: no fused gather, no fused append")
             return self._attend_many(queries, scale, out_dtype, out)
         b, hq = queries.shape[0], queries.shape[1]
@@ -505,6 +506,7 @@ class TurboQuantKVCache:
             self._dargs, self._dargs_key, self._ws_key = a, key, None
         a.q, a.out = q.data_ptr(), (None if out is None else out.data_ptr())
         a.gather = C.pointer(gather) if gather is not None else None
+        a.await_ll, a.await_epochs, a.await_words, a.await_out = after if after is not None else (None, None, 0, None)
         a.c_len, a.sink_len, a.res_len = self._compressed_len, self._sink_len, self._fp16_len
         dense_len = self._sink_len + self._fp16_len + (0 if _new is None else 1)
         ws_key = (self._compressed_len, (dense_len + 15) >> 4)        # the split plan depends on whole 16-token tiles only

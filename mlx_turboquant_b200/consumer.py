@@ -8,8 +8,11 @@ attention, SwiGLU, tied to nothing but ``torch`` library calls (GEMMs and the de
 library work, not part of the compressed path).  Two ways through the cache:
 
 * dense (the reference's only way): ``keys, values = cache.update_and_fetch(k, v)`` then softmax attention;
-* packed: for one new token per sequence, ``cache.update(k, v)`` then ``cache.attend(q)`` - attention straight
-  from packed storage.  Multi-token calls (prefill) always take the dense way.
+* packed: attention straight from packed storage - ``cache.decode_step(q, k, v)`` for one new token per sequence
+  (append and attention in one launch), ``cache.update(k, v)`` then the causal ``cache.attend(q)`` for a prefill
+  chunk.  Caches with a QJL sketch take the dense way for multi-token calls.
+
+``GraphedDecoder`` replays the library part of a decode step (everything between two cache calls) as CUDA graphs.
 
 ``generate`` is the greedy loop of the reference's command line (cli.py:81-104) without its tokenizer.
 """
@@ -179,3 +182,106 @@ def generate(model: LlamaShaped, prompt: torch.Tensor, max_new_tokens: int, cach
         if i + 1 < max_new_tokens:
             tok = model(tok, cache=cache, packed=packed, last_only=True)[:, -1].argmax(-1, keepdim=True)
     return torch.cat(out, dim=1)
+
+
+class GraphedDecoder:
+    """Greedy one-token-per-sequence decoding with the torch part of the step replayed from CUDA graphs.
+
+    A decode step is 32 cache calls with library work in between.  The cache calls stay eager: their launch parameters
+    (lengths, split plan, which buffer a token joins, whether a chunk is due for compression) are host-side state that
+    changes from step to step.  Everything between two of them - output projection, SwiGLU, the next layer's norm,
+    projections and RoPE; embedding before the first, logits and arg-max after the last - has fixed shapes and reads its
+    position from a device tensor, so each such piece is captured once and replayed: per step ``layers + 1`` graph
+    launches and ``layers`` cache calls instead of some twenty eager launches per layer.  Same arithmetic, same order, as
+    ``model(tok, cache=caches, packed=True)``.
+    """
+
+    def __init__(self, model: LlamaShaped, caches: list, first_tokens: torch.Tensor):
+        a = model.args
+        self.model, self.caches = model, caches
+        dev, dt = first_tokens.device, model.lm_head.weight.dtype
+        B = first_tokens.shape[0]
+        hq, hkv, d = a.num_attention_heads, a.num_key_value_heads, a.head_dim
+        self.tok = first_tokens.clone().reshape(B, 1)
+        self.pos = torch.full((1,), float(caches[0].offset), dtype=torch.float32, device=dev)
+        self.h = torch.empty(B, 1, a.hidden_size, dtype=dt, device=dev)
+        self.q = torch.empty(B, hq, 1, d, dtype=dt, device=dev)
+        self.k = torch.empty(B, hkv, 1, d, dtype=dt, device=dev)
+        self.v = torch.empty(B, hkv, 1, d, dtype=dt, device=dev)
+        self.attn = torch.zeros(B, hq, 1, d, dtype=dt, device=dev)
+        half = d // 2
+        self._inv = a.rope_theta ** (-torch.arange(0, half, device=dev, dtype=torch.float32) / half)
+        n = len(model.layers)
+        pieces = [self._piece(i) for i in range(n + 1)]
+        # warm up on a side stream (library handles, autotuning), then capture each piece
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        saved = (self.tok.clone(), self.pos.clone())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                for f in pieces:
+                    f()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self.graphs = []
+        pool = None
+        for f in pieces:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=pool):
+                f()
+            pool = pool or g.pool()
+            self.graphs.append(g)
+        self.tok.copy_(saved[0])
+        self.pos.copy_(saved[1])
+
+    def _pre_attention(self, i: int, h: torch.Tensor) -> None:
+        m, a = self.model, self.model.args
+        att = m.layers[i].self_attn
+        hq, hkv, d = att.n_heads, att.n_kv_heads, att.head_dim
+        B = h.shape[0]
+        qkv = att.qkv_proj(_rms_norm(h, m.layers[i].input_layernorm, a.rms_norm_eps)).view(B, 1, hq + 2 * hkv, d).transpose(1, 2)
+        ang = self.pos[:, None] * self._inv[None, :]                                  # (1, d/2): this step's position
+        cos, sin = ang.cos(), ang.sin()
+        qk = apply_rope(qkv[:, :hq + hkv], (torch.cat([cos, cos], dim=-1), torch.cat([-sin, sin], dim=-1)))
+        self.q.copy_(qk[:, :hq])
+        self.k.copy_(qk[:, hq:])
+        self.v.copy_(qkv[:, hq + hkv:])
+
+    def _post_attention(self, i: int) -> torch.Tensor:
+        m, a = self.model, self.model.args
+        layer = m.layers[i]
+        B = self.attn.shape[0]
+        h = self.h + layer.self_attn.o_proj(self.attn.transpose(1, 2).reshape(B, 1, -1))
+        gate, up = layer.gate_up_proj(_rms_norm(h, layer.post_attention_layernorm, a.rms_norm_eps)).chunk(2, dim=-1)
+        return h + layer.down_proj(F.silu(gate) * up)
+
+    def _piece(self, i: int):
+        m, n = self.model, len(self.model.layers)
+
+        def first():
+            h = m.embed_tokens(self.tok)
+            self.h.copy_(h)
+            self._pre_attention(0, h)
+
+        def middle():
+            h = self._post_attention(i - 1)
+            self.h.copy_(h)
+            self._pre_attention(i, h)
+
+        def last():
+            h = self._post_attention(n - 1)
+            logits = m.lm_head(_rms_norm(h, m.norm, m.args.rms_norm_eps))
+            self.tok.copy_(logits[:, -1].argmax(-1, keepdim=True))
+            self.pos.add_(1.0)
+
+        return first if i == 0 else last if i == n else middle
+
+    @torch.no_grad()
+    def step(self) -> torch.Tensor:
+        """Feeds ``self.tok`` (B, 1) through the model and the caches and leaves the next greedy token there (returned too;
+        the same tensor every step - clone it to keep it)."""
+        scale = self.model.layers[0].self_attn.scale
+        for i, c in enumerate(self.caches):
+            self.graphs[i].replay()
+            c.decode_step(self.q, self.k, self.v, scale, out=self.attn)
+        self.graphs[-1].replay()
+        return self.tok

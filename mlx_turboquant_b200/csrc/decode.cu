@@ -119,6 +119,7 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
         }
     }
     pdl_wait();        // from here on: the query, the cache and the workspace of the previous launch are settled
+    await_gather(p);   // (head-sharded decoding) ... and the peers' heads of an earlier call have arrived
 
     // ---------------- the query heads of this group: float32, then (rotated) scaled fp16 --------------------
     // q_rot[h][j] = sum_k q[h][k] R[j][k]  (rotation.py:81-110)
@@ -569,16 +570,24 @@ __global__ void __launch_bounds__(GNW * 32, D <= 128 ? 2 : 1) decode_attn_kernel
             L = fmaf(w, x.y, L);
             acc = fmaf(w, __ldcg(src + sidx * stride), acc);
         }
-        // fused gather: the group's first head in the peers' (batch, heads_total, d) buffers
-        const int64_t gbase = (int64_t(blockIdx.z) * p.heads_total + p.head_offset + int64_t(blockIdx.y / p.HG) * p.G + (blockIdx.y % p.HG) * HPG) * D;
-        store_result(p, qbase + e, gbase + e, acc / L);
+        // fused gather: staged in the result's element type where the float32 query sat, sent below
+        if (p.n_peers > 0) store_from_f32(qf, p.out_dtype, e, acc / L);
+        else store_from_f32(p.out, p.out_dtype, qbase + e, acc / L);
     }
-    signal_peers(p);
+    if (p.n_peers > 0) {
+        const unsigned epoch = next_epoch(p, int(grp));
+        __syncthreads();
+        // the group's first head in the peers' (batch, heads_total, d) buffers
+        const int64_t gbase = (int64_t(blockIdx.z) * p.heads_total + p.head_offset + int64_t(blockIdx.y / p.HG) * p.G + (blockIdx.y % p.HG) * HPG) * D;
+        const int es = out_elem_bytes(p.out_dtype);
+        publish_result(p, qf, heads_here * D * es, gbase * es, int(grp), epoch);
+    }
 }
 
 // ---- host side ------------------------------------------------------------------------------------
 static int g_tune_ctas_per_sm = 2;     // CTAs of the general path resident per SM at d <= 128 (split heuristic)
-static int g_tune_wait_polls = 2000000;  // polls of tq_gather_wait before it gives up (about 1.2 us each: some two seconds)
+static int g_tune_wait_polls = 2000000;  // polls of a word of a gather before the wait gives up (about a microsecond each: some two seconds)
+constexpr int64_t MAX_AWAIT_WORDS_IN_KERNEL = 8192;
 static int g_tune_force_general = 0;   // 1: never take the direct path (testing)
 static int g_tune_splits = 0;          // > 0: fixed number of packed splits
 static int g_tune_pdl = 1;             // programmatic dependent launch between consecutive calls
@@ -765,10 +774,18 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
             return fail(TQ_ERR_INVALID, "tq_decode_attn: gather: n_peers %d, heads %d + %d of %d", gth->n_peers, gth->head_offset, a->n_q_heads,
                         gth->heads_total);
         for (int r = 0; r < gth->n_peers; ++r)
-            if (!gth->out[r] || !gth->arrivals[r] || !aligned(gth->arrivals[r], 8))
-                return fail(TQ_ERR_INVALID, "tq_decode_attn: gather: null or misaligned buffer of peer %d", r);
+            if (!gth->ll[r] || !aligned(gth->ll[r], 8)) return fail(TQ_ERR_INVALID, "tq_decode_attn: gather: null or misaligned landing buffer of peer %d", r);
+        if (!gth->epochs || !aligned(gth->epochs, 4)) return fail(TQ_ERR_INVALID, "tq_decode_attn: gather: null or misaligned epoch array");
         p.n_peers = gth->n_peers; p.heads_total = gth->heads_total; p.head_offset = gth->head_offset;
-        for (int r = 0; r < gth->n_peers; ++r) { p.peer_out[r] = gth->out[r]; p.peer_arrivals[r] = gth->arrivals[r]; }
+        for (int r = 0; r < gth->n_peers; ++r) p.peer_ll[r] = gth->ll[r];
+        p.epochs = gth->epochs;
+    }
+    if (a->await_ll) {
+        if (!a->await_epochs || !aligned(a->await_ll, 8) || !aligned(a->await_epochs, 4) || !aligned(a->await_out, 4) || a->await_words < 1)
+            return fail(TQ_ERR_INVALID, "tq_decode_attn: await: null or misaligned buffers, or no words");
+        p.await_ll = a->await_ll; p.await_epochs = a->await_epochs; p.await_words = a->await_words; p.await_out = a->await_out;
+        p.await_polls = g_tune_wait_polls;
+        if (!(p.status = decode_status_ptr())) return fail(TQ_ERR_LAUNCH, "tq_decode_attn: cannot locate the status word");
     }
     p.pdl = g_tune_pdl;
     p.words_ok = (a->c_len > 0 && aligned(a->k_hi, 4) && aligned(a->v_hi, 4)) ? 1 : 0;   // packed rows readable as 32-bit words
@@ -778,7 +795,12 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
     return TQ_OK;
 }
 
-int decode_launch(const DecodeParams& p, bool direct, cudaStream_t s) {
+int decode_launch(const DecodeParams& p0, bool direct, cudaStream_t s) {
+    DecodeParams p = p0;
+    if (p.await_ll && p.await_words > MAX_AWAIT_WORDS_IN_KERNEL) {      // too many words for every CTA to poll: a wait launch first
+        if (int rc = launch_gather_wait(p.await_ll, p.await_epochs, p.await_words, p.await_out, p.await_polls, s)) return rc;
+        p.await_ll = nullptr;
+    }
     if (direct) return launch_decode_direct(p, s);
     const bool qjl = p.qjl_proj != nullptr;
     if (p.D == 64) return qjl ? launch_decode<64, true>(p, s) : launch_decode<64, false>(p, s);
@@ -803,12 +825,13 @@ extern "C" int tq_set_tuning(const char* key, int value) {
     return TQ_OK;
 }
 
-extern "C" int tq_gather_wait(const unsigned long long* arrivals, unsigned long long* consumed, unsigned long long count, void* stream) {
-    if (!arrivals || !aligned(arrivals, 8) || !aligned(consumed, 8)) return fail(TQ_ERR_INVALID, "tq_gather_wait: null or misaligned counter");
-    return launch_gather_wait(arrivals, consumed, count, g_tune_wait_polls, static_cast<cudaStream_t>(stream));
+extern "C" int tq_gather_wait(const unsigned long long* ll, const unsigned* epochs, int64_t n_words, void* out, void* stream) {
+    if (!ll || !epochs || !aligned(ll, 8) || !aligned(epochs, 4) || !aligned(out, 4) || n_words < 1)
+        return fail(TQ_ERR_INVALID, "tq_gather_wait: null or misaligned buffers, or no words");
+    return launch_gather_wait(ll, epochs, n_words, out, g_tune_wait_polls, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int64_t tq_gather_arrivals_per_call(int batch, int n_q_heads, int n_kv_heads) {
+extern "C" int64_t tq_gather_groups(int batch, int n_q_heads, int n_kv_heads) {
     if (batch <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads) return 0;
     const int G = n_q_heads / n_kv_heads;
     return int64_t(batch) * n_kv_heads * ((G + HPG - 1) / HPG);     // one merging CTA per (sequence, KV head, head group)

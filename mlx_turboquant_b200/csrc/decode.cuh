@@ -37,11 +37,19 @@ struct DecodeParams {
     int pdl;                           // launch with programmatic stream serialisation
     int words_ok;                      // packed key / value rows start on 4-byte boundaries
     const void* tables;                // prebuilt constants of the direct kernel (decode_direct.cu: DirectTables), or null
-    // fused gather (n_peers > 0): results go to every peer's buffer at head index head_offset + local head, then
-    // every peer's arrival counter is incremented once per merging CTA
+    // fused gather (n_peers > 0): the merging CTAs send their heads, as {payload, epoch} words, into every peer's landing
+    // buffer at the place of head index head_offset + local head
     int n_peers, heads_total, head_offset;
-    void* peer_out[TQ_MAX_PEERS];
-    unsigned long long* peer_arrivals[TQ_MAX_PEERS];
+    unsigned long long* peer_ll[TQ_MAX_PEERS];
+    unsigned* epochs;                  // this GPU's call counts per (sequence, KV head, head group) of the slot
+    // wait for an earlier call's gather before the query is read (or null): every word of the landing buffer carries
+    // the epoch of that call; the first CTA also unpacks it into await_out
+    const unsigned long long* await_ll;
+    const unsigned* await_epochs;
+    int64_t await_words;
+    void* await_out;
+    int await_polls;
+    int* status;                       // the device's status word (first bounded wait that ran out)
 };
 
 // Validates the arguments, picks the path and the split plan and fills the kernel parameters for the given
@@ -56,7 +64,8 @@ bool direct_supported();
 size_t direct_tables_bytes();
 int direct_tables_build(const float* rot, const float* k_cent, const float* v_cent, float v_scale, void* tables, cudaStream_t s);
 int launch_decode_direct(const DecodeParams& p, cudaStream_t s);
-int launch_gather_wait(const unsigned long long* arrivals, unsigned long long* consumed, unsigned long long count, int max_polls, cudaStream_t s);
+int launch_gather_wait(const unsigned long long* ll, const unsigned* epochs, int64_t n_words, void* out, int max_polls, cudaStream_t s);
+int* decode_status_ptr();          // device address of the status word on the current device (null on error)
 int decode_status_host();          // code of the first bounded wait that ran out on this device (0 = none), -1 on error
 
 }  // namespace tq

@@ -73,24 +73,58 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
 // ---- per-warp running softmax state ------------------------------------------------------------------
 constexpr float MAX_SLACK = 6.f;   // scores may exceed the running reference by 2^6 before it is refreshed
 // ---- result stores ---------------------------------------------------------------------------------
-// One element of the result: into the caller's buffer, or (fused gather) into the same place of every peer's buffer.
-// `gather_head` is the global index of the group's first head: sequence * heads_total + head_offset + local head.
-__device__ __forceinline__ void store_result(const DecodeParams& p, int64_t local_idx, int64_t gather_idx, float v) {
-    if (p.n_peers == 0) {
-        store_from_f32(p.out, p.out_dtype, local_idx, v);
-        return;
+// Fused gather, producer side.  The merging CTA first stages its heads in shared memory in the result's element type
+// (`stage`, 4-byte aligned, `bytes` = heads * D * element size) and passes a barrier; then every thread calls this.
+// Each 4 bytes of the block travel as one 64-bit word {payload, epoch} written with a single store into every peer's
+// landing buffer: a word is complete when its epoch is, so no fence and no separate flag follow the data and nothing
+// waits for the stores to be acknowledged.  `byte_off` is where the group's first head sits in a (batch, heads_total, d)
+// result; `epoch` is this (slot, group)'s call count including this call (the caller read epochs[grp] + 1 before the
+// barrier), stored back for the next call.
+__device__ __forceinline__ void publish_result(const DecodeParams& p, const void* stage, int bytes, int64_t byte_off, int grp, unsigned epoch) {
+    const int n_words = bytes >> 2;
+    const uint32_t* src = static_cast<const uint32_t*>(stage);
+    const int64_t w0 = byte_off >> 2;
+    for (int i = threadIdx.x; i < n_words * p.n_peers; i += blockDim.x) {
+        const int r = i / n_words, w = i - r * n_words;
+        const unsigned long long v = static_cast<unsigned long long>(src[w]) | (static_cast<unsigned long long>(epoch) << 32);
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p.peer_ll[r] + w0 + w), "l"(v) : "memory");
     }
-    for (int r = 0; r < p.n_peers; ++r) store_from_f32(p.peer_out[r], p.out_dtype, gather_idx, v);
+    if (threadIdx.x == 0) p.epochs[grp] = epoch;
 }
-// After the result stores of a merging CTA; every thread of the CTA calls it.  The barrier orders all threads' stores
-// before thread 0's fence at system scope (cumulative), which orders them before the counter increments the peers poll.
-__device__ __forceinline__ void signal_peers(const DecodeParams& p) {
-    if (p.n_peers == 0) return;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence_system();
-        for (int r = 0; r < p.n_peers; ++r) atomicAdd_system(p.peer_arrivals[r], 1ULL);
+__device__ __forceinline__ int out_elem_bytes(int dtype) { return dtype == TQ_F32 ? 4 : 2; }
+__device__ __forceinline__ unsigned next_epoch(const DecodeParams& p, int grp) {
+    return p.n_peers > 0 ? *reinterpret_cast<const volatile unsigned*>(p.epochs + grp) + 1u : 0u;
+}
+
+// Fused gather, consumer side: polls the words of this GPU's landing buffer until each carries `epoch` (bounded: a
+// thread that runs out of polls gives up on its remaining words too) and, if `out` is given, writes the payloads there
+// as the plain (batch, heads_total, d) result.  Returns false if a word never arrived.
+__device__ __forceinline__ bool collect_words(const unsigned long long* ll, int64_t first, int64_t n_words, int64_t stride, unsigned epoch,
+                                              uint32_t* out, int max_polls) {
+    for (int64_t w = first; w < n_words; w += stride) {
+        unsigned long long v;
+        int it = 0;
+        for (;;) {
+            asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(ll + w) : "memory");
+            if (static_cast<unsigned>(v >> 32) == epoch) break;
+            if (++it >= max_polls) return false;
+            if (it > 64) __nanosleep(500);
+        }
+        if (out) out[w] = static_cast<uint32_t>(v);
     }
+    return true;
+}
+// ... inside the kernel that follows on the stream: every thread calls it after griddepcontrol.wait (the producing call
+// of this GPU is complete by then, so its epoch is final; every rank makes the same calls, so it is the peers' epoch
+// too).  Every CTA checks every word - the whole result has to be in before any of the query may be believed - and
+// the first CTA also writes the plain copy.
+__device__ __forceinline__ void await_gather(const DecodeParams& p) {
+    if (p.await_ll == nullptr) return;
+    const unsigned epoch = *reinterpret_cast<const volatile unsigned*>(p.await_epochs);
+    const bool first_cta = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    if (!collect_words(p.await_ll, threadIdx.x, p.await_words, blockDim.x, epoch, first_cta ? static_cast<uint32_t*>(p.await_out) : nullptr, p.await_polls))
+        atomicCAS(p.status, 0, 201);
+    __syncthreads();
 }
 
 // NZ: extra accumulator tiles that share the softmax weights (the QJL sketch rows of the output).

@@ -293,6 +293,8 @@ __global__ void __launch_bounds__(NT, 1) decode_direct_kernel(DecodeParams p) {
     }
     DD_STAMP(1);
     pdl_wait();        // from here on: the query, the cache and the workspace of the previous launch are settled
+    DD_STAMP(11);
+    await_gather(p);   // (head-sharded decoding) ... and the peers' heads of an earlier call have arrived
     DD_STAMP(2);
     const float inv_vs = 1.f / tb_scale;
     if (tb_magic != TABLES_MAGIC) {                      // not a buffer tq_decode_tables_build filled
@@ -633,30 +635,32 @@ __global__ void __launch_bounds__(NT, 1) decode_direct_kernel(DecodeParams p) {
             float v = s_ad[e];
 #pragma unroll
             for (int x = 0; x < NW; ++x) v += s_pp[(x * HPG + h) * D + j];
-            // fused gather: the group's first head in the peers' (batch, heads_total, d) buffers
-            const int64_t gbase = (int64_t(blockIdx.z) * p.heads_total + p.head_offset + int64_t(blockIdx.y / p.HG) * p.G + (blockIdx.y % p.HG) * HPG) * D;
-            store_result(p, qbase + e, gbase + e, v * s_il[h]);
+            // fused gather: staged in the result's element type (the rotated sums are no longer needed), sent below
+            if (p.n_peers > 0) store_from_f32(s_acc, p.out_dtype, e, v * s_il[h]);
+            else store_from_f32(p.out, p.out_dtype, qbase + e, v * s_il[h]);
         }
     }
-    signal_peers(p);
+    if (p.n_peers > 0) {
+        const int grp = int((int64_t(blockIdx.z) * p.Hkv + blockIdx.y / p.HG) * p.HG + blockIdx.y % p.HG);
+        const unsigned epoch = next_epoch(p, grp);
+        __syncthreads();
+        // the group's first head in the peers' (batch, heads_total, d) buffers
+        const int64_t gbase = (int64_t(blockIdx.z) * p.heads_total + p.head_offset + int64_t(blockIdx.y / p.HG) * p.G + (blockIdx.y % p.HG) * HPG) * D;
+        const int es = out_elem_bytes(p.out_dtype);
+        DD_STAMP(9);
+        publish_result(p, s_acc, heads_here * D * es, gbase * es, grp, epoch);
+    }
     DD_STAMP(6);
 }
 
-// Consumer side of the fused gather: returns once the arrival counter (written by the peers' merge steps) has reached
-// its target: `count` itself, or, with a `consumed` counter, *consumed + count, after which *consumed moves up by count
-// (the launch parameters then never change, so the launch can sit in a CUDA graph).  Both counters live in this GPU's
-// own memory; the poll is bounded (about two seconds), then a status is left.
-__global__ void gather_wait_kernel(const unsigned long long* arrivals, unsigned long long* consumed, unsigned long long count, int max_polls) {
-    if (threadIdx.x != 0) return;
-    const unsigned long long target = consumed ? *consumed + count : count;
-    if (consumed) *consumed = target;                       // also after a time-out: later waits keep their meaning
-    for (int it = 0; it < max_polls; ++it) {
-        unsigned long long v;
-        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(arrivals) : "memory");
-        if (v >= target) return;
-        __nanosleep(it < 64 ? 32 : 512);
-    }
-    atomicCAS(&g_status, 0, ERR_GATHER_WAIT);
+// Consumer side of the fused gather as a launch of its own (for consumers that are not one of this library's kernels):
+// returns once every word of this GPU's landing buffer carries the epoch of the latest call this GPU made into the slot
+// (the producing launch is earlier on the stream, so the count is final) and writes the plain result.  The poll is bounded
+// (about two seconds), then a status is left.
+__global__ void __launch_bounds__(256) gather_wait_kernel(const unsigned long long* ll, const unsigned* epochs, int64_t n_words, uint32_t* out, int max_polls) {
+    const unsigned epoch = *reinterpret_cast<const volatile unsigned*>(epochs);
+    if (!collect_words(ll, int64_t(blockIdx.x) * blockDim.x + threadIdx.x, n_words, int64_t(gridDim.x) * blockDim.x, epoch, out, max_polls))
+        atomicCAS(&g_status, 0, ERR_GATHER_WAIT);
 }
 
 static unsigned probe_smem_base() {
@@ -732,8 +736,23 @@ int launch_decode_direct(const DecodeParams& p, cudaStream_t s) {
     return p.slots <= 4 ? launch_nh<4>(p, s) : launch_nh<8>(p, s);
 }
 
-int launch_gather_wait(const unsigned long long* arrivals, unsigned long long* consumed, unsigned long long count, int max_polls, cudaStream_t s) {
-    dd::gather_wait_kernel<<<1, 32, 0, s>>>(arrivals, consumed, count, max_polls);
+int* decode_status_ptr() {
+    static std::atomic<int*> cache[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    int* v = cache[dev].load(std::memory_order_acquire);
+    if (!v) {
+        void* a = nullptr;
+        if (cudaGetSymbolAddress(&a, dd::g_status) != cudaSuccess) return nullptr;
+        v = static_cast<int*>(a);
+        cache[dev].store(v, std::memory_order_release);
+    }
+    return v;
+}
+
+int launch_gather_wait(const unsigned long long* ll, const unsigned* epochs, int64_t n_words, void* out, int max_polls, cudaStream_t s) {
+    const int64_t blocks = std::min<int64_t>((n_words + 255) / 256, 64);
+    dd::gather_wait_kernel<<<unsigned(blocks), 256, 0, s>>>(ll, epochs, n_words, static_cast<uint32_t*>(out), max_polls);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_gather_wait: %s", cudaGetErrorString(e));
     return TQ_OK;

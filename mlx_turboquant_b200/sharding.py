@@ -12,8 +12,8 @@ with no data-path collective.  Two plans:
   gathered once per step (``gather_heads``), the only collective on the path.
 
   ``FusedGather`` is the same exchange without a collective: the decode kernel's merge step stores each
-  rank's heads straight into every rank's output buffer (peer-mapped device memory, plain stores) and bumps an
-  arrival counter the consumer waits on.
+  rank's heads straight into every rank's landing buffer (peer-mapped device memory, plain 64-bit stores that carry
+  their own arrival mark), and the next kernel on the consumer's stream collects them.
 
 ``job_time_ms`` is the barrier-free max over ranks that multi-GPU timings must use.
 """
@@ -121,19 +121,20 @@ class SlotLedger:
 
 
 class FusedGather:
-    """Every rank's output buffers and arrival counters, mapped into every rank (ranks = GPUs of one node).
+    """Every rank's landing buffers, mapped into every rank (ranks = GPUs of one node).
 
-    ``n_buffers`` independent slots (one per layer in flight is the usual choice), each a full-size result
-    ``(batch, heads_total, d)`` of ``dtype`` plus one 64-bit arrival counter.  A decode call given ``slot(i)`` writes
-    its heads into slot ``i`` of every rank; ``wait(i)`` then orders the current stream behind the arrival of all
-    ranks' heads in the local copy, after which ``result(i)`` is complete.  Counters only grow; a second, local counter
-    per slot remembers how many arrivals earlier waits consumed, so both launches take the same arguments every step and
-    a step can be captured in a CUDA graph.  Every rank must make the same calls on the same slots, one ``wait(i)`` per
-    decode call on slot ``i``.
+    ``n_buffers`` independent slots (one per layer in flight is the usual choice).  A slot is a landing buffer of 64-bit
+    words {4 bytes of the result, 32-bit epoch} that every rank's merge steps write into, this rank's epoch array (how many
+    calls it has made into the slot) and a plain result ``(batch, heads_total, d)`` of ``dtype``.  A decode call given
+    ``slot(i)`` sends its heads into slot ``i`` of every rank; the gather is complete on this rank once every word of its
+    landing buffer carries this rank's own epoch (every rank makes the same calls with the same sizes).  The consumer
+    waits for that, and unpacks the words into ``result(i)``, inside the next decode call -
+    ``attend(..., after=arrived(i))``, no launch in between - or with ``wait(i)``, a small kernel on the current stream,
+    before a reader that is not one of this package's kernels.  Epochs are kept on the device, so every launch takes the
+    same arguments every step and a step can be captured in a CUDA graph.
 
-    A slot may be rewritten by a peer as soon as that peer has passed its own ``wait`` on a LATER call that this rank
-    issues after reading the slot, which holds when a rank reads ``result(i)`` before it launches its next decode
-    call (stream order) and slots are reused no sooner than every other call.
+    A slot may take its next call only when every rank has collected the previous one, which holds when slots are used
+    in turn (no slot twice in a row) and every call waits for its predecessor's gather.
     """
 
     def __init__(self, batch: int, heads_total: int, d: int, dtype: torch.dtype, n_buffers: int, head_offset: int,
@@ -145,23 +146,35 @@ class FusedGather:
             raise ValueError(f"at most {_lib.TQ_MAX_PEERS} ranks")
         self._ledger = SlotLedger(self.world, n_buffers)
         self.shape, self.dtype, self.n_buffers, self.device = (batch, heads_total, d), dtype, n_buffers, device
-        elem = _TYPESTR[dtype][1]
-        self._slot_bytes = (batch * heads_total * d * elem + 255) // 256 * 256
-        self._ctr_off = n_buffers * self._slot_bytes
-        self._used_off = self._ctr_off + (n_buffers * 8 + 255) // 256 * 256          # local "consumed" counters
-        total = self._used_off + (n_buffers * 8 + 255) // 256 * 256
         lib = _lib.lib()
+        elem = _TYPESTR[dtype][1]
+        self._words = batch * heads_total * d * elem // 4
+        groups = int(lib.tq_gather_groups(batch, n_local_heads, n_local_kv_heads))
+        if groups < 1:
+            raise ValueError(f"{n_local_heads} query heads over {n_local_kv_heads} KV heads")
+        pad = lambda n: (n + 255) // 256 * 256
+        self._ll_bytes = pad(self._words * 8)
+        self._out_off = n_buffers * self._ll_bytes                                   # plain results (local use only)
+        self._out_bytes = pad(self._words * 4)
+        self._epoch_off = self._out_off + n_buffers * self._out_bytes                # epoch arrays (local use only)
+        self._epoch_bytes = pad(groups * 4)
+        total = self._epoch_off + n_buffers * self._epoch_bytes
         with torch.cuda.device(device):
             base = C.c_void_p()
             handle = C.create_string_buffer(64)
             _lib.check(lib.tq_peer_buffer_create(total, C.byref(base), handle))
             self._own = base.value
-            mine = (device.index if device.index is not None else torch.cuda.current_device(), bytes(handle.raw))
+            mine = (device.index if device.index is not None else torch.cuda.current_device(), bytes(handle.raw),
+                    (batch, n_local_heads, n_local_kv_heads))
             everyone = [None] * self.world
             dist.all_gather_object(everyone, mine, group=group)
             self._bases, self._opened = [], []
             failure = None
-            for r, (peer_dev, h) in enumerate(everyone):
+            if any(e[2] != mine[2] for e in everyone):     # the completion rule counts on every rank making the same calls
+                failure = f"rank {self.rank}: ranks hold different numbers of heads: {[e[2] for e in everyone]}"
+            for r, (peer_dev, h, _) in enumerate(everyone):
+                if failure:
+                    break
                 if r == self.rank:
                     self._bases.append(self._own)
                     continue
@@ -184,17 +197,16 @@ class FusedGather:
             g.n_peers, g.heads_total, g.head_offset = self.world, heads_total, head_offset
             g.dtype, g.shape = dtype, (batch, d)                    # (Python attributes: attend checks its call against them)
             for r, b in enumerate(self._bases):
-                g.out[r] = b + i * self._slot_bytes
-                g.arrivals[r] = b + self._ctr_off + 8 * i
+                g.ll[r] = b + i * self._ll_bytes
+            g.epochs = self._own + self._epoch_off + i * self._epoch_bytes
             self._structs.append(g)
-        self._per_call = self.world * int(lib.tq_gather_arrivals_per_call(batch, n_local_heads, n_local_kv_heads))
         self._results = [self._view(i) for i in range(n_buffers)]
         if dist.get_world_size(group) > 1:
             dist.barrier(group=group)          # nobody writes before everybody has mapped everybody
 
     def _view(self, i: int) -> torch.Tensor:
         b, h, d = self.shape
-        addr = self._own + i * self._slot_bytes
+        addr = self._own + self._out_off + i * self._out_bytes
         typestr = _TYPESTR[self.dtype][0]
         if typestr is None:                    # bfloat16 has no array-interface code: wrap as int16, reinterpret
             t = torch.as_tensor(_DeviceView(addr, (b, h, d), "<i2"), device=self.device).view(torch.bfloat16)
@@ -208,13 +220,19 @@ class FusedGather:
         self._ledger.use(i)
         return self._structs[i]
 
+    def arrived(self, i: int) -> tuple[int, int, int, int]:
+        """The ``after=`` argument of a later ``attend`` on this stream: that kernel waits for slot ``i`` to be complete
+        here and fills ``result(i)``."""
+        return (self._own + i * self._ll_bytes, self._own + self._epoch_off + i * self._epoch_bytes, self._words,
+                self._own + self._out_off + i * self._out_bytes)
+
     def wait(self, i: int) -> None:
-        """Order the current stream behind the arrival of every rank's heads for one more decode call on slot ``i``."""
-        _lib.check(_lib.launch(self.device, "tq_gather_wait", self._own + self._ctr_off + 8 * i, self._own + self._used_off + 8 * i,
-                               self._per_call, _lib.stream_ptr(self.device)))
+        """Order the current stream behind the arrival of every rank's heads of the latest decode call on slot ``i``;
+        fills ``result(i)``."""
+        _lib.check(_lib.launch(self.device, "tq_gather_wait", *self.arrived(i), _lib.stream_ptr(self.device)))
 
     def result(self, i: int) -> torch.Tensor:
-        """(batch, heads_total, d) view of this rank's copy of slot ``i`` (complete once ``wait(i)`` has run)."""
+        """(batch, heads_total, d) view of this rank's copy of slot ``i`` (complete once the slot has been waited for)."""
         return self._results[i]
 
     def close(self) -> None:

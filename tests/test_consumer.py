@@ -131,3 +131,32 @@ def test_generate_through_compressed_caches_bf16():
     assert out.shape == (3, 8) and int(out.min()) >= 0 and int(out.max()) < 512
     c = cache[0]
     assert isinstance(c, TurboQuantKVCache) and c.offset == 707 and c._compressed_len > 0 and c._sink_len == 128
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_graphed_decoder_equals_eager_steps(dtype):
+    """The decode step with its library part replayed from CUDA graphs produces the tokens of the eager step, across a
+    drain of the recent-token buffer (steps that compress are ordinary cache calls between two graph launches)."""
+    from mlx_turboquant_b200 import apply_turboquant
+    from mlx_turboquant_b200.consumer import GraphedDecoder
+    m = LlamaShaped(ModelArgs(**TINY), dtype=dtype, device="cuda", seed=9, std=0.05)
+    apply_turboquant(m, key_bits=4, value_bits=2, residual_window=32, fp16_sink_size=16, auto_detect_outliers=False)
+    g = torch.Generator().manual_seed(10)
+    prompt = torch.randint(0, 512, (3, 100), generator=g).cuda()
+    runs = []
+    for graphed in (False, True):
+        cache = m.make_cache()
+        tok = m(prompt, cache=cache, packed=True, last_only=True)[:, -1].argmax(-1, keepdim=True)
+        toks = []
+        if graphed:
+            dec = GraphedDecoder(m, cache, tok)
+            for _ in range(80):
+                toks.append(dec.step().clone())
+        else:
+            for _ in range(80):
+                tok = m(tok, cache=cache, packed=True)[:, -1].argmax(-1, keepdim=True)
+                toks.append(tok)
+        assert cache[0].offset == 180 and cache[0]._compressed_len > 0
+        runs.append(torch.cat(toks, dim=1))
+    assert torch.equal(runs[0], runs[1])

@@ -1,6 +1,6 @@
-"""Fused output gather of head-sharded decoding: the merge step stores each shard's heads into every rank's buffer and
-bumps arrival counters.  On one GPU the ranks are emulated as consecutive launches whose "peer" buffers all live on the
-same device (no launch waits for another: the wait kernels run after both decode launches on the same stream)."""
+"""Fused output gather of head-sharded decoding: the merge step sends each shard's heads into every rank's landing buffer
+as {payload, epoch} words.  On one GPU the ranks are emulated as consecutive launches whose "peer" buffers all live on the
+same device (no launch waits for another: the waits run after both decode launches on the same stream)."""
 
 import ctypes as C
 
@@ -35,25 +35,34 @@ def test_two_emulated_ranks_fill_both_buffers(d, kb, vb, ctx):
     hq_loc = hq // world
     want = torch.cat([caches[r].attend(q[:, r * hq_loc:(r + 1) * hq_loc].contiguous()) for r in range(world)], dim=1)
 
-    bufs = [torch.full((1, hq, d), float("nan"), dtype=torch.float16, device="cuda") for _ in range(world)]
-    ctrs = torch.zeros(world, dtype=torch.int64, device="cuda")
-    per_call = int(_lib.lib().tq_gather_arrivals_per_call(1, hq_loc, hkv // world))
-    assert per_call == hkv // world
-    for rep in (1, 2):                                     # counters only grow: the second round waits for twice as many
+    words = hq * d // 2
+    lls = [torch.zeros(words, dtype=torch.int64, device="cuda") for _ in range(world)]        # rank j's landing buffer
+    outs = [torch.full((1, hq, d), float("nan"), dtype=torch.float16, device="cuda") for _ in range(world)]
+    groups = int(_lib.lib().tq_gather_groups(1, hq_loc, hkv // world))
+    assert groups == hkv // world
+    epochs = [torch.zeros(groups, dtype=torch.int32, device="cuda") for _ in range(world)]
+    stream = _lib.stream_ptr(q.device)
+    for rep in (1, 2, 3):
         for r in range(world):
             gs = _lib.PeerGather()
             gs.n_peers, gs.heads_total, gs.head_offset = world, hq, r * hq_loc
             for j in range(world):
-                gs.out[j] = bufs[j].data_ptr()
-                gs.arrivals[j] = ctrs.data_ptr() + 8 * j
+                gs.ll[j] = lls[j].data_ptr()
+            gs.epochs = epochs[r].data_ptr()
             assert caches[r].attend(q[:, r * hq_loc:(r + 1) * hq_loc].contiguous(), gather=gs) is None
-        for j in range(world):
-            _lib.check(_lib.lib().tq_gather_wait(ctrs.data_ptr() + 8 * j, None, rep * world * per_call, _lib.stream_ptr(q.device)))
+        if rep < 3:
+            for j in range(world):
+                _lib.check(_lib.lib().tq_gather_wait(lls[j].data_ptr(), epochs[j].data_ptr(), words, outs[j].data_ptr(), stream))
+        else:       # the wait inside a following decode call (both producers are earlier on the stream: nothing waits for a later launch)
+            for j in range(world):
+                caches[j].attend(q[:, j * hq_loc:(j + 1) * hq_loc].contiguous(),
+                                 after=(lls[j].data_ptr(), epochs[j].data_ptr(), words, outs[j].data_ptr()))
         torch.cuda.synchronize()
-        assert ctrs.tolist() == [rep * world * per_call] * world
         for j in range(world):
-            assert torch.equal(bufs[j].reshape(1, hq, 1, d), want)      # same kernel, same arithmetic: identical bits
-        for b in bufs:
+            assert epochs[j].tolist() == [rep] * groups
+            assert (lls[j] >> 32).tolist() == [rep] * words
+            assert torch.equal(outs[j].reshape(1, hq, 1, d), want)      # same kernel, same arithmetic: identical bits
+        for b in outs:
             b.fill_(float("nan"))
     assert _lib.lib().tq_device_status() == 0
 
@@ -64,17 +73,19 @@ def test_gather_argument_errors():
     q = torch.zeros(1, 4, 1, 128, dtype=torch.float16, device="cuda")
     gs = _lib.PeerGather()
     gs.n_peers, gs.heads_total, gs.head_offset = 1, 4, 2    # heads 2..5 do not fit in 4
-    buf = torch.zeros(1, 4, 128, dtype=torch.float16, device="cuda")
-    ctr = torch.zeros(1, dtype=torch.int64, device="cuda")
-    gs.out[0], gs.arrivals[0] = buf.data_ptr(), ctr.data_ptr()
+    ll = torch.zeros(4 * 128 // 2, dtype=torch.int64, device="cuda")
+    ep = torch.zeros(2, dtype=torch.int32, device="cuda")
+    gs.ll[0], gs.epochs = ll.data_ptr(), ep.data_ptr()
     with pytest.raises(ValueError):
         caches[0].attend(q, gather=gs)
     gs.head_offset = 0
-    gs.arrivals[0] = None
+    gs.epochs = None
     with pytest.raises(ValueError):
         caches[0].attend(q, gather=gs)
     with pytest.raises(ValueError):
-        _lib.check(_lib.lib().tq_gather_wait(None, None, 1, _lib.stream_ptr(q.device)))
+        _lib.check(_lib.lib().tq_gather_wait(None, None, 1, None, _lib.stream_ptr(q.device)))
+    with pytest.raises(ValueError):
+        caches[0].attend(q, after=(ll.data_ptr(), None, 256, None))
 
 
 def test_fused_gather_object_single_rank():
@@ -96,11 +107,13 @@ def test_fused_gather_object_single_rank():
             torch.cuda.synchronize()
             assert torch.equal(fg.result(i).reshape(1, 8, 1, 128), want)
             fg.result(i).zero_()
-        # the pair of launches takes the same arguments every time: capture once, replay
+        # the launches take the same arguments every time: capture once, replay; the second call waits for the first
+        # one's gather in its prologue, the last one's gather gets a wait launch
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             caches[0].attend(q, gather=fg.slot(1))
-            fg.wait(1)
+            caches[0].attend(q, gather=fg.slot(0), after=fg.arrived(1))
+            fg.wait(0)
         for _ in range(3):
             fg.result(1).zero_()
             graph.replay()
@@ -120,18 +133,32 @@ def test_wait_that_nothing_satisfies_gives_up_and_reports():
     from mlx_turboquant_b200 import _lib, kernels
     lib = _lib.lib()
     assert lib.tq_device_status() == 0
-    ctr = torch.zeros(2, dtype=torch.int64, device="cuda")             # [arrivals, consumed]
-    kernels.set_tuning("gather_wait_polls", 20000)                      # some 25 ms
+    ll = torch.zeros(256, dtype=torch.int64, device="cuda")            # no word carries epoch 3
+    ep = torch.tensor([3], dtype=torch.int32, device="cuda")
+    out = torch.zeros(256, dtype=torch.int32, device="cuda")
+    kernels.set_tuning("gather_wait_polls", 20000)                      # some 10 ms
     try:
-        _lib.check(lib.tq_gather_wait(ctr.data_ptr(), ctr.data_ptr() + 8, 3, _lib.stream_ptr(ctr.device)))
+        _lib.check(lib.tq_gather_wait(ll.data_ptr(), ep.data_ptr(), 256, out.data_ptr(), _lib.stream_ptr(ll.device)))
         torch.cuda.synchronize()
         assert lib.tq_device_status() == 201
-        assert ctr.tolist() == [0, 3]                                   # the consumed counter moved on all the same
         assert lib.tq_device_status_clear() == 0 and lib.tq_device_status() == 0
-        ctr[0] = 5
-        _lib.check(lib.tq_gather_wait(ctr.data_ptr(), ctr.data_ptr() + 8, 2, _lib.stream_ptr(ctr.device)))   # 5 >= 3 + 2
+        # the same wait inside a decode call: the kernel gives up, reports and still computes its result
+        caches = _shard_caches(2, 128, 300, 4, 2, 1, seed=15)
+        q = (torch.randn(1, 8, 1, 128, device="cuda") / 128 ** 0.5).half()
+        want = caches[0].attend(q)
+        after = (ll.data_ptr(), ep.data_ptr(), 256, out.data_ptr())
+        got = caches[0].attend(q, after=after)
         torch.cuda.synchronize()
-        assert lib.tq_device_status() == 0 and ctr.tolist() == [5, 5]
+        assert lib.tq_device_status() == 201 and torch.equal(got, want)
+        assert lib.tq_device_status_clear() == 0
+        ll.copy_((torch.arange(256, device="cuda") + 7) | (3 << 32))   # the words arrive
+        _lib.check(lib.tq_gather_wait(ll.data_ptr(), ep.data_ptr(), 256, out.data_ptr(), _lib.stream_ptr(ll.device)))
+        torch.cuda.synchronize()
+        assert lib.tq_device_status() == 0 and out.tolist() == list(range(7, 263))
+        out.zero_()
+        got = caches[0].attend(q, after=after)
+        torch.cuda.synchronize()
+        assert lib.tq_device_status() == 0 and out.tolist() == list(range(7, 263)) and torch.equal(got, want)
     finally:
         kernels.set_tuning("gather_wait_polls", 2000000)
         lib.tq_device_status_clear()
