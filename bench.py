@@ -43,12 +43,21 @@ LAYERS, HQ, HKV, D, CTX, SINK, RW = 32, 32, 8, 128, 32768, 128, 128
 T_C = CTX - SINK - RW
 # algorithmic bytes of one layer-step: packed codes + norms, fp16 sink/recent tokens, query in, result out
 BYTES_PER_LAYER_STEP = HKV * T_C * (D * 4 // 8 + 4 + D * 2 // 8 + 4) + HKV * (SINK + RW) * 2 * D * 2 + HQ * D * 4
-# DRAM bytes (read + write) of one decode launch on this workload, from the ncu capture summarised in
-# profiles/decode_direct_kernel_c1_k4v2_ctx32768.md (it equals the algorithmic bytes within 1 %: nothing is re-read)
-NCU_DRAM_BYTES_PER_LAUNCH = 28250624
+# the ncu summary of the decode kernel on this workload; its "DRAM traffic per launch" line feeds roofline.traffic
+DECODE_PROFILE = "profiles/decode_direct_kernel_c1_k4v2_ctx32768.md"
 WORKLOAD = "llama31_8b_layer_decode_attn_ctx32768_k4v2_sink128_rw128"
 # quantize+pack: 4096-token chunks x 8 KV heads, K and V, fp16 in; bytes per (token, head): read 2*D*2, write codes + norms
 QCHUNK = 4096
+
+
+def ncu_traffic_bytes():
+    """DRAM bytes (read + write) of one decode launch, as captured by ncu and written into the profile summary."""
+    import re
+    try:
+        m = re.search(r"DRAM traffic per launch \(read \+ write\): ([0-9,]+) bytes", (ROOT / DECODE_PROFILE).read_text())
+        return int(m.group(1).replace(",", "")) if m else None
+    except OSError:
+        return None
 
 
 def peaks():
@@ -333,6 +342,44 @@ def bench_c3(torch, dev, steps, warmup, peak):
     return {"workload": "phi35mini_layer_decode_attn_b16_ctx8192_k4v2_qjl_sink128_rw128", "us_per_layer_step": us,
             "algorithmic_bytes_per_launch": bytes_step, "hbm_gbs": gbs, "frac_of_peak": gbs / peak,
             "kernel": "decode_attn_kernel<96, qjl> (general kernel: unpack to shared memory, ldmatrix)"}
+
+
+def bench_prefill(torch, dev, steps, warmup):
+    """One prefill chunk of a Llama-3.1-8B layer straight from packed storage: 4 sequences, 32 query / 8 KV heads,
+    head_dim 128, the last 512 tokens of a 16384-token cache (128 sink + packed 4-bit keys / 2-bit values + recent)
+    attending causally over all of it.  One launch = one layer-chunk; two layer caches are cycled."""
+    from mlx_turboquant_b200 import TurboQuantKVCache
+    b, ctx, tq = 4, 16384, 512
+    caches, qs = [], []
+    for li in range(2):
+        g = torch.Generator(device=dev).manual_seed(3500 + li)
+        c = TurboQuantKVCache(head_dim=D, num_kv_heads=HKV, key_bits=4, value_bits=2, residual_window=RW, fp16_sink_size=SINK)
+        for _ in range(ctx // 4096):
+            k = (torch.randn(b, HKV, 4096, D, device=dev, generator=g) * torch.exp(0.5 * torch.randn(b, HKV, 4096, 1, device=dev, generator=g))).half()
+            v = (torch.randn(b, HKV, 4096, D, device=dev, generator=g) * torch.exp(0.5 * torch.randn(b, HKV, 4096, 1, device=dev, generator=g))).half()
+            c.update(k, v)
+        caches.append(c)
+        qs.append((torch.randn(b, HQ, tq, D, device=dev, generator=g) / D ** 0.5).half())
+        del k, v
+    outs = [torch.empty_like(q) for q in qs]
+
+    def step():
+        for c, q, o in zip(caches, qs, outs):
+            c.attend(q, out=o)
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / (steps * len(caches))
+    flops = 4.0 * b * HQ * tq * (ctx - tq / 2) * D                  # QK^T and PV over the causal extent
+    return {"workload": "llama31_8b_layer_prefill_chunk_b4_ctx16384_tq512_k4v2_sink128_rw128", "ms_per_layer_chunk": ms,
+            "tflops": flops / (ms * 1e-3) / 1e12, "query_tokens_per_s": b * tq / (ms * 1e-3),
+            "kernel": "prefill_attn_kernel<128> (64 query columns per CTA, stages unpacked to fp16 in shared memory, mma.sync)"}
 
 
 def bench_head_split(torch, dist, dev, world, rank, steps, warmup):
@@ -693,8 +740,8 @@ def run_b200(args):
         "clocks": clk.summary(),
         "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
                      "peak_source": peak_src, "frac_of_nominal_8tbs": value / world / 8000.0,
-                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH if LAYERS == 32 else None, "traffic_unit": "bytes per launch (ncu, one capture)",
-                     "kernel": "decode_direct_kernel<4> (one launch per layer: query rotation, packed attention, merge)",
+                     "traffic": ncu_traffic_bytes(), "traffic_unit": "bytes per launch (ncu, one capture)", "traffic_source": DECODE_PROFILE,
+                     "kernel": "decode_direct_kernel<4> (one launch per layer: query rotation on the tensor cores, attention over packed and fp16 tokens, last-arrival merge)",
                      "algorithmic_bytes_per_launch": BYTES_PER_LAYER_STEP},
     }
     if rank == 0 and world == 1 and not args.no_secondary:
@@ -702,6 +749,7 @@ def run_b200(args):
                              "chunk_tokens": QCHUNK, **bench_quantize(torch, dev, 3, 3, peak, args.quantize_pool)}
         line["secondary"]["compress_qjl_d96_b16"] = bench_quantize_c3(torch, dev, 3, 2, peak)
         line["secondary"]["decode_qjl_d96_b16"] = bench_c3(torch, dev, 5, 3, peak)
+        line["secondary"]["prefill_chunk_attn"] = bench_prefill(torch, dev, 3, 2)
     if world > 1 and not split and not args.no_secondary and HKV % world == 0:
         hs = bench_head_split(torch, dist, dev, world, rank, args.steps, args.warmup)
         line["secondary"] = {"head_split": hs}
