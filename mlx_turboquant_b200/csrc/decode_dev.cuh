@@ -251,6 +251,13 @@ __device__ __forceinline__ void tile_from_smem(const __half* Ks, const __half* V
     }
 }
 
+// Staging scale of a token row from the float bits of its largest magnitude: 2^(7 - floor(log2 max)); rows of zeros
+// (and non-finite rows) keep scale 1.
+__device__ __forceinline__ float stage_scale(uint32_t max_bits) {
+    const int e = int(max_bits >> 23) & 0xff;
+    return (e >= 16 && e <= 240) ? __int_as_float((261 - e) << 23) : 1.f;
+}
+
 // Attention over the uncompressed tokens [sink | residual window] of cache lane kvl with the unrotated query:
 // this warp takes tiles tile_lo + warp, + NW, ... below tile_hi; Ks / Vs are its fp16 staging buffers.
 template <int D, int NW, int NZ>
@@ -310,49 +317,93 @@ __device__ __forceinline__ void dense_tiles(const DecodeParams& p, int64_t kvl, 
         } else {
             // float32 / bfloat16 tokens can lie outside the fp16 range: every token row is staged as fp16 under its own
             // power-of-two scale (largest magnitude into [2^7, 2^8)); the scores and the softmax weights take the inverse
-            // scales where the packed tokens take their norms.  Lane pair (2r, 2r+1) scans row r of the tile.
-            {
-                const int r = lane >> 1, hf = lane & 1;
-                const int64_t tok = tok0 + r;
-                float mk = 0.f, mv = 0.f;
-                if (tok < n_tok) {
-                    int64_t e;
-                    const void* kb = row_of(tok, true, e);
-                    const void* vb = row_of(tok, false, e);
-                    e += hf * (D / 2);
-                    for (int i = 0; i < D / 2; ++i) {
-                        mk = fmaxf(mk, fabsf(load_as_f32(kb, p.dense_dtype, e + i)));
-                        mv = fmaxf(mv, fabsf(load_as_f32(vb, p.dense_dtype, e + i)));
-                    }
-                }
-                mk = fmaxf(mk, __shfl_xor_sync(0xffffffffu, mk, 1));
-                mv = fmaxf(mv, __shfl_xor_sync(0xffffffffu, mv, 1));
-                // scale 2^(7 - floor(log2 max)); rows of zeros (and non-finite rows) keep scale 1
-                const int ek = (__float_as_int(mk) >> 23) & 0xff, ev = (__float_as_int(mv) >> 23) & 0xff;
-                sck = (ek >= 16 && ek <= 240) ? __int_as_float((261 - ek) << 23) : 1.f;
-                scv = (ev >= 16 && ev <= 240) ? __int_as_float((261 - ev) << 23) : 1.f;
-            }
-            for (int c = lane; c < TILE * (D / 8); c += 32) {
-                const int r = c / (D / 8), c8 = c - r * (D / 8);
-                const int64_t tok = tok0 + r;
-                const float fk = __shfl_sync(0xffffffffu, sck, 2 * r), fv = __shfl_sync(0xffffffffu, scv, 2 * r);
-                uint4 kv = make_uint4(0, 0, 0, 0), vv = kv;
-                if (tok < n_tok) {
-                    int64_t e;
-                    const void* kb = row_of(tok, true, e);
-                    const void* vb = row_of(tok, false, e);
-                    e += c8 * 8;
-                    __half hk[8], hv[8];
+            // scales where the packed tokens take their norms.  A tensor's 16-byte chunks are all loaded first; each lane
+            // folds the largest magnitude of its chunks into the row's slot (the 16 bytes of padding at the end of the
+            // row's staging line: keys' maximum in word 0, values' in word 1; non-negative floats order like integers).
+            if (lane < TILE) *reinterpret_cast<uint2*>(Ks + lane * LD + D) = make_uint2(0u, 0u);
+            __syncwarp();
+            if (p.dense_dtype == TQ_BF16) {
+                uint4 kv[NCH], vv[NCH];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        hk[i] = __float2half_rn(load_as_f32(kb, p.dense_dtype, e + i) * fk);
-                        hv[i] = __float2half_rn(load_as_f32(vb, p.dense_dtype, e + i) * fv);
+                for (int i = 0; i < NCH; ++i) {
+                    const int c = lane + 32 * i, r = c / (D / 8), c8 = c - r * (D / 8);
+                    const int64_t tok = tok0 + r;
+                    kv[i] = make_uint4(0, 0, 0, 0); vv[i] = kv[i];
+                    if (tok < n_tok) {
+                        int64_t e;
+                        const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(row_of(tok, true, e));
+                        const __nv_bfloat16* vb = static_cast<const __nv_bfloat16*>(row_of(tok, false, e));
+                        kv[i] = __ldg(reinterpret_cast<const uint4*>(kb + e + c8 * 8));
+                        vv[i] = __ldg(reinterpret_cast<const uint4*>(vb + e + c8 * 8));
                     }
-                    kv = *reinterpret_cast<uint4*>(hk);
-                    vv = *reinterpret_cast<uint4*>(hv);
                 }
-                *reinterpret_cast<uint4*>(Ks + r * LD + c8 * 8) = kv;
-                *reinterpret_cast<uint4*>(Vs + r * LD + c8 * 8) = vv;
+                auto absmax16 = [](const uint4& v) -> uint32_t {      // float bits of the largest |x| of eight bfloat16
+                    const uint32_t m = 0x7fff7fffu;
+                    const uint32_t a = __vmaxu2(__vmaxu2(v.x & m, v.y & m), __vmaxu2(v.z & m, v.w & m));
+                    return max(a & 0xffffu, a >> 16) << 16;
+                };
+#pragma unroll
+                for (int i = 0; i < NCH; ++i) {
+                    const int r = (lane + 32 * i) / (D / 8);
+                    uint32_t* slot = reinterpret_cast<uint32_t*>(Ks + r * LD + D);
+                    atomicMax(slot, absmax16(kv[i]));
+                    atomicMax(slot + 1, absmax16(vv[i]));
+                }
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < NCH; ++i) {
+                    const int c = lane + 32 * i, r = c / (D / 8), c8 = c - r * (D / 8);
+                    const uint2 mx = *reinterpret_cast<const uint2*>(Ks + r * LD + D);
+                    const float fk = stage_scale(mx.x), fv = stage_scale(mx.y);
+                    auto conv = [](const uint4& v, float f) -> uint4 {
+                        auto two = [&](uint32_t w) -> uint32_t {
+                            return pack_h2(__uint_as_float(w << 16) * f, __uint_as_float(w & 0xffff0000u) * f);
+                        };
+                        return make_uint4(two(v.x), two(v.y), two(v.z), two(v.w));
+                    };
+                    *reinterpret_cast<uint4*>(Ks + r * LD + c8 * 8) = conv(kv[i], fk);
+                    *reinterpret_cast<uint4*>(Vs + r * LD + c8 * 8) = conv(vv[i], fv);
+                }
+            } else {
+                // float32: a chunk holds four values; keys first, then values (register budget)
+                constexpr int NCH4 = TILE * (D / 4) / 32;
+#pragma unroll 1
+                for (int side = 0; side < 2; ++side) {
+                    uint4 xv[NCH4];
+#pragma unroll
+                    for (int i = 0; i < NCH4; ++i) {
+                        const int c = lane + 32 * i, r = c / (D / 4), c4 = c - r * (D / 4);
+                        const int64_t tok = tok0 + r;
+                        xv[i] = make_uint4(0, 0, 0, 0);
+                        if (tok < n_tok) {
+                            int64_t e;
+                            const float* xb = static_cast<const float*>(row_of(tok, side == 0, e));
+                            xv[i] = __ldg(reinterpret_cast<const uint4*>(xb + e + c4 * 4));
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < NCH4; ++i) {
+                        const int r = (lane + 32 * i) / (D / 4);
+                        const uint32_t m = 0x7fffffffu;
+                        atomicMax(reinterpret_cast<uint32_t*>(Ks + r * LD + D) + side, max(max(xv[i].x & m, xv[i].y & m), max(xv[i].z & m, xv[i].w & m)));
+                    }
+                    __syncwarp();
+                    __half* dst = side == 0 ? Ks : Vs;
+#pragma unroll
+                    for (int i = 0; i < NCH4; ++i) {
+                        const int c = lane + 32 * i, r = c / (D / 4), c4 = c - r * (D / 4);
+                        const float f = stage_scale(reinterpret_cast<const uint32_t*>(Ks + r * LD + D)[side]);
+                        *reinterpret_cast<uint2*>(dst + r * LD + c4 * 4) =
+                            make_uint2(pack_h2(__uint_as_float(xv[i].x) * f, __uint_as_float(xv[i].y) * f),
+                                       pack_h2(__uint_as_float(xv[i].z) * f, __uint_as_float(xv[i].w) * f));
+                    }
+                }
+            }
+            __syncwarp();
+            {
+                const uint2 mx = *reinterpret_cast<const uint2*>(Ks + (lane >> 1) * LD + D);
+                sck = stage_scale(mx.x);
+                scv = stage_scale(mx.y);
             }
         }
         __syncwarp();
