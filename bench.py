@@ -465,6 +465,7 @@ def run_c4(args):
     32 x (projections, RoPE, cache.decode_step, output projection, SwiGLU), logits, arg-max.  GEMMs and element-wise work
     are torch library calls replayed from CUDA graphs (consumer.GraphedDecoder); the cache calls are this repository's
     kernels.  The timed region is the generation; the prefill is timed separately."""
+    os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")    # caches grow while activations come and go
     import torch
     import torch.distributed as dist
 

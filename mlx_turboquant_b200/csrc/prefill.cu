@@ -417,6 +417,13 @@ template <int D> static int launch(const Params& P, cudaStream_t s) {
 
 }  // namespace tq
 
+namespace tq {
+// prefill_tc.cu: the tensor-core kernel for head_dim 128 with 4-bit keys and 2-bit values
+bool prefill_tc_applicable(const tq_decode_args* a, int t_q);
+int launch_prefill_tc(const DecodeParams& c, const void* q, int q_dtype, void* out, int out_dtype, int t_q, int64_t q_pos0, cudaStream_t s);
+int g_tune_prefill_tc = 1;     // 0: always the mma.sync kernel (testing)
+}  // namespace tq
+
 using namespace tq;
 
 extern "C" int tq_prefill_attn(const tq_decode_args* a, int t_q, void* stream) {
@@ -465,6 +472,7 @@ extern "C" int tq_prefill_attn(const tq_decode_args* a, int t_q, void* stream) {
     P.GP = gmin <= 1 ? 1 : gmin <= 2 ? 2 : gmin <= 4 ? 4 : 8;
     P.QT = pf::COLS / P.GP;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (g_tune_prefill_tc && prefill_tc_applicable(a, t_q)) return launch_prefill_tc(p, a->q, a->q_dtype, a->out, a->out_dtype, t_q, P.q_pos0, s);
     if (d == 64) return pf::launch<64>(P, s);
     if (d == 96) return pf::launch<96>(P, s);
     if (d == 128) return pf::launch<128>(P, s);

@@ -15,6 +15,18 @@ from gpu_util import cu, host, host_tables, kv_like
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=["tcgen05", "mma.sync"], autouse=True)
+def which_kernel(request):
+    """Every case runs twice: with the tensor-core (tcgen05) kernel where it applies - head_dim 128, 4-bit keys, 2-bit values,
+    at least 64 query rows - and with the mma.sync kernel everywhere."""
+    from mlx_turboquant_b200 import kernels
+    kernels.set_tuning("prefill_tc", 1 if request.param == "tcgen05" else 0)
+    yield request.param
+    kernels.set_tuning("prefill_tc", 1)
+    from mlx_turboquant_b200 import _lib
+    assert _lib.lib().tq_device_status() == 0
+
+
 def causal_reference(q, k, v, scale=None):
     """q (B, Hq, Tq, D): the last Tq tokens; k, v (B, Hkv, T, D) float32.  float32 softmax, GQA head repeat."""
     q, k, v = (np.asarray(x).astype(np.float32) for x in (q, k, v))
@@ -130,3 +142,16 @@ def test_argument_errors(oracle):
     cq.update(cu(kv_like(rs, (1, 2, 300, 128))), cu(kv_like(rs, (1, 2, 300, 128))))
     with pytest.raises(NotImplementedError):
         cq.attend(q)
+
+
+@pytest.mark.parametrize("b,hq,hkv,t,tq,rw,sink", ((1, 8, 2, 4000, 512, 16, 4), (2, 32, 8, 3000, 1000, 128, 128), (1, 4, 4, 2500, 2500, 64, 0),
+                                                  (1, 16, 2, 1500, 130, 0, 32)))
+def test_long_chunks_k4v2(oracle, b, hq, hkv, t, tq, rw, sink):
+    """4-bit keys / 2-bit values at head_dim 128 (the tensor-core kernel's shape): chunks that span many 128-token tiles,
+    a chunk that is the whole cache, row tiles that end inside a query token's head group, no recent window."""
+    rs = np.random.RandomState(b * 1000 + tq)
+    c, q, ref = _case(oracle, rs, b, hq, hkv, t, tq, 128, 4, 2, rw, sink)
+    _check(c.attend(q, out_dtype=torch.float32), ref)
+    out16 = c.attend(q)
+    assert out16.dtype == torch.float16
+    _check(out16, ref, tol=1e-3 + 2.0 ** -11)
