@@ -746,11 +746,16 @@ def run_b200(args):
                      "algorithmic_bytes_per_launch": BYTES_PER_LAYER_STEP},
     }
     if rank == 0 and world == 1 and not args.no_secondary:
-        line["secondary"] = {"metric": "quantize_pack_mtokens_per_s", "unit": "Mtokens/s (token = position x 8 KV heads x 32 layers)",
-                             "chunk_tokens": QCHUNK, **bench_quantize(torch, dev, 3, 3, peak, args.quantize_pool)}
-        line["secondary"]["compress_qjl_d96_b16"] = bench_quantize_c3(torch, dev, 3, 2, peak)
-        line["secondary"]["decode_qjl_d96_b16"] = bench_c3(torch, dev, 5, 3, peak)
-        line["secondary"]["prefill_chunk_attn"] = bench_prefill(torch, dev, 3, 2)
+        legs = set(args.legs.split(","))
+        line["secondary"] = {"metric": "quantize_pack_mtokens_per_s", "unit": "Mtokens/s (token = position x 8 KV heads x 32 layers)", "chunk_tokens": QCHUNK}
+        if "quantize" in legs:
+            line["secondary"].update(bench_quantize(torch, dev, 3, 3, peak, args.quantize_pool))
+        if "compress_c3" in legs:
+            line["secondary"]["compress_qjl_d96_b16"] = bench_quantize_c3(torch, dev, 3, 2, peak)
+        if "decode_c3" in legs:
+            line["secondary"]["decode_qjl_d96_b16"] = bench_c3(torch, dev, 5, 3, peak)
+        if "prefill" in legs:
+            line["secondary"]["prefill_chunk_attn"] = bench_prefill(torch, dev, 3, 2)
     if world > 1 and not split and not args.no_secondary and HKV % world == 0:
         hs = bench_head_split(torch, dist, dev, world, rank, args.steps, args.warmup)
         line["secondary"] = {"head_split": hs}
@@ -791,7 +796,9 @@ def main():
     ap.add_argument("--no-gather", action="store_true", help="with --split-heads: leave every GPU with its own heads' outputs")
     ap.add_argument("--fused-gather", action="store_true", help="with --split-heads: the decode kernel stores its heads into every GPU's "
                     "result buffer (peer-mapped memory) instead of an NCCL all-gather")
-    ap.add_argument("--no-secondary", action="store_true", help="skip the quantize+pack leg")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary legs")
+    ap.add_argument("--legs", default="quantize,compress_c3,decode_c3,prefill", help="which secondary legs run (comma list; profilers "
+                    "capture one kernel at a time with little else on the device)")
     ap.add_argument("--workload", default="c1", choices=("c1", "c4"), help="c1: the headline layer-decode benchmark; c4: end-to-end "
                     "batched decoding of a Llama-3.1-8B-shaped model through compressed caches (about 75 GB on the device at the defaults)")
     ap.add_argument("--c4-batch", type=int, default=64, help="c4: sequences in total over all GPUs")

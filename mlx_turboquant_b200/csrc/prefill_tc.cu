@@ -37,9 +37,10 @@ constexpr uint32_t OFF_QR = 0, OFF_QD = TILE_BYTES, OFF_K = 2 * TILE_BYTES, OFF_
 constexpr uint32_t OFF_KN = 5 * TILE_BYTES;                                 // float [128] key norms (or inverse staging scales)
 constexpr uint32_t OFF_VN = OFF_KN + 512;                                   // float [128]
 constexpr uint32_t OFF_POS = OFF_VN + 512;                                  // int   [128] absolute positions of the tile's tokens
-constexpr uint32_t OFF_T4 = OFF_POS + 512;                                  // uint  [256] byte of two 4-bit codes -> half2
-constexpr uint32_t OFF_T2 = OFF_T4 + 1024;                                  // uint2 [256] byte of four 2-bit codes -> 4 halves
-constexpr uint32_t OFF_CTAB = OFF_T2 + 2048;                                // half  [32]
+constexpr uint32_t OFF_T4 = OFF_POS + 512;                                  // uint  [256][TREP] byte of two 4-bit codes -> half2
+constexpr int TREP = 8;                                                      // copies of every table entry (lane l reads copy l mod 8)
+constexpr uint32_t OFF_T2 = OFF_T4 + 1024 * TREP;                           // uint2 [256][TREP] byte of four 2-bit codes -> 4 halves
+constexpr uint32_t OFF_CTAB = OFF_T2 + 2048 * TREP;                                // half  [32]
 constexpr uint32_t OFF_BAR = OFF_CTAB + 64;                                 // two mbarriers
 constexpr uint32_t OFF_SLOT = OFF_BAR + 16;                                 // tensor-memory base, largest value norm of the tile, abort flag
 constexpr uint32_t SMEM_USED = OFF_SLOT + 16;
@@ -162,10 +163,11 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
     uint32_t* t4 = reinterpret_cast<uint32_t*>(smem + OFF_T4);
     uint2* t2 = reinterpret_cast<uint2*>(smem + OFF_T2);
     __half* ctab = reinterpret_cast<__half*>(smem + OFF_CTAB);
-    volatile uint32_t* slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_SLOT);   // [0] tmem base, [1] tile's largest value norm (bits), [2] abort
+    volatile uint32_t* slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_SLOT);   // [0] tmem base, [1] tile's largest value norm (bits), [2] abort, [3] every row sees every token of the tile
     const uint32_t bar_s = sbase + OFF_BAR, bar_o = bar_s + 8;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t cp = uint32_t(lane) & (TREP - 1);
     const int hkv = blockIdx.y / p.HG, hg = blockIdx.y % p.HG, b = blockIdx.z;
     const int64_t kvl = int64_t(b) * p.Hkv + hkv;
     const int heads_here = min(HPG, p.G - hg * HPG);
@@ -197,10 +199,13 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
     {
         const int e = tid;      // NT == 256 entries
         const __half2 hk = __halves2half2(ctab[e & 15], ctab[e >> 4]);
-        t4[e] = *reinterpret_cast<const uint32_t*>(&hk);
         const __half2 v01 = __halves2half2(ctab[16 + (e & 3)], ctab[16 + ((e >> 2) & 3)]);
         const __half2 v23 = __halves2half2(ctab[16 + ((e >> 4) & 3)], ctab[16 + (e >> 6)]);
-        t2[e] = make_uint2(*reinterpret_cast<const uint32_t*>(&v01), *reinterpret_cast<const uint32_t*>(&v23));
+#pragma unroll
+        for (int r = 0; r < TREP; ++r) {
+            t4[e * TREP + r] = *reinterpret_cast<const uint32_t*>(&hk);
+            t2[e * TREP + r] = make_uint2(*reinterpret_cast<const uint32_t*>(&v01), *reinterpret_cast<const uint32_t*>(&v23));
+        }
     }
 
     // ---------------- the query block: raw (scaled) and rotated (scaled), fp16 operand tiles ------------------------
@@ -256,8 +261,9 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
 
     // ---------------- per-row softmax state (threads 0 .. 127 own rows) ---------------------------------------------
     const bool row_thread = tid < TM;
-    const int64_t q_pos = (row_thread && row_valid(tid)) ? P.q_pos0 + tq0 + tid / GP : -1;    // the latest position this row sees
+    const int q_pos = (row_thread && row_valid(tid)) ? int(P.q_pos0 + tq0 + tid / GP) : -1;   // the latest position this row sees
     const int64_t cta_q_max = P.q_pos0 + min(tq0 + P.QT, P.Tq) - 1;
+    const int64_t min_q_pos = P.q_pos0 + tq0;                                      // the earliest position any (valid) row sits at
     float m_ref = -1e30f, m_thr = -1e30f, l_sum = 0.f, vsc = 1.f, vthr = VSC_CAP;
     const uint32_t t_row = tmem_base + (uint32_t((warp & 3) * 32) << 16);
     const uint32_t idesc_qk = make_idesc(false), idesc_pv = make_idesc(true);
@@ -290,23 +296,11 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
         ph_s ^= 1u;
         tc_fence_after();
         if (row_thread) {
-            // (2) first pass: the row's largest masked score
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c0 = 0; c0 < TN; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(t_row + COL_S + c0, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const float s = __uint_as_float(v[j]) * s_kn[c0 + j];
-                    if (int64_t(s_pos[c0 + j]) <= q_pos) mx = fmaxf(mx, s);
-                }
-            }
             const float vmax = __uint_as_float(slot[1]);
-            // (3) reference maximum / value scale: refreshed for the whole warp when any row needs it (the tensor-memory
-            //     loads and stores below are warp-wide)
-            if (__any_sync(0xffffffffu, mx > m_thr || vmax > vthr)) {
+            const bool masked = slot[3] == 0u;                                // some token of the tile is hidden from some row (or dead)
+            // Reference maximum / value scale: refreshed for the whole warp when any row needs it (the tensor-memory loads
+            // and stores are warp-wide).  mx: the row's largest visible score of this tile.
+            auto refresh = [&](float mx) {
                 const float mn = fmaxf(fmaxf(m_ref, mx), -1e30f);
                 float a = ex2(m_ref - mn);
                 m_ref = mn; m_thr = mn + MAX_SLACK;
@@ -334,26 +328,55 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
                     }
                     tmem_st_wait();
                 }
-            }
-            // (4) second pass: weights; P = p * value norm * scale as fp16 into the A-operand tile, row = this thread
+            };
+            // One sweep over the row's 128 scores: weights against the current reference, P = p * value norm * scale as fp16
+            // into the A-operand tile (row = this thread), the row's largest score alongside.  WRITE = false: the maximum only.
+            auto sweep = [&](bool write, float& mx, float& lsum) {
+                mx = -INFINITY; lsum = 0.f;
 #pragma unroll 1
-            for (int c0 = 0; c0 < TN; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(t_row + COL_S + c0, v);
-                tmem_ld_wait();
-                uint32_t h[16];
+                for (int c0 = 0; c0 < TN; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(t_row + COL_S + c0, v);
+                    tmem_ld_wait();
+                    uint32_t h[16];
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    float p0 = 0.f, p1 = 0.f;
-                    if (int64_t(s_pos[c0 + j]) <= q_pos) p0 = ex2(__uint_as_float(v[j]) * s_kn[c0 + j] - m_ref);
-                    if (int64_t(s_pos[c0 + j + 1]) <= q_pos) p1 = ex2(__uint_as_float(v[j + 1]) * s_kn[c0 + j + 1] - m_ref);
-                    l_sum += p0 + p1;
-                    h[j >> 1] = pack_h2(p0 * (s_vn[c0 + j] * vsc), p1 * (s_vn[c0 + j + 1] * vsc));
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 kn = *reinterpret_cast<const float4*>(s_kn + c0 + j);
+                        float s0 = __uint_as_float(v[j]) * kn.x, s1 = __uint_as_float(v[j + 1]) * kn.y;
+                        float s2 = __uint_as_float(v[j + 2]) * kn.z, s3 = __uint_as_float(v[j + 3]) * kn.w;
+                        if (masked) {
+                            const int4 ps = *reinterpret_cast<const int4*>(s_pos + c0 + j);
+                            s0 = ps.x <= q_pos ? s0 : -INFINITY; s1 = ps.y <= q_pos ? s1 : -INFINITY;
+                            s2 = ps.z <= q_pos ? s2 : -INFINITY; s3 = ps.w <= q_pos ? s3 : -INFINITY;
+                        }
+                        mx = fmaxf(fmaxf(mx, fmaxf(s0, s1)), fmaxf(s2, s3));
+                        if (write) {
+                            const float4 vn = *reinterpret_cast<const float4*>(s_vn + c0 + j);
+                            const float p0 = ex2(s0 - m_ref), p1 = ex2(s1 - m_ref), p2 = ex2(s2 - m_ref), p3 = ex2(s3 - m_ref);
+                            lsum += (p0 + p1) + (p2 + p3);
+                            h[j >> 1] = pack_h2(p0 * (vn.x * vsc), p1 * (vn.y * vsc));
+                            h[(j >> 1) + 1] = pack_h2(p2 * (vn.z * vsc), p3 * (vn.w * vsc));
+                        }
+                    }
+                    if (write) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            *reinterpret_cast<uint4*>(smem + OFF_P + chunk_off(tid, (c0 >> 3) + c)) = make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+                    }
                 }
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    *reinterpret_cast<uint4*>(smem + OFF_P + chunk_off(tid, (c0 >> 3) + c)) = make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+            };
+            float mx, lsum;
+            // the very first tile (no reference yet) and a tile that moves the value scale: settle the references first
+            if (__any_sync(0xffffffffu, m_ref <= -1e30f || vmax > vthr)) {
+                sweep(false, mx, lsum);
+                refresh(mx);
             }
+            sweep(true, mx, lsum);
+            if (__any_sync(0xffffffffu, mx > m_thr)) {        // a score beyond the slack: new reference, weights again (rare)
+                refresh(mx);
+                sweep(true, mx, lsum);
+            }
+            l_sum += lsum;
         }
         fence_proxy_async();        // P (generic-proxy stores) before the tensor core reads it
         tc_fence_before();
@@ -388,14 +411,18 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
             drain_pv();
             if (__syncthreads_or(int(slot[2]))) break;                        // everybody is past the previous tile; leave together after a failed wait
             const int rows = int(min(int64_t(TN), p.c_len - tok0));
-            if (tid == 0) slot[1] = 0u;
+            if (tid == 0) {
+                slot[1] = 0u;
+                slot[3] = (rows == TN && p.sink_len + tok0 + TN - 1 <= min_q_pos) ? 1u : 0u;
+            }
             {
                 const uint32_t* src = reinterpret_cast<const uint32_t*>(p.k_hi + (kvl * p.c_ls + tok0) * (D / 2));
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     const int i = tid + NT * k, r = i >> 4, w = i & 15;
                     const uint32_t x = r < rows ? __ldg(src + i) : 0u;
-                    *reinterpret_cast<uint4*>(smem + OFF_K + chunk_off(r, w)) = make_uint4(t4[x & 255u], t4[(x >> 8) & 255u], t4[(x >> 16) & 255u], t4[x >> 24]);
+                    *reinterpret_cast<uint4*>(smem + OFF_K + chunk_off(r, w)) =
+                        make_uint4(t4[(x & 255u) * TREP + cp], t4[((x >> 8) & 255u) * TREP + cp], t4[((x >> 16) & 255u) * TREP + cp], t4[(x >> 24) * TREP + cp]);
                 }
             }
             {
@@ -404,7 +431,7 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
                 for (int k = 0; k < 4; ++k) {
                     const int i = tid + NT * k, r = i >> 3, w = i & 7;
                     const uint32_t x = r < rows ? __ldg(src + i) : 0u;
-                    const uint2 a = t2[x & 255u], bb = t2[(x >> 8) & 255u], cc = t2[(x >> 16) & 255u], ee = t2[x >> 24];
+                    const uint2 a = t2[(x & 255u) * TREP + cp], bb = t2[((x >> 8) & 255u) * TREP + cp], cc = t2[((x >> 16) & 255u) * TREP + cp], ee = t2[(x >> 24) * TREP + cp];
                     *reinterpret_cast<uint4*>(smem + OFF_V + chunk_off(r, 2 * w)) = make_uint4(a.x, a.y, bb.x, bb.y);
                     *reinterpret_cast<uint4*>(smem + OFF_V + chunk_off(r, 2 * w + 1)) = make_uint4(cc.x, cc.y, ee.x, ee.y);
                 }
@@ -436,7 +463,11 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
         for (int64_t tok0 = 0; tok0 < vis_d; tok0 += TN) {
             drain_pv();
             if (__syncthreads_or(int(slot[2]))) break;
-            if (tid == 0) slot[1] = 0u;
+            if (tid == 0) {
+                slot[1] = 0u;
+                const int64_t tl = tok0 + TN - 1;                             // the tile's last token, if it has 128
+                slot[3] = (tl < n_dense && (tl < p.sink_len ? tl : p.c_len + tl) <= min_q_pos) ? 1u : 0u;
+            }
             __syncthreads();
             // two threads per token row: each converts 64 coordinates of the key row and of the value row; float32 /
             // bfloat16 rows under a per-token power-of-two scale (largest magnitude into [2^7, 2^8)) whose inverse goes
