@@ -4,23 +4,25 @@
 // attention; sketched for packed keys in kernels.py:558-590 and docs/FUSED_ATTENTION_DESIGN.md:281-283).
 //
 // A CTA owns 128 rows = 128 / GP query tokens x the GP (1, 2, 4 or 8) query heads of one GQA group, and walks the cache
-// in tiles of 128 tokens.  Per tile:
-//   1. all 8 warps unpack the tile to fp16 in shared memory - keys and values both token-major, in the 128-byte-swizzled
-//      layout the tensor core's shared-memory descriptors describe (keys: the K-major B operand of S = Q K^T; values:
-//      the MN-major B operand of O += P V, so no transpose is ever materialised) - and stage the tile's norms;
-//   2. one thread issues S = Q K^T as eight tcgen05.mma (M 128, N 128, K 16) into tensor memory and commits to an
-//      mbarrier;
-//   3. the four warps that own the 128 accumulator lanes (one row per thread) read S back (tcgen05.ld), apply key
-//      norms, causal mask and the running-maximum softmax, and write P (weights x value norms, fp16) as the next A
-//      operand; when a row's reference maximum or the value-norm scale moves, its O rows in tensor memory are rescaled
-//      (tcgen05.ld / st);
-//   4. one thread issues O += P V (eight more MMAs) into the accumulator of the region: packed tokens accumulate in
-//      rotated space under the rotated query, sink / recent tokens under the raw query in a second accumulator.
-// At the end the rotation of the packed part is undone once (y @ R, rotation.py:68-78), the parts are added, divided by
-// the softmax denominators and stored.  Tensor memory: S 128 columns, O (packed) 128, O (uncompressed) 128.
+// in tiles of 128 tokens, warp-specialised:
+//   * warps 4-7 (producers) unpack tile g into key / value buffer g & 1: fp16, keys and values both token-major, in the
+//     128-byte-swizzled layout the tensor core's shared-memory descriptors describe (keys: the K-major B operand of
+//     S = Q K^T; values: the MN-major B operand of O += P V, so no transpose is ever materialised), plus the tile's norms
+//     and positions;
+//   * one thread of warp 8 issues S_g = Q K_g^T as eight tcgen05.mma (M 128, N 128, K 16) into score columns g & 1 of
+//     tensor memory, then O += P_{g-1} V_{g-1}, each followed by tcgen05.commit to mbarriers: the scores of tile g are
+//     computed while the rows are still busy with tile g - 1;
+//   * warps 0-3 own the 128 accumulator lanes (one row per thread): they read S back (tcgen05.ld), apply key norms,
+//     causal mask (skipped on tiles every row sees in full) and the running-maximum softmax in one sweep, and write
+//     P (weights x value norms, fp16) as the next A operand; when a row's reference maximum or the value-norm scale
+//     moves, its O rows in tensor memory are rescaled (tcgen05.ld / st) and the sweep is repeated (rare).
+// Packed tokens accumulate in rotated space under the rotated query; sink / recent tokens form a second region under
+// the raw query (which takes the rotated one's place in shared memory) with a second accumulator.  At the end the
+// rotation of the packed part is undone once (y @ R, rotation.py:68-78), the parts are added, divided by the softmax
+// denominators and stored.  Tensor memory: S twice 128 columns, O (packed) 128, O (uncompressed) 128.
 //
-// Every mbarrier wait is bounded; a wait that runs out leaves status 104 (tq_device_status), every thread leaves the
-// tile loop at the next barrier, and the tensor memory is freed on every path.
+// Every mbarrier wait is bounded; a wait that runs out leaves status 104 (tq_device_status) and raises a flag that ends
+// every other wait, the threads meet at the end of the region, and the tensor memory is freed on every path.
 #include <algorithm>
 
 #include "decode_dev.cuh"
@@ -31,26 +33,33 @@ int* decode_status_ptr();
 
 namespace pftc {
 
-constexpr int D = 128, TM = 128, TN = 128, NT = 256;
+constexpr int D = 128, TM = 128, TN = 128;
+constexpr int NT = 288;                               // warps 0-3: one accumulator row per thread; 4-7: unpack; 8: MMA issue
+constexpr int ROW_T = 128, PROD_T = 128;
 constexpr uint32_t KBLK = 16384, TILE_BYTES = 2 * KBLK;                     // a 128 x 128 fp16 operand tile: two 64-column blocks
-constexpr uint32_t OFF_QR = 0, OFF_QD = TILE_BYTES, OFF_K = 2 * TILE_BYTES, OFF_V = 3 * TILE_BYTES, OFF_P = 4 * TILE_BYTES;
-constexpr uint32_t OFF_KN = 5 * TILE_BYTES;                                 // float [128] key norms (or inverse staging scales)
-constexpr uint32_t OFF_VN = OFF_KN + 512;                                   // float [128]
-constexpr uint32_t OFF_POS = OFF_VN + 512;                                  // int   [128] absolute positions of the tile's tokens
-constexpr uint32_t OFF_T4 = OFF_POS + 512;                                  // uint  [256][TREP] byte of two 4-bit codes -> half2
-constexpr int TREP = 8;                                                      // copies of every table entry (lane l reads copy l mod 8)
+constexpr uint32_t OFF_Q = 0;                                               // the query tile: rotated, later raw
+constexpr uint32_t OFF_K = TILE_BYTES, OFF_V = 3 * TILE_BYTES;              // two key tiles, two value tiles
+constexpr uint32_t OFF_P = 5 * TILE_BYTES;
+constexpr uint32_t OFF_KN = 6 * TILE_BYTES;                                 // float [2][128] key norms (or inverse staging scales)
+constexpr uint32_t OFF_VN = OFF_KN + 1024;                                  // float [2][128]
+constexpr uint32_t OFF_POS = OFF_VN + 1024;                                 // int   [2][128] absolute positions of the tile's tokens
+constexpr int TREP = 4;                                                     // copies of every table entry (lane l reads copy l mod 4)
+constexpr uint32_t OFF_T4 = OFF_POS + 1024;                                 // uint  [256][TREP] byte of two 4-bit codes -> half2
 constexpr uint32_t OFF_T2 = OFF_T4 + 1024 * TREP;                           // uint2 [256][TREP] byte of four 2-bit codes -> 4 halves
-constexpr uint32_t OFF_CTAB = OFF_T2 + 2048 * TREP;                                // half  [32]
-constexpr uint32_t OFF_BAR = OFF_CTAB + 64;                                 // two mbarriers
-constexpr uint32_t OFF_SLOT = OFF_BAR + 16;                                 // tensor-memory base, largest value norm of the tile, abort flag
-constexpr uint32_t SMEM_USED = OFF_SLOT + 16;
+constexpr uint32_t OFF_CTAB = OFF_T2 + 2048 * TREP;                         // half  [32]
+constexpr uint32_t OFF_BAR = OFF_CTAB + 64;                                 // mbarriers (see Bars)
+constexpr uint32_t OFF_SLOT = OFF_BAR + 128;                                // words: [0] tensor-memory base, [1] abort, [4..5] "every row sees every token" of tile buffer 0 / 1, [8..15] largest value norm per buffer and producer warp
+constexpr uint32_t SMEM_USED = OFF_SLOT + 64;
 constexpr size_t SMEM_BYTES = SMEM_USED + 1024;                             // + slack to align the tiles to 1024 bytes
+static_assert(SMEM_BYTES <= 227u * 1024u, "shared-memory plan");
 // the finish reuses the tiles: two [128][129] float arrays
 constexpr uint32_t FIN_LD = 129, OFF_FD = 0, OFF_FP = 66560;
 static_assert(OFF_FP + 128 * FIN_LD * 4 <= OFF_KN && 128 * FIN_LD * 4 <= OFF_FP, "finish scratch");
 constexpr uint32_t WAIT_LIMIT = 4u << 20;
 constexpr int ERR_WAIT = 104;
-constexpr uint32_t TMEM_COLS = 512, COL_S = 0, COL_OP = 128, COL_OD = 256;
+constexpr uint32_t TMEM_COLS = 512, COL_S = 0, COL_OP = 256, COL_OD = 384;  // S twice (tile parity), O of the packed part, O of the uncompressed part
+// mbarriers, 8 bytes each from OFF_BAR
+enum Bars { KV_FULL = 0, KV_FREE = 2, S_FULL = 4, S_FREE = 6, P_FULL = 8, PV_DONE = 9, N_BARS = 10 };
 
 struct Params {
     DecodeParams c;
@@ -71,6 +80,9 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -157,14 +169,14 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
     const uint32_t sbase = (raw_addr + 1023u) & ~1023u;
     unsigned char* smem = smem_raw + (sbase - raw_addr);
     const DecodeParams& p = P.c;
-    float* s_kn = reinterpret_cast<float*>(smem + OFF_KN);
+    float* s_kn = reinterpret_cast<float*>(smem + OFF_KN);                   // [2][128]
     float* s_vn = reinterpret_cast<float*>(smem + OFF_VN);
     int* s_pos = reinterpret_cast<int*>(smem + OFF_POS);
     uint32_t* t4 = reinterpret_cast<uint32_t*>(smem + OFF_T4);
     uint2* t2 = reinterpret_cast<uint2*>(smem + OFF_T2);
     __half* ctab = reinterpret_cast<__half*>(smem + OFF_CTAB);
-    volatile uint32_t* slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_SLOT);   // [0] tmem base, [1] tile's largest value norm (bits), [2] abort, [3] every row sees every token of the tile
-    const uint32_t bar_s = sbase + OFF_BAR, bar_o = bar_s + 8;
+    volatile uint32_t* slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_SLOT);
+    auto bar = [&](int which) -> uint32_t { return sbase + OFF_BAR + 8u * uint32_t(which); };
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t cp = uint32_t(lane) & (TREP - 1);
@@ -180,12 +192,16 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
 
     // ---------------- set-up: barriers, tensor memory, tables ------------------------------------------------------
     if (tid == 0) {
-        mbar_init(bar_s, 1);
-        mbar_init(bar_o, 1);
+        mbar_init(bar(KV_FULL), PROD_T); mbar_init(bar(KV_FULL + 1), PROD_T);
+        mbar_init(bar(KV_FREE), 1); mbar_init(bar(KV_FREE + 1), 1);
+        mbar_init(bar(S_FULL), 1); mbar_init(bar(S_FULL + 1), 1);
+        mbar_init(bar(S_FREE), ROW_T); mbar_init(bar(S_FREE + 1), ROW_T);
+        mbar_init(bar(P_FULL), ROW_T);
+        mbar_init(bar(PV_DONE), 1);
         fence_barrier_init();
-        slot[2] = 0u;
+        slot[1] = 0u;
     }
-    if (warp == 4) {
+    if (warp == 8) {
         tmem_alloc(sbase + OFF_SLOT, TMEM_COLS);
         tmem_relinquish();
     }
@@ -196,8 +212,8 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
         ctab[tid] = __float2half_rn((src != nullptr && k < (which ? 4 : 16)) ? src[k] * sc : 0.f);
     }
     __syncthreads();
-    {
-        const int e = tid;      // NT == 256 entries
+    if (tid < 256) {
+        const int e = tid;
         const __half2 hk = __halves2half2(ctab[e & 15], ctab[e >> 4]);
         const __half2 v01 = __halves2half2(ctab[16 + (e & 3)], ctab[16 + ((e >> 2) & 3)]);
         const __half2 v23 = __halves2half2(ctab[16 + ((e >> 4) & 3)], ctab[16 + (e >> 6)]);
@@ -208,21 +224,14 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
         }
     }
 
-    // ---------------- the query block: raw (scaled) and rotated (scaled), fp16 operand tiles ------------------------
+    // ---------------- the query block, rotated and scaled, as the fp16 A-operand tile -------------------------------
     const float f = p.scale * LOG2E;
     {
-        float* qf = reinterpret_cast<float*>(smem + OFF_K);                  // [128][D] float32 (the K and V tiles' space)
+        float* qf = reinterpret_cast<float*>(smem + OFF_K);                  // [128][D] float32 (the key tiles' space)
         float* rs = reinterpret_cast<float*>(smem + OFF_P);                  // [32][D + 1] slab of R
         for (int e = tid; e < TM * D; e += NT) {
             const int m = e / D, k = e - m * D;
             qf[e] = row_valid(m) ? load_as_f32(P.q, P.q_dtype, row_q_index(m) + k) * f : 0.f;
-        }
-        __syncthreads();
-        for (int i = tid; i < TM * 16; i += NT) {                            // raw query tile: 16-byte chunks
-            const int m = i >> 4, c = i & 15;
-            const float4 a = *reinterpret_cast<const float4*>(qf + m * D + c * 8), bb = *reinterpret_cast<const float4*>(qf + m * D + c * 8 + 4);
-            *reinterpret_cast<uint4*>(smem + OFF_QD + chunk_off(m, c)) =
-                make_uint4(pack_h2(a.x, a.y), pack_h2(a.z, a.w), pack_h2(bb.x, bb.y), pack_h2(bb.z, bb.w));
         }
         // q_rot[m][j] = sum_k q[m][k] R[j][k] (rotation.py:81-110): 32 rows of R at a time; thread = (row j of the slab, 16 query rows)
         constexpr int RS = D + 1;
@@ -234,22 +243,24 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
                 rs[r * RS + k] = __ldg(p.rot + int64_t(j0 + r) * D + k);
             }
             __syncthreads();
-            float acc[16];
+            if (cg < 8) {
+                float acc[16];
 #pragma unroll
-            for (int u = 0; u < 16; ++u) acc[u] = 0.f;
-            for (int k = 0; k < D; k += 4) {
-                const float r0 = rs[jl * RS + k], r1 = rs[jl * RS + k + 1], r2 = rs[jl * RS + k + 2], r3 = rs[jl * RS + k + 3];
+                for (int u = 0; u < 16; ++u) acc[u] = 0.f;
+                for (int k = 0; k < D; k += 4) {
+                    const float r0 = rs[jl * RS + k], r1 = rs[jl * RS + k + 1], r2 = rs[jl * RS + k + 2], r3 = rs[jl * RS + k + 3];
+#pragma unroll
+                    for (int u = 0; u < 16; ++u) {
+                        const float4 x = *reinterpret_cast<const float4*>(qf + (cg * 16 + u) * D + k);
+                        acc[u] = fmaf(x.x, r0, fmaf(x.y, r1, fmaf(x.z, r2, fmaf(x.w, r3, acc[u]))));
+                    }
+                }
+                const int j = j0 + jl;
 #pragma unroll
                 for (int u = 0; u < 16; ++u) {
-                    const float4 x = *reinterpret_cast<const float4*>(qf + (cg * 16 + u) * D + k);
-                    acc[u] = fmaf(x.x, r0, fmaf(x.y, r1, fmaf(x.z, r2, fmaf(x.w, r3, acc[u]))));
+                    const int m = cg * 16 + u;
+                    *reinterpret_cast<__half*>(smem + OFF_Q + chunk_off(m, j >> 3) + (j & 7) * 2) = __float2half_rn(acc[u]);
                 }
-            }
-            const int j = j0 + jl;
-#pragma unroll
-            for (int u = 0; u < 16; ++u) {
-                const int m = cg * 16 + u;
-                *reinterpret_cast<__half*>(smem + OFF_QR + chunk_off(m, j >> 3) + (j & 7) * 2) = __float2half_rn(acc[u]);
             }
         }
     }
@@ -259,298 +270,334 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
     tc_fence_after();
     const uint32_t tmem_base = slot[0];
 
-    // ---------------- per-row softmax state (threads 0 .. 127 own rows) ---------------------------------------------
-    const bool row_thread = tid < TM;
-    const int q_pos = (row_thread && row_valid(tid)) ? int(P.q_pos0 + tq0 + tid / GP) : -1;   // the latest position this row sees
-    const int64_t cta_q_max = P.q_pos0 + min(tq0 + P.QT, P.Tq) - 1;
+    const int64_t cta_q_max = P.q_pos0 + min(tq0 + P.QT, P.Tq) - 1;               // the latest position any row sees
     const int64_t min_q_pos = P.q_pos0 + tq0;                                      // the earliest position any (valid) row sits at
+    const uint32_t idesc_qk = make_idesc(false), idesc_pv = make_idesc(true);
+
+    // bounded wait on an mbarrier; a thread that runs out raises the abort flag for everybody
+    auto wait_bar = [&](uint32_t addr, uint32_t parity) -> bool {
+        for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+            if (mbar_try(addr, parity)) return true;
+            if ((i & 1023u) == 1023u && slot[1]) return false;
+        }
+        slot[1] = 1u;
+        atomicCAS(P.status, 0, ERR_WAIT);
+        return false;
+    };
+
+    // per-row softmax state (threads 0 .. 127 own rows)
+    const int q_pos = (tid < ROW_T && row_valid(tid)) ? int(P.q_pos0 + tq0 + tid / GP) : -1;   // the latest position this row sees
     float m_ref = -1e30f, m_thr = -1e30f, l_sum = 0.f, vsc = 1.f, vthr = VSC_CAP;
     const uint32_t t_row = tmem_base + (uint32_t((warp & 3) * 32) << 16);
-    const uint32_t idesc_qk = make_idesc(false), idesc_pv = make_idesc(true);
-    bool have_op = false, have_od = false;        // the accumulators hold sums (uniform over the CTA)
-    uint32_t ph_s = 0, ph_o = 0;
-    bool pv_pending = false;
+    bool have_op = false, have_od = false;        // the accumulators hold sums (same in every thread)
 
-    // bounded wait of every thread on an mbarrier; a thread that runs out raises the abort flag for everybody
-    auto wait_bar = [&](uint32_t bar, uint32_t parity) {
-        for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-            if (mbar_try(bar, parity)) return;
-            if ((i & 1023u) == 1023u && slot[2]) return;
-        }
-        slot[2] = 1u;
-        atomicCAS(P.status, 0, ERR_WAIT);
-    };
-
-    // One tile whose K / V / norms / positions are in shared memory: S, softmax, P, O += P V.
-    auto run_tile = [&](bool dense_region) {
-        // (1) scores
-        if (tid == 0) {
-            tc_fence_after();
-            const uint32_t a_tile = sbase + (dense_region ? OFF_QD : OFF_QR);
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-                umma_f16(tmem_base + COL_S, desc_kmajor(a_tile, ks), desc_kmajor(sbase + OFF_K, ks), idesc_qk, ks > 0 ? 1u : 0u);
-            umma_commit(bar_s);
-        }
-        wait_bar(bar_s, ph_s);
-        ph_s ^= 1u;
-        tc_fence_after();
-        if (row_thread) {
-            const float vmax = __uint_as_float(slot[1]);
-            const bool masked = slot[3] == 0u;                                // some token of the tile is hidden from some row (or dead)
-            // Reference maximum / value scale: refreshed for the whole warp when any row needs it (the tensor-memory loads
-            // and stores are warp-wide).  mx: the row's largest visible score of this tile.
-            auto refresh = [&](float mx) {
-                const float mn = fmaxf(fmaxf(m_ref, mx), -1e30f);
-                float a = ex2(m_ref - mn);
-                m_ref = mn; m_thr = mn + MAX_SLACK;
-                l_sum *= a;
-                if (vmax > vthr) {
-                    int eb = (__float_as_int(vmax) >> 23) & 0xff;
-                    eb = min(max(eb, 16), 240);
-                    const float nsc = __int_as_float((261 - eb) << 23);
-                    a *= nsc / vsc;
-                    vsc = nsc;
-                    vthr = VSC_CAP / nsc;
-                }
-#pragma unroll 1
-                for (int acc = 0; acc < 2; ++acc) {
-                    if (acc == 0 ? !have_op : !have_od) continue;
-                    const uint32_t col = acc == 0 ? COL_OP : COL_OD;
-#pragma unroll 1
-                    for (int c0 = 0; c0 < D; c0 += 32) {
-                        uint32_t v[32];
-                        tmem_ld32(t_row + col + c0, v);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * a);
-                        tmem_st32(t_row + col + c0, v);
-                    }
-                    tmem_st_wait();
-                }
-            };
-            // One sweep over the row's 128 scores: weights against the current reference, P = p * value norm * scale as fp16
-            // into the A-operand tile (row = this thread), the row's largest score alongside.  WRITE = false: the maximum only.
-            auto sweep = [&](bool write, float& mx, float& lsum) {
-                mx = -INFINITY; lsum = 0.f;
-#pragma unroll 1
-                for (int c0 = 0; c0 < TN; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(t_row + COL_S + c0, v);
-                    tmem_ld_wait();
-                    uint32_t h[16];
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        const float4 kn = *reinterpret_cast<const float4*>(s_kn + c0 + j);
-                        float s0 = __uint_as_float(v[j]) * kn.x, s1 = __uint_as_float(v[j + 1]) * kn.y;
-                        float s2 = __uint_as_float(v[j + 2]) * kn.z, s3 = __uint_as_float(v[j + 3]) * kn.w;
-                        if (masked) {
-                            const int4 ps = *reinterpret_cast<const int4*>(s_pos + c0 + j);
-                            s0 = ps.x <= q_pos ? s0 : -INFINITY; s1 = ps.y <= q_pos ? s1 : -INFINITY;
-                            s2 = ps.z <= q_pos ? s2 : -INFINITY; s3 = ps.w <= q_pos ? s3 : -INFINITY;
-                        }
-                        mx = fmaxf(fmaxf(mx, fmaxf(s0, s1)), fmaxf(s2, s3));
-                        if (write) {
-                            const float4 vn = *reinterpret_cast<const float4*>(s_vn + c0 + j);
-                            const float p0 = ex2(s0 - m_ref), p1 = ex2(s1 - m_ref), p2 = ex2(s2 - m_ref), p3 = ex2(s3 - m_ref);
-                            lsum += (p0 + p1) + (p2 + p3);
-                            h[j >> 1] = pack_h2(p0 * (vn.x * vsc), p1 * (vn.y * vsc));
-                            h[(j >> 1) + 1] = pack_h2(p2 * (vn.z * vsc), p3 * (vn.w * vsc));
-                        }
-                    }
-                    if (write) {
-#pragma unroll
-                        for (int c = 0; c < 4; ++c)
-                            *reinterpret_cast<uint4*>(smem + OFF_P + chunk_off(tid, (c0 >> 3) + c)) = make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
-                    }
-                }
-            };
-            float mx, lsum;
-            // the very first tile (no reference yet) and a tile that moves the value scale: settle the references first
-            if (__any_sync(0xffffffffu, m_ref <= -1e30f || vmax > vthr)) {
-                sweep(false, mx, lsum);
-                refresh(mx);
-            }
-            sweep(true, mx, lsum);
-            if (__any_sync(0xffffffffu, mx > m_thr)) {        // a score beyond the slack: new reference, weights again (rare)
-                refresh(mx);
-                sweep(true, mx, lsum);
-            }
-            l_sum += lsum;
-        }
-        fence_proxy_async();        // P (generic-proxy stores) before the tensor core reads it
-        tc_fence_before();
-        __syncthreads();
-        // (5) values
-        if (tid == 0) {
-            tc_fence_after();
-            const uint32_t col = dense_region ? COL_OD : COL_OP;
-            const bool have = dense_region ? have_od : have_op;
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-                umma_f16(tmem_base + col, desc_kmajor(sbase + OFF_P, ks), desc_mnmajor(sbase + OFF_V, ks), idesc_pv, (have || ks > 0) ? 1u : 0u);
-            umma_commit(bar_o);
-        }
-        if (dense_region) have_od = true; else have_op = true;
-        pv_pending = true;
-    };
-    // before the tiles are overwritten (and before O is touched): the previous tile's second product has finished
-    auto drain_pv = [&]() {
-        if (pv_pending) {
-            wait_bar(bar_o, ph_o);
-            ph_o ^= 1u;
-            tc_fence_after();
-            pv_pending = false;
-        }
-    };
-
-    // ---------------- packed tokens: absolute positions sink_len .. sink_len + c_len - 1 -----------------------------
-    {
-        const int64_t vis = min(p.c_len, cta_q_max - p.sink_len + 1);
-        for (int64_t tok0 = 0; tok0 < vis; tok0 += TN) {
-            drain_pv();
-            if (__syncthreads_or(int(slot[2]))) break;                        // everybody is past the previous tile; leave together after a failed wait
-            const int rows = int(min(int64_t(TN), p.c_len - tok0));
-            if (tid == 0) {
-                slot[1] = 0u;
-                slot[3] = (rows == TN && p.sink_len + tok0 + TN - 1 <= min_q_pos) ? 1u : 0u;
-            }
-            {
-                const uint32_t* src = reinterpret_cast<const uint32_t*>(p.k_hi + (kvl * p.c_ls + tok0) * (D / 2));
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const int i = tid + NT * k, r = i >> 4, w = i & 15;
-                    const uint32_t x = r < rows ? __ldg(src + i) : 0u;
-                    *reinterpret_cast<uint4*>(smem + OFF_K + chunk_off(r, w)) =
-                        make_uint4(t4[(x & 255u) * TREP + cp], t4[((x >> 8) & 255u) * TREP + cp], t4[((x >> 16) & 255u) * TREP + cp], t4[(x >> 24) * TREP + cp]);
-                }
-            }
-            {
-                const uint32_t* src = reinterpret_cast<const uint32_t*>(p.v_hi + (kvl * p.c_ls + tok0) * (D / 4));
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int i = tid + NT * k, r = i >> 3, w = i & 7;
-                    const uint32_t x = r < rows ? __ldg(src + i) : 0u;
-                    const uint2 a = t2[(x & 255u) * TREP + cp], bb = t2[((x >> 8) & 255u) * TREP + cp], cc = t2[((x >> 16) & 255u) * TREP + cp], ee = t2[(x >> 24) * TREP + cp];
-                    *reinterpret_cast<uint4*>(smem + OFF_V + chunk_off(r, 2 * w)) = make_uint4(a.x, a.y, bb.x, bb.y);
-                    *reinterpret_cast<uint4*>(smem + OFF_V + chunk_off(r, 2 * w + 1)) = make_uint4(cc.x, cc.y, ee.x, ee.y);
-                }
-            }
-            __syncthreads();                                                  // slot[1] reset before the maxima below
-            if (tid < TN) {
-                const bool live = tid < rows;
-                const int64_t n = kvl * p.c_ls + tok0 + (live ? tid : 0);
-                const float kn = live ? __ldg(p.k_norms + n) : 0.f, vn = live ? __ldg(p.v_norms + n) : 0.f;
-                s_kn[tid] = kn; s_vn[tid] = vn;
-                s_pos[tid] = live ? int(p.sink_len + tok0 + tid) : 0x7fffffff;
-                float vm = vn;
-#pragma unroll
-                for (int off = 16; off; off >>= 1) vm = fmaxf(vm, __shfl_xor_sync(0xffffffffu, vm, off));
-                if (lane == 0) atomicMax(const_cast<uint32_t*>(slot + 1), __float_as_uint(fmaxf(vm, 0.f)));
-            }
-            fence_proxy_async();
-            tc_fence_before();
-            __syncthreads();
-            run_tile(false);
-        }
-    }
-
-    // ---------------- uncompressed tokens: sink (positions 0 ..), recent (positions sink_len + c_len ..), raw query ----------------
-    {
+    // Tiles are numbered g = 0, 1, ... across both regions; tile g uses key / value / norm buffer g & 1 and score columns
+    // COL_S + 128 (g & 1).  Barrier phases follow from g: the per-buffer barriers complete once per two tiles, P_FULL and
+    // PV_DONE once per tile.
+    int g0 = 0;                                   // number of the region's first tile
+    for (int region = 0; region < 2; ++region) {
+        const bool dense_region = region == 1;
         const int64_t n_dense = p.sink_len + p.res_len;
-        // dense index t -> position: t < sink_len ? t : c_len + t; tokens past the CTA's last position are not visited
-        const int64_t vis_d = min(n_dense, max(p.sink_len, cta_q_max - p.c_len + 1));
-        for (int64_t tok0 = 0; tok0 < vis_d; tok0 += TN) {
-            drain_pv();
-            if (__syncthreads_or(int(slot[2]))) break;
-            if (tid == 0) {
-                slot[1] = 0u;
-                const int64_t tl = tok0 + TN - 1;                             // the tile's last token, if it has 128
-                slot[3] = (tl < n_dense && (tl < p.sink_len ? tl : p.c_len + tl) <= min_q_pos) ? 1u : 0u;
-            }
-            __syncthreads();
-            // two threads per token row: each converts 64 coordinates of the key row and of the value row; float32 /
-            // bfloat16 rows under a per-token power-of-two scale (largest magnitude into [2^7, 2^8)) whose inverse goes
-            // where the packed tokens have their norms
-            {
-                const int r = tid >> 1, hf = tid & 1;
-                const int64_t tok = tok0 + r;
-                const bool live = tok < n_dense;
-                const bool in_sink = tok < p.sink_len;
-                const int64_t e0 = live ? (in_sink ? kvl * p.sink_ls + tok : kvl * p.res_ls + (tok - p.sink_len)) * D + hf * (D / 2) : 0;
-                float inv_k = 0.f, inv_v = 0.f;
-#pragma unroll 1
-                for (int side = 0; side < 2; ++side) {
-                    const void* base = side == 0 ? (in_sink ? p.sink_k : p.res_k) : (in_sink ? p.sink_v : p.res_v);
-                    const uint32_t dst = side == 0 ? OFF_K : OFF_V;
-                    float sc = 1.f;
-                    if (p.dense_dtype == TQ_F16) {
+        // tokens of the region some row of the CTA sees: packed token t sits at position sink_len + t; uncompressed token t at
+        // t (sink) or c_len + t (recent)
+        const int64_t vis = dense_region ? min(n_dense, max(p.sink_len, cta_q_max - p.c_len + 1)) : min(p.c_len, cta_q_max - p.sink_len + 1);
+        const int n_tiles = vis > 0 ? int((vis + TN - 1) / TN) : 0;
+        if (dense_region) {
+            // the raw query takes the rotated one's place (every product of the packed region has completed)
+            for (int i = tid; i < TM * 16; i += NT) {
+                const int m = i >> 4, c = i & 15;
+                uint32_t h[4] = {0u, 0u, 0u, 0u};
+                if (row_valid(m)) {
+                    const int64_t e = row_q_index(m) + c * 8;
 #pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            const uint4 x = live ? __ldg(reinterpret_cast<const uint4*>(static_cast<const __half*>(base) + e0) + c) : make_uint4(0, 0, 0, 0);
-                            *reinterpret_cast<uint4*>(smem + dst + chunk_off(r, hf * 8 + c)) = x;
-                        }
-                    } else if (p.dense_dtype == TQ_BF16) {
-                        uint4 x[8];
-                        uint32_t mxb = 0u;
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            x[c] = live ? __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(base) + e0) + c) : make_uint4(0, 0, 0, 0);
-                            const uint32_t mm = 0x7fff7fffu;
-                            const uint32_t a = __vmaxu2(__vmaxu2(x[c].x & mm, x[c].y & mm), __vmaxu2(x[c].z & mm, x[c].w & mm));
-                            mxb = max(mxb, max(a & 0xffffu, a >> 16) << 16);
-                        }
-                        mxb = max(mxb, __shfl_xor_sync(0xffffffffu, mxb, 1));
-                        sc = stage_scale(mxb);
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            auto two = [&](uint32_t w) -> uint32_t { return pack_h2(__uint_as_float(w << 16) * sc, __uint_as_float(w & 0xffff0000u) * sc); };
-                            *reinterpret_cast<uint4*>(smem + dst + chunk_off(r, hf * 8 + c)) = make_uint4(two(x[c].x), two(x[c].y), two(x[c].z), two(x[c].w));
-                        }
-                    } else {
-                        uint4 x[16];
-                        uint32_t mxb = 0u;
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) {
-                            x[c] = live ? __ldg(reinterpret_cast<const uint4*>(static_cast<const float*>(base) + e0) + c) : make_uint4(0, 0, 0, 0);
-                            const uint32_t mm = 0x7fffffffu;
-                            mxb = max(mxb, max(max(x[c].x & mm, x[c].y & mm), max(x[c].z & mm, x[c].w & mm)));
-                        }
-                        mxb = max(mxb, __shfl_xor_sync(0xffffffffu, mxb, 1));
-                        sc = stage_scale(mxb);
-#pragma unroll
-                        for (int c = 0; c < 8; ++c)
-                            *reinterpret_cast<uint4*>(smem + dst + chunk_off(r, hf * 8 + c)) =
-                                make_uint4(pack_h2(__uint_as_float(x[2 * c].x) * sc, __uint_as_float(x[2 * c].y) * sc),
-                                           pack_h2(__uint_as_float(x[2 * c].z) * sc, __uint_as_float(x[2 * c].w) * sc),
-                                           pack_h2(__uint_as_float(x[2 * c + 1].x) * sc, __uint_as_float(x[2 * c + 1].y) * sc),
-                                           pack_h2(__uint_as_float(x[2 * c + 1].z) * sc, __uint_as_float(x[2 * c + 1].w) * sc));
-                    }
-                    if (side == 0) inv_k = live ? 1.f / sc : 0.f; else inv_v = live ? 1.f / sc : 0.f;
+                    for (int u = 0; u < 4; ++u) h[u] = pack_h2(load_as_f32(P.q, P.q_dtype, e + 2 * u) * f, load_as_f32(P.q, P.q_dtype, e + 2 * u + 1) * f);
                 }
-                if (hf == 0) {
-                    s_kn[r] = inv_k; s_vn[r] = inv_v;
-                    const int64_t pos = in_sink ? tok : p.c_len + tok;
-                    s_pos[r] = live ? int(pos) : 0x7fffffff;
-                }
-                float vm = inv_v;
-#pragma unroll
-                for (int off = 16; off; off >>= 1) vm = fmaxf(vm, __shfl_xor_sync(0xffffffffu, vm, off));
-                if (lane == 0) atomicMax(const_cast<uint32_t*>(slot + 1), __float_as_uint(vm));
+                *reinterpret_cast<uint4*>(smem + OFF_Q + chunk_off(m, c)) = make_uint4(h[0], h[1], h[2], h[3]);
             }
             fence_proxy_async();
             tc_fence_before();
             __syncthreads();
-            run_tile(true);
+            tc_fence_after();
         }
+
+        if (warp >= 4 && warp < 8) {
+            // ======================= producers: unpack tile g into buffer g & 1 =======================
+            const int pt = tid - ROW_T;                                       // 0 .. 127
+            for (int it = 0; it < n_tiles; ++it) {
+                const int g = g0 + it, bf = g & 1;
+                if (g >= 2 && !wait_bar(bar(KV_FREE + bf), uint32_t(((g >> 1) - 1) & 1))) break;     // the products of tile g - 2 have read the buffer
+                const int64_t tok0 = int64_t(it) * TN;
+                unsigned char* kt = smem + OFF_K + bf * TILE_BYTES;
+                unsigned char* vt = smem + OFF_V + bf * TILE_BYTES;
+                float* kn = s_kn + bf * TN; float* vn = s_vn + bf * TN; int* ps = s_pos + bf * TN;
+                float my_vn = 0.f;
+                if (!dense_region) {
+                    const int rows = int(min(int64_t(TN), p.c_len - tok0));
+                    if (pt == 0) slot[4 + bf] = (rows == TN && p.sink_len + tok0 + TN - 1 <= min_q_pos) ? 1u : 0u;
+                    const uint32_t* ksrc = reinterpret_cast<const uint32_t*>(p.k_hi + (kvl * p.c_ls + tok0) * (D / 2));
+                    const uint32_t* vsrc = reinterpret_cast<const uint32_t*>(p.v_hi + (kvl * p.c_ls + tok0) * (D / 4));
+                    uint32_t kx[16], vx[8];
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) {
+                        const int i = pt + PROD_T * k, r = i >> 4;
+                        kx[k] = r < rows ? __ldg(ksrc + i) : 0u;
+                    }
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const int i = pt + PROD_T * k, r = i >> 3;
+                        vx[k] = r < rows ? __ldg(vsrc + i) : 0u;
+                    }
+                    {
+                        const bool live = pt < rows;
+                        const int64_t n = kvl * p.c_ls + tok0 + (live ? pt : 0);
+                        const float a = live ? __ldg(p.k_norms + n) : 0.f;
+                        my_vn = live ? __ldg(p.v_norms + n) : 0.f;
+                        kn[pt] = a; vn[pt] = my_vn;
+                        ps[pt] = live ? int(p.sink_len + tok0 + pt) : 0x7fffffff;
+                    }
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) {
+                        const int i = pt + PROD_T * k, r = i >> 4, w = i & 15;
+                        const uint32_t x = kx[k];
+                        *reinterpret_cast<uint4*>(kt + chunk_off(r, w)) =
+                            make_uint4(t4[(x & 255u) * TREP + cp], t4[((x >> 8) & 255u) * TREP + cp], t4[((x >> 16) & 255u) * TREP + cp], t4[(x >> 24) * TREP + cp]);
+                    }
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const int i = pt + PROD_T * k, r = i >> 3, w = i & 7;
+                        const uint32_t x = vx[k];
+                        const uint2 a = t2[(x & 255u) * TREP + cp], bb = t2[((x >> 8) & 255u) * TREP + cp], cc = t2[((x >> 16) & 255u) * TREP + cp], ee = t2[(x >> 24) * TREP + cp];
+                        *reinterpret_cast<uint4*>(vt + chunk_off(r, 2 * w)) = make_uint4(a.x, a.y, bb.x, bb.y);
+                        *reinterpret_cast<uint4*>(vt + chunk_off(r, 2 * w + 1)) = make_uint4(cc.x, cc.y, ee.x, ee.y);
+                    }
+                } else {
+                    // one thread per token row; float32 / bfloat16 rows under a per-token power-of-two scale (largest magnitude into
+                    // [2^7, 2^8)) whose inverse goes where the packed tokens have their norms: a pass for the maximum, a pass to convert
+                    const int r = pt;
+                    const int64_t tok = tok0 + r;
+                    const bool live = tok < n_dense;
+                    const bool in_sink = tok < p.sink_len;
+                    const int64_t e0 = live ? (in_sink ? kvl * p.sink_ls + tok : kvl * p.res_ls + (tok - p.sink_len)) * D : 0;
+                    if (pt == 0) {
+                        const int64_t tl = tok0 + TN - 1;                     // the tile's last token, if it has 128
+                        slot[4 + bf] = (tl < n_dense && (tl < p.sink_len ? tl : p.c_len + tl) <= min_q_pos) ? 1u : 0u;
+                    }
+                    float inv[2] = {0.f, 0.f};
+#pragma unroll 1
+                    for (int side = 0; side < 2; ++side) {
+                        const void* base = side == 0 ? (in_sink ? p.sink_k : p.res_k) : (in_sink ? p.sink_v : p.res_v);
+                        unsigned char* dst = side == 0 ? kt : vt;
+                        float sc = 1.f;
+                        if (p.dense_dtype == TQ_F16) {
+#pragma unroll 4
+                            for (int c = 0; c < 16; ++c)
+                                *reinterpret_cast<uint4*>(dst + chunk_off(r, c)) =
+                                    live ? __ldg(reinterpret_cast<const uint4*>(static_cast<const __half*>(base) + e0) + c) : make_uint4(0, 0, 0, 0);
+                        } else if (p.dense_dtype == TQ_BF16) {
+                            const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(base) + e0);
+                            uint32_t mxb = 0u;
+                            if (live) {
+#pragma unroll 4
+                                for (int c = 0; c < 16; ++c) {
+                                    const uint4 x = __ldg(src + c);
+                                    const uint32_t mm = 0x7fff7fffu;
+                                    const uint32_t a = __vmaxu2(__vmaxu2(x.x & mm, x.y & mm), __vmaxu2(x.z & mm, x.w & mm));
+                                    mxb = max(mxb, max(a & 0xffffu, a >> 16) << 16);
+                                }
+                            }
+                            sc = stage_scale(mxb);
+                            auto two = [&](uint32_t w) -> uint32_t { return pack_h2(__uint_as_float(w << 16) * sc, __uint_as_float(w & 0xffff0000u) * sc); };
+#pragma unroll 4
+                            for (int c = 0; c < 16; ++c) {
+                                const uint4 x = live ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
+                                *reinterpret_cast<uint4*>(dst + chunk_off(r, c)) = make_uint4(two(x.x), two(x.y), two(x.z), two(x.w));
+                            }
+                        } else {
+                            const uint4* src = reinterpret_cast<const uint4*>(static_cast<const float*>(base) + e0);
+                            uint32_t mxb = 0u;
+                            if (live) {
+#pragma unroll 4
+                                for (int c = 0; c < 32; ++c) {
+                                    const uint4 x = __ldg(src + c);
+                                    const uint32_t mm = 0x7fffffffu;
+                                    mxb = max(mxb, max(max(x.x & mm, x.y & mm), max(x.z & mm, x.w & mm)));
+                                }
+                            }
+                            sc = stage_scale(mxb);
+#pragma unroll 4
+                            for (int c = 0; c < 16; ++c) {
+                                const uint4 x = live ? __ldg(src + 2 * c) : make_uint4(0, 0, 0, 0), y = live ? __ldg(src + 2 * c + 1) : make_uint4(0, 0, 0, 0);
+                                *reinterpret_cast<uint4*>(dst + chunk_off(r, c)) =
+                                    make_uint4(pack_h2(__uint_as_float(x.x) * sc, __uint_as_float(x.y) * sc), pack_h2(__uint_as_float(x.z) * sc, __uint_as_float(x.w) * sc),
+                                               pack_h2(__uint_as_float(y.x) * sc, __uint_as_float(y.y) * sc), pack_h2(__uint_as_float(y.z) * sc, __uint_as_float(y.w) * sc));
+                            }
+                        }
+                        inv[side] = live ? 1.f / sc : 0.f;
+                    }
+                    kn[r] = inv[0]; vn[r] = inv[1];
+                    ps[r] = live ? int(in_sink ? tok : p.c_len + tok) : 0x7fffffff;
+                    my_vn = inv[1];
+                }
+#pragma unroll
+                for (int off = 16; off; off >>= 1) my_vn = fmaxf(my_vn, __shfl_xor_sync(0xffffffffu, my_vn, off));
+                if (lane == 0) slot[8 + bf * 4 + (warp - 4)] = __float_as_uint(fmaxf(my_vn, 0.f));     // this warp's largest value norm
+                fence_proxy_async();                                          // the tiles (generic-proxy stores) before the tensor core reads them
+                mbar_arrive(bar(KV_FULL + bf));
+            }
+        } else if (warp == 8) {
+            // ======================= MMA issue: one thread =======================
+            if (lane == 0) {
+                auto issue_pv = [&](int g) -> bool {                          // O += P V of tile g
+                    const int bf = g & 1;
+                    if (!wait_bar(bar(P_FULL), uint32_t(g & 1))) return false;
+                    tc_fence_after();
+                    const uint32_t col = dense_region ? COL_OD : COL_OP;
+                    const bool first = g == g0;                               // the region's first product starts its accumulator
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks)
+                        umma_f16(tmem_base + col, desc_kmajor(sbase + OFF_P, ks), desc_mnmajor(sbase + OFF_V + bf * TILE_BYTES, ks), idesc_pv,
+                                 (!first || ks > 0) ? 1u : 0u);
+                    umma_commit(bar(KV_FREE + bf));
+                    umma_commit(bar(PV_DONE));
+                    return true;
+                };
+                bool ok = true;
+                for (int it = 0; it < n_tiles && ok; ++it) {
+                    const int g = g0 + it, bf = g & 1;
+                    ok = wait_bar(bar(KV_FULL + bf), uint32_t((g >> 1) & 1));
+                    if (ok && g >= 2) ok = wait_bar(bar(S_FREE + bf), uint32_t(((g >> 1) - 1) & 1));     // the rows have read the scores of tile g - 2
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks)
+                        umma_f16(tmem_base + COL_S + bf * TN, desc_kmajor(sbase + OFF_Q, ks), desc_kmajor(sbase + OFF_K + bf * TILE_BYTES, ks), idesc_qk, ks > 0 ? 1u : 0u);
+                    umma_commit(bar(S_FULL + bf));
+                    if (it > 0) ok = issue_pv(g - 1);                         // the scores of tile g are under way while the rows finish tile g - 1
+                }
+                if (ok && n_tiles > 0) issue_pv(g0 + n_tiles - 1);
+            }
+        } else {
+            // ======================= rows: softmax of tile g, P for its second product =======================
+            for (int it = 0; it < n_tiles; ++it) {
+                const int g = g0 + it, bf = g & 1;
+                // the tile's norms, positions and flags come from the producers directly; the scores from the tensor core
+                if (!wait_bar(bar(KV_FULL + bf), uint32_t((g >> 1) & 1))) break;
+                if (!wait_bar(bar(S_FULL + bf), uint32_t((g >> 1) & 1))) break;
+                // P and the O rows are free once the second product of tile g - 1 has finished
+                if (g >= 1 && !wait_bar(bar(PV_DONE), uint32_t((g - 1) & 1))) break;
+                tc_fence_after();
+                const float* kn_t = s_kn + bf * TN; const float* vn_t = s_vn + bf * TN; const int* ps_t = s_pos + bf * TN;
+                const float vmax = fmaxf(fmaxf(__uint_as_float(slot[8 + bf * 4]), __uint_as_float(slot[9 + bf * 4])),
+                                         fmaxf(__uint_as_float(slot[10 + bf * 4]), __uint_as_float(slot[11 + bf * 4])));
+                const bool masked = slot[4 + bf] == 0u;                       // some token of the tile is hidden from some row (or dead)
+                const uint32_t s_col = t_row + COL_S + bf * TN;
+                // Reference maximum / value scale: refreshed for the whole warp when any row needs it (the tensor-memory loads
+                // and stores are warp-wide).  mx: the row's largest visible score of this tile.
+                auto refresh = [&](float mx) {
+                    const float mn = fmaxf(fmaxf(m_ref, mx), -1e30f);
+                    float a = ex2(m_ref - mn);
+                    m_ref = mn; m_thr = mn + MAX_SLACK;
+                    l_sum *= a;
+                    if (vmax > vthr) {
+                        int eb = (__float_as_int(vmax) >> 23) & 0xff;
+                        eb = min(max(eb, 16), 240);
+                        const float nsc = __int_as_float((261 - eb) << 23);
+                        a *= nsc / vsc;
+                        vsc = nsc;
+                        vthr = VSC_CAP / nsc;
+                    }
+#pragma unroll 1
+                    for (int acc = 0; acc < 2; ++acc) {
+                        // an accumulator holds sums once a product of its region has completed: the packed one from the second packed
+                        // tile on, the other from the second uncompressed tile on (the region's first product overwrites)
+                        const bool holds = acc == 0 ? have_op : have_od;
+                        if (!holds) continue;
+                        const uint32_t col = acc == 0 ? COL_OP : COL_OD;
+#pragma unroll 1
+                        for (int c0 = 0; c0 < D; c0 += 32) {
+                            uint32_t v[32];
+                            tmem_ld32(t_row + col + c0, v);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * a);
+                            tmem_st32(t_row + col + c0, v);
+                        }
+                        tmem_st_wait();
+                    }
+                };
+                // One sweep over the row's 128 scores: weights against the current reference, P = p * value norm * scale as fp16
+                // into the A-operand tile (row = this thread), the row's largest score alongside.  write = false: the maximum only.
+                auto sweep = [&](bool write, float& mx, float& lsum) {
+                    mx = -INFINITY; lsum = 0.f;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < TN; c0 += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(s_col + c0, v);
+                        tmem_ld_wait();
+                        uint32_t h[16];
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 kn = *reinterpret_cast<const float4*>(kn_t + c0 + j);
+                            float s0 = __uint_as_float(v[j]) * kn.x, s1 = __uint_as_float(v[j + 1]) * kn.y;
+                            float s2 = __uint_as_float(v[j + 2]) * kn.z, s3 = __uint_as_float(v[j + 3]) * kn.w;
+                            if (masked) {
+                                const int4 ps = *reinterpret_cast<const int4*>(ps_t + c0 + j);
+                                s0 = ps.x <= q_pos ? s0 : -INFINITY; s1 = ps.y <= q_pos ? s1 : -INFINITY;
+                                s2 = ps.z <= q_pos ? s2 : -INFINITY; s3 = ps.w <= q_pos ? s3 : -INFINITY;
+                            }
+                            mx = fmaxf(fmaxf(mx, fmaxf(s0, s1)), fmaxf(s2, s3));
+                            if (write) {
+                                const float4 vn = *reinterpret_cast<const float4*>(vn_t + c0 + j);
+                                const float p0 = ex2(s0 - m_ref), p1 = ex2(s1 - m_ref), p2 = ex2(s2 - m_ref), p3 = ex2(s3 - m_ref);
+                                lsum += (p0 + p1) + (p2 + p3);
+                                h[j >> 1] = pack_h2(p0 * (vn.x * vsc), p1 * (vn.y * vsc));
+                                h[(j >> 1) + 1] = pack_h2(p2 * (vn.z * vsc), p3 * (vn.w * vsc));
+                            }
+                        }
+                        if (write) {
+#pragma unroll
+                            for (int c = 0; c < 4; ++c)
+                                *reinterpret_cast<uint4*>(smem + OFF_P + chunk_off(tid, (c0 >> 3) + c)) = make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+                        }
+                    }
+                };
+                have_op = dense_region ? have_op : it >= 1;
+                have_od = dense_region && it >= 1;
+                float mx, lsum;
+                // the very first tile (no reference yet; every valid row sees its first token) and a tile that moves the value
+                // scale: settle the references first
+                if (g == 0 || vmax > vthr) {
+                    sweep(false, mx, lsum);
+                    refresh(mx);
+                }
+                sweep(true, mx, lsum);
+                if (__any_sync(0xffffffffu, mx > m_thr)) {    // a score beyond the slack: new reference, weights again (rare)
+                    refresh(mx);
+                    sweep(true, mx, lsum);
+                }
+                l_sum += lsum;
+                tc_fence_before();                                            // this thread's tensor-memory loads of the scores are complete
+                mbar_arrive(bar(S_FREE + bf));
+                fence_proxy_async();                                          // P (generic-proxy stores) before the tensor core reads it
+                mbar_arrive(bar(P_FULL));
+            }
+        }
+        // ---- end of the region: every product has completed before anything is reused ----
+        if (n_tiles > 0) wait_bar(bar(PV_DONE), uint32_t((g0 + n_tiles - 1) & 1));
+        tc_fence_after();
+        if (n_tiles > 0) { if (dense_region) have_od = true; else have_op = true; }
+        g0 += n_tiles;
+        tc_fence_before();
+        if (__syncthreads_or(int(slot[1]))) break;                            // leave together after a failed wait
     }
-    drain_pv();
 
     // ---------------- finish: value scales, rotation of the packed part, normalise, store ---------------------------
     __syncthreads();                                                              // the tiles are dead
+    tc_fence_after();
     float* fd = reinterpret_cast<float*>(smem + OFF_FD);                          // [128][129] sums of the uncompressed part
     float* fp = reinterpret_cast<float*>(smem + OFF_FP);                          // [128][129] sums of the packed part, rotated space
-    if (row_thread) {
+    const bool failed = slot[1] != 0u;
+    if (tid < ROW_T) {
         const float ip = 1.f / (vsc * p.v_scale_hi), id = 1.f / vsc;
 #pragma unroll 1
         for (int c0 = 0; c0 < D; c0 += 32) {
@@ -566,7 +613,7 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
     }
     tc_fence_before();
     __syncthreads();
-    {
+    if (warp < 8) {
         // out[m][j] = (sum_k fp[m][k] R[k][j] + fd[m][j]) / l[m]  (y @ R, rotation.py:68-78): warp -> 16 rows, lane -> j = lane + 32 i
         float acc[16][4];
 #pragma unroll
@@ -586,7 +633,6 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
                 }
             }
         }
-        const bool failed = slot[2] != 0u;
 #pragma unroll
         for (int u = 0; u < 16; ++u) {
             const int m = warp * 16 + u;
@@ -602,7 +648,7 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
     }
     // ---------------- teardown --------------------------------------------------------------------------------------
     __syncthreads();
-    if (warp == 4) {
+    if (warp == 8) {
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
