@@ -43,7 +43,7 @@ constexpr uint32_t OFF_P = 5 * TILE_BYTES;
 constexpr uint32_t OFF_KN = 6 * TILE_BYTES;                                 // float [2][128] key norms (or inverse staging scales)
 constexpr uint32_t OFF_VN = OFF_KN + 1024;                                  // float [2][128]
 constexpr uint32_t OFF_POS = OFF_VN + 1024;                                 // int   [2][128] absolute positions of the tile's tokens
-constexpr int TREP = 4;                                                     // copies of every table entry (lane l reads copy l mod 4)
+constexpr int TREP = 8;                                                     // copies of every table entry (lane l reads copy l mod 8)
 constexpr uint32_t OFF_T4 = OFF_POS + 1024;                                 // uint  [256][TREP] byte of two 4-bit codes -> half2
 constexpr uint32_t OFF_T2 = OFF_T4 + 1024 * TREP;                           // uint2 [256][TREP] byte of four 2-bit codes -> 4 halves
 constexpr uint32_t OFF_CTAB = OFF_T2 + 2048 * TREP;                         // half  [32]
@@ -323,6 +323,31 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
         if (warp >= 4 && warp < 8) {
             // ======================= producers: unpack tile g into buffer g & 1 =======================
             const int pt = tid - ROW_T;                                       // 0 .. 127
+            // packed region: the words and norms of a tile are requested one tile ahead, so that their latency passes while
+            // the thread waits for the buffer and converts the previous tile
+            uint32_t kx[16], vx[8];
+            float nk = 0.f, nv = 0.f;
+            auto request_packed = [&](int it) {
+                const int64_t tok0 = int64_t(it) * TN;
+                const int rows = int(min(int64_t(TN), p.c_len - tok0));
+                const uint32_t* ksrc = reinterpret_cast<const uint32_t*>(p.k_hi + (kvl * p.c_ls + tok0) * (D / 2));
+                const uint32_t* vsrc = reinterpret_cast<const uint32_t*>(p.v_hi + (kvl * p.c_ls + tok0) * (D / 4));
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
+                    const int i = pt + PROD_T * k, r = i >> 4;
+                    kx[k] = r < rows ? __ldg(ksrc + i) : 0u;
+                }
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int i = pt + PROD_T * k, r = i >> 3;
+                    vx[k] = r < rows ? __ldg(vsrc + i) : 0u;
+                }
+                const bool live = pt < rows;
+                const int64_t n = kvl * p.c_ls + tok0 + (live ? pt : 0);
+                nk = live ? __ldg(p.k_norms + n) : 0.f;
+                nv = live ? __ldg(p.v_norms + n) : 0.f;
+            };
+            if (!dense_region && n_tiles > 0) request_packed(0);
             for (int it = 0; it < n_tiles; ++it) {
                 const int g = g0 + it, bf = g & 1;
                 if (g >= 2 && !wait_bar(bar(KV_FREE + bf), uint32_t(((g >> 1) - 1) & 1))) break;     // the products of tile g - 2 have read the buffer
@@ -334,27 +359,9 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
                 if (!dense_region) {
                     const int rows = int(min(int64_t(TN), p.c_len - tok0));
                     if (pt == 0) slot[4 + bf] = (rows == TN && p.sink_len + tok0 + TN - 1 <= min_q_pos) ? 1u : 0u;
-                    const uint32_t* ksrc = reinterpret_cast<const uint32_t*>(p.k_hi + (kvl * p.c_ls + tok0) * (D / 2));
-                    const uint32_t* vsrc = reinterpret_cast<const uint32_t*>(p.v_hi + (kvl * p.c_ls + tok0) * (D / 4));
-                    uint32_t kx[16], vx[8];
-#pragma unroll
-                    for (int k = 0; k < 16; ++k) {
-                        const int i = pt + PROD_T * k, r = i >> 4;
-                        kx[k] = r < rows ? __ldg(ksrc + i) : 0u;
-                    }
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        const int i = pt + PROD_T * k, r = i >> 3;
-                        vx[k] = r < rows ? __ldg(vsrc + i) : 0u;
-                    }
-                    {
-                        const bool live = pt < rows;
-                        const int64_t n = kvl * p.c_ls + tok0 + (live ? pt : 0);
-                        const float a = live ? __ldg(p.k_norms + n) : 0.f;
-                        my_vn = live ? __ldg(p.v_norms + n) : 0.f;
-                        kn[pt] = a; vn[pt] = my_vn;
-                        ps[pt] = live ? int(p.sink_len + tok0 + pt) : 0x7fffffff;
-                    }
+                    my_vn = nv;
+                    kn[pt] = nk; vn[pt] = nv;
+                    ps[pt] = pt < rows ? int(p.sink_len + tok0 + pt) : 0x7fffffff;
 #pragma unroll
                     for (int k = 0; k < 16; ++k) {
                         const int i = pt + PROD_T * k, r = i >> 4, w = i & 15;
@@ -370,6 +377,7 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
                         *reinterpret_cast<uint4*>(vt + chunk_off(r, 2 * w)) = make_uint4(a.x, a.y, bb.x, bb.y);
                         *reinterpret_cast<uint4*>(vt + chunk_off(r, 2 * w + 1)) = make_uint4(cc.x, cc.y, ee.x, ee.y);
                     }
+                    if (it + 1 < n_tiles) request_packed(it + 1);
                 } else {
                     // one thread per token row; float32 / bfloat16 rows under a per-token power-of-two scale (largest magnitude into
                     // [2^7, 2^8)) whose inverse goes where the packed tokens have their norms: a pass for the maximum, a pass to convert
@@ -529,11 +537,7 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
                 // into the A-operand tile (row = this thread), the row's largest score alongside.  write = false: the maximum only.
                 auto sweep = [&](bool write, float& mx, float& lsum) {
                     mx = -INFINITY; lsum = 0.f;
-#pragma unroll 1
-                    for (int c0 = 0; c0 < TN; c0 += 32) {
-                        uint32_t v[32];
-                        tmem_ld32(s_col + c0, v);
-                        tmem_ld_wait();
+                    auto chunk = [&](const uint32_t (&v)[32], int c0) {       // 32 scores: columns c0 .. c0 + 31
                         uint32_t h[16];
 #pragma unroll
                         for (int j = 0; j < 32; j += 4) {
@@ -559,6 +563,19 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
                             for (int c = 0; c < 4; ++c)
                                 *reinterpret_cast<uint4*>(smem + OFF_P + chunk_off(tid, (c0 >> 3) + c)) = make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
                         }
+                    };
+                    // the next 32 columns are on their way from tensor memory while the current ones are worked on
+                    uint32_t va[32], vb[32];
+                    tmem_ld32(s_col, va);
+                    tmem_ld_wait();
+#pragma unroll 1
+                    for (int c0 = 0; c0 < TN; c0 += 64) {
+                        tmem_ld32(s_col + c0 + 32, vb);
+                        chunk(va, c0);
+                        tmem_ld_wait();
+                        if (c0 + 64 < TN) tmem_ld32(s_col + c0 + 64, va);
+                        chunk(vb, c0 + 32);
+                        tmem_ld_wait();
                     }
                 };
                 have_op = dense_region ? have_op : it >= 1;
