@@ -99,7 +99,7 @@ int tq_quantize_pack(const tq_quantize_args* a, void* stream);
 
 /* The tensor-core quantize kernel (fp16 rows, d = 128) and the 4-bit-key / 2-bit-value decode kernel wait on
  * mbarriers with an iteration limit; if a wait ever runs out the kernel drains and finishes, and this returns the
- * code of the first such wait on the current device (quantize 1-9, decode 101-103, several-query-token attention 104, gather wait 201; 0 = none).  Synchronises the
+ * code of the first such wait on the current device (quantize 1-9, decode 101-103, several-query-token attention 104, dequantize 105, gather wait 201; 0 = none).  Synchronises the
  * device; no reference counterpart. */
 int tq_device_status(void);
 /* Back to 0 (after the caller has dealt with a reported time-out). */
@@ -305,6 +305,8 @@ float tq_fp16_table_scale(const float* centroids_host, int n);
 
 /* Host-side tuning knobs of the split heuristic (process-wide; no reference counterpart):
  *   "decode_ctas_per_sm" 1..8, "decode_splits" 0 (auto)..448, "decode_force_general" 0/1,
+ *   "dequantize_tc" 0/1 (tq_dequantize at d = 64 / 96 / 128 without QJL correction: the tcgen05 kernel, default, or always the
+ *   CUDA-core row kernel),
  *   "prefill_tc" 0/1 (tq_prefill_attn at d = 128 with 4-bit keys / 2-bit values: the tcgen05 kernel, default, or always
  *   the mma.sync kernel),
  *   "decode_pdl" 0/1 (programmatic dependent launch: a call's prologue overlaps the previous kernel's tail),

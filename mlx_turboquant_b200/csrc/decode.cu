@@ -590,6 +590,7 @@ static int g_tune_wait_polls = 2000000;  // polls of a word of a gather before t
 constexpr int64_t MAX_AWAIT_WORDS_IN_KERNEL = 8192;
 static int g_tune_force_general = 0;   // 1: never take the direct path (testing)
 static int g_tune_splits = 0;          // > 0: fixed number of packed splits
+extern int g_tune_dequantize_tc;       // rowops.cu: 0 = dequantize always on the CUDA-core row kernel
 extern int g_tune_prefill_tc;          // prefill.cu: 0 = several-query-token attention always on the mma.sync kernel
 static int g_tune_pdl = 1;             // programmatic dependent launch between consecutive calls
 
@@ -823,6 +824,7 @@ extern "C" int tq_set_tuning(const char* key, int value) {
     else if (k == "decode_splits" && value >= 0 && value <= MAX_SPLITS - 64) g_tune_splits = value;
     else if (k == "gather_wait_polls" && value >= 1000 && value <= 4000000) g_tune_wait_polls = value;
     else if (k == "prefill_tc" && (value == 0 || value == 1)) g_tune_prefill_tc = value;
+    else if (k == "dequantize_tc" && (value == 0 || value == 1)) g_tune_dequantize_tc = value;
     else return fail(TQ_ERR_INVALID, "tq_set_tuning: unknown key or bad value: %s=%d", key, value);
     return TQ_OK;
 }

@@ -337,6 +337,11 @@ extern "C" int tq_quantize_pack(const tq_quantize_args* q, void* stream) {
     return launch_rowops(a, s, "tq_quantize_pack");
 }
 
+namespace tq {
+int tq_dequantize_tc(const tq_dequantize_args* q, cudaStream_t s, bool* handled);      // dequantize_tc.cu
+int g_tune_dequantize_tc = 1;      // 0: always the row kernel (testing)
+}  // namespace tq
+
 extern "C" int tq_dequantize(const tq_dequantize_args* q, void* stream) {
     if (!q) return fail(TQ_ERR_INVALID, "tq_dequantize: null args");
     if (!d_ok(q->d)) return fail(TQ_ERR_UNSUPPORTED, "tq_dequantize: d=%d (need a multiple of 16 in 16..256)", q->d);
@@ -346,6 +351,11 @@ extern "C" int tq_dequantize(const tq_dequantize_args* q, void* stream) {
     if (!q->packed_hi || !q->norms || !q->cent_hi || !q->rot || !q->out) return fail(TQ_ERR_INVALID, "tq_dequantize: null pointer");
     if (q->bits_lo && (!q->packed_lo || !q->cent_lo)) return fail(TQ_ERR_INVALID, "tq_dequantize: fractional mode needs packed_lo and cent_lo");
     if (q->qjl_bits && (!q->qjl_proj || !q->qjl_gamma)) return fail(TQ_ERR_INVALID, "tq_dequantize: QJL needs proj and gamma");
+    if (g_tune_dequantize_tc) {
+        bool handled = false;
+        const int rc = tq_dequantize_tc(q, static_cast<cudaStream_t>(stream), &handled);
+        if (handled) return rc;
+    }
     RowArgs a{};
     a.mode = MODE_DEQUANT; a.d = q->d; a.inverse = 1; a.n_lanes = q->n_lanes; a.n_rows = q->n_rows;
     a.rot = q->rot; a.in_hi = q->packed_hi; a.in_lo = q->packed_lo; a.norms_in = q->norms; a.in_lane_stride = q->in_lane_stride;
