@@ -382,6 +382,41 @@ def bench_prefill(torch, dev, steps, warmup):
             "kernel": "prefill_attn_kernel<128> (64 query columns per CTA, stages unpacked to fp16 in shared memory, mma.sync)"}
 
 
+def bench_dequantize(torch, dev, steps, warmup, peak):
+    """The reference's own read path: dense reassembly of the packed middle (cache.py:276-343) - unpack, centroid lookup,
+    inverse rotation, scale - for 16 layers' worth of C1-shaped caches at once (16 x 8 KV heads x 32512 tokens, head_dim 128;
+    4-bit keys and 2-bit values -> fp16 rows).  Algorithmic bytes per row: packed codes + norm in, 256 B out."""
+    from mlx_turboquant_b200 import kernels
+    from mlx_turboquant_b200.codebook import get_codebook
+    from mlx_turboquant_b200.rotation import get_rotation_matrix
+    rot = get_rotation_matrix(D, 42, dev)
+    n_l, t = 16, T_C
+    g = torch.Generator(device=dev).manual_seed(2300)
+    sides = []
+    for bits in (4, 2):
+        cent, _ = get_codebook(D, bits, dev)
+        sides.append(dict(bits=bits, cent=cent, p=torch.randint(0, 256, (n_l, HKV, t, D * bits // 8), dtype=torch.uint8, device=dev, generator=g),
+                          n=torch.rand(n_l, HKV, t, device=dev, generator=g) + 0.5, o=torch.empty(n_l, HKV, t, D, dtype=torch.float16, device=dev)))
+
+    def step():
+        for sd in sides:
+            kernels.dequantize_rows(sd["p"], None, sd["n"], rot, sd["cent"], sd["bits"], None, 0, D, out=sd["o"])
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / steps
+    nbytes = sum(sd["p"].numel() + sd["n"].numel() * 4 + sd["o"].numel() * 2 for sd in sides)
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"workload": "llama31_8b_dense_reassembly_16layers_ctx32768_k4v2_fp16", "ms_per_step": ms, "rows": 2 * n_l * HKV * t,
+            "hbm_gbs": gbs, "frac_of_peak": gbs / peak, "kernel": "dequantize_tc_kernel (tcgen05: three split products, accumulators in tensor memory)"}
+
+
 def bench_head_split(torch, dist, dev, world, rank, steps, warmup):
     """N > 1: the headline workload as ONE sequence whose KV heads are dealt to the GPUs (strong scaling of a single
     sequence), timed three ways in the same process group: every GPU keeps its own heads' outputs (no exchange); the
@@ -754,6 +789,8 @@ def run_b200(args):
             line["secondary"]["compress_qjl_d96_b16"] = bench_quantize_c3(torch, dev, 3, 2, peak)
         if "decode_c3" in legs:
             line["secondary"]["decode_qjl_d96_b16"] = bench_c3(torch, dev, 5, 3, peak)
+        if "dequantize" in legs:
+            line["secondary"]["dequantize_k4v2"] = bench_dequantize(torch, dev, 3, 2, peak)
         if "prefill" in legs:
             line["secondary"]["prefill_chunk_attn"] = bench_prefill(torch, dev, 3, 2)
     if world > 1 and not split and not args.no_secondary and HKV % world == 0:
@@ -797,7 +834,7 @@ def main():
     ap.add_argument("--fused-gather", action="store_true", help="with --split-heads: the decode kernel stores its heads into every GPU's "
                     "result buffer (peer-mapped memory) instead of an NCCL all-gather")
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary legs")
-    ap.add_argument("--legs", default="quantize,compress_c3,decode_c3,prefill", help="which secondary legs run (comma list; profilers "
+    ap.add_argument("--legs", default="quantize,compress_c3,decode_c3,dequantize,prefill", help="which secondary legs run (comma list; profilers "
                     "capture one kernel at a time with little else on the device)")
     ap.add_argument("--workload", default="c1", choices=("c1", "c4"), help="c1: the headline layer-decode benchmark; c4: end-to-end "
                     "batched decoding of a Llama-3.1-8B-shaped model through compressed caches (about 75 GB on the device at the defaults)")
