@@ -17,7 +17,7 @@
 //     M 128, K 16) into accumulator pair t & 1
 //     of tensor memory - R sits in shared memory as two MN-major B tiles built once per CTA - and commits to mbarriers;
 //   * warps 0-3 own the 128 accumulator lanes (a row per thread): tcgen05.ld of both accumulators, combine, scale by the
-//     norm, convert, 16-byte stores.
+//     norm, convert, and write out through a small per-warp staging area so that stores cover whole 128-byte lines.
 // Every mbarrier wait is bounded (status 105); tensor memory is freed on every path.
 #include <algorithm>
 
@@ -36,7 +36,9 @@ constexpr uint32_t OFF_A = 2 * TILE_BYTES;                                  // [
 constexpr uint32_t OFF_NRM = 6 * TILE_BYTES;                                // float   [4][128] row norms (slot = tile & 3)
 constexpr uint32_t OFF_OFFS = OFF_NRM + 2048;                               // int64   [4][128] output element offsets (-1: no such row)
 constexpr uint32_t OFF_CTAB = OFF_OFFS + 4096;                              // uint32  [2][16] centroids as {hi, lo} fp16 pairs: first half's table, second half's
-constexpr uint32_t OFF_BAR = OFF_CTAB + 128;
+constexpr uint32_t STAGE_LD = 144;                                          // bytes per staged row: 128 + 16 (rows start four banks apart)
+constexpr uint32_t OFF_STAGE = OFF_CTAB + 128;                              // [4 warps][32 rows][STAGE_LD] results on their way out
+constexpr uint32_t OFF_BAR = OFF_STAGE + 4 * 32 * STAGE_LD;
 constexpr uint32_t OFF_SLOT = OFF_BAR + 64;                                 // [0] tensor-memory base, [1] abort
 constexpr uint32_t SMEM_USED = OFF_SLOT + 16;
 constexpr size_t SMEM_BYTES = SMEM_USED + 1024;
@@ -314,39 +316,57 @@ __global__ void __launch_bounds__(NT, 1) dequantize_tc_kernel(Params p) {
             if (!wait_bar(bar(ACC_FULL + bf), uint32_t((it >> 1) & 1))) break;
             tc_fence_after();
             const float nrm = s_nrm[(it & 3) * TM + tid];
-            const long long off = s_off[(it & 3) * TM + tid];
+            const long long* offs = s_off + (it & 3) * TM + warp * 32;       // output offsets of this warp's 32 rows
             const uint32_t acc = t_row + uint32_t(bf) * 256u;
+            unsigned char* stg = smem + OFF_STAGE + warp * (32 * STAGE_LD);   // this warp's [32 rows][128 bytes + pad]
+            // 32 columns at a time: this thread's row out of tensor memory, combined, scaled and converted into the warp's staging
+            // rows; once a row's 128 staged bytes are full (64 columns of a 16-bit type, 32 of float32) the warp writes them out
+            // with eight lanes per row, so that a store instruction covers four whole 128-byte lines instead of 32 half-sectors
+            const int es = p.out_dtype == TQ_F32 ? 4 : 2;
 #pragma unroll 1
             for (int c0 = 0; c0 < d; c0 += 32) {
                 uint32_t hi[32], lo[32];
                 tmem_ld32(acc + c0, hi);
                 tmem_ld32(acc + 128u + c0, lo);
                 tmem_ld_wait();
-                if (off >= 0) {
-                    float v[32];
+                float v[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = fmaf(__uint_as_float(lo[j]), 1.f / 2048.f, __uint_as_float(hi[j])) * nrm;
-                    if (p.out_dtype == TQ_F32) {
-                        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + off + c0);
+                for (int j = 0; j < 32; ++j) v[j] = fmaf(__uint_as_float(lo[j]), 1.f / 2048.f, __uint_as_float(hi[j])) * nrm;
+                if (es == 4) {
+                    float4* dst = reinterpret_cast<float4*>(stg + lane * STAGE_LD);
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                    } else {
-                        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.out) + off + c0);
+                    for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                } else {
+                    uint4* dst = reinterpret_cast<uint4*>(stg + lane * STAGE_LD + ((c0 >> 5) & 1) * 64);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            uint32_t w[4];
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t w[4];
 #pragma unroll
-                            for (int u = 0; u < 4; ++u) {
-                                const float x0 = v[8 * j + 2 * u], x1 = v[8 * j + 2 * u + 1];
-                                if (p.out_dtype == TQ_F16) w[u] = h2_bits(x0, x1);
-                                else {
-                                    const __nv_bfloat162 bb = __floats2bfloat162_rn(x0, x1);
-                                    w[u] = *reinterpret_cast<const uint32_t*>(&bb);
-                                }
+                        for (int u = 0; u < 4; ++u) {
+                            const float x0 = v[8 * j + 2 * u], x1 = v[8 * j + 2 * u + 1];
+                            if (p.out_dtype == TQ_F16) w[u] = h2_bits(x0, x1);
+                            else {
+                                const __nv_bfloat162 bb = __floats2bfloat162_rn(x0, x1);
+                                w[u] = *reinterpret_cast<const uint32_t*>(&bb);
                             }
-                            dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
                         }
+                        dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
                     }
+                }
+                const bool flush = es == 4 || ((c0 >> 5) & 1) == 1 || c0 + 32 >= d;     // the staged rows are complete (or the row ends)
+                if (flush) {
+                    __syncwarp();
+                    const int col0 = es == 4 ? c0 : (c0 & ~63);                        // first column of the staged bytes
+                    const int n_bytes = (min(c0 + 32, d) - col0) * es;                 // staged bytes per row: 128, or 64 at the end of a 96-column 16-bit row
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const int r = 4 * k + (lane >> 3), ch = lane & 7;
+                        const long long o = offs[r];
+                        if (o >= 0 && ch * 16 < n_bytes)
+                            *reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.out) + (o + col0) * es + ch * 16) =
+                                *reinterpret_cast<const uint4*>(stg + r * STAGE_LD + ch * 16);
+                    }
+                    __syncwarp();
                 }
             }
             tc_fence_before();
