@@ -11,7 +11,7 @@
 // resolution).
 //
 // Persistent CTAs (one per SM) walk the 128-row tiles, warp-specialised:
-//   * warps 4-7 unpack a tile's codes into two fp16 A-operand tiles (hi / lo parts of the centroids; K-major, 128-byte
+//   * warps 4-7 and 9-12 (two groups, alternating tiles) unpack a tile's codes into two fp16 A-operand tiles (hi / lo parts of the centroids; K-major, 128-byte
 //     swizzle), buffer t & 1, and stage the rows' norms and output offsets;
 //   * one thread of warp 8 issues the 2 x d/16 tcgen05.mma of the tile (c_hi [R_hi | R_lo] with N 256, c_lo R_hi with N 128;
 //     M 128, K 16) into accumulator pair t & 1
@@ -29,7 +29,7 @@ int* decode_status_ptr();
 
 namespace dqtc {
 
-constexpr int TM = 128, NT = 288, ROW_T = 128, PROD_T = 128;
+constexpr int TM = 128, NT = 416, ROW_T = 128, PROD_T = 128;          // warps 0-3 rows, 4-7 and 9-12 two producer groups, 8 MMA issue
 constexpr uint32_t KBLK = 16384, TILE_BYTES = 2 * KBLK;                     // a 128 x 128 fp16 operand tile: two 64-column blocks
 constexpr uint32_t OFF_RHI = 0, OFF_RLO = TILE_BYTES;                       // R as B operands (rows = k, columns = j)
 constexpr uint32_t OFF_A = 2 * TILE_BYTES;                                  // [2 buffers][hi, lo] A tiles
@@ -45,6 +45,7 @@ constexpr size_t SMEM_BYTES = SMEM_USED + 1024;
 static_assert(SMEM_BYTES <= 227u * 1024u, "shared-memory plan");
 constexpr uint32_t WAIT_LIMIT = 4u << 20;
 constexpr int ERR_WAIT = 105;
+constexpr int PF_AHEAD = 4;                                                 // a tile's packed rows are asked for in L2 this many tiles early
 constexpr uint32_t TMEM_COLS = 512;                                         // buffer b: c_hi R_hi at 256 b, the mixed products at 256 b + 128
 enum Bars { A_FULL = 0, A_FREE = 2, ACC_FULL = 4, ACC_FREE = 6 };
 
@@ -103,6 +104,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                  : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void prefetch_l2(const void* ptr) { asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr)); }
 __device__ __forceinline__ uint32_t h2_bits(float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<const uint32_t*>(&h);
@@ -140,6 +142,17 @@ constexpr uint32_t IDESC = (1u << 4) | (1u << 16) | (uint32_t(128 >> 3) << 17) |
 constexpr uint32_t IDESC_N256 = (1u << 4) | (1u << 16) | (uint32_t(256 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
 static_assert(OFF_RLO == OFF_RHI + TILE_BYTES, "the N = 256 product reads R_hi and R_lo as one operand");
 
+// Eight codes of BITS bits each: BITS bytes of a packed row (4 bits: one aligned word; 2 bits: an aligned half-word).
+template <int BITS> __device__ __forceinline__ uint32_t load_codes(const uint8_t* src) {
+    if (BITS == 4) return __ldg(reinterpret_cast<const uint32_t*>(src));
+    if (BITS == 2) return __ldg(reinterpret_cast<const uint16_t*>(src));
+    if (BITS == 1) return __ldg(src);
+    return uint32_t(__ldg(src)) | (uint32_t(__ldg(src + 1)) << 8) | (uint32_t(__ldg(src + 2)) << 16);
+}
+
+// BH / BL: bits of the first / second half of the coordinates (BL = 0: one width for the whole row); compile-time so that the
+// code extraction is immediate shifts and masks.
+template <int BH, int BL>
 __global__ void __launch_bounds__(NT, 1) dequantize_tc_kernel(Params p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const uint32_t raw_addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem_raw));
@@ -212,9 +225,12 @@ __global__ void __launch_bounds__(NT, 1) dequantize_tc_kernel(Params p) {
     const int n_mine = p.n_tiles > int(blockIdx.x) ? (p.n_tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x) : 0;   // tiles blockIdx.x, + gridDim.x, ...
     const int ksteps = d / 16;
 
-    if (warp >= 4 && warp < 8) {
-        // ======================= producers: warp w unpacks rows 32 w .. 32 w + 31 of the tile =======================
-        const int pw = warp - 4;
+    if ((warp >= 4 && warp < 8) || warp >= 9) {
+        // ======================= producers: two groups of four warps; group g takes the tiles with it & 1 == g (and so always
+        // fills A buffer g); warp w of a group unpacks rows 32 w .. 32 w + 31 of the tile.  Two groups keep two tiles' worth
+        // of global loads in flight per SM: one group alone was bound by their latency. =======================
+        const int grp = warp >= 9 ? 1 : 0;
+        const int pw = warp - (grp ? 9 : 4);
         // A tile's packed words, norms and row offsets are requested one tile ahead, before the previous tile is converted:
         // their latency passes under that work.  Chunk c = lane + 32 k of the warp's 32 rows: row c >> 4,
         // coordinates 8 (c & 15) ...; eight codes are `bits` bytes of the packed row.
@@ -232,27 +248,33 @@ __global__ void __launch_bounds__(NT, 1) dequantize_tc_kernel(Params p) {
                 off_next = ln * p.out_lane_stride + rw * p.out_row_stride;
                 nrm_next = __ldg(p.norms + in_row);
             }
+            {   // the same row of the tile PF_AHEAD tiles further on: asked for in L2 now (a packed row is at most 64 bytes, so
+                // every 128-byte line of the tile holds the start of some row)
+                const int64_t gp = gr + int64_t(PF_AHEAD) * gridDim.x * TM;
+                if (gp < p.total) {
+                    const int64_t ln = gp / p.n_rows, rw = gp - ln * p.n_rows;
+                    const int64_t ir = ln * p.in_lane_stride + rw;
+                    prefetch_l2(p.packed_hi + ir * p.w_hi);
+                    if (BL != 0) prefetch_l2(p.packed_lo + ir * p.w_lo);
+                    if ((lane & 31) == 0 || rw == 0) prefetch_l2(p.norms + ir);
+                }
+            }
 #pragma unroll
             for (int k = 0; k < 16; ++k) {
                 const int c = lane + 32 * k, rl = c >> 4, j8 = c & 15;
                 const long long src_row = __shfl_sync(0xffffffffu, in_row, rl);
-                const bool second = p.bits_lo != 0 && j8 * 8 >= p.half;
-                const int bits = second ? p.bits_lo : p.bits_hi;
-                const int jc = second ? j8 - p.half / 8 : j8;
+                const bool second = BL != 0 && j8 * 8 >= p.half;
                 uint32_t x = 0u;
                 if (src_row >= 0 && j8 * 8 < d) {
-                    const uint8_t* src = (second ? p.packed_lo + src_row * p.w_lo : p.packed_hi + src_row * p.w_hi) + jc * bits;
-                    if (bits == 4) x = __ldg(reinterpret_cast<const uint32_t*>(src));
-                    else if (bits == 2) x = __ldg(reinterpret_cast<const uint16_t*>(src));
-                    else if (bits == 1) x = __ldg(src);
-                    else x = uint32_t(__ldg(src)) | (uint32_t(__ldg(src + 1)) << 8) | (uint32_t(__ldg(src + 2)) << 16);
+                    if (!second) x = load_codes<BH>(p.packed_hi + src_row * p.w_hi + j8 * BH);
+                    else x = load_codes<BL>(p.packed_lo + src_row * p.w_lo + (j8 - p.half / 8) * BL);
                 }
                 w[k] = x;
             }
         };
-        if (n_mine > 0) request(0, w);
+        if (n_mine > grp) request(grp, w);
         off_cur = off_next; nrm_cur = nrm_next;
-        for (int it = 0; it < n_mine; ++it) {
+        for (int it = grp; it < n_mine; it += 2) {
             const int bf = it & 1;
             bool ok = true;
             // the MMAs of tile it - 2 have read the A buffer (the norm / offset slots are four deep: the rows of tile it - 4
@@ -261,20 +283,22 @@ __global__ void __launch_bounds__(NT, 1) dequantize_tc_kernel(Params p) {
             if (!__all_sync(0xffffffffu, ok)) break;
             unsigned char* a_hi = smem + OFF_A + bf * 2 * TILE_BYTES;
             unsigned char* a_lo = a_hi + TILE_BYTES;
-            if (it + 1 < n_mine) request(it + 1, wn);                         // in flight while this tile is converted
+            if (it + 2 < n_mine) request(it + 2, wn);                         // in flight while this tile is converted
             s_nrm[(it & 3) * TM + pw * 32 + lane] = nrm_cur;
             s_off[(it & 3) * TM + pw * 32 + lane] = off_cur;
 #pragma unroll
             for (int k = 0; k < 16; ++k) {
                 const int c = lane + 32 * k, rl = c >> 4, j8 = c & 15;
                 if (j8 * 8 >= d) continue;
-                const bool second = p.bits_lo != 0 && j8 * 8 >= p.half;
-                const int bits = second ? p.bits_lo : p.bits_hi;
-                const uint32_t mask = (1u << bits) - 1u;
-                const uint32_t* tab = ctab + (second ? 16 : 0);
+                const bool second = BL != 0 && j8 * 8 >= p.half;
                 uint32_t e[8];
+                if (!second) {
 #pragma unroll
-                for (int u = 0; u < 8; ++u) e[u] = tab[(w[k] >> (bits * u)) & mask];
+                    for (int u = 0; u < 8; ++u) e[u] = ctab[(w[k] >> (BH * u)) & ((1u << BH) - 1u)];
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) e[u] = ctab[16 + ((w[k] >> (BL * u)) & ((1u << (BL ? BL : 1)) - 1u))];
+                }
                 const int r = pw * 32 + rl;
                 *reinterpret_cast<uint4*>(a_hi + chunk_off(r, j8)) =
                     make_uint4(__byte_perm(e[0], e[1], 0x5410), __byte_perm(e[2], e[3], 0x5410), __byte_perm(e[4], e[5], 0x5410), __byte_perm(e[6], e[7], 0x5410));
@@ -312,7 +336,9 @@ __global__ void __launch_bounds__(NT, 1) dequantize_tc_kernel(Params p) {
         const uint32_t t_row = tmem_base + (uint32_t((warp & 3) * 32) << 16);
         for (int it = 0; it < n_mine; ++it) {
             const int bf = it & 1;
-            if (!wait_bar(bar(A_FULL + bf), uint32_t((it >> 1) & 1))) break;        // norms and offsets (from the producers directly)
+            // (the norms and offsets were written before the producers' arrival that the MMA thread waited for before it issued
+            //  the products this barrier tracks; the rows must not wait on A_FULL themselves: its next phase may complete - the
+            //  next tile for the buffer only needs the MMAs, not the rows - before a late row thread has looked)
             if (!wait_bar(bar(ACC_FULL + bf), uint32_t((it >> 1) & 1))) break;
             tc_fence_after();
             const float nrm = s_nrm[(it & 3) * TM + tid];
@@ -390,6 +416,7 @@ int tq_dequantize_tc(const tq_dequantize_args* q, cudaStream_t s, bool* handled)
     const int d = q->d;
     if (d != 64 && d != 96 && d != 128) return TQ_OK;
     if (q->qjl_bits) return TQ_OK;
+    if (q->bits_lo && q->bits_lo != q->bits_hi - 1) return TQ_OK;              // the reference's fractional widths are (b, b - 1)
     const int half = q->bits_lo ? d / 2 : d;
     if (half % 8 || (d - half) % 8) return TQ_OK;
     const int es = q->out_dtype == TQ_F32 ? 4 : 2;
@@ -420,14 +447,19 @@ int tq_dequantize_tc(const tq_dequantize_args* q, cudaStream_t s, bool* handled)
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 16) dev = 0;
+    using Kernel = void (*)(dqtc::Params);
+    const Kernel kernels[7] = {dqtc::dequantize_tc_kernel<1, 0>, dqtc::dequantize_tc_kernel<2, 0>, dqtc::dequantize_tc_kernel<3, 0>, dqtc::dequantize_tc_kernel<4, 0>,
+                               dqtc::dequantize_tc_kernel<2, 1>, dqtc::dequantize_tc_kernel<3, 2>, dqtc::dequantize_tc_kernel<4, 3>};
     if (!set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(dqtc::dequantize_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dqtc::SMEM_BYTES));
-        if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_dequantize: shared memory %zu B: %s", dqtc::SMEM_BYTES, cudaGetErrorString(e));
+        for (Kernel k : kernels) {
+            cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dqtc::SMEM_BYTES));
+            if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_dequantize: shared memory %zu B: %s", dqtc::SMEM_BYTES, cudaGetErrorString(e));
+        }
         if (cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms[dev] <= 0) sms[dev] = 148;
         set[dev] = true;
     }
     const unsigned grid = unsigned(std::min<int64_t>(tiles, sms[dev]));
-    dqtc::dequantize_tc_kernel<<<grid, dqtc::NT, dqtc::SMEM_BYTES, s>>>(p);
+    kernels[q->bits_lo ? 2 + q->bits_hi : q->bits_hi - 1]<<<grid, dqtc::NT, dqtc::SMEM_BYTES, s>>>(p);
     return check_launch("tq_dequantize");
 }
 
