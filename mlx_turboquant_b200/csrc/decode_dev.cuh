@@ -317,85 +317,76 @@ __device__ __forceinline__ void dense_tiles(const DecodeParams& p, int64_t kvl, 
         } else {
             // float32 / bfloat16 tokens can lie outside the fp16 range: every token row is staged as fp16 under its own
             // power-of-two scale (largest magnitude into [2^7, 2^8)); the scores and the softmax weights take the inverse
-            // scales where the packed tokens take their norms.  A tensor's 16-byte chunks are all loaded first; each lane
-            // folds the largest magnitude of its chunks into the row's slot (the 16 bytes of padding at the end of the
-            // row's staging line: keys' maximum in word 0, values' in word 1; non-negative floats order like integers).
+            // scales where the packed tokens take their norms.  Each lane folds the largest magnitude of its 16-byte chunks
+            // into the row's slot (the 16 bytes of padding at the end of the row's staging line: keys' maximum in word 0,
+            // values' in word 1; non-negative floats order like integers).
             if (lane < TILE) *reinterpret_cast<uint2*>(Ks + lane * LD + D) = make_uint2(0u, 0u);
             __syncwarp();
-            if (p.dense_dtype == TQ_BF16) {
-                uint4 kv[NCH], vv[NCH];
-#pragma unroll
-                for (int i = 0; i < NCH; ++i) {
-                    const int c = lane + 32 * i, r = c / (D / 8), c8 = c - r * (D / 8);
-                    const int64_t tok = tok0 + r;
-                    kv[i] = make_uint4(0, 0, 0, 0); vv[i] = kv[i];
-                    if (tok < n_tok) {
-                        int64_t e;
-                        const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(row_of(tok, true, e));
-                        const __nv_bfloat16* vb = static_cast<const __nv_bfloat16*>(row_of(tok, false, e));
-                        kv[i] = __ldg(reinterpret_cast<const uint4*>(kb + e + c8 * 8));
-                        vv[i] = __ldg(reinterpret_cast<const uint4*>(vb + e + c8 * 8));
-                    }
-                }
-                auto absmax16 = [](const uint4& v) -> uint32_t {      // float bits of the largest |x| of eight bfloat16
-                    const uint32_t m = 0x7fff7fffu;
-                    const uint32_t a = __vmaxu2(__vmaxu2(v.x & m, v.y & m), __vmaxu2(v.z & m, v.w & m));
-                    return max(a & 0xffffu, a >> 16) << 16;
-                };
-#pragma unroll
-                for (int i = 0; i < NCH; ++i) {
-                    const int r = (lane + 32 * i) / (D / 8);
-                    uint32_t* slot = reinterpret_cast<uint32_t*>(Ks + r * LD + D);
-                    atomicMax(slot, absmax16(kv[i]));
-                    atomicMax(slot + 1, absmax16(vv[i]));
-                }
-                __syncwarp();
-#pragma unroll
-                for (int i = 0; i < NCH; ++i) {
-                    const int c = lane + 32 * i, r = c / (D / 8), c8 = c - r * (D / 8);
-                    const uint2 mx = *reinterpret_cast<const uint2*>(Ks + r * LD + D);
-                    const float fk = stage_scale(mx.x), fv = stage_scale(mx.y);
-                    auto conv = [](const uint4& v, float f) -> uint4 {
-                        auto two = [&](uint32_t w) -> uint32_t {
-                            return pack_h2(__uint_as_float(w << 16) * f, __uint_as_float(w & 0xffff0000u) * f);
-                        };
-                        return make_uint4(two(v.x), two(v.y), two(v.z), two(v.w));
-                    };
-                    *reinterpret_cast<uint4*>(Ks + r * LD + c8 * 8) = conv(kv[i], fk);
-                    *reinterpret_cast<uint4*>(Vs + r * LD + c8 * 8) = conv(vv[i], fv);
-                }
-            } else {
-                // float32: a chunk holds four values; keys first, then values (register budget)
-                constexpr int NCH4 = TILE * (D / 4) / 32;
+            // Two passes over the tile's 16-byte chunks, four chunks of one tensor in flight at a time (few registers: this code sits
+            // inside kernels whose main loops need them): first the row maxima, then - the chunks come from L1 / L2 now - the scaled
+            // conversion.  ES: bytes per element.
+            const int es = p.dense_dtype == TQ_BF16 ? 2 : 4;
+            const int cpr = D * es / 16;                      // chunks per row
+            const int n_chunks = TILE * cpr;
+            auto chunk_ptr = [&](int c, bool keys) -> const uint4* {
+                const int r = c / cpr, cc = c - r * cpr;
+                const int64_t tok = tok0 + r;
+                if (tok >= n_tok) return nullptr;
+                int64_t e;
+                const unsigned char* base = static_cast<const unsigned char*>(row_of(tok, keys, e));
+                return reinterpret_cast<const uint4*>(base + e * es) + cc;
+            };
 #pragma unroll 1
-                for (int side = 0; side < 2; ++side) {
-                    uint4 xv[NCH4];
+            for (int side = 0; side < 2; ++side) {
+#pragma unroll 1
+                for (int c0 = lane; c0 < n_chunks; c0 += 128) {
+                    uint4 x[4];
 #pragma unroll
-                    for (int i = 0; i < NCH4; ++i) {
-                        const int c = lane + 32 * i, r = c / (D / 4), c4 = c - r * (D / 4);
-                        const int64_t tok = tok0 + r;
-                        xv[i] = make_uint4(0, 0, 0, 0);
-                        if (tok < n_tok) {
-                            int64_t e;
-                            const float* xb = static_cast<const float*>(row_of(tok, side == 0, e));
-                            xv[i] = __ldg(reinterpret_cast<const uint4*>(xb + e + c4 * 4));
+                    for (int u = 0; u < 4; ++u) {
+                        const uint4* src = c0 + 32 * u < n_chunks ? chunk_ptr(c0 + 32 * u, side == 0) : nullptr;
+                        x[u] = src ? __ldg(src) : make_uint4(0, 0, 0, 0);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (c0 + 32 * u >= n_chunks) continue;
+                        uint32_t mb;
+                        if (es == 2) {
+                            const uint32_t m = 0x7fff7fffu;
+                            const uint32_t a = __vmaxu2(__vmaxu2(x[u].x & m, x[u].y & m), __vmaxu2(x[u].z & m, x[u].w & m));
+                            mb = max(a & 0xffffu, a >> 16) << 16;
+                        } else {
+                            const uint32_t m = 0x7fffffffu;
+                            mb = max(max(x[u].x & m, x[u].y & m), max(x[u].z & m, x[u].w & m));
                         }
+                        atomicMax(reinterpret_cast<uint32_t*>(Ks + ((c0 + 32 * u) / cpr) * LD + D) + side, mb);
+                    }
+                }
+            }
+            __syncwarp();
+#pragma unroll 1
+            for (int side = 0; side < 2; ++side) {
+                __half* dst = side == 0 ? Ks : Vs;
+#pragma unroll 1
+                for (int c0 = lane; c0 < n_chunks; c0 += 128) {
+                    uint4 x[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const uint4* src = c0 + 32 * u < n_chunks ? chunk_ptr(c0 + 32 * u, side == 0) : nullptr;
+                        x[u] = src ? __ldg(src) : make_uint4(0, 0, 0, 0);
                     }
 #pragma unroll
-                    for (int i = 0; i < NCH4; ++i) {
-                        const int r = (lane + 32 * i) / (D / 4);
-                        const uint32_t m = 0x7fffffffu;
-                        atomicMax(reinterpret_cast<uint32_t*>(Ks + r * LD + D) + side, max(max(xv[i].x & m, xv[i].y & m), max(xv[i].z & m, xv[i].w & m)));
-                    }
-                    __syncwarp();
-                    __half* dst = side == 0 ? Ks : Vs;
-#pragma unroll
-                    for (int i = 0; i < NCH4; ++i) {
-                        const int c = lane + 32 * i, r = c / (D / 4), c4 = c - r * (D / 4);
+                    for (int u = 0; u < 4; ++u) {
+                        const int c = c0 + 32 * u;
+                        if (c >= n_chunks) continue;
+                        const int r = c / cpr, cc = c - r * cpr;
                         const float f = stage_scale(reinterpret_cast<const uint32_t*>(Ks + r * LD + D)[side]);
-                        *reinterpret_cast<uint2*>(dst + r * LD + c4 * 4) =
-                            make_uint2(pack_h2(__uint_as_float(xv[i].x) * f, __uint_as_float(xv[i].y) * f),
-                                       pack_h2(__uint_as_float(xv[i].z) * f, __uint_as_float(xv[i].w) * f));
+                        if (es == 2) {
+                            auto two = [&](uint32_t w) -> uint32_t { return pack_h2(__uint_as_float(w << 16) * f, __uint_as_float(w & 0xffff0000u) * f); };
+                            *reinterpret_cast<uint4*>(dst + r * LD + cc * 8) = make_uint4(two(x[u].x), two(x[u].y), two(x[u].z), two(x[u].w));
+                        } else {
+                            *reinterpret_cast<uint2*>(dst + r * LD + cc * 4) =
+                                make_uint2(pack_h2(__uint_as_float(x[u].x) * f, __uint_as_float(x[u].y) * f), pack_h2(__uint_as_float(x[u].z) * f, __uint_as_float(x[u].w) * f));
+                        }
                     }
                 }
             }
