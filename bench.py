@@ -379,7 +379,7 @@ def bench_prefill(torch, dev, steps, warmup):
     flops = 4.0 * b * HQ * tq * (ctx - tq / 2) * D                  # QK^T and PV over the causal extent
     return {"workload": "llama31_8b_layer_prefill_chunk_b4_ctx16384_tq512_k4v2_sink128_rw128", "ms_per_layer_chunk": ms,
             "tflops": flops / (ms * 1e-3) / 1e12, "query_tokens_per_s": b * tq / (ms * 1e-3),
-            "kernel": "prefill_attn_kernel<128> (64 query columns per CTA, stages unpacked to fp16 in shared memory, mma.sync)"}
+            "kernel": "prefill_tc_kernel (tcgen05: 128 query rows per CTA, scores and outputs in tensor memory, unpacked tiles as shared-memory operands)"}
 
 
 def bench_dequantize(torch, dev, steps, warmup, peak):
