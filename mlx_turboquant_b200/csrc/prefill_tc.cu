@@ -287,7 +287,8 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
 
     // per-row softmax state (threads 0 .. 127 own rows)
     const int q_pos = (tid < ROW_T && row_valid(tid)) ? int(P.q_pos0 + tq0 + tid / GP) : -1;   // the latest position this row sees
-    float m_ref = -1e30f, m_thr = -1e30f, l_sum = 0.f, vsc = 1.f, vthr = VSC_CAP;
+    float m_ref = -1e30f, l_sum = 0.f, vsc = 1.f, vthr = 0.f;                   // (vthr 0: the first tile with a non-zero value norm picks the scale)
+    float lvsc = 0.f, bias = 0.f, t_thr = MAX_SLACK;                             // log2(vsc); lvsc - m_ref (0 until the first tile has set the reference); MAX_SLACK + lvsc
     const uint32_t t_row = tmem_base + (uint32_t((warp & 3) * 32) << 16);
     bool have_op = false, have_od = false;        // the accumulators hold sums (same in every thread)
 
@@ -504,8 +505,7 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
                 auto refresh = [&](float mx) {
                     const float mn = fmaxf(fmaxf(m_ref, mx), -1e30f);
                     float a = ex2(m_ref - mn);
-                    m_ref = mn; m_thr = mn + MAX_SLACK;
-                    l_sum *= a;
+                    m_ref = mn;
                     if (vmax > vthr) {
                         int eb = (__float_as_int(vmax) >> 23) & 0xff;
                         eb = min(max(eb, 16), 240);
@@ -513,7 +513,11 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
                         a *= nsc / vsc;
                         vsc = nsc;
                         vthr = VSC_CAP / nsc;
+                        lvsc = float(134 - eb);                            // log2 of the scale
                     }
+                    l_sum *= a;                                           // the denominator carries the value scale like the sums do
+                    bias = lvsc - m_ref;
+                    t_thr = MAX_SLACK + lvsc;
 #pragma unroll 1
                     for (int acc = 0; acc < 2; ++acc) {
                         // an accumulator holds sums once a product of its region has completed: the packed one from the second packed
@@ -541,9 +545,11 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
                         uint32_t h[16];
 #pragma unroll
                         for (int j = 0; j < 32; j += 4) {
+                            // t = score * key norm - reference + log2(value scale): one multiply-add per score; the weight ex2(t)
+                            // already carries the value scale, and so does the denominator it is summed into
                             const float4 kn = *reinterpret_cast<const float4*>(kn_t + c0 + j);
-                            float s0 = __uint_as_float(v[j]) * kn.x, s1 = __uint_as_float(v[j + 1]) * kn.y;
-                            float s2 = __uint_as_float(v[j + 2]) * kn.z, s3 = __uint_as_float(v[j + 3]) * kn.w;
+                            float s0 = fmaf(__uint_as_float(v[j]), kn.x, bias), s1 = fmaf(__uint_as_float(v[j + 1]), kn.y, bias);
+                            float s2 = fmaf(__uint_as_float(v[j + 2]), kn.z, bias), s3 = fmaf(__uint_as_float(v[j + 3]), kn.w, bias);
                             if (masked) {
                                 const int4 ps = *reinterpret_cast<const int4*>(ps_t + c0 + j);
                                 s0 = ps.x <= q_pos ? s0 : -INFINITY; s1 = ps.y <= q_pos ? s1 : -INFINITY;
@@ -552,10 +558,10 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
                             mx = fmaxf(fmaxf(mx, fmaxf(s0, s1)), fmaxf(s2, s3));
                             if (write) {
                                 const float4 vn = *reinterpret_cast<const float4*>(vn_t + c0 + j);
-                                const float p0 = ex2(s0 - m_ref), p1 = ex2(s1 - m_ref), p2 = ex2(s2 - m_ref), p3 = ex2(s3 - m_ref);
+                                const float p0 = ex2(s0), p1 = ex2(s1), p2 = ex2(s2), p3 = ex2(s3);
                                 lsum += (p0 + p1) + (p2 + p3);
-                                h[j >> 1] = pack_h2(p0 * (vn.x * vsc), p1 * (vn.y * vsc));
-                                h[(j >> 1) + 1] = pack_h2(p2 * (vn.z * vsc), p3 * (vn.w * vsc));
+                                h[j >> 1] = pack_h2(p0 * vn.x, p1 * vn.y);
+                                h[(j >> 1) + 1] = pack_h2(p2 * vn.z, p3 * vn.w);
                             }
                         }
                         if (write) {
@@ -583,13 +589,14 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
                 float mx, lsum;
                 // the very first tile (no reference yet; every valid row sees its first token) and a tile that moves the value
                 // scale: settle the references first
+                // (sweep returns the row's largest t; the score itself is t - bias)
                 if (g == 0 || vmax > vthr) {
                     sweep(false, mx, lsum);
-                    refresh(mx);
+                    refresh(mx - bias);
                 }
                 sweep(true, mx, lsum);
-                if (__any_sync(0xffffffffu, mx > m_thr)) {    // a score beyond the slack: new reference, weights again (rare)
-                    refresh(mx);
+                if (__any_sync(0xffffffffu, mx > t_thr)) {    // a score beyond the slack: new reference, weights again (rare)
+                    refresh(mx - bias);
                     sweep(true, mx, lsum);
                 }
                 l_sum += lsum;
@@ -615,7 +622,7 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
     float* fp = reinterpret_cast<float*>(smem + OFF_FP);                          // [128][129] sums of the packed part, rotated space
     const bool failed = slot[1] != 0u;
     if (tid < ROW_T) {
-        const float ip = 1.f / (vsc * p.v_scale_hi), id = 1.f / vsc;
+        const float ip = 1.f / p.v_scale_hi, id = 1.f;                            // (sums and denominator carry the same value scale)
 #pragma unroll 1
         for (int c0 = 0; c0 < D; c0 += 32) {
             uint32_t v[32];

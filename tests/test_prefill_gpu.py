@@ -155,3 +155,23 @@ def test_long_chunks_k4v2(oracle, b, hq, hkv, t, tq, rw, sink):
     out16 = c.attend(q)
     assert out16.dtype == torch.float16
     _check(out16, ref, tol=1e-3 + 2.0 ** -11)
+
+
+@pytest.mark.parametrize("v_scale", (1e-4, 3e4))
+def test_value_norm_range(oracle, v_scale):
+    """Value norms far from 1 (the weights ride on fp16 operands under a power-of-two scale that follows the largest norm)."""
+    from mlx_turboquant_b200 import TurboQuantKVCache
+    rs = np.random.RandomState(77)
+    b, hq, hkv, t, tq, d = 1, 8, 2, 1200, 256, 128
+    k = kv_like(rs, (b, hkv, t, d), np.float32)
+    v = (kv_like(rs, (b, hkv, t, d), np.float32) * v_scale * np.exp(rs.randn(b, hkv, t, 1))).astype(np.float32)
+    q = (rs.randn(b, hq, tq, d) / np.sqrt(d)).astype(np.float32)
+    ref_c = oracle.KVCacheOracle(d, host_tables(d), 4, 2, 64, fp16_sink_size=16, chunk_size=0)
+    rk, rv = ref_c.update_and_fetch(k, v)
+    c = TurboQuantKVCache(head_dim=d, num_kv_heads=hkv, key_bits=4, value_bits=2, residual_window=64, fp16_sink_size=16)
+    g = lambda a: None if a is None else cu(a)   # noqa: E731
+    ck, cv = ref_c.comp["k"], ref_c.comp["v"]
+    c.state = (g(ref_c.k), g(ref_c.v), g(ck[0]), g(ck[2]), g(cv[0]), g(cv[2]), g(ref_c.sink_k), g(ref_c.sink_v), g(ck[1]), g(cv[1]))
+    c.meta_state = {"offset": str(ref_c.offset), "compressed_len": str(ref_c.comp_len), "sink_len": str(ref_c.sink_len),
+                    "fp16_len": str(ref_c.fp_len), "fp16_capacity": str(ref_c.k.shape[2])}
+    _check(c.attend(cu(q)), causal_reference(q, rk, rv))
