@@ -307,7 +307,7 @@ float tq_fp16_table_scale(const float* centroids_host, int n);
  *   "decode_ctas_per_sm" 1..8, "decode_splits" 0 (auto)..448, "decode_force_general" 0/1,
  *   "dequantize_tc" 0/1 (tq_dequantize at d = 64 / 96 / 128 without QJL correction: the tcgen05 kernel, default, or always the
  *   CUDA-core row kernel),
- *   "prefill_tc" 0/1 (tq_prefill_attn at d = 128 with 4-bit keys / 2-bit values: the tcgen05 kernel, default, or always
+ *   "prefill_tc" 0/1 (tq_prefill_attn at d = 128 with at least 64 query rows: the tcgen05 kernel, default, or always
  *   the mma.sync kernel),
  *   "decode_pdl" 0/1 (programmatic dependent launch: a call's prologue overlaps the previous kernel's tail),
  *   "gather_wait_polls" 1000..4000000 (polls of one word of a gather before the wait gives up; default 2000000, some two seconds).

@@ -1,5 +1,5 @@
 // Causal attention for several query tokens per sequence over the compressed cache, on the fifth-generation tensor
-// cores: the large-tile form of prefill.cu for head_dim 128 with 4-bit keys and 2-bit values (same contract, same
+// cores: the large-tile form of prefill.cu for head_dim 128 (same contract, same
 // arithmetic: what the reference does as dense reassembly, cache.py:674-706, followed by the consumer's masked
 // attention; sketched for packed keys in kernels.py:558-590 and docs/FUSED_ATTENTION_DESIGN.md:281-283).
 //
@@ -46,8 +46,8 @@ constexpr uint32_t OFF_POS = OFF_VN + 1024;                                 // i
 constexpr int TREP = 8;                                                     // copies of every table entry (lane l reads copy l mod 8)
 constexpr uint32_t OFF_T4 = OFF_POS + 1024;                                 // uint  [256][TREP] byte of two 4-bit codes -> half2
 constexpr uint32_t OFF_T2 = OFF_T4 + 1024 * TREP;                           // uint2 [256][TREP] byte of four 2-bit codes -> 4 halves
-constexpr uint32_t OFF_CTAB = OFF_T2 + 2048 * TREP;                         // half  [32]
-constexpr uint32_t OFF_BAR = OFF_CTAB + 64;                                 // mbarriers (see Bars)
+constexpr uint32_t OFF_CTAB = OFF_T2 + 2048 * TREP;                         // half  [64]: key centroids (first half, second half), value centroids (first, second)
+constexpr uint32_t OFF_BAR = OFF_CTAB + 128 + 256;                                 // mbarriers (see Bars)
 constexpr uint32_t OFF_SLOT = OFF_BAR + 128;                                // words: [0] tensor-memory base, [1] abort, [4..5] "every row sees every token" of tile buffer 0 / 1, [8..15] largest value norm per buffer and producer warp
 constexpr uint32_t SMEM_USED = OFF_SLOT + 64;
 constexpr size_t SMEM_BYTES = SMEM_USED + 1024;                             // + slack to align the tiles to 1024 bytes
@@ -175,6 +175,7 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
     uint32_t* t4 = reinterpret_cast<uint32_t*>(smem + OFF_T4);
     uint2* t2 = reinterpret_cast<uint2*>(smem + OFF_T2);
     __half* ctab = reinterpret_cast<__half*>(smem + OFF_CTAB);
+    uint32_t* ctab32 = reinterpret_cast<uint32_t*>(smem + OFF_CTAB + 128);   // the same 64 centroids, one per 32-bit word (code-by-code unpack)
     volatile uint32_t* slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_SLOT);
     auto bar = [&](int which) -> uint32_t { return sbase + OFF_BAR + 8u * uint32_t(which); };
 
@@ -205,18 +206,23 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
         tmem_alloc(sbase + OFF_SLOT, TMEM_COLS);
         tmem_relinquish();
     }
-    if (tid < 32) {
+    if (tid < 64) {
         const int which = tid >> 4, k = tid & 15;
-        const float* src = which == 0 ? p.kc_hi : p.vc_hi;
-        const float sc = which == 1 ? p.v_scale_hi : 1.f;
-        ctab[tid] = __float2half_rn((src != nullptr && k < (which ? 4 : 16)) ? src[k] * sc : 0.f);
+        const float* src = which == 0 ? p.kc_hi : which == 1 ? p.kc_lo : which == 2 ? p.vc_hi : p.vc_lo;
+        const int bits = which == 0 ? p.kb_hi : which == 1 ? p.kb_lo : which == 2 ? p.vb_hi : p.vb_lo;
+        const float sc = which == 2 ? p.v_scale_hi : which == 3 ? p.v_scale_lo : 1.f;     // value tables: fp16 under a table-wide scale, divided out at the end
+        ctab[tid] = __float2half_rn((src != nullptr && bits > 0 && k < (1 << bits)) ? src[k] * sc : 0.f);
+        ctab32[tid] = uint32_t(__half_as_ushort(ctab[tid]));
     }
     __syncthreads();
+    // whole-byte tables for the commonest widths (4-bit keys, 2-bit values, not fractional, word-aligned rows): a tile is then
+    // unpacked a 32-bit word at a time; every other width goes code by code through the 16-entry tables
+    const bool fast_unpack = p.kb_hi == 4 && p.kb_lo == 0 && p.vb_hi == 2 && p.vb_lo == 0 && p.words_ok;
     if (tid < 256) {
         const int e = tid;
         const __half2 hk = __halves2half2(ctab[e & 15], ctab[e >> 4]);
-        const __half2 v01 = __halves2half2(ctab[16 + (e & 3)], ctab[16 + ((e >> 2) & 3)]);
-        const __half2 v23 = __halves2half2(ctab[16 + ((e >> 4) & 3)], ctab[16 + (e >> 6)]);
+        const __half2 v01 = __halves2half2(ctab[32 + (e & 3)], ctab[32 + ((e >> 2) & 3)]);
+        const __half2 v23 = __halves2half2(ctab[32 + ((e >> 4) & 3)], ctab[32 + (e >> 6)]);
 #pragma unroll
         for (int r = 0; r < TREP; ++r) {
             t4[e * TREP + r] = *reinterpret_cast<const uint32_t*>(&hk);
@@ -348,7 +354,7 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
                 nk = live ? __ldg(p.k_norms + n) : 0.f;
                 nv = live ? __ldg(p.v_norms + n) : 0.f;
             };
-            if (!dense_region && n_tiles > 0) request_packed(0);
+            if (!dense_region && fast_unpack && n_tiles > 0) request_packed(0);
             for (int it = 0; it < n_tiles; ++it) {
                 const int g = g0 + it, bf = g & 1;
                 if (g >= 2 && !wait_bar(bar(KV_FREE + bf), uint32_t(((g >> 1) - 1) & 1))) break;     // the products of tile g - 2 have read the buffer
@@ -357,7 +363,57 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
                 unsigned char* vt = smem + OFF_V + bf * TILE_BYTES;
                 float* kn = s_kn + bf * TN; float* vn = s_vn + bf * TN; int* ps = s_pos + bf * TN;
                 float my_vn = 0.f;
-                if (!dense_region) {
+                if (!dense_region && !fast_unpack) {
+                    // any width 1-4, fractional splits: chunk c = pt + 128 k of a tensor is row c >> 4, coordinates 8 (c & 15) ...;
+                    // eight codes are `bits` bytes of the packed row (read bytewise: no alignment asked of the rows)
+                    const int rows = int(min(int64_t(TN), p.c_len - tok0));
+                    if (pt == 0) slot[4 + bf] = (rows == TN && p.sink_len + tok0 + TN - 1 <= min_q_pos) ? 1u : 0u;
+                    {
+                        const bool live = pt < rows;
+                        const int64_t n = kvl * p.c_ls + tok0 + (live ? pt : 0);
+                        const float a = live ? __ldg(p.k_norms + n) : 0.f;
+                        my_vn = live ? __ldg(p.v_norms + n) : 0.f;
+                        kn[pt] = a; vn[pt] = my_vn;
+                        ps[pt] = live ? int(p.sink_len + tok0 + pt) : 0x7fffffff;
+                    }
+#pragma unroll 1
+                    for (int side = 0; side < 2; ++side) {
+                        const int b_hi = side ? p.vb_hi : p.kb_hi, b_lo = side ? p.vb_lo : p.kb_lo;
+                        const int half = b_lo ? D / 2 : D;
+                        const int w_hi = half * b_hi / 8, w_lo = b_lo ? (D - half) * b_lo / 8 : 0;
+                        const uint8_t* base_hi = (side ? p.v_hi : p.k_hi) + (kvl * p.c_ls + tok0) * w_hi;
+                        const uint8_t* base_lo = b_lo ? (side ? p.v_lo : p.k_lo) + (kvl * p.c_ls + tok0) * w_lo : nullptr;
+                        unsigned char* dst = side ? vt : kt;
+                        // packed rows can be read as aligned 32-bit words when every row starts on a 4-byte boundary
+                        const bool words = (reinterpret_cast<uintptr_t>(base_hi) & 3u) == 0 && (w_hi & 3) == 0 &&
+                                           (b_lo == 0 || ((reinterpret_cast<uintptr_t>(base_lo) & 3u) == 0 && (w_lo & 3) == 0));
+#pragma unroll 8
+                        for (int k = 0; k < 16; ++k) {
+                            const int c = pt + PROD_T * k, r = c >> 4, j8 = c & 15;
+                            const bool second = b_lo != 0 && j8 * 8 >= half;
+                            const int bits = second ? b_lo : b_hi;
+                            uint32_t w = 0u;
+                            if (r < rows) {
+                                const uint8_t* src = second ? base_lo + int64_t(r) * w_lo + (j8 - half / 8) * bits : base_hi + int64_t(r) * w_hi + j8 * bits;
+                                if (words) {          // aligned words around the `bits` bytes, shifted into place
+                                    const uint32_t sh = uint32_t(reinterpret_cast<uintptr_t>(src)) & 3u;
+                                    const uint32_t* a4 = reinterpret_cast<const uint32_t*>(src - sh);
+                                    const uint32_t lo = __ldg(a4), hi = sh + uint32_t(bits) > 4u ? __ldg(a4 + 1) : 0u;
+                                    w = __funnelshift_r(lo, hi, sh * 8u);
+                                } else {
+                                    for (int u = 0; u < bits; ++u) w |= uint32_t(__ldg(src + u)) << (8 * u);
+                                }
+                            }
+                            const uint32_t mask = (1u << bits) - 1u;
+                            const uint32_t* tb = ctab32 + side * 32 + (second ? 16 : 0);
+                            uint32_t e[8];
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) e[u] = tb[(w >> (bits * u)) & mask];
+                            *reinterpret_cast<uint4*>(dst + chunk_off(r, j8)) =
+                                make_uint4(__byte_perm(e[0], e[1], 0x5410), __byte_perm(e[2], e[3], 0x5410), __byte_perm(e[4], e[5], 0x5410), __byte_perm(e[6], e[7], 0x5410));
+                        }
+                    }
+                } else if (!dense_region) {
                     const int rows = int(min(int64_t(TN), p.c_len - tok0));
                     if (pt == 0) slot[4 + bf] = (rows == TN && p.sink_len + tok0 + TN - 1 <= min_q_pos) ? 1u : 0u;
                     my_vn = nv;
@@ -622,13 +678,13 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
     float* fp = reinterpret_cast<float*>(smem + OFF_FP);                          // [128][129] sums of the packed part, rotated space
     const bool failed = slot[1] != 0u;
     if (tid < ROW_T) {
-        const float ip = 1.f / p.v_scale_hi, id = 1.f;                            // (sums and denominator carry the same value scale)
+        const float ip_hi = 1.f / p.v_scale_hi, ip_lo = 1.f / (p.vb_lo ? p.v_scale_lo : p.v_scale_hi), id = 1.f;   // (sums and denominator carry the same value scale)
 #pragma unroll 1
         for (int c0 = 0; c0 < D; c0 += 32) {
             uint32_t v[32];
             if (have_op) { tmem_ld32(t_row + COL_OP + c0, v); tmem_ld_wait(); }
 #pragma unroll
-            for (int j = 0; j < 32; ++j) fp[tid * FIN_LD + c0 + j] = have_op ? __uint_as_float(v[j]) * ip : 0.f;
+            for (int j = 0; j < 32; ++j) fp[tid * FIN_LD + c0 + j] = have_op ? __uint_as_float(v[j]) * (c0 < D / 2 ? ip_hi : ip_lo) : 0.f;
             if (have_od) { tmem_ld32(t_row + COL_OD + c0, v); tmem_ld_wait(); }
 #pragma unroll
             for (int j = 0; j < 32; ++j) fd[tid * FIN_LD + c0 + j] = have_od ? __uint_as_float(v[j]) * id : 0.f;
@@ -683,8 +739,8 @@ __global__ void __launch_bounds__(NT, 1) prefill_tc_kernel(Params P) {
 // Whether the tensor-core kernel takes this call; the caller has validated the arguments.
 bool prefill_tc_applicable(const tq_decode_args* a, int t_q) {
     if (a->d != 128) return false;
-    if (a->c_len > 0 && (a->k_bits_hi != 4 || a->k_bits_lo != 0 || a->v_bits_hi != 2 || a->v_bits_lo != 0 || !aligned(a->k_hi, 4) || !aligned(a->v_hi, 4)))
-        return false;
+    // fractional widths split the coordinates in halves of 64: (b, b - 1) bits as the reference does (cache.py:232-274)
+    if (a->c_len > 0 && ((a->k_bits_lo && a->k_bits_lo != a->k_bits_hi - 1) || (a->v_bits_lo && a->v_bits_lo != a->v_bits_hi - 1))) return false;
     if (a->c_len + a->sink_len + a->res_len >= 0x7fffffff) return false;       // positions are kept as 32-bit integers
     // uncompressed rows are read as 16-byte chunks
     if ((a->sink_len > 0 && (!aligned(a->sink_k, 16) || !aligned(a->sink_v, 16))) || (a->res_len > 0 && (!aligned(a->res_k, 16) || !aligned(a->res_v, 16))))

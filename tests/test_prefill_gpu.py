@@ -17,8 +17,8 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(params=["tcgen05", "mma.sync"], autouse=True)
 def which_kernel(request):
-    """Every case runs twice: with the tensor-core (tcgen05) kernel where it applies - head_dim 128, 4-bit keys, 2-bit values,
-    at least 64 query rows - and with the mma.sync kernel everywhere."""
+    """Every case runs twice: with the tensor-core (tcgen05) kernel where it applies - head_dim 128, at least 64 query rows;
+    byte-table unpack for 4-bit keys / 2-bit values, code by code for every other width - and with the mma.sync kernel everywhere."""
     from mlx_turboquant_b200 import kernels
     kernels.set_tuning("prefill_tc", 1 if request.param == "tcgen05" else 0)
     yield request.param
