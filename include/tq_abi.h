@@ -99,7 +99,7 @@ int tq_quantize_pack(const tq_quantize_args* a, void* stream);
 
 /* The tensor-core quantize kernel (fp16 rows, d = 128) and the 4-bit-key / 2-bit-value decode kernel wait on
  * mbarriers with an iteration limit; if a wait ever runs out the kernel drains and finishes, and this returns the
- * code of the first such wait on the current device (quantize 1-9, decode 101-103, several-query-token attention 104, dequantize 105, gather wait 201; 0 = none).  Synchronises the
+ * code of the first such wait on the current device (quantize 1-9, decode 101-103 and 106-108, several-query-token attention 104, dequantize 105, gather wait 201; 0 = none).  Synchronises the
  * device; no reference counterpart. */
 int tq_device_status(void);
 /* Back to 0 (after the caller has dealt with a reported time-out). */
@@ -310,9 +310,18 @@ float tq_fp16_table_scale(const float* centroids_host, int n);
  *   "prefill_tc" 0/1 (tq_prefill_attn at d = 128 with at least 64 query rows: the tcgen05 kernel, default, or always
  *   the mma.sync kernel),
  *   "decode_pdl" 0/1 (programmatic dependent launch: a call's prologue overlaps the previous kernel's tail),
- *   "gather_wait_polls" 1000..4000000 (polls of one word of a gather before the wait gives up; default 2000000, some two seconds).
+ *   "gather_wait_polls" 1000..4000000 (polls of one word of a gather before the wait gives up; default 2000000, some two seconds),
+ *   "decode_stream" 0/1 (the persistent streaming kernel for 4-bit keys / 2-bit values at d = 96 / 128 may be chosen, default, or never),
+ *   "decode_stream_min_run" 1.. (fewest packed 16-token tiles per warp of the persistent grid for which it is chosen; default 24).
  * Changing them changes tq_decode_workspace_bytes for the same sizes. */
 int tq_set_tuning(const char* key, int value);
+
+/* Which kernel tq_decode_attn would run for these arguments under the current tuning (no launch; no reference counterpart):
+ * 0 = general kernel (any width, d = 64 / 96 / 128 / 256), 1 = table-lookup kernel (4-bit keys / 2-bit values, d = 128: one CTA
+ * per (sequence, KV head, split)), 2 = streaming kernel (the same widths at d = 96 / 128, sign sketches allowed: persistent
+ * grid, chosen when the packed tokens of all lanes give every warp a long run).  Negative: the arguments are invalid
+ * (tq_last_error has the text). */
+int tq_decode_kernel_choice(const tq_decode_args* a);
 
 #ifdef __cplusplus
 }

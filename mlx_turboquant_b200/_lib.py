@@ -100,6 +100,7 @@ PROTOTYPES = {
     "tq_prefill_attn": (_i, [C.POINTER(DecodeArgs), _i, _vp]),
     "tq_decode_attn_static": (_i, [C.POINTER(DecodeArgs), _vp]),
     "tq_set_tuning": (_i, [C.c_char_p, _i]),
+    "tq_decode_kernel_choice": (_i, [C.POINTER(DecodeArgs)]),
     "tq_fp16_table_scale": (_f, [_vp, _i]),
     "tq_device_status": (_i, []),
     "tq_device_status_clear": (_i, []),

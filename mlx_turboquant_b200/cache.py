@@ -147,7 +147,7 @@ class TurboQuantKVCache:
         self._rotation = get_rotation_matrix(d, self.rotation_seed, device)
         self._k.load_tables(d, device)
         self._v.load_tables(d, device)
-        if not (self._k.fractional or self._v.fractional or self.qjl_correction):
+        if not (self._k.fractional or self._v.fractional):      # (the streaming decode kernel takes sign sketches too)
             self._tables = kernels.decode_tables(d, self.rotation_seed, self._rotation, self._k.cent_hi, self._k.bits_hi,
                                                  self._v.cent_hi, self._v.bits_hi, self._v.fp16_scale_hi)
         if self.qjl_correction:

@@ -593,6 +593,8 @@ static int g_tune_splits = 0;          // > 0: fixed number of packed splits
 extern int g_tune_dequantize_tc;       // rowops.cu: 0 = dequantize always on the CUDA-core row kernel
 extern int g_tune_prefill_tc;          // prefill.cu: 0 = several-query-token attention always on the mma.sync kernel
 static int g_tune_pdl = 1;             // programmatic dependent launch between consecutive calls
+static int g_tune_stream = 1;          // 0: never take the streaming kernel
+static int g_tune_stream_min_run = 24; // fewest packed tiles per warp for which the streaming kernel is chosen
 
 static int sm_count() {
     static int n = 0;
@@ -742,9 +744,23 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
     const bool direct = !g_tune_force_general && a->tables && d == 128 && a->c_len > 0 && a->k_bits_hi == 4 && a->k_bits_lo == 0 &&
                         a->v_bits_hi == 2 && a->v_bits_lo == 0 && !a->k_qjl_bits && aligned(a->k_hi, 16) && aligned(a->v_hi, 16) &&
                         aligned(a->k_norms, 16) && aligned(a->v_norms, 16) && a->c_lane_stride % 16 == 0 && direct_supported();
+    // streaming path: the same widths at d = 96 / 128, sign sketches allowed, when every warp of a persistent grid gets a long run of tiles
+    const bool qjl = a->c_len > 0 && a->k_qjl_bits != nullptr;
+    bool stream = g_tune_stream && !g_tune_force_general && a->tables && (d == 96 || d == 128) && a->c_len > 0 && a->k_bits_hi == 4 && a->k_bits_lo == 0 &&
+                  a->v_bits_hi == 2 && a->v_bits_lo == 0 && aligned(a->k_hi, 16) && aligned(a->v_hi, 16) && aligned(a->k_norms, 16) &&
+                  aligned(a->v_norms, 16) && a->c_lane_stride % 16 == 0 && !a->gather && !a->await_ll &&
+                  (!qjl || (aligned(a->k_qjl_bits, 16) && aligned(a->v_qjl_bits, 16) && aligned(a->k_qjl_gamma, 16) && aligned(a->v_qjl_gamma, 16) && aligned(a->qjl_proj, 16)));
+    StreamPlan stp{};
+    if (stream) {
+        stp = stream_plan(a->batch, a->n_q_heads, a->n_kv_heads, d, a->c_len, dense_len, sm_count());
+        stream = stp.range >= g_tune_stream_min_run && stp.npp + stp.nd <= 64 && stream_supported(d, qjl);
+    }
     const SplitPlan sp = plan_splits(a->batch, a->n_q_heads, a->n_kv_heads, a->c_len, dense_len, sm_count(), direct);
     const WsLayout wl = ws_layout(a->batch, a->n_q_heads, a->n_kv_heads, d, sp);
-    if (wl.total > workspace_bytes) return fail(TQ_ERR_INVALID, "tq_decode_attn: workspace %zu B < %zu B", workspace_bytes, wl.total);
+    const size_t st_base = align_up(std::max(size_t(a->batch) * a->n_kv_heads * sp.hg * sizeof(int), COUNTER_AREA), 256);
+    if (stream && st_base + stp.q16_bytes + stp.part_bytes > workspace_bytes)
+        return fail(TQ_ERR_INVALID, "tq_decode_attn: workspace %zu B < %zu B", workspace_bytes, st_base + stp.q16_bytes + stp.part_bytes);
+    if (!stream && wl.total > workspace_bytes) return fail(TQ_ERR_INVALID, "tq_decode_attn: workspace %zu B < %zu B", workspace_bytes, wl.total);
     if (sp.n_ps + sp.n_ds > MAX_SPLITS) return fail(TQ_ERR_UNSUPPORTED, "tq_decode_attn: too many splits");
 
     DecodeParams p{};
@@ -791,9 +807,15 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
     }
     p.pdl = g_tune_pdl;
     p.words_ok = (a->c_len > 0 && aligned(a->k_hi, 4) && aligned(a->v_hi, 4)) ? 1 : 0;   // packed rows readable as 32-bit words
-    p.tables = direct ? a->tables : nullptr;
+    p.tables = (direct || stream) ? a->tables : nullptr;
+    if (stream) {
+        p.st_grid = stp.grid; p.st_npp = stp.npp; p.st_nd = stp.nd; p.st_dt = stp.dt; p.st_range = stp.range;
+        p.st_q16 = reinterpret_cast<__half*>(ws + st_base);
+        p.st_part = reinterpret_cast<float*>(ws + st_base + stp.q16_bytes);
+        if (!(p.status = decode_status_ptr())) return fail(TQ_ERR_LAUNCH, "tq_decode_attn: cannot locate the status word");
+    }
     *out = p;
-    *direct_out = direct;
+    *direct_out = direct && !stream;
     return TQ_OK;
 }
 
@@ -803,6 +825,7 @@ int decode_launch(const DecodeParams& p0, bool direct, cudaStream_t s) {
         if (int rc = launch_gather_wait(p.await_ll, p.await_epochs, p.await_words, p.await_out, p.await_polls, s)) return rc;
         p.await_ll = nullptr;
     }
+    if (p.st_grid > 0) return launch_decode_stream(p, s);
     if (direct) return launch_decode_direct(p, s);
     const bool qjl = p.qjl_proj != nullptr;
     if (p.D == 64) return qjl ? launch_decode<64, true>(p, s) : launch_decode<64, false>(p, s);
@@ -821,12 +844,21 @@ extern "C" int tq_set_tuning(const char* key, int value) {
     if (k == "decode_ctas_per_sm" && value >= 1 && value <= 8) g_tune_ctas_per_sm = value;
     else if (k == "decode_force_general" && (value == 0 || value == 1)) g_tune_force_general = value;
     else if (k == "decode_pdl" && (value == 0 || value == 1)) g_tune_pdl = value;
+    else if (k == "decode_stream" && (value == 0 || value == 1)) g_tune_stream = value;
+    else if (k == "decode_stream_min_run" && value >= 1 && value <= (1 << 20)) g_tune_stream_min_run = value;
     else if (k == "decode_splits" && value >= 0 && value <= MAX_SPLITS - 64) g_tune_splits = value;
     else if (k == "gather_wait_polls" && value >= 1000 && value <= 4000000) g_tune_wait_polls = value;
     else if (k == "prefill_tc" && (value == 0 || value == 1)) g_tune_prefill_tc = value;
     else if (k == "dequantize_tc" && (value == 0 || value == 1)) g_tune_dequantize_tc = value;
     else return fail(TQ_ERR_INVALID, "tq_set_tuning: unknown key or bad value: %s=%d", key, value);
     return TQ_OK;
+}
+
+extern "C" int tq_decode_kernel_choice(const tq_decode_args* a) {
+    DecodeParams p;
+    bool direct = false;
+    if (decode_prepare(a, a ? a->workspace : nullptr, a ? a->workspace_bytes : 0, &p, &direct)) return -1;
+    return p.st_grid > 0 ? 2 : direct ? 1 : 0;
 }
 
 extern "C" int tq_gather_wait(const unsigned long long* ll, const unsigned* epochs, int64_t n_words, void* out, void* stream) {
@@ -906,7 +938,7 @@ extern "C" float tq_fp16_table_scale(const float* centroids_host, int n) {
 }
 
 extern "C" size_t tq_decode_tables_bytes(int d, int k_bits, int v_bits) {
-    return (d == 128 && k_bits == 4 && v_bits == 2) ? direct_tables_bytes() : 0;
+    return ((d == 128 || d == 96) && k_bits == 4 && v_bits == 2) ? direct_tables_bytes() : 0;
 }
 
 extern "C" int tq_decode_tables_build(int d, const float* rot, const float* k_cent, int k_bits, const float* v_cent, int v_bits,
@@ -915,7 +947,7 @@ extern "C" int tq_decode_tables_build(int d, const float* rot, const float* k_ce
     if (need == 0) return fail(TQ_ERR_UNSUPPORTED, "tq_decode_tables_build: no kernel uses prebuilt constants for d=%d at %d-bit keys / %d-bit values", d, k_bits, v_bits);
     if (!rot || !k_cent || !v_cent || !tables) return fail(TQ_ERR_INVALID, "tq_decode_tables_build: null pointer");
     if (!aligned(tables, 256) || bytes < need) return fail(TQ_ERR_INVALID, "tq_decode_tables_build: the buffer must be 256-byte aligned and hold %zu bytes", need);
-    return direct_tables_build(rot, k_cent, v_cent, v_cent_scale, tables, static_cast<cudaStream_t>(stream));
+    return direct_tables_build(d, rot, k_cent, v_cent, v_cent_scale, tables, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" size_t tq_decode_workspace_bytes(int batch, int n_q_heads, int n_kv_heads, int d, int64_t c_len,
@@ -924,7 +956,14 @@ extern "C" size_t tq_decode_workspace_bytes(int batch, int n_q_heads, int n_kv_h
     // The larger of the two split plans tq_decode_attn can choose for these sizes (current tuning values).
     const size_t a = ws_layout(batch, n_q_heads, n_kv_heads, d, plan_splits(batch, n_q_heads, n_kv_heads, c_len, dense_len, sm_count(), false)).total;
     const size_t b = ws_layout(batch, n_q_heads, n_kv_heads, d, plan_splits(batch, n_q_heads, n_kv_heads, c_len, dense_len, sm_count(), true)).total;
-    return a > b ? a : b;
+    size_t c = 0;
+    if ((d == 96 || d == 128) && c_len > 0) {      // the streaming kernel's layout: counters' area, prepared queries, partials
+        const StreamPlan sp = stream_plan(batch, n_q_heads, n_kv_heads, d, c_len, dense_len, sm_count());
+        const int hg = (n_q_heads / n_kv_heads + HPG - 1) / HPG;
+        if (sp.npp + sp.nd <= 64)
+            c = align_up(std::max(size_t(batch) * n_kv_heads * hg * sizeof(int), COUNTER_AREA), 256) + sp.q16_bytes + sp.part_bytes;
+    }
+    return std::max(a, std::max(b, c));
 }
 
 extern "C" int tq_decode_step(const tq_decode_args* a, const void* k_new, const void* v_new, void* stream) {

@@ -50,7 +50,32 @@ struct DecodeParams {
     void* await_out;
     int await_polls;
     int* status;                       // the device's status word (first bounded wait that ran out)
+    // streaming kernel (decode_stream.cu): every warp of a persistent grid walks its own contiguous run of the packed
+    // tiles of all cache lanes; partials per (lane, slot) and the prepared queries live in the workspace
+    int st_grid;                       // CTAs of the persistent grid (0: another kernel runs)
+    int st_npp, st_nd, st_dt;          // packed-partial slots per lane; dense items per lane and tiles per dense item
+    int64_t st_range;                  // packed tiles per warp
+    __half* st_q16;                    // workspace: per query head [rotated | raw | sketch] scaled fp16 query
+    float* st_part;                    // workspace: partials (lane, slot, head, D + 36)
 };
+
+// Constants of the 4-bit-key / 2-bit-value kernels in global memory, built once per (rotation, codebooks) by
+// tq_decode_tables_build: the 64 KB image of the shared-memory lookup tables (slot e at e * 256: 32 copies of
+// half2(kc[e & 15], kc[e >> 4]), then 16 copies of the value entry) and, for d = 128, R split into two fp16 matrices in
+// mma A-fragment order.
+namespace dd {
+constexpr uint32_t TABLES_MAGIC = 0x54513432u;
+struct DirectTables {
+    uint32_t magic; int d, kb, vb; float v_scale; uint32_t pad[59];          // 256 B
+    uint4 lut[256 * 16];                                       // image of the shared-memory tables (64 KB)
+    uint4 rfrag[8 * 8 * 2 * 32];                               // d = 128: [warp][k-step][hi | lo][lane] mma A fragments of R_hi, R_lo (64 KB)
+};
+static_assert(sizeof(DirectTables) == 256 + 65536 + 65536, "table buffer layout");
+constexpr uint32_t LO_BASE = 2048u;                            // lowest shared-window address the kernels use
+constexpr uint32_t LUT_BASE = 0x10000u;                        // 256 slots of 256 B, addressed by one byte-permute
+constexpr uint32_t C_BASE = 0x20000u;                          // first byte above the tables
+unsigned probe_smem_base();                                    // shared-window address where dynamic shared memory starts (~0u on error)
+}  // namespace dd
 
 // Validates the arguments, picks the path and the split plan and fills the kernel parameters for the given
 // scratch buffer (which must be zero-filled before its first use; the kernel leaves its counters at zero).
@@ -62,8 +87,14 @@ int decode_launch(const DecodeParams& p, bool direct, cudaStream_t s);
 // device (one tiny synchronous probe launch on first use) that the kernel's shared-memory plan fits the device.
 bool direct_supported();
 size_t direct_tables_bytes();
-int direct_tables_build(const float* rot, const float* k_cent, const float* v_cent, float v_scale, void* tables, cudaStream_t s);
+int direct_tables_build(int d, const float* rot, const float* k_cent, const float* v_cent, float v_scale, void* tables, cudaStream_t s);
 int launch_decode_direct(const DecodeParams& p, cudaStream_t s);
+// decode_stream.cu: persistent kernel for 4-bit keys / 2-bit values at d = 96 / 128 (sign sketches optional) when the
+// packed tokens of all lanes amount to many tiles per warp.
+struct StreamPlan { int grid, npp, nd, dt; int64_t range; size_t q16_bytes, part_bytes; };
+bool stream_supported(int d, bool qjl);
+StreamPlan stream_plan(int batch, int n_q_heads, int n_kv_heads, int d, int64_t c_len, int64_t dense_len, int sms);
+int launch_decode_stream(const DecodeParams& p, cudaStream_t s);
 int launch_gather_wait(const unsigned long long* ll, const unsigned* epochs, int64_t n_words, void* out, int max_polls, cudaStream_t s);
 int* decode_status_ptr();          // device address of the status word on the current device (null on error)
 int decode_status_host();          // code of the first bounded wait that ran out on this device (0 = none), -1 on error

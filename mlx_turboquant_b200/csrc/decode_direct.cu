@@ -49,9 +49,6 @@ constexpr int PF_AHEAD = 12;                                   // a tile is aske
 
 // Absolute shared-window addresses.  The dynamic allocation starts at `sbase` <= LO_BASE (reserved system bytes come
 // first); the tables must start on a 64 KB boundary.
-constexpr uint32_t LO_BASE = 2048u;
-constexpr uint32_t LUT_BASE = 0x10000u;                        // 256 slots of 256 B
-constexpr uint32_t C_BASE = 0x20000u;
 constexpr uint32_t HI_BYTES = 72u * 1024u;                     // above the tables: reduction scratch
 constexpr uint32_t LUT_BAR = C_BASE + HI_BYTES;                // arrival of the table image
 constexpr uint32_t QS = LUT_BAR + 64;                          // [8][D] half: scaled fp16 query (rotated or raw)
@@ -77,15 +74,8 @@ static_assert(LO_BASE + uint32_t(NW) * DSTAGE <= LUT_BAR, "dense staging must en
 constexpr uint32_t WAIT_LIMIT = 4u << 20;
 constexpr int ERR_TABLES = 102, ERR_LAYOUT = 103, ERR_GATHER_WAIT = 201;
 
-// Constants of the kernel in global memory, built once per (rotation, codebooks) by direct_tables_build.
-constexpr uint32_t TABLES_MAGIC = 0x54513432u;
 constexpr int ROT_WARPS = D / 16;                              // warps that rotate the query: one 16-row slab of R each
-struct DirectTables {
-    uint32_t magic; int d, kb, vb; float v_scale; uint32_t pad[59];          // 256 B
-    uint4 lut[256 * 16];                                       // image of the shared-memory tables (64 KB)
-    uint4 rfrag[ROT_WARPS * (D / 16) * 2 * 32];                // [warp][k-step][hi | lo][lane]: mma A fragments of R_hi, R_lo (64 KB)
-};
-static_assert(sizeof(DirectTables) == 256 + 65536 + 65536, "table buffer layout");
+static_assert(sizeof(DirectTables::rfrag) == sizeof(uint4) * ROT_WARPS * (D / 16) * 2 * 32, "rotation fragments");
 
 __device__ int g_status = 0;
 __device__ unsigned g_probe_base = 0;
@@ -140,7 +130,7 @@ __global__ void smem_base_probe() {
 // One block builds the constants.  Table slot e at e * 256: +0 32 copies of half2(kc[e & 15], kc[e >> 4]); +128 16
 // copies of the value entry (two half2: one per coordinate, each pairing the two tokens of a pair); copies r with
 // (r & 2) serve lanes that read the token pair in swapped order.
-__global__ void __launch_bounds__(1024) build_tables_kernel(const float* rot, const float* kc, const float* vc, float v_scale, DirectTables* t) {
+__global__ void __launch_bounds__(1024) build_tables_kernel(const float* rot, const float* kc, const float* vc, float v_scale, int d, DirectTables* t) {
     __shared__ __half ctab[32];
     const int tid = threadIdx.x, nt = blockDim.x;
     if (tid < 32) {
@@ -149,7 +139,7 @@ __global__ void __launch_bounds__(1024) build_tables_kernel(const float* rot, co
         if (k < (which ? 4 : 16)) c = (which ? vc : kc)[k];
         ctab[tid] = __float2half_rn(c * (which ? v_scale : 1.f));
     }
-    if (tid == 0) { t->magic = TABLES_MAGIC; t->d = D; t->kb = 4; t->vb = 2; t->v_scale = v_scale; }
+    if (tid == 0) { t->magic = TABLES_MAGIC; t->d = d; t->kb = 4; t->vb = 2; t->v_scale = v_scale; }
     __syncthreads();
     for (int idx = tid; idx < 256 * 16; idx += nt) {
         const int e = idx >> 4, q = idx & 15;
@@ -171,7 +161,7 @@ __global__ void __launch_bounds__(1024) build_tables_kernel(const float* rot, co
     }
     // A fragments (m16n8k16, row-major A) of the 16 x 16 blocks of R: a0 = (row g, cols 2t, 2t+1), a1 = (row g+8, same
     // cols), a2 = (row g, cols 2t+8, 2t+9), a3 = (row g+8, cols 2t+8, 2t+9); warp w owns rows 16 w .. 16 w + 15
-    for (int idx = tid; idx < ROT_WARPS * (D / 16) * 32; idx += nt) {
+    for (int idx = tid; d == D && idx < ROT_WARPS * (D / 16) * 32; idx += nt) {       // (other head dims: the streaming kernel's queries are rotated by a launch of their own)
         const int w = idx / ((D / 16) * 32), ks = (idx / 32) % (D / 16), lane = idx & 31, g = lane >> 2, tt = lane & 3;
         uint32_t hi[4], lo[4];
 #pragma unroll
@@ -663,7 +653,7 @@ __global__ void __launch_bounds__(256) gather_wait_kernel(const unsigned long lo
         atomicCAS(&g_status, 0, ERR_GATHER_WAIT);
 }
 
-static unsigned probe_smem_base() {
+unsigned probe_smem_base() {
     // The kernel addresses its tables by absolute shared-window address; where the dynamic allocation starts is a
     // property of the device / driver, read once per device with a one-thread launch (tq_decode_tables_build does it
     // at set-up; a decode call only if no tables were ever built on the device).
@@ -694,8 +684,8 @@ bool direct_supported() {
 
 size_t direct_tables_bytes() { return sizeof(dd::DirectTables); }
 
-int direct_tables_build(const float* rot, const float* k_cent, const float* v_cent, float v_scale, void* tables, cudaStream_t s) {
-    dd::build_tables_kernel<<<1, 1024, 0, s>>>(rot, k_cent, v_cent, v_scale > 0.f ? v_scale : 1.f, static_cast<dd::DirectTables*>(tables));
+int direct_tables_build(int d, const float* rot, const float* k_cent, const float* v_cent, float v_scale, void* tables, cudaStream_t s) {
+    dd::build_tables_kernel<<<1, 1024, 0, s>>>(rot, k_cent, v_cent, v_scale > 0.f ? v_scale : 1.f, d, static_cast<dd::DirectTables*>(tables));
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
     if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_decode_tables_build: %s", cudaGetErrorString(e));
