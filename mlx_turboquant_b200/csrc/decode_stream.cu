@@ -39,7 +39,10 @@ using dd::LO_BASE;
 using dd::LUT_BASE;
 using dd::TABLES_MAGIC;
 
-constexpr int NW = 16, NT = NW * 32;
+#ifndef TQ_STREAM_WARPS
+#define TQ_STREAM_WARPS 16
+#endif
+constexpr int NW = TQ_STREAM_WARPS, NT = NW * 32;
 #ifndef TQ_STREAM_STAGES
 #define TQ_STREAM_STAGES 4
 #endif
@@ -120,61 +123,81 @@ __device__ __forceinline__ int tok_of_slot(int s) {
 
 // ---- launch 1: the queries ------------------------------------------------------------------------------
 // q_rot[h][j] = sum_k q[h][k] R[j][k] (rotation.py:81-110), u[h][p] = sum_k q[h][k] S[p][k] (qjl.py:70-94), both times
-// scale * log2(e), as fp16; the raw query likewise (for the uncompressed tokens).  Block = 8 query heads, thread = a row
-// of R or S.
+// scale * log2(e), as fp16; the raw query likewise (for the uncompressed tokens).  Block = QPB query heads; R and S are
+// staged in shared memory with coalesced loads (rows padded by 4 floats: the 128-bit row reads of 8 consecutive threads
+// then cover all 32 banks); thread = (row of R or S, half of the block's heads).
+constexpr int QPB = 16, QNT = 256;
+template <int D> __host__ __device__ constexpr size_t query_smem() { return (size_t(D + QM) * (D + 4) + size_t(QPB) * D) * sizeof(float); }
 template <int D>
-__global__ void __launch_bounds__(128) stream_query_kernel(DecodeParams p) {
-    __shared__ __align__(16) float qf[8][D];
+__global__ void __launch_bounds__(QNT) stream_query_kernel(DecodeParams p) {
+    extern __shared__ __align__(16) unsigned char smem_q[];
+    constexpr int LDR = D + 4, QS = q_stride(D);
+    float* rs = reinterpret_cast<float*>(smem_q);                // [D + 32][LDR]: R, then S
+    float* qf = rs + (D + QM) * LDR;                             // [QPB][D]
     const int tid = threadIdx.x;
-    const int64_t n_q = int64_t(p.B) * p.Hq, q0 = int64_t(blockIdx.x) * 8;
-    constexpr int QS = q_stride(D);
+    const int64_t n_q = int64_t(p.B) * p.Hq, q0 = int64_t(blockIdx.x) * QPB;
+    const int rows = D + (p.qjl_proj ? QM : 0);
     pdl_trigger();
+    for (int i = tid; i < rows * (D / 4); i += QNT) {            // constants: before the wait
+        const int r = i / (D / 4), k4 = i - r * (D / 4);
+        const float4 x = __ldg(reinterpret_cast<const float4*>(r < D ? p.rot + int64_t(r) * D : p.qjl_proj + int64_t(r - D) * D) + k4);
+        *reinterpret_cast<float4*>(rs + r * LDR + 4 * k4) = x;
+    }
     pdl_wait();
-    for (int e = tid; e < 8 * D; e += 128) {
+    const float f = p.scale * LOG2E;
+    for (int e = tid; e < QPB * D; e += QNT) {
         const int v = e / D, c = e - v * D;
-        qf[v][c] = q0 + v < n_q ? load_as_f32(p.q, p.q_dtype, (q0 + v) * D + c) : 0.f;
+        const float x = q0 + v < n_q ? load_as_f32(p.q, p.q_dtype, (q0 + v) * D + c) : 0.f;
+        qf[e] = x;
+        if (q0 + v < n_q) p.st_q16[(q0 + v) * QS + D + c] = __float2half_rn(x * f);
     }
     __syncthreads();
-    const float f = p.scale * LOG2E;
-    const int rows = D + (p.qjl_proj ? QM : 0);
-    for (int r = tid; r < rows; r += 128) {
-        const float4* row = reinterpret_cast<const float4*>(r < D ? p.rot + int64_t(r) * D : p.qjl_proj + int64_t(r - D) * D);
+    const int vh = tid / 128, r0 = tid - vh * 128;               // heads vh * 8 .. vh * 8 + 7 of the block
+    for (int r = r0; r < rows; r += 128) {
+        const float4* row = reinterpret_cast<const float4*>(rs + r * LDR);
         float acc[8];
 #pragma unroll
         for (int v = 0; v < 8; ++v) acc[v] = 0.f;
 #pragma unroll 4
         for (int k = 0; k < D / 4; ++k) {
-            const float4 x = __ldg(row + k);
+            const float4 x = row[k];
 #pragma unroll
             for (int v = 0; v < 8; ++v) {
-                const float4 y = *reinterpret_cast<const float4*>(&qf[v][4 * k]);
+                const float4 y = *reinterpret_cast<const float4*>(qf + (vh * 8 + v) * D + 4 * k);
                 acc[v] = fmaf(x.x, y.x, fmaf(x.y, y.y, fmaf(x.z, y.z, fmaf(x.w, y.w, acc[v]))));
             }
         }
         const int dst = r < D ? r : 2 * D + (r - D);
 #pragma unroll
         for (int v = 0; v < 8; ++v)
-            if (q0 + v < n_q) p.st_q16[(q0 + v) * QS + dst] = __float2half_rn(acc[v] * f);
-    }
-    for (int e = tid; e < 8 * D; e += 128) {
-        const int v = e / D, c = e - v * D;
-        if (q0 + v < n_q) p.st_q16[(q0 + v) * QS + D + c] = __float2half_rn(qf[v][c] * f);
+            if (q0 + vh * 8 + v < n_q) p.st_q16[(q0 + vh * 8 + v) * QS + dst] = __float2half_rn(acc[v] * f);
     }
 }
 
-// half2 of two signs (+1 for a set bit) from a word that holds the two sign bits at positions 15 and 31
-__device__ __forceinline__ uint32_t sign_pair16(uint32_t x) { return 0xBC00BC00u ^ (x & 0x80008000u); }
+// Three-input logic in ONE instruction with both constants in registers (written as two C operators with two literal
+// constants the compiler emits two instructions: an instruction takes one immediate only).  The integer pipe is what
+// bounds this kernel.
+template <int LUT> __device__ __forceinline__ uint32_t lop3(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(d) : "r"(a), "r"(b), "r"(c), "n"(LUT));
+    return d;
+}
+// loop-invariant constants kept in registers (the asm hides their values from constant propagation)
+__device__ __forceinline__ uint32_t reg_const(uint32_t v) {
+    uint32_t r;
+    asm volatile("mov.b32 %0, %1;" : "=r"(r) : "r"(v));
+    return r;
+}
+struct BitConsts { uint32_t sign_mask, minus_ones, lo_nibbles; };
+// half2 of two signs (+1 for a set bit) from a word that holds the two sign bits at positions 15 and 31: (x & 0x80008000) ^ 0xBC00BC00
+__device__ __forceinline__ uint32_t sign_pair16(uint32_t x, const BitConsts& k) { return lop3<0x6A>(x, k.sign_mask, k.minus_ones); }
+// (a & 0x0F0F0F0F) | (b & 0xF0F0F0F0)
+__device__ __forceinline__ uint32_t nibble_mix(uint32_t a, uint32_t b, const BitConsts& k) { return lop3<0xE4>(a, b, k.lo_nibbles); }
 
-// Softmax step on scores that already carry the key norms (and the sketch term).  `partial`: the tile reaches past
-// the end of the cache and ok0 / ok1 say which of this lane's two tokens exist.  pr: the four weights times the value scale.
+// Softmax step on scores that already carry the key norms (and the sketch term); tokens past the end of the cache come
+// in with score -inf and norm 0.  pr: the four weights times the value scale.
 template <int NZ>
-__device__ __forceinline__ void softmax_stream(float (&s)[4], float vn0, float vn1, float vx, bool partial, bool ok0, bool ok1,
-                                               WarpAcc<128, NZ>& st, uint32_t (&bp)[2], float (&pr)[4]) {
-    if (partial) {
-        vn0 = ok0 ? vn0 : 0.f; vn1 = ok1 ? vn1 : 0.f;
-        s[0] = ok0 ? s[0] : -INFINITY; s[1] = ok0 ? s[1] : -INFINITY;
-        s[2] = ok1 ? s[2] : -INFINITY; s[3] = ok1 ? s[3] : -INFINITY;
-    }
+__device__ __forceinline__ void softmax_stream(float (&s)[4], float vn0, float vn1, float vx, WarpAcc<128, NZ>& st, uint32_t (&bp)[2], float (&pr)[4]) {
     const float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]), vmax = fmaxf(fmaxf(vn0, vn1), vx);
     if (__any_sync(0xffffffffu, mx0 > st.mt[0] || mx1 > st.mt[1] || vmax > st.vt)) softmax_refresh<128, NZ>(mx0, mx1, vmax, st);
     const float p0 = ex2(s[0] - st.m[0]), p1 = ex2(s[1] - st.m[1]), p2 = ex2(s[2] - st.m[0]), p3 = ex2(s[3] - st.m[1]);
@@ -349,6 +372,8 @@ __global__ void __launch_bounds__(NT, 1) decode_stream_kernel(DecodeParams p) {
         const uint32_t v_off0 = uint32_t(tokV0) * (D / 4) + 4u * g, v_off1 = uint32_t(tokV1) * (D / 4) + 4u * g;   // (row groups without a word read their neighbours' bytes: padding rows)
         const uint32_t p_off = 4u * tokP, q_off = 4u * tokQ;
 
+        BitConsts kc;
+        kc.sign_mask = reg_const(0x80008000u); kc.minus_ones = reg_const(0xBC00BC00u); kc.lo_nibbles = reg_const(0x0F0F0F0Fu);
         const int tail_ti = (c_len & (TILE - 1)) ? n_tiles - 1 : -1;          // the tile that reaches past the end of the cache
         int a = int(T0 / n_tiles), ti = int(T0 - int64_t(a) * n_tiles);       // lane and tile being computed
         int slot = wg - int((int64_t(a) * n_tiles) / p.st_range);            // partial slot = this warp's rank among the lane's warps
@@ -429,8 +454,6 @@ __global__ void __launch_bounds__(NT, 1) decode_stream_kernel(DecodeParams p) {
                 break;
             }
             const bool partial = ti == tail_ti;
-            bool ok0 = true, ok1 = true;
-            if (partial) { ok0 = ti * TILE + tokA < c_len; ok1 = ti * TILE + tokA + 8 < c_len; }
 
             // ---- scores: S[token][head] = K . q^T, keys straight from the byte table ----
             uint32_t kwa[KW], kwb[KW];
@@ -466,19 +489,27 @@ __global__ void __launch_bounds__(NT, 1) decode_stream_kernel(DecodeParams p) {
                 float sq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int ks = 0; ks < QM / 16; ++ks)
-                    mma16816(sq, sign_pair16(zs0 << (3 - 2 * ks)), sign_pair16(zs1 << (3 - 2 * ks)), sign_pair16(zs0 << (2 - 2 * ks)),
-                             sign_pair16(zs1 << (2 - 2 * ks)), bu[ks][0], bu[ks][1]);
+                    mma16816(sq, sign_pair16(zs0 << (3 - 2 * ks), kc), sign_pair16(zs1 << (3 - 2 * ks), kc), sign_pair16(zs0 << (2 - 2 * ks), kc),
+                             sign_pair16(zs1 << (2 - 2 * ks), kc), bu[ks][0], bu[ks][1]);
                 const float gk0 = ring_f32o<P::O_KG>(aa) * (QJL_C / D), gk1 = ring_f32o<P::O_KG + 32>(aa) * (QJL_C / D);
                 s[0] = fmaf(s[0], kn0, sq[0] * gk0); s[1] = fmaf(s[1], kn0, sq[1] * gk0);
                 s[2] = fmaf(s[2], kn1, sq[2] * gk1); s[3] = fmaf(s[3], kn1, sq[3] * gk1);
                 gv0 = ring_f32o<P::O_VG>(aa); gv1 = ring_f32o<P::O_VG + 32>(aa);
-                if (partial) { gv0 = ok0 ? gv0 : 0.f; gv1 = ok1 ? gv1 : 0.f; }
             } else {
                 s[0] *= kn0; s[1] *= kn0; s[2] *= kn1; s[3] *= kn1;
             }
+            if (partial) {
+                // the last tile of a lane reaches past the end of the cache: its missing tokens (arbitrary bytes) get no weight.
+                // A real branch (the barrier keeps it one): once per lane, not a dozen selects per tile.
+                __syncwarp();
+                const bool ok0 = ti * TILE + tokA < c_len, ok1 = ti * TILE + tokA + 8 < c_len;
+                vn0 = ok0 ? vn0 : 0.f; vn1 = ok1 ? vn1 : 0.f; gv0 = ok0 ? gv0 : 0.f; gv1 = ok1 ? gv1 : 0.f;
+                s[0] = ok0 ? s[0] : -INFINITY; s[1] = ok0 ? s[1] : -INFINITY;
+                s[2] = ok1 ? s[2] : -INFINITY; s[3] = ok1 ? s[3] : -INFINITY;
+            }
             uint32_t bp[2];
             float pr[4];
-            softmax_stream<NZ>(s, vn0, vn1, fmaxf(gv0, gv1), partial, ok0, ok1, st, bp, pr);
+            softmax_stream<NZ>(s, vn0, vn1, fmaxf(gv0, gv1), st, bp, pr);
 
             // ---- values: O^T[coordinate][head] += V^T . P^T ----
             {
@@ -487,8 +518,8 @@ __global__ void __launch_bounds__(NT, 1) decode_stream_kernel(DecodeParams p) {
                 // pair the nibbles (two adjacent coordinates) of the two tokens: byte j of z0 = (first word, nibble 2j) |
                 // (second word, nibble 2j) << 4, z1 the odd nibbles; one 64-bit lookup yields the two operand registers of
                 // rows g and g + 8 (the two coordinates, the token pair in each)
-                const uint32_t z0 = (va & 0x0F0F0F0Fu) | ((vb << 4) & 0xF0F0F0F0u), z1 = ((va >> 4) & 0x0F0F0F0Fu) | (vb & 0xF0F0F0F0u);
-                const uint32_t w0 = (vc & 0x0F0F0F0Fu) | ((vd << 4) & 0xF0F0F0F0u), w1 = ((vc >> 4) & 0x0F0F0F0Fu) | (vd & 0xF0F0F0F0u);
+                const uint32_t z0 = nibble_mix(va, vb << 4, kc), z1 = nibble_mix(va >> 4, vb, kc);
+                const uint32_t w0 = nibble_mix(vc, vd << 4, kc), w1 = nibble_mix(vc >> 4, vd, kc);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const uint2 e01 = lut64(__byte_perm(z0, c2, 0x7604 | (k << 4)));   // m-tile 2k:   k slots 2t, 2t+1
@@ -508,8 +539,8 @@ __global__ void __launch_bounds__(NT, 1) decode_stream_kernel(DecodeParams p) {
                 // put the two tokens' half-words side by side (row r of the first at bit r, of the second at bit r + 16)
                 const uint32_t x01 = __byte_perm(zv0, zv1, 0x5410) << (7 - g), y01 = __byte_perm(zv0, zv1, 0x7632) << (7 - g);
                 const uint32_t x23 = __byte_perm(zv2, zv3, 0x5410) << (7 - g), y23 = __byte_perm(zv2, zv3, 0x7632) << (7 - g);
-                mma16816(st.z[0], sign_pair16(x01 << 8), sign_pair16(x01), sign_pair16(x23 << 8), sign_pair16(x23), bz0, bz1);
-                mma16816(st.z[NZ ? 1 : 0], sign_pair16(y01 << 8), sign_pair16(y01), sign_pair16(y23 << 8), sign_pair16(y23), bz0, bz1);
+                mma16816(st.z[0], sign_pair16(x01 << 8, kc), sign_pair16(x01, kc), sign_pair16(x23 << 8, kc), sign_pair16(x23, kc), bz0, bz1);
+                mma16816(st.z[NZ ? 1 : 0], sign_pair16(y01 << 8, kc), sign_pair16(y01, kc), sign_pair16(y23 << 8, kc), sign_pair16(y23, kc), bz0, bz1);
             }
 
             // ---- the stage is free: ask for the tile NS further on ----
@@ -528,14 +559,30 @@ __global__ void __launch_bounds__(NT, 1) decode_stream_kernel(DecodeParams p) {
 }
 
 // ---- launch 3: merge --------------------------------------------------------------------------------------
-// One block per lane (sequence, KV head, head group), one thread per coordinate.
+// A block takes LPB lanes (sequence, KV head, head group), D threads each (one per coordinate); R and S are staged in
+// shared memory once per block, so the rotation back costs shared-memory reads instead of a chain of L2 round trips.
+constexpr int LPB = 4;
+template <int D> __host__ __device__ constexpr size_t merge_smem() { return (size_t(D + QM) * D + size_t(LPB) * (2 * MAX_PARTS + D + QM)) * sizeof(float); }
 template <int D, bool QJL>
-__global__ void __launch_bounds__(D) stream_merge_kernel(DecodeParams p) {
+__global__ void __launch_bounds__(LPB * D) stream_merge_kernel(DecodeParams p) {
+    extern __shared__ __align__(16) unsigned char smem_m[];
     constexpr int PS = part_stride(D);
-    __shared__ float s_m[MAX_PARTS], s_l[MAX_PARTS], s_rot[D], s_z[QM];
-    const int a = blockIdx.x, c = threadIdx.x;
+    float* rs = reinterpret_cast<float*>(smem_m);                 // [D][D] R, then [32][D] S
+    const int tid = threadIdx.x, sub = tid / D, c = tid - sub * D;
+    float* s_m = rs + (D + QM) * D + sub * (2 * MAX_PARTS + D + QM);
+    float* s_l = s_m + MAX_PARTS;
+    float* s_rot = s_l + MAX_PARTS;
+    float* s_z = s_rot + D;
     pdl_trigger();
+    const int rows = D + (QJL ? QM : 0);
+    for (int i = tid; i < rows * (D / 4); i += LPB * D) {         // constants: before the wait
+        const int r = i / (D / 4), k4 = i - r * (D / 4);
+        *reinterpret_cast<float4*>(rs + r * D + 4 * k4) = __ldg(reinterpret_cast<const float4*>(r < D ? p.rot + int64_t(r) * D : p.qjl_proj + int64_t(r - D) * D) + k4);
+    }
     pdl_wait();
+    const int L = p.B * p.Hkv * p.HG;
+    const int a = min(blockIdx.x * LPB + sub, L - 1);
+    const bool live = blockIdx.x * LPB + sub < L;
     const int kvl = a / p.HG, hg = a - kvl * p.HG, b = kvl / p.Hkv, hkv = kvl - b * p.Hkv;
     const int heads_here = min(HPG, p.G - hg * HPG);
     const int64_t qhead0 = int64_t(b) * p.Hq + int64_t(hkv) * p.G + hg * HPG;
@@ -546,11 +593,11 @@ __global__ void __launch_bounds__(D) stream_merge_kernel(DecodeParams p) {
     const int n_pp = n_tiles > 0 ? lw - fw + 1 : 0;
     const float inv_vs = 1.f / p.v_scale_hi;
     const float* base = p.st_part + int64_t(a) * n_slots * p.slots * PS;
-    for (int h = 0; h < heads_here; ++h) {
+    const int64_t sstride = int64_t(p.slots) * PS;
+    for (int h = 0; h < p.slots; ++h) {
         const float* ph = base + h * PS;
-        const int64_t sstride = int64_t(p.slots) * PS;
         if (c < n_slots) {
-            const bool valid = c < n_pp || c >= p.st_npp;
+            const bool valid = h < heads_here && (c < n_pp || c >= p.st_npp);
             s_m[c] = valid ? __ldcg(ph + c * sstride + D + QM) : -INFINITY;
             s_l[c] = valid ? __ldcg(ph + c * sstride + D + QM + 1) : 0.f;
         }
@@ -558,15 +605,15 @@ __global__ void __launch_bounds__(D) stream_merge_kernel(DecodeParams p) {
         float M = -INFINITY;
         for (int i = 0; i < n_slots; ++i) M = fmaxf(M, s_m[i]);
         float Lsum = 0.f, ar = 0.f, ad = 0.f, az = 0.f;
+#pragma unroll 4
         for (int i = 0; i < n_slots; ++i) {
             const float mi = s_m[i];
-            if (mi == -INFINITY) continue;
-            const float w = ex2(mi - M);
+            const float w = mi == -INFINITY ? 0.f : ex2(mi - M);
+            const float v = mi == -INFINITY ? 0.f : __ldcg(ph + i * sstride + c);
             Lsum = fmaf(w, s_l[i], Lsum);
-            const float v = __ldcg(ph + i * sstride + c);
             if (i < p.st_npp) {
                 ar = fmaf(w, v, ar);
-                if (QJL && c < QM) az = fmaf(w, __ldcg(ph + i * sstride + D + c), az);
+                if (QJL && c < QM && mi != -INFINITY) az = fmaf(w, __ldcg(ph + i * sstride + D + c), az);
             } else {
                 ad = fmaf(w, v, ad);
             }
@@ -577,12 +624,12 @@ __global__ void __launch_bounds__(D) stream_merge_kernel(DecodeParams p) {
         // undo the rotation of the packed part (y @ R, rotation.py:68-78) and add (c/d) z @ S (qjl.py:89-92)
         float v = ad;
 #pragma unroll 8
-        for (int j = 0; j < D; ++j) v = fmaf(s_rot[j], __ldg(p.rot + int64_t(j) * D + c), v);
+        for (int j = 0; j < D; ++j) v = fmaf(s_rot[j], rs[j * D + c], v);
         if (QJL) {
 #pragma unroll 8
-            for (int i = 0; i < QM; ++i) v = fmaf(s_z[i], __ldg(p.qjl_proj + int64_t(i) * D + c), v);
+            for (int i = 0; i < QM; ++i) v = fmaf(s_z[i], rs[(D + i) * D + c], v);
         }
-        store_from_f32(p.out, p.out_dtype, (qhead0 + h) * D + c, v / Lsum);
+        if (live && h < heads_here) store_from_f32(p.out, p.out_dtype, (qhead0 + h) * D + c, v / Lsum);
         __syncthreads();
     }
 }
@@ -605,6 +652,8 @@ template <int D, bool QJL> static int launch(const DecodeParams& p, cudaStream_t
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !set[dev].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(decode_stream_kernel<D, QJL>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(stream_query_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(query_smem<D>()));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(stream_merge_kernel<D, QJL>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(merge_smem<D>()));
         if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_decode_attn: shared memory %zu B: %s", smem, cudaGetErrorString(e));
         set[dev].store(true, std::memory_order_release);
     }
@@ -616,9 +665,9 @@ template <int D, bool QJL> static int launch(const DecodeParams& p, cudaStream_t
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const int64_t n_q = int64_t(p.B) * p.Hq;
-    cfg.gridDim = dim3(unsigned((n_q + 7) / 8));
-    cfg.blockDim = dim3(128);
-    cfg.dynamicSmemBytes = 0;
+    cfg.gridDim = dim3(unsigned((n_q + QPB - 1) / QPB));
+    cfg.blockDim = dim3(QNT);
+    cfg.dynamicSmemBytes = query_smem<D>();
     cudaError_t e = cudaLaunchKernelEx(&cfg, stream_query_kernel<D>, p);
     if (e == cudaSuccess) {
         cfg.gridDim = dim3(unsigned(p.st_grid));
@@ -627,9 +676,9 @@ template <int D, bool QJL> static int launch(const DecodeParams& p, cudaStream_t
         e = cudaLaunchKernelEx(&cfg, decode_stream_kernel<D, QJL>, p);
     }
     if (e == cudaSuccess) {
-        cfg.gridDim = dim3(unsigned(p.B * p.Hkv * p.HG));
-        cfg.blockDim = dim3(D);
-        cfg.dynamicSmemBytes = 0;
+        cfg.gridDim = dim3(unsigned((p.B * p.Hkv * p.HG + LPB - 1) / LPB));
+        cfg.blockDim = dim3(LPB * D);
+        cfg.dynamicSmemBytes = merge_smem<D>();
         e = cudaLaunchKernelEx(&cfg, stream_merge_kernel<D, QJL>, p);
     }
     if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_decode_attn: %s", cudaGetErrorString(e));
