@@ -339,9 +339,15 @@ def bench_c3(torch, dev, steps, warmup, peak):
     torch.cuda.synchronize(dev)
     us = e0.elapsed_time(e1) * 1e3 / (steps * len(caches))
     gbs = bytes_step / (us * 1e-6) / 1e9
+    import ctypes as C
+    from mlx_turboquant_b200 import _lib
+    choice = _lib.lib().tq_decode_kernel_choice(C.byref(caches[0]._dargs))
+    names = {0: "decode_attn_kernel<96, qjl> (general kernel: unpack to shared memory, ldmatrix)",
+             2: "decode_stream_kernel<96, qjl> (persistent grid over the packed tiles of all lanes; stream_query_kernel before it, "
+                "stream_merge_kernel after it: three launches per layer-step)"}
     return {"workload": "phi35mini_layer_decode_attn_b16_ctx8192_k4v2_qjl_sink128_rw128", "us_per_layer_step": us,
             "algorithmic_bytes_per_launch": bytes_step, "hbm_gbs": gbs, "frac_of_peak": gbs / peak,
-            "kernel": "decode_attn_kernel<96, qjl> (general kernel: unpack to shared memory, ldmatrix)"}
+            "kernel": names.get(choice, str(choice))}
 
 
 def bench_prefill(torch, dev, steps, warmup):

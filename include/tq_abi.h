@@ -312,7 +312,9 @@ float tq_fp16_table_scale(const float* centroids_host, int n);
  *   "decode_pdl" 0/1 (programmatic dependent launch: a call's prologue overlaps the previous kernel's tail),
  *   "gather_wait_polls" 1000..4000000 (polls of one word of a gather before the wait gives up; default 2000000, some two seconds),
  *   "decode_stream" 0/1 (the persistent streaming kernel for 4-bit keys / 2-bit values at d = 96 / 128 may be chosen, default, or never),
- *   "decode_stream_min_run" 1.. (fewest packed 16-token tiles per warp of the persistent grid for which it is chosen; default 24).
+ *   "decode_stream_min_run" 1.. (fewest packed 16-token tiles per warp of the persistent grid for which it is chosen over the
+ *   table-lookup kernel, default 24; over the general kernel a third of that),
+ *   "decode_stream_max_parts" 1..64 (most partial results per lane with which it is chosen over the table-lookup kernel; default 40).
  * Changing them changes tq_decode_workspace_bytes for the same sizes. */
 int tq_set_tuning(const char* key, int value);
 

@@ -594,7 +594,8 @@ extern int g_tune_dequantize_tc;       // rowops.cu: 0 = dequantize always on th
 extern int g_tune_prefill_tc;          // prefill.cu: 0 = several-query-token attention always on the mma.sync kernel
 static int g_tune_pdl = 1;             // programmatic dependent launch between consecutive calls
 static int g_tune_stream = 1;          // 0: never take the streaming kernel
-static int g_tune_stream_min_run = 24; // fewest packed tiles per warp for which the streaming kernel is chosen
+static int g_tune_stream_min_run = 24; // fewest packed tiles per warp for which the streaming kernel is chosen over the table-lookup kernel (a third of it over the general kernel)
+static int g_tune_stream_max_parts = 40;  // most partials per lane with which it is chosen over the table-lookup kernel (64 over the general kernel)
 
 static int sm_count() {
     static int n = 0;
@@ -753,7 +754,11 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
     StreamPlan stp{};
     if (stream) {
         stp = stream_plan(a->batch, a->n_q_heads, a->n_kv_heads, d, a->c_len, dense_len, sm_count());
-        stream = stp.range >= g_tune_stream_min_run && stp.npp + stp.nd <= 64 && stream_supported(d, qjl);
+        // against the table-lookup kernel it pays once runs are long and the merge has few partials per lane; against the
+        // general kernel (sign sketches, d = 96) almost always
+        const int min_run = direct ? g_tune_stream_min_run : std::max(1, g_tune_stream_min_run / 3);
+        const int max_parts = direct ? std::min(g_tune_stream_max_parts, 64) : 64;
+        stream = stp.range >= min_run && stp.npp + stp.nd <= max_parts && stream_supported(d, qjl);
     }
     const SplitPlan sp = plan_splits(a->batch, a->n_q_heads, a->n_kv_heads, a->c_len, dense_len, sm_count(), direct);
     const WsLayout wl = ws_layout(a->batch, a->n_q_heads, a->n_kv_heads, d, sp);
@@ -846,6 +851,7 @@ extern "C" int tq_set_tuning(const char* key, int value) {
     else if (k == "decode_pdl" && (value == 0 || value == 1)) g_tune_pdl = value;
     else if (k == "decode_stream" && (value == 0 || value == 1)) g_tune_stream = value;
     else if (k == "decode_stream_min_run" && value >= 1 && value <= (1 << 20)) g_tune_stream_min_run = value;
+    else if (k == "decode_stream_max_parts" && value >= 1 && value <= 64) g_tune_stream_max_parts = value;
     else if (k == "decode_splits" && value >= 0 && value <= MAX_SPLITS - 64) g_tune_splits = value;
     else if (k == "gather_wait_polls" && value >= 1000 && value <= 4000000) g_tune_wait_polls = value;
     else if (k == "prefill_tc" && (value == 0 || value == 1)) g_tune_prefill_tc = value;

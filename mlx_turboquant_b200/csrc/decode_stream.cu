@@ -26,6 +26,7 @@
 //
 // Every mbarrier wait is bounded; a wait that runs out records a status (tq_device_status), the warp drains the copies
 // it still has in flight (bounded again) and stops.
+#include <algorithm>
 #include <atomic>
 
 #include "decode_dev.cuh"
@@ -559,32 +560,34 @@ __global__ void __launch_bounds__(NT, 1) decode_stream_kernel(DecodeParams p) {
 }
 
 // ---- launch 3: merge --------------------------------------------------------------------------------------
-// A block takes LPB lanes (sequence, KV head, head group), D threads each (one per coordinate); R and S are staged in
-// shared memory once per block, so the rotation back costs shared-memory reads instead of a chain of L2 round trips.
-constexpr int LPB = 4;
-template <int D> __host__ __device__ constexpr size_t merge_smem() { return (size_t(D + QM) * D + size_t(LPB) * (2 * MAX_PARTS + D + QM)) * sizeof(float); }
+// A thread per (lane, query head, coordinate); a block takes as many lanes (sequence, KV head, head group) as fit some
+// 512 threads.  R and S are staged in shared memory once per block, so the rotation back costs shared-memory reads
+// instead of a chain of L2 round trips.
+constexpr int MERGE_SETS = 10;      // (lane, head) pairs per block at most: 1024 threads / 96
+template <int D> __host__ __device__ constexpr size_t merge_smem() { return (size_t(D + QM) * D + size_t(MERGE_SETS) * (2 * MAX_PARTS + D + QM)) * sizeof(float); }
+inline int merge_lanes_per_block(int slots, int d) { return std::max(1, 512 / (slots * d)); }
 template <int D, bool QJL>
-__global__ void __launch_bounds__(LPB * D) stream_merge_kernel(DecodeParams p) {
+__global__ void __launch_bounds__(1024) stream_merge_kernel(DecodeParams p, int lpb) {
     extern __shared__ __align__(16) unsigned char smem_m[];
     constexpr int PS = part_stride(D);
     float* rs = reinterpret_cast<float*>(smem_m);                 // [D][D] R, then [32][D] S
-    const int tid = threadIdx.x, sub = tid / D, c = tid - sub * D;
-    float* s_m = rs + (D + QM) * D + sub * (2 * MAX_PARTS + D + QM);
+    const int tid = threadIdx.x, set = tid / D, c = tid - set * D, sub = set / p.slots, h = set - sub * p.slots;
+    float* s_m = rs + (D + QM) * D + set * (2 * MAX_PARTS + D + QM);
     float* s_l = s_m + MAX_PARTS;
     float* s_rot = s_l + MAX_PARTS;
     float* s_z = s_rot + D;
     pdl_trigger();
     const int rows = D + (QJL ? QM : 0);
-    for (int i = tid; i < rows * (D / 4); i += LPB * D) {         // constants: before the wait
+    for (int i = tid; i < rows * (D / 4); i += blockDim.x) {      // constants: before the wait
         const int r = i / (D / 4), k4 = i - r * (D / 4);
         *reinterpret_cast<float4*>(rs + r * D + 4 * k4) = __ldg(reinterpret_cast<const float4*>(r < D ? p.rot + int64_t(r) * D : p.qjl_proj + int64_t(r - D) * D) + k4);
     }
     pdl_wait();
     const int L = p.B * p.Hkv * p.HG;
-    const int a = min(blockIdx.x * LPB + sub, L - 1);
-    const bool live = blockIdx.x * LPB + sub < L;
+    const int a = min(blockIdx.x * lpb + sub, L - 1);
     const int kvl = a / p.HG, hg = a - kvl * p.HG, b = kvl / p.Hkv, hkv = kvl - b * p.Hkv;
     const int heads_here = min(HPG, p.G - hg * HPG);
+    const bool live = blockIdx.x * lpb + sub < L && h < heads_here;
     const int64_t qhead0 = int64_t(b) * p.Hq + int64_t(hkv) * p.G + hg * HPG;
     const int n_tiles = int((p.c_len + TILE - 1) / TILE);
     const int n_slots = p.st_npp + p.st_nd;
@@ -592,46 +595,42 @@ __global__ void __launch_bounds__(LPB * D) stream_merge_kernel(DecodeParams p) {
     const int fw = int((int64_t(a) * n_tiles) / p.st_range), lw = int((int64_t(a + 1) * n_tiles - 1) / p.st_range);
     const int n_pp = n_tiles > 0 ? lw - fw + 1 : 0;
     const float inv_vs = 1.f / p.v_scale_hi;
-    const float* base = p.st_part + int64_t(a) * n_slots * p.slots * PS;
+    const float* ph = p.st_part + (int64_t(a) * n_slots * p.slots + h) * PS;
     const int64_t sstride = int64_t(p.slots) * PS;
-    for (int h = 0; h < p.slots; ++h) {
-        const float* ph = base + h * PS;
-        if (c < n_slots) {
-            const bool valid = h < heads_here && (c < n_pp || c >= p.st_npp);
-            s_m[c] = valid ? __ldcg(ph + c * sstride + D + QM) : -INFINITY;
-            s_l[c] = valid ? __ldcg(ph + c * sstride + D + QM + 1) : 0.f;
-        }
-        __syncthreads();
-        float M = -INFINITY;
-        for (int i = 0; i < n_slots; ++i) M = fmaxf(M, s_m[i]);
-        float Lsum = 0.f, ar = 0.f, ad = 0.f, az = 0.f;
-#pragma unroll 4
-        for (int i = 0; i < n_slots; ++i) {
-            const float mi = s_m[i];
-            const float w = mi == -INFINITY ? 0.f : ex2(mi - M);
-            const float v = mi == -INFINITY ? 0.f : __ldcg(ph + i * sstride + c);
-            Lsum = fmaf(w, s_l[i], Lsum);
-            if (i < p.st_npp) {
-                ar = fmaf(w, v, ar);
-                if (QJL && c < QM && mi != -INFINITY) az = fmaf(w, __ldcg(ph + i * sstride + D + c), az);
-            } else {
-                ad = fmaf(w, v, ad);
-            }
-        }
-        s_rot[c] = ar * inv_vs;
-        if (QJL && c < QM) s_z[c] = az * (QJL_C / D);
-        __syncthreads();
-        // undo the rotation of the packed part (y @ R, rotation.py:68-78) and add (c/d) z @ S (qjl.py:89-92)
-        float v = ad;
-#pragma unroll 8
-        for (int j = 0; j < D; ++j) v = fmaf(s_rot[j], rs[j * D + c], v);
-        if (QJL) {
-#pragma unroll 8
-            for (int i = 0; i < QM; ++i) v = fmaf(s_z[i], rs[(D + i) * D + c], v);
-        }
-        if (live && h < heads_here) store_from_f32(p.out, p.out_dtype, (qhead0 + h) * D + c, v / Lsum);
-        __syncthreads();
+    if (c < n_slots) {
+        const bool valid = h < heads_here && (c < n_pp || c >= p.st_npp);
+        s_m[c] = valid ? __ldcg(ph + c * sstride + D + QM) : -INFINITY;
+        s_l[c] = valid ? __ldcg(ph + c * sstride + D + QM + 1) : 0.f;
     }
+    __syncthreads();
+    float M = -INFINITY;
+    for (int i = 0; i < n_slots; ++i) M = fmaxf(M, s_m[i]);
+    float Lsum = 0.f, ar = 0.f, ad = 0.f, az = 0.f;
+#pragma unroll 8
+    for (int i = 0; i < n_slots; ++i) {
+        const float mi = s_m[i];
+        const float w = mi == -INFINITY ? 0.f : ex2(mi - M);
+        const float v = mi == -INFINITY ? 0.f : __ldcg(ph + i * sstride + c);
+        Lsum = fmaf(w, s_l[i], Lsum);
+        if (i < p.st_npp) {
+            ar = fmaf(w, v, ar);
+            if (QJL && c < QM && mi != -INFINITY) az = fmaf(w, __ldcg(ph + i * sstride + D + c), az);
+        } else {
+            ad = fmaf(w, v, ad);
+        }
+    }
+    s_rot[c] = ar * inv_vs;
+    if (QJL && c < QM) s_z[c] = az * (QJL_C / D);
+    __syncthreads();
+    // undo the rotation of the packed part (y @ R, rotation.py:68-78) and add (c/d) z @ S (qjl.py:89-92)
+    float v = ad;
+#pragma unroll 8
+    for (int j = 0; j < D; ++j) v = fmaf(s_rot[j], rs[j * D + c], v);
+    if (QJL) {
+#pragma unroll 8
+        for (int i = 0; i < QM; ++i) v = fmaf(s_z[i], rs[(D + i) * D + c], v);
+    }
+    if (live) store_from_f32(p.out, p.out_dtype, (qhead0 + h) * D + c, v / Lsum);
 }
 
 // ---- host side ------------------------------------------------------------------------------------------------
@@ -676,10 +675,11 @@ template <int D, bool QJL> static int launch(const DecodeParams& p, cudaStream_t
         e = cudaLaunchKernelEx(&cfg, decode_stream_kernel<D, QJL>, p);
     }
     if (e == cudaSuccess) {
-        cfg.gridDim = dim3(unsigned((p.B * p.Hkv * p.HG + LPB - 1) / LPB));
-        cfg.blockDim = dim3(LPB * D);
+        const int lpb = merge_lanes_per_block(p.slots, D);
+        cfg.gridDim = dim3(unsigned((p.B * p.Hkv * p.HG + lpb - 1) / lpb));
+        cfg.blockDim = dim3(unsigned(lpb * p.slots * D));
         cfg.dynamicSmemBytes = merge_smem<D>();
-        e = cudaLaunchKernelEx(&cfg, stream_merge_kernel<D, QJL>, p);
+        e = cudaLaunchKernelEx(&cfg, stream_merge_kernel<D, QJL>, p, lpb);
     }
     if (e != cudaSuccess) return fail(TQ_ERR_LAUNCH, "tq_decode_attn: %s", cudaGetErrorString(e));
     return TQ_OK;

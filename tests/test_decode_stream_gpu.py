@@ -21,8 +21,10 @@ pytestmark = pytest.mark.gpu
 def stream_forced():
     from mlx_turboquant_b200.kernels import set_tuning
     set_tuning("decode_stream_min_run", 1)
+    set_tuning("decode_stream_max_parts", 64)
     yield
     set_tuning("decode_stream_min_run", 24)
+    set_tuning("decode_stream_max_parts", 40)
 
 
 def _choice(c):
