@@ -197,10 +197,10 @@ __device__ __forceinline__ uint32_t nibble_mix(uint32_t a, uint32_t b, const Bit
 
 // Softmax step on scores that already carry the key norms (and the sketch term); tokens past the end of the cache come
 // in with score -inf and norm 0.  pr: the four weights times the value scale.
-template <int NZ>
-__device__ __forceinline__ void softmax_stream(float (&s)[4], float vn0, float vn1, float vx, WarpAcc<128, NZ>& st, uint32_t (&bp)[2], float (&pr)[4]) {
+template <int D, int NZ>
+__device__ __forceinline__ void softmax_stream(float (&s)[4], float vn0, float vn1, float vx, WarpAcc<D, NZ>& st, uint32_t (&bp)[2], float (&pr)[4]) {
     const float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]), vmax = fmaxf(fmaxf(vn0, vn1), vx);
-    if (__any_sync(0xffffffffu, mx0 > st.mt[0] || mx1 > st.mt[1] || vmax > st.vt)) softmax_refresh<128, NZ>(mx0, mx1, vmax, st);
+    if (__any_sync(0xffffffffu, mx0 > st.mt[0] || mx1 > st.mt[1] || vmax > st.vt)) softmax_refresh<D, NZ>(mx0, mx1, vmax, st);
     const float p0 = ex2(s[0] - st.m[0]), p1 = ex2(s[1] - st.m[1]), p2 = ex2(s[2] - st.m[0]), p3 = ex2(s[3] - st.m[1]);
     st.l[0] += p0 + p2;
     st.l[1] += p1 + p3;
@@ -216,7 +216,6 @@ __global__ void __launch_bounds__(NT, 1) decode_stream_kernel(DecodeParams p) {
     constexpr int NZ = QJL ? QM / 16 : 0, NS = P::NS;
     constexpr int QS = q_stride(D), PS = part_stride(D);
     constexpr int KW = D / 32;                 // 32-bit words of a quarter key row
-    constexpr int VG = D / 16;                 // row groups that own a value word
     extern __shared__ __align__(16) unsigned char smem[];
     const uint32_t sbase = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
@@ -370,7 +369,11 @@ __global__ void __launch_bounds__(NT, 1) decode_stream_kernel(DecodeParams p) {
         // per-lane offsets into a stage; everything else is an immediate
         const uint32_t k_off = uint32_t(tokA) * (D / 2) + (D == 128 ? 16u * t : 4u * t);
         const uint32_t a_off = 4u * tokA;                           // scalars of tokens tokA (and + 8: 32 bytes on)
-        const uint32_t v_off0 = uint32_t(tokV0) * (D / 4) + 4u * g, v_off1 = uint32_t(tokV1) * (D / 4) + 4u * g;   // (row groups without a word read their neighbours' bytes: padding rows)
+        // value codes of row group g: word g of the row at d = 128; bytes 3g .. 3g+2 of the 24-byte row at d = 96, read as the two
+        // aligned words around them and one byte-permute (v_sel)
+        const uint32_t v_grp = D == 128 ? 4u * g : (3u * g) & ~3u;
+        const uint32_t v_sel = 0x3210u + 0x1111u * ((3u * g) & 3u);
+        const uint32_t v_off0 = uint32_t(tokV0) * (D / 4) + v_grp, v_off1 = uint32_t(tokV1) * (D / 4) + v_grp;
         const uint32_t p_off = 4u * tokP, q_off = 4u * tokQ;
 
         BitConsts kc;
@@ -407,7 +410,7 @@ __global__ void __launch_bounds__(NT, 1) decode_stream_kernel(DecodeParams p) {
                     }
             }
         };
-        WarpAcc<128, NZ> st;       // eight value m-tiles whatever the head dim (see above)
+        WarpAcc<D, NZ> st;
         st.init();
         load_query();
         auto flush = [&]() {       // one partial: (lane a, slot)
@@ -422,13 +425,11 @@ __global__ void __launch_bounds__(NT, 1) decode_stream_kernel(DecodeParams p) {
                 const bool two = 2 * t + 1 < heads_here;
                 float* h0 = pp + (2 * t) * PS;
                 float* h1 = h0 + PS;
-                if (g < VG) {
 #pragma unroll
-                    for (int mt = 0; mt < 8; ++mt) {               // rows g, g + 8 of m-tile mt: coordinates 16g + 2mt, + 1
-                        const int c = 16 * g + 2 * mt;
-                        *reinterpret_cast<float2*>(h0 + c) = make_float2(st.o[mt][0], st.o[mt][2]);
-                        if (two) *reinterpret_cast<float2*>(h1 + c) = make_float2(st.o[mt][1], st.o[mt][3]);
-                    }
+                for (int mt = 0; mt < D / 16; ++mt) {              // rows g, g + 8 of m-tile mt: coordinates (D/8) g + 2mt, + 1
+                    const int c = (D / 8) * g + 2 * mt;
+                    *reinterpret_cast<float2*>(h0 + c) = make_float2(st.o[mt][0], st.o[mt][2]);
+                    if (two) *reinterpret_cast<float2*>(h1 + c) = make_float2(st.o[mt][1], st.o[mt][3]);
                 }
 #pragma unroll
                 for (int mz = 0; mz < NZ; ++mz) {
@@ -510,19 +511,27 @@ __global__ void __launch_bounds__(NT, 1) decode_stream_kernel(DecodeParams p) {
             }
             uint32_t bp[2];
             float pr[4];
-            softmax_stream<NZ>(s, vn0, vn1, fmaxf(gv0, gv1), st, bp, pr);
+            softmax_stream<D, NZ>(s, vn0, vn1, fmaxf(gv0, gv1), st, bp, pr);
 
             // ---- values: O^T[coordinate][head] += V^T . P^T ----
             {
-                const uint32_t va = ring32o<P::O_V>(sa + v_off0), vb = ring32o<P::O_V>(sa + v_off1);
-                const uint32_t vc = ring32o<P::O_V + 8 * (D / 4)>(sa + v_off0), vd = ring32o<P::O_V + 8 * (D / 4)>(sa + v_off1);
+                uint32_t va, vb, vc, vd;
+                if constexpr (D == 128) {
+                    va = ring32o<P::O_V>(sa + v_off0); vb = ring32o<P::O_V>(sa + v_off1);
+                    vc = ring32o<P::O_V + 8 * (D / 4)>(sa + v_off0); vd = ring32o<P::O_V + 8 * (D / 4)>(sa + v_off1);
+                } else {
+                    va = __byte_perm(ring32o<P::O_V>(sa + v_off0), ring32o<P::O_V + 4>(sa + v_off0), v_sel);
+                    vb = __byte_perm(ring32o<P::O_V>(sa + v_off1), ring32o<P::O_V + 4>(sa + v_off1), v_sel);
+                    vc = __byte_perm(ring32o<P::O_V + 8 * (D / 4)>(sa + v_off0), ring32o<P::O_V + 8 * (D / 4) + 4>(sa + v_off0), v_sel);
+                    vd = __byte_perm(ring32o<P::O_V + 8 * (D / 4)>(sa + v_off1), ring32o<P::O_V + 8 * (D / 4) + 4>(sa + v_off1), v_sel);
+                }
                 // pair the nibbles (two adjacent coordinates) of the two tokens: byte j of z0 = (first word, nibble 2j) |
                 // (second word, nibble 2j) << 4, z1 the odd nibbles; one 64-bit lookup yields the two operand registers of
                 // rows g and g + 8 (the two coordinates, the token pair in each)
                 const uint32_t z0 = nibble_mix(va, vb << 4, kc), z1 = nibble_mix(va >> 4, vb, kc);
                 const uint32_t w0 = nibble_mix(vc, vd << 4, kc), w1 = nibble_mix(vc >> 4, vd, kc);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
+                for (int k = 0; k < D / 32; ++k) {
                     const uint2 e01 = lut64(__byte_perm(z0, c2, 0x7604 | (k << 4)));   // m-tile 2k:   k slots 2t, 2t+1
                     const uint2 e23 = lut64(__byte_perm(w0, c2, 0x7604 | (k << 4)));   //             k slots 2t+8, 2t+9
                     const uint2 f01 = lut64(__byte_perm(z1, c2, 0x7604 | (k << 4)));   // m-tile 2k+1
