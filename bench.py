@@ -849,7 +849,12 @@ def main():
     ap.add_argument("--c4-prefill", default="model", choices=("model", "synthetic"), help="c4: prefill the prompt through the model, "
                     "or fill the caches with synthetic K/V")
     ap.add_argument("--c4-prefill-chunk", type=int, default=512, help="c4: prompt tokens per prefill call")
+    ap.add_argument("--no-stream", action="store_true", help="never take the persistent streaming decode kernel (profiling the other two kernels "
+                    "on the shapes it would take)")
     args = ap.parse_args()
+    if args.no_stream and args.impl != "reference":
+        from mlx_turboquant_b200.kernels import set_tuning
+        set_tuning("decode_stream", 0)
     if args.impl == "reference":
         run_reference(args)
     elif args.workload == "c4":

@@ -3,7 +3,8 @@
 //
 // This file: the host side (argument checks, split plan, workspace layout, launch) and the GENERAL kernel, which
 // handles every bit width (1-4, fractional splits) and d in {64, 96, 128, 256}.  4-bit keys with 2-bit values at
-// d = 128 take the specialised kernel of decode_direct.cu instead.
+// d = 128 take the table-lookup kernel of decode_direct.cu instead, and the same widths at d = 96 / 128 (sign sketches
+// allowed) the persistent streaming kernel of decode_stream.cu once every warp of its grid gets a long run of tiles.
 //
 // decode_attn_kernel, grid (splits, kv_heads * head_groups, batch).  Every CTA
 //   1. rotates the query heads of its GQA group once (q @ R^T, float32), folds scale*log2(e) in and keeps

@@ -11,18 +11,23 @@
 //
 // Three launches, chained with programmatic dependent launch:
 //   1. stream_query_kernel   rotates every query head once (q R^T, and S q for the sketches) into the workspace as
-//                            scaled fp16 - 8 heads per block, so R is read B * Hq / 8 times instead of once per CTA;
+//                            scaled fp16 - 16 heads per block, R and S staged in shared memory;
 //   2. decode_stream_kernel  the persistent grid.  Raw packed tiles (keys, values, norms, sign words, residual norms:
-//                            2 to 8 arrays) reach a warp through its own ring of NS stages in shared memory, filled by
-//                            bulk copies that complete on the stage's mbarrier (whole sectors whatever the row length,
-//                            no registers held across the global-memory latency, NS - 1 tiles in flight per warp).
-//                            Operand fragments come from the byte tables of decode_direct.cu (one byte-permute forms
-//                            the address); value rows of 24 bytes (d = 96) are treated as 6 of 8 words, the two
-//                            word-less row groups of every m-tile computing padding.  The uncompressed tokens (sink,
-//                            recent window, the token a step appends) are dealt out too, a few tiles per warp, before
-//                            the packed runs start; their staging buffer is the warp's ring.
-//   3. stream_merge_kernel   one block per lane: log-sum-exp merge of the lane's partials, rotation of the packed part
-//                            back (y R, float32), sketch rows times S, normalisation, store.
+//                            4 to 8 arrays) reach a warp through its own ring of NS stages in shared memory: a stage is
+//                            the tile's arrays back to back, every lane copies three or four 16-byte chunks of it with
+//                            asynchronous copies and arrives on the stage's mbarrier when they have landed (whole
+//                            sectors whatever the row length, no registers held across the global-memory latency,
+//                            NS - 1 tiles in flight per warp).  Operand fragments come from the byte tables of
+//                            decode_direct.cu (one byte-permute forms the address); at d = 96 a row group owns three
+//                            bytes of the 24-byte value row, read as the two aligned words around them.  The
+//                            uncompressed tokens (sink, recent window, the token a step appends) are dealt out too, a
+//                            few tiles per warp, before the packed runs start; their staging buffer is the warp's ring.
+//   3. stream_merge_kernel   a thread per (lane, head, coordinate): log-sum-exp merge of the lane's partials, rotation of
+//                            the packed part back (y R, float32, R staged in shared memory), sketch rows times S,
+//                            normalisation, store.
+//
+// The loop is bound by the integer pipe (byte-permutes, logic ops and shifts that turn packed codes and sign bits into
+// operands): measured 375 warp-instructions per 16-token tile at d = 96 with sketches, 288 at d = 128 without.
 //
 // Every mbarrier wait is bounded; a wait that runs out records a status (tq_device_status), the warp drains the copies
 // it still has in flight (bounded again) and stops.
