@@ -601,6 +601,11 @@ def run_c4(args):
     attn_bytes = (b * HKV * c0._compressed_len * (D // 2 + 4 + D // 4 + 4) + b * HKV * (c0._sink_len + c0._fp16_len) * 2 * D * 2
                   + b * HQ * D * 4)
     attn_gbs = attn_bytes / (attn_us * 1e-6) / 1e9
+    import ctypes as C
+    from mlx_turboquant_b200 import _lib
+    choice = _lib.lib().tq_decode_kernel_choice(C.byref(c0._dargs))     # 2: streaming kernel = query + persistent grid + merge launches
+    launches_per_call = 3 if choice == 2 else 1
+    attn_kernel = {0: "decode_attn_kernel", 1: "decode_direct_kernel", 2: "stream_query_kernel + decode_stream_kernel + stream_merge_kernel"}.get(choice, str(choice))
     weight_bytes = sum(p.numel() * p.element_size() for p in model.parameters()) - model.embed_tokens.weight.numel() * 2
     floor_ms = (attn_bytes * args.layers + weight_bytes) / (peak * 1e9) * 1e3
     line = {
@@ -615,11 +620,11 @@ def run_c4(args):
                    "decode_step": "eager" if args.no_graph else "library part replayed from CUDA graphs, cache calls eager",
                    "l2_policy": "inputs larger than L2",
                    "sharding": "sequences dealt to the GPUs, full weights on each, no collective"},
-        "gpu_launches": args.layers * args.steps,
+        "gpu_launches": args.layers * args.steps * launches_per_call,
         "clocks": clk.summary(),
         "prefill": {"seconds": prefill_s, "tokens_per_s": args.c4_batch * prompt / prefill_s, "mode": args.c4_prefill},
         "attention": {"us_per_layer_step": attn_us, "algorithmic_bytes_per_launch": attn_bytes, "hbm_gbs": attn_gbs, "frac_of_peak": attn_gbs / peak,
-                      "peak": peak, "peak_source": peak_src, "share_of_step": attn_us * args.layers / (ms_step * 1e3)},
+                      "peak": peak, "peak_source": peak_src, "share_of_step": attn_us * args.layers / (ms_step * 1e3), "kernel": attn_kernel},
         "hbm_floor_ms_per_step": floor_ms, "step_over_floor": ms_step / floor_ms,
         "weight_read_floor_ms_per_step": weight_bytes / (peak * 1e9) * 1e3,
         "cache_bytes_per_gpu": sum(c.nbytes for c in caches), "weight_bytes_read_per_step": weight_bytes,
