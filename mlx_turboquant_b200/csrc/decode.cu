@@ -764,8 +764,7 @@ int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_by
     const SplitPlan sp = plan_splits(a->batch, a->n_q_heads, a->n_kv_heads, a->c_len, dense_len, sm_count(), direct);
     const WsLayout wl = ws_layout(a->batch, a->n_q_heads, a->n_kv_heads, d, sp);
     const size_t st_base = align_up(std::max(size_t(a->batch) * a->n_kv_heads * sp.hg * sizeof(int), COUNTER_AREA), 256);
-    if (stream && st_base + stp.q16_bytes + stp.part_bytes > workspace_bytes)
-        return fail(TQ_ERR_INVALID, "tq_decode_attn: workspace %zu B < %zu B", workspace_bytes, st_base + stp.q16_bytes + stp.part_bytes);
+    if (stream && st_base + stp.q16_bytes + stp.part_bytes > workspace_bytes) stream = false;   // (a workspace sized for the other kernels only)
     if (!stream && wl.total > workspace_bytes) return fail(TQ_ERR_INVALID, "tq_decode_attn: workspace %zu B < %zu B", workspace_bytes, wl.total);
     if (sp.n_ps + sp.n_ds > MAX_SPLITS) return fail(TQ_ERR_UNSUPPORTED, "tq_decode_attn: too many splits");
 
@@ -957,12 +956,20 @@ extern "C" int tq_decode_tables_build(int d, const float* rot, const float* k_ce
     return direct_tables_build(d, rot, k_cent, v_cent, v_cent_scale, tables, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" size_t tq_decode_workspace_bytes(int batch, int n_q_heads, int n_kv_heads, int d, int64_t c_len,
-                                            int64_t dense_len) {
+namespace tq {
+size_t decode_workspace_bytes_split_kernels(int batch, int n_q_heads, int n_kv_heads, int d, int64_t c_len, int64_t dense_len) {
     if (batch <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || d <= 0 || n_q_heads % n_kv_heads || c_len < 0 || dense_len < 0) return 0;
     // The larger of the two split plans tq_decode_attn can choose for these sizes (current tuning values).
     const size_t a = ws_layout(batch, n_q_heads, n_kv_heads, d, plan_splits(batch, n_q_heads, n_kv_heads, c_len, dense_len, sm_count(), false)).total;
     const size_t b = ws_layout(batch, n_q_heads, n_kv_heads, d, plan_splits(batch, n_q_heads, n_kv_heads, c_len, dense_len, sm_count(), true)).total;
+    return std::max(a, b);
+}
+}  // namespace tq
+
+extern "C" size_t tq_decode_workspace_bytes(int batch, int n_q_heads, int n_kv_heads, int d, int64_t c_len,
+                                            int64_t dense_len) {
+    const size_t a = decode_workspace_bytes_split_kernels(batch, n_q_heads, n_kv_heads, d, c_len, dense_len), b = 0;
+    if (a == 0) return 0;
     size_t c = 0;
     if ((d == 96 || d == 128) && c_len > 0) {      // the streaming kernel's layout: counters' area, prepared queries, partials
         const StreamPlan sp = stream_plan(batch, n_q_heads, n_kv_heads, d, c_len, dense_len, sm_count());

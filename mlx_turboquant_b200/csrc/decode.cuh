@@ -82,6 +82,9 @@ unsigned probe_smem_base();                                    // shared-window 
 int decode_prepare(const tq_decode_args* a, void* workspace, size_t workspace_bytes, DecodeParams* out, bool* direct_out,
                    const void* k_new = nullptr, const void* v_new = nullptr);
 int decode_launch(const DecodeParams& p, bool direct, cudaStream_t s);
+// Scratch the general and the table-lookup kernel need for these sizes (the streaming kernel may need more; a call whose
+// workspace is too small for it takes one of the other two).
+size_t decode_workspace_bytes_split_kernels(int batch, int n_q_heads, int n_kv_heads, int d, int64_t c_len, int64_t dense_len);
 
 // decode_direct.cu: the kernel for 4-bit keys / 2-bit values at d = 128.  direct_supported() checks once per
 // device (one tiny synchronous probe launch on first use) that the kernel's shared-memory plan fits the device.

@@ -56,7 +56,8 @@ using namespace tq;
 
 extern "C" int tq_decode_attn_static(const tq_decode_args* a, void* stream) {
     if (!a) return fail(TQ_ERR_INVALID, "tq_decode_attn_static: null args");
-    const size_t need = tq_decode_workspace_bytes(a->batch, a->n_q_heads, a->n_kv_heads, a->d, a->c_len, a->sink_len + a->res_len);
+    // (the persistent streaming kernel is taken only where its larger scratch fits the array too)
+    const size_t need = decode_workspace_bytes_split_kernels(a->batch, a->n_q_heads, a->n_kv_heads, a->d, a->c_len, a->sink_len + a->res_len);
     if (need == 0) return fail(TQ_ERR_INVALID, "tq_decode_attn_static: bad sizes");
     if (need > size_t(TQ_DECODE_STATIC_SCRATCH_BYTES))
         return fail(TQ_ERR_UNSUPPORTED, "tq_decode_attn_static: these sizes need %zu bytes of scratch, the built-in array holds %zu; "

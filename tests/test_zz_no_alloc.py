@@ -91,3 +91,29 @@ def test_static_scratch_refuses_sizes_beyond_its_array():
     assert lib.tq_decode_attn_static(C.byref(a), None) == -2
     assert b"built-in array" in lib.tq_last_error()
     assert lib.tq_decode_attn_static(None, None) == -1
+
+
+def test_static_scratch_keeps_its_shapes_where_the_streaming_kernel_would_need_more():
+    """Many lanes of a short context: tq_decode_attn takes the persistent streaming kernel, whose partials (one per lane
+    and warp that touches it) need more scratch than the built-in array has; the static entry point runs the
+    table-lookup kernel on the same arguments instead of refusing them."""
+    from mlx_turboquant_b200 import _lib
+    lib = _lib.lib()
+    rs = np.random.RandomState(99)
+    b, hq, hkv, t, d = 64, 32, 8, 2000, 128
+    cache, q = _cache(rs, b, hq, hkv, t, d, 4, 2)
+    dense_len = cache._sink_len + cache._fp16_len
+    need = lib.tq_decode_workspace_bytes(b, hq, hkv, d, cache._compressed_len, dense_len)
+    assert need > 8 << 20
+    ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    ref = torch.empty(b, hq, d, dtype=torch.float32, device="cuda")
+    a = _args_for(cache, q, ref, ws)
+    assert lib.tq_decode_kernel_choice(C.byref(a)) == 2
+    _lib.check(lib.tq_decode_attn(C.byref(a), stream))
+    out = torch.full((b, hq, d), float("nan"), dtype=torch.float32, device="cuda")
+    _lib.check(lib.tq_decode_attn_static(C.byref(_args_for(cache, q, out, None)), stream))
+    torch.cuda.synchronize()
+    assert torch.isfinite(out).all()
+    assert (out - ref).abs().max().item() / ref.abs().max().item() < 2e-3        # two kernels, one answer
+    assert lib.tq_device_status() == 0
