@@ -63,12 +63,14 @@ constexpr int OFF_R3 = OFF_A + 2 * OPER_BYTES;             // bf16: third term o
 constexpr int OFF_R1 = OFF_A + 3 * OPER_BYTES;             // R_hi / R_1
 constexpr int OFF_R2 = OFF_R1 + OPER_BYTES;                // R_lo / R_2
 constexpr int OFF_BINS = OFF_R2 + OPER_BYTES;              // NBINS x BIN_REP x 8 B: the table of the 4-bit codebook (only bits_hi can be 4)
-constexpr int OFF_PT = OFF_BINS + NBINS * BIN_REP * 8;     // QJL: (S R^T)^T, [d][32] floats
+constexpr int OFF_PT = OFF_BINS + NBINS * BIN_REP * 8;     // QJL: (S R^T) as fp16 high / low parts in mma B-fragment order: [d / 16][4 n-tiles][hi | lo][32 lanes] x 8 bytes
 constexpr int OFF_BND = OFF_PT + DMAX * QM * 4;            // 2 x 16 floats raw boundaries, 2 x 16 floats centroids
 constexpr int OFF_NSQ = OFF_BND + 256;                     // A_STAGES_MAX x 2 x 128 floats: partial sums of squares
 constexpr int OFF_BAR = OFF_NSQ + A_STAGES_MAX * 2 * TM * 4;   // mbarriers: 3 full, 3 a_free, 3 norm-ready, 4 acc_full, 4 acc_free
 constexpr int OFF_MISC = OFF_BAR + 24 * 8;                 // tmem base, abort flag
-constexpr int SMEM_BYTES = OFF_MISC + 64;
+constexpr int SK_LD = 48;                                  // QJL: bytes per staged row of 16 fp16 residuals (32 + padding: the eight rows of an 8 x 8 matrix land in distinct banks)
+constexpr int OFF_SKETCH = (OFF_MISC + 64 + 127) / 128 * 128;   // QJL: one 32-row staging buffer per epilogue warp
+constexpr int SMEM_BYTES = OFF_SKETCH + 8 * 32 * SK_LD;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared-memory plan");
 
 struct Params {
@@ -305,24 +307,99 @@ struct EpiCtx {
     volatile int* abort_flag; int warp, lane;
 };
 
-// QJL: residual of sixteen coordinates (normalised rotated value minus its centroid) into the 32 projections and the
-// residual's sum of squares.  PT: [d][32] floats, read as warp-wide broadcasts.
+// QJL: the residual of sixteen coordinates (normalised rotated value minus its centroid) enters the 32 projections and
+// the residual's sum of squares.  A thread owns a row, a warp 32 rows: the projections of the warp's rows are a
+// 32 x 16 by 16 x 32 product per call, done with mma.sync (a CUDA-core version cost 32 multiply-adds and 8 shared-memory
+// reads per coordinate and thread: two thirds of the kernel's instructions).  Only the SIGN of a projection is kept, so
+// the residual is scaled by 2^8 (clear of fp16 subnormals) and split into fp16 high and low parts, as is S R^T:
+// acc += hi x hi + lo x hi + hi x lo reproduces the float32 product to about 2^-21.  The operands go through a
+// 32-row staging buffer of the warp (row = lane) and come back as fragments with ldmatrix.
+struct Sketch {
+    float acc[2][4][4];        // [16-row half of the warp][8 projections][mma accumulator]: rows g / g + 8, projections 2t, 2t + 1
+    uint32_t stage;            // shared-window address of the warp's staging buffer
+    const uint2* bfrag;        // B fragments of S R^T (OFF_PT)
+    int lane;
+};
+__device__ __forceinline__ void sk_mma(float (&c)[4], const uint32_t (&a)[4], uint2 b) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b.x), "r"(b.y));
+}
+__device__ __forceinline__ void sk_ldsm(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void sk_sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 template <int BITS>
-__device__ __forceinline__ void sketch16(const uint32_t* v, uint32_t g0, uint32_t g1, float rinv, const float* cent, const float* PT, int col0,
-                                         float (&proj)[QM], float& ee) {
+__device__ __forceinline__ void sketch16(const uint32_t* v, uint32_t g0, uint32_t g1, float rinv, const float* cent, int col0, Sketch& sk, float& ee) {
+    uint32_t hi[8], lo[8];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const uint32_t code = ((i < 8 ? g0 : g1) >> (BITS * (i & 7))) & ((1u << BITS) - 1u);
-        const float e = fmaf(__uint_as_float(v[i]), rinv, -cent[code]);
-        ee = fmaf(e, e, ee);
-        const float4* row = reinterpret_cast<const float4*>(PT + (col0 + i) * QM);
+    for (int i = 0; i < 16; i += 2) {
+        float e2[2];
 #pragma unroll
-        for (int q = 0; q < QM / 4; ++q) {
-            const float4 s = row[q];
-            proj[4 * q] = fmaf(e, s.x, proj[4 * q]); proj[4 * q + 1] = fmaf(e, s.y, proj[4 * q + 1]);
-            proj[4 * q + 2] = fmaf(e, s.z, proj[4 * q + 2]); proj[4 * q + 3] = fmaf(e, s.w, proj[4 * q + 3]);
+        for (int u = 0; u < 2; ++u) {
+            const uint32_t code = (((i + u) < 8 ? g0 : g1) >> (BITS * ((i + u) & 7))) & ((1u << BITS) - 1u);
+            const float e = fmaf(__uint_as_float(v[i + u]), rinv, -cent[code]);
+            ee = fmaf(e, e, ee);
+            e2[u] = e * 256.f;
+        }
+        const __half2 h = __floats2half2_rn(e2[0], e2[1]);
+        const float2 hf = __half22float2(h);
+        const __half2 l = __floats2half2_rn(e2[0] - hf.x, e2[1] - hf.y);
+        hi[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+        lo[i >> 1] = *reinterpret_cast<const uint32_t*>(&l);
+    }
+    const uint32_t row = sk.stage + uint32_t(sk.lane) * SK_LD;
+    const uint32_t frag = sk.stage + uint32_t(sk.lane & 15) * SK_LD + uint32_t(sk.lane >> 4) * 16;     // ldmatrix row of this lane (second half: + 16 rows)
+    uint32_t ah[2][4], al[2][4];
+    sk_sts128(row, hi[0], hi[1], hi[2], hi[3]);
+    sk_sts128(row + 16, hi[4], hi[5], hi[6], hi[7]);
+    __syncwarp();
+    sk_ldsm(ah[0], frag);
+    sk_ldsm(ah[1], frag + 16 * SK_LD);
+    __syncwarp();
+    sk_sts128(row, lo[0], lo[1], lo[2], lo[3]);
+    sk_sts128(row + 16, lo[4], lo[5], lo[6], lo[7]);
+    __syncwarp();
+    sk_ldsm(al[0], frag);
+    sk_ldsm(al[1], frag + 16 * SK_LD);
+    __syncwarp();
+    const uint2* bf = sk.bfrag + (col0 >> 4) * (4 * 2 * 32) + sk.lane;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+        const uint2 bh = bf[(nt * 2 + 0) * 32], bl = bf[(nt * 2 + 1) * 32];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+            sk_mma(sk.acc[mt][nt], ah[mt], bh);
+            sk_mma(sk.acc[mt][nt], al[mt], bh);
+            sk_mma(sk.acc[mt][nt], ah[mt], bl);
         }
     }
+}
+// The sign word of this thread's row (row = lane) from the warp's accumulators: bit p set iff projection p >= 0.
+__device__ __forceinline__ uint32_t sketch_bits(const Sketch& sk) {
+    const int g = sk.lane >> 2, t = sk.lane & 3;
+    uint32_t w[4];                                         // rows g, g + 8, 16 + g, 24 + g: this lane's two bits per n-tile
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t x = 0;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+                x |= ((sk.acc[mt][nt][2 * h] >= 0.f ? 1u : 0u) | (sk.acc[mt][nt][2 * h + 1] >= 0.f ? 2u : 0u)) << (8 * nt + 2 * t);
+            x |= __shfl_xor_sync(0xffffffffu, x, 1);
+            x |= __shfl_xor_sync(0xffffffffu, x, 2);
+            w[mt * 2 + h] = x;
+        }
+    // row r = lane is held by the lanes of group g = r & 7 as word (r >> 3)
+    const int src = (sk.lane & 7) * 4;
+    const uint32_t w0 = __shfl_sync(0xffffffffu, w[0], src), w1 = __shfl_sync(0xffffffffu, w[1], src);
+    const uint32_t w2 = __shfl_sync(0xffffffffu, w[2], src), w3 = __shfl_sync(0xffffffffu, w[3], src);
+    const int k = sk.lane >> 3;
+    (void)g;
+    return k == 0 ? w0 : k == 1 ? w1 : k == 2 ? w2 : w3;
 }
 
 // A run of a row's coordinates ([col0, col0 + 16 * nch) at BITS bits) in rolled steps of 32 coordinates; the step's codes
@@ -332,7 +409,7 @@ __device__ __forceinline__ void sketch16(const uint32_t* v, uint32_t g0, uint32_
 // NCH: the number of chunks when it is known at compile time (1 or 2: a single step whose shape folds), 0 = nch_rt.
 template <int BITS, bool QJL, bool SPLITACC, int NCH>
 __device__ __forceinline__ void quantize_part(uint32_t t_row, int col0, int nch_rt, int lo_off, const RowCtx& rc, const float (&sb)[7], const float* raw,
-                                              const float* cent, const float* PT, uint8_t* dst, bool live, float (&proj)[QM], float& ee) {
+                                              const float* cent, uint8_t* dst, bool live, Sketch& sk, float& ee) {
     constexpr int NW = 2 * 16 * BITS / 32;                                          // words of a step: BITS
     const int nch = NCH ? NCH : nch_rt;
 #pragma unroll 1
@@ -366,7 +443,7 @@ __device__ __forceinline__ void quantize_part(uint32_t t_row, int col0, int nch_
                 quantize16<BITS>(vc, rc, sb, raw, g0, g1);
                 put_group<BITS, NW>(w, 2 * c, g0);
                 put_group<BITS, NW>(w, 2 * c + 1, g1);
-                if constexpr (QJL) sketch16<BITS>(vc, g0, g1, rc.rinv, cent, PT, col0 + (c0 + c) * 16, proj, ee);
+                if constexpr (QJL) sketch16<BITS>(vc, g0, g1, rc.rinv, cent, col0 + (c0 + c) * 16, sk, ee);
             }
         }
         if (live) store_words<NW>(dst + c0 * 2 * BITS, w, nc * 2 * BITS);
@@ -407,7 +484,10 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
     const float* raw_l = raw_h + 16;
     const float* cent_h = raw_h + 32;
     const float* cent_l = raw_h + 48;
-    const float* PT = reinterpret_cast<const float*>(e.smem + OFF_PT);
+    Sketch sk;
+    sk.stage = static_cast<uint32_t>(__cvta_generic_to_shared(e.smem + OFF_SKETCH)) + uint32_t(e.warp) * 32 * SK_LD;
+    sk.bfrag = reinterpret_cast<const uint2*>(e.smem + OFF_PT);
+    sk.lane = e.lane;
     RowCtx rc;
     rc.bins = reinterpret_cast<const float2*>(e.smem + OFF_BINS) + (e.lane & (BIN_REP - 1));      // 4-bit side only
     float bnd_h[7], bnd_l[7];
@@ -443,23 +523,22 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
         lane_o += step_o; tl += step_t;
         if (tl >= tpl) { tl -= tpl; ++lane_o; }
         const uint32_t t_row = e.tmem_base + (uint32_t(quad * 32) << 16) + a * Sh::STAGE_COLS;
-        float proj[QM], ee = 0.f;
+        float ee = 0.f;
         if (QJL) {
 #pragma unroll
-            for (int q = 0; q < QM; ++q) proj[q] = 0.f;
+            for (int i = 0; i < 32; ++i) (&sk.acc[0][0][0])[i] = 0.f;
         }
         // with head_dim 128 and quarter shares every thread has two chunks of an integer width, or one of each fractional width
         constexpr int NCH_H = (DC == 128 && Sh::SPLIT == 4) ? (BL ? 1 : 2) : 0, NCH_L = (DC == 128 && Sh::SPLIT == 4) ? 1 : 0;
-        quantize_part<BH, QJL, SPLITACC, NCH_H>(t_row, h0 * 16, h1 - h0, d, rc, sb_h, raw_h, cent_h, PT, p.p_hi + orow * nb_h + h0 * 2 * BH, live, proj, ee);
-        if (BL) quantize_part<(BL ? BL : 1), QJL, SPLITACC, NCH_L>(t_row, half + l0 * 16, l1 - l0, d, rc, sb_l, raw_l, cent_l, PT, p.p_lo + orow * nb_l + l0 * 2 * BL, live, proj, ee);
+        quantize_part<BH, QJL, SPLITACC, NCH_H>(t_row, h0 * 16, h1 - h0, d, rc, sb_h, raw_h, cent_h, p.p_hi + orow * nb_h + h0 * 2 * BH, live, sk, ee);
+        if (BL) quantize_part<(BL ? BL : 1), QJL, SPLITACC, NCH_L>(t_row, half + l0 * 16, l1 - l0, d, rc, sb_l, raw_l, cent_l, p.p_lo + orow * nb_l + l0 * 2 * BL, live, sk, ee);
         tc_fence_before();
         mbar_arrive(e.bar_accfree + 8 * a);                     // the accumulator may be overwritten
+        uint32_t zb = 0;
+        if (QJL) zb = sketch_bits(sk);                          // (every lane of the warp takes part)
         if (live && part == 0) {
             p.norms[orow] = nrm;
             if (QJL) {
-                uint32_t zb = 0;
-#pragma unroll
-                for (int q = 0; q < QM; ++q) zb |= (proj[q] >= 0.f ? 1u : 0u) << q;
                 if (nrm == 0.f) zb = 0xffffffffu;               // zero row: the reference's residual is exactly 0, and 0 >= 0
                 p.qjl_bits[orow] = zb;
                 p.qjl_gamma[orow] = nrm * sqrtf(ee);            // |x - dequant(x)| = |x| |y_n - c| (the rotation is orthogonal)
@@ -560,11 +639,24 @@ __global__ void __launch_bounds__(n_threads(QJL), 1) quantize_tc_kernel(Params p
             raw[tid] = val;
         }
         if (QJL) {
-            // (S R^T) is (32, d): transposed so that one coordinate's 32 factors are 128 contiguous bytes
-            float* PT = reinterpret_cast<float*>(smem + OFF_PT);
-            for (int idx = tid; idx < QM * d; idx += NT) {
-                const int q = idx / d, j = idx - q * d;
-                PT[j * QM + q] = __ldg(p.qjl_proj_rot + idx);
+            // (S R^T) is (32, d): as mma B fragments (k = coordinate, n = projection), fp16 high and low parts;
+            // lane (g, t) of fragment (k-step ks, n-tile nt): b0 = coordinates 16 ks + 2t, + 1 of projection 8 nt + g, b1 = the same + 8
+            uint2* bf = reinterpret_cast<uint2*>(smem + OFF_PT);
+            for (int idx = tid; idx < (d / 16) * 4 * 32; idx += NT) {
+                const int ks = idx >> 7, nt = (idx >> 5) & 3, ln = idx & 31, g = ln >> 2, t = ln & 3;
+                const float* srow = p.qjl_proj_rot + (8 * nt + g) * d + 16 * ks + 2 * t;
+                uint32_t hw[2], lw[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const float x0 = __ldg(srow + 8 * u), x1 = __ldg(srow + 8 * u + 1);
+                    const __half2 h = __floats2half2_rn(x0, x1);
+                    const float2 hf = __half22float2(h);
+                    const __half2 l = __floats2half2_rn(x0 - hf.x, x1 - hf.y);
+                    hw[u] = *reinterpret_cast<const uint32_t*>(&h);
+                    lw[u] = *reinterpret_cast<const uint32_t*>(&l);
+                }
+                bf[((ks * 4 + nt) * 2 + 0) * 32 + ln] = make_uint2(hw[0], hw[1]);
+                bf[((ks * 4 + nt) * 2 + 1) * 32 + ln] = make_uint2(lw[0], lw[1]);
             }
         }
         __syncthreads();
