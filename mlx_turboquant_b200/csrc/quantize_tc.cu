@@ -48,7 +48,13 @@ constexpr int A_STAGES_MAX = 3, ACC_STAGES = 4;
 constexpr int N_NORM = 128;                      // threads that read the rows back for the norms
 // epilogue warps: 16, or 8 with the QJL sketch on (its 32 running projections per thread need the registers); then the
 // MMA warp, the norm warps, the TMA warp
-__host__ __device__ constexpr int epi_warps(bool qjl) { return qjl ? 8 : 16; }
+// (twelve warps in three groups were measured too: the compiler then has 96 registers per thread, spills 300 bytes, and the
+// launch takes the same time - the sketch variant is bound by its instruction count, some 30-37 per coordinate, not by how
+// many warps issue them)
+#ifndef TQ_QJL_EPI_WARPS
+#define TQ_QJL_EPI_WARPS 8
+#endif
+__host__ __device__ constexpr int epi_warps(bool qjl) { return qjl ? TQ_QJL_EPI_WARPS : 16; }
 __host__ __device__ constexpr int n_threads(bool qjl) { return epi_warps(qjl) * 32 + 32 + N_NORM + 32; }     // 704 / 448
 constexpr int BIN_REP = 8;                       // copies of every lookup-table entry (lane & 7 picks one): fewer bank conflicts
 constexpr int KBLK_BYTES = TM * 128;             // one 64-column K-block of a 128-row operand: 16 KB
@@ -68,9 +74,9 @@ constexpr int OFF_BND = OFF_PT + DMAX * QM * 4;            // 2 x 16 floats raw 
 constexpr int OFF_NSQ = OFF_BND + 256;                     // A_STAGES_MAX x 2 x 128 floats: partial sums of squares
 constexpr int OFF_BAR = OFF_NSQ + A_STAGES_MAX * 2 * TM * 4;   // mbarriers: 3 full, 3 a_free, 3 norm-ready, 4 acc_full, 4 acc_free
 constexpr int OFF_MISC = OFF_BAR + 24 * 8;                 // tmem base, abort flag
-constexpr int SK_LD = 48;                                  // QJL: bytes per staged row of 16 fp16 residuals (32 + padding: the eight rows of an 8 x 8 matrix land in distinct banks)
+constexpr int SK_LD = 32;                                  // QJL: bytes per staged row of 16 fp16 residuals; the two 16-byte halves of rows 4-7 (mod 8) swap places, so the eight rows of an 8 x 8 matrix land in distinct banks
 constexpr int OFF_SKETCH = (OFF_MISC + 64 + 127) / 128 * 128;   // QJL: one 32-row staging buffer per epilogue warp
-constexpr int SMEM_BYTES = OFF_SKETCH + 8 * 32 * SK_LD;
+constexpr int SMEM_BYTES = OFF_SKETCH + TQ_QJL_EPI_WARPS * 32 * SK_LD;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared-memory plan");
 
 struct Params {
@@ -340,9 +346,9 @@ __device__ __forceinline__ void sketch16(const uint32_t* v, uint32_t g0, uint32_
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             const uint32_t code = (((i + u) < 8 ? g0 : g1) >> (BITS * ((i + u) & 7))) & ((1u << BITS) - 1u);
-            const float e = fmaf(__uint_as_float(v[i + u]), rinv, -cent[code]);
+            const float e = fmaf(__uint_as_float(v[i + u]), rinv, -cent[code]);       // 2^8 times the residual (rinv and the centroids carry the factor)
             ee = fmaf(e, e, ee);
-            e2[u] = e * 256.f;
+            e2[u] = e;
         }
         const __half2 h = __floats2half2_rn(e2[0], e2[1]);
         const float2 hf = __half22float2(h);
@@ -350,17 +356,18 @@ __device__ __forceinline__ void sketch16(const uint32_t* v, uint32_t g0, uint32_
         hi[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
         lo[i >> 1] = *reinterpret_cast<const uint32_t*>(&l);
     }
+    const uint32_t swz = uint32_t((sk.lane >> 2) & 1) * 16;                                            // rows 4-7 (mod 8): halves swapped
     const uint32_t row = sk.stage + uint32_t(sk.lane) * SK_LD;
-    const uint32_t frag = sk.stage + uint32_t(sk.lane & 15) * SK_LD + uint32_t(sk.lane >> 4) * 16;     // ldmatrix row of this lane (second half: + 16 rows)
+    const uint32_t frag = sk.stage + uint32_t(sk.lane & 15) * SK_LD + ((uint32_t(sk.lane >> 4) * 16) ^ swz);   // ldmatrix row of this lane (second half: + 16 rows)
     uint32_t ah[2][4], al[2][4];
-    sk_sts128(row, hi[0], hi[1], hi[2], hi[3]);
-    sk_sts128(row + 16, hi[4], hi[5], hi[6], hi[7]);
+    sk_sts128(row + swz, hi[0], hi[1], hi[2], hi[3]);
+    sk_sts128(row + (16 ^ swz), hi[4], hi[5], hi[6], hi[7]);
     __syncwarp();
     sk_ldsm(ah[0], frag);
     sk_ldsm(ah[1], frag + 16 * SK_LD);
     __syncwarp();
-    sk_sts128(row, lo[0], lo[1], lo[2], lo[3]);
-    sk_sts128(row + 16, lo[4], lo[5], lo[6], lo[7]);
+    sk_sts128(row + swz, lo[0], lo[1], lo[2], lo[3]);
+    sk_sts128(row + (16 ^ swz), lo[4], lo[5], lo[6], lo[7]);
     __syncwarp();
     sk_ldsm(al[0], frag);
     sk_ldsm(al[1], frag + 16 * SK_LD);
@@ -443,7 +450,7 @@ __device__ __forceinline__ void quantize_part(uint32_t t_row, int col0, int nch_
                 quantize16<BITS>(vc, rc, sb, raw, g0, g1);
                 put_group<BITS, NW>(w, 2 * c, g0);
                 put_group<BITS, NW>(w, 2 * c + 1, g1);
-                if constexpr (QJL) sketch16<BITS>(vc, g0, g1, rc.rinv, cent, col0 + (c0 + c) * 16, sk, ee);
+                if constexpr (QJL) sketch16<BITS>(vc, g0, g1, rc.rinv * 256.f, cent, col0 + (c0 + c) * 16, sk, ee);
             }
         }
         if (live) store_words<NW>(dst + c0 * 2 * BITS, w, nc * 2 * BITS);
@@ -460,7 +467,7 @@ __device__ __forceinline__ void quantize_part(uint32_t t_row, int col0, int nch_
 //     two groups of four that take alternate tiles, one accumulator per tile, two stages per group.
 template <bool QJL, bool SPLITACC> struct EpiShape {
     static constexpr int EW = epi_warps(QJL), NT = n_threads(QJL), N_EPI = EW * 32;
-    static constexpr int GROUPS = SPLITACC ? 1 : 2;                                 // groups of warps that take tiles in turn
+    static constexpr int GROUPS = SPLITACC ? 1 : QJL ? epi_warps(true) / 4 : 2;     // groups of warps that take tiles in turn
     static constexpr int WPG = EW / GROUPS;                                         // warps per group: 4 row quadrants x SPLIT shares of the columns
     static constexpr int SPLIT = WPG / 4;
     static constexpr int STAGES = SPLITACC ? 2 : 4;                                 // accumulator stages
@@ -541,7 +548,7 @@ __device__ __forceinline__ void epilogue_loop(const EpiCtx& e) {
             if (QJL) {
                 if (nrm == 0.f) zb = 0xffffffffu;               // zero row: the reference's residual is exactly 0, and 0 >= 0
                 p.qjl_bits[orow] = zb;
-                p.qjl_gamma[orow] = nrm * sqrtf(ee);            // |x - dequant(x)| = |x| |y_n - c| (the rotation is orthogonal)
+                p.qjl_gamma[orow] = nrm * sqrtf(ee) * (1.f / 256.f);   // |x - dequant(x)| = |x| |y_n - c| (the rotation is orthogonal); ee sums 2^16 times the squares
             }
         }
     }
@@ -634,7 +641,7 @@ __global__ void __launch_bounds__(n_threads(QJL), 1) quantize_tc_kernel(Params p
                 if (src != nullptr && bits > 0 && i < (1 << bits) - 1) val = src[i];
             } else if (QJL) {
                 const float* src = (which & 1) ? p.cent_lo : p.cent_hi;
-                if (src != nullptr && bits > 0 && i < (1 << bits)) val = src[i];
+                if (src != nullptr && bits > 0 && i < (1 << bits)) val = src[i] * 256.f;     // (the sketch works on 2^8 times the residual)
             }
             raw[tid] = val;
         }
