@@ -47,6 +47,27 @@ def test_version_and_argument_errors_without_gpu(built):
         built.check(-2)
 
 
+def test_decode_workspace_sizes_without_gpu(built):
+    """Pure host arithmetic (the split plans and the streaming kernel's layout for 148 SMs when no device answers): the
+    scratch for a call the streaming kernel can take holds its prepared queries and partials on top of the other kernels'
+    need; sizes it cannot take (other head dims, no packed tokens) are unaffected; the knobs are accepted."""
+    lib = built.lib()
+    assert lib.tq_decode_kernel_choice(None) == -1
+    c3 = lib.tq_decode_workspace_bytes(16, 32, 32, 96, 7936, 256)        # batch 16, MHA, d = 96
+    d64 = lib.tq_decode_workspace_bytes(16, 32, 32, 64, 7936, 256)
+    assert c3 > d64 > 0
+    # queries: 512 heads x (2 x 96 + 32) halves; partials: 512 lanes x (6 + 4) slots x (96 + 36) floats
+    assert c3 >= 65536 + 512 * 224 * 2 + 512 * 10 * 132 * 4
+    assert 0 < lib.tq_decode_workspace_bytes(16, 32, 32, 96, 0, 256) < c3                 # only uncompressed tokens: no streaming layout
+    assert lib.tq_decode_workspace_bytes(0, 32, 32, 96, 7936, 256) == 0
+    for key, good, bad in ((b"decode_stream", 0, 2), (b"decode_stream_min_run", 8, 0), (b"decode_stream_max_parts", 64, 65)):
+        assert lib.tq_set_tuning(key, bad) == -1
+        assert lib.tq_set_tuning(key, good) == 0
+    assert lib.tq_decode_workspace_bytes(16, 32, 32, 96, 7936, 256) == c3    # (the knobs steer the choice, not the size)
+    assert lib.tq_set_tuning(b"decode_stream", 1) == 0 and lib.tq_set_tuning(b"decode_stream_min_run", 24) == 0
+    assert lib.tq_set_tuning(b"decode_stream_max_parts", 40) == 0
+
+
 def test_missing_library_fails_loudly(monkeypatch, built):
     monkeypatch.setattr(built, "_lib", None)
     monkeypatch.setattr(built, "LIB_PATH", ROOT / "does_not_exist.so")
