@@ -273,8 +273,8 @@ __global__ void __launch_bounds__(NT, 1) decode_stream_kernel(DecodeParams p) {
             uint32_t bq[D / 16][2];
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
-                bq[ks][0] = g < heads_here ? *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * t) : 0u;
-                bq[ks][1] = g < heads_here ? *reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * t + 8) : 0u;
+                bq[ks][0] = g < heads_here ? __ldcg(reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * t)) : 0u;
+                bq[ks][1] = g < heads_here ? __ldcg(reinterpret_cast<const uint32_t*>(qh + ks * 16 + 2 * t + 8)) : 0u;
             }
             WarpAcc<D, 0> sd;
             sd.init();
@@ -396,8 +396,9 @@ __global__ void __launch_bounds__(NT, 1) decode_stream_kernel(DecodeParams p) {
             for (int ks = 0; ks < D / 16; ++ks) {
                 // this thread's bytes 2ks, 2ks+1 of a key row: coordinates 2 * kb .. 2 * kb + 3
                 const int kb = D == 128 ? 16 * t + 2 * ks : 16 * (ks >> 1) + 4 * t + 2 * (ks & 1);
-                bq[ks][0] = g < heads_here ? __ldg(reinterpret_cast<const uint32_t*>(qh + 2 * kb)) : 0u;
-                bq[ks][1] = g < heads_here ? __ldg(reinterpret_cast<const uint32_t*>(qh + 2 * kb + 2)) : 0u;
+                // (written by the launch before this one while this grid may already have been resident: read at L2, never through a non-coherent path)
+                bq[ks][0] = g < heads_here ? __ldcg(reinterpret_cast<const uint32_t*>(qh + 2 * kb)) : 0u;
+                bq[ks][1] = g < heads_here ? __ldcg(reinterpret_cast<const uint32_t*>(qh + 2 * kb + 2)) : 0u;
             }
             if (QJL) {
                 // k slot (ks, register hh, half e) of lane t stands for sketch row 4t + 2ks + hh + 16e: the halves of an
@@ -409,8 +410,9 @@ __global__ void __launch_bounds__(NT, 1) decode_stream_kernel(DecodeParams p) {
                         const int pi = 4 * t + 2 * ks + hh;
                         bu[ks][hh] = 0u;
                         if (g < heads_here) {
-                            const __half2 u2 = __halves2half2(qh[2 * D + pi], qh[2 * D + pi + 16]);
-                            bu[ks][hh] = *reinterpret_cast<const uint32_t*>(&u2);
+                            const unsigned short lo16 = __ldcg(reinterpret_cast<const unsigned short*>(qh + 2 * D + pi));
+                            const unsigned short hi16 = __ldcg(reinterpret_cast<const unsigned short*>(qh + 2 * D + pi + 16));
+                            bu[ks][hh] = uint32_t(lo16) | (uint32_t(hi16) << 16);
                         }
                     }
             }
