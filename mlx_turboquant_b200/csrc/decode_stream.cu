@@ -49,10 +49,10 @@ using dd::TABLES_MAGIC;
 #define TQ_STREAM_WARPS 16
 #endif
 constexpr int NW = TQ_STREAM_WARPS, NT = NW * 32;
-#ifndef TQ_STREAM_STAGES
-#define TQ_STREAM_STAGES 4
-#endif
-constexpr int NS_WANTED = TQ_STREAM_STAGES;    // ring stages per warp (d = 128: at most 4 fit)
+// Ring stages per warp and copies of the tile loop's body.  The depth of the ring makes no difference to the time (2, 3, 4,
+// 6 measured: the wait finds its stage complete); with as many copies of the body as stages the stage offsets fold into the
+// instructions, which pays at d = 128 (3 %) and not at d = 96.
+template <int D> struct Ring { static constexpr int NS = D == 128 ? 2 : 4, UNROLL = D == 128 ? 2 : 1; };
 constexpr int QM = 32;                         // sketch rows (one 32-bit sign word per token)
 constexpr float QJL_C = 1.2533141373155003f;   // sqrt(pi / 2), qjl.py:91-92
 constexpr uint32_t WAIT_LIMIT = 4u << 20;
@@ -63,7 +63,7 @@ template <int D, bool QJL> struct Plan {
     static constexpr uint32_t KT = TILE * D / 2, VT = TILE * D / 4, SC = TILE * 4;   // bytes per tile: keys, values, one scalar array
     static constexpr int NSC = QJL ? 6 : 2;
     static constexpr uint32_t O_V = KT, O_KN = KT + VT, O_VN = O_KN + SC, O_KB = O_VN + SC, O_KG = O_KB + SC, O_VB = O_KG + SC, O_VG = O_VB + SC;
-    static constexpr int NS = (D > 96 && NS_WANTED > 4) ? 4 : NS_WANTED;
+    static constexpr int NS = Ring<D>::NS;
     static constexpr uint32_t STAGE = KT + VT + NSC * SC;
     static constexpr uint32_t RING = NS * STAGE;
     static constexpr uint32_t DSTAGE = 2u * TILE * stage_ld<D>() * 2u;               // fp16 keys + values of one uncompressed tile
@@ -450,7 +450,7 @@ __global__ void __launch_bounds__(NT, 1) decode_stream_kernel(DecodeParams p) {
             }
         };
 
-#pragma unroll 1
+#pragma unroll (Ring<D>::UNROLL)
         for (int n = 0; n < n_my; ++n) {
             const int stage = n % NS;
             const uint32_t sa = my_area + uint32_t(stage) * P::STAGE;
