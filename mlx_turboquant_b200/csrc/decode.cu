@@ -968,7 +968,7 @@ size_t decode_workspace_bytes_split_kernels(int batch, int n_q_heads, int n_kv_h
 
 extern "C" size_t tq_decode_workspace_bytes(int batch, int n_q_heads, int n_kv_heads, int d, int64_t c_len,
                                             int64_t dense_len) {
-    const size_t a = decode_workspace_bytes_split_kernels(batch, n_q_heads, n_kv_heads, d, c_len, dense_len), b = 0;
+    const size_t a = decode_workspace_bytes_split_kernels(batch, n_q_heads, n_kv_heads, d, c_len, dense_len);
     if (a == 0) return 0;
     size_t c = 0;
     if ((d == 96 || d == 128) && c_len > 0) {      // the streaming kernel's layout: counters' area, prepared queries, partials
@@ -977,7 +977,7 @@ extern "C" size_t tq_decode_workspace_bytes(int batch, int n_q_heads, int n_kv_h
         if (sp.npp + sp.nd <= 64)
             c = align_up(std::max(size_t(batch) * n_kv_heads * hg * sizeof(int), COUNTER_AREA), 256) + sp.q16_bytes + sp.part_bytes;
     }
-    return std::max(a, std::max(b, c));
+    return std::max(a, c);
 }
 
 extern "C" int tq_decode_step(const tq_decode_args* a, const void* k_new, const void* v_new, void* stream) {
